@@ -1,0 +1,391 @@
+/*
+ * TEST INFRASTRUCTURE.  CPU oracle for the fused row-wise hot path: a plain-C restatement of the reference's
+ * CPU definition, written to be read next to the reference lines each function cites.  Build with
+ * -ffp-contract=off and without -march=native: several results depend on a multiply and an add staying two
+ * roundings (fn/quant/decode.h:5-6 makes the same requirement of the reference's own decoders).
+ *
+ * Pinning.  The quantisers and decoders are checked bit-for-bit against the reference's own C
+ * (ggml/src/ggml-quants.c compiled from the reference tree into oracle/_ref, see oracle/Makefile) and against
+ * the golden vectors that build produced (tests/golden).  rms_norm, swiglu and rope have no CPU source in the
+ * reference tree (its ggml carries no CPU backend): they follow the lines cited on each function and are
+ * pinned at tolerance level by FP64 restatements of the reference's own tests, not bit-for-bit.
+ */
+#include "fnb_oracle.h"
+
+#include <math.h>
+#include <string.h>
+
+#include "fnb_exact_math.h"
+
+static int g_use_libm = 0;
+void fnbo_use_libm(int on) { g_use_libm = on; }
+
+float fnbo_expf_exact(float x) { return fnbo_expf(x); }
+float fnbo_sinf_exact(float x) { return fnbo_sinf(x); }
+float fnbo_cosf_exact(float x) { return fnbo_cosf(x); }
+
+static inline float o_expf(float x) { return g_use_libm ? expf(x) : fnbo_expf(x); }
+static inline float o_sinf(float x) { return g_use_libm ? sinf(x) : fnbo_sinf(x); }
+static inline float o_cosf(float x) { return g_use_libm ? cosf(x) : fnbo_cosf(x); }
+
+/* ---- FP16 <-> FP32: IEEE round-to-nearest-even; NaN -> 0x7E00 with the sign, as
+ * ggml/src/ggml-impl.h:412-438 (ggml_compute_fp32_to_fp16) produces; widening is exact (:391-410). ---- */
+uint16_t fnbo_f32_to_f16(float f) {
+    const uint32_t x = fnbo_bits_f32(f);
+    const uint32_t sign = (x >> 16) & 0x8000u;
+    const uint32_t ax = x & 0x7fffffffu;
+    if (ax > 0x7f800000u) return (uint16_t) (sign | 0x7e00u);
+    if (ax >= 0x477ff000u) return (uint16_t) (sign | 0x7c00u); /* rounds to 2^16 or beyond: inf */
+    if (ax < 0x33000001u) return (uint16_t) sign;              /* <= 2^-25: ties-to-even gives zero */
+    const int32_t e = (int32_t) (ax >> 23) - 127;
+    uint32_t man = (ax & 0x7fffffu) | 0x800000u;
+    uint32_t shift, base;
+    if (e < -14) { /* FP16 subnormal: value = man * 2^(e-23), unit 2^-24 */
+        shift = (uint32_t) (-e - 1); /* 23 - (e + 24) */
+        base = 0;
+    } else {
+        shift = 13;
+        base = (uint32_t) (e + 15) << 10;
+        man &= 0x7fffffu;
+    }
+    uint32_t h = man >> shift;
+    const uint32_t rem = man & ((1u << shift) - 1u);
+    const uint32_t half = 1u << (shift - 1);
+    h += base;
+    if (rem > half || (rem == half && (h & 1u))) ++h;
+    return (uint16_t) (sign | h);
+}
+
+float fnbo_f16_to_f32(uint16_t h) {
+    const uint32_t sign = (uint32_t) (h & 0x8000u) << 16;
+    const uint32_t ex = (h >> 10) & 0x1fu;
+    uint32_t man = h & 0x3ffu;
+    if (ex == 0) {
+        if (man == 0) return fnbo_f32_bits(sign);
+        const float v = (float) man * 0x1p-24f; /* exact */
+        return fnbo_f32_bits(fnbo_bits_f32(v) | sign);
+    }
+    if (ex == 31) return fnbo_f32_bits(sign | 0x7f800000u | (man << 13));
+    return fnbo_f32_bits(sign | ((ex + 112u) << 23) | (man << 13));
+}
+
+/* C's (int8_t) of a rounded float goes through a 32-bit convert on x86-64: out of range or NaN gives
+ * INT32_MIN, whose low byte is 0.  Stated explicitly so the rule is the same on every target. */
+static inline int8_t o_to_i8(float r) {
+    if (!(r > -2147483904.0f && r < 2147483648.0f)) return 0;
+    return (int8_t) (uint8_t) ((uint32_t) (int32_t) r & 0xffu);
+}
+
+/* ---- Q8_0: ggml/src/ggml-quants.c:274-297 (quantize_row_q8_0_ref) ---- */
+void fnbo_quantize_row_q8_0(const float * x, void * yv, int64_t k) {
+    uint8_t * y = (uint8_t *) yv;
+    for (int64_t b = 0; b < k / 32; ++b) {
+        const float * v = x + 32 * b;
+        float amax = 0.0f;
+        for (int j = 0; j < 32; ++j) {
+            const float a = fabsf(v[j]);
+            amax = amax > a ? amax : a;
+        }
+        const float d = amax / 127.0f;
+        const float id = d ? 1.0f / d : 0.0f;
+        const uint16_t dh = fnbo_f32_to_f16(d);
+        memcpy(y + 34 * b, &dh, 2);
+        for (int j = 0; j < 32; ++j) {
+            ((int8_t *) y)[34 * b + 2 + j] = o_to_i8(roundf(v[j] * id));
+        }
+    }
+}
+
+/* ---- Q8_1: ggml/src/ggml-quants.c:300-333 (quantize_row_q8_1_ref); s = fp16(sum * d), d unrounded ---- */
+void fnbo_quantize_row_q8_1(const float * x, void * yv, int64_t k) {
+    uint8_t * y = (uint8_t *) yv;
+    for (int64_t b = 0; b < k / 32; ++b) {
+        const float * v = x + 32 * b;
+        float amax = 0.0f;
+        for (int j = 0; j < 32; ++j) {
+            const float a = fabsf(v[j]);
+            amax = amax > a ? amax : a;
+        }
+        const float d = amax / 127.0f;
+        const float id = d ? 1.0f / d : 0.0f;
+        const uint16_t dh = fnbo_f32_to_f16(d);
+        int sum = 0;
+        for (int j = 0; j < 32; ++j) {
+            const int8_t q = o_to_i8(roundf(v[j] * id));
+            ((int8_t *) y)[36 * b + 4 + j] = q;
+            sum += q;
+        }
+        const uint16_t sh = fnbo_f32_to_f16((float) sum * d);
+        memcpy(y + 36 * b, &dh, 2);
+        memcpy(y + 36 * b + 2, &sh, 2);
+    }
+}
+
+/* ---- ggml/src/ggml-quants.c:551-565 ---- */
+void fnbo_dequantize_row_q8_0(const void * xv, float * y, int64_t k) {
+    const uint8_t * x = (const uint8_t *) xv;
+    for (int64_t b = 0; b < k / 32; ++b) {
+        uint16_t dh;
+        memcpy(&dh, x + 34 * b, 2);
+        const float d = fnbo_f16_to_f32(dh);
+        for (int j = 0; j < 32; ++j) y[32 * b + j] = (float) ((const int8_t *) x)[34 * b + 2 + j] * d;
+    }
+}
+
+/* ---- Q4_K: ggml/src/ggml-quants.c:1527-1549 with the 6-bit scale/min unpack of :878-886; the same rule is
+ * stated independently at fn/quant/decode.cpp:88-106.  y = d*sc*q - dmin*m, product then subtract. ---- */
+static inline void o_scale_min_k4(int j, const uint8_t * s, uint8_t * sc, uint8_t * m) {
+    if (j < 4) {
+        *sc = s[j] & 63;
+        *m = s[j + 4] & 63;
+    } else {
+        *sc = (uint8_t) ((s[j + 4] & 0x0f) | ((s[j - 4] >> 6) << 4));
+        *m = (uint8_t) ((s[j + 4] >> 4) | ((s[j] >> 6) << 4));
+    }
+}
+
+void fnbo_dequantize_row_q4_k(const void * xv, float * y, int64_t k) {
+    const uint8_t * x = (const uint8_t *) xv;
+    for (int64_t b = 0; b < k / 256; ++b, x += 144) {
+        uint16_t dh, mh;
+        memcpy(&dh, x, 2);
+        memcpy(&mh, x + 2, 2);
+        const float d = fnbo_f16_to_f32(dh), dmin = fnbo_f16_to_f32(mh);
+        const uint8_t * scales = x + 4;
+        const uint8_t * q = x + 16;
+        for (int g = 0; g < 4; ++g) {
+            uint8_t sc, m;
+            o_scale_min_k4(2 * g, scales, &sc, &m);
+            const float d1 = d * (float) sc, m1 = dmin * (float) m;
+            o_scale_min_k4(2 * g + 1, scales, &sc, &m);
+            const float d2 = d * (float) sc, m2 = dmin * (float) m;
+            for (int l = 0; l < 32; ++l) *y++ = d1 * (float) (q[l] & 0x0f) - m1;
+            for (int l = 0; l < 32; ++l) *y++ = d2 * (float) (q[l] >> 4) - m2;
+            q += 32;
+        }
+    }
+}
+
+/* ---- IQ3_XXS: ggml/src/ggml-quants.c:2573-2601; codebook ggml/src/ggml-common.h:1062, sign rule :554-567
+ * (7 stored sign bits, the eighth is their parity); independently at fn/quant/decode.cpp:224-242. ---- */
+static const uint16_t o_grid_packed[256] = {
+#include "../fnfl_v100_b200/csrc/iq3xxs_grid_packed.inc"
+};
+
+static inline float o_grid_mag(unsigned level) { return level == 7 ? 62.0f : (float) (4 + 8 * level); }
+
+void fnbo_dequantize_row_iq3_xxs(const void * xv, float * y, int64_t k) {
+    const uint8_t * x = (const uint8_t *) xv;
+    for (int64_t b = 0; b < k / 256; ++b, x += 98) {
+        uint16_t dh;
+        memcpy(&dh, x, 2);
+        const float d = fnbo_f16_to_f32(dh);
+        const uint8_t * qs = x + 2;
+        const uint8_t * sas = x + 2 + 64;
+        for (int ib = 0; ib < 8; ++ib) {
+            uint32_t aux;
+            memcpy(&aux, sas + 4 * ib, 4);
+            const float db = d * (0.5f + (float) (aux >> 28)) * 0.5f;
+            for (int l = 0; l < 4; ++l) {
+                const unsigned s7 = (aux >> (7 * l)) & 127u;
+                const unsigned signs = s7 | ((unsigned) (__builtin_popcount(s7) & 1) << 7);
+                for (int h = 0; h < 2; ++h) {
+                    const unsigned code = o_grid_packed[qs[8 * ib + 2 * l + h]];
+                    for (int j = 0; j < 4; ++j) {
+                        const float g = o_grid_mag((code >> (3 * j)) & 7u);
+                        const float sg = (signs >> (4 * h + j)) & 1u ? -1.0f : 1.0f;
+                        y[4 * h + j] = db * g * sg;
+                    }
+                }
+                y += 8;
+            }
+        }
+    }
+}
+
+/* ---- get_rows on a quantised table is the row decoder applied to row ids[t] (the ggml op's definition);
+ * the bad-id rule is the reference kernel's: fn/kernels/embed/embed.cu:43-48, embed.h:15-17. ---- */
+void fnbo_get_rows_q4_k(const void * table, int64_t n_vocab, const int32_t * ids, float * out, uint32_t * err,
+                        int64_t rows, int32_t cols) {
+    const size_t rb = (size_t) (cols / 256) * 144;
+    for (int64_t t = 0; t < rows; ++t) {
+        if (ids[t] < 0 || ids[t] >= n_vocab) {
+            if (err) *err |= FNBO_ERR_TOKEN;
+            continue;
+        }
+        fnbo_dequantize_row_q4_k((const uint8_t *) table + rb * (size_t) ids[t], out + (size_t) t * cols, cols);
+    }
+}
+
+void fnbo_get_rows_iq3_xxs(const void * table, int64_t n_vocab, const int32_t * ids, float * out, uint32_t * err,
+                           int64_t rows, int32_t cols) {
+    const size_t rb = (size_t) (cols / 256) * 98;
+    for (int64_t t = 0; t < rows; ++t) {
+        if (ids[t] < 0 || ids[t] >= n_vocab) {
+            if (err) *err |= FNBO_ERR_TOKEN;
+            continue;
+        }
+        fnbo_dequantize_row_iq3_xxs((const uint8_t *) table + rb * (size_t) ids[t], out + (size_t) t * cols, cols);
+    }
+}
+
+/* ---- RMSNorm.  The reference mirrors the graph "rms_norm(x) then mul by the weight"
+ * (fn/kernels/draft/draft.h:31; fn/kernels/qsa/attend.h:14-15,33): scale = 1/sqrtf(mean + eps),
+ * y = (x * scale) * w.  The CPU op it mirrors (ggml's CPU backend, not in the reference tree) sums the F32
+ * squares into a double in element order and narrows the mean once; that published rule is restated here.
+ * FP64 statements of the same norm: fn/kernels/qsa/qa2_test.cpp:244-252,
+ * fn/kernels/draft/draft_prompt_test.cpp:66-75. ---- */
+void fnbo_rms_norm_f32(const float * x, const float * w, float eps, float * y, int64_t rows, int32_t cols) {
+    for (int64_t r = 0; r < rows; ++r) {
+        const float * xr = x + (size_t) r * cols;
+        float * yr = y + (size_t) r * cols;
+        double sum = 0.0;
+        for (int i = 0; i < cols; ++i) sum += (double) (xr[i] * xr[i]);
+        const float mean = (float) (sum / cols);
+        const float scale = 1.0f / sqrtf(mean + eps);
+        if (w) {
+            for (int i = 0; i < cols; ++i) yr[i] = (xr[i] * scale) * w[i];
+        } else {
+            for (int i = 0; i < cols; ++i) yr[i] = xr[i] * scale;
+        }
+    }
+}
+
+/* ---- SwiGLU: silu(g) * u with silu(g) = g / (1 + expf(-g)) in F32, the form every in-tree statement uses
+ * (fn/kernels/experts/experts_dev.cuh:197, fn/kernels/dense/dense.cu:148,
+ * fn/kernels/experts/cpu_iq_avx2.cpp:442), then the Q8_1 row quantiser over the product. ---- */
+static inline float o_swiglu(float g, float u) { return (g / (1.0f + o_expf(-g))) * u; }
+
+void fnbo_swiglu_q8_1(const float * gate, const float * up, void * out, float * f32_out, int64_t rows,
+                      int32_t cols) {
+    float tmp[32];
+    const int64_t nb = rows * (cols / 32);
+    for (int64_t b = 0; b < nb; ++b) {
+        for (int j = 0; j < 32; ++j) tmp[j] = o_swiglu(gate[32 * b + j], up[32 * b + j]);
+        if (f32_out) memcpy(f32_out + 32 * b, tmp, sizeof tmp);
+        fnbo_quantize_row_q8_1(tmp, (uint8_t *) out + 36 * b, 32);
+    }
+}
+
+/* theta_scale = powf(freq_base, -2/n_rot), computed once on the host: fn/kernels/qsa/attend.cu:830-832 */
+float fnbo_theta_scale(float freq_base, int32_t n_rot) { return powf(freq_base, -2.0f / (float) n_rot); }
+
+/* ---- per-head norm, NeoX partial RoPE, Q8_0 append.
+ * Norm and rope: fn/kernels/qsa/attend.h:19-23 (semantics), attend.cu:153-197 (device form),
+ * fn/kernels/qsa/qa2_test.cpp:230-259 (theta as an F32 product chain; pairs (i, i + n_rot/2);
+ * x0 c - x1 s, x0 s + x1 c).  Text rows: every rope plane is the position (fn/kernels/qsa/imrope.cuh:7-9),
+ * which is plain NeoX.  K = rope(norm(k)), V raw, both appended at the row's cell:
+ * fn/kernels/qsa/qsa_prompt_attn.cu:77-122.  The cell format here is ggml Q8_0. ---- */
+static void o_head(const float * x, const float * w, float eps, int hd, int n_rot, const float * cs, float * y) {
+    if (w) {
+        fnbo_rms_norm_f32(x, w, eps, y, 1, hd);
+    } else {
+        memcpy(y, x, (size_t) hd * sizeof(float));
+    }
+    const int half = n_rot / 2;
+    for (int i = 0; i < half; ++i) {
+        const float c = cs[2 * i], s = cs[2 * i + 1];
+        const float x0 = y[i], x1 = y[i + half];
+        y[i] = x0 * c - x1 * s;
+        y[i + half] = x0 * s + x1 * c;
+    }
+}
+
+void fnbo_rope_neox_q8_0_append(const fnbo_rope_kv_args * a) {
+    const int hd = a->head_dim, half = a->n_rot / 2;
+    const size_t row_blocks = (size_t) hd / 32;
+    float cs[512];
+    float tmp[1024];
+    for (int64_t t = 0; t < a->rows; ++t) {
+        const int64_t slot = a->slots ? a->slots[t] : a->pos[t];
+        if (slot < 0 || slot >= a->cache_slots) {
+            if (a->err) *a->err |= FNBO_ERR_SLOT;
+            continue;
+        }
+        float theta = (float) a->pos[t];
+        for (int i = 0; i < half; ++i) {
+            cs[2 * i] = o_cosf(theta);
+            cs[2 * i + 1] = o_sinf(theta);
+            theta *= a->theta_scale;
+        }
+        for (int h = 0; h < a->n_q_heads; ++h) {
+            const size_t off = ((size_t) t * a->n_q_heads + h) * hd;
+            o_head(a->q + off, a->q_norm_w, a->eps, hd, a->n_rot, cs, a->q_out + off);
+        }
+        for (int h = 0; h < a->n_kv_heads; ++h) {
+            const size_t off = ((size_t) t * a->n_kv_heads + h) * hd;
+            const size_t cell = ((size_t) slot * a->n_kv_heads + h) * row_blocks * 34;
+            o_head(a->k + off, a->k_norm_w, a->eps, hd, a->n_rot, cs, tmp);
+            if (a->k_f32) memcpy(a->k_f32 + off, tmp, (size_t) hd * sizeof(float));
+            fnbo_quantize_row_q8_0(tmp, (uint8_t *) a->k_cache + cell, hd);
+            fnbo_quantize_row_q8_0(a->v + off, (uint8_t *) a->v_cache + cell, hd);
+        }
+    }
+}
+
+/* ---- the reference's own activation format: fn/kernels/act/act.h:8-15, fn/quant/act_ref.cpp:8-30.
+ * d = amax/127, id = 127/amax (0 when amax is 0), q = nearest-even(x id) clamped to +-127, NaN -> 0,
+ * s = d * (float) sum q. ---- */
+void fnbo_act_quantize(const float * x, int64_t rows, int32_t k, int8_t * codes, float * scales) {
+    const int64_t nb = rows * (k / 32);
+    for (int64_t b = 0; b < nb; ++b) {
+        const float * v = x + 32 * b;
+        float amax = 0.0f;
+        for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(v[j]));
+        const float d = amax / 127.0f;
+        const float id = amax > 0.0f ? 127.0f / amax : 0.0f;
+        int32_t sum = 0;
+        for (int j = 0; j < 32; ++j) {
+            const float e = v[j] * id;
+            int32_t q = 0;
+            if (e == e) {
+                float r = nearbyintf(e);
+                r = r < -127.0f ? -127.0f : r > 127.0f ? 127.0f : r;
+                q = (int32_t) r;
+            }
+            codes[32 * b + j] = (int8_t) q;
+            sum += q;
+        }
+        scales[2 * b] = d;
+        scales[2 * b + 1] = d * (float) sum;
+    }
+}
+
+/* fn/kernels/experts/experts.cu:716-729 with experts_dev.cuh:196-213: the GLU, then the act format */
+void fnbo_swiglu_act(const float * gate, const float * up, int8_t * codes, float * scales, float * f32_out,
+                     int64_t rows, int32_t cols) {
+    float tmp[32];
+    const int64_t nb = rows * (cols / 32);
+    for (int64_t b = 0; b < nb; ++b) {
+        for (int j = 0; j < 32; ++j) tmp[j] = o_swiglu(gate[32 * b + j], up[32 * b + j]);
+        if (f32_out) memcpy(f32_out + 32 * b, tmp, sizeof tmp);
+        fnbo_act_quantize(tmp, 1, 32, codes + 32 * b, scales + 2 * b);
+    }
+}
+
+/* ---- KV8: fn/kernels/qsa/kv_q8.cuh:29-52, fn/quant/kv_q8_ref.cpp:72-87.  Per 64 values:
+ * scale = fp16_rn(amax/127), s its F32 value, code = clamp(nearest-even(x / s), +-127), 0 when s is 0. ---- */
+void fnbo_kv8_quantize(const float * x, int64_t n, int8_t * codes, uint16_t * scales) {
+    for (int64_t g = 0; g < n / 64; ++g) {
+        const float * v = x + 64 * g;
+        float amax = 0.0f;
+        for (int j = 0; j < 64; ++j) amax = fmaxf(amax, fabsf(v[j]));
+        uint32_t hb = fnbo_bits_f32(amax / 127.0f);
+        uint16_t h;
+        if ((hb & 0x7fffffffu) > 0x7f800000u) {
+            h = (uint16_t) (((hb >> 16) & 0x8000u) | 0x7e00u);
+        } else {
+            h = fnbo_f32_to_f16(amax / 127.0f);
+        }
+        scales[g] = h;
+        const float s = fnbo_f16_to_f32(h);
+        for (int j = 0; j < 64; ++j) {
+            int32_t q = 0;
+            if (s > 0.0f) {
+                const float r = nearbyintf(v[j] / s);
+                q = r < -127.0f ? -127 : r > 127.0f ? 127 : (int32_t) r;
+            }
+            codes[64 * g + j] = (int8_t) q;
+        }
+    }
+}

@@ -1,0 +1,84 @@
+/*
+ * TEST INFRASTRUCTURE.  The CPU oracle: a plain-C restatement of the reference's CPU definition of the fused
+ * row-wise hot path.  Only tests, the smoke check and the bench's CPU-baseline leg may call it; the product
+ * library never does.
+ *
+ * Each function's comment in fnb_oracle.c names the reference lines it follows.  Block layouts are ggml's
+ * (ggml/src/ggml-common.h:258-276 Q8_0 / Q8_1, :334-345 Q4_K, :414-418 IQ3_XXS).
+ */
+#ifndef FNB_ORACLE_H
+#define FNB_ORACLE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FNBO_ERR_TOKEN 1u /* a token id outside [0, n_vocab) */
+#define FNBO_ERR_SLOT 2u  /* a cache slot outside [0, cache_slots) */
+
+/* 0 = restated exact expf / sinf / cosf (default), 1 = the host libm's */
+void fnbo_use_libm(int on);
+
+uint16_t fnbo_f32_to_f16(float f);
+float fnbo_f16_to_f32(uint16_t h);
+float fnbo_expf_exact(float x);
+float fnbo_sinf_exact(float x);
+float fnbo_cosf_exact(float x);
+
+void fnbo_quantize_row_q8_0(const float * x, void * y, int64_t k);
+void fnbo_quantize_row_q8_1(const float * x, void * y, int64_t k);
+void fnbo_dequantize_row_q8_0(const void * x, float * y, int64_t k);
+void fnbo_dequantize_row_q4_k(const void * x, float * y, int64_t k);
+void fnbo_dequantize_row_iq3_xxs(const void * x, float * y, int64_t k);
+
+/* get_rows: out[t] = dequantised row ids[t]; a bad id sets FNBO_ERR_TOKEN in *err and leaves the row unwritten */
+void fnbo_get_rows_q4_k(const void * table, int64_t n_vocab, const int32_t * ids, float * out, uint32_t * err,
+                        int64_t rows, int32_t cols);
+void fnbo_get_rows_iq3_xxs(const void * table, int64_t n_vocab, const int32_t * ids, float * out, uint32_t * err,
+                           int64_t rows, int32_t cols);
+
+/* y = (x * scale) * w, scale = 1/sqrtf(mean(x^2) + eps); w may be NULL (no weight) */
+void fnbo_rms_norm_f32(const float * x, const float * w, float eps, float * y, int64_t rows, int32_t cols);
+
+/* out block b of row r = Q8_1(silu(gate) * up); f32_out (optional) takes the unquantised product */
+void fnbo_swiglu_q8_1(const float * gate, const float * up, void * out_q8_1, float * f32_out, int64_t rows,
+                      int32_t cols);
+
+typedef struct fnbo_rope_kv_args {
+    const float * q;         /* [rows][n_q_heads][head_dim] */
+    const float * k;         /* [rows][n_kv_heads][head_dim] */
+    const float * v;         /* [rows][n_kv_heads][head_dim] */
+    const int32_t * pos;     /* [rows] rotary position */
+    const int32_t * slots;   /* [rows] cache slot, or NULL: the slot is the position */
+    const float * q_norm_w;  /* [head_dim] or NULL: no per-head norm on q */
+    const float * k_norm_w;  /* [head_dim] or NULL */
+    float * q_out;           /* [rows][n_q_heads][head_dim] */
+    void * k_cache;          /* Q8_0 [cache_slots][n_kv_heads][head_dim / 32] */
+    void * v_cache;
+    float * k_f32;           /* optional [rows][n_kv_heads][head_dim]: k after norm and rope, before quantising */
+    uint32_t * err;
+    int64_t rows;
+    int64_t cache_slots;
+    int32_t n_q_heads, n_kv_heads, head_dim, n_rot;
+    float theta_scale;       /* powf(freq_base, -2.0f / n_rot) */
+    float eps;
+} fnbo_rope_kv_args;
+
+void fnbo_rope_neox_q8_0_append(const fnbo_rope_kv_args * a);
+float fnbo_theta_scale(float freq_base, int32_t n_rot);
+
+/* "next" formats of the reference's own GPU path */
+/* FNFL activation format: codes int8 [rows][k], scales {d, s} F32 [rows][k/32][2] */
+void fnbo_act_quantize(const float * x, int64_t rows, int32_t k, int8_t * codes, float * scales);
+void fnbo_swiglu_act(const float * gate, const float * up, int8_t * codes, float * scales, float * f32_out,
+                     int64_t rows, int32_t cols);
+/* KV8: groups of 64, codes int8 [n], FP16 scale bits [n / 64] */
+void fnbo_kv8_quantize(const float * x, int64_t n, int8_t * codes, uint16_t * scales);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

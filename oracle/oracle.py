@@ -1,0 +1,248 @@
+"""TEST INFRASTRUCTURE: ctypes access to the CPU oracle (liboracle.so) and, when it was built, to the
+reference's own CPU sources (oracle/_ref/libfnb_ref.so).
+
+Only tests, the smoke check and the bench's CPU-baseline leg import this module.  Nothing under the product
+package does, and the product never falls back to it.
+
+All functions take and return numpy arrays; layouts are ggml's block layouts
+(ggml/src/ggml-common.h:258-276, :334-345, :414-418 in the reference tree).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+from concurrent.futures import ThreadPoolExecutor
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(_HERE, "liboracle.so")
+REF_SO = os.path.join(_HERE, "_ref", "libfnb_ref.so")
+
+ERR_TOKEN = 1
+ERR_SLOT = 2
+
+Q8_0_BYTES, Q8_1_BYTES, Q4_K_BYTES, IQ3_XXS_BYTES = 34, 36, 144, 98
+
+
+def build(with_ref: bool | None = None) -> None:
+    """Compile the oracle (and the reference build when the reference tree is present)."""
+    ref_root = os.environ.get("FNB_REFERENCE", "/root/reference")
+    if with_ref is None:
+        with_ref = os.path.isdir(os.path.join(ref_root, "ggml", "src"))
+    targets = ["all"] + (["ref"] if with_ref else [])
+    subprocess.run(["make", "-C", _HERE, "REFERENCE=" + ref_root] + targets, check=True, capture_output=True)
+
+
+class _RopeArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("pos", C.c_void_p), ("slots", C.c_void_p),
+        ("q_norm_w", C.c_void_p), ("k_norm_w", C.c_void_p), ("q_out", C.c_void_p), ("k_cache", C.c_void_p),
+        ("v_cache", C.c_void_p), ("k_f32", C.c_void_p), ("err", C.c_void_p), ("rows", C.c_int64),
+        ("cache_slots", C.c_int64), ("n_q_heads", C.c_int32), ("n_kv_heads", C.c_int32), ("head_dim", C.c_int32),
+        ("n_rot", C.c_int32), ("theta_scale", C.c_float), ("eps", C.c_float),
+    ]
+
+
+_lib = None
+_ref = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(ORACLE_SO):
+            build()
+        _lib = C.CDLL(ORACLE_SO)
+        _lib.fnbo_f32_to_f16.restype = C.c_uint16
+        _lib.fnbo_f32_to_f16.argtypes = [C.c_float]
+        _lib.fnbo_f16_to_f32.restype = C.c_float
+        _lib.fnbo_f16_to_f32.argtypes = [C.c_uint16]
+        for name in ("fnbo_expf_exact", "fnbo_sinf_exact", "fnbo_cosf_exact"):
+            getattr(_lib, name).restype = C.c_float
+            getattr(_lib, name).argtypes = [C.c_float]
+    return _lib
+
+
+def have_ref() -> bool:
+    return os.path.exists(REF_SO)
+
+
+def ref() -> C.CDLL:
+    """The reference's own CPU sources (only exists where the reference tree was present at build time)."""
+    global _ref
+    if _ref is None:
+        _ref = C.CDLL(REF_SO)
+        _ref.ref_f32_to_f16.restype = C.c_uint16
+        _ref.ref_f32_to_f16.argtypes = [C.c_float]
+        _ref.ref_f16_to_f32.restype = C.c_float
+        _ref.ref_f16_to_f32.argtypes = [C.c_uint16]
+        _ref.ref_kv_q8_stress_rows.restype = C.c_int64
+    return _ref
+
+
+def _p(a: np.ndarray | None) -> C.c_void_p:
+    if a is None:
+        return C.c_void_p(0)
+    assert a.flags["C_CONTIGUOUS"]
+    return C.c_void_p(a.ctypes.data)
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def use_libm(on: bool) -> None:
+    lib().fnbo_use_libm(C.c_int(1 if on else 0))
+
+
+# ---- scalar helpers -------------------------------------------------------------------------------------
+
+def f32_to_f16_bits(x: np.ndarray) -> np.ndarray:
+    l = lib()
+    return np.array([l.fnbo_f32_to_f16(float(v)) for v in np.asarray(x, np.float32).ravel()], np.uint16)
+
+
+def f16_bits_to_f32(h: np.ndarray) -> np.ndarray:
+    l = lib()
+    return np.array([l.fnbo_f16_to_f32(int(v)) for v in np.asarray(h, np.uint16).ravel()], np.float32)
+
+
+# ---- quantisers / decoders ------------------------------------------------------------------------------
+
+def quantize_q8_0(x: np.ndarray) -> np.ndarray:
+    x = _f32(x)
+    out = np.empty(x.size // 32 * Q8_0_BYTES, np.uint8)
+    lib().fnbo_quantize_row_q8_0(_p(x), _p(out), C.c_int64(x.size))
+    return out
+
+
+def quantize_q8_1(x: np.ndarray) -> np.ndarray:
+    x = _f32(x)
+    out = np.empty(x.size // 32 * Q8_1_BYTES, np.uint8)
+    lib().fnbo_quantize_row_q8_1(_p(x), _p(out), C.c_int64(x.size))
+    return out
+
+
+def dequantize_q8_0(b: np.ndarray) -> np.ndarray:
+    b = np.ascontiguousarray(b, np.uint8)
+    out = np.empty(b.size // Q8_0_BYTES * 32, np.float32)
+    lib().fnbo_dequantize_row_q8_0(_p(b), _p(out), C.c_int64(out.size))
+    return out
+
+
+def dequantize_q4_k(b: np.ndarray) -> np.ndarray:
+    b = np.ascontiguousarray(b, np.uint8)
+    out = np.empty(b.size // Q4_K_BYTES * 256, np.float32)
+    lib().fnbo_dequantize_row_q4_k(_p(b), _p(out), C.c_int64(out.size))
+    return out
+
+
+def dequantize_iq3_xxs(b: np.ndarray) -> np.ndarray:
+    b = np.ascontiguousarray(b, np.uint8)
+    out = np.empty(b.size // IQ3_XXS_BYTES * 256, np.float32)
+    lib().fnbo_dequantize_row_iq3_xxs(_p(b), _p(out), C.c_int64(out.size))
+    return out
+
+
+def get_rows(fmt: str, table: np.ndarray, n_vocab: int, ids: np.ndarray, cols: int, out: np.ndarray | None = None):
+    """Returns (out [rows][cols] F32, err word).  Rows with a bad id keep `out`'s previous contents."""
+    table = np.ascontiguousarray(table, np.uint8)
+    ids = np.ascontiguousarray(ids, np.int32)
+    if out is None:
+        out = np.zeros((ids.size, cols), np.float32)
+    err = np.zeros(1, np.uint32)
+    fn = {"q4_k": lib().fnbo_get_rows_q4_k, "iq3_xxs": lib().fnbo_get_rows_iq3_xxs}[fmt]
+    fn(_p(table), C.c_int64(n_vocab), _p(ids), _p(out), _p(err), C.c_int64(ids.size), C.c_int32(cols))
+    return out, int(err[0])
+
+
+def rms_norm(x: np.ndarray, w: np.ndarray | None, eps: float) -> np.ndarray:
+    x = _f32(x)
+    cols = x.shape[-1]
+    w = None if w is None else _f32(w)
+    y = np.empty_like(x)
+    lib().fnbo_rms_norm_f32(_p(x), _p(w), C.c_float(eps), _p(y), C.c_int64(x.size // cols), C.c_int32(cols))
+    return y
+
+
+def swiglu_q8_1(gate: np.ndarray, up: np.ndarray, want_f32: bool = False):
+    gate, up = _f32(gate), _f32(up)
+    cols = gate.shape[-1]
+    rows = gate.size // cols
+    out = np.empty((rows, cols // 32 * Q8_1_BYTES), np.uint8)
+    f32 = np.empty_like(gate) if want_f32 else None
+    lib().fnbo_swiglu_q8_1(_p(gate), _p(up), _p(out), _p(f32), C.c_int64(rows), C.c_int32(cols))
+    return (out, f32) if want_f32 else out
+
+
+def swiglu_act(gate: np.ndarray, up: np.ndarray):
+    gate, up = _f32(gate), _f32(up)
+    cols = gate.shape[-1]
+    rows = gate.size // cols
+    codes = np.empty((rows, cols), np.int8)
+    scales = np.empty((rows, cols // 32, 2), np.float32)
+    f32 = np.empty_like(gate)
+    lib().fnbo_swiglu_act(_p(gate), _p(up), _p(codes), _p(scales), _p(f32), C.c_int64(rows), C.c_int32(cols))
+    return codes, scales, f32
+
+
+def act_quantize(x: np.ndarray):
+    x = _f32(x)
+    k = x.shape[-1]
+    rows = x.size // k
+    codes = np.empty((rows, k), np.int8)
+    scales = np.empty((rows, k // 32, 2), np.float32)
+    lib().fnbo_act_quantize(_p(x), C.c_int64(rows), C.c_int32(k), _p(codes), _p(scales))
+    return codes, scales
+
+
+def kv8_quantize(x: np.ndarray):
+    x = _f32(x)
+    codes = np.empty(x.size, np.int8)
+    scales = np.empty(x.size // 64, np.uint16)
+    lib().fnbo_kv8_quantize(_p(x), C.c_int64(x.size), _p(codes), _p(scales))
+    return codes, scales
+
+
+def rope_kv_append(q, k, v, pos, *, n_rot: int, theta_scale: float, k_cache: np.ndarray, v_cache: np.ndarray,
+                   cache_slots: int, slots=None, q_norm_w=None, k_norm_w=None, eps: float = 1e-6,
+                   want_k_f32: bool = False, q_out: np.ndarray | None = None):
+    """q [rows][n_q][hd], k/v [rows][n_kv][hd]; caches are uint8 [cache_slots][n_kv][hd/32*34], updated in place.
+    Returns (q_out, k_f32 or None, err)."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    rows, n_q, hd = q.shape
+    n_kv = k.shape[1]
+    pos = np.ascontiguousarray(pos, np.int32)
+    slots = None if slots is None else np.ascontiguousarray(slots, np.int32)
+    qw = None if q_norm_w is None else _f32(q_norm_w)
+    kw = None if k_norm_w is None else _f32(k_norm_w)
+    if q_out is None:
+        q_out = np.zeros_like(q)
+    k_f32 = np.zeros_like(k) if want_k_f32 else None
+    err = np.zeros(1, np.uint32)
+    a = _RopeArgs(_p(q), _p(k), _p(v), _p(pos), _p(slots), _p(qw), _p(kw), _p(q_out), _p(k_cache), _p(v_cache),
+                  _p(k_f32), _p(err), rows, cache_slots, n_q, n_kv, hd, n_rot, theta_scale, eps)
+    lib().fnbo_rope_neox_q8_0_append(C.byref(a))
+    return q_out, k_f32, int(err[0])
+
+
+def theta_scale(freq_base: float, n_rot: int) -> float:
+    """powf(freq_base, -2/n_rot) in F32, as fn/kernels/qsa/attend.cu:830-832 computes it on the host."""
+    l = lib()
+    l.fnbo_theta_scale.restype = C.c_float
+    return float(l.fnbo_theta_scale(C.c_float(freq_base), C.c_int32(n_rot)))
+
+
+# ---- multi-threaded row split, for the timed CPU baseline ------------------------------------------------
+
+def parallel_rows(fn, rows: int, threads: int) -> None:
+    """Run fn(r0, r1) over an even split of [0, rows) on `threads` host threads (ctypes drops the GIL)."""
+    threads = max(1, min(threads, rows))
+    cuts = [rows * i // threads for i in range(threads + 1)]
+    if threads == 1:
+        fn(0, rows)
+        return
+    with ThreadPoolExecutor(threads) as ex:
+        list(ex.map(lambda i: fn(cuts[i], cuts[i + 1]), range(threads)))

@@ -1,0 +1,73 @@
+// TEST INFRASTRUCTURE.  C entry points over the reference's own CPU sources, compiled where they lie in the
+// reference tree (see Makefile: nothing is copied).  The ggml (de)quantisers are exported by ggml-quants.c
+// itself under their own names (quantize_row_q8_0_ref, quantize_row_q8_1_ref, dequantize_row_q4_K,
+// dequantize_row_iq3_xxs, dequantize_row_q8_0); this file adds the four symbols ggml-quants.c leaves undefined
+// when built alone, and C wrappers for the C++ references under fn/quant.
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+#include "fn/quant/act_ref.h"
+#include "fn/quant/decode.h"
+#include "fn/quant/formats.h"
+#include "fn/quant/kv_q8_ref.h"
+#include "fn/quant/synth.h"
+
+extern "C" {
+
+// ggml-quants.c's unresolved externals: only reached from quantisation paths the oracle never calls
+void ggml_abort(const char * file, int line, const char * fmt, ...) {
+    std::fprintf(stderr, "ggml_abort %s:%d: ", file, line);
+    va_list ap;
+    va_start(ap, fmt);
+    std::vfprintf(stderr, fmt, ap);
+    va_end(ap);
+    std::fputc('\n', stderr);
+    std::abort();
+}
+size_t ggml_row_size(int, int64_t) { std::abort(); }
+const char * ggml_type_name(int) { return "?"; }
+size_t ggml_type_size(int) { std::abort(); }
+
+void ref_act_quantize(const float * x, int32_t rows, int32_t k, int8_t * codes, float * scales) {
+    fn::quant::act_quantize_ref(x, rows, k, codes, scales);
+}
+
+void ref_kv_q8_quantize(const float * x, int32_t n, int8_t * codes, uint16_t * scales) {
+    fn::quant::kv_q8_quantize(x, n, codes, scales);
+}
+
+// the KV8 stress rows (fn/quant/kv_q8_ref.cpp:99-169): returns the value count; copies up to cap values
+int64_t ref_kv_q8_stress_rows(uint64_t seed, int32_t random_rows, float * out, int64_t cap) {
+    const std::vector<float> v = fn::quant::kv_q8_stress_rows(seed, random_rows);
+    const int64_t n = int64_t(v.size());
+    if (out != nullptr) {
+        std::memcpy(out, v.data(), size_t(n < cap ? n : cap) * sizeof(float));
+    }
+    return n;
+}
+
+static bool fmt_of(const char * name, fn::quant::wfmt & f) { return fn::quant::wfmt_of_name(name, f); }
+
+int32_t ref_block_bytes(const char * fmt) {
+    fn::quant::wfmt f;
+    return fmt_of(fmt, f) ? fn::quant::info(f).block_bytes : -1;
+}
+
+int32_t ref_decode_row(const char * fmt, const void * src, float * dst, int64_t n) {
+    fn::quant::wfmt f;
+    return fmt_of(fmt, f) && fn::quant::decode_row(f, src, dst, n) ? 0 : 1;
+}
+
+int32_t ref_synth_blocks(const char * fmt, uint64_t seed, int64_t n_blocks, uint8_t * dst) {
+    fn::quant::wfmt f;
+    return fmt_of(fmt, f) && fn::quant::synth_blocks(f, seed, n_blocks, dst) ? 0 : 1;
+}
+
+uint16_t ref_f32_to_f16(float f) { return fn::quant::f32_to_f16(f); }
+float ref_f16_to_f32(uint16_t h) { return fn::quant::f16_to_f32(h); }
+
+}  // extern "C"
