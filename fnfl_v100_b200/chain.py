@@ -1,0 +1,130 @@
+"""The fused-op chain of one prefill chunk on one GPU's shard of token rows.
+
+    ids --get_rows(Q4_K)--> hidden --RMSNorm--> normed_attn         (a QKV projection would consume this)
+    q, k, v --per-head RMSNorm + NeoX partial RoPE--> q_out, K/V appended to the Q8_0 cache
+    hidden --RMSNorm--> normed_ffn                                   (the expert gate/up products would consume this)
+    gate, up --SwiGLU + Q8_1--> activations for the expert down product
+
+Only get_rows -> RMSNorm is truly chained; the tensors a dense product would produce (q, k, v, gate, up) are
+seeded synthetic inputs, because contractions are outside this path.  Five launches per step, no host
+synchronisation, no allocation after construction, so a step can be captured in a CUDA graph and replayed,
+which is how the reference's prompt path replays its unit graphs.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, asdict
+
+import torch
+
+from . import ops, synth
+
+
+@dataclass
+class ChainConfig:
+    tokens: int = 65536          # rows of this GPU's shard
+    hidden: int = 2048
+    n_q_heads: int = 16
+    n_kv_heads: int = 2
+    head_dim: int = 256
+    n_rot: int = 64
+    freq_base: float = 1e7
+    top_k: int = 10              # expert rows per token
+    inter: int = 512             # expert intermediate width
+    n_vocab: int = 151936
+    cache_slots: int = 262144
+    depth: int = 196608          # context depth: the first token's position and cache slot
+    eps: float = 1e-6
+    table_fmt: str = "q4_k"
+    seed_case: int = 5
+
+    # algorithmic bytes per token of each stage (compulsory reads + writes)
+    def bytes_per_token(self) -> dict:
+        row_b = ops.table_row_bytes(self.table_fmt, self.hidden)
+        hd, nq, nkv = self.head_dim, self.n_q_heads, self.n_kv_heads
+        cell = hd // 32 * ops.Q8_0_BLOCK
+        rope = 2 * nq * hd * 4 + 2 * nkv * hd * 4 + 2 * nkv * cell + 4
+        glu_rows = self.top_k
+        glu = glu_rows * (2 * self.inter * 4 + self.inter // 32 * ops.Q8_1_BLOCK)
+        norm = 2 * self.hidden * 4
+        return {"get_rows": row_b + 4 + self.hidden * 4, "rms_norm_attn": norm, "rope_kv": rope,
+                "rms_norm_ffn": norm, "swiglu_q8_1": glu}
+
+
+class PrefillChain:
+    """Owns every buffer of the chain for one shard; `step()` enqueues the five launches."""
+
+    STAGES = ("get_rows", "rms_norm_attn", "rope_kv", "rms_norm_ffn", "swiglu_q8_1")
+
+    def __init__(self, cfg: ChainConfig, device, first_token: int = 0):
+        self.cfg, self.device = cfg, torch.device(device)
+        c, dev, T = cfg, self.device, cfg.tokens
+        gen = synth.torch_gen(dev, c.seed_case)
+        self.table = synth.torch_table(c.table_fmt, gen, c.n_vocab, c.hidden, dev)
+        self.ids = torch.randint(0, c.n_vocab, (T,), dtype=torch.int32, device=dev, generator=gen)
+        # positions are contiguous per shard: depth + the shard's first token + t
+        self.pos = (c.depth + first_token + torch.arange(T, device=dev, dtype=torch.int64)).to(torch.int32)
+        self.w_attn = 1.0 + 0.1 * synth.torch_normal(gen, (c.hidden,), 1.0, dev)
+        self.w_ffn = 1.0 + 0.1 * synth.torch_normal(gen, (c.hidden,), 1.0, dev)
+        self.w_q = 1.0 + 0.1 * synth.torch_normal(gen, (c.head_dim,), 1.0, dev)
+        self.w_k = 1.0 + 0.1 * synth.torch_normal(gen, (c.head_dim,), 1.0, dev)
+        self.q = synth.torch_normal(gen, (T, c.n_q_heads, c.head_dim), 1.0, dev)
+        self.k = synth.torch_normal(gen, (T, c.n_kv_heads, c.head_dim), 1.0, dev)
+        self.v = synth.torch_normal(gen, (T, c.n_kv_heads, c.head_dim), 1.0, dev)
+        self.gate = synth.torch_normal(gen, (T * c.top_k, c.inter), 0.5, dev)
+        self.up = synth.torch_normal(gen, (T * c.top_k, c.inter), 0.5, dev)
+        self.theta_scale = ops.theta_scale(c.freq_base, c.n_rot)
+        # outputs
+        self.hidden = torch.empty((T, c.hidden), dtype=torch.float32, device=dev)
+        self.normed_attn = torch.empty_like(self.hidden)
+        self.normed_ffn = torch.empty_like(self.hidden)
+        self.q_out = torch.empty_like(self.q)
+        self.k_cache = ops.new_kv_cache(c.cache_slots, c.n_kv_heads, c.head_dim, dev)
+        self.v_cache = ops.new_kv_cache(c.cache_slots, c.n_kv_heads, c.head_dim, dev)
+        self.act = torch.empty((T * c.top_k, c.inter // 32 * ops.Q8_1_BLOCK), dtype=torch.uint8, device=dev)
+        self.err = ops.new_err(dev)
+
+    # ---- stages, individually callable so each can be timed alone ----
+    def get_rows(self):
+        ops.get_rows(self.cfg.table_fmt, self.table, self.ids, self.cfg.hidden, out=self.hidden, err=self.err)
+
+    def rms_norm_attn(self):
+        ops.rms_norm(self.hidden, self.w_attn, self.cfg.eps, out=self.normed_attn)
+
+    def rope_kv(self):
+        c = self.cfg
+        ops.rope_neox_q8_0_append(self.q, self.k, self.v, self.pos, n_rot=c.n_rot, theta_scale=self.theta_scale,
+                                  k_cache=self.k_cache, v_cache=self.v_cache, q_norm_w=self.w_q, k_norm_w=self.w_k,
+                                  eps=c.eps, q_out=self.q_out, err=self.err)
+
+    def rms_norm_ffn(self):
+        ops.rms_norm(self.hidden, self.w_ffn, self.cfg.eps, out=self.normed_ffn)
+
+    def swiglu_q8_1(self):
+        ops.swiglu_q8_1(self.gate, self.up, out=self.act)
+
+    def step(self):
+        for name in self.STAGES:
+            getattr(self, name)()
+
+    launches_per_step = 5
+
+    def capture(self) -> torch.cuda.CUDAGraph:
+        """Record one step into a CUDA graph (the launchers neither synchronise nor allocate)."""
+        s = torch.cuda.Stream(self.device)
+        s.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(s):
+            self.step()  # warm the context before capture
+        torch.cuda.current_stream(self.device).wait_stream(s)
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.step()
+        return g
+
+    def kv_cells(self):
+        """The cells this shard appended: (K, V) uint8 [tokens][n_kv][cell bytes]."""
+        lo = int(self.pos[0].item())
+        return self.k_cache[lo:lo + self.cfg.tokens], self.v_cache[lo:lo + self.cfg.tokens]
+
+    def describe(self) -> dict:
+        return asdict(self.cfg)

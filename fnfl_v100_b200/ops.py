@@ -1,0 +1,234 @@
+"""Host-side operators over torch CUDA tensors: thin, checked calls into the C ABI (include/fnb200.h).
+
+The names and argument meaning follow the reference's launcher families (fn::draft::dcp_norm,
+fn::experts::glu_finish, fn::act::quantize, fn::qsa::qsp_kv, fn::embed::embed_rows); torch only supplies device
+memory and the current stream.  Every function enqueues on `torch.cuda.current_stream()` and returns without
+synchronising.  A rejected argument raises ValueError (the reference returns false with nothing enqueued); there
+is no CPU or eager fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+
+Q8_0_BLOCK, Q8_1_BLOCK, Q4_K_BLOCK, IQ3_XXS_BLOCK = 34, 36, 144, 98
+ERR_TOKEN, ERR_SLOT = _lib.ERR_TOKEN, _lib.ERR_SLOT
+
+_TABLE_BLOCK = {"q4_k": (256, Q4_K_BLOCK), "iq3_xxs": (256, IQ3_XXS_BLOCK), "q8_0": (32, Q8_0_BLOCK)}
+
+
+def _stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: torch.Tensor | None) -> C.c_void_p:
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _dev(t: torch.Tensor, dtype: torch.dtype, name: str) -> torch.Tensor:
+    if not (isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == dtype and t.is_contiguous()):
+        raise ValueError(f"{name}: expected a contiguous CUDA tensor of {dtype}")
+    return t
+
+
+def _check(status: int, what: str) -> None:
+    if status == _lib.OK:
+        return
+    msg = f"{what}: {_lib.status_name(status)}"
+    raise ValueError(msg) if status == _lib.REJECTED else RuntimeError(msg)
+
+
+def new_err(device) -> torch.Tensor:
+    """A zeroed device error word (uint32 viewed as int32) for the kernels' data-dependent faults."""
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+# ---- RMSNorm ------------------------------------------------------------------------------------------------
+
+def rms_norm(x: torch.Tensor, w: torch.Tensor | None, eps: float = 1e-6, out: torch.Tensor | None = None):
+    """y = (x * scale) * w per row of x [..., cols]; replaces fn::draft::dcp_norm's arithmetic."""
+    _dev(x, torch.float32, "x")
+    if w is not None:
+        _dev(w, torch.float32, "w")
+        if w.numel() != x.shape[-1]:
+            raise ValueError("w: expected [cols]")
+    out = torch.empty_like(x) if out is None else _dev(out, torch.float32, "out")
+    cols = x.shape[-1]
+    _check(_lib.lib().fnb_rms_norm_f32(_ptr(x), _ptr(w), eps, _ptr(out), x.numel() // cols, cols, _stream()),
+           "rms_norm")
+    return out
+
+
+def rms_norm_heads(x: torch.Tensor, w: torch.Tensor | None, eps: float = 1e-6, out: torch.Tensor | None = None):
+    """The per-head Q/K norm over x [rows][n_heads][head_dim] with one weight [head_dim]."""
+    _dev(x, torch.float32, "x")
+    if x.dim() != 3:
+        raise ValueError("x: expected [rows][n_heads][head_dim]")
+    if w is not None:
+        _dev(w, torch.float32, "w")
+    out = torch.empty_like(x) if out is None else _dev(out, torch.float32, "out")
+    rows, n_heads, hd = x.shape
+    _check(_lib.lib().fnb_rms_norm_heads_f32(_ptr(x), _ptr(w), eps, _ptr(out), rows, n_heads, hd, _stream()),
+           "rms_norm_heads")
+    return out
+
+
+# ---- SwiGLU + requantisation --------------------------------------------------------------------------------
+
+def _rows_cols(x: torch.Tensor) -> tuple[int, int]:
+    cols = x.shape[-1]
+    return x.numel() // cols, cols
+
+
+def swiglu_q8_1(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor | None = None,
+                out_f32: torch.Tensor | None = None) -> torch.Tensor:
+    """silu(gate) * up -> ggml Q8_1 blocks, uint8 [rows][cols / 32 * 36]; replaces fn::experts::glu_finish."""
+    _dev(gate, torch.float32, "gate")
+    _dev(up, torch.float32, "up")
+    if up.shape != gate.shape:
+        raise ValueError("gate and up must have one shape")
+    rows, cols = _rows_cols(gate)
+    if out is None:
+        out = torch.empty((rows, cols // 32 * Q8_1_BLOCK), dtype=torch.uint8, device=gate.device)
+    _dev(out, torch.uint8, "out")
+    if out_f32 is not None:
+        _dev(out_f32, torch.float32, "out_f32")
+    _check(_lib.lib().fnb_swiglu_q8_1(_ptr(gate), _ptr(up), _ptr(out), _ptr(out_f32), rows, cols, _stream()),
+           "swiglu_q8_1")
+    return out
+
+
+def swiglu_act(gate: torch.Tensor, up: torch.Tensor, out_f32: torch.Tensor | None = None):
+    """silu(gate) * up -> the reference's activation format: (codes int8 [rows][cols], scales F32 [rows][cols/32][2])."""
+    _dev(gate, torch.float32, "gate")
+    _dev(up, torch.float32, "up")
+    rows, cols = _rows_cols(gate)
+    codes = torch.empty((rows, cols), dtype=torch.int8, device=gate.device)
+    scales = torch.empty((rows, cols // 32, 2), dtype=torch.float32, device=gate.device)
+    _check(_lib.lib().fnb_swiglu_act(_ptr(gate), _ptr(up), _ptr(codes), _ptr(scales), _ptr(out_f32), rows, cols,
+                                     _stream()), "swiglu_act")
+    return codes, scales
+
+
+def quantize_q8_1(x: torch.Tensor) -> torch.Tensor:
+    _dev(x, torch.float32, "x")
+    rows, cols = _rows_cols(x)
+    out = torch.empty((rows, cols // 32 * Q8_1_BLOCK), dtype=torch.uint8, device=x.device)
+    _check(_lib.lib().fnb_quantize_q8_1(_ptr(x), _ptr(out), rows, cols, _stream()), "quantize_q8_1")
+    return out
+
+
+def quantize_q8_0(x: torch.Tensor) -> torch.Tensor:
+    _dev(x, torch.float32, "x")
+    rows, cols = _rows_cols(x)
+    out = torch.empty((rows, cols // 32 * Q8_0_BLOCK), dtype=torch.uint8, device=x.device)
+    _check(_lib.lib().fnb_quantize_q8_0(_ptr(x), _ptr(out), rows, cols, _stream()), "quantize_q8_0")
+    return out
+
+
+def act_quantize(x: torch.Tensor):
+    """fn::act::quantize: F32 [rows][k] -> (codes int8 [rows][k], scales F32 [rows][k/32][2])."""
+    _dev(x, torch.float32, "x")
+    rows, cols = _rows_cols(x)
+    codes = torch.empty((rows, cols), dtype=torch.int8, device=x.device)
+    scales = torch.empty((rows, cols // 32, 2), dtype=torch.float32, device=x.device)
+    _check(_lib.lib().fnb_act_quantize(_ptr(x), _ptr(codes), _ptr(scales), rows, cols, _stream()), "act_quantize")
+    return codes, scales
+
+
+# ---- RoPE + KV append -----------------------------------------------------------------------------------------
+
+def theta_scale(freq_base: float, n_rot: int) -> float:
+    return float(_lib.lib().fnb_rope_theta_scale(freq_base, n_rot))
+
+
+def new_kv_cache(cache_slots: int, n_kv_heads: int, head_dim: int, device, fmt: str = "q8_0"):
+    """Zeroed cache planes.  q8_0: uint8 [slots][n_kv][head_dim/32*34]; kv8: (codes int8, scales fp16-bits int16)."""
+    if fmt == "q8_0":
+        return torch.zeros((cache_slots, n_kv_heads, head_dim // 32 * Q8_0_BLOCK), dtype=torch.uint8, device=device)
+    codes = torch.zeros((cache_slots, n_kv_heads, head_dim), dtype=torch.int8, device=device)
+    scales = torch.zeros((cache_slots, n_kv_heads, head_dim // 64), dtype=torch.int16, device=device)
+    return codes, scales
+
+
+def _rope_args(q, k, v, pos, slots, q_norm_w, k_norm_w, q_out, k_cache, v_cache, k_f32, err, n_rot, ts, eps):
+    _dev(q, torch.float32, "q")
+    _dev(k, torch.float32, "k")
+    _dev(v, torch.float32, "v")
+    _dev(pos, torch.int32, "pos")
+    if q.dim() != 3 or k.dim() != 3 or v.shape != k.shape or q.shape[0] != k.shape[0] or q.shape[2] != k.shape[2]:
+        raise ValueError("q [rows][n_q][hd], k and v [rows][n_kv][hd]")
+    rows, n_q, hd = q.shape
+    if pos.numel() != rows or (slots is not None and slots.numel() != rows):
+        raise ValueError("pos / slots: expected [rows]")
+    cache_slots = k_cache.shape[0]
+    a = _lib.RopeKvArgs(
+        _ptr(q).value, _ptr(k).value, _ptr(v).value, _ptr(pos).value, _ptr(slots).value, _ptr(q_norm_w).value,
+        _ptr(k_norm_w).value, _ptr(q_out).value, _ptr(k_cache).value, _ptr(v_cache).value, _ptr(k_f32).value,
+        _ptr(err).value, rows, cache_slots, n_q, k.shape[1], hd, n_rot, ts, eps)
+    return a
+
+
+def rope_neox_q8_0_append(q, k, v, pos, *, n_rot: int, theta_scale: float, k_cache, v_cache, slots=None,
+                          q_norm_w=None, k_norm_w=None, eps: float = 1e-6, q_out=None, k_f32=None, err=None):
+    """Per-head norm (optional) + NeoX partial RoPE; Q -> q_out (F32), K/V -> Q8_0 cells at each token's slot.
+    Replaces fn::qsa::qsp_kv and the prepare phase of fn::qsa::attn::attend.  Returns q_out."""
+    if q_out is None:
+        q_out = torch.empty_like(q)
+    _dev(k_cache, torch.uint8, "k_cache")
+    _dev(v_cache, torch.uint8, "v_cache")
+    a = _rope_args(q, k, v, pos, slots, q_norm_w, k_norm_w, q_out, k_cache, v_cache, k_f32, err, n_rot,
+                   theta_scale, eps)
+    _check(_lib.lib().fnb_rope_neox_q8_0_append(C.byref(a), _stream()), "rope_neox_q8_0_append")
+    return q_out
+
+
+def rope_neox_kv8_append(q, k, v, pos, *, n_rot: int, theta_scale: float, k_cache, v_cache, k_scale, v_scale,
+                         slots=None, q_norm_w=None, k_norm_w=None, eps: float = 1e-6, q_out=None, k_f32=None,
+                         err=None):
+    """The same step into the reference's KV8 format (int8 codes + FP16 scale per 64 values)."""
+    if q_out is None:
+        q_out = torch.empty_like(q)
+    _dev(k_cache, torch.int8, "k_cache")
+    _dev(v_cache, torch.int8, "v_cache")
+    _dev(k_scale, torch.int16, "k_scale")
+    _dev(v_scale, torch.int16, "v_scale")
+    base = _rope_args(q, k, v, pos, slots, q_norm_w, k_norm_w, q_out, k_cache, v_cache, k_f32, err, n_rot,
+                      theta_scale, eps)
+    a = _lib.RopeKv8Args(base, _ptr(k_scale).value, _ptr(v_scale).value)
+    _check(_lib.lib().fnb_rope_neox_kv8_append(C.byref(a), _stream()), "rope_neox_kv8_append")
+    return q_out
+
+
+# ---- embedding get_rows ---------------------------------------------------------------------------------------
+
+def table_row_bytes(fmt: str, cols: int) -> int:
+    values, nbytes = _TABLE_BLOCK[fmt]
+    return cols // values * nbytes
+
+
+def get_rows(fmt: str, table: torch.Tensor, ids: torch.Tensor, cols: int, out: torch.Tensor | None = None,
+             err: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t] = dequantised row ids[t] of `table` (uint8 [n_vocab][row_bytes]); replaces fn::embed::embed_rows."""
+    _dev(table, torch.uint8, "table")
+    _dev(ids, torch.int32, "ids")
+    rb = table_row_bytes(fmt, cols)
+    if table.numel() % rb != 0:
+        raise ValueError("table: size is not a whole number of rows")
+    n_vocab = table.numel() // rb
+    if out is None:
+        out = torch.empty((ids.numel(), cols), dtype=torch.float32, device=table.device)
+    _dev(out, torch.float32, "out")
+    fn = getattr(_lib.lib(), "fnb_get_rows_" + fmt)
+    _check(fn(_ptr(table), n_vocab, _ptr(ids), _ptr(out), _ptr(err), ids.numel(), cols, _stream()), "get_rows_" + fmt)
+    return out
+
+
+def check_tokens(ids_host: torch.Tensor, n_vocab: int) -> int:
+    """Host check before upload (fn::embed::check_tokens): 0, or 1 + the index of the first id outside [0, n_vocab)."""
+    if ids_host.is_cuda or ids_host.dtype != torch.int32 or not ids_host.is_contiguous():
+        raise ValueError("ids_host: expected a contiguous host int32 tensor")
+    return int(_lib.lib().fnb_check_tokens(C.c_void_p(ids_host.data_ptr()), ids_host.numel(), n_vocab))

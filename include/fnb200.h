@@ -1,0 +1,182 @@
+/*
+ * fnb200 - B200 (sm_100a) kernels for the FNFL engine's fused per-layer row-wise path, C ABI.
+ *
+ * The reference engine has no extern "C" layer: fn/model and fn/runtime call fn/kernels through one C++
+ * convention, `bool fn::<family>::<op>(const <op>_args &, void * stream)` with raw device pointers, "false
+ * and nothing enqueued" for an argument outside the contract, and a device error word for data-dependent
+ * faults (fn/kernels/act/act.h:64-66, fn/kernels/embed/embed.h:56-60, fn/kernels/qsa/qsa_prompt.h:90-105,
+ * fn/kernels/experts/experts.h:277, fn/kernels/draft/draft_prompt.h:34).  Each entry point below replaces one
+ * of those launchers and keeps that convention: plain pointers and sizes, the caller owns every buffer, the
+ * call only enqueues work on `stream` (a cudaStream_t passed as void *, null = the default stream), never
+ * synchronises and never allocates, so it is legal inside stream capture.  include/fnb200_fn.hpp restores the
+ * `bool op(args, stream)` spelling on top of these.
+ *
+ * Return value: FNB_OK (enqueued), FNB_REJECTED (argument outside the contract, nothing enqueued) or
+ * FNB_LAUNCH_FAILED (the launch was refused; the CUDA error is left for cudaPeekAtLastError).
+ * Device error word (`err`, optional): bits are OR-ed in by the kernel; the offending row is left unwritten.
+ *
+ * Numerics: built with --fmad=false; every product and sum that the CPU definition rounds separately is
+ * rounded separately here.  Block layouts are ggml's (Q8_0 34 B, Q8_1 36 B, Q4_K 144 B, IQ3_XXS 98 B).
+ */
+#ifndef FNB200_H
+#define FNB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FNB_OK 0
+#define FNB_REJECTED 1
+#define FNB_LAUNCH_FAILED 2
+
+#define FNB_ERR_TOKEN 1u /* a token id outside [0, n_vocab): as fn::xchg::err_token in fn/kernels/embed/embed.h:37 */
+#define FNB_ERR_SLOT 2u  /* a cache slot outside [0, cache_slots): fn/kernels/qsa/attend.h:109-110 */
+
+#define FNB_Q8_0_BLOCK_BYTES 34
+#define FNB_Q8_1_BLOCK_BYTES 36
+#define FNB_Q4_K_BLOCK_BYTES 144
+#define FNB_IQ3_XXS_BLOCK_BYTES 98
+
+/* Library version (major * 10000 + minor * 100 + patch) and the name of a return code. */
+int32_t fnb_version(void);
+const char * fnb_status_name(int32_t status);
+
+/*
+ * Hidden RMSNorm, one row per token: y = (x * scale) * w, scale = 1 / sqrtf(mean(x^2) + eps), the sum of
+ * squares accumulated in double.  w may be null (no weight).  x, y: F32 [rows][cols], 16-byte aligned, cols a
+ * multiple of 4 in [4, 65536]; rows in [1, 2^31).  x and y may be the same buffer.
+ * Replaces fn::draft::dcp_norm (fn/kernels/draft/draft_prompt.h:22-34, draft_prompt.cu:26-68) and the norm half
+ * of draft_in_send / draft_in_recv (fn/kernels/draft/draft.h:110-139).
+ */
+int32_t fnb_rms_norm_f32(const float * x, const float * w, float eps, float * y, int64_t rows, int32_t cols,
+                         void * stream);
+
+/*
+ * Per-head Q/K RMSNorm: the same norm over each head_dim-wide head of x [rows][n_heads][head_dim] with one
+ * weight vector [head_dim] shared by all heads.  Stand-alone form of the norm that
+ * fnb_rope_neox_q8_0_append fuses.  Replaces the norm half of norm_rope
+ * (fn/kernels/qsa/attend.cu:153-171, fn/kernels/qsa/qsa_prompt_attn.cu:33-55).
+ */
+int32_t fnb_rms_norm_heads_f32(const float * x, const float * w, float eps, float * y, int64_t rows,
+                               int32_t n_heads, int32_t head_dim, void * stream);
+
+/*
+ * SwiGLU fused with Q8_1 requantisation: v = (gate / (1 + expf(-gate))) * up in F32, then each run of 32
+ * values becomes one ggml block_q8_1 {fp16 d, fp16 s = d * sum(q), int8 q[32]} with d = amax / 127,
+ * id = 1 / d, q = roundf(v * id) (ggml/src/ggml-quants.c:300-333).  gate, up: F32 [rows][cols], 16-byte
+ * aligned, cols a multiple of 32; out_q8_1: [rows][cols / 32] blocks, 16-byte aligned; out_f32 (optional,
+ * F32 [rows][cols]) receives v before quantisation, which is how the reference's own tests pin the codes
+ * (fn/kernels/experts/experts.h:45-47).  expf is evaluated exactly as glibc 2.39's non-FMA expf.
+ * Replaces fn::experts::glu_finish (fn/kernels/experts/experts.h:273-277, experts.cu:716-729) and the GLU
+ * epilogues glu_out / glu_run (experts_gu.cuh:308-340, experts_dev.cuh:196-213).
+ */
+int32_t fnb_swiglu_q8_1(const float * gate, const float * up, void * out_q8_1, float * out_f32, int64_t rows,
+                        int32_t cols, void * stream);
+
+/*
+ * The same GLU into the reference's own activation format: int8 codes [rows][cols] and F32 {d, s} pairs
+ * [rows][cols / 32][2], d = amax / 127, id = 127 / amax, q = nearest-even(v * id) clamped to +-127,
+ * s = d * (float) sum q (fn/kernels/act/act.h:8-15).  codes 16-byte aligned, scales 8-byte aligned.
+ * Bitwise drop-in for fn::experts::glu_finish's outputs.
+ */
+int32_t fnb_swiglu_act(const float * gate, const float * up, int8_t * codes, float * scales, float * out_f32,
+                       int64_t rows, int32_t cols, void * stream);
+
+/*
+ * Stand-alone requantisers of F32 [rows][cols] (cols a multiple of 32): ggml Q8_1 blocks, ggml Q8_0 blocks, and
+ * the reference's activation format.  fnb_act_quantize replaces fn::act::quantize
+ * (fn/kernels/act/act.h:57-66, act.cu:17-49); the Q8 forms replace the CPU quantize_q8_1 / quantize_q8_0 of
+ * the expert miss path (fn/kernels/experts/experts_cpu.cpp:359-367) with ggml's reference rounding rule.
+ */
+int32_t fnb_quantize_q8_1(const float * x, void * out_q8_1, int64_t rows, int32_t cols, void * stream);
+int32_t fnb_quantize_q8_0(const float * x, void * out_q8_0, int64_t rows, int32_t cols, void * stream);
+int32_t fnb_act_quantize(const float * x, int8_t * codes, float * scales, int64_t rows, int32_t cols,
+                         void * stream);
+
+/*
+ * Optional per-head RMSNorm, NeoX partial-rotary RoPE, and Q8_0 quantise-and-append of K and V into the cache.
+ * Per token t at rotary position pos[t] and cache slot slots[t] (or pos[t] when slots is null):
+ *   q_out[t][h] = rope(norm(q[t][h]))            F32, all head_dim values (dims >= n_rot pass through)
+ *   k_cache[slot][h] = Q8_0(rope(norm(k[t][h])))  8 blocks of 34 bytes per 256-wide head
+ *   v_cache[slot][h] = Q8_0(v[t][h])
+ * rope: pair i = (dim i, dim i + n_rot/2), angle = (float) pos * theta_scale^i built as an F32 product chain,
+ * cosf / sinf evaluated exactly as glibc 2.39's non-FMA forms; y0 = x0 c - x1 s, y1 = x0 s + x1 c.
+ * norm: as fnb_rms_norm_f32 over head_dim with q_norm_w / k_norm_w [head_dim]; null = no norm for that tensor.
+ * k_f32 (optional, F32 [rows][n_kv_heads][head_dim]) receives k after norm and rope, before quantising.
+ * A slot outside [0, cache_slots) sets FNB_ERR_SLOT in *err and nothing is written for that token.
+ * head_dim in {64, 128, 256}; n_rot a multiple of 2 * (head_dim / 32), 0 <= n_rot <= head_dim; all pointers
+ * 16-byte aligned (pos, slots 4-byte).  q_out may alias q.
+ * Replaces fn::qsa::qsp_kv (fn/kernels/qsa/qsa_prompt.h:90-105, qsa_prompt_attn.cu:77-122), the prepare phase
+ * of fn::qsa::attn::attend (fn/kernels/qsa/attend.cu:153-260) and fn::draft::dcp_prepare
+ * (fn/kernels/draft/draft_prompt.h:44-59).
+ */
+typedef struct fnb_rope_kv_args {
+    const float * q;
+    const float * k;
+    const float * v;
+    const int32_t * pos;
+    const int32_t * slots;
+    const float * q_norm_w;
+    const float * k_norm_w;
+    float * q_out;
+    void * k_cache;
+    void * v_cache;
+    float * k_f32;
+    uint32_t * err;
+    int64_t rows;
+    int64_t cache_slots;
+    int32_t n_q_heads;
+    int32_t n_kv_heads;
+    int32_t head_dim;
+    int32_t n_rot;
+    float theta_scale;
+    float eps;
+} fnb_rope_kv_args;
+
+int32_t fnb_rope_neox_q8_0_append(const fnb_rope_kv_args * args, void * stream);
+
+/*
+ * The same step into the reference's KV8 cache format: int8 codes [cache_slots][n_kv_heads][head_dim] and FP16
+ * scales per 64 values [cache_slots][n_kv_heads][head_dim / 64] (fn/kernels/qsa/kv_q8.cuh:8-14, :29-52):
+ * scale = fp16_rn(amax / 127), code = clamp(nearest-even(x / f32(scale)), +-127), 0 when the scale is 0.
+ * k_cache / v_cache hold the codes, k_scale / v_scale the scales.  head_dim in {64, 128, 256}.
+ */
+typedef struct fnb_rope_kv8_args {
+    fnb_rope_kv_args base;
+    uint16_t * k_scale;
+    uint16_t * v_scale;
+} fnb_rope_kv8_args;
+
+int32_t fnb_rope_neox_kv8_append(const fnb_rope_kv8_args * args, void * stream);
+
+/* theta_scale = powf(freq_base, -2 / n_rot), the host-side constant of fn/kernels/qsa/attend.cu:830-832. */
+float fnb_rope_theta_scale(float freq_base, int32_t n_rot);
+
+/*
+ * Token-embedding get_rows: out[t] = the dequantised row ids[t] of a quantised table [n_vocab][cols], F32,
+ * bit-exact with ggml's row decoders (ggml/src/ggml-quants.c:1527-1549 Q4_K, :2573-2601 IQ3_XXS, :551-565
+ * Q8_0).  table, out 16-byte aligned; cols a multiple of 256 (Q4_K, IQ3_XXS; and the row's bytes a multiple
+ * of 16) or of 32 (Q8_0), at most 16384; ids I32 [rows] on the device.  An id outside [0, n_vocab) sets
+ * FNB_ERR_TOKEN in *err and leaves that output row unwritten.
+ * Replaces fn::embed::embed_rows / fn::embed::embed (fn/kernels/embed/embed.h:56-87, embed_prompt.cu:26-107).
+ */
+int32_t fnb_get_rows_q4_k(const void * table, int64_t n_vocab, const int32_t * ids, float * out, uint32_t * err,
+                          int64_t rows, int32_t cols, void * stream);
+int32_t fnb_get_rows_iq3_xxs(const void * table, int64_t n_vocab, const int32_t * ids, float * out,
+                             uint32_t * err, int64_t rows, int32_t cols, void * stream);
+int32_t fnb_get_rows_q8_0(const void * table, int64_t n_vocab, const int32_t * ids, float * out, uint32_t * err,
+                          int64_t rows, int32_t cols, void * stream);
+
+/*
+ * Host-side check before upload: 0 when every id is in [0, n_vocab), else 1 + the index of the first bad id.
+ * Replaces fn::embed::check_tokens (fn/kernels/embed/embed.h:56).
+ */
+int64_t fnb_check_tokens(const int32_t * ids_host, int64_t rows, int64_t n_vocab);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

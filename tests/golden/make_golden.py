@@ -1,0 +1,108 @@
+#!/usr/bin/env python3
+"""Generate tests/golden/*.npz from the reference's own CPU sources.
+
+Runs only where the reference tree is present: oracle/Makefile compiles ggml/src/ggml-quants.c and
+fn/quant/*.cpp from the reference into oracle/_ref/libfnb_ref.so, and this script records that library's outputs
+on seeded inputs.  The committed .npz files are what the tests read, so the tests need neither the reference
+tree nor the reference build.
+
+    python tests/golden/make_golden.py
+
+quant.npz    inputs F32 [n][32] (stress + random runs) and, from the reference: Q8_0 and Q8_1 blocks
+             (quantize_row_q8_0_ref / quantize_row_q8_1_ref, ggml-quants.c:274, :300), the activation format
+             (fn::quant::act_quantize_ref, act_ref.cpp:8-30) and KV8 (fn::quant::kv_q8_quantize,
+             kv_q8_ref.cpp:72-97; rows of 64)
+decode.npz   seeded synthetic blocks (fn::quant::synth_blocks with the reference's seeds, synth.h:24-28) of
+             Q4_K, IQ3_XXS and Q8_0 and their decode by dequantize_row_q4_K / _iq3_xxs / _q8_0
+             (ggml-quants.c:1527, :2573, :551), cross-checked against fn::quant::decode_row (decode.cpp)
+"""
+import ctypes as C
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+from oracle import oracle as O  # noqa: E402
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def stress_blocks() -> np.ndarray:
+    g = np.random.Generator(np.random.Philox(0x43324143))  # the seed of the reference's act-test
+    out = []
+    # random runs: per-run magnitude 1e-6 .. 1e3, one value in 64 an outlier x20 (act_test.cpp:104-120's recipe)
+    n = 1536
+    mag = 10.0 ** g.uniform(-6, 3, size=(n, 1))
+    x = g.standard_normal((n, 32)) * mag
+    x = np.where(g.random((n, 32)) < 1 / 64, x * 20, x)
+    out.append(x.astype(np.float32))
+    # all zeros; one large value; one tiny value
+    z = np.zeros((4, 32), np.float32)
+    z[1, 7] = 1000.0
+    z[2, 31] = -3.5e-5
+    z[3, 0] = 65504.0 * 127
+    out.append(z)
+    # exact rounding midpoints: amax 127 -> id 1 (x = k + 0.5); amax 254 -> id 0.5 (x = 2k + 1)
+    m = np.zeros((4, 32), np.float32)
+    m[0, :] = np.arange(32) + 0.5
+    m[0, 31] = 127.0
+    m[1, :] = -(np.arange(32) + 0.5)
+    m[1, 31] = -127.0
+    m[2, :] = 2 * np.arange(32) + 1
+    m[2, 31] = 254.0
+    m[3, :] = -(2 * np.arange(32) + 1)
+    m[3, 0] = 254.0
+    out.append(m)
+    # the reference's KV8 stress rows (kv_q8_ref.cpp:99-169): half steps, FP16-subnormal scales, scale underflow,
+    # F32 subnormal inputs, magnitudes up to 127 x 65504, random ranges
+    r = O.ref()
+    cnt = r.ref_kv_q8_stress_rows(C.c_uint64(0x464E464C + 8), C.c_int32(16), None, C.c_int64(0))
+    buf = np.empty(cnt, np.float32)
+    r.ref_kv_q8_stress_rows(C.c_uint64(0x464E464C + 8), C.c_int32(16), O._p(buf), C.c_int64(cnt))
+    out.append(buf.reshape(-1, 32))
+    x = np.concatenate(out, 0)
+    assert x.shape[0] % 2 == 0
+    return np.ascontiguousarray(x)
+
+
+def main() -> None:
+    O.build(with_ref=True)
+    r = O.ref()
+    x = stress_blocks()
+    n = x.shape[0]
+    q80 = np.empty(n * 34, np.uint8)
+    q81 = np.empty(n * 36, np.uint8)
+    r.quantize_row_q8_0_ref(O._p(x), O._p(q80), C.c_int64(x.size))
+    r.quantize_row_q8_1_ref(O._p(x), O._p(q81), C.c_int64(x.size))
+    codes = np.empty((n, 32), np.int8)
+    scales = np.empty((n, 2), np.float32)
+    r.ref_act_quantize(O._p(x), C.c_int32(n), C.c_int32(32), O._p(codes), O._p(scales))
+    kv_codes = np.empty(x.size, np.int8)
+    kv_scales = np.empty(x.size // 64, np.uint16)
+    r.ref_kv_q8_quantize(O._p(x), C.c_int32(x.size), O._p(kv_codes), O._p(kv_scales))
+    np.savez_compressed(os.path.join(HERE, "quant.npz"), x=x, q8_0=q80.reshape(n, 34), q8_1=q81.reshape(n, 36),
+                        act_codes=codes, act_scales=scales, kv8_codes=kv_codes.reshape(-1, 64), kv8_scales=kv_scales)
+
+    dec = {}
+    nblk = 96
+    for i, (fmt, bb, bv, fn) in enumerate((("q4_k", 144, 256, r.dequantize_row_q4_K),
+                                           ("iq3_xxs", 98, 256, r.dequantize_row_iq3_xxs),
+                                           ("q8_0", 34, 32, r.dequantize_row_q8_0))):
+        blk = np.empty(nblk * bb, np.uint8)
+        assert r.ref_synth_blocks(fmt.encode(), C.c_uint64(0x464E464C + i), C.c_int64(nblk), O._p(blk)) == 0
+        y = np.empty(nblk * bv, np.float32)
+        fn(O._p(blk), O._p(y), C.c_int64(y.size))
+        y2 = np.empty_like(y)
+        assert r.ref_decode_row(fmt.encode(), O._p(blk), O._p(y2), C.c_int64(y.size)) == 0
+        assert np.array_equal(y.view(np.uint32), y2.view(np.uint32)), fmt  # two in-tree statements agree
+        dec[fmt + "_blocks"] = blk.reshape(nblk, bb)
+        dec[fmt + "_values"] = y.reshape(nblk, bv)
+    np.savez_compressed(os.path.join(HERE, "decode.npz"), **dec)
+    for f in ("quant.npz", "decode.npz"):
+        print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,92 @@
+"""The C-ABI library on a machine without a GPU: it loads, exports every symbol include/fnb200.h declares, and
+rejects arguments outside the contract before touching CUDA (nothing enqueued)."""
+import ctypes as C
+import os
+import re
+import subprocess
+
+import numpy as np
+import pytest
+
+from fnfl_v100_b200 import _lib, build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    build.build()
+    return _lib.lib()
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "fnb200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fnb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_what_the_binding_binds():
+    assert declared_symbols() == sorted(_lib.SIGNATURES)
+
+
+def test_library_exports_every_declared_symbol(lib):
+    out = subprocess.run(["nm", "-D", "--defined-only", _lib.LIB_PATH], capture_output=True, text=True, check=True).stdout
+    exported = set(re.findall(r"\bT (fnb_[a-z0-9_]+)$", out, flags=re.M))
+    missing = [s for s in declared_symbols() if s not in exported]
+    assert not missing, missing
+
+
+def test_version_and_status_names(lib):
+    assert lib.fnb_version() >= 100
+    assert _lib.status_name(0) == "ok" and "rejected" in _lib.status_name(1) and "launch" in _lib.status_name(2)
+
+
+def test_theta_scale_is_powf(lib, oracle):
+    assert lib.fnb_rope_theta_scale(1e7, 64) == pytest.approx(oracle.theta_scale(1e7, 64), abs=0)
+
+
+def test_check_tokens(lib):
+    ids = np.array([0, 5, 151935, 151936, -1], np.int32)
+    p = C.c_void_p(ids.ctypes.data)
+    assert lib.fnb_check_tokens(p, 3, 151936) == 0
+    assert lib.fnb_check_tokens(p, 5, 151936) == 4      # 1 + index of the first bad id
+    assert lib.fnb_check_tokens(None, 5, 151936) == -1
+
+
+A16 = 0x7F0000001000   # a 16-byte aligned, never dereferenced address: rejection happens before any launch
+ODD = A16 + 4
+
+
+def test_rejections_enqueue_nothing(lib):
+    R = _lib.REJECTED
+    # rms_norm: null, misaligned, bad shapes
+    assert lib.fnb_rms_norm_f32(None, A16, 1e-6, A16, 4, 2048, None) == R
+    assert lib.fnb_rms_norm_f32(ODD, A16, 1e-6, A16, 4, 2048, None) == R
+    assert lib.fnb_rms_norm_f32(A16, A16, 1e-6, A16, 0, 2048, None) == R
+    assert lib.fnb_rms_norm_f32(A16, A16, 1e-6, A16, 4, 2050, None) == R
+    assert lib.fnb_rms_norm_f32(A16, A16, -1.0, A16, 4, 2048, None) == R
+    assert lib.fnb_rms_norm_heads_f32(A16, A16, 1e-6, A16, 4, 0, 256, None) == R
+    # swiglu / requantisers: cols must be a multiple of 32, pointers 16-byte aligned
+    assert lib.fnb_swiglu_q8_1(A16, A16, A16, None, 8, 48, None) == R
+    assert lib.fnb_swiglu_q8_1(A16, None, A16, None, 8, 512, None) == R
+    assert lib.fnb_swiglu_q8_1(A16, A16, ODD, None, 8, 512, None) == R
+    assert lib.fnb_swiglu_act(A16, A16, A16, None, None, 8, 512, None) == R
+    assert lib.fnb_quantize_q8_1(A16, A16, -3, 512, None) == R
+    assert lib.fnb_quantize_q8_0(None, A16, 3, 512, None) == R
+    assert lib.fnb_act_quantize(A16, A16, ODD + 2, 3, 512, None) == R       # scales need 8-byte alignment
+    # get_rows
+    assert lib.fnb_get_rows_q4_k(A16, 100, A16, A16, None, 8, 2000, None) == R
+    assert lib.fnb_get_rows_q4_k(A16, 0, A16, A16, None, 8, 2048, None) == R
+    assert lib.fnb_get_rows_iq3_xxs(A16, 100, None, A16, None, 8, 2048, None) == R
+    assert lib.fnb_get_rows_q8_0(A16, 100, A16, ODD, None, 8, 2048, None) == R
+    # rope: head_dim, n_rot, null struct
+    assert lib.fnb_rope_neox_q8_0_append(None, None) == R
+    a = _lib.RopeKvArgs(A16, A16, A16, A16, None, None, None, A16, A16, A16, None, None, 4, 64, 16, 2, 256, 64,
+                        0.5, 1e-6)
+    for field, bad in (("head_dim", 96), ("n_rot", 66), ("n_rot", 512), ("rows", 0), ("cache_slots", 0),
+                       ("q", ODD), ("k_cache", None), ("theta_scale", 0.0)):
+        b = _lib.RopeKvArgs.from_buffer_copy(a)
+        setattr(b, field, bad)
+        assert lib.fnb_rope_neox_q8_0_append(C.byref(b), None) == R, field
+    k8 = _lib.RopeKv8Args(a, None, A16)
+    assert lib.fnb_rope_neox_kv8_append(C.byref(k8), None) == R

@@ -1,0 +1,326 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI (fnfl_v100_b200.ops -> libfnb200.so).
+
+Bars: bit-exact for quantised bytes, dequantised embeddings and every F32 value whose CPU definition is a fixed
+sequence of IEEE operations; RMSNorm outputs (whose sum of squares is reduced in a different order than the
+CPU's sequential sum) within 2 ULP.  Outputs are poisoned before each launch and guard rows around them are
+checked afterwards, so an unwritten or overrun value cannot pass.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from fnfl_v100_b200 import ops, synth
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+POISON = 0x5A
+
+
+def to_dev(a, dev):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+
+
+def bits(a):
+    return np.ascontiguousarray(a).view(np.uint32)
+
+
+def ulp_diff(a, b):
+    """Distance in units in the last place between two float32 arrays (same sign assumed where it matters)."""
+    ia = bits(a).astype(np.int64)
+    ib = bits(b).astype(np.int64)
+    ia = np.where(ia & 0x80000000, 0x80000000 - ia, ia)
+    ib = np.where(ib & 0x80000000, 0x80000000 - ib, ib)
+    return np.abs(ia - ib)
+
+
+class Guarded:
+    """A device output with poisoned guard rows before and after the live region."""
+
+    def __init__(self, shape, dtype, dev, guard_rows=2):
+        self.g = guard_rows
+        full = (shape[0] + 2 * guard_rows,) + tuple(shape[1:])
+        self.full = torch.empty(full, dtype=torch.uint8 if dtype == torch.uint8 else dtype, device=dev)
+        self.full.view(torch.uint8).fill_(POISON)
+        self.live = self.full[guard_rows:guard_rows + shape[0]]
+
+    def check_guards(self):
+        raw = self.full.view(torch.uint8).reshape(self.full.shape[0], -1)
+        assert bool((raw[: self.g] == POISON).all()) and bool((raw[-self.g:] == POISON).all()), "guard rows overwritten"
+
+    def numpy(self):
+        return self.live.cpu().numpy()
+
+
+# ---- RMSNorm ---------------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("rows,cols", [(512, 2048), (1, 2048), (7, 2048), (33, 256), (1030, 256), (5, 128),
+                                       (9, 512), (6, 1024), (3, 2560), (3, 4096), (5, 320), (4, 36), (2, 8192)])
+def test_rms_norm_matches_oracle(dev, oracle, rows, cols):
+    g = synth.rng(1)
+    x = synth.normal(g, (rows, cols))
+    w = synth.norm_weight(g, cols)
+    out = Guarded((rows, cols), torch.float32, dev)
+    ops.rms_norm(to_dev(x, dev), to_dev(w, dev), 1e-6, out=out.live)
+    torch.cuda.synchronize()
+    want = oracle.rms_norm(x, w, 1e-6)
+    got = out.numpy()
+    out.check_guards()
+    d = ulp_diff(got, want)
+    assert d.max() <= 2, f"max ulp {d.max()}"
+    assert (d == 0).mean() >= 0.9999
+
+
+def test_rms_norm_without_weight_and_heads_form(dev, oracle):
+    g = synth.rng(1)
+    x = synth.normal(g, (40, 16, 256), 3.0)
+    w = synth.norm_weight(g, 256)
+    got = ops.rms_norm_heads(to_dev(x, dev), to_dev(w, dev), 1e-6).cpu().numpy()
+    assert ulp_diff(got, oracle.rms_norm(x, w, 1e-6)).max() <= 2
+    got = ops.rms_norm(to_dev(x, dev), None, 1e-6).cpu().numpy()
+    assert ulp_diff(got, oracle.rms_norm(x, None, 1e-6)).max() <= 2
+
+
+# ---- SwiGLU + Q8_1 and the requantisers ------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("rows,cols", [(2048, 512), (1, 32), (7, 96), (33, 320), (50, 320), (3, 2048), (129, 512)])
+def test_swiglu_q8_1_bytes_and_f32_bit_exact(dev, oracle, rows, cols):
+    g = synth.rng(3)
+    gate, up = synth.normal(g, (rows, cols), 0.5), synth.normal(g, (rows, cols), 0.5)
+    out = Guarded((rows, cols // 32 * 36), torch.uint8, dev)
+    f32 = Guarded((rows, cols), torch.float32, dev)
+    ops.swiglu_q8_1(to_dev(gate, dev), to_dev(up, dev), out=out.live, out_f32=f32.live)
+    torch.cuda.synchronize()
+    want, want_f32 = oracle.swiglu_q8_1(gate, up, want_f32=True)
+    got, got_f32 = out.numpy(), f32.numpy()
+    out.check_guards()
+    f32.check_guards()
+    assert np.array_equal(bits(got_f32), bits(want_f32)), "F32 GLU differs from the CPU definition"
+    # the reference's protocol: codes are the CPU quantiser of the kernel's own F32 ...
+    assert np.array_equal(got.reshape(-1), oracle.quantize_q8_1(got_f32))
+    # ... and end to end against the all-CPU oracle the mismatch count is zero
+    assert int((got != want).sum()) == 0
+    # without the optional F32 output the bytes are the same
+    out2 = ops.swiglu_q8_1(to_dev(gate, dev), to_dev(up, dev)).cpu().numpy()
+    assert np.array_equal(out2, want)
+
+
+def test_swiglu_extreme_gates(dev, oracle):
+    gate = np.array([[-200.0, -104.0, -103.5, -90.0, -88.0, -20.0, -1e-3, 0.0, 1e-30, 20.0, 88.0, 89.0, 100.0, 3e4,
+                      -3e4, 1.0] * 2], np.float32)
+    up = np.ones_like(gate)
+    f32 = torch.empty((1, 32), dtype=torch.float32, device=dev)
+    got = ops.swiglu_q8_1(to_dev(gate, dev), to_dev(up, dev), out_f32=f32).cpu().numpy()
+    want, want_f32 = oracle.swiglu_q8_1(gate, up, want_f32=True)
+    assert np.array_equal(bits(f32.cpu().numpy()), bits(want_f32))
+    assert np.array_equal(got, want)
+
+
+def test_requantisers_match_reference_golden_bytes(dev, oracle):
+    """Inputs and expected bytes were produced by the reference's own quantize_row_q8_0_ref / _q8_1_ref and
+    act_quantize_ref (tests/golden/make_golden.py): midpoints, zeros, subnormals, 127 x 65504, random runs."""
+    gold = np.load(os.path.join(GOLD, "quant.npz"))
+    x = to_dev(gold["x"], dev)
+    assert np.array_equal(ops.quantize_q8_0(x).cpu().numpy(), gold["q8_0"])
+    assert np.array_equal(ops.quantize_q8_1(x).cpu().numpy(), gold["q8_1"])
+    codes, scales = ops.act_quantize(x)
+    assert np.array_equal(codes.cpu().numpy(), gold["act_codes"])
+    assert np.array_equal(bits(scales.cpu().numpy().reshape(-1, 2)), bits(gold["act_scales"]))
+
+
+def test_swiglu_act_format_matches_oracle(dev, oracle):
+    g = synth.rng(3)
+    gate, up = synth.normal(g, (50, 320), 0.5), synth.normal(g, (50, 320), 0.5)
+    codes, scales = ops.swiglu_act(to_dev(gate, dev), to_dev(up, dev))
+    wc, ws, _ = oracle.swiglu_act(gate, up)
+    assert np.array_equal(codes.cpu().numpy(), wc)
+    assert np.array_equal(bits(scales.cpu().numpy()), bits(ws))
+
+
+# ---- RoPE + KV append ------------------------------------------------------------------------------------------------
+
+def _rope_case(g, rows, nq, nkv, hd, norm):
+    q, k, v = synth.normal(g, (rows, nq, hd)), synth.normal(g, (rows, nkv, hd)), synth.normal(g, (rows, nkv, hd))
+    wq = synth.norm_weight(g, hd) if norm else None
+    wk = synth.norm_weight(g, hd) if norm else None
+    return q, k, v, wq, wk
+
+
+@pytest.mark.parametrize("rows,nq,nkv,hd,n_rot,norm", [
+    (256, 16, 2, 256, 64, False),   # the rope + KV configuration, reduced rows
+    (256, 16, 2, 256, 64, True),    # with the per-head Q/K norm fused, as the chain runs it
+    (1, 16, 2, 256, 64, True), (7, 12, 1, 256, 64, True), (33, 3, 1, 256, 256, False), (5, 4, 4, 256, 0, True),
+    (19, 8, 2, 128, 64, True), (19, 8, 2, 64, 32, False), (3, 40, 2, 256, 64, False),
+])
+def test_rope_kv_append_matches_oracle(dev, oracle, rows, nq, nkv, hd, n_rot, norm):
+    g = synth.rng(2)
+    q, k, v, wq, wk = _rope_case(g, rows, nq, nkv, hd, norm)
+    slots_total = 4096
+    pos = synth.positions(g, rows)                       # offsets up to 258 048: the large-argument sin/cos path
+    slot = (g.permutation(slots_total - 8)[:rows] + 4).astype(np.int32)
+    ts = oracle.theta_scale(1e7, max(n_rot, 2))
+    cell = hd // 32 * 34
+    kc = Guarded((slots_total, nkv, cell), torch.uint8, dev)
+    vc = Guarded((slots_total, nkv, cell), torch.uint8, dev)
+    qo = Guarded((rows, nq, hd), torch.float32, dev)
+    kf = Guarded((rows, nkv, hd), torch.float32, dev)
+    err = ops.new_err(dev)
+    D = lambda a: None if a is None else to_dev(a, dev)  # noqa: E731
+    ops.rope_neox_q8_0_append(D(q), D(k), D(v), D(pos), n_rot=n_rot, theta_scale=ts, k_cache=kc.live, v_cache=vc.live,
+                              slots=D(slot), q_norm_w=D(wq), k_norm_w=D(wk), q_out=qo.live, k_f32=kf.live, err=err)
+    torch.cuda.synchronize()
+    wkc = np.full((slots_total, nkv, cell), POISON, np.uint8)
+    wvc = wkc.copy()
+    wq_out, wk_f32, werr = oracle.rope_kv_append(q, k, v, pos, n_rot=n_rot, theta_scale=ts, k_cache=wkc, v_cache=wvc,
+                                                 cache_slots=slots_total, slots=slot, q_norm_w=wq, k_norm_w=wk,
+                                                 want_k_f32=True)
+    assert int(err.item()) == werr == 0
+    for o in (kc, vc, qo, kf):
+        o.check_guards()
+    got_q, got_k = qo.numpy(), kf.numpy()
+    if norm:
+        assert ulp_diff(got_q, wq_out).max() <= 2 and ulp_diff(got_k, wk_f32).max() <= 2
+        assert (ulp_diff(got_q, wq_out) == 0).mean() >= 0.9999
+    else:
+        assert np.array_equal(bits(got_q), bits(wq_out)), "rope output differs from the CPU definition"
+        assert np.array_equal(bits(got_k), bits(wk_f32))
+    # V cells are bit-exact unconditionally; K cells are the CPU quantiser of the kernel's own F32 k, and equal
+    # the all-CPU oracle's bytes end to end
+    assert np.array_equal(vc.numpy(), wvc)
+    assert np.array_equal(kc.numpy()[slot].reshape(-1), oracle.quantize_q8_0(got_k))
+    assert int((kc.numpy() != wkc).sum()) == 0
+
+
+def test_rope_slot_is_position_by_default_and_bad_slot_is_flagged(dev, oracle):
+    g = synth.rng(2)
+    q, k, v, _, _ = _rope_case(g, 6, 4, 2, 256, False)
+    pos = np.array([10, 11, 70000, 12, -1, 13], np.int32)   # 70000 and -1 are outside a 64-slot cache
+    ts = oracle.theta_scale(1e7, 64)
+    kc = Guarded((64, 2, 272), torch.uint8, dev)
+    vc = Guarded((64, 2, 272), torch.uint8, dev)
+    qo = Guarded((6, 4, 256), torch.float32, dev)
+    err = ops.new_err(dev)
+    ops.rope_neox_q8_0_append(to_dev(q, dev), to_dev(k, dev), to_dev(v, dev), to_dev(pos, dev), n_rot=64,
+                              theta_scale=ts, k_cache=kc.live, v_cache=vc.live, q_out=qo.live, err=err)
+    torch.cuda.synchronize()
+    wkc = np.full((64, 2, 272), POISON, np.uint8)
+    wvc = wkc.copy()
+    wq = np.full((6, 4, 256), 0, np.float32)
+    wq.view(np.uint8)[:] = POISON
+    wq, _, werr = oracle.rope_kv_append(q, k, v, pos, n_rot=64, theta_scale=ts, k_cache=wkc, v_cache=wvc,
+                                        cache_slots=64, q_out=wq)
+    assert int(err.item()) == werr == ops.ERR_SLOT
+    assert np.array_equal(kc.numpy(), wkc) and np.array_equal(vc.numpy(), wvc)
+    assert np.array_equal(bits(qo.numpy()), bits(wq))       # rows 2 and 4 stay poisoned in both
+    for o in (kc, vc, qo):
+        o.check_guards()
+
+
+def test_rope_kv8_format_matches_reference_rule(dev, oracle):
+    g = synth.rng(2)
+    rows, nq, nkv, hd = 64, 12, 1, 256
+    q, k, v, wq, wk = _rope_case(g, rows, nq, nkv, hd, True)
+    # V rows: the reference's own KV8 stress rows (half steps, FP16-subnormal scales, underflow, huge magnitudes)
+    gold = np.load(os.path.join(GOLD, "quant.npz"))
+    stress = gold["x"].reshape(-1)[-(rows * hd):].reshape(rows, nkv, hd)
+    v = np.ascontiguousarray(stress)
+    pos = synth.positions(g, rows, 4096 - rows)
+    ts = oracle.theta_scale(1e7, 64)
+    kc, ks = ops.new_kv_cache(4096, nkv, hd, dev, fmt="kv8")
+    vc, vs = ops.new_kv_cache(4096, nkv, hd, dev, fmt="kv8")
+    kf = torch.empty((rows, nkv, hd), dtype=torch.float32, device=dev)
+    ops.rope_neox_kv8_append(to_dev(q, dev), to_dev(k, dev), to_dev(v, dev), to_dev(pos, dev), n_rot=64,
+                             theta_scale=ts, k_cache=kc, v_cache=vc, k_scale=ks, v_scale=vs, q_norm_w=to_dev(wq, dev),
+                             k_norm_w=to_dev(wk, dev), k_f32=kf)
+    torch.cuda.synchronize()
+    got_k = kf.cpu().numpy()
+    wc, wsc = oracle.kv8_quantize(got_k)
+    pos = torch.from_numpy(pos).long().to(dev)
+    assert np.array_equal(kc[pos].cpu().numpy().reshape(-1), wc)
+    assert np.array_equal(ks[pos].cpu().numpy().view(np.uint16).reshape(-1), wsc)
+    wc, wsc = oracle.kv8_quantize(v)
+    assert np.array_equal(vc[pos].cpu().numpy().reshape(-1), wc)
+    assert np.array_equal(vs[pos].cpu().numpy().view(np.uint16).reshape(-1), wsc)
+
+
+# ---- get_rows ----------------------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("fmt,cols,vocab,rows", [
+    ("q4_k", 2048, 1000, 777), ("iq3_xxs", 2048, 1000, 777), ("q8_0", 2048, 500, 300),
+    ("q4_k", 256, 64, 1), ("q4_k", 4096, 64, 7), ("q4_k", 2560, 64, 33), ("iq3_xxs", 4096, 64, 33),
+    ("q8_0", 1280, 64, 5), ("q8_0", 32, 64, 9),
+])
+def test_get_rows_bit_exact_and_bad_ids(dev, oracle, fmt, cols, vocab, rows):
+    g = synth.rng(4)
+    table = {"q4_k": synth.q4_k_table, "iq3_xxs": synth.iq3_xxs_table, "q8_0": synth.q8_0_table}[fmt](g, vocab, cols)
+    ids = g.integers(0, vocab, rows).astype(np.int32)
+    if rows >= 5:
+        ids[1], ids[rows - 2] = -1, vocab        # out of range on both sides
+    out = Guarded((rows, cols), torch.float32, dev)
+    err = ops.new_err(dev)
+    ops.get_rows(fmt, to_dev(table, dev), to_dev(ids, dev), cols, out=out.live, err=err)
+    torch.cuda.synchronize()
+    if fmt == "q8_0":
+        want = np.zeros((rows, cols), np.float32)
+        want.view(np.uint8)[:] = POISON
+        werr = 0
+        for t, i in enumerate(ids):
+            if 0 <= i < vocab:
+                want[t] = oracle.dequantize_q8_0(table[i])
+            else:
+                werr = oracle.ERR_TOKEN
+    else:
+        want = np.zeros((rows, cols), np.float32)
+        want.view(np.uint8)[:] = POISON
+        want, werr = oracle.get_rows(fmt, table, vocab, ids, cols, want)
+    out.check_guards()
+    assert int(err.item()) == werr
+    assert np.array_equal(bits(out.numpy()), bits(want))
+
+
+def test_get_rows_matches_reference_golden_decode(dev):
+    """Blocks generated by the reference's fn::quant::synth_blocks and decoded by its dequantize_row_* (golden)."""
+    gold = np.load(os.path.join(GOLD, "decode.npz"))
+    for fmt, bv, per_row in (("q4_k", 256, 8), ("iq3_xxs", 256, 8), ("q8_0", 32, 8)):
+        blocks, values = gold[fmt + "_blocks"], gold[fmt + "_values"]
+        n_rows = blocks.shape[0] // per_row
+        table = blocks.reshape(n_rows, -1)
+        ids = np.arange(n_rows - 1, -1, -1).astype(np.int32)
+        got = ops.get_rows(fmt, to_dev(table, dev), to_dev(ids, dev), per_row * bv).cpu().numpy()
+        want = values.reshape(n_rows, per_row * bv)[ids]
+        assert np.array_equal(bits(got), bits(want)), fmt
+
+
+# ---- the chain, and graph replay -----------------------------------------------------------------------------------
+
+def test_chain_matches_oracle_and_replays_in_a_graph(dev, oracle):
+    from fnfl_v100_b200 import ChainConfig, PrefillChain
+    cfg = ChainConfig(tokens=96, n_vocab=512, cache_slots=1024, depth=700, top_k=10)
+    ch = PrefillChain(cfg, dev)
+    ch.step()
+    torch.cuda.synchronize()
+    H = lambda t: t.cpu().numpy()  # noqa: E731
+    hidden, err = oracle.get_rows("q4_k", H(ch.table), cfg.n_vocab, H(ch.ids), cfg.hidden)
+    assert err == 0 and int(ch.err.item()) == 0
+    assert np.array_equal(bits(H(ch.hidden)), bits(hidden))
+    assert ulp_diff(H(ch.normed_attn), oracle.rms_norm(hidden, H(ch.w_attn), cfg.eps)).max() <= 2
+    assert ulp_diff(H(ch.normed_ffn), oracle.rms_norm(hidden, H(ch.w_ffn), cfg.eps)).max() <= 2
+    kc = np.zeros((cfg.cache_slots, cfg.n_kv_heads, 272), np.uint8)
+    vc = np.zeros_like(kc)
+    q_out, _, werr = oracle.rope_kv_append(H(ch.q), H(ch.k), H(ch.v), H(ch.pos), n_rot=cfg.n_rot,
+                                           theta_scale=ch.theta_scale, k_cache=kc, v_cache=vc,
+                                           cache_slots=cfg.cache_slots, q_norm_w=H(ch.w_q), k_norm_w=H(ch.w_k))
+    assert werr == 0
+    assert ulp_diff(H(ch.q_out), q_out).max() <= 2
+    assert np.array_equal(H(ch.k_cache), kc) and np.array_equal(H(ch.v_cache), vc)
+    assert np.array_equal(H(ch.act), oracle.swiglu_q8_1(H(ch.gate), H(ch.up)))
+    # one graph replay over poisoned outputs reproduces the same bytes
+    snap = [H(t).copy() for t in (ch.hidden, ch.normed_attn, ch.q_out, ch.k_cache, ch.act)]
+    graph = ch.capture()
+    for t in (ch.hidden, ch.normed_attn, ch.q_out, ch.act):
+        t.view(torch.uint8).fill_(POISON)
+    graph.replay()
+    torch.cuda.synchronize()
+    for a, t in zip(snap, (ch.hidden, ch.normed_attn, ch.q_out, ch.k_cache, ch.act)):
+        assert np.array_equal(a.view(np.uint8), H(t).view(np.uint8))

@@ -1,0 +1,119 @@
+"""The CPU oracle against the golden vectors recorded from the reference's own CPU sources
+(tests/golden/make_golden.py) and, where the reference build is present, against that build directly."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+@pytest.fixture(scope="module")
+def quant():
+    return np.load(os.path.join(GOLD, "quant.npz"))
+
+
+@pytest.fixture(scope="module")
+def decode():
+    return np.load(os.path.join(GOLD, "decode.npz"))
+
+
+def test_q8_0_matches_reference_bytes(oracle, quant):
+    got = oracle.quantize_q8_0(quant["x"]).reshape(-1, 34)
+    assert np.array_equal(got, quant["q8_0"])
+
+
+def test_q8_1_matches_reference_bytes(oracle, quant):
+    got = oracle.quantize_q8_1(quant["x"]).reshape(-1, 36)
+    assert np.array_equal(got, quant["q8_1"])
+
+
+def test_act_format_matches_reference(oracle, quant):
+    codes, scales = oracle.act_quantize(quant["x"])
+    assert np.array_equal(codes, quant["act_codes"])
+    assert np.array_equal(scales.reshape(-1, 2).view(np.uint32), quant["act_scales"].view(np.uint32))
+
+
+def test_kv8_matches_reference(oracle, quant):
+    codes, scales = oracle.kv8_quantize(quant["x"])
+    assert np.array_equal(codes.reshape(-1, 64), quant["kv8_codes"])
+    assert np.array_equal(scales, quant["kv8_scales"])
+
+
+@pytest.mark.parametrize("fmt", ["q4_k", "iq3_xxs", "q8_0"])
+def test_decoders_match_reference_bits(oracle, decode, fmt):
+    fn = {"q4_k": oracle.dequantize_q4_k, "iq3_xxs": oracle.dequantize_iq3_xxs, "q8_0": oracle.dequantize_q8_0}[fmt]
+    got = fn(decode[fmt + "_blocks"])
+    assert np.array_equal(got.view(np.uint32), decode[fmt + "_values"].reshape(-1).view(np.uint32))
+
+
+def test_q8_midpoints_round_half_away(oracle):
+    # amax 127 -> d = 1, id = 1: x = k + 0.5 must round away from zero (roundf), not to even
+    x = np.zeros(32, np.float32)
+    x[:8] = [0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 126.5, 127.0]
+    b = oracle.quantize_q8_0(x)
+    assert list(b[2:10].view(np.int8)) == [1, 2, 3, -1, -2, -3, 127, 127]
+    assert b[:2].view(np.uint16)[0] == 0x3C00  # d = 1.0
+
+
+def test_q8_1_sum_field(oracle):
+    g = np.random.default_rng(3)
+    x = g.standard_normal(32 * 50).astype(np.float32)
+    b = oracle.quantize_q8_1(x).reshape(-1, 36)
+    for blk, xs in zip(b, x.reshape(-1, 32)):
+        d = np.float32(np.abs(xs).max()) / np.float32(127)
+        s = np.float32(int(blk[4:].view(np.int8).astype(np.int32).sum())) * d
+        assert blk[2:4].view(np.uint16)[0] == np.float32(s).astype(np.float16).view(np.uint16)
+
+
+def test_get_rows_is_row_decode_and_flags_bad_ids(oracle, decode):
+    blocks = decode["q4_k_blocks"]            # 96 blocks = 12 rows of 2048
+    table = blocks.reshape(12, 8 * 144)
+    ids = np.array([3, 0, 11, -1, 12, 7], np.int32)
+    out = np.full((6, 2048), 7.0, np.float32)
+    out, err = oracle.get_rows("q4_k", table, 12, ids, 2048, out)
+    vals = decode["q4_k_values"].reshape(12, 2048)
+    assert err == oracle.ERR_TOKEN
+    for t, i in enumerate(ids):
+        if 0 <= i < 12:
+            assert np.array_equal(out[t], vals[i])
+        else:
+            assert np.all(out[t] == 7.0)      # unwritten
+
+
+def test_f16_conversion_against_numpy(oracle):
+    g = np.random.default_rng(5)
+    x = np.concatenate([g.standard_normal(2000) * 10.0 ** g.uniform(-9, 6, 2000),
+                        [0.0, -0.0, 65504.0, 65519.9, 65520.0, 1e9, 2.0 ** -24, 2.0 ** -25, 2.0 ** -25 * 1.0001,
+                         6.1e-5, 5.96e-8]]).astype(np.float32)
+    with np.errstate(over="ignore"):
+        want = x.astype(np.float16).view(np.uint16)
+    assert np.array_equal(oracle.f32_to_f16_bits(x), want)
+    h = np.arange(0, 0x7C00, 7, dtype=np.uint16)
+    assert np.array_equal(oracle.f16_bits_to_f32(h), h.view(np.float16).astype(np.float32))
+    assert oracle.lib().fnbo_f32_to_f16(float("nan")) & 0x7FFF == 0x7E00
+
+
+@pytest.mark.skipif(not __import__("oracle.oracle", fromlist=["x"]).have_ref(), reason="reference build absent")
+def test_oracle_equals_live_reference_build(oracle):
+    """Wider than the fixtures: 20k random blocks through the reference library itself."""
+    r = oracle.ref()
+    g = np.random.default_rng(11)
+    x = (g.standard_normal(32 * 20000) * 10.0 ** g.uniform(-5, 4, 32 * 20000)).astype(np.float32)
+    a = oracle.quantize_q8_0(x)
+    b = np.empty_like(a)
+    r.quantize_row_q8_0_ref(oracle._p(x), oracle._p(b), C.c_int64(x.size))
+    assert np.array_equal(a, b)
+    a = oracle.quantize_q8_1(x)
+    b = np.empty_like(a)
+    r.quantize_row_q8_1_ref(oracle._p(x), oracle._p(b), C.c_int64(x.size))
+    assert np.array_equal(a, b)
+    from fnfl_v100_b200 import synth
+    for fmt, mk, dq, fn in (("q4_k", synth.q4_k_table, oracle.dequantize_q4_k, r.dequantize_row_q4_K),
+                            ("iq3_xxs", synth.iq3_xxs_table, oracle.dequantize_iq3_xxs, r.dequantize_row_iq3_xxs)):
+        t = mk(synth.rng(4), 256, 2048)
+        a = dq(t)
+        b = np.empty_like(a)
+        fn(oracle._p(t), oracle._p(b), C.c_int64(a.size))
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32)), fmt
