@@ -16,46 +16,50 @@ namespace fnb {
 
 static __constant__ unsigned long long c_exp2_tab[32] = FNB_EXP2_TABLE_INIT;
 static __constant__ uint32_t c_inv_pio4[24] = FNB_INV_PIO4_INIT;
+// expf's double constants live in constant memory so the FP64 instructions read them as constant-bank
+// operands instead of rebuilding 64-bit immediates in registers for every value:
+// N / ln2, the 1.5 * 2^52 rounding shift, and the cubic's coefficients scaled by 1 / N^3, 1 / N^2, 1 / N (N = 32)
+static __constant__ double c_exp_k[5] = {0x1.71547652b82fep+0 * 32.0, 0x1.8p+52, 0x1.c6af84b912394p-5 / 32768.0,
+                                         0x1.ebfce50fac4f3p-3 / 1024.0, 0x1.62e42ff0c52d6p-1 / 32.0};
 
-// The table lookup index varies per lane, so kernels stage the 256-byte table in shared memory
-// (constant memory would serialise divergent indices) and pass the shared pointer here.
-__device__ __forceinline__ void load_exp2_table(unsigned long long * smem_tab) {
-    for (int i = threadIdx.x; i < 32; i += blockDim.x) smem_tab[i] = c_exp2_tab[i];
+// The 2^(i/32) table is indexed per lane, so it is staged in shared memory (constant memory would serialise
+// divergent indices).  A kernel that calls exact_expf / expf_core runs load_exp2_table and a block barrier first.
+static __shared__ unsigned long long s_exp2_tab[32];
+
+__device__ __forceinline__ void load_exp2_table() {
+    for (int i = threadIdx.x; i < 32; i += blockDim.x) s_exp2_tab[i] = c_exp2_tab[i];
 }
 
-static __device__ __noinline__ float expf_rare(float x) {
+// e^x for |x| < 88 (no overflow, underflow or NaN handling): 12 FP64 operations, two conversions
+__device__ __forceinline__ float expf_core(float x) {
+    const double z = __dmul_rn(c_exp_k[0], double(x));
+    double kd = __dadd_rn(z, c_exp_k[1]);
+    const unsigned long long ki = (unsigned long long) __double_as_longlong(kd);
+    kd = __dsub_rn(kd, c_exp_k[1]);
+    const double r = __dsub_rn(z, kd);
+    const unsigned long long t = s_exp2_tab[ki & 31] + (ki << 47);
+    const double s = __longlong_as_double((long long) t);
+    const double p = __dadd_rn(__dmul_rn(c_exp_k[2], r), c_exp_k[3]);
+    const double r2 = __dmul_rn(r, r);
+    double y = __dadd_rn(__dmul_rn(c_exp_k[4], r), 1.0);
+    y = __dadd_rn(__dmul_rn(p, r2), y);
+    y = __dmul_rn(y, s);
+    return __double2float_rn(y);
+}
+
+static __device__ __noinline__ float expf_special(float x) {
     const uint32_t bits = __float_as_uint(x);
     if (bits == 0xff800000u) return 0.0f;
     if ((bits & 0x7fffffffu) >= 0x7f800000u) return __fadd_rn(x, x);
     if (x > 0x1.62e42ep6f) return __uint_as_float(0x7f800000u);
     if (x < -0x1.9fe368p6f) return 0.0f;
     if (x < -0x1.9d1d9ep6f) return 0x1p-149f;
-    return -1.0f;  // not a special case after all: tell the caller to take the main path
+    return expf_core(x);
 }
 
-__device__ __forceinline__ float exact_expf(float x, const unsigned long long * tab) {
-    if ((__float_as_uint(x) & 0x7fffffffu) >= 0x42b00000u) {  // |x| >= 88 or NaN
-        const float r = expf_rare(x);
-        if (r != -1.0f) return r;
-    }
-    const double inv_ln2_n = 0x1.71547652b82fep+0 * 32.0;
-    const double shift = 0x1.8p+52;
-    const double c0 = 0x1.c6af84b912394p-5 / 32.0 / 32.0 / 32.0;
-    const double c1 = 0x1.ebfce50fac4f3p-3 / 32.0 / 32.0;
-    const double c2 = 0x1.62e42ff0c52d6p-1 / 32.0;
-    const double z = __dmul_rn(inv_ln2_n, double(x));
-    double kd = __dadd_rn(z, shift);
-    const unsigned long long ki = (unsigned long long) __double_as_longlong(kd);
-    kd = __dsub_rn(kd, shift);
-    const double r = __dsub_rn(z, kd);
-    const unsigned long long t = tab[ki & 31] + (ki << 47);
-    const double s = __longlong_as_double((long long) t);
-    const double p = __dadd_rn(__dmul_rn(c0, r), c1);
-    const double r2 = __dmul_rn(r, r);
-    double y = __dadd_rn(__dmul_rn(c2, r), 1.0);
-    y = __dadd_rn(__dmul_rn(p, r2), y);
-    y = __dmul_rn(y, s);
-    return __double2float_rn(y);
+// e^x for every float, special cases included
+__device__ __forceinline__ float exact_expf(float x) {
+    return (__float_as_uint(x) & 0x7fffffffu) >= 0x42b00000u ? expf_special(x) : expf_core(x);  // |x| >= 88 or NaN
 }
 
 // sine polynomial on the reduced argument

@@ -17,7 +17,9 @@ namespace fnb {
 namespace {
 
 __device__ __forceinline__ float norm_scale(double sum, int cols, float eps) {
-    const float mean = __double2float_rn(__ddiv_rn(sum, double(cols)));
+    // sum / cols; for a power-of-two cols the product with the exact reciprocal is the same double and much cheaper
+    const double m = (cols & (cols - 1)) == 0 ? __dmul_rn(sum, 1.0 / double(cols)) : __ddiv_rn(sum, double(cols));
+    const float mean = __double2float_rn(m);
     return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
 }
 

@@ -16,11 +16,10 @@
 // Cells are assembled in shared memory and leave as aligned 128-bit stores.
 #include "common.cuh"
 #include "exact_math.cuh"
+#include "rope_kv.cuh"
 
 namespace fnb {
 namespace {
-
-enum class kv_fmt { q8_0, kv8 };
 
 template <int EPL>
 struct row_regs {
@@ -62,7 +61,7 @@ __device__ __forceinline__ void head_norm(row_regs<EPL> & r, const float * __res
 #pragma unroll
     for (int e = 0; e < EPL; ++e) acc = __dadd_rn(acc, double(__fmul_rn(r.v[e], r.v[e])));
     acc = warp_sum_f64(acc);
-    const float mean = __double2float_rn(__ddiv_rn(acc, double(32 * EPL)));
+    const float mean = __double2float_rn(__dmul_rn(acc, 1.0 / double(32 * EPL)));  // a power of two: exact, as the division is
     const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
 #pragma unroll
     for (int e = 0; e < EPL; ++e) r.v[e] = __fmul_rn(__fmul_rn(r.v[e], scale), __ldg(w + lane * EPL + e));
@@ -101,8 +100,7 @@ __device__ __forceinline__ void put_q8_0(const row_regs<EPL> & r, uint8_t * dst,
     if (pos == 0) s16[0] = f32_to_f16_bits(rule.d);
 #pragma unroll
     for (int e = 0; e < EPL; e += 2) {
-        const uint32_t a = rule.code(r.v[e]), b = rule.code(r.v[e + 1]);
-        s16[1 + (pos * EPL + e) / 2] = uint16_t(a | (b << 8));
+        s16[1 + (pos * EPL + e) / 2] = uint16_t(__byte_perm(rule.code(r.v[e]), rule.code(r.v[e + 1]), 0x0040));
     }
     __syncwarp();
     // a 256-wide head is 272 bytes (17 x 16), a 128-wide one 136 (17 x 8), a 64-wide one 68 (17 x 4): the cell's
@@ -151,18 +149,7 @@ __device__ __forceinline__ void put_kv8(const row_regs<EPL> & r, uint8_t * codes
     if (lane % G == 0) scales[lane / G] = sb;
 }
 
-struct kernel_args {
-    const float *q, *k, *v;
-    const int32_t *pos, *slots;
-    const float *q_norm_w, *k_norm_w;
-    float *q_out, *k_f32;
-    uint8_t *k_cache, *v_cache;
-    uint16_t *k_scale, *v_scale;
-    uint32_t * err;
-    int64_t rows, cache_slots;
-    int32_t n_q, n_kv, n_rot;
-    float theta_scale, eps;
-};
+using kernel_args = rope_kernel_args;
 
 constexpr int kMaxWarps = 16;
 
@@ -279,6 +266,8 @@ int32_t launch(const fnb_rope_kv_args * p, uint16_t * k_scale, uint16_t * v_scal
     a.rows = p->rows, a.cache_slots = p->cache_slots;
     a.n_q = p->n_q_heads, a.n_kv = p->n_kv_heads, a.n_rot = p->n_rot;
     a.theta_scale = p->theta_scale, a.eps = p->eps;
+
+    if (rope_kv_pipe_try_launch(a, hd, F, s)) return launch_status();
 
     const int heads = a.n_q + 2 * a.n_kv;
     int warps = (heads + 1) / 2;

@@ -1,0 +1,122 @@
+"""Per-operator timing on synthetic inputs: `python -m fnfl_v100_b200.opbench --op swiglu_q8_1 --tokens 65536`.
+
+Follows the reference's bench protocol (fn/kernels/act/act_bench.cpp:18-22, :60-140): warm launches, then timed
+launches measured with CUDA events on the launching stream, median and p90 reported, cold (inputs rotated over
+more distinct buffers than fit in L2) and hot (same buffers), one JSON line per point with bytes per launch and
+the fraction of the HBM peak.  Small `--tokens` make it the target of an `ncu` capture of one kernel.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from . import ops, synth
+from .chain import ChainConfig
+
+OPS = ("get_rows_q4_k", "get_rows_iq3_xxs", "rms_norm", "rms_norm_heads", "rope_kv", "swiglu_q8_1", "swiglu_act",
+       "rope_kv8", "quantize_q8_1")
+
+
+def hbm_peak() -> float:
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    try:
+        with open(os.path.join(root, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"])
+    except Exception:
+        return 6650.0
+
+
+def make_case(op: str, T: int, dev, gen, c: ChainConfig):
+    """Returns (launch, algorithmic bytes)."""
+    N = synth.torch_normal
+    if op.startswith("get_rows"):
+        fmt = op[len("get_rows_"):]
+        table = synth.torch_table(fmt, gen, c.n_vocab, c.hidden, dev)
+        ids = torch.randint(0, c.n_vocab, (T,), dtype=torch.int32, device=dev, generator=gen)
+        out = torch.empty((T, c.hidden), dtype=torch.float32, device=dev)
+        err = ops.new_err(dev)
+        return (lambda: ops.get_rows(fmt, table, ids, c.hidden, out=out, err=err),
+                T * (ops.table_row_bytes(fmt, c.hidden) + 4 + c.hidden * 4))
+    if op == "rms_norm":
+        x, w = N(gen, (T, c.hidden), 1.0, dev), 1 + 0.1 * N(gen, (c.hidden,), 1.0, dev)
+        y = torch.empty_like(x)
+        return (lambda: ops.rms_norm(x, w, c.eps, out=y)), T * c.hidden * 8 + c.hidden * 4
+    if op == "rms_norm_heads":
+        h = c.n_q_heads + c.n_kv_heads
+        x, w = N(gen, (T, h, c.head_dim), 1.0, dev), 1 + 0.1 * N(gen, (c.head_dim,), 1.0, dev)
+        y = torch.empty_like(x)
+        return (lambda: ops.rms_norm_heads(x, w, c.eps, out=y)), T * h * c.head_dim * 8
+    if op in ("rope_kv", "rope_kv8"):
+        q = N(gen, (T, c.n_q_heads, c.head_dim), 1.0, dev)
+        k = N(gen, (T, c.n_kv_heads, c.head_dim), 1.0, dev)
+        v = N(gen, (T, c.n_kv_heads, c.head_dim), 1.0, dev)
+        wq, wk = 1 + 0.1 * N(gen, (c.head_dim,), 1.0, dev), 1 + 0.1 * N(gen, (c.head_dim,), 1.0, dev)
+        pos = (c.depth + torch.arange(T, device=dev)).to(torch.int32)
+        q_out = torch.empty_like(q)
+        err = ops.new_err(dev)
+        ts = ops.theta_scale(c.freq_base, c.n_rot)
+        io = 2 * c.n_q_heads * c.head_dim * 4 + 2 * c.n_kv_heads * c.head_dim * 4 + 4
+        if op == "rope_kv":
+            kc = ops.new_kv_cache(c.cache_slots, c.n_kv_heads, c.head_dim, dev)
+            vc = ops.new_kv_cache(c.cache_slots, c.n_kv_heads, c.head_dim, dev)
+            cell = c.head_dim // 32 * ops.Q8_0_BLOCK
+            return (lambda: ops.rope_neox_q8_0_append(q, k, v, pos, n_rot=c.n_rot, theta_scale=ts, k_cache=kc,
+                                                      v_cache=vc, q_norm_w=wq, k_norm_w=wk, eps=c.eps, q_out=q_out,
+                                                      err=err)), T * (io + 2 * c.n_kv_heads * cell)
+        kc, ks = ops.new_kv_cache(c.cache_slots, c.n_kv_heads, c.head_dim, dev, fmt="kv8")
+        vc, vs = ops.new_kv_cache(c.cache_slots, c.n_kv_heads, c.head_dim, dev, fmt="kv8")
+        cell = c.head_dim + c.head_dim // 64 * 2
+        return (lambda: ops.rope_neox_kv8_append(q, k, v, pos, n_rot=c.n_rot, theta_scale=ts, k_cache=kc, v_cache=vc,
+                                                 k_scale=ks, v_scale=vs, q_norm_w=wq, k_norm_w=wk, eps=c.eps,
+                                                 q_out=q_out, err=err)), T * (io + 2 * c.n_kv_heads * cell)
+    rows = T * c.top_k
+    gate, up = N(gen, (rows, c.inter), 0.5, dev), N(gen, (rows, c.inter), 0.5, dev)
+    if op == "swiglu_q8_1":
+        out = torch.empty((rows, c.inter // 32 * 36), dtype=torch.uint8, device=dev)
+        return (lambda: ops.swiglu_q8_1(gate, up, out=out)), rows * (c.inter * 8 + c.inter // 32 * 36)
+    if op == "swiglu_act":
+        return (lambda: ops.swiglu_act(gate, up)), rows * (c.inter * 8 + c.inter // 32 * 40)
+    if op == "quantize_q8_1":
+        return (lambda: ops.quantize_q8_1(gate)), rows * (c.inter * 4 + c.inter // 32 * 36)
+    raise SystemExit("unknown op " + op)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", choices=OPS + ("all",), default="all")
+    ap.add_argument("--tokens", type=int, default=65536)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--sets", type=int, default=1, help="distinct input sets rotated between launches (cold when > 1)")
+    args = ap.parse_args()
+    dev = torch.device("cuda:0")
+    peak = hbm_peak()
+    cfg = ChainConfig(tokens=args.tokens)
+    for op in (OPS if args.op == "all" else (args.op,)):
+        gen = synth.torch_gen(dev, 7)
+        cases = [make_case(op, args.tokens, dev, gen, cfg) for _ in range(args.sets)]
+        nbytes = cases[0][1]
+        for i in range(args.warmup):
+            cases[i % args.sets][0]()
+        torch.cuda.synchronize()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.iters)]
+        for i, (a, b) in enumerate(evs):
+            a.record()
+            cases[i % args.sets][0]()
+            b.record()
+        torch.cuda.synchronize()
+        ms = sorted(a.elapsed_time(b) for a, b in evs)
+        med, p90 = ms[len(ms) // 2], ms[min(len(ms) - 1, int(len(ms) * 0.9))]
+        gbs = nbytes / (med * 1e-3) / 1e9
+        print(json.dumps({"op": op, "tokens": args.tokens, "sets": args.sets, "median_ms": round(med, 4),
+                          "p90_ms": round(p90, 4), "min_ms": round(ms[0], 4), "bytes": nbytes, "gbs": round(gbs, 1),
+                          "frac_of_hbm_peak": round(gbs / peak, 4), "tokens_per_s": round(args.tokens / (med * 1e-3))}))
+        del cases
+        torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main()

@@ -34,6 +34,8 @@ extern "C" {
 
 #define FNB_ERR_TOKEN 1u /* a token id outside [0, n_vocab): as fn::xchg::err_token in fn/kernels/embed/embed.h:37 */
 #define FNB_ERR_SLOT 2u  /* a cache slot outside [0, cache_slots): fn/kernels/qsa/attend.h:109-110 */
+#define FNB_ERR_TIMEOUT 4u /* a bounded in-kernel wait gave up (the reference's device waits do the same:
+                              fn/kernels/qsa/attend.cu:264-281); the launch's outputs are incomplete */
 
 #define FNB_Q8_0_BLOCK_BYTES 34
 #define FNB_Q8_1_BLOCK_BYTES 36
@@ -175,6 +177,13 @@ int32_t fnb_get_rows_q8_0(const void * table, int64_t n_vocab, const int32_t * i
  * Replaces fn::embed::check_tokens (fn/kernels/embed/embed.h:56).
  */
 int64_t fnb_check_tokens(const int32_t * ids_host, int64_t rows, int64_t n_vocab);
+
+/*
+ * Diagnostic with no counterpart in the reference: runs the SwiGLU fast path (branch-free expf and the written-out
+ * IEEE division) and the generic path on n pseudo-random (gate, up) pairs covering the fast path's whole domain and
+ * adds the number of results whose bits differ to *mismatches (device memory, 8-byte aligned, caller-zeroed).
+ */
+int32_t fnb_selftest_glu_math(uint64_t n, uint64_t seed, unsigned long long * mismatches, void * stream);
 
 #ifdef __cplusplus
 }

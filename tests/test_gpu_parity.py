@@ -38,7 +38,7 @@ def ulp_diff(a, b):
 class Guarded:
     """A device output with poisoned guard rows before and after the live region."""
 
-    def __init__(self, shape, dtype, dev, guard_rows=2):
+    def __init__(self, shape, dtype, dev, guard_rows=16):   # 16 rows keep the live region 16-byte aligned
         self.g = guard_rows
         full = (shape[0] + 2 * guard_rows,) + tuple(shape[1:])
         self.full = torch.empty(full, dtype=torch.uint8 if dtype == torch.uint8 else dtype, device=dev)
@@ -324,3 +324,16 @@ def test_chain_matches_oracle_and_replays_in_a_graph(dev, oracle):
     torch.cuda.synchronize()
     for a, t in zip(snap, (ch.hidden, ch.normed_attn, ch.q_out, ch.k_cache, ch.act)):
         assert np.array_equal(a.view(np.uint8), H(t).view(np.uint8))
+
+
+def test_glu_fast_path_equals_generic_path_on_its_whole_domain(dev):
+    """2^28 pseudo-random (gate, up) pairs over |gate| in [2^-40, 64): the branch-free expf and the written-out
+    division must give the same bits as the generic path (special-case aware expf, __fdiv_rn)."""
+    import ctypes as C
+    from fnfl_v100_b200 import _lib
+    bad = torch.zeros(1, dtype=torch.int64, device=dev)
+    st = _lib.lib().fnb_selftest_glu_math(1 << 28, 12345, C.c_void_p(bad.data_ptr()),
+                                          C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert st == 0
+    torch.cuda.synchronize()
+    assert int(bad.item()) == 0
