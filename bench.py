@@ -252,19 +252,26 @@ def run_ours(args) -> None:
 
     # end to end from pinned host memory (chunks of 8192 tokens over three streams)
     e2e_steps = max(1, min(args.e2e_steps, K))
-    pipe = HostChunkPipeline(cfg, dev, chunk=min(8192, T), source=chain)
-    pipe.step()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(cur)
-    for _ in range(e2e_steps):
+    e2e = None
+    if not args.no_e2e:
+        pipe = HostChunkPipeline(cfg, dev, chunk=min(8192, T), source=chain)
         pipe.step()
-    e1.record(cur)
-    barrier()
-    e2e_ms = torch.tensor([e0.elapsed_time(e1) / e2e_steps], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
-    e2e_ms = float(e2e_ms)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(cur)
+        for _ in range(e2e_steps):
+            pipe.step()
+        e1.record(cur)
+        barrier()
+        e2e_ms = torch.tensor([e0.elapsed_time(e1) / e2e_steps], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+        e2e_ms = float(e2e_ms)
+        if int(pipe.h_err.item()) != 0:
+            raise SystemExit("bench.py: the host pipeline reported a device error word of %d" % int(pipe.h_err.item()))
+        e2e = {"value": T * world / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": pipe.h2d_bytes,
+               "d2h_bytes_per_step": pipe.d2h_bytes, "ms_per_step": e2e_ms, "chunk_tokens": pipe.chunk,
+               "launches_per_step": pipe.launches_per_step}
 
     # optional final gather of the quantised outputs over NVLink (not part of the timed chain)
     gather_ms = None
@@ -307,8 +314,7 @@ def run_ours(args) -> None:
             "roofline": {"kernel": "glu_quant_kernel (SwiGLU + Q8_1)", "bound": "hbm", "achieved": achieved,
                          "peak": peak, "peak_source": peak_kind, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": traffic, "algorithmic_bytes": dom_bytes},
-            "e2e": {"value": T * world / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": pipe.h2d_bytes,
-                    "d2h_bytes_per_step": pipe.d2h_bytes, "ms_per_step": e2e_ms, "chunk_tokens": pipe.chunk},
+            "e2e": e2e,
             "gpu_launches": 5 * K * world,
             "clocks": clocks,
         }
@@ -331,6 +337,7 @@ def main() -> None:
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--gather", action="store_true", help="also time an all-gather of the Q8_1 outputs (N > 1)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -111,6 +111,10 @@ int32_t fnb_act_quantize(const float * x, int8_t * codes, float * scales, int64_
  * A slot outside [0, cache_slots) sets FNB_ERR_SLOT in *err and nothing is written for that token.
  * head_dim in {64, 128, 256}; n_rot a multiple of 2 * (head_dim / 32), 0 <= n_rot <= head_dim; all pointers
  * 16-byte aligned (pos, slots 4-byte).  q_out may alias q.
+ * The first call on a device raises the kernel's dynamic shared-memory limit (cudaFuncSetAttribute, once per
+ * device and head_dim): make that first call outside a stream capture.  Shapes whose token tile does not fit in
+ * shared memory, or whose n_rot is not a multiple of 64, run a slower row-per-warp kernel with the same results.
+ * A bounded in-kernel wait that gives up sets FNB_ERR_TIMEOUT in *err.
  * Replaces fn::qsa::qsp_kv (fn/kernels/qsa/qsa_prompt.h:90-105, qsa_prompt_attn.cu:77-122), the prepare phase
  * of fn::qsa::attn::attend (fn/kernels/qsa/attend.cu:153-260) and fn::draft::dcp_prepare
  * (fn/kernels/draft/draft_prompt.h:44-59).

@@ -1,0 +1,145 @@
+// Header-only C++ shims over the C ABI (fnb200.h) in the reference engine's launcher convention:
+//
+//     namespace <family> { struct <op>_args { raw device pointers, PODs }; bool <op>(const <op>_args &, void * stream); }
+//
+// `false` means nothing was enqueued (argument outside the contract) or the launch was refused (the CUDA error is left
+// for cudaPeekAtLastError), exactly as fn::act::quantize (fn/kernels/act/act.h:64-66), fn::embed::embed_rows
+// (fn/kernels/embed/embed.h:85), fn::qsa::qsp_kv (fn/kernels/qsa/qsa_prompt.h:105), fn::experts::glu_finish
+// (fn/kernels/experts/experts.h:277) and fn::draft::dcp_norm (fn/kernels/draft/draft_prompt.h:34) behave.  `stream` is a
+// cudaStream_t passed as void * so this header stays CUDA-free, as the reference's headers do; null is the default
+// stream.  The launchers own nothing, allocate nothing and never synchronise.
+//
+// The families keep the reference's names; the operators carry the formats this library implements (ggml Q8_0 / Q8_1 /
+// Q4_K / IQ3_XXS next to the reference's own activation and KV8 formats).
+#pragma once
+
+#include <cstdint>
+
+#include "fnb200.h"
+
+namespace fnb {
+
+constexpr uint32_t err_token = FNB_ERR_TOKEN;      // fn::xchg::err_token's role
+constexpr uint32_t err_slot = FNB_ERR_SLOT;
+constexpr uint32_t err_timeout = FNB_ERR_TIMEOUT;
+
+namespace draft {  // hidden RMSNorm: fn::draft::dcp_norm's arithmetic, F32 out
+
+struct norm_args {
+    int64_t rows = 0;
+    int32_t cols = 0;
+    const float * x = nullptr;  // [rows][cols]
+    const float * w = nullptr;  // [cols] or null
+    float eps = 1e-6f;
+    float * y = nullptr;        // [rows][cols]
+};
+inline bool dcp_norm(const norm_args & a, void * stream) {
+    return fnb_rms_norm_f32(a.x, a.w, a.eps, a.y, a.rows, a.cols, stream) == FNB_OK;
+}
+
+}  // namespace draft
+
+namespace act {  // fn::act::quantize and its ggml-format siblings
+
+constexpr int32_t run = 32;
+
+struct out_view {  // fn::act::out_view: codes int8 [rows][k], scales F32 [rows][k / 32][2]
+    int8_t * codes = nullptr;
+    float * scales = nullptr;
+    int32_t rows = 0;
+    int32_t k = 0;
+};
+inline bool quantize(const float * x, const out_view & o, void * stream) {
+    return fnb_act_quantize(x, o.codes, o.scales, o.rows, o.k, stream) == FNB_OK;
+}
+inline bool quantize_q8_1(const float * x, void * blocks, int64_t rows, int32_t k, void * stream) {
+    return fnb_quantize_q8_1(x, blocks, rows, k, stream) == FNB_OK;
+}
+inline bool quantize_q8_0(const float * x, void * blocks, int64_t rows, int32_t k, void * stream) {
+    return fnb_quantize_q8_0(x, blocks, rows, k, stream) == FNB_OK;
+}
+
+}  // namespace act
+
+namespace experts {  // SwiGLU + requantisation: fn::experts::glu_finish
+
+// gs, us: F32 [n][cols] gate and up sums; the GLU leaves in the reference's activation format
+inline bool glu_finish(const float * gs, const float * us, int64_t n, int32_t cols, int8_t * codes, float * scales,
+                       void * stream) {
+    return fnb_swiglu_act(gs, us, codes, scales, nullptr, n, cols, stream) == FNB_OK;
+}
+// the same GLU as ggml Q8_1 blocks [n][cols / 32]; glu_f32 (optional) receives the F32 GLU the codes were made from
+inline bool glu_finish_q8_1(const float * gs, const float * us, int64_t n, int32_t cols, void * blocks, float * glu_f32,
+                            void * stream) {
+    return fnb_swiglu_q8_1(gs, us, blocks, glu_f32, n, cols, stream) == FNB_OK;
+}
+
+}  // namespace experts
+
+namespace qsa {  // per-head norm + NeoX partial RoPE + KV append: fn::qsa::qsp_kv and attend's prepare phase
+
+struct qsp_kv_args {
+    const float * q = nullptr;        // [rows][n_q_heads][head_dim]; n_q_heads may be 0 (K/V only, as qsp_kv)
+    const float * kv_k = nullptr;     // [rows][n_kv_heads][head_dim]
+    const float * kv_v = nullptr;
+    const float * q_norm = nullptr;   // [head_dim] or null
+    const float * k_norm = nullptr;
+    const int32_t * pos = nullptr;    // [rows] device: rotary position
+    const int32_t * cells = nullptr;  // [rows] device: cache cell, or null = the position
+    int64_t rows = 0, max_cells = 0;
+    int32_t n_q_heads = 0, n_kv_heads = 1, head_dim = 256, n_rot = 64;
+    float theta_scale = 0.0f;         // fnb_rope_theta_scale(freq_base, n_rot)
+    float eps = 1e-6f;
+    float * q_out = nullptr;          // [rows][n_q_heads][head_dim]
+    void * k_cache = nullptr;         // Q8_0 cells, or int8 codes when k_scale / v_scale are set (KV8)
+    void * v_cache = nullptr;
+    uint16_t * k_scale = nullptr;     // KV8: both set, FP16 scales [max_cells][n_kv_heads][head_dim / 64]
+    uint16_t * v_scale = nullptr;
+    float * k_f32 = nullptr;          // optional: k after norm and rope, before quantising
+    uint32_t * err = nullptr;
+};
+inline bool qsp_kv(const qsp_kv_args & a, void * stream) {
+    fnb_rope_kv8_args w{};
+    w.base.q = a.q, w.base.k = a.kv_k, w.base.v = a.kv_v, w.base.pos = a.pos, w.base.slots = a.cells;
+    w.base.q_norm_w = a.q_norm, w.base.k_norm_w = a.k_norm, w.base.q_out = a.q_out;
+    w.base.k_cache = a.k_cache, w.base.v_cache = a.v_cache, w.base.k_f32 = a.k_f32, w.base.err = a.err;
+    w.base.rows = a.rows, w.base.cache_slots = a.max_cells;
+    w.base.n_q_heads = a.n_q_heads, w.base.n_kv_heads = a.n_kv_heads, w.base.head_dim = a.head_dim;
+    w.base.n_rot = a.n_rot, w.base.theta_scale = a.theta_scale, w.base.eps = a.eps;
+    w.k_scale = a.k_scale, w.v_scale = a.v_scale;
+    if ((a.k_scale != nullptr) != (a.v_scale != nullptr)) return false;  // KV8 needs both planes, as the reference
+    return (a.k_scale != nullptr ? fnb_rope_neox_kv8_append(&w, stream) : fnb_rope_neox_q8_0_append(&w.base, stream)) ==
+           FNB_OK;
+}
+
+}  // namespace qsa
+
+namespace embed {  // token-embedding get_rows: fn::embed::embed_rows / check_tokens
+
+enum class table_fmt : int32_t { q4_k, iq3_xxs, q8_0 };
+
+struct rows_args {
+    const void * table = nullptr;   // [n_vocab][row bytes], ggml block layout
+    table_fmt fmt = table_fmt::q4_k;
+    int64_t n_vocab = 0;
+    const int32_t * tok = nullptr;  // [rows] device
+    int64_t rows = 0;
+    int32_t cols = 0;
+    float * out = nullptr;          // [rows][cols]
+    uint32_t * err = nullptr;       // err_token is OR-ed in for an id outside [0, n_vocab); that row stays unwritten
+};
+inline bool embed_rows(const rows_args & a, void * stream) {
+    switch (a.fmt) {
+        case table_fmt::q4_k: return fnb_get_rows_q4_k(a.table, a.n_vocab, a.tok, a.out, a.err, a.rows, a.cols, stream) == FNB_OK;
+        case table_fmt::iq3_xxs: return fnb_get_rows_iq3_xxs(a.table, a.n_vocab, a.tok, a.out, a.err, a.rows, a.cols, stream) == FNB_OK;
+        case table_fmt::q8_0: return fnb_get_rows_q8_0(a.table, a.n_vocab, a.tok, a.out, a.err, a.rows, a.cols, stream) == FNB_OK;
+    }
+    return false;
+}
+// host check before upload: true when every id is in [0, n_vocab)
+inline bool check_tokens(const int32_t * tok_host, int64_t rows, int64_t n_vocab) {
+    return fnb_check_tokens(tok_host, rows, n_vocab) == 0;
+}
+
+}  // namespace embed
+}  // namespace fnb
