@@ -9,7 +9,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libfnb200.so")
+LIB_PATH = os.environ.get("FNB200_LIB") or os.path.join(HERE, "libfnb200.so")   # FNB200_LIB: load another build
 
 OK, REJECTED, LAUNCH_FAILED = 0, 1, 2
 ERR_TOKEN, ERR_SLOT = 1, 2

@@ -10,10 +10,10 @@
 // Work decomposition: a warp owns a token.  All of the row's table bytes are requested before the first
 // value is decoded (Q4_K: per super-block one broadcast 16-byte header load and one coalesced 128-byte load
 // of the nibbles, 8 super-blocks in flight per lane; IQ3_XXS: the 784-byte row is staged into the warp's
-// shared-memory slot with 128-bit loads because its 98-byte super-blocks are only 2-byte aligned).  Every
+// shared-memory slot by cp.async because its 98-byte super-blocks are only 2-byte aligned).  Every
 // store instruction of the warp writes whole 128-byte lines with the streaming hint, so the 126 MB L2 keeps
-// the table rather than the output.  The IQ3_XXS codebook (256 x 4 magnitudes) and its sign table are expanded
-// into shared memory once per CTA; the CTAs are persistent (grid = SM count x resident CTAs) so that cost and
+// the table rather than the output.  The IQ3_XXS codebook (256 x 4 magnitudes, as floats) and its sign table are
+// expanded into shared memory once per CTA; the CTAs are persistent (grid = SM count x resident CTAs) so that cost and
 // the id fetch are amortised over many rows.
 #include "common.cuh"
 
@@ -115,22 +115,39 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32)
 // ---- IQ3_XXS ---------------------------------------------------------------------------------------------
 // super-block: fp16 d, 64 codebook indices, 8 words of {4-bit scale, 4 x 7 sign bits}.  Lane i decodes indices
 // 2i and 2i+1 (outputs 8i .. 8i+7) of each super-block: two 128-bit stores, a full 1 KiB per warp.
+//
+// What ncu showed on the first version (30 % issue rate at 65 % occupancy, stalls: long scoreboard 10, MIO throttle
+// 9, short scoreboard 7 per issue; 800 warp instructions per row) shaped this one:
+//   * the codebook is expanded to FLOAT magnitudes in shared memory (256 x float4 = 4 KiB), so an index costs one
+//     128-bit shared load and no byte extraction or integer-to-float conversion;
+//   * a sign is applied by choosing +db or -db as the multiplier ((-db) g and -(db g) are the same bits), eight
+//     predicates from one sign byte;
+//   * the row being decoded sits in a double-buffered shared slot filled by cp.async, so the global latency of row
+//     k + 1 (whose id was fetched an iteration earlier) overlaps the decode of row k;
+//   * the super-block loop is unrolled for the common 2048-wide row so every shared address is an immediate.
+__device__ __forceinline__ void cp_async16(void * smem_dst, const void * gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(uint32_t(__cvta_generic_to_shared(smem_dst))), "l"(gmem_src)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
+template <int NSB>  // super-blocks per row when known at compile time, 0 = read cols at run time
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
     get_rows_iq3_xxs_kernel(const uint8_t * __restrict__ table, int64_t n_vocab, const int32_t * __restrict__ ids,
                             float * __restrict__ out, uint32_t * err, int64_t rows, int cols) {
-    extern __shared__ __align__(16) uint8_t s_dyn[];
-    __shared__ uint32_t s_grid[256];   // four magnitudes per entry, byte j = magnitude j
-    __shared__ uint8_t s_signs[128];   // 7 stored sign bits -> 8 sign bits (the eighth is their parity)
+    extern __shared__ __align__(16) uint8_t s_dyn[];  // [warps][2][row bytes]
+    __shared__ float4 s_grid[256];                     // the codebook's four magnitudes per entry, as floats
+    __shared__ uint8_t s_signs[128];                   // 7 stored sign bits -> 8 sign bits (the eighth is their parity)
     for (int i = threadIdx.x; i < 256; i += blockDim.x) {
         const uint32_t c = c_iq3xxs_grid_packed[i];
-        uint32_t g = 0;
+        float m[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const uint32_t lvl = (c >> (3 * j)) & 7u;
-            g |= (lvl == 7u ? 62u : 4u + 8u * lvl) << (8 * j);
+            m[j] = lvl == 7u ? 62.0f : float(4u + 8u * lvl);
         }
-        s_grid[i] = g;
+        s_grid[i] = make_float4(m[0], m[1], m[2], m[3]);
     }
     for (int i = threadIdx.x; i < 128; i += blockDim.x) s_signs[i] = uint8_t(i | ((__popc(i) & 1) << 7));
     __syncthreads();
@@ -138,42 +155,69 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32)
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int64_t warp = int64_t(blockIdx.x) * kWarpsPerCta + wid;
     const int64_t n_warps = int64_t(gridDim.x) * kWarpsPerCta;
-    const int nsb = cols / 256;
+    const int nsb = NSB > 0 ? NSB : cols / 256;
     const int row_bytes = nsb * 98;
     const int row_vec = row_bytes / 16;
-    uint8_t * stage = s_dyn + size_t(wid) * size_t(row_bytes);
+    uint8_t * slot0 = s_dyn + size_t(wid) * 2 * size_t(row_bytes);
 
-    for (int64_t t = warp; t < rows; t += n_warps) {
-        const int64_t id = row_of(ids, t, n_vocab, err, lane);
-        if (id < 0) continue;
-        const uint4 * src = reinterpret_cast<const uint4 *>(table + id * int64_t(row_bytes));
-        for (int i = lane; i < row_vec; i += 32) reinterpret_cast<uint4 *>(stage)[i] = __ldg(src + i);
-        __syncwarp();
-        float * dst = out + t * cols;
-        for (int sb = 0; sb < nsb; ++sb) {
-            const uint8_t * blk = stage + sb * 98;
-            const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(blk));
-            const uint16_t idx = *reinterpret_cast<const uint16_t *>(blk + 2 + 2 * lane);
-            const uint16_t * sas = reinterpret_cast<const uint16_t *>(blk + 66 + 4 * (lane >> 2));
-            const uint32_t aux = uint32_t(sas[0]) | (uint32_t(sas[1]) << 16);
-            const float db = __fmul_rn(__fmul_rn(d, __fadd_rn(0.5f, float(aux >> 28))), 0.5f);
-            const uint32_t signs = s_signs[(aux >> (7 * (lane & 3))) & 127u];
-            const uint32_t g1 = s_grid[idx & 0xffu], g2 = s_grid[idx >> 8];
-            float4 a, b;
-            a.x = __fmul_rn(__fmul_rn(db, float(g1 & 0xffu)), (signs & 1u) ? -1.0f : 1.0f);
-            a.y = __fmul_rn(__fmul_rn(db, float((g1 >> 8) & 0xffu)), (signs & 2u) ? -1.0f : 1.0f);
-            a.z = __fmul_rn(__fmul_rn(db, float((g1 >> 16) & 0xffu)), (signs & 4u) ? -1.0f : 1.0f);
-            a.w = __fmul_rn(__fmul_rn(db, float(g1 >> 24)), (signs & 8u) ? -1.0f : 1.0f);
-            b.x = __fmul_rn(__fmul_rn(db, float(g2 & 0xffu)), (signs & 16u) ? -1.0f : 1.0f);
-            b.y = __fmul_rn(__fmul_rn(db, float((g2 >> 8) & 0xffu)), (signs & 32u) ? -1.0f : 1.0f);
-            b.z = __fmul_rn(__fmul_rn(db, float((g2 >> 16) & 0xffu)), (signs & 64u) ? -1.0f : 1.0f);
-            b.w = __fmul_rn(__fmul_rn(db, float(g2 >> 24)), (signs & 128u) ? -1.0f : 1.0f);
-            float4 * o = reinterpret_cast<float4 *>(dst + sb * 256) + 2 * lane;
-            st_stream(o, a);
-            st_stream(o + 1, b);
+    // start the copy of table row `id` into slot `buf`; an id outside the table copies nothing and is recorded
+    auto fetch = [&](int32_t id, int buf) -> bool {
+        if (id < 0 || id >= n_vocab) {
+            if (lane == 0 && err != nullptr) atomicOr(err, FNB_ERR_TOKEN);
+            return false;
         }
+        const uint8_t * src = table + int64_t(id) * int64_t(row_bytes);
+        uint8_t * dst = slot0 + size_t(buf) * row_bytes;
+        for (int i = lane; i < row_vec; i += 32) cp_async16(dst + 16 * i, src + 16 * i);
+        return true;
+    };
+
+    // ids run two rows ahead of the decode and the row copy one row ahead, so neither latency is exposed
+    int64_t t = warp;
+    int32_t id_next = t + n_warps < rows ? __ldg(ids + t + n_warps) : 0;
+    bool cur_ok = t < rows ? fetch(__ldg(ids + t), 0) : false;
+    cp_async_commit();
+    for (int k = 0; t < rows; t += n_warps, ++k) {
+        const int64_t tn = t + n_warps;
+        const int32_t id_after = tn + n_warps < rows ? __ldg(ids + tn + n_warps) : 0;
+        cp_async_wait_all();  // row t has landed
         __syncwarp();
+        const bool next_ok = tn < rows ? fetch(id_next, (k + 1) & 1) : false;
+        cp_async_commit();
+        id_next = id_after;
+        if (cur_ok) {
+            const uint8_t * stage = slot0 + size_t(k & 1) * row_bytes;
+            float * dst = out + t * cols;
+#pragma unroll
+            for (int sb = 0; sb < (NSB > 0 ? NSB : 1); ++sb) {
+                for (int sbr = sb; sbr < nsb; sbr += (NSB > 0 ? nsb : 1)) {  // one trip when unrolled, nsb trips otherwise
+                    const uint8_t * blk = stage + sbr * 98;
+                    const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(blk));
+                    const uint32_t idx = *reinterpret_cast<const uint16_t *>(blk + 2 + 2 * lane);
+                    const uint16_t * sas = reinterpret_cast<const uint16_t *>(blk + 66 + 4 * (lane >> 2));
+                    const uint32_t aux = uint32_t(sas[0]) | (uint32_t(sas[1]) << 16);
+                    const float db = __fmul_rn(__fmul_rn(d, __fadd_rn(0.5f, float(aux >> 28))), 0.5f);
+                    const float nb = -db;
+                    const uint32_t sg = s_signs[(aux >> (7 * (lane & 3))) & 127u];
+                    const float4 g1 = s_grid[idx & 0xffu], g2 = s_grid[idx >> 8];
+                    float4 a, b;
+                    a.x = __fmul_rn((sg & 1u) ? nb : db, g1.x);
+                    a.y = __fmul_rn((sg & 2u) ? nb : db, g1.y);
+                    a.z = __fmul_rn((sg & 4u) ? nb : db, g1.z);
+                    a.w = __fmul_rn((sg & 8u) ? nb : db, g1.w);
+                    b.x = __fmul_rn((sg & 16u) ? nb : db, g2.x);
+                    b.y = __fmul_rn((sg & 32u) ? nb : db, g2.y);
+                    b.z = __fmul_rn((sg & 64u) ? nb : db, g2.z);
+                    b.w = __fmul_rn((sg & 128u) ? nb : db, g2.w);
+                    float4 * o = reinterpret_cast<float4 *>(dst + sbr * 256) + 2 * lane;
+                    st_stream(o, a);
+                    st_stream(o + 1, b);
+                }
+            }
+        }
+        cur_ok = next_ok;
     }
+    cp_async_wait_all();
 }
 
 // ---- Q8_0 ------------------------------------------------------------------------------------------------
@@ -238,10 +282,15 @@ extern "C" int32_t fnb_get_rows_iq3_xxs(const void * table, int64_t n_vocab, con
                                         uint32_t * err, int64_t rows, int32_t cols, void * stream) {
     using namespace fnb;
     if (!common_ok(table, n_vocab, ids, out, err, rows, cols, 256, 98, 16)) return FNB_REJECTED;
-    const size_t smem = size_t(kWarpsPerCta) * size_t(cols / 256) * 98;
-    if (smem > 40 * 1024) return FNB_REJECTED;  // rows are staged in the default 48 KiB: cols <= 13312
-    get_rows_iq3_xxs_kernel<<<persistent_grid(rows, 8), kWarpsPerCta * 32, smem, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint8_t *>(table), n_vocab, ids, out, err, rows, cols);
+    const size_t smem = size_t(kWarpsPerCta) * 2 * size_t(cols / 256) * 98;
+    if (smem > 40 * 1024) return FNB_REJECTED;  // two rows per warp are staged in the default 48 KiB: cols <= 6144
+    const cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const uint8_t * tb = static_cast<const uint8_t *>(table);
+    if (cols == 2048) {
+        get_rows_iq3_xxs_kernel<8><<<persistent_grid(rows, 6), kWarpsPerCta * 32, smem, s>>>(tb, n_vocab, ids, out, err, rows, cols);
+    } else {
+        get_rows_iq3_xxs_kernel<0><<<persistent_grid(rows, 6), kWarpsPerCta * 32, smem, s>>>(tb, n_vocab, ids, out, err, rows, cols);
+    }
     return launch_status();
 }
 
