@@ -52,6 +52,7 @@ SIGNATURES = {
     "fnb_get_rows_q8_0": (_I32, [_P, _I64, _P, _P, _P, _I64, _I32, _P]),
     "fnb_check_tokens": (_I64, [_P, _I64, _I64]),
     "fnb_selftest_glu_math": (_I32, [C.c_uint64, C.c_uint64, _P, _P]),
+    "fnb_selftest_kv8_math": (_I32, [C.c_uint64, C.c_uint64, _P, _P]),
 }
 
 _lib = None

@@ -113,32 +113,64 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32)
 }
 
 // ---- IQ3_XXS ---------------------------------------------------------------------------------------------
-// super-block: fp16 d, 64 codebook indices, 8 words of {4-bit scale, 4 x 7 sign bits}.  Lane i decodes indices
-// 2i and 2i+1 (outputs 8i .. 8i+7) of each super-block: two 128-bit stores, a full 1 KiB per warp.
+// super-block: fp16 d, 64 codebook indices, 8 words of {4-bit scale, 4 x 7 sign bits}; index n decodes to the four
+// outputs 4n .. 4n + 3.  Lane L takes indices L and L + 32 of each super-block, so the warp's two store instructions
+// per super-block each write 512 contiguous bytes (whole 32-byte sectors).
 //
-// What ncu showed on the first version (30 % issue rate at 65 % occupancy, stalls: long scoreboard 10, MIO throttle
-// 9, short scoreboard 7 per issue; 800 warp instructions per row) shaped this one:
+// What ncu showed on earlier versions shaped this one:
+//   * first version (row staged in shared memory, byte codebook, lane = indices 2L and 2L + 1): 30 % issue rate at
+//     65 % occupancy, stalls per issue long scoreboard 10, MIO throttle 9, short scoreboard 7; 800 warp instructions
+//     per row.  Three different load structures (staged, cp.async double buffer, direct) all ran at the same 0.16 ms
+//     because the limit was the STORE shape: with adjacent indices per lane every store instruction wrote half of 32
+//     sectors.  Hence indices L and L + 32;
+//   * no staging: the 98-byte super-blocks are 2-byte aligned, so each lane fetches exactly the pieces it needs (d,
+//     its two index bytes, its two scale/sign words as halves) straight from global memory through L1, four
+//     super-blocks issued before the first use, as the Q4_K kernel does;
 //   * the codebook is expanded to FLOAT magnitudes in shared memory (256 x float4 = 4 KiB), so an index costs one
 //     128-bit shared load and no byte extraction or integer-to-float conversion;
-//   * a sign is applied by choosing +db or -db as the multiplier ((-db) g and -(db g) are the same bits), eight
-//     predicates from one sign byte;
-//   * the row being decoded sits in a double-buffered shared slot filled by cp.async, so the global latency of row
-//     k + 1 (whose id was fetched an iteration earlier) overlaps the decode of row k;
-//   * the super-block loop is unrolled for the common 2048-wide row so every shared address is an immediate.
-__device__ __forceinline__ void cp_async16(void * smem_dst, const void * gmem_src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(uint32_t(__cvta_generic_to_shared(smem_dst))), "l"(gmem_src)
-                 : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+//   * a sign is applied by choosing +db or -db as the multiplier ((-db) g and -(db g) are the same bits); the sign
+//     byte comes from the 128-entry sign table in shared memory.
+__device__ __forceinline__ uint32_t ldg_u16(const uint8_t * p) { return __ldg(reinterpret_cast<const uint16_t *>(p)); }
+__device__ __forceinline__ uint32_t ldg_u8(const uint8_t * p) { return __ldg(p); }
 
-template <int NSB>  // super-blocks per row when known at compile time, 0 = read cols at run time
+// one index: aux is its 32-value group's scale/sign word, n the index within the super-block
+__device__ __forceinline__ float4 iq3_decode(float d, uint32_t q, uint32_t aux, int n, const float4 * s_grid,
+                                             const uint8_t * s_signs) {
+    const float db = __fmul_rn(__fmul_rn(d, __fadd_rn(0.5f, float(aux >> 28))), 0.5f);
+    const float nb = -db;
+    const uint32_t sg = uint32_t(s_signs[(aux >> (7 * ((n >> 1) & 3))) & 127u]) >> (4 * (n & 1));
+    const float4 g = s_grid[q];
+    return make_float4(__fmul_rn((sg & 1u) ? nb : db, g.x), __fmul_rn((sg & 2u) ? nb : db, g.y),
+                       __fmul_rn((sg & 4u) ? nb : db, g.z), __fmul_rn((sg & 8u) ? nb : db, g.w));
+}
+
+struct iq3_sb_regs {
+    uint32_t dq, q0, q1, a0lo, a0hi, a1lo, a1hi;
+};
+__device__ __forceinline__ void iq3_load(iq3_sb_regs & r, const uint8_t * blk, int lane) {
+    const int o_aux = 66 + 4 * (lane >> 3);
+    r.dq = ldg_u16(blk);
+    r.q0 = ldg_u8(blk + 2 + lane);
+    r.q1 = ldg_u8(blk + 34 + lane);
+    r.a0lo = ldg_u16(blk + o_aux);
+    r.a0hi = ldg_u16(blk + o_aux + 2);
+    r.a1lo = ldg_u16(blk + o_aux + 16);
+    r.a1hi = ldg_u16(blk + o_aux + 18);
+}
+__device__ __forceinline__ void iq3_finish(const iq3_sb_regs & r, float * dst256, int lane, const float4 * s_grid,
+                                           const uint8_t * s_signs) {
+    const float d = f16_bits_to_f32(uint16_t(r.dq));
+    float4 * o = reinterpret_cast<float4 *>(dst256) + lane;
+    st_stream(o, iq3_decode(d, r.q0, r.a0lo | (r.a0hi << 16), lane, s_grid, s_signs));
+    st_stream(o + 32, iq3_decode(d, r.q1, r.a1lo | (r.a1hi << 16), lane, s_grid, s_signs));  // n = lane + 32: same parity bits
+}
+
+template <int NSB>  // super-blocks per row when known at compile time (a multiple of 4), 0 = read cols at run time
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
     get_rows_iq3_xxs_kernel(const uint8_t * __restrict__ table, int64_t n_vocab, const int32_t * __restrict__ ids,
                             float * __restrict__ out, uint32_t * err, int64_t rows, int cols) {
-    extern __shared__ __align__(16) uint8_t s_dyn[];  // [warps][2][row bytes]
-    __shared__ float4 s_grid[256];                     // the codebook's four magnitudes per entry, as floats
-    __shared__ uint8_t s_signs[128];                   // 7 stored sign bits -> 8 sign bits (the eighth is their parity)
+    __shared__ float4 s_grid[256];    // the codebook's four magnitudes per entry, as floats
+    __shared__ uint8_t s_signs[128];  // 7 stored sign bits -> 8 sign bits (the eighth is their parity)
     for (int i = threadIdx.x; i < 256; i += blockDim.x) {
         const uint32_t c = c_iq3xxs_grid_packed[i];
         float m[4];
@@ -152,72 +184,39 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32)
     for (int i = threadIdx.x; i < 128; i += blockDim.x) s_signs[i] = uint8_t(i | ((__popc(i) & 1) << 7));
     __syncthreads();
 
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    const int64_t warp = int64_t(blockIdx.x) * kWarpsPerCta + wid;
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = int64_t(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
     const int64_t n_warps = int64_t(gridDim.x) * kWarpsPerCta;
     const int nsb = NSB > 0 ? NSB : cols / 256;
-    const int row_bytes = nsb * 98;
-    const int row_vec = row_bytes / 16;
-    uint8_t * slot0 = s_dyn + size_t(wid) * 2 * size_t(row_bytes);
+    const int64_t row_bytes = int64_t(nsb) * 98;
 
-    // start the copy of table row `id` into slot `buf`; an id outside the table copies nothing and is recorded
-    auto fetch = [&](int32_t id, int buf) -> bool {
+    int32_t id_next = warp < rows ? __ldg(ids + warp) : 0;  // ids run one row ahead of the decode
+    for (int64_t t = warp; t < rows; t += n_warps) {
+        const int32_t id = id_next;
+        if (t + n_warps < rows) id_next = __ldg(ids + t + n_warps);
         if (id < 0 || id >= n_vocab) {
             if (lane == 0 && err != nullptr) atomicOr(err, FNB_ERR_TOKEN);
-            return false;
+            continue;
         }
-        const uint8_t * src = table + int64_t(id) * int64_t(row_bytes);
-        uint8_t * dst = slot0 + size_t(buf) * row_bytes;
-        for (int i = lane; i < row_vec; i += 32) cp_async16(dst + 16 * i, src + 16 * i);
-        return true;
-    };
-
-    // ids run two rows ahead of the decode and the row copy one row ahead, so neither latency is exposed
-    int64_t t = warp;
-    int32_t id_next = t + n_warps < rows ? __ldg(ids + t + n_warps) : 0;
-    bool cur_ok = t < rows ? fetch(__ldg(ids + t), 0) : false;
-    cp_async_commit();
-    for (int k = 0; t < rows; t += n_warps, ++k) {
-        const int64_t tn = t + n_warps;
-        const int32_t id_after = tn + n_warps < rows ? __ldg(ids + tn + n_warps) : 0;
-        cp_async_wait_all();  // row t has landed
-        __syncwarp();
-        const bool next_ok = tn < rows ? fetch(id_next, (k + 1) & 1) : false;
-        cp_async_commit();
-        id_next = id_after;
-        if (cur_ok) {
-            const uint8_t * stage = slot0 + size_t(k & 1) * row_bytes;
-            float * dst = out + t * cols;
+        const uint8_t * row = table + int64_t(id) * row_bytes;
+        float * dst = out + t * cols;
+        if constexpr (NSB > 0) {
 #pragma unroll
-            for (int sb = 0; sb < (NSB > 0 ? NSB : 1); ++sb) {
-                for (int sbr = sb; sbr < nsb; sbr += (NSB > 0 ? nsb : 1)) {  // one trip when unrolled, nsb trips otherwise
-                    const uint8_t * blk = stage + sbr * 98;
-                    const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(blk));
-                    const uint32_t idx = *reinterpret_cast<const uint16_t *>(blk + 2 + 2 * lane);
-                    const uint16_t * sas = reinterpret_cast<const uint16_t *>(blk + 66 + 4 * (lane >> 2));
-                    const uint32_t aux = uint32_t(sas[0]) | (uint32_t(sas[1]) << 16);
-                    const float db = __fmul_rn(__fmul_rn(d, __fadd_rn(0.5f, float(aux >> 28))), 0.5f);
-                    const float nb = -db;
-                    const uint32_t sg = s_signs[(aux >> (7 * (lane & 3))) & 127u];
-                    const float4 g1 = s_grid[idx & 0xffu], g2 = s_grid[idx >> 8];
-                    float4 a, b;
-                    a.x = __fmul_rn((sg & 1u) ? nb : db, g1.x);
-                    a.y = __fmul_rn((sg & 2u) ? nb : db, g1.y);
-                    a.z = __fmul_rn((sg & 4u) ? nb : db, g1.z);
-                    a.w = __fmul_rn((sg & 8u) ? nb : db, g1.w);
-                    b.x = __fmul_rn((sg & 16u) ? nb : db, g2.x);
-                    b.y = __fmul_rn((sg & 32u) ? nb : db, g2.y);
-                    b.z = __fmul_rn((sg & 64u) ? nb : db, g2.z);
-                    b.w = __fmul_rn((sg & 128u) ? nb : db, g2.w);
-                    float4 * o = reinterpret_cast<float4 *>(dst + sbr * 256) + 2 * lane;
-                    st_stream(o, a);
-                    st_stream(o + 1, b);
-                }
+            for (int sb0 = 0; sb0 < NSB; sb0 += 4) {
+                iq3_sb_regs r[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) iq3_load(r[j], row + (sb0 + j) * 98, lane);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) iq3_finish(r[j], dst + (sb0 + j) * 256, lane, s_grid, s_signs);
+            }
+        } else {
+            for (int sb = 0; sb < nsb; ++sb) {
+                iq3_sb_regs r;
+                iq3_load(r, row + sb * 98, lane);
+                iq3_finish(r, dst + sb * 256, lane, s_grid, s_signs);
             }
         }
-        cur_ok = next_ok;
     }
-    cp_async_wait_all();
 }
 
 // ---- Q8_0 ------------------------------------------------------------------------------------------------
@@ -281,15 +280,13 @@ extern "C" int32_t fnb_get_rows_q4_k(const void * table, int64_t n_vocab, const 
 extern "C" int32_t fnb_get_rows_iq3_xxs(const void * table, int64_t n_vocab, const int32_t * ids, float * out,
                                         uint32_t * err, int64_t rows, int32_t cols, void * stream) {
     using namespace fnb;
-    if (!common_ok(table, n_vocab, ids, out, err, rows, cols, 256, 98, 16)) return FNB_REJECTED;
-    const size_t smem = size_t(kWarpsPerCta) * 2 * size_t(cols / 256) * 98;
-    if (smem > 40 * 1024) return FNB_REJECTED;  // two rows per warp are staged in the default 48 KiB: cols <= 6144
+    if (!common_ok(table, n_vocab, ids, out, err, rows, cols, 256, 98, 2)) return FNB_REJECTED;
     const cudaStream_t s = static_cast<cudaStream_t>(stream);
     const uint8_t * tb = static_cast<const uint8_t *>(table);
     if (cols == 2048) {
-        get_rows_iq3_xxs_kernel<8><<<persistent_grid(rows, 6), kWarpsPerCta * 32, smem, s>>>(tb, n_vocab, ids, out, err, rows, cols);
+        get_rows_iq3_xxs_kernel<8><<<persistent_grid(rows, 8), kWarpsPerCta * 32, 0, s>>>(tb, n_vocab, ids, out, err, rows, cols);
     } else {
-        get_rows_iq3_xxs_kernel<0><<<persistent_grid(rows, 6), kWarpsPerCta * 32, smem, s>>>(tb, n_vocab, ids, out, err, rows, cols);
+        get_rows_iq3_xxs_kernel<0><<<persistent_grid(rows, 8), kWarpsPerCta * 32, 0, s>>>(tb, n_vocab, ids, out, err, rows, cols);
     }
     return launch_status();
 }

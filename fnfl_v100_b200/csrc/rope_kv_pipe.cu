@@ -317,20 +317,13 @@ __global__ void __launch_bounds__(kThreads, 1) rope_kv_pipe_kernel(const rope_ke
                 uint16_t * scl = (kind == 1 ? a.k_scale : a.v_scale) + c * (HD / 64);
 #pragma unroll
                 for (int g = 0; g < NJ / 2; ++g) {
-                    const uint16_t sb = f32_to_f16_bits(__fdiv_rn(fmaxf(am[2 * g], am[2 * g + 1]), 127.0f));
-                    const float sc = f16_bits_to_f32(sb);
+                    const kv8_rule rule(fmaxf(am[2 * g], am[2 * g + 1]));
 #pragma unroll
                     for (int j = 2 * g; j < 2 * g + 2; ++j) {
-                        int q[4];
-                        const float v[4] = {x[j].x, x[j].y, x[j].z, x[j].w};
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            // cvt.rni saturates +-inf and maps NaN to 0; the clamp then gives the rule's +-127
-                            q[e] = sc > 0.0f ? max(-127, min(127, __float2int_rn(__fdiv_rn(v[e], sc)))) : 0;
-                        }
-                        if (is_kv) st_stream(reinterpret_cast<uint32_t *>(codes) + 8 * j + sub, pack4(q[0], q[1], q[2], q[3]));
+                        const uint32_t wrd = rule.code4(x[j]);
+                        if (is_kv) st_stream(reinterpret_cast<uint32_t *>(codes) + 8 * j + sub, wrd);
                     }
-                    if (is_kv && sub == 0) scl[g] = sb;
+                    if (is_kv && sub == 0) scl[g] = rule.sb;
                 }
             }
         }
@@ -385,6 +378,35 @@ bool launch_one(const rope_kernel_args & a, cudaStream_t s) {
     return true;
 }
 
+// Self-check of kv8_rule's written-out division against __fdiv_rn: every positive finite FP16 scale (i mod 31743)
+// with pseudo-random x of magnitude up to 300 s; counts codes that differ.
+__global__ void kv8_selftest_kernel(uint64_t n, uint64_t seed, unsigned long long * mismatches) {
+    unsigned long long bad = 0;
+    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += uint64_t(gridDim.x) * blockDim.x) {
+        uint64_t z = (i + seed) * 0x9E3779B97F4A7C15ull;  // splitmix64 finaliser
+        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+        z ^= z >> 31;
+        const float s = f16_bits_to_f32(uint16_t(1u + uint32_t(i % 31743u)));  // 0x0001 .. 0x7BFF
+        // x = s * m with m log-uniform in [2^-12, 300), half of them pushed onto exact k + 0.5 multiples of s
+        const float mant = __uint_as_float(0x3f800000u | (uint32_t(z) & 0x7fffffu));
+        float m = mant * exp2f(float(int((z >> 24) % 21u)) - 12.0f);
+        if (z & (1ull << 60)) m = floorf(fminf(m, 200.0f)) + 0.5f;
+        float x = __fmul_rn(s, m);
+        if (z & (1ull << 61)) x = -x;
+        kv8_rule rule(__fmul_rn(s, 127.0f));  // amax that maps back onto the scale (or its neighbour)
+        rule.sb = 0, rule.s = s;
+        rule.fast = s >= 0x1p-24f && s <= 65504.0f;
+        float r0;
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(s));
+        rule.r = __fmaf_rn(r0, __fmaf_rn(-s, r0, 1.0f), r0);
+        const int fast = rule.code(x);
+        const int ref = max(-127, min(127, __float2int_rn(__fdiv_rn(x, s))));
+        bad += fast != ref;
+    }
+    if (bad != 0) atomicAdd(mismatches, bad);
+}
+
 }  // namespace
 
 bool rope_kv_pipe_try_launch(const rope_kernel_args & a, int head_dim, kv_fmt fmt, cudaStream_t s) {
@@ -398,3 +420,9 @@ bool rope_kv_pipe_try_launch(const rope_kernel_args & a, int head_dim, kv_fmt fm
 }
 
 }  // namespace fnb
+
+extern "C" int32_t fnb_selftest_kv8_math(uint64_t n, uint64_t seed, unsigned long long * mismatches, void * stream) {
+    if (!fnb::ok_ptr(mismatches, 8) || n == 0) return FNB_REJECTED;
+    fnb::kv8_selftest_kernel<<<fnb::kSmCount * 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(n, seed, mismatches);
+    return fnb::launch_status();
+}

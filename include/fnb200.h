@@ -72,6 +72,8 @@ int32_t fnb_rms_norm_heads_f32(const float * x, const float * w, float eps, floa
  * aligned, cols a multiple of 32; out_q8_1: [rows][cols / 32] blocks, 16-byte aligned; out_f32 (optional,
  * F32 [rows][cols]) receives v before quantisation, which is how the reference's own tests pin the codes
  * (fn/kernels/experts/experts.h:45-47).  expf is evaluated exactly as glibc 2.39's non-FMA expf.
+ * As with the rope entry points, the first call of each SwiGLU / requantiser variant on a device raises its
+ * kernel's dynamic shared-memory limit (cudaFuncSetAttribute): make that first call outside a stream capture.
  * Replaces fn::experts::glu_finish (fn/kernels/experts/experts.h:273-277, experts.cu:716-729) and the GLU
  * epilogues glu_out / glu_run (experts_gu.cuh:308-340, experts_dev.cuh:196-213).
  */
@@ -164,8 +166,8 @@ float fnb_rope_theta_scale(float freq_base, int32_t n_rot);
 /*
  * Token-embedding get_rows: out[t] = the dequantised row ids[t] of a quantised table [n_vocab][cols], F32,
  * bit-exact with ggml's row decoders (ggml/src/ggml-quants.c:1527-1549 Q4_K, :2573-2601 IQ3_XXS, :551-565
- * Q8_0).  table, out 16-byte aligned; cols a multiple of 256 (Q4_K, IQ3_XXS; and the row's bytes a multiple
- * of 16) or of 32 (Q8_0), at most 16384; ids I32 [rows] on the device.  An id outside [0, n_vocab) sets
+ * Q8_0).  table, out 16-byte aligned; cols a multiple of 256 (Q4_K, IQ3_XXS) or of 32 (Q8_0), at most 16384;
+ * ids I32 [rows] on the device.  An id outside [0, n_vocab) sets
  * FNB_ERR_TOKEN in *err and leaves that output row unwritten.
  * Replaces fn::embed::embed_rows / fn::embed::embed (fn/kernels/embed/embed.h:56-87, embed_prompt.cu:26-107).
  */
@@ -188,6 +190,13 @@ int64_t fnb_check_tokens(const int32_t * ids_host, int64_t rows, int64_t n_vocab
  * adds the number of results whose bits differ to *mismatches (device memory, 8-byte aligned, caller-zeroed).
  */
 int32_t fnb_selftest_glu_math(uint64_t n, uint64_t seed, unsigned long long * mismatches, void * stream);
+
+/*
+ * Diagnostic with no counterpart in the reference: the KV8 rule's written-out division by the group scale against
+ * __fdiv_rn, over every positive finite FP16 scale and n pseudo-random values (half of them on exact half steps);
+ * adds the number of differing codes to *mismatches.
+ */
+int32_t fnb_selftest_kv8_math(uint64_t n, uint64_t seed, unsigned long long * mismatches, void * stream);
 
 #ifdef __cplusplus
 }

@@ -249,6 +249,7 @@ def test_rope_kv8_format_matches_reference_rule(dev, oracle):
 @pytest.mark.parametrize("fmt,cols,vocab,rows", [
     ("q4_k", 2048, 1000, 777), ("iq3_xxs", 2048, 1000, 777), ("q8_0", 2048, 500, 300),
     ("q4_k", 256, 64, 1), ("q4_k", 4096, 64, 7), ("q4_k", 2560, 64, 33), ("iq3_xxs", 4096, 64, 33),
+    ("iq3_xxs", 256, 64, 9), ("iq3_xxs", 768, 64, 5),
     ("q8_0", 1280, 64, 5), ("q8_0", 32, 64, 9),
 ])
 def test_get_rows_bit_exact_and_bad_ids(dev, oracle, fmt, cols, vocab, rows):
@@ -333,6 +334,18 @@ def test_glu_fast_path_equals_generic_path_on_its_whole_domain(dev):
     from fnfl_v100_b200 import _lib
     bad = torch.zeros(1, dtype=torch.int64, device=dev)
     st = _lib.lib().fnb_selftest_glu_math(1 << 28, 12345, C.c_void_p(bad.data_ptr()),
+                                          C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert st == 0
+    torch.cuda.synchronize()
+    assert int(bad.item()) == 0
+
+
+def test_kv8_written_out_division_equals_ieee_division(dev):
+    """Every positive finite FP16 scale x 2^27 pseudo-random values (half on exact half steps): same codes as __fdiv_rn."""
+    import ctypes as C
+    from fnfl_v100_b200 import _lib
+    bad = torch.zeros(1, dtype=torch.int64, device=dev)
+    st = _lib.lib().fnb_selftest_kv8_math(1 << 27, 777, C.c_void_p(bad.data_ptr()),
                                           C.c_void_p(torch.cuda.current_stream().cuda_stream))
     assert st == 0
     torch.cuda.synchronize()
