@@ -44,6 +44,9 @@ SIGNATURES = {
     "fnb_quantize_q8_1": (_I32, [_P, _P, _I64, _I32, _P]),
     "fnb_quantize_q8_0": (_I32, [_P, _P, _I64, _I32, _P]),
     "fnb_act_quantize": (_I32, [_P, _P, _P, _I64, _I32, _P]),
+    "fnb_rms_norm_q8_1": (_I32, [_P, _P, _F, _P, _P, _I64, _I32, _P]),
+    "fnb_rms_norm_q8_0": (_I32, [_P, _P, _F, _P, _P, _I64, _I32, _P]),
+    "fnb_rms_norm_act": (_I32, [_P, _P, _F, _P, _P, _P, _I64, _I32, _P]),
     "fnb_rope_neox_q8_0_append": (_I32, [C.POINTER(RopeKvArgs), _P]),
     "fnb_rope_neox_kv8_append": (_I32, [C.POINTER(RopeKv8Args), _P]),
     "fnb_rope_theta_scale": (_F, [_F, _I32]),

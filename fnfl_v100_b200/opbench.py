@@ -17,7 +17,7 @@ from . import ops, synth
 from .chain import ChainConfig
 
 OPS = ("get_rows_q4_k", "get_rows_iq3_xxs", "rms_norm", "rms_norm_heads", "rope_kv", "swiglu_q8_1", "swiglu_act",
-       "rope_kv8", "quantize_q8_1")
+       "rope_kv8", "quantize_q8_1", "rms_norm_q8_1")
 
 
 def hbm_peak() -> float:
@@ -44,6 +44,9 @@ def make_case(op: str, T: int, dev, gen, c: ChainConfig):
         x, w = N(gen, (T, c.hidden), 1.0, dev), 1 + 0.1 * N(gen, (c.hidden,), 1.0, dev)
         y = torch.empty_like(x)
         return (lambda: ops.rms_norm(x, w, c.eps, out=y)), T * c.hidden * 8 + c.hidden * 4
+    if op == "rms_norm_q8_1":
+        x, w = N(gen, (T, c.hidden), 1.0, dev), 1 + 0.1 * N(gen, (c.hidden,), 1.0, dev)
+        return (lambda: ops.rms_norm_quant(x, w, c.eps, "q8_1")), T * c.hidden * 4 + T * c.hidden // 32 * 36 + c.hidden * 4
     if op == "rms_norm_heads":
         h = c.n_q_heads + c.n_kv_heads
         x, w = N(gen, (T, h, c.head_dim), 1.0, dev), 1 + 0.1 * N(gen, (c.head_dim,), 1.0, dev)

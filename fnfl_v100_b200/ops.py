@@ -76,6 +76,30 @@ def rms_norm_heads(x: torch.Tensor, w: torch.Tensor | None, eps: float = 1e-6, o
     return out
 
 
+def rms_norm_quant(x: torch.Tensor, w: torch.Tensor | None, eps: float = 1e-6, fmt: str = "q8_1",
+                   out_f32: torch.Tensor | None = None):
+    """RMSNorm fused with requantisation of its output.  fmt "q8_1" / "q8_0": returns uint8 blocks [rows][cols/32*B];
+    fmt "act": returns (codes int8 [rows][cols], scales F32 [rows][cols/32][2])."""
+    _dev(x, torch.float32, "x")
+    if w is not None:
+        _dev(w, torch.float32, "w")
+    if out_f32 is not None:
+        _dev(out_f32, torch.float32, "out_f32")
+    rows, cols = _rows_cols(x)
+    L = _lib.lib()
+    if fmt == "act":
+        codes = torch.empty((rows, cols), dtype=torch.int8, device=x.device)
+        scales = torch.empty((rows, cols // 32, 2), dtype=torch.float32, device=x.device)
+        _check(L.fnb_rms_norm_act(_ptr(x), _ptr(w), eps, _ptr(codes), _ptr(scales), _ptr(out_f32), rows, cols, _stream()),
+               "rms_norm_act")
+        return codes, scales
+    bb = {"q8_1": Q8_1_BLOCK, "q8_0": Q8_0_BLOCK}[fmt]
+    out = torch.empty((rows, cols // 32 * bb), dtype=torch.uint8, device=x.device)
+    fn = L.fnb_rms_norm_q8_1 if fmt == "q8_1" else L.fnb_rms_norm_q8_0
+    _check(fn(_ptr(x), _ptr(w), eps, _ptr(out), _ptr(out_f32), rows, cols, _stream()), "rms_norm_" + fmt)
+    return out
+
+
 # ---- SwiGLU + requantisation --------------------------------------------------------------------------------
 
 def _rows_cols(x: torch.Tensor) -> tuple[int, int]:

@@ -101,6 +101,21 @@ int32_t fnb_act_quantize(const float * x, int8_t * codes, float * scales, int64_
                          void * stream);
 
 /*
+ * Hidden RMSNorm fused with the requantisation of its output (the activation the next quantised mat-vec reads):
+ * y as fnb_rms_norm_f32, then every 32 values of y become one Q8_1 / Q8_0 block or the reference's activation
+ * format, exactly as the stand-alone requantisers would produce from y.  cols a multiple of 32, at most 4096;
+ * out_f32 (optional, F32 [rows][cols]) receives y.  The reference fuses the same pair in its split hidden norm
+ * (fn/kernels/draft/draft_in.cu:85-132, which writes the activation format: fn/kernels/draft/draft.h:110-139).
+ * First call per device and variant sets a kernel attribute (see fnb_swiglu_q8_1).
+ */
+int32_t fnb_rms_norm_q8_1(const float * x, const float * w, float eps, void * out_q8_1, float * out_f32, int64_t rows,
+                          int32_t cols, void * stream);
+int32_t fnb_rms_norm_q8_0(const float * x, const float * w, float eps, void * out_q8_0, float * out_f32, int64_t rows,
+                          int32_t cols, void * stream);
+int32_t fnb_rms_norm_act(const float * x, const float * w, float eps, int8_t * codes, float * scales, float * out_f32,
+                         int64_t rows, int32_t cols, void * stream);
+
+/*
  * Optional per-head RMSNorm, NeoX partial-rotary RoPE, and Q8_0 quantise-and-append of K and V into the cache.
  * Per token t at rotary position pos[t] and cache slot slots[t] (or pos[t] when slots is null):
  *   q_out[t][h] = rope(norm(q[t][h]))            F32, all head_dim values (dims >= n_rot pass through)

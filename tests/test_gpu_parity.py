@@ -350,3 +350,35 @@ def test_kv8_written_out_division_equals_ieee_division(dev):
     assert st == 0
     torch.cuda.synchronize()
     assert int(bad.item()) == 0
+
+
+@pytest.mark.parametrize("rows,cols,fmt", [(512, 2048, "q8_1"), (7, 2048, "q8_0"), (33, 2560, "q8_1"), (5, 4096, "q8_1"),
+                                           (9, 1024, "act"), (3, 320, "act"), (1, 32, "q8_1"), (130, 2048, "act")])
+def test_rms_norm_fused_with_requantisation(dev, oracle, rows, cols, fmt):
+    g = synth.rng(1)
+    x = synth.normal(g, (rows, cols), 2.0)
+    w = synth.norm_weight(g, cols)
+    y = Guarded((rows, cols), torch.float32, dev)
+    res = ops.rms_norm_quant(to_dev(x, dev), to_dev(w, dev), 1e-6, fmt, out_f32=y.live)
+    torch.cuda.synchronize()
+    y.check_guards()
+    got_y = y.numpy()
+    want_y = oracle.rms_norm(x, w, 1e-6)
+    assert ulp_diff(got_y, want_y).max() <= 2
+    # blocks are the CPU quantiser of the kernel's own F32 row, and equal the all-CPU result end to end
+    if fmt == "act":
+        codes, scales = (t.cpu().numpy() for t in res)
+        wc, ws = oracle.act_quantize(got_y)
+        assert np.array_equal(codes, wc) and np.array_equal(bits(scales), bits(ws))
+        ec, es = oracle.act_quantize(want_y)
+        assert int((codes != ec).sum()) == 0 and np.array_equal(bits(scales), bits(es))
+    else:
+        q = oracle.quantize_q8_1 if fmt == "q8_1" else oracle.quantize_q8_0
+        got = res.cpu().numpy().reshape(-1)
+        assert np.array_equal(got, q(got_y))
+        assert int((got != q(want_y)).sum()) == 0
+    # same bytes without the optional F32 output
+    res2 = ops.rms_norm_quant(to_dev(x, dev), to_dev(w, dev), 1e-6, fmt)
+    a = res2[0] if fmt == "act" else res2
+    b = res[0] if fmt == "act" else res
+    assert torch.equal(a, b)
