@@ -26,6 +26,18 @@ class RopeKvArgs(C.Structure):
     ]
 
 
+class EmbedArgs(C.Structure):
+    """fnb_embed_args"""
+    _fields_ = [
+        ("table", C.c_void_p), ("tok", C.c_void_p), ("own", C.c_void_p), ("full", C.c_void_p), ("streams", C.c_void_p),
+        ("err", C.c_void_p), ("n_vocab", C.c_int64), ("rows", C.c_int64), ("fmt", C.c_int32), ("n_own", C.c_int32),
+        ("n_full", C.c_int32), ("col0", C.c_int32), ("n_streams", C.c_int32),
+    ]
+
+
+TABLE_Q4_K, TABLE_IQ3_XXS, TABLE_Q8_0, TABLE_IQ3_S = 0, 1, 2, 3
+
+
 class RopeKv8Args(C.Structure):
     """fnb_rope_kv8_args"""
     _fields_ = [("base", RopeKvArgs), ("k_scale", C.c_void_p), ("v_scale", C.c_void_p)]
@@ -53,6 +65,9 @@ SIGNATURES = {
     "fnb_get_rows_q4_k": (_I32, [_P, _I64, _P, _P, _P, _I64, _I32, _P]),
     "fnb_get_rows_iq3_xxs": (_I32, [_P, _I64, _P, _P, _P, _I64, _I32, _P]),
     "fnb_get_rows_q8_0": (_I32, [_P, _I64, _P, _P, _P, _I64, _I32, _P]),
+    "fnb_embed_rows": (_I32, [C.POINTER(EmbedArgs), _P]),
+    "fnb_embed_join": (_I32, [C.POINTER(EmbedArgs), _P, _I32, _P]),
+    "fnb_embed_supply": (_I32, [C.POINTER(EmbedArgs), _P, _I64, _I64, _P]),
     "fnb_check_tokens": (_I64, [_P, _I64, _I64]),
     "fnb_selftest_glu_math": (_I32, [C.c_uint64, C.c_uint64, _P, _P]),
     "fnb_selftest_kv8_math": (_I32, [C.c_uint64, C.c_uint64, _P, _P]),

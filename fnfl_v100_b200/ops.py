@@ -251,6 +251,41 @@ def get_rows(fmt: str, table: torch.Tensor, ids: torch.Tensor, cols: int, out: t
     return out
 
 
+def _embed_args(fmt, table, tok, n_own, own, full, streams, col0, err):
+    _dev(table, torch.uint8, "table")
+    _dev(tok, torch.int32, "tok")
+    code, (bv, bb) = {"iq3_s": (_lib.TABLE_IQ3_S, (256, 110)), "q8_0": (_lib.TABLE_Q8_0, (32, 34))}[fmt]
+    n_vocab = table.numel() // (n_own // bv * bb)
+    for name, t in (("own", own), ("full", full), ("streams", streams)):
+        if t is not None:
+            _dev(t, torch.float32, name)
+    n_full = full.shape[-1] if full is not None else streams.shape[-1] if streams is not None else n_own
+    n_streams = streams.shape[-2] if streams is not None else 0
+    return _lib.EmbedArgs(_ptr(table).value, _ptr(tok).value, _ptr(own).value, _ptr(full).value, _ptr(streams).value,
+                          _ptr(err).value, n_vocab, tok.numel(), code, n_own, n_full, col0, n_streams)
+
+
+def embed_rows(fmt: str, table, tok, n_own: int, *, own=None, full=None, streams=None, col0: int = 0, err=None) -> None:
+    """fn::embed::embed_rows: decode each token's `n_own` features (IQ3_S or Q8_0 table) into own [rows][n_own], columns
+    col0.. of full [rows][n_full] and of every stream of streams [rows][n_streams][n_full]."""
+    a = _embed_args(fmt, table, tok, n_own, own, full, streams, col0, err)
+    _check(_lib.lib().fnb_embed_rows(C.byref(a), _stream()), "embed_rows")
+
+
+def embed_join(fmt: str, table, tok, n_own: int, peer, peer_col0: int, *, full=None, streams=None) -> None:
+    """fn::embed::embed_join: the peer card's half [rows][n_own] into columns peer_col0.. of full and the streams."""
+    _dev(peer, torch.float32, "peer")
+    a = _embed_args(fmt, table, tok, n_own, None, full, streams, 0, None)
+    _check(_lib.lib().fnb_embed_join(C.byref(a), _ptr(peer), peer_col0, _stream()), "embed_join")
+
+
+def embed_supply(fmt: str, table, tok, n_own: int, src, row0: int, *, own=None, full=None, streams=None, col0: int = 0):
+    """fn::embed::embed_supply: rows row0 .. row0 + len(src) - 1 overwritten from src [n][n_own]."""
+    _dev(src, torch.float32, "src")
+    a = _embed_args(fmt, table, tok, n_own, own, full, streams, col0, None)
+    _check(_lib.lib().fnb_embed_supply(C.byref(a), _ptr(src), row0, src.shape[0], _stream()), "embed_supply")
+
+
 def check_tokens(ids_host: torch.Tensor, n_vocab: int) -> int:
     """Host check before upload (fn::embed::check_tokens): 0, or 1 + the index of the first id outside [0, n_vocab)."""
     if ids_host.is_cuda or ids_host.dtype != torch.int32 or not ids_host.is_contiguous():

@@ -194,6 +194,45 @@ int32_t fnb_get_rows_q8_0(const void * table, int64_t n_vocab, const int32_t * i
                           int64_t rows, int32_t cols, void * stream);
 
 /*
+ * The reference engine's own embedding layouts (fn/kernels/embed/embed.h:70-105, embed_prompt.cu:26-146): the table
+ * holds `n_own` features of every token (one card's share) in IQ3_S (110-byte super-blocks, ggml-quants.c:2605-2644) or
+ * Q8_0; each decoded row is written to own [rows][n_own], to columns col0 .. col0 + n_own - 1 of full [rows][n_full] and
+ * to the same columns of each of n_streams streams [rows][n_streams][n_full] (null destinations are skipped; at least
+ * one must be given).  The reference's fixed widths are arguments: its card r passes n_own 1280, n_full 2560,
+ * col0 1280 r, n_streams 4; one GPU holding whole rows passes n_own = n_full, col0 = 0.
+ *   fnb_embed_rows    decode (replaces fn::embed::embed_rows); a bad id sets FNB_ERR_TOKEN, its row stays unwritten
+ *   fnb_embed_join    the peer card's F32 half [rows][n_own] into columns peer_col0 .. of full and the streams, skipping
+ *                     rows whose id is bad (replaces fn::embed::embed_join)
+ *   fnb_embed_supply  rows row0 .. row0 + n - 1 overwritten from src [n][n_own] in own, full and the streams
+ *                     (replaces fn::embed::embed_supply)
+ * All F32 pointers 16-byte aligned, n_own / n_full / col0 multiples of 4, n_own a multiple of 256 (IQ3_S) or 32 (Q8_0).
+ */
+#define FNB_TABLE_Q4_K 0
+#define FNB_TABLE_IQ3_XXS 1
+#define FNB_TABLE_Q8_0 2
+#define FNB_TABLE_IQ3_S 3
+
+typedef struct fnb_embed_args {
+    const void * table;
+    const int32_t * tok;
+    float * own;
+    float * full;
+    float * streams;
+    uint32_t * err;
+    int64_t n_vocab;
+    int64_t rows;
+    int32_t fmt; /* FNB_TABLE_IQ3_S or FNB_TABLE_Q8_0 */
+    int32_t n_own;
+    int32_t n_full;
+    int32_t col0;
+    int32_t n_streams;
+} fnb_embed_args;
+
+int32_t fnb_embed_rows(const fnb_embed_args * args, void * stream);
+int32_t fnb_embed_join(const fnb_embed_args * args, const float * peer, int32_t peer_col0, void * stream);
+int32_t fnb_embed_supply(const fnb_embed_args * args, const float * src, int64_t row0, int64_t n, void * stream);
+
+/*
  * Host-side check before upload: 0 when every id is in [0, n_vocab), else 1 + the index of the first bad id.
  * Replaces fn::embed::check_tokens (fn/kernels/embed/embed.h:56).
  */

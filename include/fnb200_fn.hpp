@@ -136,6 +136,44 @@ inline bool embed_rows(const rows_args & a, void * stream) {
     }
     return false;
 }
+// The reference's own layout (fn::embed::rows_args, fn/kernels/embed/embed.h:70-87): a card's IQ3_S or Q8_0 table of
+// n_own features per token, decoded into own [rows][n_own], the card's columns of full [rows][n_full] and of all
+// n_streams streams [rows][n_streams][n_full].  The reference's constants (1280, 2560, 4) are the defaults.
+struct card_rows_args {
+    const uint8_t * table = nullptr;  // the card's token_embd slice
+    const int32_t * tok = nullptr;    // [rows] device
+    int64_t n_vocab = 0;
+    int32_t rows = 0;
+    int32_t card = 0;
+    float * own = nullptr;            // [rows][n_own]
+    float * full = nullptr;           // [rows][n_full]
+    float * streams = nullptr;        // [rows][n_streams][n_full]
+    uint32_t * err = nullptr;
+    bool q8 = false;                  // the table is Q8_0 instead of IQ3_S
+    int32_t n_own = 1280, n_full = 2560, n_streams = 4;
+};
+inline fnb_embed_args to_c(const card_rows_args & a) {
+    fnb_embed_args c{};
+    c.table = a.table, c.tok = a.tok, c.own = a.own, c.full = a.full, c.streams = a.streams, c.err = a.err;
+    c.n_vocab = a.n_vocab, c.rows = a.rows, c.fmt = a.q8 ? FNB_TABLE_Q8_0 : FNB_TABLE_IQ3_S;
+    c.n_own = a.n_own, c.n_full = a.n_full, c.col0 = a.card * a.n_own, c.n_streams = a.n_streams;
+    return c;
+}
+inline bool embed_rows(const card_rows_args & a, void * stream) {
+    const fnb_embed_args c = to_c(a);
+    return fnb_embed_rows(&c, stream) == FNB_OK;
+}
+// peer: the received [rows][n_own] of the other card (two-card layout: its columns are (1 - card) * n_own ..)
+inline bool embed_join(const card_rows_args & a, const float * peer, void * stream) {
+    const fnb_embed_args c = to_c(a);
+    return fnb_embed_join(&c, peer, (1 - a.card) * a.n_own, stream) == FNB_OK;
+}
+// rows row0 .. row0 + n - 1 of the chunk take src [n][n_own] in own, full and every stream
+inline bool embed_supply(const card_rows_args & a, const float * src, int32_t row0, int32_t n, void * stream) {
+    const fnb_embed_args c = to_c(a);
+    return fnb_embed_supply(&c, src, row0, n, stream) == FNB_OK;
+}
+
 // host check before upload: true when every id is in [0, n_vocab)
 inline bool check_tokens(const int32_t * tok_host, int64_t rows, int64_t n_vocab) {
     return fnb_check_tokens(tok_host, rows, n_vocab) == 0;

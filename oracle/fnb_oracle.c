@@ -203,6 +203,37 @@ void fnbo_dequantize_row_iq3_xxs(const void * xv, float * y, int64_t k) {
     }
 }
 
+/* ---- IQ3_S (the reference engine's own embedding format): ggml/src/ggml-quants.c:2605-2644; block
+ * ggml/src/ggml-common.h:420-428 {fp16 d, qs[64], qh[8], signs[32], scales[4]}; codebook iq3s_grid (512 entries of
+ * four odd magnitudes).  Index n of a block: 9-bit codebook index qs[n] | bit (n % 8) of qh[n / 8] << 8, scale
+ * d * (1 + 2 * nibble (n / 8) of scales), sign bits (n % 2) * 4 .. + 3 of signs[n / 2]; independently at
+ * fn/quant/decode.cpp (decode_iq3_s) and fn/kernels/dense/iq3s.cuh:53-77. ---- */
+static const uint16_t o_grid3s_packed[512] = {
+#include "../fnfl_v100_b200/csrc/iq3s_grid_packed.inc"
+};
+
+void fnbo_dequantize_row_iq3_s(const void * xv, float * y, int64_t k) {
+    const uint8_t * x = (const uint8_t *) xv;
+    for (int64_t b = 0; b < k / 256; ++b, x += 110) {
+        uint16_t dh;
+        memcpy(&dh, x, 2);
+        const float d = fnbo_f16_to_f32(dh);
+        const uint8_t * qs = x + 2, * qh = x + 66, * signs = x + 74, * scales = x + 106;
+        for (int n = 0; n < 64; ++n) {
+            const int ib = n / 8, m = n % 8;
+            const int nib = (ib & 1) ? scales[ib / 2] >> 4 : scales[ib / 2] & 0x0f;
+            const float db = d * (float) (1 + 2 * nib);
+            const unsigned code = o_grid3s_packed[qs[n] | (((qh[ib] >> m) & 1u) << 8)];
+            const unsigned sg = signs[n / 2] >> (4 * (n & 1));
+            for (int j = 0; j < 4; ++j) {
+                const float g = (float) (2 * ((code >> (3 * j)) & 7u) + 1);
+                y[4 * n + j] = db * g * ((sg >> j) & 1u ? -1.0f : 1.0f);
+            }
+        }
+        y += 256;
+    }
+}
+
 /* ---- get_rows on a quantised table is the row decoder applied to row ids[t] (the ggml op's definition);
  * the bad-id rule is the reference kernel's: fn/kernels/embed/embed.cu:43-48, embed.h:15-17. ---- */
 void fnbo_get_rows_q4_k(const void * table, int64_t n_vocab, const int32_t * ids, float * out, uint32_t * err,

@@ -33,6 +33,7 @@ void fnbo_quantize_row_q8_1(const float * x, void * y, int64_t k);
 void fnbo_dequantize_row_q8_0(const void * x, float * y, int64_t k);
 void fnbo_dequantize_row_q4_k(const void * x, float * y, int64_t k);
 void fnbo_dequantize_row_iq3_xxs(const void * x, float * y, int64_t k);
+void fnbo_dequantize_row_iq3_s(const void * x, float * y, int64_t k);
 
 /* get_rows: out[t] = dequantised row ids[t]; a bad id sets FNBO_ERR_TOKEN in *err and leaves the row unwritten */
 void fnbo_get_rows_q4_k(const void * table, int64_t n_vocab, const int32_t * ids, float * out, uint32_t * err,

@@ -146,6 +146,13 @@ def dequantize_iq3_xxs(b: np.ndarray) -> np.ndarray:
     return out
 
 
+def dequantize_iq3_s(b: np.ndarray) -> np.ndarray:
+    b = np.ascontiguousarray(b, np.uint8)
+    out = np.empty(b.size // 110 * 256, np.float32)
+    lib().fnbo_dequantize_row_iq3_s(_p(b), _p(out), C.c_int64(out.size))
+    return out
+
+
 def get_rows(fmt: str, table: np.ndarray, n_vocab: int, ids: np.ndarray, cols: int, out: np.ndarray | None = None):
     """Returns (out [rows][cols] F32, err word).  Rows with a bad id keep `out`'s previous contents."""
     table = np.ascontiguousarray(table, np.uint8)

@@ -13,8 +13,8 @@ quant.npz    inputs F32 [n][32] (stress + random runs) and, from the reference: 
              (fn::quant::act_quantize_ref, act_ref.cpp:8-30) and KV8 (fn::quant::kv_q8_quantize,
              kv_q8_ref.cpp:72-97; rows of 64)
 decode.npz   seeded synthetic blocks (fn::quant::synth_blocks with the reference's seeds, synth.h:24-28) of
-             Q4_K, IQ3_XXS and Q8_0 and their decode by dequantize_row_q4_K / _iq3_xxs / _q8_0
-             (ggml-quants.c:1527, :2573, :551), cross-checked against fn::quant::decode_row (decode.cpp)
+             Q4_K, IQ3_XXS, Q8_0 and IQ3_S and their decode by dequantize_row_q4_K / _iq3_xxs / _q8_0 / _iq3_s
+             (ggml-quants.c:1527, :2573, :551, :2605), cross-checked against fn::quant::decode_row (decode.cpp)
 """
 import ctypes as C
 import os
@@ -89,7 +89,8 @@ def main() -> None:
     nblk = 96
     for i, (fmt, bb, bv, fn) in enumerate((("q4_k", 144, 256, r.dequantize_row_q4_K),
                                            ("iq3_xxs", 98, 256, r.dequantize_row_iq3_xxs),
-                                           ("q8_0", 34, 32, r.dequantize_row_q8_0))):
+                                           ("q8_0", 34, 32, r.dequantize_row_q8_0),
+                                           ("iq3_s", 110, 256, r.dequantize_row_iq3_s))):
         blk = np.empty(nblk * bb, np.uint8)
         assert r.ref_synth_blocks(fmt.encode(), C.c_uint64(0x464E464C + i), C.c_int64(nblk), O._p(blk)) == 0
         y = np.empty(nblk * bv, np.float32)

@@ -90,3 +90,25 @@ def test_rejections_enqueue_nothing(lib):
         assert lib.fnb_rope_neox_q8_0_append(C.byref(b), None) == R, field
     k8 = _lib.RopeKv8Args(a, None, A16)
     assert lib.fnb_rope_neox_kv8_append(C.byref(k8), None) == R
+
+
+def test_embed_layout_rejections(lib):
+    R = _lib.REJECTED
+    ok = dict(table=A16, tok=A16, own=A16, full=A16, streams=A16, err=None, n_vocab=100, rows=8, fmt=_lib.TABLE_IQ3_S,
+              n_own=1280, n_full=2560, col0=1280, n_streams=4)
+    for field, bad in (("n_own", 1000), ("col0", 1284), ("col0", 2), ("n_full", 1000), ("rows", 0), ("fmt", 0),
+                       ("tok", None), ("own", ODD), ("n_streams", 0), ("n_vocab", 0)):
+        a = _lib.EmbedArgs(**{**ok, field: bad})
+        assert lib.fnb_embed_rows(C.byref(a), None) == R, field
+    a = _lib.EmbedArgs(**ok)
+    assert lib.fnb_embed_join(C.byref(a), None, 0, None) == R
+    assert lib.fnb_embed_join(C.byref(a), A16, 1284, None) == R
+    assert lib.fnb_embed_supply(C.byref(a), A16, 6, 3, None) == R          # rows 6..8 of 8
+    assert lib.fnb_embed_supply(C.byref(a), ODD, 0, 1, None) == R
+    none = _lib.EmbedArgs(**{**ok, "own": None, "full": None, "streams": None})
+    assert lib.fnb_embed_rows(C.byref(none), None) == R
+    # fused norm + requant
+    assert lib.fnb_rms_norm_q8_1(A16, A16, 1e-6, A16, None, 4, 2040, None) == R
+    assert lib.fnb_rms_norm_q8_0(A16, A16, 1e-6, None, None, 4, 2048, None) == R
+    assert lib.fnb_rms_norm_act(A16, A16, 1e-6, A16, None, None, 4, 2048, None) == R
+    assert lib.fnb_rms_norm_q8_1(A16, A16, 1e-6, A16, None, 4, 8192, None) == R

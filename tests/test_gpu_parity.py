@@ -382,3 +382,61 @@ def test_rms_norm_fused_with_requantisation(dev, oracle, rows, cols, fmt):
     a = res2[0] if fmt == "act" else res2
     b = res[0] if fmt == "act" else res
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("fmt,rows", [("iq3_s", 1), ("iq3_s", 7), ("iq3_s", 1536), ("q8_0", 33)])
+def test_reference_embedding_layout_two_cards(dev, oracle, fmt, rows):
+    """The reference's pe-test (fn/kernels/ple/ple_prompt_test.cpp:27-147) restated: two card tables of 1280 features,
+    every output row of own, full and the four streams on both cards must be memcmp-equal to the CPU decode; then the
+    join of the peer half, a supplied-row overwrite, and a bad id that leaves its rows unwritten."""
+    n_own, n_full, n_streams, vocab = 1280, 2560, 4, 4096
+    gold = np.load(os.path.join(GOLD, "decode.npz"))
+    g = synth.rng(0x454d42)
+    bb, bv = (110, 256) if fmt == "iq3_s" else (34, 32)
+    pool = gold[fmt + "_blocks"]                                      # blocks made by the reference's synth_blocks
+    tables = [pool[g.integers(0, len(pool), (vocab, n_own // bv))].reshape(vocab, -1).copy() for _ in range(2)]
+    deq = oracle.dequantize_iq3_s if fmt == "iq3_s" else oracle.dequantize_q8_0
+    tok = g.integers(0, vocab, rows).astype(np.int32)
+    if rows >= 7:
+        tok[3] = vocab                                                 # out of range
+    good = (tok >= 0) & (tok < vocab)
+    want_half = [np.where(good[:, None], deq(t[np.clip(tok, 0, vocab - 1)]).reshape(rows, n_own), np.nan).astype(np.float32)
+                 for t in tables]
+    dtok = to_dev(tok, dev)
+    outs = []
+    for card in (0, 1):
+        own = Guarded((rows, n_own), torch.float32, dev)
+        full = Guarded((rows, n_full), torch.float32, dev)
+        streams = Guarded((rows, n_streams, n_full), torch.float32, dev)
+        err = ops.new_err(dev)
+        ops.embed_rows(fmt, to_dev(tables[card], dev), dtok, n_own, own=own.live, full=full.live, streams=streams.live,
+                       col0=card * n_own, err=err)
+        torch.cuda.synchronize()
+        assert int(err.item()) == (0 if good.all() else ops.ERR_TOKEN)
+        outs.append((own, full, streams))
+    poison = np.frombuffer(bytes([POISON] * 4), np.float32)[0]
+    for card in (0, 1):
+        own, full, streams = outs[card]
+        peer = outs[1 - card][0]
+        ops.embed_join(fmt, to_dev(tables[card], dev), dtok, n_own, peer.live, (1 - card) * n_own, full=full.live,
+                       streams=streams.live)
+        torch.cuda.synchronize()
+        for o in (own, full, streams):
+            o.check_guards()
+        want_full = np.full((rows, n_full), poison, np.float32)
+        for c in (0, 1):
+            want_full[good, c * n_own:(c + 1) * n_own] = want_half[c][good]
+        assert np.array_equal(bits(own.numpy())[good], bits(want_half[card])[good])
+        assert (bits(own.numpy())[~good] == bits(np.array([poison]))[0]).all()       # unwritten
+        assert np.array_equal(bits(full.numpy()), bits(want_full))
+        for s in range(n_streams):
+            assert np.array_equal(bits(streams.numpy()[:, s]), bits(want_full))
+    if rows >= 7:   # supplied rows (an image's) over rows 2..4 of card 0, the bad row included
+        own, full, streams = outs[0]
+        src = synth.normal(g, (3, n_own))
+        ops.embed_supply(fmt, to_dev(tables[0], dev), dtok, n_own, to_dev(src, dev), 2, own=own.live, full=full.live,
+                         streams=streams.live, col0=0)
+        torch.cuda.synchronize()
+        assert np.array_equal(bits(own.numpy()[2:5]), bits(src))
+        assert np.array_equal(bits(full.numpy()[2:5, :n_own]), bits(src))
+        assert np.array_equal(bits(streams.numpy()[2:5, 3, :n_own]), bits(src))

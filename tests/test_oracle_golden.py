@@ -41,9 +41,10 @@ def test_kv8_matches_reference(oracle, quant):
     assert np.array_equal(scales, quant["kv8_scales"])
 
 
-@pytest.mark.parametrize("fmt", ["q4_k", "iq3_xxs", "q8_0"])
+@pytest.mark.parametrize("fmt", ["q4_k", "iq3_xxs", "q8_0", "iq3_s"])
 def test_decoders_match_reference_bits(oracle, decode, fmt):
-    fn = {"q4_k": oracle.dequantize_q4_k, "iq3_xxs": oracle.dequantize_iq3_xxs, "q8_0": oracle.dequantize_q8_0}[fmt]
+    fn = {"q4_k": oracle.dequantize_q4_k, "iq3_xxs": oracle.dequantize_iq3_xxs, "q8_0": oracle.dequantize_q8_0,
+          "iq3_s": oracle.dequantize_iq3_s}[fmt]
     got = fn(decode[fmt + "_blocks"])
     assert np.array_equal(got.view(np.uint32), decode[fmt + "_values"].reshape(-1).view(np.uint32))
 
