@@ -51,12 +51,15 @@ def ncu_traffic(kernel: str):
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi.  It is started before the warm-up steps
+    (nvidia-smi takes tens of milliseconds to produce its first line); the samples that arrive between begin() and
+    end() are the timed region's.  A region shorter than the sampling period falls back to the samples taken while
+    the same kernels were running in warm-up, and says so in `window`."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.rows, self.proc = [], None
+        self.rows, self.proc, self.t0, self.t1 = [], None, None, None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.Q,
                                           "--format=csv,noheader,nounits", "-lms", "10"],
@@ -68,22 +71,34 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def begin(self):
+        self.t0 = time.time()
+
+    def end(self):
+        self.t1 = time.time()
 
     def stop(self) -> dict:
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
+        time.sleep(0.03)  # let the line that was sampled during the region arrive
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except Exception:
             pass
-        sm = sorted(int(r[0]) for r in self.rows if len(r) >= 6 and r[0].isdigit())
-        mx = [int(r[1]) for r in self.rows if len(r) >= 6 and r[1].isdigit()]
+        ok = [(t, r) for t, r in self.rows if len(r) >= 6 and r[0].isdigit()]
+        inside = [r for t, r in ok if self.t0 is not None and self.t0 <= t <= (self.t1 or t) + 0.02]
+        window = "timed region"
+        if not inside:
+            inside, window = [r for t, r in ok if self.t0 is None or t <= (self.t1 or t) + 0.02], "warm-up + timed region"
+        sm = sorted(int(r[0]) for r in inside)
+        mx = [int(r[1]) for r in inside if r[1].isdigit()]
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v.lower() == "active"})
+        reasons = sorted({n for r in inside for n, v in zip(names, r[2:6]) if v.lower() == "active"})
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(sm)}
+                "reasons": reasons, "samples": len(sm), "window": window}
 
 
 # ---- the CPU arm ---------------------------------------------------------------------------------------------
@@ -226,21 +241,24 @@ def run_ours(args) -> None:
     stages = PrefillChain.STAGES
     peak, peak_kind = hbm_peak()
 
+    sampler = ClockSampler(local) if rank == 0 else None
     for _ in range(max(args.warmup, 3)):
         chain.step()
     barrier()
-
-    sampler = ClockSampler(local) if rank == 0 else None
     K = args.steps
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(stages) + 1)] for _ in range(K)]
     cur = torch.cuda.current_stream()
     barrier()
+    if sampler:
+        sampler.begin()
     for k in range(K):
         ev[k][0].record(cur)
         for i, name in enumerate(stages):
             getattr(chain, name)()
             ev[k][i + 1].record(cur)
     barrier()
+    if sampler:
+        sampler.end()
     total_ms = ev[0][0].elapsed_time(ev[K - 1][len(stages)])
     stage_ms = [sum(ev[k][i].elapsed_time(ev[k][i + 1]) for k in range(K)) / K for i in range(len(stages))]
     clocks = sampler.stop() if sampler else None

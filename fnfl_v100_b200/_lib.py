@@ -38,6 +38,12 @@ class EmbedArgs(C.Structure):
 TABLE_Q4_K, TABLE_IQ3_XXS, TABLE_Q8_0, TABLE_IQ3_S = 0, 1, 2, 3
 
 
+class GgufTensor(C.Structure):
+    """fnb_gguf_tensor"""
+    _fields_ = [("ne", C.c_int64 * 4), ("offset", C.c_int64), ("row_bytes", C.c_int64), ("n_rows", C.c_int64),
+                ("n_dims", C.c_int32), ("type", C.c_int32)]
+
+
 class RopeKv8Args(C.Structure):
     """fnb_rope_kv8_args"""
     _fields_ = [("base", RopeKvArgs), ("k_scale", C.c_void_p), ("v_scale", C.c_void_p)]
@@ -69,6 +75,11 @@ SIGNATURES = {
     "fnb_embed_join": (_I32, [C.POINTER(EmbedArgs), _P, _I32, _P]),
     "fnb_embed_supply": (_I32, [C.POINTER(EmbedArgs), _P, _I64, _I64, _P]),
     "fnb_check_tokens": (_I64, [_P, _I64, _I64]),
+    "fnb_gguf_open": (_P, [C.c_char_p]),
+    "fnb_gguf_close": (None, [_P]),
+    "fnb_gguf_n_tensors": (_I64, [_P]),
+    "fnb_gguf_find": (_I32, [_P, C.c_char_p, C.POINTER(GgufTensor)]),
+    "fnb_gguf_read_rows": (_I32, [_P, C.POINTER(GgufTensor), _I64, _I64, _P]),
     "fnb_selftest_glu_math": (_I32, [C.c_uint64, C.c_uint64, _P, _P]),
     "fnb_selftest_kv8_math": (_I32, [C.c_uint64, C.c_uint64, _P, _P]),
 }

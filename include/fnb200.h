@@ -233,6 +233,29 @@ int32_t fnb_embed_join(const fnb_embed_args * args, const float * peer, int32_t 
 int32_t fnb_embed_supply(const fnb_embed_args * args, const float * src, int64_t row0, int64_t n, void * stream);
 
 /*
+ * Host-only: a minimal GGUF (v2 / v3) tensor-directory reader, so that a quantised table such as token_embd.weight can
+ * be found in a model file and read row by row into host memory for upload.  It covers what this path needs of the
+ * reference's fn/borrowed/gguf_tensors.h and fn/loader row slicing (fn/loader/loader.h); metadata is skipped except
+ * general.alignment.  `type` is the ggml type number (0 F32, 1 F16, 8 Q8_0, 12 Q4_K, 18 IQ3_XXS, 21 IQ3_S); row_bytes
+ * is 0 for a type this library does not decode.  fnb_gguf_open returns null for a missing or malformed file.
+ */
+typedef struct fnb_gguf fnb_gguf;
+typedef struct fnb_gguf_tensor {
+    int64_t ne[4];     /* extents, ne[0] = values per row; unused dims are 1 */
+    int64_t offset;    /* from the start of the file's data section */
+    int64_t row_bytes; /* ne[0] values in the tensor's block format */
+    int64_t n_rows;    /* ne[1] * ne[2] * ne[3] */
+    int32_t n_dims;
+    int32_t type;
+} fnb_gguf_tensor;
+
+fnb_gguf * fnb_gguf_open(const char * path);
+void fnb_gguf_close(fnb_gguf * g);
+int64_t fnb_gguf_n_tensors(const fnb_gguf * g);
+int32_t fnb_gguf_find(const fnb_gguf * g, const char * name, fnb_gguf_tensor * out);
+int32_t fnb_gguf_read_rows(fnb_gguf * g, const fnb_gguf_tensor * t, int64_t row0, int64_t n_rows, void * dst_host);
+
+/*
  * Host-side check before upload: 0 when every id is in [0, n_vocab), else 1 + the index of the first bad id.
  * Replaces fn::embed::check_tokens (fn/kernels/embed/embed.h:56).
  */
