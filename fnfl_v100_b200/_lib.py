@@ -82,6 +82,7 @@ SIGNATURES = {
     "fnb_gguf_read_rows": (_I32, [_P, C.POINTER(GgufTensor), _I64, _I64, _P]),
     "fnb_selftest_glu_math": (_I32, [C.c_uint64, C.c_uint64, _P, _P]),
     "fnb_selftest_kv8_math": (_I32, [C.c_uint64, C.c_uint64, _P, _P]),
+    "fnb_selftest_expf": (_I32, [_P, _P]),
 }
 
 _lib = None

@@ -30,8 +30,9 @@ __device__ __forceinline__ void load_exp2_table() {
     for (int i = threadIdx.x; i < 32; i += blockDim.x) s_exp2_tab[i] = c_exp2_tab[i];
 }
 
-// e^x for |x| < 88 (no overflow, underflow or NaN handling): 12 FP64 operations, two conversions
-__device__ __forceinline__ float expf_core(float x) {
+// e^x for |x| < 88 (no overflow, underflow or NaN handling), operation for operation the definition: 12 FP64
+// operations, two conversions
+__device__ __forceinline__ float expf_steps(float x) {
     const double z = __dmul_rn(c_exp_k[0], double(x));
     double kd = __dadd_rn(z, c_exp_k[1]);
     const unsigned long long ki = (unsigned long long) __double_as_longlong(kd);
@@ -47,6 +48,24 @@ __device__ __forceinline__ float expf_core(float x) {
     return __double2float_rn(y);
 }
 
+// The same function in 8 FP64 operations: the reduction as above (so k and r are the definition's), the cubic as
+// a fused Horner chain.  The two doubles differ by at most 2 units in the last place and the FLOAT they round to is
+// the same for EVERY float |x| < 88: checked by enumerating all 2 x 0x42b00000 inputs, on the CPU
+// (tests/cpp/expf_fma_exhaustive.c) and on the device (fnb_selftest_expf).  Fusing the reduction too
+// (r = fma(x, N/ln2, -k)) is NOT equivalent: two inputs round differently.
+__device__ __forceinline__ float expf_core(float x) {
+    const double z = __dmul_rn(c_exp_k[0], double(x));
+    double kd = __dadd_rn(z, c_exp_k[1]);
+    const unsigned long long ki = (unsigned long long) __double_as_longlong(kd);
+    kd = __dsub_rn(kd, c_exp_k[1]);
+    const double r = __dsub_rn(z, kd);
+    const unsigned long long t = s_exp2_tab[ki & 31] + (ki << 47);
+    const double s = __longlong_as_double((long long) t);
+    double q = __fma_rn(c_exp_k[2], r, c_exp_k[3]);
+    q = __fma_rn(q, r, c_exp_k[4]);
+    return __double2float_rn(__dmul_rn(__fma_rn(q, r, 1.0), s));
+}
+
 static __device__ __noinline__ float expf_special(float x) {
     const uint32_t bits = __float_as_uint(x);
     if (bits == 0xff800000u) return 0.0f;
@@ -54,12 +73,12 @@ static __device__ __noinline__ float expf_special(float x) {
     if (x > 0x1.62e42ep6f) return __uint_as_float(0x7f800000u);
     if (x < -0x1.9fe368p6f) return 0.0f;
     if (x < -0x1.9d1d9ep6f) return 0x1p-149f;
-    return expf_core(x);
+    return expf_steps(x);
 }
 
 // e^x for every float, special cases included
 __device__ __forceinline__ float exact_expf(float x) {
-    return (__float_as_uint(x) & 0x7fffffffu) >= 0x42b00000u ? expf_special(x) : expf_core(x);  // |x| >= 88 or NaN
+    return (__float_as_uint(x) & 0x7fffffffu) >= 0x42b00000u ? expf_special(x) : expf_steps(x);  // |x| >= 88 or NaN
 }
 
 // sine polynomial on the reduced argument

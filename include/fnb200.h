@@ -275,6 +275,13 @@ int32_t fnb_selftest_glu_math(uint64_t n, uint64_t seed, unsigned long long * mi
  */
 int32_t fnb_selftest_kv8_math(uint64_t n, uint64_t seed, unsigned long long * mismatches, void * stream);
 
+/*
+ * Diagnostic with no counterpart in the reference: for EVERY float |x| < 88 (both signs, 2 x 0x42b00000 inputs)
+ * compares the SwiGLU fast path's e^x (reduction as defined, cubic as a fused Horner chain, 8 FP64 operations) with the
+ * operation-for-operation evaluation of the definition (12) and adds the number of differing results to *mismatches.
+ */
+int32_t fnb_selftest_expf(unsigned long long * mismatches, void * stream);
+
 #ifdef __cplusplus
 }
 #endif

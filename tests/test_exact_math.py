@@ -55,3 +55,19 @@ def test_special_values(oracle):
     assert l.fnbo_sinf_exact(0.0) == 0.0 and l.fnbo_cosf_exact(0.0) == 1.0
     assert np.isnan(l.fnbo_sinf_exact(float("inf")))
     assert l.fnbo_sinf_exact(1e-5) == np.float32(1e-5)
+
+
+def test_fused_horner_expf_is_the_same_function_for_every_float(tmp_path):
+    """Enumerates all floats |x| < 88: the CUDA fast path's evaluation order (fused Horner cubic) gives the float the
+    definition gives, and fusing the reduction as well does not (so the kernels must not do that)."""
+    if "fma" not in open("/proc/cpuinfo").read().split("flags", 1)[-1].split("\n", 1)[0].split():
+        import pytest
+        pytest.skip("host has no hardware fused multiply-add; the enumeration would take hours in software")
+    here = os.path.dirname(os.path.abspath(__file__))
+    exe = str(tmp_path / "expf_fma_exhaustive.bin")
+    subprocess.run(["gcc", "-O2", "-mfma", "-ffp-contract=off", "-o", exe,
+                    os.path.join(here, "cpp", "expf_fma_exhaustive.c"), "-lm", "-lpthread"], check=True)
+    out = subprocess.run([exe, str(os.cpu_count() or 8)], check=True, capture_output=True, text=True).stdout.split()
+    rec = dict(zip(out[0::2], map(int, out[1::2])))
+    assert rec["inputs"] == 2 * 0x42b00000 and rec["float_differ"] == 0 and rec["max_double_ulp"] <= 2
+    assert rec["float_differ_fused_reduction"] > 0

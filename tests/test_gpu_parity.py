@@ -340,6 +340,17 @@ def test_glu_fast_path_equals_generic_path_on_its_whole_domain(dev):
     assert int(bad.item()) == 0
 
 
+def test_fused_expf_equals_the_definition_for_every_float(dev):
+    """All 2 x 0x42b00000 floats |x| < 88: the 8-operation evaluation rounds to the same float as the 12-operation one."""
+    import ctypes as C
+    from fnfl_v100_b200 import _lib
+    bad = torch.zeros(1, dtype=torch.int64, device=dev)
+    st = _lib.lib().fnb_selftest_expf(C.c_void_p(bad.data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert st == 0
+    torch.cuda.synchronize()
+    assert int(bad.item()) == 0
+
+
 def test_kv8_written_out_division_equals_ieee_division(dev):
     """Every positive finite FP16 scale x 2^27 pseudo-random values (half on exact half steps): same codes as __fdiv_rn."""
     import ctypes as C
