@@ -56,6 +56,89 @@ __device__ __forceinline__ void scale_min_k4(int is, uint32_t s0, uint32_t s1, u
     *mn = float(mv);
 }
 
+// one super-block: hdr its first 16 bytes (d, dmin, scales), w this lane's nibble word
+__device__ __forceinline__ void q4_k_finish(uint4 hdr, uint32_t w, float * dst256, int grp, int pos) {
+    const float d = f16_bits_to_f32(uint16_t(hdr.x & 0xffffu));
+    const float dmin = f16_bits_to_f32(uint16_t(hdr.x >> 16));
+    float sc, mn;
+    scale_min_k4(2 * grp, hdr.y, hdr.z, hdr.w, &sc, &mn);
+    const float d1 = __fmul_rn(d, sc), m1 = __fmul_rn(dmin, mn);
+    scale_min_k4(2 * grp + 1, hdr.y, hdr.z, hdr.w, &sc, &mn);
+    const float d2 = __fmul_rn(d, sc), m2 = __fmul_rn(dmin, mn);
+    float4 lo, hi;
+    lo.x = __fsub_rn(__fmul_rn(d1, float(w & 15u)), m1);
+    lo.y = __fsub_rn(__fmul_rn(d1, float((w >> 8) & 15u)), m1);
+    lo.z = __fsub_rn(__fmul_rn(d1, float((w >> 16) & 15u)), m1);
+    lo.w = __fsub_rn(__fmul_rn(d1, float((w >> 24) & 15u)), m1);
+    hi.x = __fsub_rn(__fmul_rn(d2, float((w >> 4) & 15u)), m2);
+    hi.y = __fsub_rn(__fmul_rn(d2, float((w >> 12) & 15u)), m2);
+    hi.z = __fsub_rn(__fmul_rn(d2, float((w >> 20) & 15u)), m2);
+    hi.w = __fsub_rn(__fmul_rn(d2, float(w >> 28)), m2);
+    float4 * o = reinterpret_cast<float4 *>(dst256 + grp * 64) + pos;
+    st_stream(o, lo);
+    st_stream(o + 8, hi);
+}
+
+// Rows of 8 super-blocks (2048 columns, 1152 bytes): the whole row is fetched with three 128-bit loads per lane one
+// row ahead of its decode and parked in the warp's shared-memory slot (ids run two rows ahead), so no lane ever
+// waits on a global load it has just issued.
+constexpr int kQ4kRowBytes = 8 * 144;
+// CTAs of a staged kernel resident per SM (the launch bound holds registers to that) and CTAs LAUNCHED per SM.
+// Measured at 65536 rows: a grid of exactly one resident wave (6 per SM, 11 rows per warp) ran at 83 % of the HBM
+// roofline, 8 per SM at 87 %, 24 at 91-93 %, 32 and more at 93-95 %: SMs do not drain their share of rows at the
+// same rate, and only the hardware's CTA dispatch evens that out.  At 32 per SM a warp still decodes two rows or
+// more, so the row fetched ahead keeps paying.
+constexpr int kStagedCtasPerSm = 6;
+constexpr int kStagedGridPerSm = 32;
+__device__ __forceinline__ void q4_k_fetch_row(const uint8_t * __restrict__ table, int32_t id, int lane, uint4 (&r)[3]) {
+    const uint4 * p = reinterpret_cast<const uint4 *>(table + int64_t(id) * kQ4kRowBytes);
+    r[0] = __ldg(p + lane);
+    r[1] = __ldg(p + 32 + lane);
+    r[2] = lane < kQ4kRowBytes / 16 - 64 ? __ldg(p + 64 + lane) : make_uint4(0u, 0u, 0u, 0u);
+}
+__global__ void __launch_bounds__(kWarpsPerCta * 32, kStagedCtasPerSm)
+    get_rows_q4_k_staged_kernel(const uint8_t * __restrict__ table, int64_t n_vocab, const int32_t * __restrict__ ids,
+                                float * __restrict__ out, uint32_t * err, int64_t rows) {
+    __shared__ __align__(16) uint8_t s_rows[kWarpsPerCta][kQ4kRowBytes];
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = int64_t(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
+    const int64_t n_warps = int64_t(gridDim.x) * kWarpsPerCta;
+    const int grp = lane >> 3, pos = lane & 7;
+    uint8_t * buf = s_rows[threadIdx.x >> 5];
+    auto valid = [&](int32_t id) { return id >= 0 && id < n_vocab; };
+
+    int32_t id = warp < rows ? __ldg(ids + warp) : -1;
+    int32_t id_next = warp + n_warps < rows ? __ldg(ids + warp + n_warps) : -1;
+    uint4 r[3] = {};
+    if (valid(id)) q4_k_fetch_row(table, id, lane, r);
+    for (int64_t t = warp; t < rows; t += n_warps) {
+        const bool ok = valid(id);
+        if (ok) {
+            reinterpret_cast<uint4 *>(buf)[lane] = r[0];
+            reinterpret_cast<uint4 *>(buf)[32 + lane] = r[1];
+            if (lane < kQ4kRowBytes / 16 - 64) reinterpret_cast<uint4 *>(buf)[64 + lane] = r[2];
+        } else if (lane == 0 && err != nullptr) {
+            atomicOr(err, FNB_ERR_TOKEN);
+        }
+        __syncwarp();
+        const int64_t t2 = t + 2 * n_warps;
+        const int32_t id_after = t2 < rows ? __ldg(ids + t2) : -1;
+        if (valid(id_next)) q4_k_fetch_row(table, id_next, lane, r);
+        if (ok) {
+            float * dst = out + t * 2048;
+#pragma unroll
+            for (int sb = 0; sb < 8; ++sb) {
+                const uint8_t * blk = buf + 144 * sb;
+                q4_k_finish(*reinterpret_cast<const uint4 *>(blk), reinterpret_cast<const uint32_t *>(blk + 16)[lane],
+                            dst + 256 * sb, grp, pos);
+            }
+        }
+        __syncwarp();  // every lane is done with the slot before the next row overwrites it
+        id = id_next;
+        id_next = id_after;
+    }
+}
+
 template <int NSB>  // super-blocks per row held in flight at once
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
     get_rows_q4_k_kernel(const uint8_t * __restrict__ table, int64_t n_vocab, const int32_t * __restrict__ ids,
@@ -85,28 +168,7 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32)
             }
 #pragma unroll
             for (int j = 0; j < NSB; ++j) {
-                if (sb0 + j < nsb) {
-                    const float d = f16_bits_to_f32(uint16_t(hdr[j].x & 0xffffu));
-                    const float dmin = f16_bits_to_f32(uint16_t(hdr[j].x >> 16));
-                    float sc, mn;
-                    scale_min_k4(2 * grp, hdr[j].y, hdr[j].z, hdr[j].w, &sc, &mn);
-                    const float d1 = __fmul_rn(d, sc), m1 = __fmul_rn(dmin, mn);
-                    scale_min_k4(2 * grp + 1, hdr[j].y, hdr[j].z, hdr[j].w, &sc, &mn);
-                    const float d2 = __fmul_rn(d, sc), m2 = __fmul_rn(dmin, mn);
-                    const uint32_t w = qw[j];
-                    float4 lo, hi;
-                    lo.x = __fsub_rn(__fmul_rn(d1, float(w & 15u)), m1);
-                    lo.y = __fsub_rn(__fmul_rn(d1, float((w >> 8) & 15u)), m1);
-                    lo.z = __fsub_rn(__fmul_rn(d1, float((w >> 16) & 15u)), m1);
-                    lo.w = __fsub_rn(__fmul_rn(d1, float((w >> 24) & 15u)), m1);
-                    hi.x = __fsub_rn(__fmul_rn(d2, float((w >> 4) & 15u)), m2);
-                    hi.y = __fsub_rn(__fmul_rn(d2, float((w >> 12) & 15u)), m2);
-                    hi.z = __fsub_rn(__fmul_rn(d2, float((w >> 20) & 15u)), m2);
-                    hi.w = __fsub_rn(__fmul_rn(d2, float(w >> 28)), m2);
-                    float4 * o = reinterpret_cast<float4 *>(dst + (sb0 + j) * 256 + grp * 64) + pos;
-                    st_stream(o, lo);
-                    st_stream(o + 8, hi);
-                }
+                if (sb0 + j < nsb) q4_k_finish(hdr[j], qw[j], dst + (sb0 + j) * 256, grp, pos);
             }
         }
     }
@@ -126,22 +188,30 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32)
 //   * no staging: the 98-byte super-blocks are 2-byte aligned, so each lane fetches exactly the pieces it needs (d,
 //     its two index bytes, its two scale/sign words as halves) straight from global memory through L1, four
 //     super-blocks issued before the first use, as the Q4_K kernel does;
-//   * the codebook is expanded to FLOAT magnitudes in shared memory (256 x float4 = 4 KiB), so an index costs one
-//     128-bit shared load and no byte extraction or integer-to-float conversion;
-//   * a sign is applied by choosing +db or -db as the multiplier ((-db) g and -(db g) are the same bits); the sign
-//     byte comes from the 128-entry sign table in shared memory.
+//   * the codebook sits in shared memory as one 32-bit word of four magnitude bytes per entry; a byte becomes a
+//     float with one byte permute and one exact subtraction (an earlier build kept FLOAT magnitudes, 256 x float4:
+//     no conversion, but the random 128-bit lookups cost ~11 shared-memory wavefronts each and, with the stores'
+//     own wavefronts, kept the load/store pipe ~70 % busy at 77 % of the HBM roofline);
+//   * a sign is applied by choosing +db or -db as the multiplier ((-db) g and -(db g) are the same bits); the
+//     eighth sign bit is the parity of the seven stored ones (a population count, no table).
 __device__ __forceinline__ uint32_t ldg_u16(const uint8_t * p) { return __ldg(reinterpret_cast<const uint16_t *>(p)); }
 __device__ __forceinline__ uint32_t ldg_u8(const uint8_t * p) { return __ldg(p); }
 
+// magnitude byte J of a codebook word as a float: 0x4B0000bb is 2^23 + bb exactly, so one byte permute and one
+// exact subtraction convert it
+template <int J>
+__device__ __forceinline__ float grid_byte_f32(uint32_t g) {
+    return __fadd_rn(__uint_as_float(__byte_perm(g, 0x4B000000u, 0x7540u + J)), -8388608.0f);
+}
 // one index: aux is its 32-value group's scale/sign word, n the index within the super-block
-__device__ __forceinline__ float4 iq3_decode(float d, uint32_t q, uint32_t aux, int n, const float4 * s_grid,
-                                             const uint8_t * s_signs) {
+__device__ __forceinline__ float4 iq3_decode(float d, uint32_t q, uint32_t aux, int n, const uint32_t * s_grid) {
     const float db = __fmul_rn(__fmul_rn(d, __fadd_rn(0.5f, float(aux >> 28))), 0.5f);
     const float nb = -db;
-    const uint32_t sg = uint32_t(s_signs[(aux >> (7 * ((n >> 1) & 3))) & 127u]) >> (4 * (n & 1));
-    const float4 g = s_grid[q];
-    return make_float4(__fmul_rn((sg & 1u) ? nb : db, g.x), __fmul_rn((sg & 2u) ? nb : db, g.y),
-                       __fmul_rn((sg & 4u) ? nb : db, g.z), __fmul_rn((sg & 8u) ? nb : db, g.w));
+    const uint32_t s7 = (aux >> (7 * ((n >> 1) & 3))) & 127u;            // seven stored sign bits,
+    const uint32_t sg = (s7 | ((__popc(s7) & 1u) << 7)) >> (4 * (n & 1));  // the eighth is their parity
+    const uint32_t g = s_grid[q];
+    return make_float4(__fmul_rn((sg & 1u) ? nb : db, grid_byte_f32<0>(g)), __fmul_rn((sg & 2u) ? nb : db, grid_byte_f32<1>(g)),
+                       __fmul_rn((sg & 4u) ? nb : db, grid_byte_f32<2>(g)), __fmul_rn((sg & 8u) ? nb : db, grid_byte_f32<3>(g)));
 }
 
 struct iq3_sb_regs {
@@ -157,37 +227,37 @@ __device__ __forceinline__ void iq3_load(iq3_sb_regs & r, const uint8_t * blk, i
     r.a1lo = ldg_u16(blk + o_aux + 16);
     r.a1hi = ldg_u16(blk + o_aux + 18);
 }
-__device__ __forceinline__ void iq3_finish(const iq3_sb_regs & r, float * dst256, int lane, const float4 * s_grid,
-                                           const uint8_t * s_signs) {
+__device__ __forceinline__ void iq3_finish(const iq3_sb_regs & r, float * dst256, int lane, const uint32_t * s_grid) {
     const float d = f16_bits_to_f32(uint16_t(r.dq));
     float4 * o = reinterpret_cast<float4 *>(dst256) + lane;
-    st_stream(o, iq3_decode(d, r.q0, r.a0lo | (r.a0hi << 16), lane, s_grid, s_signs));
-    st_stream(o + 32, iq3_decode(d, r.q1, r.a1lo | (r.a1hi << 16), lane, s_grid, s_signs));  // n = lane + 32: same parity bits
+    st_stream(o, iq3_decode(d, r.q0, r.a0lo | (r.a0hi << 16), lane, s_grid));
+    st_stream(o + 32, iq3_decode(d, r.q1, r.a1lo | (r.a1hi << 16), lane, s_grid));  // n = lane + 32: same parity bits
 }
 
-template <int NSB>  // super-blocks per row when known at compile time (a multiple of 4), 0 = read cols at run time
+// any column count that is a multiple of 256 (2048 columns take the staged kernel after this one)
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
     get_rows_iq3_xxs_kernel(const uint8_t * __restrict__ table, int64_t n_vocab, const int32_t * __restrict__ ids,
                             float * __restrict__ out, uint32_t * err, int64_t rows, int cols) {
-    __shared__ float4 s_grid[256];    // the codebook's four magnitudes per entry, as floats
-    __shared__ uint8_t s_signs[128];  // 7 stored sign bits -> 8 sign bits (the eighth is their parity)
+    // The codebook's four magnitudes per entry as BYTES (one 32-bit word per entry): a lookup is a 32-bit shared
+    // load, where 32 random entries collide on a bank about three deep.  As float4 entries (one 128-bit load, no
+    // conversion) the same lookup took about eleven wavefronts and the kernel ran against the shared-memory pipe.
+    __shared__ uint32_t s_grid[256];
     for (int i = threadIdx.x; i < 256; i += blockDim.x) {
         const uint32_t c = c_iq3xxs_grid_packed[i];
-        float m[4];
+        uint32_t w = 0;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const uint32_t lvl = (c >> (3 * j)) & 7u;
-            m[j] = lvl == 7u ? 62.0f : float(4u + 8u * lvl);
+            w |= (lvl == 7u ? 62u : 4u + 8u * lvl) << (8 * j);
         }
-        s_grid[i] = make_float4(m[0], m[1], m[2], m[3]);
+        s_grid[i] = w;
     }
-    for (int i = threadIdx.x; i < 128; i += blockDim.x) s_signs[i] = uint8_t(i | ((__popc(i) & 1) << 7));
     __syncthreads();
 
     const int lane = threadIdx.x & 31;
     const int64_t warp = int64_t(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
     const int64_t n_warps = int64_t(gridDim.x) * kWarpsPerCta;
-    const int nsb = NSB > 0 ? NSB : cols / 256;
+    const int nsb = cols / 256;
     const int64_t row_bytes = int64_t(nsb) * 98;
 
     int32_t id_next = warp < rows ? __ldg(ids + warp) : 0;  // ids run one row ahead of the decode
@@ -200,22 +270,98 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32)
         }
         const uint8_t * row = table + int64_t(id) * row_bytes;
         float * dst = out + t * cols;
-        if constexpr (NSB > 0) {
-#pragma unroll
-            for (int sb0 = 0; sb0 < NSB; sb0 += 4) {
-                iq3_sb_regs r[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) iq3_load(r[j], row + (sb0 + j) * 98, lane);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) iq3_finish(r[j], dst + (sb0 + j) * 256, lane, s_grid, s_signs);
-            }
-        } else {
-            for (int sb = 0; sb < nsb; ++sb) {
-                iq3_sb_regs r;
-                iq3_load(r, row + sb * 98, lane);
-                iq3_finish(r, dst + sb * 256, lane, s_grid, s_signs);
-            }
+        for (int sb = 0; sb < nsb; ++sb) {
+            iq3_sb_regs r;
+            iq3_load(r, row + sb * 98, lane);
+            iq3_finish(r, dst + sb * 256, lane, s_grid);
         }
+    }
+}
+
+// Rows of 8 super-blocks (2048 columns) are 784 bytes, a multiple of 16, and start 16-byte aligned: the whole row is
+// fetched with two 128-bit loads per lane ONE ROW AHEAD of its decode (held in eight registers), then parked in the
+// warp's own shared-memory slot, from which every lane picks its pieces.  With per-lane 1- and 2-byte global loads
+// issued just before their use the kernel sat on global-load latency (ncu: 20 long-scoreboard stall cycles per issue,
+// 45 % issue rate at 85 % occupancy).
+constexpr int kIq3RowBytes = 8 * 98;
+__device__ __forceinline__ void iq3_fetch_row(const uint8_t * __restrict__ table, int32_t id, int lane, uint4 & a, uint4 & b) {
+    const uint4 * p = reinterpret_cast<const uint4 *>(table + int64_t(id) * kIq3RowBytes);
+    a = __ldg(p + lane);
+    b = lane < kIq3RowBytes / 16 - 32 ? __ldg(p + 32 + lane) : make_uint4(0u, 0u, 0u, 0u);
+}
+template <int SB>
+__device__ __forceinline__ void iq3_finish_staged(const uint8_t * buf, float * dst, int lane, const uint32_t * s_grid) {
+    const uint8_t * blk = buf + 98 * SB;
+    const int o_aux = 66 + 4 * (lane >> 3);
+    const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(blk));
+    const uint32_t q0 = blk[2 + lane], q1 = blk[34 + lane];
+    uint32_t a0, a1;
+    if constexpr ((SB & 1) != 0) {  // 98 SB + 66 is a multiple of 4: the scale/sign words are aligned
+        a0 = *reinterpret_cast<const uint32_t *>(blk + o_aux);
+        a1 = *reinterpret_cast<const uint32_t *>(blk + o_aux + 16);
+    } else {
+        const uint16_t * h = reinterpret_cast<const uint16_t *>(blk + o_aux);
+        a0 = uint32_t(h[0]) | (uint32_t(h[1]) << 16);
+        a1 = uint32_t(h[8]) | (uint32_t(h[9]) << 16);
+    }
+    float4 * o = reinterpret_cast<float4 *>(dst + 256 * SB) + lane;
+    st_stream(o, iq3_decode(d, q0, a0, lane, s_grid));
+    st_stream(o + 32, iq3_decode(d, q1, a1, lane, s_grid));  // n = lane + 32: same parity bits
+}
+__global__ void __launch_bounds__(kWarpsPerCta * 32, kStagedCtasPerSm)
+    get_rows_iq3_xxs_staged_kernel(const uint8_t * __restrict__ table, int64_t n_vocab, const int32_t * __restrict__ ids,
+                                   float * __restrict__ out, uint32_t * err, int64_t rows) {
+    __shared__ uint32_t s_grid[256];
+    __shared__ __align__(16) uint8_t s_rows[kWarpsPerCta][kIq3RowBytes];
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+        const uint32_t c = c_iq3xxs_grid_packed[i];
+        uint32_t w = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t lvl = (c >> (3 * j)) & 7u;
+            w |= (lvl == 7u ? 62u : 4u + 8u * lvl) << (8 * j);
+        }
+        s_grid[i] = w;
+    }
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = int64_t(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
+    const int64_t n_warps = int64_t(gridDim.x) * kWarpsPerCta;
+    uint8_t * buf = s_rows[threadIdx.x >> 5];
+    auto valid = [&](int32_t id) { return id >= 0 && id < n_vocab; };
+
+    // ids run two rows ahead of the decode, row bytes one
+    int32_t id = warp < rows ? __ldg(ids + warp) : -1;
+    int32_t id_next = warp + n_warps < rows ? __ldg(ids + warp + n_warps) : -1;
+    uint4 a = make_uint4(0u, 0u, 0u, 0u), b = a;
+    if (valid(id)) iq3_fetch_row(table, id, lane, a, b);
+    for (int64_t t = warp; t < rows; t += n_warps) {
+        const bool ok = valid(id);
+        if (ok) {
+            reinterpret_cast<uint4 *>(buf)[lane] = a;
+            if (lane < kIq3RowBytes / 16 - 32) reinterpret_cast<uint4 *>(buf)[32 + lane] = b;
+        } else if (lane == 0 && err != nullptr) {
+            atomicOr(err, FNB_ERR_TOKEN);
+        }
+        __syncwarp();
+        const int64_t t2 = t + 2 * n_warps;
+        const int32_t id_after = t2 < rows ? __ldg(ids + t2) : -1;
+        if (valid(id_next)) iq3_fetch_row(table, id_next, lane, a, b);  // (an id past the end is -1: nothing fetched)
+        if (ok) {
+            float * dst = out + t * 2048;
+            iq3_finish_staged<0>(buf, dst, lane, s_grid);
+            iq3_finish_staged<1>(buf, dst, lane, s_grid);
+            iq3_finish_staged<2>(buf, dst, lane, s_grid);
+            iq3_finish_staged<3>(buf, dst, lane, s_grid);
+            iq3_finish_staged<4>(buf, dst, lane, s_grid);
+            iq3_finish_staged<5>(buf, dst, lane, s_grid);
+            iq3_finish_staged<6>(buf, dst, lane, s_grid);
+            iq3_finish_staged<7>(buf, dst, lane, s_grid);
+        }
+        __syncwarp();  // every lane is done with the slot before the next row overwrites it
+        id = id_next;
+        id_next = id_after;
     }
 }
 
@@ -272,8 +418,13 @@ extern "C" int32_t fnb_get_rows_q4_k(const void * table, int64_t n_vocab, const 
                                      uint32_t * err, int64_t rows, int32_t cols, void * stream) {
     using namespace fnb;
     if (!common_ok(table, n_vocab, ids, out, err, rows, cols, 256, 144, 16)) return FNB_REJECTED;
-    get_rows_q4_k_kernel<8><<<persistent_grid(rows, 8), kWarpsPerCta * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint8_t *>(table), n_vocab, ids, out, err, rows, cols);
+    const cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const uint8_t * tb = static_cast<const uint8_t *>(table);
+    if (cols == 2048) {
+        get_rows_q4_k_staged_kernel<<<persistent_grid(rows, kStagedGridPerSm), kWarpsPerCta * 32, 0, s>>>(tb, n_vocab, ids, out, err, rows);
+    } else {
+        get_rows_q4_k_kernel<8><<<persistent_grid(rows, 8), kWarpsPerCta * 32, 0, s>>>(tb, n_vocab, ids, out, err, rows, cols);
+    }
     return launch_status();
 }
 
@@ -284,9 +435,9 @@ extern "C" int32_t fnb_get_rows_iq3_xxs(const void * table, int64_t n_vocab, con
     const cudaStream_t s = static_cast<cudaStream_t>(stream);
     const uint8_t * tb = static_cast<const uint8_t *>(table);
     if (cols == 2048) {
-        get_rows_iq3_xxs_kernel<8><<<persistent_grid(rows, 8), kWarpsPerCta * 32, 0, s>>>(tb, n_vocab, ids, out, err, rows, cols);
+        get_rows_iq3_xxs_staged_kernel<<<persistent_grid(rows, kStagedGridPerSm), kWarpsPerCta * 32, 0, s>>>(tb, n_vocab, ids, out, err, rows);
     } else {
-        get_rows_iq3_xxs_kernel<0><<<persistent_grid(rows, 8), kWarpsPerCta * 32, 0, s>>>(tb, n_vocab, ids, out, err, rows, cols);
+        get_rows_iq3_xxs_kernel<<<persistent_grid(rows, 8), kWarpsPerCta * 32, 0, s>>>(tb, n_vocab, ids, out, err, rows, cols);
     }
     return launch_status();
 }

@@ -280,6 +280,30 @@ def test_get_rows_bit_exact_and_bad_ids(dev, oracle, fmt, cols, vocab, rows):
     assert np.array_equal(bits(out.numpy()), bits(want))
 
 
+@pytest.mark.parametrize("fmt", ["q4_k", "iq3_xxs"])
+def test_get_rows_many_rows_per_warp_with_bad_ids(dev, oracle, fmt):
+    """More rows than the grid has warps (each warp decodes several rows, fetching one ahead), bad ids sprinkled in:
+    every good row equals the oracle's decode of its table row, every bad row stays untouched."""
+    vocab, cols, rows = 1024, 2048, 150001
+    g = synth.rng(11)
+    table = {"q4_k": synth.q4_k_table, "iq3_xxs": synth.iq3_xxs_table}[fmt](g, vocab, cols)
+    deq = oracle.dequantize_q4_k if fmt == "q4_k" else oracle.dequantize_iq3_xxs
+    decoded = to_dev(deq(table).reshape(vocab, cols).view(np.int32), dev)
+    ids = g.integers(0, vocab, rows).astype(np.int32)
+    bad = np.arange(7, rows, 1001)
+    ids[bad[::2]], ids[bad[1::2]] = -3, vocab + 5
+    ids[-1] = vocab                                             # the last row of the last warp too
+    ids_d = to_dev(ids, dev)
+    out = torch.full((rows, cols), 0x5a5a5a5a, dtype=torch.int32, device=dev)
+    err = ops.new_err(dev)
+    ops.get_rows(fmt, to_dev(table, dev), ids_d, cols, out=out.view(torch.float32), err=err)
+    torch.cuda.synchronize()
+    assert int(err.item()) == oracle.ERR_TOKEN
+    ok = (ids_d >= 0) & (ids_d < vocab)
+    assert torch.equal(out[ok], decoded[ids_d[ok].long()])
+    assert bool((out[~ok] == 0x5a5a5a5a).all())
+
+
 def test_get_rows_matches_reference_golden_decode(dev):
     """Blocks generated by the reference's fn::quant::synth_blocks and decoded by its dequantize_row_* (golden)."""
     gold = np.load(os.path.join(GOLD, "decode.npz"))
