@@ -42,26 +42,33 @@ __device__ __forceinline__ uint32_t ldg_u16(const uint8_t * p) { return __ldg(re
 __device__ __forceinline__ uint32_t ldg_u8(const uint8_t * p) { return __ldg(p); }
 
 // index n of an IQ3_S super-block -> its four values (ggml/src/ggml-quants.c:2605-2644 restated per index)
+// magnitude byte J of a codebook word as a float: 0x4B0000bb is 2^23 + bb exactly
+template <int J>
+__device__ __forceinline__ float grid_byte_f32(uint32_t g) {
+    return __fadd_rn(__uint_as_float(__byte_perm(g, 0x4B000000u, 0x7540u + J)), -8388608.0f);
+}
 __device__ __forceinline__ float4 iq3s_decode(float d, uint32_t q, uint32_t qh, uint32_t sg, uint32_t sc, int n,
-                                              const float4 * s_grid) {
+                                              const uint32_t * s_grid) {
     const int m = n & 7, ib = n >> 3;
     const uint32_t nib = (ib & 1) ? sc >> 4 : sc & 0x0fu;
     const float db = __fmul_rn(d, float(1 + 2 * int(nib)));
     const float nb = -db;
-    const float4 g = s_grid[q | (((qh >> m) & 1u) << 8)];
+    const uint32_t g = s_grid[q | (((qh >> m) & 1u) << 8)];
     const uint32_t s4 = sg >> (4 * (n & 1));
-    return make_float4(__fmul_rn((s4 & 1u) ? nb : db, g.x), __fmul_rn((s4 & 2u) ? nb : db, g.y),
-                       __fmul_rn((s4 & 4u) ? nb : db, g.z), __fmul_rn((s4 & 8u) ? nb : db, g.w));
+    return make_float4(__fmul_rn((s4 & 1u) ? nb : db, grid_byte_f32<0>(g)), __fmul_rn((s4 & 2u) ? nb : db, grid_byte_f32<1>(g)),
+                       __fmul_rn((s4 & 4u) ? nb : db, grid_byte_f32<2>(g)), __fmul_rn((s4 & 8u) ? nb : db, grid_byte_f32<3>(g)));
 }
 
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
     embed_iq3s_kernel(const uint8_t * __restrict__ table, int64_t n_vocab, const int32_t * __restrict__ tok, int64_t rows,
                       const row_sink sink, uint32_t * err) {
-    __shared__ float4 s_grid[512];
+    // four magnitude bytes per entry: a random 32-bit lookup collides on a bank about three deep, where a float4
+    // entry (no conversion) cost about eleven shared-memory wavefronts
+    __shared__ uint32_t s_grid[512];
     for (int i = threadIdx.x; i < 512; i += blockDim.x) {
         const uint32_t c = c_iq3s_grid_packed[i];
-        s_grid[i] = make_float4(float(2 * (c & 7u) + 1), float(2 * ((c >> 3) & 7u) + 1), float(2 * ((c >> 6) & 7u) + 1),
-                                float(2 * ((c >> 9) & 7u) + 1));
+        s_grid[i] = (2 * (c & 7u) + 1) | ((2 * ((c >> 3) & 7u) + 1) << 8) | ((2 * ((c >> 6) & 7u) + 1) << 16) |
+                    ((2 * ((c >> 9) & 7u) + 1) << 24);
     }
     __syncthreads();
     const int lane = threadIdx.x & 31;
@@ -164,7 +171,8 @@ extern "C" int32_t fnb_embed_rows(const fnb_embed_args * a, void * stream) {
     if (!ok_ptr(a->table, 2) || !ok_ptr(a->tok, 4) || !ok_opt(a->err, 4) || a->n_vocab < 1 || a->n_vocab > INT32_MAX) {
         return FNB_REJECTED;
     }
-    const int grid = grid_for((a->rows + kWarpsPerCta - 1) / kWarpsPerCta, 8);
+    // many more CTAs than are resident: the CTA dispatcher evens out SMs that drain their rows at different rates
+    const int grid = grid_for((a->rows + kWarpsPerCta - 1) / kWarpsPerCta, 32);
     const cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint8_t * tb = static_cast<const uint8_t *>(a->table);
     if (a->fmt == FNB_TABLE_IQ3_S) {

@@ -4,9 +4,9 @@
 // cosf - evaluated with the same IEEE operations in the same order.  Every double operation is written with
 // an explicit round-to-nearest intrinsic so no multiply-add is ever contracted.
 //
-// Cost: expf is 12 FP64 operations and two conversions per value.  At one value per 8 bytes of HBM traffic
-// this stays below the FP64 pipe's rate on B200, so SwiGLU remains memory-bound; sin/cos are needed once per
-// token and rotary pair (32 per token), which is noise.
+// Cost: expf is 12 FP64 operations and two conversions per value as defined (expf_steps); the SwiGLU fast path uses
+// expf_core, 8 FP64 operations, which rounds to the same float for every input (see there).  sin/cos are needed
+// once per token and rotary pair (32 per token), which is noise.
 #pragma once
 
 #include "common.cuh"

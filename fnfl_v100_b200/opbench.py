@@ -17,7 +17,7 @@ from . import ops, synth
 from .chain import ChainConfig
 
 OPS = ("get_rows_q4_k", "get_rows_iq3_xxs", "rms_norm", "rms_norm_heads", "rope_kv", "swiglu_q8_1", "swiglu_act",
-       "rope_kv8", "quantize_q8_1", "rms_norm_q8_1")
+       "rope_kv8", "quantize_q8_1", "rms_norm_q8_1", "embed_iq3_s")
 
 
 def hbm_peak() -> float:
@@ -40,6 +40,17 @@ def make_case(op: str, T: int, dev, gen, c: ChainConfig):
         err = ops.new_err(dev)
         return (lambda: ops.get_rows(fmt, table, ids, c.hidden, out=out, err=err),
                 T * (ops.table_row_bytes(fmt, c.hidden) + 4 + c.hidden * 4))
+    if op == "embed_iq3_s":
+        # the reference's two-card layout (fn/kernels/embed/embed.h:70-87): 1280 own features of 2560, four streams
+        n_own, n_full, n_streams, vocab = 1280, 2560, 4, 248320
+        table = synth.torch_table("iq3_s", gen, vocab, n_own, dev)
+        tok = torch.randint(0, vocab, (T,), dtype=torch.int32, device=dev, generator=gen)
+        own = torch.empty((T, n_own), dtype=torch.float32, device=dev)
+        full = torch.empty((T, n_full), dtype=torch.float32, device=dev)
+        streams = torch.empty((T, n_streams, n_full), dtype=torch.float32, device=dev)
+        err = ops.new_err(dev)
+        return (lambda: ops.embed_rows("iq3_s", table, tok, n_own, own=own, full=full, streams=streams, col0=0, err=err),
+                T * (n_own // 256 * 110 + 4 + (2 + n_streams) * n_own * 4))
     if op == "rms_norm":
         x, w = N(gen, (T, c.hidden), 1.0, dev), 1 + 0.1 * N(gen, (c.hidden,), 1.0, dev)
         y = torch.empty_like(x)

@@ -77,9 +77,9 @@ def torch_normal(gen, shape, scale: float, device):
 
 
 def torch_table(fmt: str, gen, n_rows: int, cols: int, device, d_lo: float = 1e-3, d_hi: float = 1e-2):
-    """Device form of q4_k_table / iq3_xxs_table (same distributions, torch's generator)."""
+    """Device form of q4_k_table / iq3_xxs_table / an IQ3_S table (same distributions, torch's generator)."""
     import torch
-    bv, bb, nd = {"q4_k": (256, 144, 2), "iq3_xxs": (256, 98, 1)}[fmt]
+    bv, bb, nd = {"q4_k": (256, 144, 2), "iq3_xxs": (256, 98, 1), "iq3_s": (256, 110, 1)}[fmt]
     nsb = cols // bv
     t = torch.randint(0, 256, (n_rows, nsb, bb), dtype=torch.uint8, device=device, generator=gen)
     d = torch.empty((n_rows, nsb, nd), dtype=torch.float32, device=device).uniform_(d_lo, d_hi, generator=gen)
