@@ -24,8 +24,8 @@ __host__ __device__ constexpr int block_bytes() {
     return F == out_fmt::q8_1 ? 36 : F == out_fmt::q8_0 ? 34 : 32;
 }
 
-constexpr int kGroups = 3;      // 12 consumer warps + the producer = 416 threads: 128 registers each, a row of 2048 fits
-constexpr int kGroupWarps = 4;  // rows per tile
+constexpr int kGroups = 5;      // 15 consumer warps + the producer = 16 warps, four per scheduler: 128 registers each, a row of 2048 fits
+constexpr int kGroupWarps = 3;  // rows per tile
 constexpr int kConsumerWarps = kGroups * kGroupWarps;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr size_t kSmemBudget = 220 * 1024;
