@@ -53,7 +53,9 @@ __device__ __forceinline__ float expf_steps(float x) {
 // the same for EVERY float |x| < 88: checked by enumerating all 2 x 0x42b00000 inputs, on the CPU
 // (tests/cpp/expf_fma_exhaustive.c) and on the device (fnb_selftest_expf).  Fusing the reduction too
 // (r = fma(x, N/ln2, -k)) is NOT equivalent: two inputs round differently.
-__device__ __forceinline__ float expf_core(float x) {
+// NEG: returns -e^x (the sign rides on the last product: rounding is symmetric, so it is exactly the negated result)
+template <bool NEG>
+__device__ __forceinline__ float expf_core_signed(float x) {
     const double z = __dmul_rn(c_exp_k[0], double(x));
     double kd = __dadd_rn(z, c_exp_k[1]);
     const unsigned long long ki = (unsigned long long) __double_as_longlong(kd);
@@ -63,8 +65,9 @@ __device__ __forceinline__ float expf_core(float x) {
     const double s = __longlong_as_double((long long) t);
     double q = __fma_rn(c_exp_k[2], r, c_exp_k[3]);
     q = __fma_rn(q, r, c_exp_k[4]);
-    return __double2float_rn(__dmul_rn(__fma_rn(q, r, 1.0), s));
+    return __double2float_rn(__dmul_rn(__fma_rn(q, r, 1.0), NEG ? -s : s));
 }
+__device__ __forceinline__ float expf_core(float x) { return expf_core_signed<false>(x); }
 
 static __device__ __noinline__ float expf_special(float x) {
     const uint32_t bits = __float_as_uint(x);

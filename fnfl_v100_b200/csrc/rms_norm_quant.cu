@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 uint32_t * o = reinterpret_cast<uint32_t *>(my_out) + 9 * b;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    const uint32_t wd = pack4(rule.code(v[k][j].x), rule.code(v[k][j].y), rule.code(v[k][j].z), rule.code(v[k][j].w));
+                    const uint32_t wd = rule.code4(v[k][j]);
                     qsum += sum4_i8(wd);
                     o[1 + ((j + lane) & 7)] = wd;
                 }
@@ -170,7 +170,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 uint16_t * o = reinterpret_cast<uint16_t *>(my_out) + 17 * b;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    const uint32_t wd = pack4(rule.code(v[k][j].x), rule.code(v[k][j].y), rule.code(v[k][j].z), rule.code(v[k][j].w));
+                    const uint32_t wd = rule.code4(v[k][j]);
                     const int c = (j + lane) & 7;
                     o[1 + 2 * c] = uint16_t(wd);
                     o[2 + 2 * c] = uint16_t(wd >> 16);
@@ -181,7 +181,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 uint32_t * o = reinterpret_cast<uint32_t *>(my_out) + 8 * b;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    const uint32_t wd = pack4(rule.code(v[k][j].x), rule.code(v[k][j].y), rule.code(v[k][j].z), rule.code(v[k][j].w));
+                    const uint32_t wd = rule.code4(v[k][j]);
                     qsum += sum4_i8(wd);
                     o[(j + lane) & 7] = wd;
                 }

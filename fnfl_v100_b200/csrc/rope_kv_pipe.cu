@@ -286,7 +286,7 @@ __global__ void __launch_bounds__(kThreads, 1) rope_kv_pipe_kernel(const rope_ke
                 for (int j = 0; j < NJ; ++j) {
                     ggml_q8_rule rule = own;
                     rule.id = __shfl_sync(kFull, own.id, (lane & ~7) | j);
-                    const uint32_t wrd = pack4(rule.code(x[j].x), rule.code(x[j].y), rule.code(x[j].z), rule.code(x[j].w));
+                    const uint32_t wrd = rule.code4(x[j]);
                     s16[17 * j + 1 + 2 * sub] = uint16_t(wrd);
                     s16[17 * j + 2 + 2 * sub] = uint16_t(wrd >> 16);
                 }
@@ -403,6 +403,7 @@ __global__ void kv8_selftest_kernel(uint64_t n, uint64_t seed, unsigned long lon
         const int fast = rule.code(x);
         const int ref = max(-127, min(127, __float2int_rn(__fdiv_rn(x, s))));
         bad += fast != ref;
+        bad += rule.code4(make_float4(x, -x, x, -x)) != pack4(ref, -ref, ref, -ref);  // the form the kernel calls
     }
     if (bad != 0) atomicAdd(mismatches, bad);
 }
