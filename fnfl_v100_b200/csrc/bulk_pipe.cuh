@@ -13,7 +13,10 @@ namespace fnb {
 // A failed poll suspends the thread for up to kPollNs, so the hint is also the granularity with which a waiter
 // notices completion: 2 us made a latency-sensitive pipeline (consumers faster than memory) three times slower.
 constexpr uint32_t kSpinLimit = 1u << 24;  // polls of at most kPollNs each: about a second in the worst case
-constexpr uint32_t kPollNs = 64;
+#ifndef FNB_POLL_NS
+#define FNB_POLL_NS 64
+#endif
+constexpr uint32_t kPollNs = FNB_POLL_NS;
 
 __device__ __forceinline__ uint32_t smem_u32(const void * p) { return uint32_t(__cvta_generic_to_shared(p)); }
 
