@@ -105,6 +105,9 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--sets", type=int, default=1, help="distinct input sets rotated between launches (cold when > 1)")
+    ap.add_argument("--graph", type=int, default=0, metavar="N",
+                    help="time N launches replayed from one CUDA graph (device time without the host's launch cost; "
+                         "for launches of a few microseconds)")
     args = ap.parse_args()
     dev = torch.device("cuda:0")
     peak = hbm_peak()
@@ -117,15 +120,33 @@ def main() -> None:
             cases[i % args.sets][0]()
         torch.cuda.synchronize()
         evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.iters)]
-        for i, (a, b) in enumerate(evs):
-            a.record()
-            cases[i % args.sets][0]()
-            b.record()
-        torch.cuda.synchronize()
-        ms = sorted(a.elapsed_time(b) for a, b in evs)
+        if args.graph > 0:
+            side = torch.cuda.Stream(dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, stream=side):
+                    for i in range(args.graph):
+                        cases[i % args.sets][0]()
+            torch.cuda.current_stream(dev).wait_stream(side)
+            graph.replay()
+            torch.cuda.synchronize()
+            for a, b in evs:
+                a.record()
+                graph.replay()
+                b.record()
+            torch.cuda.synchronize()
+            ms = sorted(a.elapsed_time(b) / args.graph for a, b in evs)
+        else:
+            for i, (a, b) in enumerate(evs):
+                a.record()
+                cases[i % args.sets][0]()
+                b.record()
+            torch.cuda.synchronize()
+            ms = sorted(a.elapsed_time(b) for a, b in evs)
         med, p90 = ms[len(ms) // 2], ms[min(len(ms) - 1, int(len(ms) * 0.9))]
         gbs = nbytes / (med * 1e-3) / 1e9
-        print(json.dumps({"op": op, "tokens": args.tokens, "sets": args.sets, "median_ms": round(med, 4),
+        print(json.dumps({"op": op, "tokens": args.tokens, "sets": args.sets, "graph": args.graph, "median_ms": round(med, 4),
                           "p90_ms": round(p90, 4), "min_ms": round(ms[0], 4), "bytes": nbytes, "gbs": round(gbs, 1),
                           "frac_of_hbm_peak": round(gbs / peak, 4), "tokens_per_s": round(args.tokens / (med * 1e-3))}))
         del cases
