@@ -38,6 +38,13 @@ class EmbedArgs(C.Structure):
 TABLE_Q4_K, TABLE_IQ3_XXS, TABLE_Q8_0, TABLE_IQ3_S = 0, 1, 2, 3
 
 
+class KvReadArgs(C.Structure):
+    """fnb_kv_read_args"""
+    _fields_ = [("cache", C.c_void_p), ("scale", C.c_void_p), ("cells", C.c_void_p), ("out", C.c_void_p),
+                ("err", C.c_void_p), ("rows", C.c_int64), ("cache_slots", C.c_int64), ("cell0", C.c_int64),
+                ("n_kv_heads", C.c_int32), ("head_dim", C.c_int32)]
+
+
 class GgufTensor(C.Structure):
     """fnb_gguf_tensor"""
     _fields_ = [("ne", C.c_int64 * 4), ("offset", C.c_int64), ("row_bytes", C.c_int64), ("n_rows", C.c_int64),
@@ -74,6 +81,7 @@ SIGNATURES = {
     "fnb_embed_rows": (_I32, [C.POINTER(EmbedArgs), _P]),
     "fnb_embed_join": (_I32, [C.POINTER(EmbedArgs), _P, _I32, _P]),
     "fnb_embed_supply": (_I32, [C.POINTER(EmbedArgs), _P, _I64, _I64, _P]),
+    "fnb_kv_read_f32": (_I32, [C.POINTER(KvReadArgs), _P]),
     "fnb_check_tokens": (_I64, [_P, _I64, _I64]),
     "fnb_gguf_open": (_P, [C.c_char_p]),
     "fnb_gguf_close": (None, [_P]),

@@ -17,7 +17,7 @@ from . import ops, synth
 from .chain import ChainConfig
 
 OPS = ("get_rows_q4_k", "get_rows_iq3_xxs", "rms_norm", "rms_norm_heads", "rope_kv", "swiglu_q8_1", "swiglu_act",
-       "rope_kv8", "quantize_q8_1", "rms_norm_q8_1", "embed_iq3_s")
+       "rope_kv8", "quantize_q8_1", "rms_norm_q8_1", "embed_iq3_s", "kv_read_q8_0", "kv_read_kv8")
 
 
 def hbm_peak() -> float:
@@ -51,6 +51,18 @@ def make_case(op: str, T: int, dev, gen, c: ChainConfig):
         err = ops.new_err(dev)
         return (lambda: ops.embed_rows("iq3_s", table, tok, n_own, own=own, full=full, streams=streams, col0=0, err=err),
                 T * (n_own // 256 * 110 + 4 + (2 + n_streams) * n_own * 4))
+    if op.startswith("kv_read"):
+        # T consecutive cells of a cache the append has filled (random bytes stand in: every byte pattern is a valid cell)
+        if op == "kv_read_q8_0":
+            cache = torch.randint(0, 256, (T, c.n_kv_heads, c.head_dim // 32 * 34), dtype=torch.uint8, device=dev, generator=gen)
+            cache.view(torch.float16).reshape(T, c.n_kv_heads, c.head_dim // 32, 17)[..., 0] = 0.01
+            scale, cell = None, c.head_dim // 32 * 34
+        else:
+            cache = torch.randint(-127, 128, (T, c.n_kv_heads, c.head_dim), dtype=torch.int8, device=dev, generator=gen)
+            scale = torch.full((T, c.n_kv_heads, c.head_dim // 64), 0.01, dtype=torch.float16, device=dev).view(torch.int16)
+            cell = c.head_dim + c.head_dim // 64 * 2
+        out = torch.empty((T, c.n_kv_heads, c.head_dim), dtype=torch.float32, device=dev)
+        return (lambda: ops.kv_read_f32(cache, scale=scale, out=out)), T * c.n_kv_heads * (cell + c.head_dim * 4)
     if op == "rms_norm":
         x, w = N(gen, (T, c.hidden), 1.0, dev), 1 + 0.1 * N(gen, (c.hidden,), 1.0, dev)
         y = torch.empty_like(x)

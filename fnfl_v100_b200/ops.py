@@ -234,6 +234,31 @@ def table_row_bytes(fmt: str, cols: int) -> int:
     return cols // values * nbytes
 
 
+def kv_read_f32(cache: torch.Tensor, *, scale: torch.Tensor | None = None, cells: torch.Tensor | None = None,
+                cell0: int = 0, rows: int | None = None, out: torch.Tensor | None = None,
+                err: torch.Tensor | None = None) -> torch.Tensor:
+    """Cache rows widened to F32 exactly as a consumer reads them: out [rows][n_kv][head_dim].  `cache` is a Q8_0 plane
+    from new_kv_cache (scale None) or the KV8 codes with `scale` their FP16 plane; rows are cells[t], or cell0 + t."""
+    kv8 = scale is not None
+    _dev(cache, torch.int8 if kv8 else torch.uint8, "cache")
+    slots, n_kv = cache.shape[0], cache.shape[1]
+    hd = cache.shape[2] if kv8 else cache.shape[2] // Q8_0_BLOCK * 32
+    if kv8:
+        _dev(scale, torch.int16, "scale")
+    if cells is not None:
+        _dev(cells, torch.int32, "cells")
+        rows = cells.numel()
+    elif rows is None:
+        rows = slots - cell0
+    if out is None:
+        out = torch.empty((rows, n_kv, hd), dtype=torch.float32, device=cache.device)
+    _dev(out, torch.float32, "out")
+    a = _lib.KvReadArgs(_ptr(cache).value, _ptr(scale).value, _ptr(cells).value, _ptr(out).value, _ptr(err).value,
+                        rows, slots, cell0, n_kv, hd)
+    _check(_lib.lib().fnb_kv_read_f32(C.byref(a), _stream()), "kv_read_f32")
+    return out
+
+
 def get_rows(fmt: str, table: torch.Tensor, ids: torch.Tensor, cols: int, out: torch.Tensor | None = None,
              err: torch.Tensor | None = None) -> torch.Tensor:
     """out[t] = dequantised row ids[t] of `table` (uint8 [n_vocab][row_bytes]); replaces fn::embed::embed_rows."""

@@ -256,6 +256,31 @@ int32_t fnb_gguf_find(const fnb_gguf * g, const char * name, fnb_gguf_tensor * o
 int32_t fnb_gguf_read_rows(fnb_gguf * g, const fnb_gguf_tensor * t, int64_t row0, int64_t n_rows, void * dst_host);
 
 /*
+ * Reads cache rows back as F32, exactly as a consumer of the cache widens them: out[t][h][:] = the head_dim values of
+ * cell cells[t] (or cell0 + t when cells is null), kv head h.  Q8_0 cells (scale null): value = fp16 d x code, ggml's
+ * dequantize_row_q8_0 (ggml/src/ggml-quants.c:551-565).  KV8 (scale = the FP16 scale plane, cache = the int8 codes):
+ * value = float(code) x f32(scale of its group of 64), exact in F32: fn::qsa::kv8::decode4
+ * (fn/kernels/qsa/kv_q8.cuh:61-67), CPU fn::quant::kv_q8_value (fn/quant/kv_q8_ref.h).  The reference has no
+ * stand-alone launcher for this (its attention widens cells in place); it is the read side of the append above, for
+ * consumers that want F32 rows and for checking a cache.  A cell outside [0, cache_slots) sets FNB_ERR_SLOT and
+ * leaves its row untouched.  head_dim in {64, 128, 256}; cache, out 16-byte aligned.
+ */
+typedef struct fnb_kv_read_args {
+    const void * cache;
+    const uint16_t * scale;
+    const int32_t * cells;
+    float * out;
+    uint32_t * err;
+    int64_t rows;
+    int64_t cache_slots;
+    int64_t cell0;
+    int32_t n_kv_heads;
+    int32_t head_dim;
+} fnb_kv_read_args;
+
+int32_t fnb_kv_read_f32(const fnb_kv_read_args * args, void * stream);
+
+/*
  * Host-side check before upload: 0 when every id is in [0, n_vocab), else 1 + the index of the first bad id.
  * Replaces fn::embed::check_tokens (fn/kernels/embed/embed.h:56).
  */

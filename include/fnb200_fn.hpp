@@ -112,6 +112,17 @@ inline bool qsp_kv(const qsp_kv_args & a, void * stream) {
            FNB_OK;
 }
 
+
+// cache rows widened to F32 exactly as attention widens them (fn::qsa::kv8::decode4 for KV8, ggml's Q8_0 decode else);
+// scale null: Q8_0 cells.  cells null: rows cell0 .. cell0 + rows - 1.
+inline bool kv_read(const void * cache, const uint16_t * scale, const int32_t * cells, int64_t cell0, int64_t rows,
+                    int64_t max_cells, int32_t n_kv_heads, int32_t head_dim, float * out, uint32_t * err, void * stream) {
+    fnb_kv_read_args a{};
+    a.cache = cache, a.scale = scale, a.cells = cells, a.out = out, a.err = err;
+    a.rows = rows, a.cache_slots = max_cells, a.cell0 = cell0, a.n_kv_heads = n_kv_heads, a.head_dim = head_dim;
+    return fnb_kv_read_f32(&a, stream) == FNB_OK;
+}
+
 }  // namespace qsa
 
 namespace embed {  // token-embedding get_rows: fn::embed::embed_rows / check_tokens

@@ -213,6 +213,14 @@ def kv8_quantize(x: np.ndarray):
     return codes, scales
 
 
+def kv8_dequantize(codes: np.ndarray, scales: np.ndarray) -> np.ndarray:
+    """The value each KV8 code stands for: float(code) * f32(FP16 scale of its group of 64), one F32 product, exact
+    (fn::quant::kv_q8_value, fn/quant/kv_q8_ref.cpp:95-97; device form fn/kernels/qsa/kv_q8.cuh:61-67)."""
+    c = np.ascontiguousarray(codes, np.int8).reshape(-1, 64).astype(np.float32)
+    s = np.ascontiguousarray(scales, np.uint16).reshape(-1, 1).view(np.float16).astype(np.float32)
+    return (c * s).reshape(-1)
+
+
 def rope_kv_append(q, k, v, pos, *, n_rot: int, theta_scale: float, k_cache: np.ndarray, v_cache: np.ndarray,
                    cache_slots: int, slots=None, q_norm_w=None, k_norm_w=None, eps: float = 1e-6,
                    want_k_f32: bool = False, q_out: np.ndarray | None = None):

@@ -40,6 +40,11 @@ void ref_kv_q8_quantize(const float * x, int32_t n, int8_t * codes, uint16_t * s
     fn::quant::kv_q8_quantize(x, n, codes, scales);
 }
 
+// the value a KV8 code stands for under its group's scale bits (fn/quant/kv_q8_ref.cpp:95-97), n values, group of 64
+void ref_kv_q8_values(const int8_t * codes, const uint16_t * scales, int64_t n, float * out) {
+    for (int64_t i = 0; i < n; ++i) out[i] = fn::quant::kv_q8_value(codes[i], scales[i / fn::quant::kv_q8_group]);
+}
+
 // the KV8 stress rows (fn/quant/kv_q8_ref.cpp:99-169): returns the value count; copies up to cap values
 int64_t ref_kv_q8_stress_rows(uint64_t seed, int32_t random_rows, float * out, int64_t cap) {
     const std::vector<float> v = fn::quant::kv_q8_stress_rows(seed, random_rows);

@@ -82,8 +82,11 @@ def main() -> None:
     kv_codes = np.empty(x.size, np.int8)
     kv_scales = np.empty(x.size // 64, np.uint16)
     r.ref_kv_q8_quantize(O._p(x), C.c_int32(x.size), O._p(kv_codes), O._p(kv_scales))
+    kv_values = np.empty(x.size, np.float32)
+    r.ref_kv_q8_values(O._p(kv_codes), O._p(kv_scales), C.c_int64(x.size), O._p(kv_values))
     np.savez_compressed(os.path.join(HERE, "quant.npz"), x=x, q8_0=q80.reshape(n, 34), q8_1=q81.reshape(n, 36),
-                        act_codes=codes, act_scales=scales, kv8_codes=kv_codes.reshape(-1, 64), kv8_scales=kv_scales)
+                        act_codes=codes, act_scales=scales, kv8_codes=kv_codes.reshape(-1, 64), kv8_scales=kv_scales,
+                        kv8_values=kv_values.reshape(-1, 64))
 
     dec = {}
     nblk = 96

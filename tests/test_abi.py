@@ -73,6 +73,13 @@ def test_rejections_enqueue_nothing(lib):
     assert lib.fnb_swiglu_act(A16, A16, A16, None, None, 8, 512, None) == R
     assert lib.fnb_quantize_q8_1(A16, A16, -3, 512, None) == R
     assert lib.fnb_quantize_q8_0(None, A16, 3, 512, None) == R
+    # cache read-back: head_dim outside {64, 128, 256}, a span past the cache, missing pointers
+    ka = _lib.KvReadArgs(A16, None, None, A16, None, 8, 64, 0, 2, 256)
+    for field, bad in (("head_dim", 96), ("cell0", 60), ("rows", 0), ("out", None), ("cache", ODD), ("n_kv_heads", 0)):
+        kb = _lib.KvReadArgs.from_buffer_copy(ka)
+        setattr(kb, field, bad)
+        assert lib.fnb_kv_read_f32(C.byref(kb), None) == R, field
+    assert lib.fnb_kv_read_f32(None, None) == R
     assert lib.fnb_act_quantize(A16, A16, ODD + 2, 3, 512, None) == R       # scales need 8-byte alignment
     # get_rows
     assert lib.fnb_get_rows_q4_k(A16, 100, A16, A16, None, 8, 2000, None) == R

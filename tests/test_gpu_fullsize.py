@@ -96,3 +96,11 @@ def test_rope_kv_append_full_configuration(dev, oracle):
     assert np.array_equal(kc[lo:lo + T].cpu().numpy(), wk) and np.array_equal(vc[lo:lo + T].cpu().numpy(), wv)
     assert not bool(kc[:lo].any()) and not bool(kc[lo + T:].any())        # every other cell untouched
     assert not bool(vc[:lo].any()) and not bool(vc[lo + T:].any())
+    # round trip over every appended cell: reading V back gives the oracle's decode of its own cells, and lies within
+    # half a quantisation step (+ the FP16 rounding of d) of the V that went in
+    back = ops.kv_read_f32(vc, cell0=lo, rows=T)
+    assert np.array_equal(bits(back.cpu().numpy().reshape(-1)), bits(oracle.dequantize_q8_0(wv)))
+    vin = D(v)
+    amax = vin.reshape(T, nkv, hd // 32, 32).abs().amax(-1, keepdim=True)
+    bound = amax / 127 * (0.5 + 127 * 2.0 ** -11) + 1e-30
+    assert bool(((back.reshape(T, nkv, hd // 32, 32) - vin.reshape(T, nkv, hd // 32, 32)).abs() <= bound).all())

@@ -244,6 +244,63 @@ def test_rope_kv8_format_matches_reference_rule(dev, oracle):
     assert np.array_equal(vs[pos].cpu().numpy().view(np.uint16).reshape(-1), wsc)
 
 
+# ---- reading the cache back ------------------------------------------------------------------------------------------
+
+def test_kv_read_matches_reference_decode_on_golden_cells(dev, oracle):
+    """Cells filled with the reference's own quantised stress rows: the read-back equals its decode bit for bit."""
+    gold = np.load(os.path.join(GOLD, "quant.npz"))
+    # KV8: 856 groups of 64 = 214 rows of 256
+    codes = gold["kv8_codes"].reshape(214, 1, 256)
+    scales = gold["kv8_scales"].reshape(214, 1, 4)
+    got = ops.kv_read_f32(to_dev(codes, dev), scale=to_dev(scales.view(np.int16), dev)).cpu().numpy()
+    assert np.array_equal(bits(got.reshape(-1)), bits(gold["kv8_values"].reshape(-1)))
+    # Q8_0: 1712 blocks = 214 rows of 8 blocks
+    cells = gold["q8_0"].reshape(214, 1, 272)
+    got = ops.kv_read_f32(to_dev(cells, dev)).cpu().numpy()
+    assert np.array_equal(bits(got.reshape(-1)), bits(oracle.dequantize_q8_0(cells)))
+
+
+@pytest.mark.parametrize("fmt,hd,nkv", [("q8_0", 256, 2), ("kv8", 256, 2), ("q8_0", 128, 3), ("kv8", 128, 1),
+                                        ("q8_0", 64, 2), ("kv8", 64, 5)])
+def test_append_then_read_back(dev, oracle, fmt, hd, nkv):
+    """What the append wrote, read back through a list of cells (bad cells flagged, their rows untouched), equals the
+    oracle's quantise-then-decode of the same V rows; cells nobody wrote read as zeros."""
+    g = synth.rng(21)
+    rows, nq, slots = 77, 4, 512
+    q, k, v, _, _ = _rope_case(g, rows, nq, nkv, hd, False)
+    pos = synth.positions(g, rows, slots - rows)
+    ts = oracle.theta_scale(1e7, 64)
+    D = lambda a: to_dev(a, dev)  # noqa: E731
+    if fmt == "q8_0":
+        kc, vc = ops.new_kv_cache(slots, nkv, hd, dev), ops.new_kv_cache(slots, nkv, hd, dev)
+        ops.rope_neox_q8_0_append(D(q), D(k), D(v), D(pos), n_rot=min(64, hd), theta_scale=ts, k_cache=kc, v_cache=vc)
+        want = oracle.dequantize_q8_0(oracle.quantize_q8_0(v)).reshape(rows, nkv, hd)
+        scale = None
+    else:
+        (kc, ks), (vc, vs) = ops.new_kv_cache(slots, nkv, hd, dev, fmt="kv8"), ops.new_kv_cache(slots, nkv, hd, dev, fmt="kv8")
+        ops.rope_neox_kv8_append(D(q), D(k), D(v), D(pos), n_rot=min(64, hd), theta_scale=ts, k_cache=kc, v_cache=vc,
+                                 k_scale=ks, v_scale=vs)
+        want = oracle.kv8_dequantize(*oracle.kv8_quantize(v)).reshape(rows, nkv, hd)
+        scale = vs
+    cells = np.concatenate([pos, [-1, slots, int(pos.max()) + 1]]).astype(np.int32)   # two bad cells, one unwritten
+    out = Guarded((len(cells), nkv, hd), torch.float32, dev)
+    err = ops.new_err(dev)
+    ops.kv_read_f32(vc, scale=scale, cells=D(cells), out=out.live, err=err)
+    torch.cuda.synchronize()
+    out.check_guards()
+    got = out.numpy()
+    assert int(err.item()) == ops.ERR_SLOT
+    assert np.array_equal(bits(got[:rows]), bits(want))
+    assert (got[rows:rows + 2].view(np.uint8) == POISON).all()
+    assert not got[rows + 2].any()
+    # contiguous form: cells cell0 .. cell0 + n - 1
+    lo = int(pos.min())
+    span = ops.kv_read_f32(vc, scale=scale, cell0=lo, rows=16).cpu().numpy()
+    full = np.zeros((slots, nkv, hd), np.float32)
+    full[pos] = want
+    assert np.array_equal(bits(span), bits(full[lo:lo + 16]))
+
+
 # ---- get_rows ----------------------------------------------------------------------------------------------------------
 
 @pytest.mark.parametrize("fmt,cols,vocab,rows", [

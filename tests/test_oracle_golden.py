@@ -41,6 +41,12 @@ def test_kv8_matches_reference(oracle, quant):
     assert np.array_equal(scales, quant["kv8_scales"])
 
 
+def test_kv8_decode_matches_reference(oracle, quant):
+    """value = float(code) * f32(scale): bit for bit the reference's kv_q8_value over its stress rows."""
+    got = oracle.kv8_dequantize(quant["kv8_codes"], quant["kv8_scales"])
+    assert np.array_equal(got.view(np.uint32), quant["kv8_values"].reshape(-1).view(np.uint32))
+
+
 @pytest.mark.parametrize("fmt", ["q4_k", "iq3_xxs", "q8_0", "iq3_s"])
 def test_decoders_match_reference_bits(oracle, decode, fmt):
     fn = {"q4_k": oracle.dequantize_q4_k, "iq3_xxs": oracle.dequantize_iq3_xxs, "q8_0": oracle.dequantize_q8_0,
