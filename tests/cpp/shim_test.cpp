@@ -137,6 +137,50 @@ static void parity_cases() {
         }
         CHECK(worst <= 2);
     }
+    // V rows appended as Q8_0 cells (qsp_kv, K/V only) and read back (kv_read): bitwise the oracle's decode of its
+    // own quantised rows; a cell nobody wrote reads as zeros; a bad cell is flagged and its row left alone
+    {
+        const int rows = 9, hd = 256, cells = 32;
+        std::vector<float> k(size_t(rows) * hd), v(k.size());
+        for (auto & x : k) x = nd(rng);
+        for (auto & x : v) x = nd(rng) * 4.0f;
+        std::vector<int32_t> pos(rows);
+        for (int i = 0; i < rows; ++i) pos[i] = 3 + i;
+        dev_buf<float> dk(k.size()), dv(v.size());
+        dk.up(k), dv.up(v);
+        dev_buf<int32_t> dp(rows);
+        dp.up(pos);
+        dev_buf<uint8_t> kc(size_t(cells) * 272, 0), vc(size_t(cells) * 272, 0);
+        dev_buf<uint32_t> derr(1, 0);
+        fnb::qsa::qsp_kv_args a;
+        a.kv_k = dk.p, a.kv_v = dv.p, a.pos = dp.p, a.rows = rows, a.max_cells = cells, a.n_q_heads = 0, a.n_kv_heads = 1;
+        a.theta_scale = fnb_rope_theta_scale(1e7f, 64), a.k_cache = kc.p, a.v_cache = vc.p, a.err = derr.p;
+        CHECK(fnb::qsa::qsp_kv(a, s));
+        const std::vector<int32_t> want_cells = {3, 11, 20, -1, 7};  // written, written, never written, bad, written
+        dev_buf<int32_t> dc(want_cells.size());
+        dc.up(want_cells);
+        dev_buf<float> back(want_cells.size() * hd);
+        CHECK(fnb::qsa::kv_read(vc.p, nullptr, dc.p, 0, int64_t(want_cells.size()), cells, 1, hd, back.p, derr.p, s));
+        cudaStreamSynchronize(s);
+        std::vector<uint8_t> q(size_t(rows) * 272);
+        std::vector<float> deq(v.size());
+        fnbo_quantize_row_q8_0(v.data(), q.data(), int64_t(v.size()));
+        fnbo_dequantize_row_q8_0(q.data(), deq.data(), int64_t(v.size()));
+        const std::vector<float> got = back.down();
+        CHECK(std::memcmp(&got[0 * hd], &deq[0 * hd], hd * 4) == 0);
+        CHECK(std::memcmp(&got[1 * hd], &deq[8 * hd], hd * 4) == 0);
+        CHECK(std::memcmp(&got[4 * hd], &deq[4 * hd], hd * 4) == 0);
+        bool zeros = true, poisoned = true;
+        for (int i = 0; i < hd; ++i) {
+            zeros = zeros && got[2 * hd + i] == 0.0f;
+            uint32_t bits;
+            std::memcpy(&bits, &got[3 * hd + i], 4);
+            poisoned = poisoned && bits == 0x5a5a5a5au;
+        }
+        CHECK(zeros);
+        CHECK(poisoned);
+        CHECK(derr.down()[0] == fnb::err_slot);
+    }
     cudaStreamDestroy(s);
 }
 
