@@ -5,7 +5,7 @@
 //   KV8:         value = float(code) x f32(scale of the value's group of 64), exact in F32
 //                (fn::qsa::kv8::decode4, fn/kernels/qsa/kv_q8.cuh:61-67; CPU: fn::quant::kv_q8_value)
 // HBM-bound and write-dominated (272 or 264 bytes read, 1024 written per 256-value row): a warp takes a row, every
-// lane eight consecutive values, two 128-bit streaming stores per lane; many more CTAs than are resident, as in
+// lane two groups of four values half a row apart, two 128-bit streaming stores per lane; many more CTAs than are resident, as in
 // get_rows, so that SMs which drain slower get fewer rows.
 #include "common.cuh"
 
@@ -13,6 +13,7 @@ namespace fnb {
 namespace {
 
 constexpr int kWarpsPerCta = 8;
+constexpr int kUnroll = 4;  // cache rows a warp has in flight
 
 struct kv_read_params {
     const uint8_t * cache;
@@ -45,34 +46,103 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) kv_read_kernel(const kv_rea
     const int per_row = HD / 8;              // lanes that hold values (32 for 256, 16 for 128, 8 for 64)
     const int rows_per_warp = 32 / per_row;
     const int sub = lane % per_row, rw = lane / per_row;
-    for (int64_t r0 = warp * rows_per_warp; r0 < n_rows; r0 += n_warps * rows_per_warp) {
-        const int64_t r = r0 + rw;
-        if (r >= n_rows) continue;
-        const int64_t t = r / p.n_kv;
-        const int h = int(r - t * p.n_kv);
-        const int64_t cell = p.cells != nullptr ? int64_t(__ldg(p.cells + t)) : p.cell0 + t;
-        if (cell < 0 || cell >= p.cache_slots) {
-            if (sub == 0 && p.err != nullptr) atomicOr(p.err, FNB_ERR_SLOT);
-            continue;
+    // kUnroll rows' loads are issued before the first is widened and stored: one row per trip left the kernel waiting
+    // on its own loads (79 % of the HBM roofline at 262144 cells)
+    for (int64_t base = warp * kUnroll * rows_per_warp; base < n_rows; base += n_warps * kUnroll * rows_per_warp) {
+        uint32_t w0[kUnroll], w1[kUnroll];
+        float s0[kUnroll], s1[kUnroll];
+        int64_t row[kUnroll];
+#pragma unroll
+        for (int j = 0; j < kUnroll; ++j) {
+            const int64_t r = base + int64_t(j) * rows_per_warp + rw;
+            row[j] = -1;
+            if (r >= n_rows) continue;
+            const int64_t t = r / p.n_kv;
+            const int h = int(r - t * p.n_kv);
+            const int64_t cell = p.cells != nullptr ? int64_t(__ldg(p.cells + t)) : p.cell0 + t;
+            if (cell < 0 || cell >= p.cache_slots) {
+                if (sub == 0 && p.err != nullptr) atomicOr(p.err, FNB_ERR_SLOT);
+                continue;
+            }
+            row[j] = r;
+            const int64_t c = cell * p.n_kv + h;
+            // the lane takes code words `sub` and `sub + per_row` of the row (four codes each), so that each of its two
+            // store instructions writes per_row x 16 contiguous bytes; with eight adjacent codes per lane every store
+            // instruction wrote half of each 32-byte sector it touched
+            const int k0 = sub, k1 = sub + per_row;
+            if (KV8) {
+                const uint32_t * w = reinterpret_cast<const uint32_t *>(p.cache + c * HD);
+                w0[j] = __ldg(w + k0), w1[j] = __ldg(w + k1);
+                const uint16_t * sc = p.scale + c * (HD / 64);
+                s0[j] = f16_bits_to_f32(__ldg(sc + k0 / 16)), s1[j] = f16_bits_to_f32(__ldg(sc + k1 / 16));
+            } else {
+                // 34-byte blocks: fp16 d, 32 codes; code word k is bytes 2 + 4 (k % 8) .. of block k / 8 (2-byte aligned)
+                const uint16_t * b0 = reinterpret_cast<const uint16_t *>(p.cache + (c * (HD / 32) + k0 / 8) * 34);
+                const uint16_t * b1 = reinterpret_cast<const uint16_t *>(p.cache + (c * (HD / 32) + k1 / 8) * 34);
+                s0[j] = f16_bits_to_f32(__ldg(b0)), s1[j] = f16_bits_to_f32(__ldg(b1));
+                const uint16_t * q0 = b0 + 1 + 2 * (k0 % 8);
+                const uint16_t * q1 = b1 + 1 + 2 * (k1 % 8);
+                w0[j] = uint32_t(__ldg(q0)) | (uint32_t(__ldg(q0 + 1)) << 16);
+                w1[j] = uint32_t(__ldg(q1)) | (uint32_t(__ldg(q1 + 1)) << 16);
+            }
         }
-        const int64_t c = cell * p.n_kv + h;
-        uint32_t w0, w1;
-        float s;
-        if (KV8) {
-            const uint2 w = __ldg(reinterpret_cast<const uint2 *>(p.cache + c * HD) + sub);
-            w0 = w.x, w1 = w.y;
-            s = f16_bits_to_f32(__ldg(p.scale + c * (HD / 64) + sub / 8));
-        } else {
-            // a 34-byte block: fp16 d, 32 codes; this lane's eight codes start 2 + 8 (sub % 4) bytes into block sub / 4
-            const uint16_t * blk = reinterpret_cast<const uint16_t *>(p.cache + (c * (HD / 32) + sub / 4) * 34);
-            s = f16_bits_to_f32(__ldg(blk));
-            const uint16_t * q = blk + 1 + 4 * (sub % 4);
-            w0 = uint32_t(__ldg(q)) | (uint32_t(__ldg(q + 1)) << 16);
-            w1 = uint32_t(__ldg(q + 2)) | (uint32_t(__ldg(q + 3)) << 16);
+#pragma unroll
+        for (int j = 0; j < kUnroll; ++j) {
+            if (row[j] < 0) continue;
+            float4 * dst = reinterpret_cast<float4 *>(p.out + row[j] * HD) + sub;
+            st_stream(dst, widen4(w0[j], s0[j]));
+            st_stream(dst + per_row, widen4(w1[j], s1[j]));
         }
-        float4 * dst = reinterpret_cast<float4 *>(p.out + r * HD) + 2 * sub;
-        st_stream(dst, widen4(w0, s));
-        st_stream(dst + 1, widen4(w1, s));
+    }
+}
+
+// Q8_0 cells of 256 values are 272 bytes = 17 x 16, 16-byte aligned: 17 lanes fetch a row with one 128-bit load each
+// and park it in the warp's shared-memory slot, from which every lane picks its two code words and their d (the
+// blocks are only 2-byte aligned, and six 2-byte GLOBAL loads per lane and row held this format at 71 % of the
+// roofline where KV8 ran at 93 %).
+__global__ void __launch_bounds__(kWarpsPerCta * 32) kv_read_q8_0_256_kernel(const kv_read_params p) {
+    __shared__ __align__(16) uint8_t s_rows[kWarpsPerCta][kUnroll][272];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int64_t warp = int64_t(blockIdx.x) * kWarpsPerCta + wid;
+    const int64_t n_warps = int64_t(gridDim.x) * kWarpsPerCta;
+    const int64_t n_rows = p.rows * p.n_kv;
+    for (int64_t base = warp * kUnroll; base < n_rows; base += n_warps * kUnroll) {
+        uint4 v[kUnroll];
+        bool live[kUnroll];
+#pragma unroll
+        for (int j = 0; j < kUnroll; ++j) {
+            const int64_t r = base + j;
+            live[j] = false;
+            if (r >= n_rows) continue;
+            const int64_t t = r / p.n_kv;
+            const int h = int(r - t * p.n_kv);
+            const int64_t cell = p.cells != nullptr ? int64_t(__ldg(p.cells + t)) : p.cell0 + t;
+            if (cell < 0 || cell >= p.cache_slots) {
+                if (lane == 0 && p.err != nullptr) atomicOr(p.err, FNB_ERR_SLOT);
+                continue;
+            }
+            live[j] = true;
+            if (lane < 17) v[j] = __ldg(reinterpret_cast<const uint4 *>(p.cache + (cell * p.n_kv + h) * 272) + lane);
+        }
+#pragma unroll
+        for (int j = 0; j < kUnroll; ++j) {
+            if (live[j] && lane < 17) reinterpret_cast<uint4 *>(s_rows[wid][j])[lane] = v[j];
+        }
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < kUnroll; ++j) {
+            if (!live[j]) continue;
+            // code word k: bytes 2 + 4 (k % 8) .. of block k / 8; the lane takes words `lane` and `lane + 32`
+            const uint16_t * b0 = reinterpret_cast<const uint16_t *>(s_rows[wid][j] + (lane / 8) * 34);
+            const uint16_t * b1 = b0 + 4 * 17;
+            const uint16_t * q0 = b0 + 1 + 2 * (lane % 8);
+            const uint16_t * q1 = b1 + 1 + 2 * (lane % 8);
+            const uint32_t w0 = uint32_t(q0[0]) | (uint32_t(q0[1]) << 16), w1 = uint32_t(q1[0]) | (uint32_t(q1[1]) << 16);
+            float4 * dst = reinterpret_cast<float4 *>(p.out + (base + j) * 256) + lane;
+            st_stream(dst, widen4(w0, f16_bits_to_f32(b0[0])));
+            st_stream(dst + 32, widen4(w1, f16_bits_to_f32(b1[0])));
+        }
+        __syncwarp();
     }
 }
 
@@ -92,11 +162,14 @@ extern "C" int32_t fnb_kv_read_f32(const fnb_kv_read_args * a, void * stream) {
     p.cache = static_cast<const uint8_t *>(a->cache), p.scale = a->scale, p.cells = a->cells, p.out = a->out, p.err = a->err;
     p.rows = a->rows, p.cache_slots = a->cache_slots, p.cell0 = a->cell0, p.n_kv = a->n_kv_heads, p.head_dim = a->head_dim;
     const int rows_per_warp = 32 / (a->head_dim / 8);
-    const int64_t warps = (a->rows * a->n_kv_heads + rows_per_warp - 1) / rows_per_warp;
+    const int64_t per_warp = int64_t(rows_per_warp) * kUnroll;
+    const int64_t warps = (a->rows * a->n_kv_heads + per_warp - 1) / per_warp;
     const int grid = grid_for((warps + kWarpsPerCta - 1) / kWarpsPerCta, 32);
     const cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (a->scale != nullptr) {
         kv_read_kernel<true><<<grid, kWarpsPerCta * 32, 0, s>>>(p);
+    } else if (a->head_dim == 256) {
+        kv_read_q8_0_256_kernel<<<grid, kWarpsPerCta * 32, 0, s>>>(p);
     } else {
         kv_read_kernel<false><<<grid, kWarpsPerCta * 32, 0, s>>>(p);
     }
