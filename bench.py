@@ -195,7 +195,7 @@ def run_reference(args) -> None:
     tps = sample * args.steps / dt
     desc = (f"{sample} tokens per step of the same chain on the host cores (the reference has no CPU code for the "
             "whole path in its tree: this is the oracle port, -O2 -ffp-contract=off, host libm)")
-    print(json.dumps({
+    emit({
         "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded)",
@@ -203,7 +203,7 @@ def run_reference(args) -> None:
         "cpu_baseline": {"value": tps, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
         "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
-    }))
+    })
 
 
 # ---- the GPU arm -----------------------------------------------------------------------------------------------
@@ -343,12 +343,35 @@ def run_ours(args) -> None:
             line["gather_ms"] = gather_ms
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(os.cpu_count() or 1)
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
 
+_RESULT_FD = None
+
+
+def claim_stdout() -> None:
+    """The contract is ONE JSON line on stdout.  Libraries print there too (NCCL's version banner at some debug
+    levels, whatever a C extension writes), so file descriptor 1 is pointed at stderr for the whole run and the result
+    line alone goes to the descriptor that was stdout."""
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def main() -> None:
+    claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
