@@ -31,10 +31,22 @@
 namespace fnb {
 namespace {
 
-constexpr int kGroups = 2;
-constexpr int kGroupWarps = 10;
+#ifndef FNB_ROPE_GROUPS
+#define FNB_ROPE_GROUPS 2
+#endif
+#ifndef FNB_ROPE_GROUP_WARPS
+#define FNB_ROPE_GROUP_WARPS 10
+#endif
+#ifndef FNB_ROPE_PRODUCERS
+#define FNB_ROPE_PRODUCERS 2
+#endif
+#ifndef FNB_ROPE_MAX_STAGES
+#define FNB_ROPE_MAX_STAGES 4
+#endif
+constexpr int kGroups = FNB_ROPE_GROUPS;
+constexpr int kGroupWarps = FNB_ROPE_GROUP_WARPS;
 constexpr int kConsumerWarps = kGroups * kGroupWarps;
-constexpr int kProducerWarps = 2;  // a token's angles are one warp's work of ~1000 cycles latency: two keep ahead
+constexpr int kProducerWarps = FNB_ROPE_PRODUCERS;  // a token's angles are one warp's work of ~1000 cycles latency
 constexpr int kThreads = (kConsumerWarps + kProducerWarps) * 32;
 constexpr int kSlotBytes = 288;    // a 272-byte cell, padded to 16
 constexpr int kMaxTile = 8;        // tokens per tile at most
@@ -332,7 +344,10 @@ __global__ void __launch_bounds__(kThreads, 1) rope_kv_pipe_kernel(const rope_ke
     }
 }
 
-constexpr size_t kSmemBudget = 212 * 1024;
+#ifndef FNB_ROPE_SMEM_KB
+#define FNB_ROPE_SMEM_KB 212
+#endif
+constexpr size_t kSmemBudget = size_t(FNB_ROPE_SMEM_KB) * 1024;
 
 template <int HD, kv_fmt F>
 bool launch_one(const rope_kernel_args & a, cudaStream_t s) {
@@ -344,20 +359,24 @@ bool launch_one(const rope_kernel_args & a, cudaStream_t s) {
     const int rpt = a.n_q + 2 * a.n_kv;
     if (rpt < 2) return false;  // r / rpt by multiply-high needs rpt >= 2
     const size_t tok_bytes = size_t(rpt) * HD * 4;
-    int tt = int(40960 / tok_bytes);
+    int tt = (kGroupWarps * 4) / rpt;  // one quad of rows per consumer warp and tile
     tt = tt < 1 ? 1 : tt > kMaxTile ? kMaxTile : tt;
     const size_t fixed = size_t(3) * HD * 4 + size_t(kConsumerWarps) * 4 * kSlotBytes + 256;
     auto need = [&](int t, int st) {
         return size_t(st) * (size_t(t) * tok_bytes + size_t(t) * (HD / 2) * 8 + 16 + size_t(t) * 4) + fixed;
     };
-    int stages = 4;
-    if (need(tt, stages) > kSmemBudget) stages = 2;
-    if (need(tt, stages) > kSmemBudget) {
+    // the ring: a multiple of the group count (a stage always goes to the same group), as deep as the budget allows
+    auto fit = [&](int t) {
+        int st = (FNB_ROPE_MAX_STAGES / kGroups) * kGroups;
+        while (st >= kGroups && need(t, st) > kSmemBudget) st -= kGroups;
+        return st;
+    };
+    int stages = fit(tt);
+    if (stages < kGroups && tt > 1) {
         tt = 1;
-        stages = 4;
-        if (need(tt, stages) > kSmemBudget) stages = 2;
-        if (need(tt, stages) > kSmemBudget) return false;
+        stages = fit(tt);
     }
+    if (stages < kGroups) return false;
     const size_t smem = need(tt, stages);
 
     static std::atomic<bool> configured[64];
