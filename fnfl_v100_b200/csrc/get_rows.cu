@@ -423,7 +423,7 @@ extern "C" int32_t fnb_get_rows_q4_k(const void * table, int64_t n_vocab, const 
     if (cols == 2048) {
         get_rows_q4_k_staged_kernel<<<persistent_grid(rows, kStagedGridPerSm), kWarpsPerCta * 32, 0, s>>>(tb, n_vocab, ids, out, err, rows);
     } else {
-        get_rows_q4_k_kernel<8><<<persistent_grid(rows, 8), kWarpsPerCta * 32, 0, s>>>(tb, n_vocab, ids, out, err, rows, cols);
+        get_rows_q4_k_kernel<8><<<persistent_grid(rows, kStagedGridPerSm), kWarpsPerCta * 32, 0, s>>>(tb, n_vocab, ids, out, err, rows, cols);
     }
     return launch_status();
 }
@@ -437,7 +437,7 @@ extern "C" int32_t fnb_get_rows_iq3_xxs(const void * table, int64_t n_vocab, con
     if (cols == 2048) {
         get_rows_iq3_xxs_staged_kernel<<<persistent_grid(rows, kStagedGridPerSm), kWarpsPerCta * 32, 0, s>>>(tb, n_vocab, ids, out, err, rows);
     } else {
-        get_rows_iq3_xxs_kernel<<<persistent_grid(rows, 8), kWarpsPerCta * 32, 0, s>>>(tb, n_vocab, ids, out, err, rows, cols);
+        get_rows_iq3_xxs_kernel<<<persistent_grid(rows, kStagedGridPerSm), kWarpsPerCta * 32, 0, s>>>(tb, n_vocab, ids, out, err, rows, cols);
     }
     return launch_status();
 }
@@ -446,7 +446,7 @@ extern "C" int32_t fnb_get_rows_q8_0(const void * table, int64_t n_vocab, const 
                                      uint32_t * err, int64_t rows, int32_t cols, void * stream) {
     using namespace fnb;
     if (!common_ok(table, n_vocab, ids, out, err, rows, cols, 32, 34, 2)) return FNB_REJECTED;
-    get_rows_q8_0_kernel<<<persistent_grid(rows, 8), kWarpsPerCta * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+    get_rows_q8_0_kernel<<<persistent_grid(rows, kStagedGridPerSm), kWarpsPerCta * 32, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint8_t *>(table), n_vocab, ids, out, err, rows, cols);
     return launch_status();
 }
