@@ -11,3 +11,11 @@ extern "C" const char * fnb_status_name(int32_t status) {
         default: return "unknown status";
     }
 }
+
+// One-time, per-device set-up of every kernel that needs more than the default shared memory, for the CURRENT device.
+// After it no launcher of this library calls anything but the launch itself, so every entry point is capturable from
+// its first call on.
+extern "C" int32_t fnb_prepare_device(void) {
+    const bool ok = fnb::glu_prepare_device() && fnb::rms_norm_quant_prepare_device() && fnb::rope_prepare_device();
+    return ok ? FNB_OK : FNB_LAUNCH_FAILED;
+}

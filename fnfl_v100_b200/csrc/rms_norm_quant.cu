@@ -204,6 +204,28 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
 }
 
+// raises the kernel's dynamic shared-memory limit once per device
+template <out_fmt F, int BPL, bool F32OUT>
+bool ensure_configured() {
+    static std::atomic<bool> configured[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    if (!configured[dev].load(std::memory_order_acquire)) {
+        if (cudaFuncSetAttribute(rms_norm_quant_kernel<F, BPL, F32OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 int(kSmemBudget)) != cudaSuccess) {
+            return false;
+        }
+        configured[dev].store(true, std::memory_order_release);
+    }
+    return true;
+}
+template <out_fmt F>
+bool prepare_fmt() {
+    return ensure_configured<F, 1, false>() && ensure_configured<F, 1, true>() && ensure_configured<F, 2, false>() &&
+           ensure_configured<F, 2, true>() && ensure_configured<F, 3, false>() && ensure_configured<F, 3, true>() &&
+           ensure_configured<F, 4, false>() && ensure_configured<F, 4, true>();
+}
+
 template <out_fmt F, int BPL, bool F32OUT>
 int32_t launch_one(const float * x, const float * w, float eps, uint8_t * out, float * scales, float * out_f32, int64_t rows,
                    int32_t cols, cudaStream_t s) {
@@ -216,16 +238,7 @@ int32_t launch_one(const float * x, const float * w, float eps, uint8_t * out, f
     if (stages < 2) return FNB_REJECTED;
     const size_t smem = size_t(stages) * tile + fixed;
 
-    static std::atomic<bool> configured[64];
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FNB_LAUNCH_FAILED;
-    if (!configured[dev].load(std::memory_order_acquire)) {
-        if (cudaFuncSetAttribute(rms_norm_quant_kernel<F, BPL, F32OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 int(kSmemBudget)) != cudaSuccess) {
-            return FNB_LAUNCH_FAILED;
-        }
-        configured[dev].store(true, std::memory_order_release);
-    }
+    if (!ensure_configured<F, BPL, F32OUT>()) return FNB_LAUNCH_FAILED;
     const int64_t n_tiles = (rows + kGroupWarps - 1) / kGroupWarps;
     const int grid = int(n_tiles < kSmCount ? n_tiles : kSmCount);
     rms_norm_quant_kernel<F, BPL, F32OUT><<<grid, kThreads, smem, s>>>(x, w, eps, out, scales, out_f32, rows, cols, stages);
@@ -256,6 +269,11 @@ int32_t launch(const float * x, const float * w, float eps, void * out, float * 
 }
 
 }  // namespace
+
+bool rms_norm_quant_prepare_device() {
+    return prepare_fmt<out_fmt::q8_1>() && prepare_fmt<out_fmt::q8_0>() && prepare_fmt<out_fmt::act>();
+}
+
 }  // namespace fnb
 
 extern "C" int32_t fnb_rms_norm_q8_1(const float * x, const float * w, float eps, void * out_q8_1, float * out_f32,

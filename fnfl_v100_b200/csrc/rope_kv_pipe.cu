@@ -349,6 +349,23 @@ __global__ void __launch_bounds__(kThreads, 1) rope_kv_pipe_kernel(const rope_ke
 #endif
 constexpr size_t kSmemBudget = size_t(FNB_ROPE_SMEM_KB) * 1024;
 
+// raises the kernel's dynamic shared-memory limit once per device
+template <int HD, kv_fmt F>
+bool ensure_configured() {
+    static std::atomic<bool> configured[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    if (!configured[dev].load(std::memory_order_acquire)) {
+        if (cudaFuncSetAttribute(rope_kv_pipe_kernel<HD, F>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 int(kSmemBudget)) != cudaSuccess) {
+            (void) cudaGetLastError();
+            return false;
+        }
+        configured[dev].store(true, std::memory_order_release);
+    }
+    return true;
+}
+
 template <int HD, kv_fmt F>
 bool launch_one(const rope_kernel_args & a, cudaStream_t s) {
     // the halves of a rotary pair must be whole blocks apart: n_rot a multiple of 64, at most head_dim
@@ -379,17 +396,7 @@ bool launch_one(const rope_kernel_args & a, cudaStream_t s) {
     if (stages < kGroups) return false;
     const size_t smem = need(tt, stages);
 
-    static std::atomic<bool> configured[64];
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
-    if (!configured[dev].load(std::memory_order_acquire)) {
-        if (cudaFuncSetAttribute(rope_kv_pipe_kernel<HD, F>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 int(kSmemBudget)) != cudaSuccess) {
-            (void) cudaGetLastError();
-            return false;
-        }
-        configured[dev].store(true, std::memory_order_release);
-    }
+    if (!ensure_configured<HD, F>()) return false;
     const int64_t n_tiles = (a.rows + tt - 1) / tt;
     const int grid = int(n_tiles < kSmCount ? n_tiles : kSmCount);
     const pipe_shape sh{tt, stages, nbh, uint32_t((0x100000000ull + uint64_t(rpt) - 1) / uint64_t(rpt))};
@@ -437,6 +444,12 @@ bool rope_kv_pipe_try_launch(const rope_kernel_args & a, int head_dim, kv_fmt fm
         case 64: return q8 ? launch_one<64, kv_fmt::q8_0>(a, s) : launch_one<64, kv_fmt::kv8>(a, s);
         default: return false;
     }
+}
+
+bool rope_prepare_device() {
+    return ensure_configured<256, kv_fmt::q8_0>() && ensure_configured<256, kv_fmt::kv8>() &&
+           ensure_configured<128, kv_fmt::q8_0>() && ensure_configured<128, kv_fmt::kv8>() &&
+           ensure_configured<64, kv_fmt::q8_0>() && ensure_configured<64, kv_fmt::kv8>();
 }
 
 }  // namespace fnb

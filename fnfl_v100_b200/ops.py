@@ -311,6 +311,11 @@ def embed_supply(fmt: str, table, tok, n_own: int, src, row0: int, *, own=None, 
     _check(_lib.lib().fnb_embed_supply(C.byref(a), _ptr(src), row0, src.shape[0], _stream()), "embed_supply")
 
 
+def prepare_device() -> None:
+    """One-time kernel attribute set-up for the current device, so that even a first call can sit inside a capture."""
+    _check(_lib.lib().fnb_prepare_device(), "prepare_device")
+
+
 def check_tokens(ids_host: torch.Tensor, n_vocab: int) -> int:
     """Host check before upload (fn::embed::check_tokens): 0, or 1 + the index of the first id outside [0, n_vocab)."""
     if ids_host.is_cuda or ids_host.dtype != torch.int32 or not ids_host.is_contiguous():

@@ -307,6 +307,15 @@ int32_t fnb_selftest_kv8_math(uint64_t n, uint64_t seed, unsigned long long * mi
  */
 int32_t fnb_selftest_expf(unsigned long long * mismatches, void * stream);
 
+/*
+ * Optional, once per device (the current one): performs the one-time kernel attribute set-up (cudaFuncSetAttribute for
+ * the kernels that use more than 48 KB of shared memory) that the SwiGLU / requantiser, fused-norm and rope entry
+ * points otherwise perform on their first call.  After it every entry point is legal inside a stream capture from
+ * its first call on.  No counterpart in the reference (its launchers have the same first-call rule and the engine
+ * warms them before recording its graphs).  FNB_OK, or FNB_LAUNCH_FAILED when a CUDA call fails.
+ */
+int32_t fnb_prepare_device(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -408,6 +408,43 @@ def test_chain_matches_oracle_and_replays_in_a_graph(dev, oracle):
         assert np.array_equal(a.view(np.uint8), H(t).view(np.uint8))
 
 
+def test_first_calls_can_be_captured_after_prepare_device(dev, oracle):
+    """In a fresh process: prepare_device, then the very first call of a pipeline kernel happens inside a stream capture
+    (no launcher may then do anything but launch) and the replayed graph gives the oracle's bytes."""
+    import subprocess
+    import sys
+    import textwrap
+    code = textwrap.dedent("""
+        import numpy as np, torch
+        from fnfl_v100_b200 import ops, synth
+        from oracle import oracle as O
+        dev = torch.device("cuda:0")
+        g = synth.rng(3)
+        gate, up = synth.normal(g, (64, 512), 0.5), synth.normal(g, (64, 512), 0.5)
+        x, w = synth.normal(g, (9, 2048)), synth.norm_weight(g, 2048)
+        dg, du, dx, dw = (torch.from_numpy(a).to(dev) for a in (gate, up, x, w))
+        out = torch.empty((64, 16 * 36), dtype=torch.uint8, device=dev)
+        ops.prepare_device()
+        torch.cuda.synchronize()
+        s = torch.cuda.Stream(dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(s):
+            with torch.cuda.graph(graph, stream=s):
+                ops.swiglu_q8_1(dg, du, out=out)          # first call of this kernel in the process
+                blocks = ops.rms_norm_quant(dx, dw, 1e-6, "q8_1")
+        graph.replay()
+        torch.cuda.synchronize()
+        want = O.swiglu_q8_1(gate, up)
+        assert np.array_equal(out.cpu().numpy().reshape(-1), want.reshape(-1))
+        again = ops.rms_norm_quant(dx, dw, 1e-6, "q8_1")       # the same launch outside a capture
+        assert torch.equal(blocks, again) and bool(blocks.any())
+        print("captured-first-call ok")
+    """)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=root, timeout=600)
+    assert r.returncode == 0 and "captured-first-call ok" in r.stdout, r.stdout + r.stderr
+
+
 def test_glu_fast_path_equals_generic_path_on_its_whole_domain(dev):
     """2^28 pseudo-random (gate, up) pairs over |gate| in [2^-40, 64): the branch-free expf and the written-out
     division must give the same bits as the generic path (special-case aware expf, __fdiv_rn)."""
