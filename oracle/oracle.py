@@ -31,7 +31,7 @@ def build(with_ref: bool | None = None) -> None:
     ref_root = os.environ.get("FNB_REFERENCE", "/root/reference")
     if with_ref is None:
         with_ref = os.path.isdir(os.path.join(ref_root, "ggml", "src"))
-    targets = ["all"] + (["ref"] if with_ref else [])
+    targets = ["all"] + (["ref", "ref-gguf"] if with_ref else [])
     subprocess.run(["make", "-C", _HERE, "REFERENCE=" + ref_root] + targets, check=True, capture_output=True)
 
 
@@ -67,6 +67,50 @@ def lib() -> C.CDLL:
 
 def have_ref() -> bool:
     return os.path.exists(REF_SO)
+
+
+REF_GGUF_SO = os.path.join(_HERE, "_ref", "libfnb_ref_gguf.so")
+_ref_gguf = None
+
+
+def build_ref_gguf() -> None:
+    """Compile the reference's GGUF writer / reader (ggml/src/gguf.cpp with the ggml core) where it lies."""
+    ref_root = os.environ.get("FNB_REFERENCE", "/root/reference")
+    subprocess.run(["make", "-C", _HERE, "REFERENCE=" + ref_root, "ref-gguf"], check=True, capture_output=True)
+
+
+def have_ref_gguf() -> bool:
+    return os.path.exists(REF_GGUF_SO)
+
+
+def ref_gguf() -> C.CDLL:
+    global _ref_gguf
+    if _ref_gguf is None:
+        _ref_gguf = C.CDLL(REF_GGUF_SO)
+    return _ref_gguf
+
+
+def ref_gguf_write(path: str, tensors, alignment: int = 32) -> None:
+    """tensors: (name, ggml type, dims (ne0, ne1, ...), raw uint8 array); written by the reference's own gguf writer."""
+    n = len(tensors)
+    names = (C.c_char_p * n)(*[t[0].encode() for t in tensors])
+    types = (C.c_int32 * n)(*[t[1] for t in tensors])
+    nd = (C.c_int32 * n)(*[len(t[2]) for t in tensors])
+    ne = (C.c_int64 * (4 * n))(*[d for t in tensors for d in (list(t[2]) + [1, 1, 1, 1])[:4]])
+    bufs = [np.ascontiguousarray(t[3], np.uint8) for t in tensors]
+    data = (C.c_void_p * n)(*[b.ctypes.data for b in bufs])
+    rc = ref_gguf().ref_gguf_write(path.encode(), n, names, types, nd, ne, data, C.c_uint32(alignment))
+    if rc != 0:
+        raise RuntimeError(f"reference gguf writer failed ({rc})")
+
+
+def ref_gguf_find(path: str, name: str):
+    """(absolute file offset, ggml type, bytes, tensor count) as the reference's own reader reports them."""
+    off, typ, nb, cnt = C.c_int64(), C.c_int32(), C.c_int64(), C.c_int64()
+    rc = ref_gguf().ref_gguf_find(path.encode(), name.encode(), C.byref(off), C.byref(typ), C.byref(nb), C.byref(cnt))
+    if rc != 0:
+        raise KeyError(name)
+    return off.value, typ.value, nb.value, cnt.value
 
 
 def ref() -> C.CDLL:

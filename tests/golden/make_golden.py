@@ -67,8 +67,35 @@ def stress_blocks() -> np.ndarray:
     return np.ascontiguousarray(x)
 
 
+def model_file() -> None:
+    """A small model file written by the reference's OWN gguf writer (ggml/src/gguf.cpp): the fixture the reader is
+    pinned against.  The tensors' bytes and the offsets the reference's own reader reports go into model_tiny.npz."""
+    from fnfl_v100_b200 import synth
+    O.build_ref_gguf()
+    g = synth.rng(0x464E464C & 0xffff)
+    tensors = [
+        ("output_norm.weight", 0, (256,), synth.norm_weight(g, 256).view(np.uint8)),
+        ("token_embd.weight", 12, (256, 24), synth.q4_k_table(g, 24, 256)),
+        ("blk.0.ffn_gate_exps.weight", 18, (256, 8), synth.iq3_xxs_table(g, 8, 256)),
+        ("blk.0.attn_k.weight", 8, (64, 5), synth.q8_0_table(g, 5, 64)),
+        ("blk.0.ffn_down.weight", 14, (256, 2), g.integers(0, 256, 2 * 210).astype(np.uint8)),   # Q6_K: listed only
+    ]
+    path = os.path.join(HERE, "model_tiny.gguf")
+    O.ref_gguf_write(path, tensors, alignment=32)   # the writer lays data out on its default 32 whatever the key says
+    rec = {}
+    for name, typ, dims, raw in tensors:
+        off, t2, nb, cnt = O.ref_gguf_find(path, name)
+        assert t2 == typ and cnt == len(tensors) and nb == np.asarray(raw).size
+        rec[name + "|bytes"] = np.ascontiguousarray(raw, np.uint8).reshape(-1)
+        rec[name + "|offset"] = np.int64(off)
+        rec[name + "|type"] = np.int32(typ)
+    np.savez_compressed(os.path.join(HERE, "model_tiny.npz"), **rec)
+    print("model_tiny.gguf", os.path.getsize(path), "bytes")
+
+
 def main() -> None:
     O.build(with_ref=True)
+    model_file()
     r = O.ref()
     x = stress_blocks()
     n = x.shape[0]

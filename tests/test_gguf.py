@@ -78,6 +78,55 @@ def test_reads_directory_and_rows(tmp_path):
     assert fmt == "q4_k" and cols == 2048 and np.array_equal(table.numpy(), q4)
 
 
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def test_reads_the_file_the_reference_writer_wrote():
+    """tests/golden/model_tiny.gguf was written by the reference's own gguf writer (ggml/src/gguf.cpp, through
+    oracle/ref_gguf_shim.cpp); model_tiny.npz holds each tensor's bytes and the file offset the reference's own READER
+    reports for it.  This reader must find the same offsets and return the same bytes."""
+    rec = np.load(os.path.join(GOLD, "model_tiny.npz"))
+    names = sorted({k.split("|")[0] for k in rec.files})
+    raw = open(os.path.join(GOLD, "model_tiny.gguf"), "rb").read()
+    with gguf.GgufFile(os.path.join(GOLD, "model_tiny.gguf")) as f:
+        assert f.n_tensors == len(names) == 5
+        for name in names:
+            t = f.find(name)
+            want = rec[name + "|bytes"]
+            off = int(rec[name + "|offset"])
+            assert int(t.type) == int(rec[name + "|type"])
+            assert raw[off:off + want.size] == want.tobytes()          # the fixture is self-consistent
+            if int(t.type) == 14:                                      # Q6_K: listed, not decodable by this library
+                assert t.row_bytes == 0
+                continue
+            got = f.read_rows(t)
+            assert got.size == want.size and np.array_equal(got.reshape(-1), want)
+            row = f.read_rows(t, int(t.n_rows) - 1, 1)                 # last row alone: offsets inside the tensor
+            assert np.array_equal(row.reshape(-1), want[-int(t.row_bytes):])
+    table, fmt, cols = gguf.load_table(os.path.join(GOLD, "model_tiny.gguf"))
+    assert fmt == "q4_k" and cols == 256 and table.shape == (24, 144)
+
+
+def test_python_writer_agrees_with_the_reference_reader(tmp_path):
+    """The files the other tests write from the format specification are also what the reference's reader accepts
+    (runs only where the reference tree was present to build its gguf code)."""
+    from oracle import oracle as O
+    if not O.have_ref_gguf():
+        pytest.skip("reference gguf library not built here")
+    g = synth.rng(5)
+    q4 = synth.q4_k_table(g, 6, 512)
+    norm = synth.norm_weight(g, 512)
+    path = str(tmp_path / "m.gguf")
+    write_gguf(path, [("output_norm.weight", 0, (512,), norm.tobytes()), ("token_embd.weight", 12, (512, 6), q4.tobytes())],
+               alignment=32)
+    off, typ, nb, cnt = O.ref_gguf_find(path, "token_embd.weight")
+    assert (typ, nb, cnt) == (12, q4.size, 2)
+    with gguf.GgufFile(path) as f:
+        t = f.find("token_embd.weight")
+        assert np.array_equal(f.read_rows(t), q4)
+    assert open(path, "rb").read()[off:off + nb] == q4.tobytes()
+
+
 def test_refuses_malformed_files(tmp_path):
     p = str(tmp_path / "bad.gguf")
     open(p, "wb").write(b"GGML" + b"\0" * 64)
