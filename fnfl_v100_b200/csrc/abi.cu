@@ -16,6 +16,7 @@ extern "C" const char * fnb_status_name(int32_t status) {
 // After it no launcher of this library calls anything but the launch itself, so every entry point is capturable from
 // its first call on.
 extern "C" int32_t fnb_prepare_device(void) {
-    const bool ok = fnb::glu_prepare_device() && fnb::rms_norm_quant_prepare_device() && fnb::rope_prepare_device();
+    const bool ok = fnb::glu_prepare_device() && fnb::rms_norm_quant_prepare_device() && fnb::rope_prepare_device() &&
+                    fnb::expert_down_prepare_device();
     return ok ? FNB_OK : FNB_LAUNCH_FAILED;
 }

@@ -1,0 +1,205 @@
+// The consumer of the Q8_1 activations SwiGLU leaves: the routed experts' down mat-vec for a decode window,
+//     out[t][r] = weight row r . act[t],   t < nt (a few rows share one pass over the weights), r in [r0, r1)
+// with ggml's Q5_1 weights (24-byte blocks: fp16 d, fp16 m, 32 high bits, 16 bytes of nibbles; value = d q + m)
+// against Q8_1 activations.  Replaces fn::experts::cpu::kq_down_rows (fn/kernels/experts/cpu_kernels.h,
+// cpu_kq_avx2.cpp:293-320, :382-394) and is BIT-IDENTICAL to it: the AVX2 kernel keeps eight F32 lanes per (row, t),
+// lane j taking bytes 4 j .. 4 j + 3 of every block by one fused multiply-add per block with the block's scale
+// product, a fused scalar side sum of m x s, and one horizontal sum at the end in a fixed order; a GPU lane owns a
+// weight row and keeps the same eight accumulators per t in registers, so every float operation happens in the
+// reference's order.
+//
+// HBM-bound on the weights for the window sizes decode uses (nt <= 3); for larger nt the per-(block, t) arithmetic
+// the bit-exact order needs (8 dp4a + 8 conversions + 9 fused multiply-adds per lane) takes over.  A warp stages 32
+// consecutive weight rows into shared memory with coalesced loads (padded so that lane = row reads are conflict-free),
+// the window's activation blocks sit in shared memory once per CTA (their fp16 d and s widened once).
+#include <atomic>
+
+#include "common.cuh"
+
+namespace fnb {
+namespace {
+
+constexpr int kMaxWarps = 4;  // warps per CTA (fewer when 32 staged rows per warp would not fit in shared memory)
+constexpr int kMaxT = 8;      // rows of a window per pass over the weights (the reference's maxt)
+constexpr int kStageUnroll = 6;  // 64-bit loads a lane has in flight while staging a tile
+constexpr size_t kSmemLimit = 200 * 1024;
+
+__device__ __forceinline__ float hsum8(const float (&a)[8]) {  // hsum_float_8's order
+    const float r0 = __fadd_rn(a[4], a[0]), r1 = __fadd_rn(a[5], a[1]), r2 = __fadd_rn(a[6], a[2]), r3 = __fadd_rn(a[7], a[3]);
+    return __fadd_rn(__fadd_rn(r0, r2), __fadd_rn(r1, r3));
+}
+
+// NT: activation rows of this pass (1..8), compile time so the accumulators stay in registers
+template <int NT>
+__global__ void __launch_bounds__(kMaxWarps * 32)
+    down_q5_1_q8_1_kernel(const uint32_t * __restrict__ w, int row_words, int nb, const uint8_t * __restrict__ act,
+                          int64_t act_stride, float * __restrict__ out, int64_t out_stride, int64_t r0, int64_t r1) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int kWarps = blockDim.x >> 5;
+    const int pad_words = row_words | 1;                       // odd stride: lane = row reads hit 32 banks
+    // activations first (16-byte aligned vectors), then the warps' staged rows
+    uint32_t * qy_sm = reinterpret_cast<uint32_t *>(smem);                     // [NT][nb][8] the activations' code words
+    float2 * ds_sm = reinterpret_cast<float2 *>(qy_sm + size_t(NT) * nb * 8);  // [NT][nb] {d, s} as F32
+    uint32_t * rows_sm = reinterpret_cast<uint32_t *>(ds_sm + size_t(NT) * nb);  // [kWarps][32][pad_words]
+
+    for (int i = threadIdx.x; i < NT * nb; i += blockDim.x) {
+        const int t = i / nb, ib = i - t * nb;
+        const uint8_t * y = act + int64_t(t) * act_stride + size_t(ib) * 36;  // 4-byte aligned: {fp16 d, fp16 s, 32 codes}
+        const uint32_t hdr = __ldg(reinterpret_cast<const uint32_t *>(y));
+        ds_sm[i] = make_float2(f16_bits_to_f32(uint16_t(hdr & 0xffffu)), f16_bits_to_f32(uint16_t(hdr >> 16)));
+#pragma unroll
+        for (int k = 0; k < 8; ++k) qy_sm[size_t(i) * 8 + k] = __ldg(reinterpret_cast<const uint32_t *>(y + 4) + k);
+    }
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    uint32_t * mine = rows_sm + size_t(wid) * 32 * pad_words;
+    const int64_t n_tiles = (r1 - r0 + 31) / 32;
+    for (int64_t tile = int64_t(blockIdx.x) * kWarps + wid; tile < n_tiles; tile += int64_t(gridDim.x) * kWarps) {
+        const int64_t row0 = r0 + tile * 32;
+        const int live = int(r1 - row0 < 32 ? r1 - row0 : 32);
+        // stage `live` consecutive rows: coalesced 64-bit loads, several in flight per lane (a row is a whole number
+        // of 8-byte pairs: 24-byte blocks); pair g of the tile belongs to row g / (row_words / 2)
+        {
+            const uint2 * src = reinterpret_cast<const uint2 *>(w + row0 * row_words);
+            const uint32_t rp = uint32_t(row_words) >> 1;
+            const uint32_t total = uint32_t(live) * rp;
+            const uint32_t inv = uint32_t((0x100000000ull + rp - 1) / rp);  // g / rp by multiply-high (g < 2^20)
+            for (uint32_t base = 0; base < total; base += 32 * kStageUnroll) {
+                uint2 v[kStageUnroll];
+#pragma unroll
+                for (int u = 0; u < kStageUnroll; ++u) {
+                    const uint32_t g = base + 32 * u + lane;
+                    v[u] = g < total ? __ldg(src + g) : make_uint2(0u, 0u);
+                }
+#pragma unroll
+                for (int u = 0; u < kStageUnroll; ++u) {
+                    const uint32_t g = base + 32 * u + lane;
+                    if (g < total) {
+                        const uint32_t row = __umulhi(g, inv), col = 2 * (g - row * rp);
+                        mine[row * pad_words + col] = v[u].x;
+                        mine[row * pad_words + col + 1] = v[u].y;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane < live) {
+            const uint32_t * my_row = mine + lane * pad_words;
+            float acc[NT][8];
+            float summs[NT];
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                summs[t] = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[t][j] = 0.0f;
+            }
+            for (int ib = 0; ib < nb; ++ib) {
+                const uint32_t * b = my_row + 6 * ib;
+                const uint32_t dm = b[0], qh = b[1];
+                const float xd = f16_bits_to_f32(uint16_t(dm & 0xffffu)), xm = f16_bits_to_f32(uint16_t(dm >> 16));
+                // bytes 4 j .. 4 j + 3 of the block's 32 five-bit values: low nibbles of qs[0..15], then the high ones,
+                // each with its bit of qh as bit 4
+                uint32_t qx[8];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint32_t q = b[2 + k];
+                    const uint32_t hl = (qh >> (4 * k)) & 15u, hh = (qh >> (16 + 4 * k)) & 15u;
+                    // spread four bits to bit 4 of four bytes: b0 -> bit 4, b1 -> bit 12, b2 -> bit 20, b3 -> bit 28
+                    const uint32_t sl = ((hl & 1u) << 4) | ((hl & 2u) << 11) | ((hl & 4u) << 18) | ((hl & 8u) << 25);
+                    const uint32_t sh = ((hh & 1u) << 4) | ((hh & 2u) << 11) | ((hh & 4u) << 18) | ((hh & 8u) << 25);
+                    qx[k] = (q & 0x0f0f0f0fu) | sl;
+                    qx[k + 4] = ((q >> 4) & 0x0f0f0f0fu) | sh;
+                }
+#pragma unroll
+                for (int t = 0; t < NT; ++t) {
+                    const float2 ds = ds_sm[t * nb + ib];
+                    const uint4 y0 = *reinterpret_cast<const uint4 *>(qy_sm + size_t(t * nb + ib) * 8);
+                    const uint4 y1 = *reinterpret_cast<const uint4 *>(qy_sm + size_t(t * nb + ib) * 8 + 4);
+                    summs[t] = __fmaf_rn(xm, ds.y, summs[t]);
+                    const float scale = __fmul_rn(xd, ds.x);
+                    const uint32_t qy[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        acc[t][j] = __fmaf_rn(float(__dp4a(int(qx[j]), int(qy[j]), 0)), scale, acc[t][j]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < NT; ++t) out[int64_t(t) * out_stride + row0 + lane] = __fadd_rn(hsum8(acc[t]), summs[t]);
+        }
+        __syncwarp();
+    }
+}
+
+// raises the kernel's dynamic shared-memory limit once per device
+template <int NT>
+bool ensure_configured() {
+    static std::atomic<bool> configured[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    if (!configured[dev].load(std::memory_order_acquire)) {
+        if (cudaFuncSetAttribute(down_q5_1_q8_1_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemLimit)) !=
+            cudaSuccess) {
+            return false;
+        }
+        configured[dev].store(true, std::memory_order_release);
+    }
+    return true;
+}
+
+template <int NT>
+int32_t launch_nt(const uint32_t * w, int row_words, int nb, const uint8_t * act, int64_t act_stride, float * out,
+                  int64_t out_stride, int64_t r0, int64_t r1, cudaStream_t s) {
+    const size_t per_warp = size_t(32) * (row_words | 1) * 4, fixed = size_t(NT) * nb * 40;
+    if (fixed + per_warp > kSmemLimit) return FNB_REJECTED;  // n beyond ~11 000 columns
+    int warps = int((kSmemLimit - fixed) / per_warp);
+    warps = warps > kMaxWarps ? kMaxWarps : warps;
+    const size_t smem = fixed + size_t(warps) * per_warp;
+    if (!ensure_configured<NT>()) return FNB_LAUNCH_FAILED;
+    const int64_t n_tiles = (r1 - r0 + 31) / 32;
+    const int grid = grid_for((n_tiles + warps - 1) / warps, 16);
+    down_q5_1_q8_1_kernel<NT><<<grid, warps * 32, smem, s>>>(w, row_words, nb, act, act_stride, out, out_stride, r0, r1);
+    return launch_status();
+}
+
+}  // namespace
+
+bool expert_down_prepare_device() {
+    return ensure_configured<1>() && ensure_configured<2>() && ensure_configured<3>() && ensure_configured<4>() &&
+           ensure_configured<5>() && ensure_configured<6>() && ensure_configured<7>() && ensure_configured<8>();
+}
+
+}  // namespace fnb
+
+extern "C" int32_t fnb_expert_down_rows_q5_1(const void * w, int64_t row_bytes, int32_t n, const void * act,
+                                             int64_t act_stride, int32_t nt, float * out, int64_t out_stride, int64_t r0,
+                                             int64_t r1, void * stream) {
+    using namespace fnb;
+    if (!ok_ptr(w, 8) || !ok_ptr(act, 4) || !ok_ptr(out, 4)) return FNB_REJECTED;
+    if (n < 32 || n > 16384 || n % 32 != 0 || nt < 1 || nt > 64 || r0 < 0 || r1 <= r0 || r1 - r0 > INT32_MAX) return FNB_REJECTED;
+    const int nb = n / 32;
+    if (row_bytes < int64_t(nb) * 24 || row_bytes % 4 != 0 || row_bytes != int64_t(nb) * 24) return FNB_REJECTED;  // rows back to back
+    if (act_stride < int64_t(nb) * 36 || act_stride % 4 != 0 || out_stride < r1) return FNB_REJECTED;
+    const cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const uint32_t * ww = static_cast<const uint32_t *>(w);
+    const uint8_t * a = static_cast<const uint8_t *>(act);
+    for (int t0 = 0; t0 < nt; t0 += kMaxT) {  // windows above eight rows take further passes, as the reference's do
+        const int m = nt - t0 < kMaxT ? nt - t0 : kMaxT;
+        const uint8_t * at = a + int64_t(t0) * act_stride;
+        float * ot = out + int64_t(t0) * out_stride;
+        int32_t st;
+        switch (m) {
+            case 1: st = launch_nt<1>(ww, nb * 6, nb, at, act_stride, ot, out_stride, r0, r1, s); break;
+            case 2: st = launch_nt<2>(ww, nb * 6, nb, at, act_stride, ot, out_stride, r0, r1, s); break;
+            case 3: st = launch_nt<3>(ww, nb * 6, nb, at, act_stride, ot, out_stride, r0, r1, s); break;
+            case 4: st = launch_nt<4>(ww, nb * 6, nb, at, act_stride, ot, out_stride, r0, r1, s); break;
+            case 5: st = launch_nt<5>(ww, nb * 6, nb, at, act_stride, ot, out_stride, r0, r1, s); break;
+            case 6: st = launch_nt<6>(ww, nb * 6, nb, at, act_stride, ot, out_stride, r0, r1, s); break;
+            case 7: st = launch_nt<7>(ww, nb * 6, nb, at, act_stride, ot, out_stride, r0, r1, s); break;
+            default: st = launch_nt<8>(ww, nb * 6, nb, at, act_stride, ot, out_stride, r0, r1, s); break;
+        }
+        if (st != FNB_OK) return st;
+    }
+    return FNB_OK;
+}

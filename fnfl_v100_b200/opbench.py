@@ -17,7 +17,8 @@ from . import ops, synth
 from .chain import ChainConfig
 
 OPS = ("get_rows_q4_k", "get_rows_iq3_xxs", "rms_norm", "rms_norm_heads", "rope_kv", "swiglu_q8_1", "swiglu_act",
-       "rope_kv8", "quantize_q8_1", "rms_norm_q8_1", "embed_iq3_s", "kv_read_q8_0", "kv_read_kv8")
+       "rope_kv8", "quantize_q8_1", "rms_norm_q8_1", "embed_iq3_s", "kv_read_q8_0", "kv_read_kv8",
+       "expert_down_q5_1_nt1", "expert_down_q5_1_nt3", "expert_down_q5_1_nt8")
 
 
 def hbm_peak() -> float:
@@ -51,6 +52,16 @@ def make_case(op: str, T: int, dev, gen, c: ChainConfig):
         err = ops.new_err(dev)
         return (lambda: ops.embed_rows("iq3_s", table, tok, n_own, own=own, full=full, streams=streams, col0=0, err=err),
                 T * (n_own // 256 * 110 + 4 + (2 + n_streams) * n_own * 4))
+    if op.startswith("expert_down_q5_1"):
+        # a decode window of nt rows against 16 T Q5_1 weight rows of 640 columns (the reference's down width); random
+        # bytes with sane fp16 d / m stand in for weights, SwiGLU-shaped Q8_1 rows for the activations
+        nt, n, rows = int(op.rsplit("nt", 1)[1]), 640, 16 * T
+        w = torch.randint(0, 256, (rows, n // 32, 24), dtype=torch.uint8, device=dev, generator=gen)
+        w.view(torch.float16).reshape(rows, n // 32, 12)[..., 0:2] = 0.01
+        w = w.reshape(rows, n // 32 * 24)
+        act = ops.quantize_q8_1(N(gen, (nt, n), 0.5, dev))
+        out = torch.empty((nt, rows), dtype=torch.float32, device=dev)
+        return (lambda: ops.expert_down_rows_q5_1(w, act, n, out=out)), rows * (n // 32 * 24 + nt * 4) + nt * n // 32 * 36
     if op.startswith("kv_read"):
         # T consecutive cells of a cache the append has filled (random bytes stand in: every byte pattern is a valid cell)
         if op == "kv_read_q8_0":

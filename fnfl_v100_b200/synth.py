@@ -49,6 +49,15 @@ def normal(g: np.random.Generator, shape, scale: float = 1.0) -> np.ndarray:
     return (g.standard_normal(shape, dtype=np.float32) * np.float32(scale)).astype(np.float32)
 
 
+def q5_1_rows(g: np.random.Generator, rows: int, n: int, d_lo: float = 1e-3, d_hi: float = 1e-2) -> np.ndarray:
+    """Random valid ggml Q5_1 rows: uint8 [rows][n/32*24] (fp16 d ~ U(d_lo, d_hi), fp16 m ~ U(-0.1, 0.1), random bits)."""
+    nb = n // 32
+    t = g.integers(0, 256, (rows, nb, 24)).astype(np.uint8)
+    t[:, :, 0:2] = g.uniform(d_lo, d_hi, (rows, nb)).astype(np.float16).view(np.uint8).reshape(rows, nb, 2)
+    t[:, :, 2:4] = g.uniform(-0.1, 0.1, (rows, nb)).astype(np.float16).view(np.uint8).reshape(rows, nb, 2)
+    return t.reshape(rows, nb * 24)
+
+
 def norm_weight(g: np.random.Generator, cols: int) -> np.ndarray:
     """1 + N(0, 0.1), the RMSNorm weight of the first configuration."""
     return (1.0 + 0.1 * g.standard_normal(cols)).astype(np.float32)

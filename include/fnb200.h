@@ -281,6 +281,20 @@ typedef struct fnb_kv_read_args {
 int32_t fnb_kv_read_f32(const fnb_kv_read_args * args, void * stream);
 
 /*
+ * The consumer of the Q8_1 blocks fnb_swiglu_q8_1 writes: the routed experts' down mat-vec for a decode window,
+ * out[t * out_stride + r] = weight row r . act[t] for t < nt and r in [r0, r1).  Weights are ggml Q5_1 rows (n / 32
+ * blocks of 24 bytes: fp16 d, fp16 m, 32 high bits, 16 nibble bytes; value = d q + m), rows back to back
+ * (row_bytes = n / 32 * 24), row r at w + r row_bytes; activations are nt rows of n / 32 Q8_1 blocks, row t at
+ * act + t act_stride.  Replaces fn::experts::cpu::kq_down_rows for fmt q5_1 (fn/kernels/experts/cpu_kernels.h,
+ * cpu_kq_avx2.cpp:293-320, :382-394) and returns the SAME BITS: eight F32 accumulators per (row, t) in the AVX2
+ * kernel's lane order, one fused multiply-add per block and lane, the m x s side sum fused, hsum_float_8's reduction
+ * order.  nt <= 64 (passes of eight rows, as the reference's); w 8-byte, act and out 4-byte aligned; act_stride a multiple
+ * of 4; out_stride >= r1.  First call per device raises a kernel attribute (see fnb_prepare_device).
+ */
+int32_t fnb_expert_down_rows_q5_1(const void * w, int64_t row_bytes, int32_t n, const void * act, int64_t act_stride,
+                                  int32_t nt, float * out, int64_t out_stride, int64_t r0, int64_t r1, void * stream);
+
+/*
  * Host-side check before upload: 0 when every id is in [0, n_vocab), else 1 + the index of the first bad id.
  * Replaces fn::embed::check_tokens (fn/kernels/embed/embed.h:56).
  */

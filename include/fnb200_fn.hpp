@@ -74,6 +74,13 @@ inline bool glu_finish_q8_1(const float * gs, const float * us, int64_t n, int32
     return fnb_swiglu_q8_1(gs, us, blocks, glu_f32, n, cols, stream) == FNB_OK;
 }
 
+// the experts' down mat-vec over a decode window (fn::experts::cpu::kq_down_rows for fmt q5_1, same bits): out[t][r] =
+// Q5_1 weight row r . Q8_1 activation row t, r in [r0, r1); w rows back to back, act rows act_stride bytes apart
+inline bool down_rows_q5_1(const uint8_t * w, int32_t n, const void * act, int64_t act_stride, int32_t nt, float * out,
+                           int64_t out_stride, int64_t r0, int64_t r1, void * stream) {
+    return fnb_expert_down_rows_q5_1(w, int64_t(n / 32) * 24, n, act, act_stride, nt, out, out_stride, r0, r1, stream) == FNB_OK;
+}
+
 }  // namespace experts
 
 namespace qsa {  // per-head norm + NeoX partial RoPE + KV append: fn::qsa::qsp_kv and attend's prepare phase

@@ -420,3 +420,64 @@ void fnbo_kv8_quantize(const float * x, int64_t n, int8_t * codes, uint16_t * sc
         }
     }
 }
+
+/* ---- the routed experts' down mat-vec (fn/kernels/experts/cpu_kq_avx2.cpp) -------------------------------------------
+ * The AVX2 kernels keep one vector of eight F32 lanes per (row, t); lane j of a block's integer products is the sum of
+ * bytes 4 j .. 4 j + 3 (maddubs + madd, :133-139), converted exactly and fused-multiply-added with the block's scale
+ * product (:314, :338).  The scalar side term of Q5_1 (m x s, :310) is `summs += xm * s`, which the reference's flags
+ * (-mfma with GCC's default contraction) compile to one fused multiply-add; fmaf states that.  hsum_float_8 (:103-109)
+ * adds lane i + 4 to lane i, then lanes 2, 3 to 0, 1, then lane 1 to lane 0. */
+static float fnbo_hsum8(const float * a) {
+    const float r0 = a[4] + a[0], r1 = a[5] + a[1], r2 = a[6] + a[2], r3 = a[7] + a[3];
+    const float s0 = r0 + r2, s1 = r1 + r3;
+    return s0 + s1;
+}
+
+void fnbo_expert_down_rows(int32_t fmt, const uint8_t * w, int64_t row_bytes, int32_t n, const uint8_t * act,
+                           int64_t act_stride, int32_t nt, float * out, int64_t out_stride, int64_t r0, int64_t r1) {
+    const int nb = n / 32;
+    for (int64_t r = r0; r < r1; ++r) {
+        const uint8_t * row = w + r * row_bytes;
+        for (int t = 0; t < nt; ++t) {
+            const uint8_t * a = act + (int64_t) t * act_stride;
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            float summs = 0.0f;
+            for (int ib = 0; ib < nb; ++ib) {
+                int qx[32];
+                float xd, scale;
+                const int8_t * qy;
+                if (fmt == 0) { /* Q5_1 {d, m fp16; qh[4]; qs[16]} x Q8_1 {d, s fp16; qs[32]} */
+                    const uint8_t * b = row + ib * 24;
+                    uint16_t dh, mh, yd, ys;
+                    uint32_t qh;
+                    memcpy(&dh, b, 2), memcpy(&mh, b + 2, 2), memcpy(&qh, b + 4, 4);
+                    for (int i = 0; i < 16; ++i) {
+                        qx[i] = (b[8 + i] & 15) | (int) (((qh >> i) & 1u) << 4);
+                        qx[i + 16] = (b[8 + i] >> 4) | (int) (((qh >> (i + 16)) & 1u) << 4);
+                    }
+                    const uint8_t * y = a + ib * 36;
+                    memcpy(&yd, y, 2), memcpy(&ys, y + 2, 2);
+                    qy = (const int8_t *) (y + 4);
+                    xd = fnbo_f16_to_f32(dh);
+                    summs = fmaf(fnbo_f16_to_f32(mh), fnbo_f16_to_f32(ys), summs);
+                    scale = xd * fnbo_f16_to_f32(yd);
+                } else { /* Q8_0 {d fp16; qs[32]} x Q8_0 */
+                    const uint8_t * b = row + ib * 34;
+                    uint16_t dh, yd;
+                    memcpy(&dh, b, 2);
+                    for (int i = 0; i < 32; ++i) qx[i] = (int8_t) b[2 + i];
+                    const uint8_t * y = a + ib * 34;
+                    memcpy(&yd, y, 2);
+                    qy = (const int8_t *) (y + 2);
+                    scale = fnbo_f16_to_f32(dh) * fnbo_f16_to_f32(yd);
+                }
+                for (int j = 0; j < 8; ++j) {
+                    int s = 0;
+                    for (int i = 0; i < 4; ++i) s += qx[4 * j + i] * (int) qy[4 * j + i];
+                    acc[j] = fmaf((float) s, scale, acc[j]);
+                }
+            }
+            out[(int64_t) t * out_stride + r] = fnbo_hsum8(acc) + summs;
+        }
+    }
+}

@@ -79,6 +79,15 @@ void fnbo_swiglu_act(const float * gate, const float * up, int8_t * codes, float
 /* KV8: groups of 64, codes int8 [n], FP16 scale bits [n / 64] */
 void fnbo_kv8_quantize(const float * x, int64_t n, int8_t * codes, uint16_t * scales);
 
+/* The consumer of the 8-bit activations: the routed experts' down mat-vec, out[t][r] = weight row r . act[t], with
+ * ggml's Q5_1 weights against Q8_1 activations (fmt 0) or Q8_0 weights against Q8_0 activations (fmt 1).  Follows the
+ * reference's CPU kernels lane for lane (fn/kernels/experts/cpu_kq_avx2.cpp:293-344, :382-394): eight F32 accumulators
+ * per (row, t), accumulator j taking bytes 4 j .. 4 j + 3 of every block by one fused multiply-add per block, reduced
+ * once at the end in hsum_float_8's order (:103-109).  w: rows of n / 32 blocks, row r at w + r row_bytes; act: nt rows of
+ * n / 32 activation blocks, row t at act + t act_stride; out[t * out_stride + r] for r in [r0, r1). */
+void fnbo_expert_down_rows(int32_t fmt, const uint8_t * w, int64_t row_bytes, int32_t n, const uint8_t * act,
+                           int64_t act_stride, int32_t nt, float * out, int64_t out_stride, int64_t r0, int64_t r1);
+
 #ifdef __cplusplus
 }
 #endif

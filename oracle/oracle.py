@@ -265,6 +265,26 @@ def kv8_dequantize(codes: np.ndarray, scales: np.ndarray) -> np.ndarray:
     return (c * s).reshape(-1)
 
 
+DOWN_FMT = {"q5_1": (0, 24, Q8_1_BYTES), "q8_0": (1, Q8_0_BYTES, Q8_0_BYTES)}   # code, weight block, activation block
+
+
+def expert_down_rows(fmt: str, w: np.ndarray, act: np.ndarray, n: int, r0: int = 0, r1: int | None = None,
+                     use_ref: bool = False) -> np.ndarray:
+    """out[t][r] = weight row r . act[t]: w uint8 [rows][n/32 * weight block], act uint8 [nt][n/32 * activation block]
+    (Q8_1 blocks for "q5_1" weights, Q8_0 blocks for "q8_0").  use_ref: the reference's own AVX2 kernel."""
+    code, wb, ab = DOWN_FMT[fmt]
+    w, act = np.ascontiguousarray(w, np.uint8), np.ascontiguousarray(act, np.uint8)
+    rows, nt = w.shape[0], act.shape[0]
+    assert w.shape[1] == n // 32 * wb and act.shape[1] == n // 32 * ab
+    r1 = rows if r1 is None else r1
+    out = np.zeros((nt, rows), np.float32)
+    fn = ref().ref_kq_down_rows if use_ref else lib().fnbo_expert_down_rows
+    last = (C.c_int32(r0), C.c_int32(r1)) if use_ref else (C.c_int64(r0), C.c_int64(r1))
+    fn(C.c_int32(code), _p(w), C.c_int64(w.shape[1]), C.c_int32(n), _p(act), C.c_int64(act.shape[1]), C.c_int32(nt),
+       _p(out), C.c_int64(rows), *last)
+    return out
+
+
 def rope_kv_append(q, k, v, pos, *, n_rot: int, theta_scale: float, k_cache: np.ndarray, v_cache: np.ndarray,
                    cache_slots: int, slots=None, q_norm_w=None, k_norm_w=None, eps: float = 1e-6,
                    want_k_f32: bool = False, q_out: np.ndarray | None = None):

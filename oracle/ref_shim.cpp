@@ -14,6 +14,7 @@
 #include "fn/quant/decode.h"
 #include "fn/quant/formats.h"
 #include "fn/quant/kv_q8_ref.h"
+#include "fn/kernels/experts/cpu_kernels.h"
 #include "fn/quant/synth.h"
 
 extern "C" {
@@ -74,5 +75,15 @@ int32_t ref_synth_blocks(const char * fmt, uint64_t seed, int64_t n_blocks, uint
 
 uint16_t ref_f32_to_f16(float f) { return fn::quant::f32_to_f16(f); }
 float ref_f16_to_f32(uint16_t h) { return fn::quant::f16_to_f32(h); }
+
+// the routed experts' down rows (fn/kernels/experts/cpu_kq_avx2.cpp:382-394): fmt 0 = Q5_1 x Q8_1, 1 = Q8_0 x Q8_0
+void ref_kq_down_rows(int32_t f, const uint8_t * w, int64_t row_bytes, int32_t n, const uint8_t * act, int64_t act_stride,
+                      int32_t nt, float * out, int64_t out_stride, int32_t r0, int32_t r1) {
+    const void * a[64];
+    float * o[64];
+    for (int t = 0; t < nt && t < 64; ++t) a[t] = act + int64_t(t) * act_stride, o[t] = out + int64_t(t) * out_stride;
+    fn::experts::cpu::kq_down_rows(f == 0 ? fn::experts::fmt::q5_1 : fn::experts::fmt::q8_0, w, size_t(row_bytes), n, a, nt,
+                                   o, r0, r1);
+}
 
 }  // extern "C"

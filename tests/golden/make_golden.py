@@ -93,9 +93,28 @@ def model_file() -> None:
     print("model_tiny.gguf", os.path.getsize(path), "bytes")
 
 
+def down_rows() -> None:
+    """The reference's own AVX2 down mat-vec (fn::experts::cpu::kq_down_rows) on seeded weights and activations."""
+    from fnfl_v100_b200 import synth
+    g = synth.rng(0x4d45)
+    rec = {}
+    for fmt, n, rows, nt in (("q5_1", 640, 67, 5), ("q5_1", 64, 9, 11), ("q8_0", 640, 67, 5)):
+        x = synth.normal(g, (nt, n), 2.0)
+        if fmt == "q5_1":
+            w, act = synth.q5_1_rows(g, rows, n), O.quantize_q8_1(x).reshape(nt, -1)
+        else:
+            w, act = synth.q8_0_table(g, rows, n), O.quantize_q8_0(x).reshape(nt, -1)
+        key = f"{fmt}_{n}"
+        rec[key + "|w"], rec[key + "|act"] = w, act
+        rec[key + "|out"] = O.expert_down_rows(fmt, w, act, n, use_ref=True)
+    np.savez_compressed(os.path.join(HERE, "down_rows.npz"), **rec)
+    print("down_rows.npz", os.path.getsize(os.path.join(HERE, "down_rows.npz")), "bytes")
+
+
 def main() -> None:
     O.build(with_ref=True)
     model_file()
+    down_rows()
     r = O.ref()
     x = stress_blocks()
     n = x.shape[0]

@@ -73,6 +73,12 @@ def test_rejections_enqueue_nothing(lib):
     assert lib.fnb_swiglu_act(A16, A16, A16, None, None, 8, 512, None) == R
     assert lib.fnb_quantize_q8_1(A16, A16, -3, 512, None) == R
     assert lib.fnb_quantize_q8_0(None, A16, 3, 512, None) == R
+    # experts' down rows: n not a multiple of 32, rows not back to back, window of 0 or 65 rows, r1 <= r0, short out rows
+    ok = (A16, 480, 640, A16, 720, 3, A16, 2560, 0, 2560, None)
+    for i, bad in ((2, 650), (1, 484), (5, 0), (5, 65), (9, 0), (7, 100), (0, None), (3, ODD + 1), (4, 718)):
+        a = list(ok)
+        a[i] = bad
+        assert lib.fnb_expert_down_rows_q5_1(*a) == R, (i, bad)
     # cache read-back: head_dim outside {64, 128, 256}, a span past the cache, missing pointers
     ka = _lib.KvReadArgs(A16, None, None, A16, None, 8, 64, 0, 2, 256)
     for field, bad in (("head_dim", 96), ("cell0", 60), ("rows", 0), ("out", None), ("cache", ODD), ("n_kv_heads", 0)):

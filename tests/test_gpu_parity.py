@@ -301,6 +301,37 @@ def test_append_then_read_back(dev, oracle, fmt, hd, nkv):
     assert np.array_equal(bits(span), bits(full[lo:lo + 16]))
 
 
+# ---- the consumer of the Q8_1 blocks: the experts' down mat-vec ---------------------------------------------------------
+
+def test_expert_down_rows_equal_the_reference_avx2_kernel_on_golden(dev):
+    gold = np.load(os.path.join(GOLD, "down_rows.npz"))
+    for key in ("q5_1_640", "q5_1_64"):
+        n = int(key.rsplit("_", 1)[1])
+        w, act, want = gold[key + "|w"], gold[key + "|act"], gold[key + "|out"]
+        got = ops.expert_down_rows_q5_1(to_dev(w, dev), to_dev(act, dev), n).cpu().numpy()
+        assert np.array_equal(bits(got), bits(want)), key
+
+
+@pytest.mark.parametrize("n,rows,nt", [(640, 2560, 1), (640, 2560, 3), (640, 1000, 8), (512, 333, 5), (32, 40, 2),
+                                       (2048, 129, 13)])
+def test_expert_down_rows_bit_exact(dev, oracle, n, rows, nt):
+    """SwiGLU's own Q8_1 output as the activations (the path's real hand-over), Q5_1 weights: every bit of the oracle's
+    lane-for-lane restatement; rows outside [r0, r1) stay untouched."""
+    g = synth.rng(31)
+    gate, up = synth.normal(g, (nt, n), 0.5), synth.normal(g, (nt, n), 0.5)
+    act = ops.swiglu_q8_1(to_dev(gate, dev), to_dev(up, dev))
+    assert np.array_equal(act.cpu().numpy(), oracle.swiglu_q8_1(gate, up))
+    w = synth.q5_1_rows(g, rows, n)
+    r0, r1 = 5, rows - 3
+    out = torch.full((nt, rows), float("nan"), dtype=torch.float32, device=dev)
+    ops.expert_down_rows_q5_1(to_dev(w, dev), act, n, r0=r0, r1=r1, out=out)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    want = oracle.expert_down_rows("q5_1", w, act.cpu().numpy(), n, r0=r0, r1=r1)
+    assert np.array_equal(bits(got[:, r0:r1]), bits(want[:, r0:r1]))
+    assert np.isnan(got[:, :r0]).all() and np.isnan(got[:, r1:]).all()
+
+
 # ---- get_rows ----------------------------------------------------------------------------------------------------------
 
 @pytest.mark.parametrize("fmt,cols,vocab,rows", [

@@ -124,3 +124,16 @@ def test_oracle_equals_live_reference_build(oracle):
         b = np.empty_like(a)
         fn(oracle._p(t), oracle._p(b), C.c_int64(a.size))
         assert np.array_equal(a.view(np.uint32), b.view(np.uint32)), fmt
+
+
+def test_expert_down_rows_match_the_reference_avx2_kernel(oracle):
+    """tests/golden/down_rows.npz: outputs of the reference's own kq_down_rows (compiled with its flags); the scalar
+    restatement reproduces every bit, for Q5_1 x Q8_1 and Q8_0 x Q8_0, also on a sub-range of rows."""
+    gold = np.load(os.path.join(GOLD, "down_rows.npz"))
+    for key in sorted({k.split("|")[0] for k in gold.files}):
+        fmt, n = key.rsplit("_", 1)[0], int(key.rsplit("_", 1)[1])
+        w, act, want = gold[key + "|w"], gold[key + "|act"], gold[key + "|out"]
+        got = oracle.expert_down_rows(fmt, w, act, n)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), key
+        part = oracle.expert_down_rows(fmt, w, act, n, r0=3, r1=8)
+        assert np.array_equal(part[:, 3:8].view(np.uint32), want[:, 3:8].view(np.uint32)) and not part[:, :3].any()
