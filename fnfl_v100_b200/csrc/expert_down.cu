@@ -21,8 +21,9 @@ namespace {
 
 constexpr int kMaxWarps = 4;  // warps per CTA (fewer when 32 staged rows per warp would not fit in shared memory)
 constexpr int kMaxT = 8;      // rows of a window per pass over the weights (the reference's maxt)
-constexpr int kStageUnroll = 6;  // 64-bit loads a lane has in flight while staging a tile
 constexpr size_t kSmemLimit = 200 * 1024;
+
+__device__ __forceinline__ uint32_t smem_addr(const void * p) { return uint32_t(__cvta_generic_to_shared(p)); }
 
 __device__ __forceinline__ float hsum8(const float (&a)[8]) {  // hsum_float_8's order
     const float r0 = __fadd_rn(a[4], a[0]), r1 = __fadd_rn(a[5], a[1]), r2 = __fadd_rn(a[6], a[2]), r3 = __fadd_rn(a[7], a[3]);
@@ -36,7 +37,9 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
                           int64_t act_stride, float * __restrict__ out, int64_t out_stride, int64_t r0, int64_t r1) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int kWarps = blockDim.x >> 5;
-    const int pad_words = row_words | 1;                       // odd stride: lane = row reads hit 32 banks
+    // row stride in shared memory: even (8-byte copies land aligned) and 2 mod 4, so lane = row reads of one word are
+    // at most two deep on a bank
+    const int pad_words = row_words + (row_words % 4 == 0 ? 2 : 0);
     // activations first (16-byte aligned vectors), then the warps' staged rows
     uint32_t * qy_sm = reinterpret_cast<uint32_t *>(smem);                     // [NT][nb][8] the activations' code words
     float2 * ds_sm = reinterpret_cast<float2 *>(qy_sm + size_t(NT) * nb * 8);  // [NT][nb] {d, s} as F32
@@ -58,30 +61,22 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
     for (int64_t tile = int64_t(blockIdx.x) * kWarps + wid; tile < n_tiles; tile += int64_t(gridDim.x) * kWarps) {
         const int64_t row0 = r0 + tile * 32;
         const int live = int(r1 - row0 < 32 ? r1 - row0 : 32);
-        // stage `live` consecutive rows: coalesced 64-bit loads, several in flight per lane (a row is a whole number
-        // of 8-byte pairs: 24-byte blocks); pair g of the tile belongs to row g / (row_words / 2)
+        // stage `live` consecutive rows with 8-byte asynchronous copies straight into shared memory (a row is a whole
+        // number of 8-byte pairs: 24-byte blocks): every copy of the tile is in flight at once, none through registers.
+        // Staging through registers, six loads at a time, cost ten memory round trips per tile and held the kernel at
+        // 35 % of the roofline.
         {
             const uint2 * src = reinterpret_cast<const uint2 *>(w + row0 * row_words);
             const uint32_t rp = uint32_t(row_words) >> 1;
             const uint32_t total = uint32_t(live) * rp;
             const uint32_t inv = uint32_t((0x100000000ull + rp - 1) / rp);  // g / rp by multiply-high (g < 2^20)
-            for (uint32_t base = 0; base < total; base += 32 * kStageUnroll) {
-                uint2 v[kStageUnroll];
-#pragma unroll
-                for (int u = 0; u < kStageUnroll; ++u) {
-                    const uint32_t g = base + 32 * u + lane;
-                    v[u] = g < total ? __ldg(src + g) : make_uint2(0u, 0u);
-                }
-#pragma unroll
-                for (int u = 0; u < kStageUnroll; ++u) {
-                    const uint32_t g = base + 32 * u + lane;
-                    if (g < total) {
-                        const uint32_t row = __umulhi(g, inv), col = 2 * (g - row * rp);
-                        mine[row * pad_words + col] = v[u].x;
-                        mine[row * pad_words + col + 1] = v[u].y;
-                    }
-                }
+            const uint32_t base_sm = smem_addr(mine);
+            for (uint32_t g = lane; g < total; g += 32) {
+                const uint32_t row = __umulhi(g, inv), col = 2 * (g - row * rp);
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(base_sm + 4 * (row * pad_words + col)), "l"(src + g)
+                             : "memory");
             }
+            asm volatile("cp.async.wait_all;" ::: "memory");
         }
         __syncwarp();
         if (lane < live) {
@@ -104,10 +99,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const uint32_t q = b[2 + k];
-                    const uint32_t hl = (qh >> (4 * k)) & 15u, hh = (qh >> (16 + 4 * k)) & 15u;
-                    // spread four bits to bit 4 of four bytes: b0 -> bit 4, b1 -> bit 12, b2 -> bit 20, b3 -> bit 28
-                    const uint32_t sl = ((hl & 1u) << 4) | ((hl & 2u) << 11) | ((hl & 4u) << 18) | ((hl & 8u) << 25);
-                    const uint32_t sh = ((hh & 1u) << 4) | ((hh & 2u) << 11) | ((hh & 4u) << 18) | ((hh & 8u) << 25);
+                    // four bits of qh to bit 4 of four bytes: bit i of the nibble times 0x02040810 lands on bit
+                    // 4 + 7 i + i = 4 + 8 i (no two partial products share a bit below 2^32), the mask keeps those
+                    const uint32_t sl = (((qh >> (4 * k)) & 15u) * 0x02040810u) & 0x10101010u;
+                    const uint32_t sh = (((qh >> (16 + 4 * k)) & 15u) * 0x02040810u) & 0x10101010u;
                     qx[k] = (q & 0x0f0f0f0fu) | sl;
                     qx[k + 4] = ((q >> 4) & 0x0f0f0f0fu) | sh;
                 }
@@ -119,9 +114,17 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
                     summs[t] = __fmaf_rn(xm, ds.y, summs[t]);
                     const float scale = __fmul_rn(xd, ds.x);
                     const uint32_t qy[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
+                    // The integer sums become floats without a conversion instruction: the dot product accumulates onto
+                    // the bits of 1.5 x 2^23, which makes the word the float 12582912 + sum (|sum| < 2^22), and one exact
+                    // subtraction leaves float(sum).  Conversions and dp4a share the half-rate integer pipe, which is
+                    // what bounded the kernel per window row; the subtraction and the fused multiply-add run two
+                    // accumulators per instruction on the FP32 pipe.
+                    const f32x2 scale2 = pk(scale, scale), magic2 = pk(-12582912.0f, -12582912.0f);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        acc[t][j] = __fmaf_rn(float(__dp4a(int(qx[j]), int(qy[j]), 0)), scale, acc[t][j]);
+                    for (int j = 0; j < 8; j += 2) {
+                        const f32x2 biased = pk(__int_as_float(__dp4a(int(qx[j]), int(qy[j]), 0x4B400000)),
+                                                __int_as_float(__dp4a(int(qx[j + 1]), int(qy[j + 1]), 0x4B400000)));
+                        unpk(fma2(add2(biased, magic2), scale2, pk(acc[t][j], acc[t][j + 1])), acc[t][j], acc[t][j + 1]);
                     }
                 }
             }
@@ -151,7 +154,7 @@ bool ensure_configured() {
 template <int NT>
 int32_t launch_nt(const uint32_t * w, int row_words, int nb, const uint8_t * act, int64_t act_stride, float * out,
                   int64_t out_stride, int64_t r0, int64_t r1, cudaStream_t s) {
-    const size_t per_warp = size_t(32) * (row_words | 1) * 4, fixed = size_t(NT) * nb * 40;
+    const size_t per_warp = size_t(32) * (row_words + (row_words % 4 == 0 ? 2 : 0)) * 4, fixed = size_t(NT) * nb * 40;
     if (fixed + per_warp > kSmemLimit) return FNB_REJECTED;  // n beyond ~11 000 columns
     int warps = int((kSmemLimit - fixed) / per_warp);
     warps = warps > kMaxWarps ? kMaxWarps : warps;
