@@ -41,17 +41,19 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
     // at most two deep on a bank
     const int pad_words = row_words + (row_words % 4 == 0 ? 2 : 0);
     // activations first (16-byte aligned vectors), then the warps' staged rows
-    uint32_t * qy_sm = reinterpret_cast<uint32_t *>(smem);                     // [NT][nb][8] the activations' code words
-    float2 * ds_sm = reinterpret_cast<float2 *>(qy_sm + size_t(NT) * nb * 8);  // [NT][nb] {d, s} as F32
+    // (block-major, so that within a block the window rows sit at compile-time offsets)
+    uint32_t * qy_sm = reinterpret_cast<uint32_t *>(smem);                     // [nb][NT][8] the activations' code words
+    float2 * ds_sm = reinterpret_cast<float2 *>(qy_sm + size_t(NT) * nb * 8);  // [nb][NT] {d, s} as F32
     uint32_t * rows_sm = reinterpret_cast<uint32_t *>(ds_sm + size_t(NT) * nb);  // [kWarps][32][pad_words]
 
     for (int i = threadIdx.x; i < NT * nb; i += blockDim.x) {
         const int t = i / nb, ib = i - t * nb;
         const uint8_t * y = act + int64_t(t) * act_stride + size_t(ib) * 36;  // 4-byte aligned: {fp16 d, fp16 s, 32 codes}
         const uint32_t hdr = __ldg(reinterpret_cast<const uint32_t *>(y));
-        ds_sm[i] = make_float2(f16_bits_to_f32(uint16_t(hdr & 0xffffu)), f16_bits_to_f32(uint16_t(hdr >> 16)));
+        const int o = ib * NT + t;
+        ds_sm[o] = make_float2(f16_bits_to_f32(uint16_t(hdr & 0xffffu)), f16_bits_to_f32(uint16_t(hdr >> 16)));
 #pragma unroll
-        for (int k = 0; k < 8; ++k) qy_sm[size_t(i) * 8 + k] = __ldg(reinterpret_cast<const uint32_t *>(y + 4) + k);
+        for (int k = 0; k < 8; ++k) qy_sm[size_t(o) * 8 + k] = __ldg(reinterpret_cast<const uint32_t *>(y + 4) + k);
     }
     __syncthreads();
 
@@ -89,6 +91,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc[t][j] = 0.0f;
             }
+#pragma unroll 2
             for (int ib = 0; ib < nb; ++ib) {
                 const uint32_t * b = my_row + 6 * ib;
                 const uint32_t dm = b[0], qh = b[1];
@@ -108,9 +111,9 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
                 }
 #pragma unroll
                 for (int t = 0; t < NT; ++t) {
-                    const float2 ds = ds_sm[t * nb + ib];
-                    const uint4 y0 = *reinterpret_cast<const uint4 *>(qy_sm + size_t(t * nb + ib) * 8);
-                    const uint4 y1 = *reinterpret_cast<const uint4 *>(qy_sm + size_t(t * nb + ib) * 8 + 4);
+                    const float2 ds = ds_sm[ib * NT + t];
+                    const uint4 y0 = *reinterpret_cast<const uint4 *>(qy_sm + size_t(ib * NT + t) * 8);
+                    const uint4 y1 = *reinterpret_cast<const uint4 *>(qy_sm + size_t(ib * NT + t) * 8 + 4);
                     summs[t] = __fmaf_rn(xm, ds.y, summs[t]);
                     const float scale = __fmul_rn(xd, ds.x);
                     const uint32_t qy[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
