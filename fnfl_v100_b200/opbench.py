@@ -18,7 +18,7 @@ from .chain import ChainConfig
 
 OPS = ("get_rows_q4_k", "get_rows_iq3_xxs", "rms_norm", "rms_norm_heads", "rope_kv", "swiglu_q8_1", "swiglu_act",
        "rope_kv8", "quantize_q8_1", "rms_norm_q8_1", "embed_iq3_s", "kv_read_q8_0", "kv_read_kv8",
-       "expert_down_q5_1_nt1", "expert_down_q5_1_nt3", "expert_down_q5_1_nt8")
+       "expert_down_q5_1_nt1", "expert_down_q5_1_nt3", "expert_down_q5_1_nt8", "expert_down_q8_0_nt1", "expert_down_q8_0_nt3")
 
 
 def hbm_peak() -> float:
@@ -62,6 +62,14 @@ def make_case(op: str, T: int, dev, gen, c: ChainConfig):
         act = ops.quantize_q8_1(N(gen, (nt, n), 0.5, dev))
         out = torch.empty((nt, rows), dtype=torch.float32, device=dev)
         return (lambda: ops.expert_down_rows_q5_1(w, act, n, out=out)), rows * (n // 32 * 24 + nt * 4) + nt * n // 32 * 36
+    if op.startswith("expert_down_q8_0"):
+        nt, n, rows = int(op.rsplit("nt", 1)[1]), 640, 16 * T
+        w = torch.randint(0, 256, (rows, n // 32, 34), dtype=torch.uint8, device=dev, generator=gen)
+        w.view(torch.float16).reshape(rows, n // 32, 17)[..., 0] = 0.01
+        w = w.reshape(rows, n // 32 * 34)
+        act = ops.quantize_q8_0(N(gen, (nt, n), 0.5, dev)).reshape(nt, -1)
+        out = torch.empty((nt, rows), dtype=torch.float32, device=dev)
+        return (lambda: ops.expert_down_rows("q8_0", w, act, n, out=out)), rows * (n // 32 * 34 + nt * 4) + nt * n // 32 * 34
     if op.startswith("kv_read"):
         # T consecutive cells of a cache the append has filled (random bytes stand in: every byte pattern is a valid cell)
         if op == "kv_read_q8_0":

@@ -311,10 +311,11 @@ def embed_supply(fmt: str, table, tok, n_own: int, src, row0: int, *, own=None, 
     _check(_lib.lib().fnb_embed_supply(C.byref(a), _ptr(src), row0, src.shape[0], _stream()), "embed_supply")
 
 
-def expert_down_rows_q5_1(w: torch.Tensor, act: torch.Tensor, n: int, r0: int = 0, r1: int | None = None,
-                          out: torch.Tensor | None = None) -> torch.Tensor:
-    """out[t][r] = Q5_1 weight row r . Q8_1 activation row t (fn::experts::cpu::kq_down_rows for q5_1, bit for bit).
-    w uint8 [rows][n/32*24], act uint8 [nt][n/32*36]; returns F32 [nt][rows] (columns r0 .. r1 - 1 written)."""
+def expert_down_rows(fmt: str, w: torch.Tensor, act: torch.Tensor, n: int, r0: int = 0, r1: int | None = None,
+                     out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t][r] = weight row r . activation row t (fn::experts::cpu::kq_down_rows, bit for bit).  fmt "q5_1": Q5_1
+    weights uint8 [rows][n/32*24] against Q8_1 activations uint8 [nt][n/32*36]; fmt "q8_0": Q8_0 weights
+    [rows][n/32*34] against Q8_0 activations [nt][n/32*34].  Returns F32 [nt][rows] (columns r0 .. r1 - 1 written)."""
     _dev(w, torch.uint8, "w")
     _dev(act, torch.uint8, "act")
     rows, nt = w.shape[0], act.shape[0]
@@ -322,9 +323,14 @@ def expert_down_rows_q5_1(w: torch.Tensor, act: torch.Tensor, n: int, r0: int = 
     if out is None:
         out = torch.zeros((nt, rows), dtype=torch.float32, device=w.device)
     _dev(out, torch.float32, "out")
-    _check(_lib.lib().fnb_expert_down_rows_q5_1(_ptr(w), w.shape[1], n, _ptr(act), act.shape[1], nt, _ptr(out),
-                                                out.shape[1], r0, r1, _stream()), "expert_down_rows_q5_1")
+    fn = {"q5_1": _lib.lib().fnb_expert_down_rows_q5_1, "q8_0": _lib.lib().fnb_expert_down_rows_q8_0}[fmt]
+    _check(fn(_ptr(w), w.shape[1], n, _ptr(act), act.shape[1], nt, _ptr(out), out.shape[1], r0, r1, _stream()),
+           "expert_down_rows_" + fmt)
     return out
+
+
+def expert_down_rows_q5_1(w, act, n, r0=0, r1=None, out=None):
+    return expert_down_rows("q5_1", w, act, n, r0, r1, out)
 
 
 def prepare_device() -> None:

@@ -295,6 +295,15 @@ int32_t fnb_expert_down_rows_q5_1(const void * w, int64_t row_bytes, int32_t n, 
                                   int32_t nt, float * out, int64_t out_stride, int64_t r0, int64_t r1, void * stream);
 
 /*
+ * The same mat-vec with ggml Q8_0 weights (34-byte blocks) against Q8_0 activations (fnb_quantize_q8_0 /
+ * fnb_rms_norm_q8_0 blocks): fn::experts::cpu::kq_down_rows for fmt q8_0 (cpu_kq_avx2.cpp:322-344), same bits (eight
+ * accumulators, one fused multiply-add per block and lane with the product of the two block scales, no side sum).
+ * n a multiple of 128 (rows are whole 8-byte pairs); row_bytes = n / 32 * 34; w 8-byte, act 2-byte aligned.
+ */
+int32_t fnb_expert_down_rows_q8_0(const void * w, int64_t row_bytes, int32_t n, const void * act, int64_t act_stride,
+                                  int32_t nt, float * out, int64_t out_stride, int64_t r0, int64_t r1, void * stream);
+
+/*
  * Host-side check before upload: 0 when every id is in [0, n_vocab), else 1 + the index of the first bad id.
  * Replaces fn::embed::check_tokens (fn/kernels/embed/embed.h:56).
  */

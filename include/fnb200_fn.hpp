@@ -81,6 +81,12 @@ inline bool down_rows_q5_1(const uint8_t * w, int32_t n, const void * act, int64
     return fnb_expert_down_rows_q5_1(w, int64_t(n / 32) * 24, n, act, act_stride, nt, out, out_stride, r0, r1, stream) == FNB_OK;
 }
 
+// the same with Q8_0 weights against Q8_0 activations (n a multiple of 128)
+inline bool down_rows_q8_0(const uint8_t * w, int32_t n, const void * act, int64_t act_stride, int32_t nt, float * out,
+                           int64_t out_stride, int64_t r0, int64_t r1, void * stream) {
+    return fnb_expert_down_rows_q8_0(w, int64_t(n / 32) * 34, n, act, act_stride, nt, out, out_stride, r0, r1, stream) == FNB_OK;
+}
+
 }  // namespace experts
 
 namespace qsa {  // per-head norm + NeoX partial RoPE + KV append: fn::qsa::qsp_kv and attend's prepare phase

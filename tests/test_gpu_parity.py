@@ -305,10 +305,10 @@ def test_append_then_read_back(dev, oracle, fmt, hd, nkv):
 
 def test_expert_down_rows_equal_the_reference_avx2_kernel_on_golden(dev):
     gold = np.load(os.path.join(GOLD, "down_rows.npz"))
-    for key in ("q5_1_640", "q5_1_64"):
-        n = int(key.rsplit("_", 1)[1])
+    for key in ("q5_1_640", "q5_1_64", "q8_0_640"):
+        fmt, n = key.rsplit("_", 1)[0], int(key.rsplit("_", 1)[1])
         w, act, want = gold[key + "|w"], gold[key + "|act"], gold[key + "|out"]
-        got = ops.expert_down_rows_q5_1(to_dev(w, dev), to_dev(act, dev), n).cpu().numpy()
+        got = ops.expert_down_rows(fmt, to_dev(w, dev), to_dev(act, dev), n).cpu().numpy()
         assert np.array_equal(bits(got), bits(want)), key
 
 
@@ -330,6 +330,19 @@ def test_expert_down_rows_bit_exact(dev, oracle, n, rows, nt):
     want = oracle.expert_down_rows("q5_1", w, act.cpu().numpy(), n, r0=r0, r1=r1)
     assert np.array_equal(bits(got[:, r0:r1]), bits(want[:, r0:r1]))
     assert np.isnan(got[:, :r0]).all() and np.isnan(got[:, r1:]).all()
+
+
+@pytest.mark.parametrize("n,rows,nt", [(640, 2560, 1), (640, 777, 5), (128, 40, 2), (2048, 129, 11)])
+def test_expert_down_rows_q8_0_bit_exact(dev, oracle, n, rows, nt):
+    """Q8_0 weights against the Q8_0 blocks fnb_quantize_q8_0 writes."""
+    g = synth.rng(32)
+    x = synth.normal(g, (nt, n), 2.0)
+    act = ops.quantize_q8_0(to_dev(x, dev))
+    assert np.array_equal(act.cpu().numpy().reshape(-1), oracle.quantize_q8_0(x).reshape(-1))
+    w = synth.q8_0_table(g, rows, n)
+    got = ops.expert_down_rows("q8_0", to_dev(w, dev), act, n).cpu().numpy()
+    want = oracle.expert_down_rows("q8_0", w, act.cpu().numpy().reshape(nt, -1), n)
+    assert np.array_equal(bits(got), bits(want))
 
 
 # ---- get_rows ----------------------------------------------------------------------------------------------------------
