@@ -18,7 +18,7 @@ from .chain import ChainConfig
 
 OPS = ("get_rows_q4_k", "get_rows_iq3_xxs", "rms_norm", "rms_norm_heads", "rope_kv", "swiglu_q8_1", "swiglu_act",
        "rope_kv8", "quantize_q8_1", "rms_norm_q8_1", "embed_iq3_s", "kv_read_q8_0", "kv_read_kv8",
-       "expert_down_q5_1_nt1", "expert_down_q5_1_nt3", "expert_down_q5_1_nt8", "expert_down_q8_0_nt1", "expert_down_q8_0_nt3")
+       "expert_down_q5_1_nt1", "expert_down_q5_1_nt3", "expert_down_q5_1_nt8", "expert_down_q8_0_nt1", "expert_down_q8_0_nt3", "quantize_q8_k")
 
 
 def hbm_peak() -> float:
@@ -70,6 +70,9 @@ def make_case(op: str, T: int, dev, gen, c: ChainConfig):
         act = ops.quantize_q8_0(N(gen, (nt, n), 0.5, dev)).reshape(nt, -1)
         out = torch.empty((nt, rows), dtype=torch.float32, device=dev)
         return (lambda: ops.expert_down_rows("q8_0", w, act, n, out=out)), rows * (n // 32 * 34 + nt * 4) + nt * n // 32 * 34
+    if op == "quantize_q8_k":
+        x = N(gen, (T, 2560), 1.0, dev)                      # the reference's d_model
+        return (lambda: ops.quantize_q8_k(x)), T * 2560 * 4 + T * 2560 // 256 * 292
     if op.startswith("kv_read"):
         # T consecutive cells of a cache the append has filled (random bytes stand in: every byte pattern is a valid cell)
         if op == "kv_read_q8_0":

@@ -153,6 +153,15 @@ def quantize_q8_0(x: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def quantize_q8_k(x: torch.Tensor) -> torch.Tensor:
+    """ggml Q8_K blocks (fn::experts::cpu::quantize_q8_k): uint8 [rows][cols/256*292]."""
+    _dev(x, torch.float32, "x")
+    rows, cols = _rows_cols(x)
+    out = torch.empty((rows, cols // 256 * 292), dtype=torch.uint8, device=x.device)
+    _check(_lib.lib().fnb_quantize_q8_k(_ptr(x), _ptr(out), rows, cols, _stream()), "quantize_q8_k")
+    return out
+
+
 def act_quantize(x: torch.Tensor):
     """fn::act::quantize: F32 [rows][k] -> (codes int8 [rows][k], scales F32 [rows][k/32][2])."""
     _dev(x, torch.float32, "x")

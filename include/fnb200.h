@@ -281,6 +281,16 @@ typedef struct fnb_kv_read_args {
 int32_t fnb_kv_read_f32(const fnb_kv_read_args * args, void * stream);
 
 /*
+ * F32 rows to ggml Q8_K blocks (292 bytes per 256 values: F32 d, 256 int8 codes, 16 int16 sums of 16 codes), the
+ * activation format the routed experts' gate / up mat-vec reads on the reference's CPU tier.  Replaces
+ * fn::experts::cpu::quantize_q8_k (fn/kernels/experts/cpu_kernels.h; cpu_iq_avx2.cpp:583-646) and ggml's
+ * quantize_row_q8_K_ref (ggml/src/ggml-quants.c:2844-2881), same bytes: the value of largest magnitude (the first one
+ * on ties) maps to -127, codes nearest-even capped at 127, d = 1 / iscale.  An all-zero block comes out as zeros,
+ * sums included.  cols a multiple of 256; x 16-byte, out 4-byte aligned; out [rows][cols / 256] blocks.
+ */
+int32_t fnb_quantize_q8_k(const float * x, void * out_q8_k, int64_t rows, int32_t cols, void * stream);
+
+/*
  * The consumer of the Q8_1 blocks fnb_swiglu_q8_1 writes: the routed experts' down mat-vec for a decode window,
  * out[t * out_stride + r] = weight row r . act[t] for t < nt and r in [r0, r1).  Weights are ggml Q5_1 rows (n / 32
  * blocks of 24 bytes: fp16 d, fp16 m, 32 high bits, 16 nibble bytes; value = d q + m), rows back to back

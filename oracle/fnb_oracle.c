@@ -481,3 +481,42 @@ void fnbo_expert_down_rows(int32_t fmt, const uint8_t * w, int64_t row_bytes, in
         }
     }
 }
+
+/* ---- Q8_K (ggml/src/ggml-quants.c:2844-2881; nearest_int :559-565) ---------------------------------------------------*/
+void fnbo_quantize_row_q8_k(const float * x, void * vy, int64_t k) {
+    uint8_t * y = (uint8_t *) vy;
+    for (int64_t i = 0; i < k / 256; ++i, x += 256, y += 292) {
+        float max = 0.0f, amax = 0.0f;
+        for (int j = 0; j < 256; ++j) {
+            const float ax = fabsf(x[j]);
+            if (ax > amax) amax = ax, max = x[j];
+        }
+        int8_t * qs = (int8_t *) (y + 4);
+        int16_t bsums[16];
+        if (!amax) {
+            const float zero = 0.0f;
+            memcpy(y, &zero, 4);
+            memset(qs, 0, 256);
+            /* the reference leaves bsums untouched here; the caller's buffer decides them.  Written as zeros so that the
+             * block is a function of its input. */
+            memset(y + 260, 0, 32);
+            continue;
+        }
+        const float iscale = -127.0f / max;
+        for (int j = 0; j < 256; ++j) {
+            const float val = iscale * x[j] + 12582912.0f; /* nearest_int: the product rounds, then the sum */
+            int32_t b;
+            memcpy(&b, &val, 4);
+            const int v = (b & 0x007fffff) - 0x00400000;
+            qs[j] = (int8_t) (v < 127 ? v : 127);
+        }
+        for (int j = 0; j < 16; ++j) {
+            int sum = 0;
+            for (int ii = 0; ii < 16; ++ii) sum += qs[16 * j + ii];
+            bsums[j] = (int16_t) sum;
+        }
+        memcpy(y + 260, bsums, 32);
+        const float d = 1.0f / iscale;
+        memcpy(y, &d, 4);
+    }
+}

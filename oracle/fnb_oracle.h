@@ -79,6 +79,12 @@ void fnbo_swiglu_act(const float * gate, const float * up, int8_t * codes, float
 /* KV8: groups of 64, codes int8 [n], FP16 scale bits [n / 64] */
 void fnbo_kv8_quantize(const float * x, int64_t n, int8_t * codes, uint16_t * scales);
 
+/* ggml's Q8_K activation blocks (292 bytes per 256 values: F32 d, 256 codes, 16 sums of 16 codes): the format the
+ * routed experts' gate / up mat-vec reads (fn/kernels/experts/cpu_kernels.h block_q8_k; experts_cpu.cpp:321).
+ * Follows quantize_row_q8_K_ref (ggml/src/ggml-quants.c:2844-2881): the value of largest magnitude (the FIRST one on
+ * ties) maps to -127, codes are nearest-even(iscale x) capped at 127, d = 1 / iscale. */
+void fnbo_quantize_row_q8_k(const float * x, void * y, int64_t k);
+
 /* The consumer of the 8-bit activations: the routed experts' down mat-vec, out[t][r] = weight row r . act[t], with
  * ggml's Q5_1 weights against Q8_1 activations (fmt 0) or Q8_0 weights against Q8_0 activations (fmt 1).  Follows the
  * reference's CPU kernels lane for lane (fn/kernels/experts/cpu_kq_avx2.cpp:293-344, :382-394): eight F32 accumulators

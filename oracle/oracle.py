@@ -265,6 +265,20 @@ def kv8_dequantize(codes: np.ndarray, scales: np.ndarray) -> np.ndarray:
     return (c * s).reshape(-1)
 
 
+Q8_K_BYTES = 292
+
+
+def quantize_q8_k(x: np.ndarray, which: str = "oracle") -> np.ndarray:
+    """ggml Q8_K blocks of x (a multiple of 256 values).  which: "oracle" (this restatement), "ggml" (the reference's
+    quantize_row_q8_K_ref) or "avx2" (the reference's fn::experts::cpu::quantize_q8_k)."""
+    x = _f32(x).reshape(-1)
+    out = np.zeros(x.size // 256 * Q8_K_BYTES, np.uint8)
+    fn = {"oracle": lambda: lib().fnbo_quantize_row_q8_k, "ggml": lambda: ref().quantize_row_q8_K_ref,
+          "avx2": lambda: ref().ref_quantize_q8_k_avx2}[which]()
+    fn(_p(x), _p(out), C.c_int64(x.size))
+    return out.reshape(-1, Q8_K_BYTES)
+
+
 DOWN_FMT = {"q5_1": (0, 24, Q8_1_BYTES), "q8_0": (1, Q8_0_BYTES, Q8_0_BYTES)}   # code, weight block, activation block
 
 

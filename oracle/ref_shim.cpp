@@ -76,6 +76,10 @@ int32_t ref_synth_blocks(const char * fmt, uint64_t seed, int64_t n_blocks, uint
 uint16_t ref_f32_to_f16(float f) { return fn::quant::f32_to_f16(f); }
 float ref_f16_to_f32(uint16_t h) { return fn::quant::f16_to_f32(h); }
 
+// Q8_K activations: the reference's AVX2 form (fn/kernels/experts/cpu_iq_avx2.cpp:583-646); ggml's scalar form
+// quantize_row_q8_K_ref is exported by ggml-quants.c itself
+void ref_quantize_q8_k_avx2(const float * x, void * y, int64_t k) { fn::experts::cpu::quantize_q8_k(x, y, k); }
+
 // the routed experts' down rows (fn/kernels/experts/cpu_kq_avx2.cpp:382-394): fmt 0 = Q5_1 x Q8_1, 1 = Q8_0 x Q8_0
 void ref_kq_down_rows(int32_t f, const uint8_t * w, int64_t row_bytes, int32_t n, const uint8_t * act, int64_t act_stride,
                       int32_t nt, float * out, int64_t out_stride, int32_t r0, int32_t r1) {

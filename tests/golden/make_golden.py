@@ -111,10 +111,35 @@ def down_rows() -> None:
     print("down_rows.npz", os.path.getsize(os.path.join(HERE, "down_rows.npz")), "bytes")
 
 
+def q8_k() -> None:
+    """ggml's quantize_row_q8_K_ref and the reference's AVX2 quantize_q8_k on stress blocks (ties between +a and -a in
+    both orders, zeros, tiny and huge magnitudes, constant blocks, half steps) and random ones; the two must agree."""
+    from fnfl_v100_b200 import synth
+    g = synth.rng(0x51384b)
+    x = synth.normal(g, (96, 256), 3.0)
+    x[1] = 0
+    x[2, 5], x[2, 200] = 7.5, -7.5        # tie, the positive one first
+    x[3, 5], x[3, 200] = -7.5, 7.5        # tie, the negative one first
+    x[4] *= np.float32(1e-30)
+    x[5] *= np.float32(1e20)
+    x[6, :] = 0.5
+    x[7, ::2] = -1.25
+    x[8] = np.round(x[8] * 4) / 4          # many exact half steps after scaling by 127 / max
+    x[8, 17] = 127.0 / 4
+    x[9, :] = 0
+    x[9, 255] = -3.0                       # the maximum in the last lane's last slot
+    x[10, 0] = np.float32(np.abs(x[10]).max() * 2)   # and in the first
+    a, b = O.quantize_q8_k(x, "ggml"), O.quantize_q8_k(x, "avx2")
+    assert np.array_equal(a, b)
+    np.savez_compressed(os.path.join(HERE, "q8_k.npz"), x=x, blocks=a)
+    print("q8_k.npz", os.path.getsize(os.path.join(HERE, "q8_k.npz")), "bytes")
+
+
 def main() -> None:
     O.build(with_ref=True)
     model_file()
     down_rows()
+    q8_k()
     r = O.ref()
     x = stress_blocks()
     n = x.shape[0]

@@ -73,6 +73,9 @@ def test_rejections_enqueue_nothing(lib):
     assert lib.fnb_swiglu_act(A16, A16, A16, None, None, 8, 512, None) == R
     assert lib.fnb_quantize_q8_1(A16, A16, -3, 512, None) == R
     assert lib.fnb_quantize_q8_0(None, A16, 3, 512, None) == R
+    assert lib.fnb_quantize_q8_k(A16, A16, 4, 300, None) == R      # cols not a multiple of 256
+    assert lib.fnb_quantize_q8_k(ODD, A16, 4, 512, None) == R
+    assert lib.fnb_quantize_q8_k(A16, None, 4, 512, None) == R
     # experts' down rows: n not a multiple of 32, rows not back to back, window of 0 or 65 rows, r1 <= r0, short out rows
     ok = (A16, 480, 640, A16, 720, 3, A16, 2560, 0, 2560, None)
     for i, bad in ((2, 650), (1, 484), (5, 0), (5, 65), (9, 0), (7, 100), (0, None), (3, ODD + 1), (4, 718)):

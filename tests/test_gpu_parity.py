@@ -301,6 +301,28 @@ def test_append_then_read_back(dev, oracle, fmt, hd, nkv):
     assert np.array_equal(bits(span), bits(full[lo:lo + 16]))
 
 
+def test_quantize_q8_k_bit_exact(dev, oracle):
+    """The reference's stress blocks (golden, from ggml's own quantiser) and a large random tensor."""
+    gold = np.load(os.path.join(GOLD, "q8_k.npz"))
+    got = ops.quantize_q8_k(to_dev(gold["x"], dev)).cpu().numpy()
+    assert np.array_equal(got.reshape(-1, 292), gold["blocks"])
+    g = synth.rng(41)
+    x = synth.normal(g, (1000, 2560), 1.5)
+    x[::7, ::5] = 0
+    out = Guarded((1000, 2560 // 256 * 292), torch.uint8, dev)
+    st = _lib_call_quantize_q8_k(to_dev(x, dev), out.live)
+    torch.cuda.synchronize()
+    out.check_guards()
+    assert st == 0 and np.array_equal(out.numpy().reshape(-1, 292), oracle.quantize_q8_k(x))
+
+
+def _lib_call_quantize_q8_k(x, out):
+    import ctypes as C
+    from fnfl_v100_b200 import _lib
+    return _lib.lib().fnb_quantize_q8_k(C.c_void_p(x.data_ptr()), C.c_void_p(out.data_ptr()), x.shape[0], x.shape[1],
+                                        C.c_void_p(torch.cuda.current_stream().cuda_stream))
+
+
 # ---- the consumer of the Q8_1 blocks: the experts' down mat-vec ---------------------------------------------------------
 
 def test_expert_down_rows_equal_the_reference_avx2_kernel_on_golden(dev):

@@ -137,3 +137,9 @@ def test_expert_down_rows_match_the_reference_avx2_kernel(oracle):
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), key
         part = oracle.expert_down_rows(fmt, w, act, n, r0=3, r1=8)
         assert np.array_equal(part[:, 3:8].view(np.uint32), want[:, 3:8].view(np.uint32)) and not part[:, :3].any()
+
+
+def test_q8_k_matches_ggml_and_the_reference_avx2_form(oracle):
+    """tests/golden/q8_k.npz: blocks from ggml's quantize_row_q8_K_ref, equal to the reference's AVX2 quantize_q8_k."""
+    gold = np.load(os.path.join(GOLD, "q8_k.npz"))
+    assert np.array_equal(oracle.quantize_q8_k(gold["x"]), gold["blocks"])
