@@ -320,6 +320,24 @@ def embed_supply(fmt: str, table, tok, n_own: int, src, row0: int, *, own=None, 
     _check(_lib.lib().fnb_embed_supply(C.byref(a), _ptr(src), row0, src.shape[0], _stream()), "embed_supply")
 
 
+def expert_gate_up_rows_q4_k(gate: torch.Tensor, up: torch.Tensor, act: torch.Tensor, n: int, r0: int = 0,
+                             r1: int | None = None, out: torch.Tensor | None = None, gu: torch.Tensor | None = None):
+    """ff[t][r] = silu(gate row r . act[t]) * (up row r . act[t]) (fn::experts::cpu::kq_gu_rows for q4_k, bit for bit):
+    Q4_K rows uint8 [rows][n/256*144], Q8_K activations uint8 [nt][n/256*292]; returns F32 [nt][rows]."""
+    _dev(gate, torch.uint8, "gate")
+    _dev(up, torch.uint8, "up")
+    _dev(act, torch.uint8, "act")
+    rows, nt = gate.shape[0], act.shape[0]
+    r1 = rows if r1 is None else r1
+    if out is None:
+        out = torch.zeros((nt, rows), dtype=torch.float32, device=gate.device)
+    _dev(out, torch.float32, "out")
+    _check(_lib.lib().fnb_expert_gate_up_rows_q4_k(_ptr(gate), _ptr(up), gate.shape[1], n, _ptr(act), act.shape[1], nt,
+                                                   _ptr(out), out.shape[1], _ptr(gu), r0, r1, _stream()),
+           "expert_gate_up_rows_q4_k")
+    return out
+
+
 def expert_down_rows(fmt: str, w: torch.Tensor, act: torch.Tensor, n: int, r0: int = 0, r1: int | None = None,
                      out: torch.Tensor | None = None) -> torch.Tensor:
     """out[t][r] = weight row r . activation row t (fn::experts::cpu::kq_down_rows, bit for bit).  fmt "q5_1": Q5_1

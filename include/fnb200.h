@@ -291,6 +291,21 @@ int32_t fnb_kv_read_f32(const fnb_kv_read_args * args, void * stream);
 int32_t fnb_quantize_q8_k(const float * x, void * out_q8_k, int64_t rows, int32_t cols, void * stream);
 
 /*
+ * The routed experts' gate / up mat-vec for a decode window with the GLU fused: ff[t * ff_stride + r] = silu(g) u,
+ * g = gate row r . act[t], u = up row r . act[t], for t < nt and r in [r0, r1).  ggml Q4_K weights (n / 256
+ * super-blocks of 144 bytes a row, rows back to back: row_bytes = n / 256 * 144; row r of either matrix at
+ * base + r row_bytes) against the Q8_K activations fnb_quantize_q8_k writes (row t at act + t act_stride).  Replaces
+ * fn::experts::cpu::kq_gu_rows for fmt q4_k (fn/kernels/experts/cpu_kernels.h; cpu_kq_avx2.cpp:166-224, :362-380) and
+ * returns the SAME BITS (lane structure, fused multiply-adds and reduction order of the AVX2 kernel; expf as the host C
+ * library's generic build evaluates it).  gu (optional, windows of up to eight rows): [2][nt][ff_stride], g then u.
+ * nt <= 64; the window's activations (nt x n / 256 x 292 bytes per pass of eight rows) must fit in 47 KB of shared
+ * memory (n <= 5120 at eight rows); gate, up 16-byte, act, ff 4-byte aligned.
+ */
+int32_t fnb_expert_gate_up_rows_q4_k(const void * gate, const void * up, int64_t row_bytes, int32_t n, const void * act,
+                                     int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, float * gu, int64_t r0,
+                                     int64_t r1, void * stream);
+
+/*
  * The consumer of the Q8_1 blocks fnb_swiglu_q8_1 writes: the routed experts' down mat-vec for a decode window,
  * out[t * out_stride + r] = weight row r . act[t] for t < nt and r in [r0, r1).  Weights are ggml Q5_1 rows (n / 32
  * blocks of 24 bytes: fp16 d, fp16 m, 32 high bits, 16 nibble bytes; value = d q + m), rows back to back

@@ -520,3 +520,60 @@ void fnbo_quantize_row_q8_k(const float * x, void * vy, int64_t k) {
         memcpy(y, &d, 4);
     }
 }
+
+/* ---- the routed experts' gate / up rows over Q8_K (fn/kernels/experts/cpu_kq_avx2.cpp:166-224, :362-380) ------------*/
+static float fnbo_q4k_dot(const uint8_t * row, int nb, const uint8_t * act) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float acc_m[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int i = 0; i < nb; ++i) {
+        const uint8_t * x = row + 144 * i;
+        const uint8_t * y = act + 292 * i;
+        uint16_t dh, mh;
+        memcpy(&dh, x, 2), memcpy(&mh, x + 2, 2);
+        const float xd = fnbo_f16_to_f32(dh), xdmin = fnbo_f16_to_f32(mh);
+        uint8_t sc[8], mn[8];
+        for (int j = 0; j < 8; ++j) o_scale_min_k4(j, x + 4, &sc[j], &mn[j]);
+        float yd;
+        memcpy(&yd, y, 4);
+        const int8_t * q8 = (const int8_t *) (y + 4);
+        int16_t bsums[16];
+        memcpy(bsums, y + 260, 32);
+        const float d = yd * xd, dmin = -yd * xdmin;
+        for (int k = 0; k < 4; ++k) { /* madd_epi16 of the mins with the pairwise (16-bit) sums of the block sums */
+            const int16_t s0 = (int16_t) (bsums[4 * k] + bsums[4 * k + 1]), s1 = (int16_t) (bsums[4 * k + 2] + bsums[4 * k + 3]);
+            const int32_t prod = (int32_t) mn[2 * k] * s0 + (int32_t) mn[2 * k + 1] * s1;
+            acc_m[k] = fmaf(dmin, (float) prod, acc_m[k]);
+        }
+        const uint8_t * q4 = x + 16;
+        for (int l = 0; l < 8; ++l) {
+            int32_t sumi = 0;
+            for (int j = 0; j < 4; ++j) {
+                int32_t lo = 0, hi = 0;
+                for (int b = 4 * l; b < 4 * l + 4; ++b) {
+                    lo += (q4[32 * j + b] & 15) * (int32_t) q8[64 * j + b];
+                    hi += (q4[32 * j + b] >> 4) * (int32_t) q8[64 * j + 32 + b];
+                }
+                sumi += (int32_t) sc[2 * j] * lo + (int32_t) sc[2 * j + 1] * hi;
+            }
+            acc[l] = fmaf(d, (float) sumi, acc[l]);
+        }
+    }
+    return fnbo_hsum8(acc) + ((acc_m[0] + acc_m[2]) + (acc_m[1] + acc_m[3]));
+}
+
+void fnbo_expert_gu_rows_q4_k(const uint8_t * gate, const uint8_t * up, int64_t row_bytes, int32_t n, const uint8_t * act,
+                              int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, float * gu, int64_t r0,
+                              int64_t r1) {
+    const int nb = n / 256;
+    for (int64_t r = r0; r < r1; ++r) {
+        for (int t = 0; t < nt; ++t) {
+            const float g = fnbo_q4k_dot(gate + r * row_bytes, nb, act + (int64_t) t * act_stride);
+            const float u = fnbo_q4k_dot(up + r * row_bytes, nb, act + (int64_t) t * act_stride);
+            ff[(int64_t) t * ff_stride + r] = (g / (1.0f + o_expf(-g))) * u;
+            if (gu != NULL) {
+                gu[(int64_t) t * ff_stride + r] = g;
+                gu[((int64_t) nt + t) * ff_stride + r] = u;
+            }
+        }
+    }
+}

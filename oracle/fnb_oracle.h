@@ -85,6 +85,17 @@ void fnbo_kv8_quantize(const float * x, int64_t n, int8_t * codes, uint16_t * sc
  * ties) maps to -127, codes are nearest-even(iscale x) capped at 127, d = 1 / iscale. */
 void fnbo_quantize_row_q8_k(const float * x, void * y, int64_t k);
 
+/* The routed experts' gate / up mat-vec with the GLU fused, ff[t][r] = silu(g) u with g = gate row r . act[t] and
+ * u = up row r . act[t]: ggml Q4_K weights (n / 256 super-blocks of 144 bytes a row, row r of either matrix at
+ * base + r row_bytes) against Q8_K activations (act + t act_stride).  Follows the reference's AVX2 kernels lane for
+ * lane (fn/kernels/experts/cpu_kq_avx2.cpp:166-224 q4k_dot, :362-380 kq_gu_rows): per (row, t) eight int32 lanes of
+ * scale-weighted 4-byte dot products per super-block, fused-multiply-added as floats with d = y.d x.d; four lanes of
+ * mins x block sums with -y.d x.dmin; hsum_float_8 plus ((m0 + m2) + (m1 + m3)); then g / (1 + expf(-g)) * u.
+ * gu: optional [2][nt][rows] receiving g and u themselves. */
+void fnbo_expert_gu_rows_q4_k(const uint8_t * gate, const uint8_t * up, int64_t row_bytes, int32_t n, const uint8_t * act,
+                              int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, float * gu, int64_t r0,
+                              int64_t r1);
+
 /* The consumer of the 8-bit activations: the routed experts' down mat-vec, out[t][r] = weight row r . act[t], with
  * ggml's Q5_1 weights against Q8_1 activations (fmt 0) or Q8_0 weights against Q8_0 activations (fmt 1).  Follows the
  * reference's CPU kernels lane for lane (fn/kernels/experts/cpu_kq_avx2.cpp:293-344, :382-394): eight F32 accumulators

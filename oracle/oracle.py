@@ -265,6 +265,25 @@ def kv8_dequantize(codes: np.ndarray, scales: np.ndarray) -> np.ndarray:
     return (c * s).reshape(-1)
 
 
+def expert_gu_rows_q4_k(gate: np.ndarray, up: np.ndarray, act: np.ndarray, n: int, r0: int = 0, r1: int | None = None,
+                        use_ref: bool = False, want_gu: bool = False):
+    """ff[t][r] = silu(gate row r . act[t]) * (up row r . act[t]): Q4_K rows uint8 [rows][n/256*144] against Q8_K
+    activations uint8 [nt][n/256*292].  use_ref: the reference's own AVX2 kernel (its libm's expf)."""
+    gate, up, act = (np.ascontiguousarray(a, np.uint8) for a in (gate, up, act))
+    rows, nt = gate.shape[0], act.shape[0]
+    r1 = rows if r1 is None else r1
+    ff = np.zeros((nt, rows), np.float32)
+    if use_ref:
+        ref().ref_kq_gu_rows_q4_k(_p(gate), _p(up), C.c_int64(gate.shape[1]), C.c_int32(n), _p(act), C.c_int64(act.shape[1]),
+                                  C.c_int32(nt), _p(ff), C.c_int64(rows), C.c_int32(r0), C.c_int32(r1))
+        return ff
+    gu = np.zeros((2, nt, rows), np.float32) if want_gu else None
+    lib().fnbo_expert_gu_rows_q4_k(_p(gate), _p(up), C.c_int64(gate.shape[1]), C.c_int32(n), _p(act),
+                                   C.c_int64(act.shape[1]), C.c_int32(nt), _p(ff), C.c_int64(rows), _p(gu), C.c_int64(r0),
+                                   C.c_int64(r1))
+    return (ff, gu) if want_gu else ff
+
+
 Q8_K_BYTES = 292
 
 

@@ -76,6 +76,15 @@ int32_t ref_synth_blocks(const char * fmt, uint64_t seed, int64_t n_blocks, uint
 uint16_t ref_f32_to_f16(float f) { return fn::quant::f32_to_f16(f); }
 float ref_f16_to_f32(uint16_t h) { return fn::quant::f16_to_f32(h); }
 
+// the routed experts' gate / up rows with the GLU (fn/kernels/experts/cpu_kq_avx2.cpp:362-380), fmt q4_k
+void ref_kq_gu_rows_q4_k(const uint8_t * gate, const uint8_t * up, int64_t row_bytes, int32_t n, const uint8_t * act,
+                         int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, int32_t r0, int32_t r1) {
+    const void * a[64];
+    float * o[64];
+    for (int t = 0; t < nt && t < 64; ++t) a[t] = act + int64_t(t) * act_stride, o[t] = ff + int64_t(t) * ff_stride;
+    fn::experts::cpu::kq_gu_rows(fn::experts::fmt::q4_k, gate, up, size_t(row_bytes), n, a, nt, o, r0, r1);
+}
+
 // Q8_K activations: the reference's AVX2 form (fn/kernels/experts/cpu_iq_avx2.cpp:583-646); ggml's scalar form
 // quantize_row_q8_K_ref is exported by ggml-quants.c itself
 void ref_quantize_q8_k_avx2(const float * x, void * y, int64_t k) { fn::experts::cpu::quantize_q8_k(x, y, k); }

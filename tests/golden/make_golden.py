@@ -135,11 +135,29 @@ def q8_k() -> None:
     print("q8_k.npz", os.path.getsize(os.path.join(HERE, "q8_k.npz")), "bytes")
 
 
+def gate_up_rows() -> None:
+    """The reference's own AVX2 gate / up mat-vec with the GLU (fn::experts::cpu::kq_gu_rows, fmt q4_k) on seeded Q4_K rows
+    and Q8_K activations.  Its expf is the host C library's; generate with
+    GLIBC_TUNABLES=glibc.cpu.hwcaps=-AVX2_Usable,-FMA_Usable,-FMA4_Usable,-AVX2,-FMA,-FMA4 so that libm runs its generic
+    build, the one the oracle restates (the assert below checks it)."""
+    from fnfl_v100_b200 import synth
+    g = synth.rng(0x4755)
+    n, rows, nt = 2560, 45, 5
+    gate, up = synth.q4_k_table(g, rows, n, 1e-5, 2e-4), synth.q4_k_table(g, rows, n, 1e-5, 2e-4)
+    act = O.quantize_q8_k(synth.normal(g, (nt, n), 1.0), "ggml").reshape(nt, -1)
+    ff = O.expert_gu_rows_q4_k(gate, up, act, n, use_ref=True)
+    O.use_libm(False)
+    assert np.array_equal(ff.view(np.uint32), O.expert_gu_rows_q4_k(gate, up, act, n).view(np.uint32)), "libm is not the generic build"
+    np.savez_compressed(os.path.join(HERE, "gate_up_rows.npz"), gate=gate, up=up, act=act, ff=ff)
+    print("gate_up_rows.npz", os.path.getsize(os.path.join(HERE, "gate_up_rows.npz")), "bytes; |ff| max", float(np.abs(ff).max()))
+
+
 def main() -> None:
     O.build(with_ref=True)
     model_file()
     down_rows()
     q8_k()
+    gate_up_rows()
     r = O.ref()
     x = stress_blocks()
     n = x.shape[0]

@@ -76,6 +76,19 @@ def test_rejections_enqueue_nothing(lib):
     assert lib.fnb_quantize_q8_k(A16, A16, 4, 300, None) == R      # cols not a multiple of 256
     assert lib.fnb_quantize_q8_k(ODD, A16, 4, 512, None) == R
     assert lib.fnb_quantize_q8_k(A16, None, 4, 512, None) == R
+    # experts' gate / up rows: n not a multiple of 256, rows not back to back, a window whose activations exceed shared
+    # memory, the debug planes with a window of more than one pass
+    okg = (A16, A16, 1440, 2560, A16, 2920, 3, A16, 640, None, 0, 640, None)
+    for i, bad in ((3, 2500), (2, 1444), (6, 0), (6, 65), (11, 0), (8, 100), (0, ODD), (4, None)):
+        a = list(okg)
+        a[i] = bad
+        assert lib.fnb_expert_gate_up_rows_q4_k(*a) == R, (i, bad)
+    big = list(okg)
+    big[2], big[3], big[5] = 144 * 64, 16384, 292 * 64
+    assert lib.fnb_expert_gate_up_rows_q4_k(*big) == R
+    dbg = list(okg)
+    dbg[6], dbg[9] = 9, A16
+    assert lib.fnb_expert_gate_up_rows_q4_k(*dbg) == R
     # experts' down rows: n not a multiple of 32, rows not back to back, window of 0 or 65 rows, r1 <= r0, short out rows
     ok = (A16, 480, 640, A16, 720, 3, A16, 2560, 0, 2560, None)
     for i, bad in ((2, 650), (1, 484), (5, 0), (5, 65), (9, 0), (7, 100), (0, None), (3, ODD + 1), (4, 718)):

@@ -323,6 +323,35 @@ def _lib_call_quantize_q8_k(x, out):
                                         C.c_void_p(torch.cuda.current_stream().cuda_stream))
 
 
+def test_expert_gate_up_rows_equal_the_reference_avx2_kernel_on_golden(dev):
+    gold = np.load(os.path.join(GOLD, "gate_up_rows.npz"))
+    got = ops.expert_gate_up_rows_q4_k(to_dev(gold["gate"], dev), to_dev(gold["up"], dev), to_dev(gold["act"], dev), 2560)
+    assert np.array_equal(bits(got.cpu().numpy()), bits(gold["ff"]))
+
+
+@pytest.mark.parametrize("n,rows,nt", [(2560, 320, 1), (2560, 999, 3), (2560, 130, 8), (256, 37, 2), (1024, 65, 13)])
+def test_expert_gate_up_rows_bit_exact(dev, oracle, n, rows, nt):
+    """RMSNorm -> Q8_K on the device (the path's hand-over), Q4_K gate and up rows: ff, and g and u themselves, carry
+    every bit of the oracle's lane-for-lane restatement; rows outside [r0, r1) stay untouched."""
+    g = synth.rng(33)
+    x = synth.normal(g, (nt, n), 1.0)
+    act = ops.quantize_q8_k(to_dev(x, dev))
+    assert np.array_equal(act.cpu().numpy().reshape(-1, 292), oracle.quantize_q8_k(x))
+    gate, up = synth.q4_k_table(g, rows, n, 1e-5, 3e-4), synth.q4_k_table(g, rows, n, 1e-5, 3e-4)
+    r0, r1 = 2, rows - 1
+    out = torch.full((nt, rows), float("nan"), dtype=torch.float32, device=dev)
+    gu = torch.zeros((2, nt, rows), dtype=torch.float32, device=dev) if nt <= 8 else None
+    ops.expert_gate_up_rows_q4_k(to_dev(gate, dev), to_dev(up, dev), act, n, r0=r0, r1=r1, out=out, gu=gu)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    want, wgu = oracle.expert_gu_rows_q4_k(gate, up, act.cpu().numpy(), n, r0=r0, r1=r1, want_gu=True)
+    assert np.array_equal(bits(got[:, r0:r1]), bits(want[:, r0:r1]))
+    assert np.isnan(got[:, :r0]).all() and np.isnan(got[:, r1:]).all()
+    if gu is not None:
+        assert np.array_equal(bits(gu.cpu().numpy()[:, :, r0:r1]), bits(wgu[:, :, r0:r1]))
+    assert np.abs(want[:, r0:r1]).max() < 1e3 and np.abs(wgu[0][:, r0:r1]).std() > 0.3   # gates of order one: the GLU is exercised
+
+
 # ---- the consumer of the Q8_1 blocks: the experts' down mat-vec ---------------------------------------------------------
 
 def test_expert_down_rows_equal_the_reference_avx2_kernel_on_golden(dev):

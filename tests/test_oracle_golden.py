@@ -143,3 +143,14 @@ def test_q8_k_matches_ggml_and_the_reference_avx2_form(oracle):
     """tests/golden/q8_k.npz: blocks from ggml's quantize_row_q8_K_ref, equal to the reference's AVX2 quantize_q8_k."""
     gold = np.load(os.path.join(GOLD, "q8_k.npz"))
     assert np.array_equal(oracle.quantize_q8_k(gold["x"]), gold["blocks"])
+
+
+def test_expert_gate_up_rows_match_the_reference_avx2_kernel(oracle):
+    """tests/golden/gate_up_rows.npz: ff of the reference's own kq_gu_rows (fmt q4_k, GLU included); the scalar
+    restatement reproduces every bit, also on a sub-range of rows."""
+    gold = np.load(os.path.join(GOLD, "gate_up_rows.npz"))
+    gate, up, act, want = gold["gate"], gold["up"], gold["act"], gold["ff"]
+    got = oracle.expert_gu_rows_q4_k(gate, up, act, 2560)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    part = oracle.expert_gu_rows_q4_k(gate, up, act, 2560, r0=7, r1=19)
+    assert np.array_equal(part[:, 7:19].view(np.uint32), want[:, 7:19].view(np.uint32)) and not part[:, :7].any()
