@@ -74,6 +74,17 @@ inline bool glu_finish_q8_1(const float * gs, const float * us, int64_t n, int32
     return fnb_swiglu_q8_1(gs, us, blocks, glu_f32, n, cols, stream) == FNB_OK;
 }
 
+// the experts' gate / up mat-vec with the GLU over a decode window (fn::experts::cpu::kq_gu_rows for fmt q4_k, same
+// bits): ff[t][r] = silu(gate row r . act[t]) * (up row r . act[t]); Q4_K rows back to back, Q8_K activation rows
+inline bool gate_up_rows_q4_k(const uint8_t * gate, const uint8_t * up, int32_t n, const void * act, int64_t act_stride,
+                              int32_t nt, float * ff, int64_t ff_stride, int64_t r0, int64_t r1, void * stream) {
+    return fnb_expert_gate_up_rows_q4_k(gate, up, int64_t(n / 256) * 144, n, act, act_stride, nt, ff, ff_stride, nullptr, r0,
+                                        r1, stream) == FNB_OK;
+}
+inline bool quantize_q8_k(const float * x, void * blocks, int64_t rows, int32_t k, void * stream) {
+    return fnb_quantize_q8_k(x, blocks, rows, k, stream) == FNB_OK;
+}
+
 // the experts' down mat-vec over a decode window (fn::experts::cpu::kq_down_rows for fmt q5_1, same bits): out[t][r] =
 // Q5_1 weight row r . Q8_1 activation row t, r in [r0, r1); w rows back to back, act rows act_stride bytes apart
 inline bool down_rows_q5_1(const uint8_t * w, int32_t n, const void * act, int64_t act_stride, int32_t nt, float * out,
