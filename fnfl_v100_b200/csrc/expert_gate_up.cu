@@ -20,14 +20,17 @@ namespace {
 constexpr int kWarps = 8;
 constexpr int kMaxT = 8;
 
-// the six-bit scale and min of sub-block j from the 12 packed bytes s (ggml get_scale_min_k4)
-__device__ __forceinline__ void scale_min(int j, uint32_t s0, uint32_t s1, uint32_t s2, int & sc, int & mn) {
-    const int sh = 8 * (j & 3);
-    const uint32_t a = (s0 >> sh) & 0xffu, b = (s1 >> sh) & 0xffu, c = (s2 >> sh) & 0xffu;
-    if (j < 4) {
-        sc = int(a & 63u), mn = int(b & 63u);
-    } else {
-        sc = int((c & 0x0fu) | ((a >> 6) << 4)), mn = int((c >> 4) | ((b >> 6) << 4));
+// the eight six-bit scales and eight mins from the 12 packed bytes, four to a word, as ggml unpacks them for its
+// vector kernels (the utmp shuffle of ggml_vec_dot_q4_K_q8_K; cpu_kq_avx2.cpp:154-166): about ten logic operations
+// for all sixteen values, where get_scale_min_k4 per value costs six each
+__device__ __forceinline__ void scales_mins(uint32_t u0, uint32_t u1, uint32_t u2, int (&sc)[8], int (&mn)[8]) {
+    const uint32_t k1 = 0x3f3f3f3fu, k2 = 0x0f0f0f0fu, k3 = 0x03030303u;
+    const uint32_t s_lo = u0 & k1, s_hi = (u2 & k2) | (((u0 >> 6) & k3) << 4);
+    const uint32_t m_lo = u1 & k1, m_hi = ((u2 >> 4) & k2) | (((u1 >> 6) & k3) << 4);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        sc[j] = int((s_lo >> (8 * j)) & 0xffu), sc[j + 4] = int((s_hi >> (8 * j)) & 0xffu);
+        mn[j] = int((m_lo >> (8 * j)) & 0xffu), mn[j + 4] = int((m_hi >> (8 * j)) & 0xffu);
     }
 }
 
@@ -45,8 +48,7 @@ __device__ __forceinline__ void row_dot(const uint8_t * __restrict__ row, int nb
         for (int j = 0; j < 4; ++j) q4[j] = __ldg(reinterpret_cast<const uint32_t *>(x + 16 + 32 * j) + l);
         const float xd = f16_bits_to_f32(uint16_t(hdr.x & 0xffffu)), xdmin = f16_bits_to_f32(uint16_t(hdr.x >> 16));
         int sc[8], mn[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) scale_min(j, hdr.y, hdr.z, hdr.w, sc[j], mn[j]);
+        scales_mins(hdr.y, hdr.z, hdr.w, sc, mn);
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
             const uint8_t * y = act_sm + (size_t(t) * nb + i) * 292;
@@ -83,8 +85,7 @@ struct q4k_lane {
 #pragma unroll
         for (int j = 0; j < 4; ++j) q4[j] = __ldg(reinterpret_cast<const uint32_t *>(x + 16 + 32 * j) + l);
         xd = f16_bits_to_f32(uint16_t(hdr.x & 0xffffu)), xdmin = f16_bits_to_f32(uint16_t(hdr.x >> 16));
-#pragma unroll
-        for (int j = 0; j < 8; ++j) scale_min(j, hdr.y, hdr.z, hdr.w, sc[j], mn[j]);
+        scales_mins(hdr.y, hdr.z, hdr.w, sc, mn);
     }
     __device__ __forceinline__ int min_pair(int l, int s0, int s1) const {  // madd of mins (2 l, 2 l + 1) with the pair sums
         return (l == 0 ? mn[0] : l == 1 ? mn[2] : l == 2 ? mn[4] : mn[6]) * s0 +
