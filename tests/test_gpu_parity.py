@@ -352,6 +352,35 @@ def test_expert_gate_up_rows_bit_exact(dev, oracle, n, rows, nt):
     assert np.abs(want[:, r0:r1]).max() < 1e3 and np.abs(wgu[0][:, r0:r1]).std() > 0.3   # gates of order one: the GLU is exercised
 
 
+def test_expert_ffn_for_a_decode_window_stage_by_stage(dev, oracle):
+    """One routed expert for a window of three rows, every hand-over on the device: RMSNorm -> Q8_K -> gate / up mat-vec
+    with the GLU (Q4_K) -> Q8_1 -> down mat-vec (Q5_1).  Each stage is checked bit for bit against the oracle applied to
+    the previous stage's device output, and the end against the all-CPU chain."""
+    g = synth.rng(77)
+    nt, d_model, d_ff = 3, 2560, 640
+    x, w = synth.normal(g, (nt, d_model), 1.0), synth.norm_weight(g, d_model)
+    gate, up = synth.q4_k_table(g, d_ff, d_model, 1e-5, 3e-4), synth.q4_k_table(g, d_ff, d_model, 1e-5, 3e-4)
+    down = synth.q5_1_rows(g, d_model, d_ff)
+    D = lambda a: to_dev(a, dev)  # noqa: E731
+    normed = ops.rms_norm(D(x), D(w), 1e-6)
+    q8k = ops.quantize_q8_k(normed)
+    ff = ops.expert_gate_up_rows_q4_k(D(gate), D(up), q8k, d_model)
+    q81 = ops.quantize_q8_1(ff)
+    out = ops.expert_down_rows("q5_1", D(down), q81, d_ff)
+    torch.cuda.synchronize()
+    H = lambda t: t.cpu().numpy()  # noqa: E731
+    assert ulp_diff(H(normed), oracle.rms_norm(x, w, 1e-6)).max() <= 2
+    assert np.array_equal(H(q8k).reshape(-1, 292), oracle.quantize_q8_k(H(normed)))
+    assert np.array_equal(bits(H(ff)), bits(oracle.expert_gu_rows_q4_k(gate, up, H(q8k), d_model)))
+    assert np.array_equal(H(q81).reshape(-1), oracle.quantize_q8_1(H(ff)).reshape(-1))
+    assert np.array_equal(bits(H(out)), bits(oracle.expert_down_rows("q5_1", down, H(q81).reshape(nt, -1), d_ff)))
+    # the all-CPU chain (its RMSNorm sums in another order: the device result may sit an ulp away, and a code with it)
+    c_norm = oracle.rms_norm(x, w, 1e-6)
+    c_ff = oracle.expert_gu_rows_q4_k(gate, up, oracle.quantize_q8_k(c_norm).reshape(nt, -1), d_model)
+    c_out = oracle.expert_down_rows("q5_1", down, oracle.quantize_q8_1(c_ff).reshape(nt, -1), d_ff)
+    assert np.abs(H(out) - c_out).max() <= 1e-3 * np.abs(c_out).max()
+
+
 # ---- the consumer of the Q8_1 blocks: the experts' down mat-vec ---------------------------------------------------------
 
 def test_expert_down_rows_equal_the_reference_avx2_kernel_on_golden(dev):
