@@ -19,7 +19,8 @@ from .chain import ChainConfig
 OPS = ("get_rows_q4_k", "get_rows_iq3_xxs", "rms_norm", "rms_norm_heads", "rope_kv", "swiglu_q8_1", "swiglu_act",
        "rope_kv8", "quantize_q8_1", "rms_norm_q8_1", "embed_iq3_s", "kv_read_q8_0", "kv_read_kv8",
        "expert_down_q5_1_nt1", "expert_down_q5_1_nt3", "expert_down_q5_1_nt8", "expert_down_q8_0_nt1", "expert_down_q8_0_nt3", "quantize_q8_k",
-       "expert_gate_up_q4_k_nt1", "expert_gate_up_q4_k_nt3", "expert_gate_up_q4_k_nt8")
+       "expert_gate_up_q4_k_nt1", "expert_gate_up_q4_k_nt3", "expert_gate_up_q4_k_nt8",
+       "expert_gate_up_iq3_xxs_nt1", "expert_gate_up_iq3_xxs_nt3", "expert_gate_up_iq3_xxs_nt8")
 
 
 def hbm_peak() -> float:
@@ -82,6 +83,13 @@ def make_case(op: str, T: int, dev, gen, c: ChainConfig):
         act = ops.quantize_q8_k(N(gen, (nt, n), 1.0, dev))
         out = torch.empty((nt, rows), dtype=torch.float32, device=dev)
         return (lambda: ops.expert_gate_up_rows_q4_k(gate, up, act, n, out=out)), rows * (2 * n // 256 * 144 + nt * 4) + nt * n // 256 * 292
+    if op.startswith("expert_gate_up_iq3_xxs"):
+        nt, n, rows = int(op.rsplit("nt", 1)[1]), 2560, 2 * T
+        gate = synth.torch_table("iq3_xxs", gen, rows, n, dev, 5e-5, 4e-4)
+        up = synth.torch_table("iq3_xxs", gen, rows, n, dev, 5e-5, 4e-4)
+        act = ops.quantize_q8_k(N(gen, (nt, n), 1.0, dev))
+        out = torch.empty((nt, rows), dtype=torch.float32, device=dev)
+        return (lambda: ops.expert_gate_up_rows_iq3_xxs(gate, up, act, n, out=out)), rows * (2 * n // 256 * 98 + nt * 4) + nt * n // 256 * 292
     if op == "quantize_q8_k":
         x = N(gen, (T, 2560), 1.0, dev)                      # the reference's d_model
         return (lambda: ops.quantize_q8_k(x)), T * 2560 * 4 + T * 2560 // 256 * 292

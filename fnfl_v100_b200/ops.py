@@ -320,10 +320,12 @@ def embed_supply(fmt: str, table, tok, n_own: int, src, row0: int, *, own=None, 
     _check(_lib.lib().fnb_embed_supply(C.byref(a), _ptr(src), row0, src.shape[0], _stream()), "embed_supply")
 
 
-def expert_gate_up_rows_q4_k(gate: torch.Tensor, up: torch.Tensor, act: torch.Tensor, n: int, r0: int = 0,
-                             r1: int | None = None, out: torch.Tensor | None = None, gu: torch.Tensor | None = None):
-    """ff[t][r] = silu(gate row r . act[t]) * (up row r . act[t]) (fn::experts::cpu::kq_gu_rows for q4_k, bit for bit):
-    Q4_K rows uint8 [rows][n/256*144], Q8_K activations uint8 [nt][n/256*292]; returns F32 [nt][rows]."""
+def expert_gate_up_rows(fmt: str, gate: torch.Tensor, up: torch.Tensor, act: torch.Tensor, n: int, r0: int = 0,
+                        r1: int | None = None, out: torch.Tensor | None = None, gu: torch.Tensor | None = None):
+    """ff[t][r] = silu(gate row r . act[t]) * (up row r . act[t]), bit for bit the reference's CPU rows: fmt "q4_k"
+    (fn::experts::cpu::kq_gu_rows; rows uint8 [rows][n/256*144]) or "iq3_xxs" (fn::experts::cpu::iq_gu_rows; rows
+    [rows][n/256*98]), Q8_K activations uint8 [nt][n/256*292]; returns F32 [nt][rows]."""
+    entry = {"q4_k": "fnb_expert_gate_up_rows_q4_k", "iq3_xxs": "fnb_expert_gate_up_rows_iq3_xxs"}[fmt]
     _dev(gate, torch.uint8, "gate")
     _dev(up, torch.uint8, "up")
     _dev(act, torch.uint8, "act")
@@ -332,10 +334,17 @@ def expert_gate_up_rows_q4_k(gate: torch.Tensor, up: torch.Tensor, act: torch.Te
     if out is None:
         out = torch.zeros((nt, rows), dtype=torch.float32, device=gate.device)
     _dev(out, torch.float32, "out")
-    _check(_lib.lib().fnb_expert_gate_up_rows_q4_k(_ptr(gate), _ptr(up), gate.shape[1], n, _ptr(act), act.shape[1], nt,
-                                                   _ptr(out), out.shape[1], _ptr(gu), r0, r1, _stream()),
-           "expert_gate_up_rows_q4_k")
+    _check(getattr(_lib.lib(), entry)(_ptr(gate), _ptr(up), gate.shape[1], n, _ptr(act), act.shape[1], nt, _ptr(out),
+                                      out.shape[1], _ptr(gu), r0, r1, _stream()), "expert_gate_up_rows_" + fmt)
     return out
+
+
+def expert_gate_up_rows_q4_k(gate, up, act, n, **kw):
+    return expert_gate_up_rows("q4_k", gate, up, act, n, **kw)
+
+
+def expert_gate_up_rows_iq3_xxs(gate, up, act, n, **kw):
+    return expert_gate_up_rows("iq3_xxs", gate, up, act, n, **kw)
 
 
 def expert_down_rows(fmt: str, w: torch.Tensor, act: torch.Tensor, n: int, r0: int = 0, r1: int | None = None,

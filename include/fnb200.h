@@ -306,6 +306,20 @@ int32_t fnb_expert_gate_up_rows_q4_k(const void * gate, const void * up, int64_t
                                      int64_t r1, void * stream);
 
 /*
+ * The same mat-vec with ggml IQ3_XXS weights (n / 256 super-blocks of 98 bytes a row, rows back to back:
+ * row_bytes = n / 256 * 98): replaces fn::experts::cpu::iq_gu_rows for fmt iq3_xxs (fn/kernels/experts/cpu_kernels.h:67;
+ * cpu_iq_avx2.cpp:256-271, :305-337, :429-445) and returns the SAME BITS - eight int32 lanes a super-block of
+ * (2 s + 1) x codebook bytes x sign-applied codes, one fused multiply-add a super-block with x.d y.d, ggml's
+ * hsum_float_8 order, the format's 1/4 on the reduced sum, g / (1 + expf(-g)) * u - including for activation codes of
+ * -128, which the reference's sign step leaves as they are.  Arguments as fnb_expert_gate_up_rows_q4_k.  n a multiple
+ * of 512 up to 16384 (rows on 4-byte boundaries); nt <= 64 in passes of up to eight rows; gu only for windows of one
+ * pass.  Uses more than the default shared memory: fnb_prepare_device covers it.
+ */
+int32_t fnb_expert_gate_up_rows_iq3_xxs(const void * gate, const void * up, int64_t row_bytes, int32_t n, const void * act,
+                                        int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, float * gu, int64_t r0,
+                                        int64_t r1, void * stream);
+
+/*
  * The consumer of the Q8_1 blocks fnb_swiglu_q8_1 writes: the routed experts' down mat-vec for a decode window,
  * out[t * out_stride + r] = weight row r . act[t] for t < nt and r in [r0, r1).  Weights are ggml Q5_1 rows (n / 32
  * blocks of 24 bytes: fp16 d, fp16 m, 32 high bits, 16 nibble bytes; value = d q + m), rows back to back

@@ -577,3 +577,62 @@ void fnbo_expert_gu_rows_q4_k(const uint8_t * gate, const uint8_t * up, int64_t 
         }
     }
 }
+
+/* ---- the same rows with IQ3_XXS weights (fn/kernels/experts/cpu_iq_avx2.cpp:256-271 fmt32<18>::decode, :305-337
+ * row_dot, :429-445 gu_rows).  Per super-block eight int32 lanes: lane l collects, over the block's eight groups of 32
+ * values, (2 s + 1) x the sum of four codebook bytes of the group's index byte l times the sign-applied Q8_K codes
+ * 32 g + 4 l ..; _mm256_sign_epi8 negates a code in two's complement, so -128 stays -128.  maddubs_epi16's 16-bit
+ * pair sums cannot saturate (2 x 62 x 128).  One fused multiply-add per super-block and lane with (x.d y.d), x.d
+ * WITHOUT the format's 1/4; ggml's hsum_float_8 order; the 1/4 multiplies the reduced sum. */
+static float fnbo_iq3xxs_dot(const uint8_t * row, int nb, const uint8_t * act) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int i = 0; i < nb; ++i) {
+        const uint8_t * x = row + 98 * i;
+        const uint8_t * y = act + 292 * i;
+        uint16_t dh;
+        memcpy(&dh, x, 2);
+        float yd;
+        memcpy(&yd, y, 4);
+        const int8_t * q8 = (const int8_t *) (y + 4);
+        int32_t acci[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int g = 0; g < 8; ++g) {
+            uint32_t w;
+            memcpy(&w, x + 66 + 4 * g, 4);
+            const int32_t sc = 2 * (int32_t) (w >> 28) + 1;
+            for (int l = 0; l < 8; ++l) {
+                const unsigned code = o_grid_packed[x[2 + 8 * g + l]];
+                const unsigned s7 = (w >> (7 * (l / 2))) & 127u;
+                const unsigned signs = s7 | ((unsigned) (__builtin_popcount(s7) & 1) << 7);
+                int32_t sum = 0;
+                for (int b = 0; b < 4; ++b) {
+                    const unsigned level = (code >> (3 * b)) & 7u;
+                    const int32_t mag = level == 7 ? 62 : 4 + 8 * (int32_t) level;
+                    const int8_t yv = q8[32 * g + 4 * l + b];
+                    const int8_t ys = (signs >> (4 * (l & 1) + b)) & 1u ? (int8_t) (0u - (unsigned) yv) : yv;
+                    sum += mag * (int32_t) ys;
+                }
+                acci[l] += sc * sum;
+            }
+        }
+        const float dxy = fnbo_f16_to_f32(dh) * yd;
+        for (int l = 0; l < 8; ++l) acc[l] = fmaf(dxy, (float) acci[l], acc[l]);
+    }
+    return 0.25f * fnbo_hsum8(acc);
+}
+
+void fnbo_expert_gu_rows_iq3_xxs(const uint8_t * gate, const uint8_t * up, int64_t row_bytes, int32_t n, const uint8_t * act,
+                                 int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, float * gu, int64_t r0,
+                                 int64_t r1) {
+    const int nb = n / 256;
+    for (int64_t r = r0; r < r1; ++r) {
+        for (int t = 0; t < nt; ++t) {
+            const float g = fnbo_iq3xxs_dot(gate + r * row_bytes, nb, act + (int64_t) t * act_stride);
+            const float u = fnbo_iq3xxs_dot(up + r * row_bytes, nb, act + (int64_t) t * act_stride);
+            ff[(int64_t) t * ff_stride + r] = (g / (1.0f + o_expf(-g))) * u;
+            if (gu != NULL) {
+                gu[(int64_t) t * ff_stride + r] = g;
+                gu[((int64_t) nt + t) * ff_stride + r] = u;
+            }
+        }
+    }
+}

@@ -96,6 +96,14 @@ void fnbo_expert_gu_rows_q4_k(const uint8_t * gate, const uint8_t * up, int64_t 
                               int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, float * gu, int64_t r0,
                               int64_t r1);
 
+/* The same with ggml IQ3_XXS weights (n / 256 super-blocks of 98 bytes a row): the reference's AVX2 row kernel lane for
+ * lane (fn/kernels/experts/cpu_iq_avx2.cpp:256-271, :305-337, :429-445) - eight int32 lanes a super-block of
+ * (2 s + 1) x codebook bytes x sign-applied Q8_K codes, one fused multiply-add a super-block with (x.d y.d), ggml's
+ * hsum_float_8 order, the format's 1/4 applied to the reduced sum, then g / (1 + expf(-g)) * u. */
+void fnbo_expert_gu_rows_iq3_xxs(const uint8_t * gate, const uint8_t * up, int64_t row_bytes, int32_t n, const uint8_t * act,
+                                 int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, float * gu, int64_t r0,
+                                 int64_t r1);
+
 /* The consumer of the 8-bit activations: the routed experts' down mat-vec, out[t][r] = weight row r . act[t], with
  * ggml's Q5_1 weights against Q8_1 activations (fmt 0) or Q8_0 weights against Q8_0 activations (fmt 1).  Follows the
  * reference's CPU kernels lane for lane (fn/kernels/experts/cpu_kq_avx2.cpp:293-344, :382-394): eight F32 accumulators

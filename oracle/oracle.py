@@ -265,23 +265,33 @@ def kv8_dequantize(codes: np.ndarray, scales: np.ndarray) -> np.ndarray:
     return (c * s).reshape(-1)
 
 
-def expert_gu_rows_q4_k(gate: np.ndarray, up: np.ndarray, act: np.ndarray, n: int, r0: int = 0, r1: int | None = None,
-                        use_ref: bool = False, want_gu: bool = False):
-    """ff[t][r] = silu(gate row r . act[t]) * (up row r . act[t]): Q4_K rows uint8 [rows][n/256*144] against Q8_K
-    activations uint8 [nt][n/256*292].  use_ref: the reference's own AVX2 kernel (its libm's expf)."""
+def expert_gu_rows(fmt: str, gate: np.ndarray, up: np.ndarray, act: np.ndarray, n: int, r0: int = 0, r1: int | None = None,
+                   use_ref: bool = False, want_gu: bool = False):
+    """ff[t][r] = silu(gate row r . act[t]) * (up row r . act[t]): weight rows uint8 [rows][n/256*block bytes] of
+    fmt "q4_k" (144) or "iq3_xxs" (98) against Q8_K activations uint8 [nt][n/256*292].  use_ref: the reference's own
+    AVX2 kernel (its libm's expf)."""
+    ref_fn, own_fn = {"q4_k": ("ref_kq_gu_rows_q4_k", "fnbo_expert_gu_rows_q4_k"),
+                      "iq3_xxs": ("ref_iq_gu_rows_iq3_xxs", "fnbo_expert_gu_rows_iq3_xxs")}[fmt]
     gate, up, act = (np.ascontiguousarray(a, np.uint8) for a in (gate, up, act))
     rows, nt = gate.shape[0], act.shape[0]
     r1 = rows if r1 is None else r1
     ff = np.zeros((nt, rows), np.float32)
     if use_ref:
-        ref().ref_kq_gu_rows_q4_k(_p(gate), _p(up), C.c_int64(gate.shape[1]), C.c_int32(n), _p(act), C.c_int64(act.shape[1]),
-                                  C.c_int32(nt), _p(ff), C.c_int64(rows), C.c_int32(r0), C.c_int32(r1))
+        getattr(ref(), ref_fn)(_p(gate), _p(up), C.c_int64(gate.shape[1]), C.c_int32(n), _p(act), C.c_int64(act.shape[1]),
+                               C.c_int32(nt), _p(ff), C.c_int64(rows), C.c_int32(r0), C.c_int32(r1))
         return ff
     gu = np.zeros((2, nt, rows), np.float32) if want_gu else None
-    lib().fnbo_expert_gu_rows_q4_k(_p(gate), _p(up), C.c_int64(gate.shape[1]), C.c_int32(n), _p(act),
-                                   C.c_int64(act.shape[1]), C.c_int32(nt), _p(ff), C.c_int64(rows), _p(gu), C.c_int64(r0),
-                                   C.c_int64(r1))
+    getattr(lib(), own_fn)(_p(gate), _p(up), C.c_int64(gate.shape[1]), C.c_int32(n), _p(act), C.c_int64(act.shape[1]),
+                           C.c_int32(nt), _p(ff), C.c_int64(rows), _p(gu), C.c_int64(r0), C.c_int64(r1))
     return (ff, gu) if want_gu else ff
+
+
+def expert_gu_rows_q4_k(gate, up, act, n, **kw):
+    return expert_gu_rows("q4_k", gate, up, act, n, **kw)
+
+
+def expert_gu_rows_iq3_xxs(gate, up, act, n, **kw):
+    return expert_gu_rows("iq3_xxs", gate, up, act, n, **kw)
 
 
 Q8_K_BYTES = 292

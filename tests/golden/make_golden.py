@@ -152,12 +152,35 @@ def gate_up_rows() -> None:
     print("gate_up_rows.npz", os.path.getsize(os.path.join(HERE, "gate_up_rows.npz")), "bytes; |ff| max", float(np.abs(ff).max()))
 
 
+def gate_up_rows_iq3_xxs() -> None:
+    """The same for IQ3_XXS rows (fn::experts::cpu::iq_gu_rows, fmt iq3_xxs), and once more with one activation code in
+    ten set to -128, which the reference's sign step (_mm256_sign_epi8) leaves as it is.  Same libm note as above."""
+    from fnfl_v100_b200 import synth
+    g = synth.rng(0x4933)
+    n, rows, nt = 2560, 45, 5
+    gate, up = synth.iq3_xxs_table(g, rows, n, 5e-5, 4e-4), synth.iq3_xxs_table(g, rows, n, 5e-5, 4e-4)
+    act = O.quantize_q8_k(synth.normal(g, (nt, n), 1.0), "ggml").reshape(nt, -1)
+    act_m128 = act.copy()
+    codes = act_m128.reshape(nt, -1, 292)[:, :, 4:260]
+    codes[g.integers(0, 10, size=codes.shape) == 0] = 0x80
+    assert (act_m128 != act).sum() > 1000
+    ff = O.expert_gu_rows_iq3_xxs(gate, up, act, n, use_ref=True)
+    ff_m128 = O.expert_gu_rows_iq3_xxs(gate, up, act_m128, n, use_ref=True)
+    O.use_libm(False)
+    for a, f in ((act, ff), (act_m128, ff_m128)):
+        assert np.array_equal(f.view(np.uint32), O.expert_gu_rows_iq3_xxs(gate, up, a, n).view(np.uint32)), "libm is not the generic build"
+    path = os.path.join(HERE, "gate_up_rows_iq3_xxs.npz")
+    np.savez_compressed(path, gate=gate, up=up, act=act, ff=ff, act_m128=act_m128, ff_m128=ff_m128)
+    print("gate_up_rows_iq3_xxs.npz", os.path.getsize(path), "bytes; |ff| max", float(np.abs(ff).max()))
+
+
 def main() -> None:
     O.build(with_ref=True)
     model_file()
     down_rows()
     q8_k()
     gate_up_rows()
+    gate_up_rows_iq3_xxs()
     r = O.ref()
     x = stress_blocks()
     n = x.shape[0]

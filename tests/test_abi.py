@@ -89,6 +89,15 @@ def test_rejections_enqueue_nothing(lib):
     dbg = list(okg)
     dbg[6], dbg[9] = 9, A16
     assert lib.fnb_expert_gate_up_rows_q4_k(*dbg) == R
+    # the IQ3_XXS form: an odd number of super-blocks a row (rows off 4-byte boundaries), rows not back to back
+    ok3 = (A16, A16, 980, 2560, A16, 2920, 3, A16, 640, None, 0, 640, None)
+    for i, bad in ((3, 2304), (2, 984), (6, 0), (6, 65), (11, 0), (8, 100), (0, ODD), (4, None), (5, 2916)):
+        a = list(ok3)
+        a[i] = bad
+        assert lib.fnb_expert_gate_up_rows_iq3_xxs(*a) == R, (i, bad)
+    dbg3 = list(ok3)
+    dbg3[6], dbg3[9] = 9, A16
+    assert lib.fnb_expert_gate_up_rows_iq3_xxs(*dbg3) == R
     # experts' down rows: n not a multiple of 32, rows not back to back, window of 0 or 65 rows, r1 <= r0, short out rows
     ok = (A16, 480, 640, A16, 720, 3, A16, 2560, 0, 2560, None)
     for i, bad in ((2, 650), (1, 484), (5, 0), (5, 65), (9, 0), (7, 100), (0, None), (3, ODD + 1), (4, 718)):

@@ -352,6 +352,47 @@ def test_expert_gate_up_rows_bit_exact(dev, oracle, n, rows, nt):
     assert np.abs(want[:, r0:r1]).max() < 1e3 and np.abs(wgu[0][:, r0:r1]).std() > 0.3   # gates of order one: the GLU is exercised
 
 
+def test_expert_gate_up_rows_iq3_xxs_equal_the_reference_avx2_kernel_on_golden(dev):
+    """The reference's own iq_gu_rows outputs, also for a window holding -128 codes (the kernel's other sign path)."""
+    gold = np.load(os.path.join(GOLD, "gate_up_rows_iq3_xxs.npz"))
+    gate, up = to_dev(gold["gate"], dev), to_dev(gold["up"], dev)
+    for act, want in ((gold["act"], gold["ff"]), (gold["act_m128"], gold["ff_m128"])):
+        got = ops.expert_gate_up_rows_iq3_xxs(gate, up, to_dev(act, dev), 2560)
+        assert np.array_equal(bits(got.cpu().numpy()), bits(want))
+
+
+@pytest.mark.parametrize("n,rows,nt,m128", [(2560, 320, 1, False), (2560, 999, 3, False), (2048, 130, 8, False),
+                                            (512, 37, 2, True), (1024, 65, 13, False), (4096, 70, 5, True),
+                                            (5632, 41, 2, False), (16384, 9, 7, False)])
+def test_expert_gate_up_rows_iq3_xxs_bit_exact(dev, oracle, n, rows, nt, m128):
+    """Q8_K on the device, IQ3_XXS gate and up rows: ff, and g and u themselves, carry every bit of the oracle's
+    lane-for-lane restatement; rows outside [r0, r1) stay untouched.  Covers rows staged whole (up to 2560 columns) and
+    in chunks with a ragged last one (5632 = 8 + 8 + 6 super-blocks), every row alignment within 16 bytes (2560 columns:
+    980-byte rows), windows of several passes, and -128 codes."""
+    g = synth.rng(35)
+    x = synth.normal(g, (nt, n), 1.0)
+    act = ops.quantize_q8_k(to_dev(x, dev))
+    if m128:
+        a = act.cpu().numpy().reshape(nt, -1, 292)
+        codes = a[:, :, 4:260]
+        codes[g.integers(0, 7, size=codes.shape) == 0] = 0x80
+        act = to_dev(a.reshape(nt, -1), dev)
+    d_hi = 4e-4 * (2560 / n) ** 0.5
+    gate, up = synth.iq3_xxs_table(g, rows, n, d_hi / 8, d_hi), synth.iq3_xxs_table(g, rows, n, d_hi / 8, d_hi)
+    r0, r1 = 2, rows - 1
+    out = torch.full((nt, rows), float("nan"), dtype=torch.float32, device=dev)
+    gu = torch.zeros((2, nt, rows), dtype=torch.float32, device=dev) if nt <= 8 else None
+    ops.expert_gate_up_rows_iq3_xxs(to_dev(gate, dev), to_dev(up, dev), act, n, r0=r0, r1=r1, out=out, gu=gu)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    want, wgu = oracle.expert_gu_rows_iq3_xxs(gate, up, act.cpu().numpy(), n, r0=r0, r1=r1, want_gu=True)
+    assert np.array_equal(bits(got[:, r0:r1]), bits(want[:, r0:r1]))
+    assert np.isnan(got[:, :r0]).all() and np.isnan(got[:, r1:]).all()
+    if gu is not None:
+        assert np.array_equal(bits(gu.cpu().numpy()[:, :, r0:r1]), bits(wgu[:, :, r0:r1]))
+    assert np.abs(want[:, r0:r1]).max() < 1e3 and np.abs(wgu[0][:, r0:r1]).std() > 0.3   # gates of order one: the GLU is exercised
+
+
 def test_expert_ffn_for_a_decode_window_stage_by_stage(dev, oracle):
     """One routed expert for a window of three rows, every hand-over on the device: RMSNorm -> Q8_K -> gate / up mat-vec
     with the GLU (Q4_K) -> Q8_1 -> down mat-vec (Q5_1).  Each stage is checked bit for bit against the oracle applied to

@@ -145,6 +145,19 @@ def test_q8_k_matches_ggml_and_the_reference_avx2_form(oracle):
     assert np.array_equal(oracle.quantize_q8_k(gold["x"]), gold["blocks"])
 
 
+def test_expert_gate_up_rows_iq3_xxs_match_the_reference_avx2_kernel(oracle):
+    """tests/golden/gate_up_rows_iq3_xxs.npz: ff of the reference's own iq_gu_rows (fmt iq3_xxs, GLU included), also for
+    activations holding -128 codes, which its sign step leaves as they are; the restatement reproduces every bit."""
+    gold = np.load(os.path.join(GOLD, "gate_up_rows_iq3_xxs.npz"))
+    gate, up = gold["gate"], gold["up"]
+    for act, want in ((gold["act"], gold["ff"]), (gold["act_m128"], gold["ff_m128"])):
+        got = oracle.expert_gu_rows_iq3_xxs(gate, up, act, 2560)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    part = oracle.expert_gu_rows_iq3_xxs(gate, up, gold["act"], 2560, r0=7, r1=19)
+    assert np.array_equal(part[:, 7:19].view(np.uint32), gold["ff"][:, 7:19].view(np.uint32)) and not part[:, :7].any()
+    assert not np.array_equal(gold["ff"], gold["ff_m128"])
+
+
 def test_expert_gate_up_rows_match_the_reference_avx2_kernel(oracle):
     """tests/golden/gate_up_rows.npz: ff of the reference's own kq_gu_rows (fmt q4_k, GLU included); the scalar
     restatement reproduces every bit, also on a sub-range of rows."""
