@@ -6,61 +6,68 @@
 // over the block's eight groups of 32 values, (2 s + 1) x the four codebook bytes of the group's index byte l times the
 // sign-applied Q8_K codes 32 g + 4 l .. - adds them as floats by one fused multiply-add per super-block and lane with
 // x.d y.d (x.d WITHOUT the format's 1/4), reduces in ggml's hsum_float_8 order, multiplies the sum by 1/4 and applies
-// g / (1 + expf(-g)) * u (expf as the host C library evaluates it: exact_math.cuh).  Here EIGHT GPU LANES stand for the
-// eight AVX2 lanes of one weight row and a warp takes four (gate, up) row pairs at a time.
+// g / (1 + expf(-g)) * u (expf as the host C library evaluates it: exact_math.cuh).
+//
+// A warp takes four (gate, up) row pairs at a time: lanes 0..15 the gate rows, lanes 16..31 the up rows, FOUR GPU
+// lanes a row, lane k standing for AVX2 lanes 2 k and 2 k + 1 (eight values of every group, which share one 7-bit
+// sign index).  At three bits a weight the kernel is bound by instruction issue and shared-memory lookups, not by HBM:
+// per eight weights one 16-bit index load, two codebook loads, about twenty integer operations for signs and scale
+// and, per window row, one 8-byte activation load, two dp4a and two multiply-adds.
 //
 // The signs go onto the CODEBOOK bytes (once per weight, whatever the window), which equals the reference's negated
 // codes unless a code is -128: _mm256_sign_epi8 leaves -128 as it is.  ggml's Q8_K quantiser cannot emit -128, but a
 // CTA that finds one in its window takes the variant that negates the codes byte-wise in two's complement instead.
 //
+// The codebook (256 entries of four magnitudes as bytes) is kept 32 times in shared memory, copy j in bank j, so that
+// a warp's 32 random lookups never collide (one copy: about three wavefronts a lookup).
+//
 // A row is 98-byte blocks; with an even number of them (n a multiple of 512) rows are 4-byte aligned.  A warp copies
 // its eight rows (up to ten super-blocks of each at a time) with cp.async into its own shared-memory buffers, one unit
 // ahead of the one it computes on: 16-byte copies between the 16-byte boundaries of the source, whose offset within 16
 // bytes the shared-memory copy keeps, and up to three 4-byte copies at either end.
-// At three bits a weight the kernel is as much arithmetic as HBM traffic: per four weights one index-byte load, one
-// codebook load, about six integer operations for the signs and, per window row, one dp4a and one multiply-add.
 #include <atomic>
 
 #include "common.cuh"
 #include "exact_math.cuh"
 
 #ifndef FNB_GU_IQ3_GRID
-#define FNB_GU_IQ3_GRID 8
+#define FNB_GU_IQ3_GRID 1
 #endif
 
 namespace fnb {
 namespace {
 
-constexpr int kMaxWarps = 8;
+constexpr int kMaxWarps = 12;
 constexpr int kMaxT = 8;
 constexpr int kWholeRowBlocks = 10;                  // rows of up to ten super-blocks (2560 columns) are staged whole,
 constexpr int kChunkBlocks = 8;                      // longer ones eight super-blocks (784 = 49 x 16 bytes) at a time
 constexpr int kSlotBytes = 1008;                     // ten blocks, 12 bytes of source offset, rounded up to 16
 constexpr int kUnitBytes = 8 * kSlotBytes;           // four gate rows, then four up rows
 constexpr int kWarpStage = 2 * kUnitBytes;           // two units: the one computed on and the one in flight
-constexpr size_t kSmemLimit = 200 * 1024;            // one CTA per SM
-constexpr size_t kSmemTwo = 113 * 1024;              // two CTAs per SM (228 KB an SM, 1 KB reserved and ~1.3 KB static a CTA)
+constexpr int kGridCopies = 32;                      // the codebook once per bank
+constexpr int kGridBytes = 256 * kGridCopies * 4;
+constexpr size_t kSmemLimit = 225 * 1024;            // one CTA an SM (227 KB less the static arrays)
 constexpr int kGridPerSm = FNB_GU_IQ3_GRID;
 
 __constant__ uint16_t c_grid_packed[256] = {
 #include "iq3xxs_grid_packed.inc"
 };
 
-// the four sign bits of values 4 l .. 4 l + 3 of a group, one per byte (0x01 where the value is negated): seven stored
-// bits per eight values, the eighth their parity (ksigns_iq2xs)
-__device__ __forceinline__ uint32_t sign_bytes(uint32_t w, int sh7, int sh4) {
-    const uint32_t s7 = (w >> sh7) & 127u;
-    const uint32_t s8 = s7 | ((__popc(s7) & 1u) << 7);
-    return (((s8 >> sh4) & 15u) * 0x00204081u) & 0x01010101u;
+// 0xFF in byte j where bit j of a 4-bit sign field is set: the field times 0x10204080 puts bit j at the top of byte j,
+// and a byte permute with the replicate-sign selectors spreads it over the byte
+__device__ __forceinline__ uint32_t spread_msb(uint32_t v) {
+    uint32_t r;  // prmt's selector bit 3 replicates the chosen byte's top bit (the __byte_perm intrinsic drops that bit)
+    asm("prmt.b32 %0, %1, %1, %2;" : "=r"(r) : "r"(v), "r"(0xba98u));
+    return r;
 }
 
-// codebook bytes (4 .. 62) negated where m1 has the byte's bit: 256 - g never carries out of its byte
-__device__ __forceinline__ int signed_grid(uint32_t g, uint32_t m1) { return int((g ^ (m1 * 0xffu)) + m1); }
+// codebook bytes (4 .. 62) negated where the mask byte is 0xFF: 256 - g never carries out of its byte
+__device__ __forceinline__ int signed_grid(uint32_t g, uint32_t mff) { return int((g ^ mff) + (mff & 0x01010101u)); }
 
-// Q8_K codes negated in two's complement where m1 has the byte's bit, -128 staying -128 (_mm256_sign_epi8)
-__device__ __forceinline__ int signed_codes(uint32_t y, uint32_t m1) {
-    const uint32_t a = y ^ (m1 * 0xffu);
-    return int(((a & 0x7f7f7f7fu) + m1) ^ (a & 0x80808080u));
+// Q8_K codes negated in two's complement where the mask byte is 0xFF, -128 staying -128 (_mm256_sign_epi8)
+__device__ __forceinline__ int signed_codes(uint32_t y, uint32_t mff) {
+    const uint32_t a = y ^ mff;
+    return int(((a & 0x7f7f7f7fu) + (mff & 0x01010101u)) ^ (a & 0x80808080u));
 }
 
 // where row r's chunk of a matrix starts; a ragged last quad re-reads the last row (its results are not stored)
@@ -99,57 +106,60 @@ __device__ __forceinline__ void stage_unit(uint32_t buf_sm, const uint8_t * __re
     asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
-// one staged unit (n_blk super-blocks of four row pairs; xg, xu: this lane's gate and up row in it) against the window
+// one staged unit (n_blk super-blocks of the lane's row, x) against the window: acc[t][0 / 1] are AVX2 lanes 2 k, 2 k + 1
 template <int NT, bool WRAP>
-__device__ __forceinline__ void dot_unit(const uint8_t * xg, const uint8_t * xu, int n_blk, const uint8_t * act_sm, int nb,
-                                         int blk0, int l, const uint32_t * s_grid, float (&g)[NT], float (&u)[NT]) {
-    const int sh7 = 7 * (l >> 1), sh4 = 4 * (l & 1);
+__device__ __forceinline__ void dot_unit(const uint8_t * x, int n_blk, const uint8_t * codes_sm, const float * d_sm, int nb,
+                                         int blk0, int k, const uint32_t * grid_lane, float (&acc)[NT][2]) {
+    const int sh7 = 7 * k;
 #pragma unroll 1
-    for (int i = 0; i < n_blk; ++i, xg += 98, xu += 98) {
-        // lane l holds the sign / scale word of group l (2-byte aligned), every lane gets each group's by a shuffle
-        const uint16_t * pg = reinterpret_cast<const uint16_t *>(xg + 66 + 4 * l);
-        const uint16_t * pu = reinterpret_cast<const uint16_t *>(xu + 66 + 4 * l);
-        const uint32_t own_g = uint32_t(pg[0]) | (uint32_t(pg[1]) << 16), own_u = uint32_t(pu[0]) | (uint32_t(pu[1]) << 16);
-        const float dg = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(xg));
-        const float du = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(xu));
-        int ag[NT], au[NT];
+    for (int i = 0; i < n_blk; ++i, x += 98) {
+        // lane k holds the sign / scale words of groups k and k + 4 (2-byte aligned); each group's reaches the row's
+        // four lanes by a shuffle
+        const uint16_t * pw = reinterpret_cast<const uint16_t *>(x + 66 + 4 * k);
+        const uint32_t own_lo = uint32_t(pw[0]) | (uint32_t(pw[1]) << 16), own_hi = uint32_t(pw[8]) | (uint32_t(pw[9]) << 16);
+        const float dx = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(x));
+        int a0[NT], a1[NT];
 #pragma unroll
-        for (int t = 0; t < NT; ++t) ag[t] = 0, au[t] = 0;
-        const uint8_t * y0 = act_sm + size_t(blk0 + i) * 292 + 4 + 4 * l;
+        for (int t = 0; t < NT; ++t) a0[t] = 0, a1[t] = 0;
+        const uint8_t * y0 = codes_sm + size_t(blk0 + i) * 256 + 8 * k;
 #pragma unroll
         for (int grp = 0; grp < 8; ++grp) {
-            const uint32_t wg = __shfl_sync(kFull, own_g, grp, 8), wu = __shfl_sync(kFull, own_u, grp, 8);
-            const uint32_t cg = s_grid[xg[2 + 8 * grp + l]], cu = s_grid[xu[2 + 8 * grp + l]];
-            const uint32_t mg = sign_bytes(wg, sh7, sh4), mu = sign_bytes(wu, sh7, sh4);
-            const int scg = int(2u * (wg >> 28) + 1u), scu = int(2u * (wu >> 28) + 1u);
-            const int vg = WRAP ? int(cg) : signed_grid(cg, mg), vu = WRAP ? int(cu) : signed_grid(cu, mu);
+            const uint32_t w = __shfl_sync(kFull, grp < 4 ? own_lo : own_hi, grp & 3, 4);
+            const uint32_t h = *reinterpret_cast<const uint16_t *>(x + 2 + 8 * grp + 2 * k);  // index bytes 2 k, 2 k + 1
+            const uint32_t c0 = grid_lane[(h & 0xffu) * kGridCopies], c1 = grid_lane[(h >> 8) * kGridCopies];
+            // the group's sign index k: seven stored bits, the eighth (value 8 k + 7) their parity (ksigns_iq2xs)
+            const uint32_t s7 = (w >> sh7) & 127u;
+            const uint32_t m0 = spread_msb((s7 & 15u) * 0x10204080u);
+            const uint32_t m1 = spread_msb((s7 >> 4) * 0x10204080u + (uint32_t(__popc(s7)) << 31));
+            const int sc = int(2u * (w >> 28) + 1u);
+            const int v0 = WRAP ? int(c0) : signed_grid(c0, m0), v1 = WRAP ? int(c1) : signed_grid(c1, m1);
 #pragma unroll
             for (int t = 0; t < NT; ++t) {
-                const uint32_t y = *reinterpret_cast<const uint32_t *>(y0 + size_t(t) * nb * 292 + 32 * grp);
+                const uint2 y = *reinterpret_cast<const uint2 *>(y0 + size_t(t) * nb * 256 + 32 * grp);
                 if (WRAP) {
-                    ag[t] += scg * __dp4a(vg, signed_codes(y, mg), 0);
-                    au[t] += scu * __dp4a(vu, signed_codes(y, mu), 0);
+                    a0[t] += sc * __dp4a(v0, signed_codes(y.x, m0), 0);
+                    a1[t] += sc * __dp4a(v1, signed_codes(y.y, m1), 0);
                 } else {
-                    ag[t] += scg * __dp4a(vg, int(y), 0);
-                    au[t] += scu * __dp4a(vu, int(y), 0);
+                    a0[t] += sc * __dp4a(v0, int(y.x), 0);
+                    a1[t] += sc * __dp4a(v1, int(y.y), 0);
                 }
             }
         }
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
-            const float yd = *reinterpret_cast<const float *>(act_sm + (size_t(t) * nb + blk0 + i) * 292);
-            g[t] = __fmaf_rn(__fmul_rn(dg, yd), float(ag[t]), g[t]);
-            u[t] = __fmaf_rn(__fmul_rn(du, yd), float(au[t]), u[t]);
+            const float dxy = __fmul_rn(dx, d_sm[t * nb + blk0 + i]);
+            acc[t][0] = __fmaf_rn(dxy, float(a0[t]), acc[t][0]);
+            acc[t][1] = __fmaf_rn(dxy, float(a1[t]), acc[t][1]);
         }
     }
 }
 
 template <int NT, bool WRAP>
 __device__ __forceinline__ void run_warp(const uint8_t * __restrict__ gate, const uint8_t * __restrict__ up, int64_t row_bytes,
-                                         int nb, const uint8_t * act_sm, uint8_t * stage, const uint32_t * s_grid,
-                                         float * __restrict__ ff, int64_t ff_stride, float * __restrict__ gu, int64_t r0,
-                                         int64_t r1) {
-    const int lane = threadIdx.x & 31, l = lane & 7, sub = lane >> 3;
+                                         int nb, const uint8_t * codes_sm, const float * d_sm, uint8_t * stage,
+                                         const uint32_t * grid_sm, float * __restrict__ ff, int64_t ff_stride,
+                                         float * __restrict__ gu, int64_t r0, int64_t r1) {
+    const int lane = threadIdx.x & 31, k = lane & 3, sub = (lane >> 2) & 3, mat = lane >> 4;
     const int warps = blockDim.x >> 5;
     const int64_t n_quads = (r1 - r0 + 3) / 4, stride = int64_t(gridDim.x) * warps;
     const int chunk_blocks = nb <= kWholeRowBlocks ? nb : kChunkBlocks;
@@ -158,56 +168,54 @@ __device__ __forceinline__ void run_warp(const uint8_t * __restrict__ gate, cons
     int64_t q = int64_t(blockIdx.x) * warps + (threadIdx.x >> 5);
     if (q >= n_quads) return;
     const uint32_t stage_sm = uint32_t(__cvta_generic_to_shared(stage));
-    int c = 0, k = 0;
+    const uint8_t * mine = mat == 0 ? gate : up;
+    int c = 0, trip = 0;
     stage_unit(stage_sm, gate, up, row_bytes, r0 + 4 * q, r1, 0, blocks_of(0) * 98, lane);
-    float g[NT], u[NT];
+    float acc[NT][2];
 #pragma unroll
-    for (int t = 0; t < NT; ++t) g[t] = 0.0f, u[t] = 0.0f;
+    for (int t = 0; t < NT; ++t) acc[t][0] = 0.0f, acc[t][1] = 0.0f;
     for (;;) {
         int64_t qn = q;
         int cn = c + 1;
         if (cn == n_chunks) cn = 0, qn = q + stride;
         const bool more = qn < n_quads;
         if (more) {
-            stage_unit(stage_sm + uint32_t((k + 1) & 1) * kUnitBytes, gate, up, row_bytes, r0 + 4 * qn, r1, cn,
+            stage_unit(stage_sm + uint32_t((trip + 1) & 1) * kUnitBytes, gate, up, row_bytes, r0 + 4 * qn, r1, cn,
                        blocks_of(cn) * 98, lane);
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncwarp();
+        const int64_t r = r0 + 4 * q + sub;
         {
-            const uint8_t * buf = stage + (k & 1) * kUnitBytes;
-            const int64_t r = r0 + 4 * q + sub;
-            const uintptr_t pg = reinterpret_cast<uintptr_t>(chunk_src(gate, row_bytes, r, r1, c));
-            const uintptr_t pu = reinterpret_cast<uintptr_t>(chunk_src(up, row_bytes, r, r1, c));
-            dot_unit<NT, WRAP>(buf + sub * kSlotBytes + (pg & 15), buf + (4 + sub) * kSlotBytes + (pu & 15), blocks_of(c), act_sm,
-                               nb, c * chunk_blocks, l, s_grid, g, u);
+            const uintptr_t src = reinterpret_cast<uintptr_t>(chunk_src(mine, row_bytes, r, r1, c));
+            const uint8_t * x = stage + (trip & 1) * kUnitBytes + (4 * mat + sub) * kSlotBytes + (src & 15);
+            dot_unit<NT, WRAP>(x, blocks_of(c), codes_sm, d_sm, nb, c * chunk_blocks, k, grid_sm + lane, acc);
         }
         __syncwarp();  // every lane is done with the buffer the next trip's copies overwrite
         if (c == n_chunks - 1) {
-            const int64_t r = r0 + 4 * q + sub;
-            const bool live = r < r1;
 #pragma unroll
             for (int t = 0; t < NT; ++t) {
-                // ggml's hsum_float_8: lane i + 4 onto lane i, lanes 2, 3 onto 0, 1, lane 1 onto lane 0
-                float a = g[t], b = u[t];
-                a = __fadd_rn(__shfl_down_sync(kFull, a, 4, 8), a), b = __fadd_rn(__shfl_down_sync(kFull, b, 4, 8), b);
-                a = __fadd_rn(a, __shfl_down_sync(kFull, a, 2, 8)), b = __fadd_rn(b, __shfl_down_sync(kFull, b, 2, 8));
-                a = __fadd_rn(a, __shfl_down_sync(kFull, a, 1, 8)), b = __fadd_rn(b, __shfl_down_sync(kFull, b, 1, 8));
-                if (l == 0 && live) {
-                    const float gs = __fmul_rn(0.25f, a), us = __fmul_rn(0.25f, b);
-                    ff[int64_t(t) * ff_stride + r] = __fmul_rn(__fdiv_rn(gs, __fadd_rn(1.0f, exact_expf(-gs))), us);
+                // ggml's hsum_float_8, r_l on lane l / 2: r_l + r_(l + 4) (two lanes up), then lanes 2, 3 onto 0, 1 (one
+                // lane up), then lane 1 onto lane 0 (the lane's own pair)
+                float a = acc[t][0], b = acc[t][1];
+                a = __fadd_rn(__shfl_down_sync(kFull, a, 2, 4), a), b = __fadd_rn(__shfl_down_sync(kFull, b, 2, 4), b);
+                a = __fadd_rn(a, __shfl_down_sync(kFull, a, 1, 4)), b = __fadd_rn(b, __shfl_down_sync(kFull, b, 1, 4));
+                const float dot = __fmul_rn(0.25f, __fadd_rn(a, b));
+                const float us = __shfl_down_sync(kFull, dot, 16);  // the up row's sits 16 lanes above the gate row's
+                if (mat == 0 && k == 0 && r < r1) {
+                    ff[int64_t(t) * ff_stride + r] = __fmul_rn(__fdiv_rn(dot, __fadd_rn(1.0f, exact_expf(-dot))), us);
                     if (gu != nullptr) {
-                        gu[int64_t(t) * ff_stride + r] = gs;
+                        gu[int64_t(t) * ff_stride + r] = dot;
                         gu[(int64_t(NT) + t) * ff_stride + r] = us;
                     }
                 }
-                g[t] = 0.0f, u[t] = 0.0f;
+                acc[t][0] = 0.0f, acc[t][1] = 0.0f;
             }
         }
         if (!more) break;
-        q = qn, c = cn, ++k;
+        q = qn, c = cn, ++trip;
     }
 }
 
@@ -216,8 +224,12 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
     gate_up_iq3_xxs_kernel(const uint8_t * __restrict__ gate, const uint8_t * __restrict__ up, int64_t row_bytes, int nb,
                            const uint8_t * __restrict__ act, int64_t act_stride, int act_bytes, float * __restrict__ ff,
                            int64_t ff_stride, float * __restrict__ gu, int64_t r0, int64_t r1) {
-    extern __shared__ __align__(16) uint8_t smem[];  // the window's Q8_K blocks [NT][nb][292], then each warp's two units
-    __shared__ uint32_t s_grid[256];                 // the codebook's four magnitudes per entry as bytes
+    // the codebook copies, the window's codes [NT][nb][256] and scales [NT][nb], then each warp's two units
+    extern __shared__ __align__(16) uint8_t smem[];
+    __shared__ uint32_t s_grid[256];  // the codebook's four magnitudes per entry as bytes
+    uint32_t * grid_sm = reinterpret_cast<uint32_t *>(smem);
+    uint8_t * codes_sm = smem + kGridBytes;
+    float * d_sm = reinterpret_cast<float *>(codes_sm + size_t(NT) * nb * 256);
     load_exp2_table();
     for (int i = threadIdx.x; i < 256; i += blockDim.x) {
         const uint32_t c = c_grid_packed[i];
@@ -230,22 +242,26 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
         s_grid[i] = w;
     }
     int has_m128 = 0;
-    for (int i = threadIdx.x; i < NT * nb * 73; i += blockDim.x) {
-        const int t = i / (nb * 73), k = i - t * nb * 73;
-        const uint32_t w = __ldg(reinterpret_cast<const uint32_t *>(act + int64_t(t) * act_stride) + k);
-        reinterpret_cast<uint32_t *>(smem)[i] = w;
-        const int word = k % 73;
-        if (word >= 1 && word <= 64) {  // a code byte equal to 0x80
-            const uint32_t v = w ^ 0x80808080u;
+    for (int i = threadIdx.x; i < NT * nb * 65; i += blockDim.x) {  // the scale and the 64 code words of every block
+        const int blk = i / 65, word = i - blk * 65;
+        const int t = blk / nb, b = blk - t * nb;
+        const uint32_t w = __ldg(reinterpret_cast<const uint32_t *>(act + int64_t(t) * act_stride) + b * 73 + word);
+        if (word == 0) {
+            d_sm[blk] = __uint_as_float(w);
+        } else {
+            reinterpret_cast<uint32_t *>(codes_sm)[blk * 64 + word - 1] = w;
+            const uint32_t v = w ^ 0x80808080u;  // a code byte equal to 0x80
             has_m128 |= ((v - 0x01010101u) & ~v & 0x80808080u) != 0u;
         }
     }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 256 * kGridCopies; i += blockDim.x) grid_sm[i] = s_grid[i / kGridCopies];
     const int wrap = __syncthreads_or(has_m128);
-    uint8_t * stage = smem + act_bytes + size_t(threadIdx.x >> 5) * kWarpStage;
+    uint8_t * stage = smem + kGridBytes + act_bytes + size_t(threadIdx.x >> 5) * kWarpStage;
     if (wrap) {
-        run_warp<NT, true>(gate, up, row_bytes, nb, smem, stage, s_grid, ff, ff_stride, gu, r0, r1);
+        run_warp<NT, true>(gate, up, row_bytes, nb, codes_sm, d_sm, stage, grid_sm, ff, ff_stride, gu, r0, r1);
     } else {
-        run_warp<NT, false>(gate, up, row_bytes, nb, smem, stage, s_grid, ff, ff_stride, gu, r0, r1);
+        run_warp<NT, false>(gate, up, row_bytes, nb, codes_sm, d_sm, stage, grid_sm, ff, ff_stride, gu, r0, r1);
     }
 }
 
@@ -264,9 +280,9 @@ bool ensure_configured() {
     return true;
 }
 
-// window rows one launch can hold for nb super-blocks a row (their Q8_K blocks and at least four warps' buffers)
+// window rows one launch can hold for nb super-blocks a row (their codes and scales and at least two warps' buffers)
 inline int window_rows(int nb) {
-    const size_t per_t = size_t(nb) * 292, room = kSmemLimit - 4 * size_t(kWarpStage) - 16;
+    const size_t per_t = size_t(nb) * 260, room = kSmemLimit - kGridBytes - 2 * size_t(kWarpStage) - 16;
     const size_t m = room / per_t;
     return int(m > size_t(kMaxT) ? size_t(kMaxT) : m);
 }
@@ -274,14 +290,12 @@ inline int window_rows(int nb) {
 template <int NT>
 int32_t launch_nt(const uint8_t * gate, const uint8_t * up, int64_t row_bytes, int nb, const uint8_t * act, int64_t act_stride,
                   float * ff, int64_t ff_stride, float * gu, int64_t r0, int64_t r1, cudaStream_t s) {
-    const size_t act_bytes = (size_t(NT) * nb * 292 + 15) & ~size_t(15);
-    // as many warps as leave room for two CTAs on an SM, else one CTA of up to eight
-    int warps = act_bytes < kSmemTwo ? int((kSmemTwo - act_bytes) / kWarpStage) : 0;
-    if (warps < 4) warps = int((kSmemLimit - act_bytes) / kWarpStage);
+    const size_t act_bytes = (size_t(NT) * nb * 260 + 15) & ~size_t(15);
+    if (kGridBytes + act_bytes + kWarpStage > kSmemLimit) return FNB_REJECTED;
+    int warps = int((kSmemLimit - kGridBytes - act_bytes) / kWarpStage);  // one CTA an SM, as many warps as fit
     warps = warps > kMaxWarps ? kMaxWarps : warps;
-    if (warps < 1) return FNB_REJECTED;
     if (!ensure_configured<NT>()) return FNB_LAUNCH_FAILED;
-    const size_t smem = act_bytes + size_t(warps) * kWarpStage;
+    const size_t smem = kGridBytes + act_bytes + size_t(warps) * kWarpStage;
     const int64_t quads = (r1 - r0 + 3) / 4;
     const int grid = grid_for((quads + warps - 1) / warps, kGridPerSm);
     gate_up_iq3_xxs_kernel<NT><<<grid, warps * 32, smem, s>>>(gate, up, row_bytes, nb, act, act_stride, int(act_bytes), ff,
