@@ -18,8 +18,10 @@
 // codes unless a code is -128: _mm256_sign_epi8 leaves -128 as it is.  ggml's Q8_K quantiser cannot emit -128, but a
 // CTA that finds one in its window takes the variant that negates the codes byte-wise in two's complement instead.
 //
-// The codebook (256 entries of four magnitudes as bytes) is kept 32 times in shared memory, copy j in bank j, so that
-// a warp's 32 random lookups never collide (one copy: about three wavefronts a lookup).
+// The kernel is bound by instruction issue, so what can be a conflict-free shared-memory lookup is one: the codebook
+// (256 entries of four magnitudes as bytes) is kept 32 times, copy j in bank j (one copy: about three wavefronts a
+// lookup), and the 128 sign indices' eight byte masks (seven stored bits and their parity) 16 times, copy j in the
+// bank pair 2 j, which replaces ten integer operations per eight weights.
 //
 // A row is 98-byte blocks; with an even number of them (n a multiple of 512) rows are 4-byte aligned.  A warp copies
 // its eight rows (up to ten super-blocks of each at a time) with cp.async into its own shared-memory buffers, one unit
@@ -46,6 +48,10 @@ constexpr int kUnitBytes = 8 * kSlotBytes;           // four gate rows, then fou
 constexpr int kWarpStage = 2 * kUnitBytes;           // two units: the one computed on and the one in flight
 constexpr int kGridCopies = 32;                      // the codebook once per bank
 constexpr int kGridBytes = 256 * kGridCopies * 4;
+constexpr int kSignCopies = 16;                      // 8-byte entries: a half-warp's lookups fill the 32 banks
+constexpr int kSignBytes = 128 * kSignCopies * 8;
+constexpr int kTableBytes = kGridBytes + kSignBytes;
+constexpr int kSpanBytes = 4 * kWholeRowBlocks * 98 + 16;  // four whole rows, back to back as in global memory
 constexpr size_t kSmemLimit = 225 * 1024;            // one CTA an SM (227 KB less the static arrays)
 constexpr int kGridPerSm = FNB_GU_IQ3_GRID;
 
@@ -106,10 +112,20 @@ __device__ __forceinline__ void stage_unit(uint32_t buf_sm, const uint8_t * __re
     asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
+// rows of up to ten super-blocks: the quad's four gate rows are one contiguous span of the matrix, its up rows another
+__device__ __forceinline__ void stage_unit_whole(uint32_t buf_sm, const uint8_t * __restrict__ gate,
+                                                 const uint8_t * __restrict__ up, int64_t row_bytes, int64_t r4, int64_t r1,
+                                                 int lane) {
+    const int rows = r1 - r4 < 4 ? int(r1 - r4) : 4;  // a ragged last quad leaves its missing rows' bytes as they were
+    stage_slot(buf_sm, gate + r4 * row_bytes, rows * int(row_bytes), lane);
+    stage_slot(buf_sm + kSpanBytes, up + r4 * row_bytes, rows * int(row_bytes), lane);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
 // one staged unit (n_blk super-blocks of the lane's row, x) against the window: acc[t][0 / 1] are AVX2 lanes 2 k, 2 k + 1
 template <int NT, bool WRAP>
 __device__ __forceinline__ void dot_unit(const uint8_t * x, int n_blk, const uint8_t * codes_sm, const float * d_sm, int nb,
-                                         int blk0, int k, const uint32_t * grid_lane, float (&acc)[NT][2]) {
+                                         int blk0, int k, const uint32_t * grid_lane, const uint2 * sign_lane, float (&acc)[NT][2]) {
     const int sh7 = 7 * k;
 #pragma unroll 1
     for (int i = 0; i < n_blk; ++i, x += 98) {
@@ -125,12 +141,10 @@ __device__ __forceinline__ void dot_unit(const uint8_t * x, int n_blk, const uin
 #pragma unroll
         for (int grp = 0; grp < 8; ++grp) {
             const uint32_t w = __shfl_sync(kFull, grp < 4 ? own_lo : own_hi, grp & 3, 4);
-            const uint32_t h = *reinterpret_cast<const uint16_t *>(x + 2 + 8 * grp + 2 * k);  // index bytes 2 k, 2 k + 1
-            const uint32_t c0 = grid_lane[(h & 0xffu) * kGridCopies], c1 = grid_lane[(h >> 8) * kGridCopies];
-            // the group's sign index k: seven stored bits, the eighth (value 8 k + 7) their parity (ksigns_iq2xs)
-            const uint32_t s7 = (w >> sh7) & 127u;
-            const uint32_t m0 = spread_msb((s7 & 15u) * 0x10204080u);
-            const uint32_t m1 = spread_msb((s7 >> 4) * 0x10204080u + (uint32_t(__popc(s7)) << 31));
+            const uint8_t * q = x + 2 + 8 * grp + 2 * k;  // index bytes 2 k, 2 k + 1
+            const uint32_t c0 = grid_lane[uint32_t(q[0]) * kGridCopies], c1 = grid_lane[uint32_t(q[1]) * kGridCopies];
+            const uint2 sg = sign_lane[((w >> sh7) & 127u) * kSignCopies];  // the group's sign index k
+            const uint32_t m0 = sg.x, m1 = sg.y;
             const int sc = int(2u * (w >> 28) + 1u);
             const int v0 = WRAP ? int(c0) : signed_grid(c0, m0), v1 = WRAP ? int(c1) : signed_grid(c1, m1);
 #pragma unroll
@@ -157,12 +171,13 @@ __device__ __forceinline__ void dot_unit(const uint8_t * x, int n_blk, const uin
 template <int NT, bool WRAP>
 __device__ __forceinline__ void run_warp(const uint8_t * __restrict__ gate, const uint8_t * __restrict__ up, int64_t row_bytes,
                                          int nb, const uint8_t * codes_sm, const float * d_sm, uint8_t * stage,
-                                         const uint32_t * grid_sm, float * __restrict__ ff, int64_t ff_stride,
-                                         float * __restrict__ gu, int64_t r0, int64_t r1) {
+                                         const uint32_t * grid_sm, const uint2 * sign_sm, float * __restrict__ ff,
+                                         int64_t ff_stride, float * __restrict__ gu, int64_t r0, int64_t r1) {
     const int lane = threadIdx.x & 31, k = lane & 3, sub = (lane >> 2) & 3, mat = lane >> 4;
     const int warps = blockDim.x >> 5;
     const int64_t n_quads = (r1 - r0 + 3) / 4, stride = int64_t(gridDim.x) * warps;
-    const int chunk_blocks = nb <= kWholeRowBlocks ? nb : kChunkBlocks;
+    const bool whole = nb <= kWholeRowBlocks;
+    const int chunk_blocks = whole ? nb : kChunkBlocks;
     const int n_chunks = (nb + chunk_blocks - 1) / chunk_blocks;
     const auto blocks_of = [&](int chunk) { return chunk == n_chunks - 1 ? nb - chunk * chunk_blocks : chunk_blocks; };
     int64_t q = int64_t(blockIdx.x) * warps + (threadIdx.x >> 5);
@@ -170,7 +185,11 @@ __device__ __forceinline__ void run_warp(const uint8_t * __restrict__ gate, cons
     const uint32_t stage_sm = uint32_t(__cvta_generic_to_shared(stage));
     const uint8_t * mine = mat == 0 ? gate : up;
     int c = 0, trip = 0;
-    stage_unit(stage_sm, gate, up, row_bytes, r0 + 4 * q, r1, 0, blocks_of(0) * 98, lane);
+    if (whole) {
+        stage_unit_whole(stage_sm, gate, up, row_bytes, r0 + 4 * q, r1, lane);
+    } else {
+        stage_unit(stage_sm, gate, up, row_bytes, r0 + 4 * q, r1, 0, blocks_of(0) * 98, lane);
+    }
     float acc[NT][2];
 #pragma unroll
     for (int t = 0; t < NT; ++t) acc[t][0] = 0.0f, acc[t][1] = 0.0f;
@@ -180,8 +199,12 @@ __device__ __forceinline__ void run_warp(const uint8_t * __restrict__ gate, cons
         if (cn == n_chunks) cn = 0, qn = q + stride;
         const bool more = qn < n_quads;
         if (more) {
-            stage_unit(stage_sm + uint32_t((trip + 1) & 1) * kUnitBytes, gate, up, row_bytes, r0 + 4 * qn, r1, cn,
-                       blocks_of(cn) * 98, lane);
+            const uint32_t next_sm = stage_sm + uint32_t((trip + 1) & 1) * kUnitBytes;
+            if (whole) {
+                stage_unit_whole(next_sm, gate, up, row_bytes, r0 + 4 * qn, r1, lane);
+            } else {
+                stage_unit(next_sm, gate, up, row_bytes, r0 + 4 * qn, r1, cn, blocks_of(cn) * 98, lane);
+            }
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
             asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -189,9 +212,16 @@ __device__ __forceinline__ void run_warp(const uint8_t * __restrict__ gate, cons
         __syncwarp();
         const int64_t r = r0 + 4 * q + sub;
         {
-            const uintptr_t src = reinterpret_cast<uintptr_t>(chunk_src(mine, row_bytes, r, r1, c));
-            const uint8_t * x = stage + (trip & 1) * kUnitBytes + (4 * mat + sub) * kSlotBytes + (src & 15);
-            dot_unit<NT, WRAP>(x, blocks_of(c), codes_sm, d_sm, nb, c * chunk_blocks, k, grid_sm + lane, acc);
+            const uint8_t * x = stage + (trip & 1) * kUnitBytes;
+            if (whole) {
+                const uintptr_t src = reinterpret_cast<uintptr_t>(mine + (r0 + 4 * q) * row_bytes);
+                x += mat * kSpanBytes + (src & 15) + sub * int(row_bytes);
+            } else {
+                const uintptr_t src = reinterpret_cast<uintptr_t>(chunk_src(mine, row_bytes, r, r1, c));
+                x += (4 * mat + sub) * kSlotBytes + (src & 15);
+            }
+            dot_unit<NT, WRAP>(x, blocks_of(c), codes_sm, d_sm, nb, c * chunk_blocks, k, grid_sm + lane,
+                               sign_sm + (lane & (kSignCopies - 1)), acc);
         }
         __syncwarp();  // every lane is done with the buffer the next trip's copies overwrite
         if (c == n_chunks - 1) {
@@ -224,11 +254,13 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
     gate_up_iq3_xxs_kernel(const uint8_t * __restrict__ gate, const uint8_t * __restrict__ up, int64_t row_bytes, int nb,
                            const uint8_t * __restrict__ act, int64_t act_stride, int act_bytes, float * __restrict__ ff,
                            int64_t ff_stride, float * __restrict__ gu, int64_t r0, int64_t r1) {
-    // the codebook copies, the window's codes [NT][nb][256] and scales [NT][nb], then each warp's two units
+    // the codebook copies, the sign masks' copies, the window's codes [NT][nb][256] and scales [NT][nb], then each
+    // warp's two units
     extern __shared__ __align__(16) uint8_t smem[];
     __shared__ uint32_t s_grid[256];  // the codebook's four magnitudes per entry as bytes
     uint32_t * grid_sm = reinterpret_cast<uint32_t *>(smem);
-    uint8_t * codes_sm = smem + kGridBytes;
+    uint2 * sign_sm = reinterpret_cast<uint2 *>(smem + kGridBytes);
+    uint8_t * codes_sm = smem + kTableBytes;
     float * d_sm = reinterpret_cast<float *>(codes_sm + size_t(NT) * nb * 256);
     load_exp2_table();
     for (int i = threadIdx.x; i < 256; i += blockDim.x) {
@@ -256,12 +288,18 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
     }
     __syncthreads();
     for (int i = threadIdx.x; i < 256 * kGridCopies; i += blockDim.x) grid_sm[i] = s_grid[i / kGridCopies];
+    for (int i = threadIdx.x; i < 128 * kSignCopies; i += blockDim.x) {
+        // sign index s7: values 0 .. 6 of its eight take bits 0 .. 6, value 7 their parity (ksigns_iq2xs)
+        const uint32_t s7 = uint32_t(i) / kSignCopies;
+        sign_sm[i] = make_uint2(spread_msb((s7 & 15u) * 0x10204080u),
+                                spread_msb((s7 >> 4) * 0x10204080u + (uint32_t(__popc(s7)) << 31)));
+    }
     const int wrap = __syncthreads_or(has_m128);
-    uint8_t * stage = smem + kGridBytes + act_bytes + size_t(threadIdx.x >> 5) * kWarpStage;
+    uint8_t * stage = smem + kTableBytes + act_bytes + size_t(threadIdx.x >> 5) * kWarpStage;
     if (wrap) {
-        run_warp<NT, true>(gate, up, row_bytes, nb, codes_sm, d_sm, stage, grid_sm, ff, ff_stride, gu, r0, r1);
+        run_warp<NT, true>(gate, up, row_bytes, nb, codes_sm, d_sm, stage, grid_sm, sign_sm, ff, ff_stride, gu, r0, r1);
     } else {
-        run_warp<NT, false>(gate, up, row_bytes, nb, codes_sm, d_sm, stage, grid_sm, ff, ff_stride, gu, r0, r1);
+        run_warp<NT, false>(gate, up, row_bytes, nb, codes_sm, d_sm, stage, grid_sm, sign_sm, ff, ff_stride, gu, r0, r1);
     }
 }
 
@@ -282,7 +320,7 @@ bool ensure_configured() {
 
 // window rows one launch can hold for nb super-blocks a row (their codes and scales and at least two warps' buffers)
 inline int window_rows(int nb) {
-    const size_t per_t = size_t(nb) * 260, room = kSmemLimit - kGridBytes - 2 * size_t(kWarpStage) - 16;
+    const size_t per_t = size_t(nb) * 260, room = kSmemLimit - kTableBytes - 2 * size_t(kWarpStage) - 16;
     const size_t m = room / per_t;
     return int(m > size_t(kMaxT) ? size_t(kMaxT) : m);
 }
@@ -291,11 +329,11 @@ template <int NT>
 int32_t launch_nt(const uint8_t * gate, const uint8_t * up, int64_t row_bytes, int nb, const uint8_t * act, int64_t act_stride,
                   float * ff, int64_t ff_stride, float * gu, int64_t r0, int64_t r1, cudaStream_t s) {
     const size_t act_bytes = (size_t(NT) * nb * 260 + 15) & ~size_t(15);
-    if (kGridBytes + act_bytes + kWarpStage > kSmemLimit) return FNB_REJECTED;
-    int warps = int((kSmemLimit - kGridBytes - act_bytes) / kWarpStage);  // one CTA an SM, as many warps as fit
+    if (kTableBytes + act_bytes + kWarpStage > kSmemLimit) return FNB_REJECTED;
+    int warps = int((kSmemLimit - kTableBytes - act_bytes) / kWarpStage);  // one CTA an SM, as many warps as fit
     warps = warps > kMaxWarps ? kMaxWarps : warps;
     if (!ensure_configured<NT>()) return FNB_LAUNCH_FAILED;
-    const size_t smem = kGridBytes + act_bytes + size_t(warps) * kWarpStage;
+    const size_t smem = kTableBytes + act_bytes + size_t(warps) * kWarpStage;
     const int64_t quads = (r1 - r0 + 3) / 4;
     const int grid = grid_for((quads + warps - 1) / warps, kGridPerSm);
     gate_up_iq3_xxs_kernel<NT><<<grid, warps * 32, smem, s>>>(gate, up, row_bytes, nb, act, act_stride, int(act_bytes), ff,
