@@ -11,8 +11,8 @@
 // A warp takes four (gate, up) row pairs at a time: lanes 0..15 the gate rows, lanes 16..31 the up rows, FOUR GPU
 // lanes a row, lane k standing for AVX2 lanes 2 k and 2 k + 1 (eight values of every group, which share one 7-bit
 // sign index).  At three bits a weight the kernel is bound by instruction issue and shared-memory lookups, not by HBM:
-// per eight weights one 16-bit index load, two codebook loads, about twenty integer operations for signs and scale
-// and, per window row, one 8-byte activation load, two dp4a and two multiply-adds.
+// per eight weights one 16-bit index load, two codebook loads, one sign-mask load, about fifteen integer operations
+// and, per window row, half a 16-byte activation load, two dp4a and two multiply-adds.
 //
 // The signs go onto the CODEBOOK bytes (once per weight, whatever the window), which equals the reference's negated
 // codes unless a code is -128: _mm256_sign_epi8 leaves -128 as it is.  ggml's Q8_K quantiser cannot emit -128, but a
@@ -137,19 +137,22 @@ __device__ __forceinline__ void dot_unit(const uint8_t * x, int n_blk, const uin
         int a0[NT], a1[NT];
 #pragma unroll
         for (int t = 0; t < NT; ++t) a0[t] = 0, a1[t] = 0;
-        const uint8_t * y0 = codes_sm + size_t(blk0 + i) * 256 + 8 * k;
+        const uint8_t * y0 = codes_sm + size_t(blk0 + i) * 256 + 16 * k;
+        uint4 y4[NT];
 #pragma unroll
         for (int grp = 0; grp < 8; ++grp) {
             const uint32_t w = __shfl_sync(kFull, grp < 4 ? own_lo : own_hi, grp & 3, 4);
-            const uint8_t * q = x + 2 + 8 * grp + 2 * k;  // index bytes 2 k, 2 k + 1
-            const uint32_t c0 = grid_lane[uint32_t(q[0]) * kGridCopies], c1 = grid_lane[uint32_t(q[1]) * kGridCopies];
+            const uint32_t h = *reinterpret_cast<const uint16_t *>(x + 2 + 8 * grp + 2 * k);  // index bytes 2 k, 2 k + 1
+            const uint32_t c0 = grid_lane[(h & 0xffu) * kGridCopies], c1 = grid_lane[(h >> 8) * kGridCopies];
             const uint2 sg = sign_lane[((w >> sh7) & 127u) * kSignCopies];  // the group's sign index k
             const uint32_t m0 = sg.x, m1 = sg.y;
             const int sc = int(2u * (w >> 28) + 1u);
             const int v0 = WRAP ? int(c0) : signed_grid(c0, m0), v1 = WRAP ? int(c1) : signed_grid(c1, m1);
 #pragma unroll
             for (int t = 0; t < NT; ++t) {
-                const uint2 y = *reinterpret_cast<const uint2 *>(y0 + size_t(t) * nb * 256 + 32 * grp);
+                // one 16-byte load brings the lane's codes of two groups (the window's blocks are stored that way)
+                if ((grp & 1) == 0) y4[t] = *reinterpret_cast<const uint4 *>(y0 + size_t(t) * nb * 256 + 32 * grp);
+                const uint2 y = (grp & 1) == 0 ? make_uint2(y4[t].x, y4[t].y) : make_uint2(y4[t].z, y4[t].w);
                 if (WRAP) {
                     a0[t] += sc * __dp4a(v0, signed_codes(y.x, m0), 0);
                     a1[t] += sc * __dp4a(v1, signed_codes(y.y, m1), 0);
@@ -281,7 +284,10 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
         if (word == 0) {
             d_sm[blk] = __uint_as_float(w);
         } else {
-            reinterpret_cast<uint32_t *>(codes_sm)[blk * 64 + word - 1] = w;
+            // codes 32 g + 8 k .. + 7 of group g (two words) go to 64 (g / 2) + 16 k + 8 (g % 2): lane k's codes of a pair
+            // of groups are 16 contiguous bytes
+            const int j = word - 1, g = j >> 3, kk = (j & 7) >> 1;
+            reinterpret_cast<uint32_t *>(codes_sm)[blk * 64 + (g >> 1) * 16 + kk * 4 + (g & 1) * 2 + (j & 1)] = w;
             const uint32_t v = w ^ 0x80808080u;  // a code byte equal to 0x80
             has_m128 |= ((v - 0x01010101u) & ~v & 0x80808080u) != 0u;
         }
