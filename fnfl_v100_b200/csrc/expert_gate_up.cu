@@ -5,9 +5,13 @@
 // keeps, per (row, t), eight int32 lanes of scale-weighted 4-byte dot products per super-block, adds them as floats by
 // one fused multiply-add per super-block and lane with d = y.d x.d, keeps four lanes of mins x block sums with
 // -y.d x.dmin, reduces once at the end in a fixed order and applies g / (1 + expf(-g)) * u (expf as the host C
-// library evaluates it: exact_math.cuh).  Here EIGHT GPU LANES stand for the eight AVX2 lanes of one weight row: lane l
-// reads bytes 4 l .. 4 l + 3 of each of the row's 32-byte nibble groups straight from global memory (eight lanes, one
-// 32-byte sector), the horizontal sums are three shuffle steps in the AVX2 order.
+// library evaluates it: exact_math.cuh).  Here FOUR GPU LANES stand for the eight AVX2 lanes of one weight row: lane k
+// reads bytes 8 k .. 8 k + 7 of each of the row's 32-byte nibble groups straight from global memory (four lanes, one
+// 32-byte sector) and keeps AVX2 lanes 2 k, 2 k + 1 and mins lane k; a warp takes four (gate, up) row pairs, the gate
+// rows on lanes 0..15 and the up rows on lanes 16..31; the horizontal sums are shuffle steps in the AVX2 order.
+// (With eight lanes a row every lane repeated the scale unpacking and header decode for half the weights: 0.115 /
+// 0.244 / 0.578 ms against this form's 0.089 / 0.160 / 0.351 ms at 2 x 131072 rows of 2560 columns and windows of
+// 1 / 3 / 8 rows.)
 //
 // HBM-bound on the weights at the window sizes decode uses: 2 x 1440 bytes per output row at 2560 columns, read once
 // for all window rows; the window's Q8_K blocks sit in shared memory.
@@ -22,113 +26,55 @@ constexpr int kMaxT = 8;
 
 // the eight six-bit scales and eight mins from the 12 packed bytes, four to a word, as ggml unpacks them for its
 // vector kernels (the utmp shuffle of ggml_vec_dot_q4_K_q8_K; cpu_kq_avx2.cpp:154-166): about ten logic operations
-// for all sixteen values, where get_scale_min_k4 per value costs six each
-__device__ __forceinline__ void scales_mins(uint32_t u0, uint32_t u1, uint32_t u2, int (&sc)[8], int (&mn)[8]) {
-    const uint32_t k1 = 0x3f3f3f3fu, k2 = 0x0f0f0f0fu, k3 = 0x03030303u;
-    const uint32_t s_lo = u0 & k1, s_hi = (u2 & k2) | (((u0 >> 6) & k3) << 4);
-    const uint32_t m_lo = u1 & k1, m_hi = ((u2 >> 4) & k2) | (((u1 >> 6) & k3) << 4);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        sc[j] = int((s_lo >> (8 * j)) & 0xffu), sc[j + 4] = int((s_hi >> (8 * j)) & 0xffu);
-        mn[j] = int((m_lo >> (8 * j)) & 0xffu), mn[j + 4] = int((m_hi >> (8 * j)) & 0xffu);
+// for all sixteen values, where get_scale_min_k4 per value costs six each.  s_lo / m_lo: values 0..3, s_hi / m_hi: 4..7.
+struct scales_mins {
+    uint32_t s_lo, s_hi, m_lo, m_hi;
+    __device__ __forceinline__ scales_mins(uint32_t u0, uint32_t u1, uint32_t u2) {
+        const uint32_t k1 = 0x3f3f3f3fu, k2 = 0x0f0f0f0fu, k3 = 0x03030303u;
+        s_lo = u0 & k1, s_hi = (u2 & k2) | (((u0 >> 6) & k3) << 4);
+        m_lo = u1 & k1, m_hi = ((u2 >> 4) & k2) | (((u1 >> 6) & k3) << 4);
     }
-}
+    __device__ __forceinline__ int scale(int j) const { return int(((j < 4 ? s_lo : s_hi) >> (8 * (j & 3))) & 0xffu); }
+    // mins 2 k and 2 k + 1 as (low byte, next byte)
+    __device__ __forceinline__ uint32_t min_pair(int k) const { return ((k < 2 ? m_lo : m_hi) >> (16 * (k & 1))) & 0xffffu; }
+};
 
-// one weight row against the window: the lane's accumulator per window row (acc) and, on lanes 0..3, the mins lane (accm)
+// One weight row against the window.  Lane k of the row's four stands for the AVX2 kernel's lanes 2 k and 2 k + 1
+// (acc[t][0 / 1]: bytes 8 k .. 8 k + 7 of every 32-byte nibble group, one 64-bit load, four lanes one sector) and for
+// its mins lane k (accm[t]).
 template <int NT>
-__device__ __forceinline__ void row_dot(const uint8_t * __restrict__ row, int nb, const uint8_t * act_sm, int l, float (&acc)[NT],
-                                        float (&accm)[NT]) {
+__device__ __forceinline__ void row_dot(const uint8_t * __restrict__ row, int nb, const uint8_t * codes_sm, const int2 * bs_sm,
+                                        const float * d_sm, int k, float (&acc)[NT][2], float (&accm)[NT]) {
 #pragma unroll
-    for (int t = 0; t < NT; ++t) acc[t] = 0.0f, accm[t] = 0.0f;
+    for (int t = 0; t < NT; ++t) acc[t][0] = 0.0f, acc[t][1] = 0.0f, accm[t] = 0.0f;
     for (int i = 0; i < nb; ++i) {
         const uint8_t * x = row + 144 * i;
         const uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(x));  // d, dmin, 12 scale bytes (144 i is 16-byte aligned)
-        uint32_t q4[4];
+        uint2 q4[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) q4[j] = __ldg(reinterpret_cast<const uint32_t *>(x + 16 + 32 * j) + l);
+        for (int j = 0; j < 4; ++j) q4[j] = __ldg(reinterpret_cast<const uint2 *>(x + 16 + 32 * j) + k);
         const float xd = f16_bits_to_f32(uint16_t(hdr.x & 0xffffu)), xdmin = f16_bits_to_f32(uint16_t(hdr.x >> 16));
-        int sc[8], mn[8];
-        scales_mins(hdr.y, hdr.z, hdr.w, sc, mn);
+        const scales_mins sm(hdr.y, hdr.z, hdr.w);
+        const uint32_t mp = sm.min_pair(k);
+        const int mn0 = int(mp & 0xffu), mn1 = int(mp >> 8);
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
-            const uint8_t * y = act_sm + (size_t(t) * nb + i) * 292;
-            const float yd = *reinterpret_cast<const float *>(y);
-            int sumi = 0;
+            const int b = t * nb + i;
+            int s0 = 0, s1 = 0;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const uint32_t lo = q4[j] & 0x0f0f0f0fu, hi = (q4[j] >> 4) & 0x0f0f0f0fu;
-                const int ylo = *reinterpret_cast<const int *>(y + 4 + 64 * j + 4 * l);
-                const int yhi = *reinterpret_cast<const int *>(y + 4 + 64 * j + 32 + 4 * l);
-                sumi += sc[2 * j] * __dp4a(int(lo), ylo, 0) + sc[2 * j + 1] * __dp4a(int(hi), yhi, 0);
+                // the lane's codes of nibble group j: low nibbles' eight, then high nibbles' eight (stored that way)
+                const uint4 y = *reinterpret_cast<const uint4 *>(codes_sm + size_t(b) * 256 + 64 * j + 16 * k);
+                const int lo = sm.scale(2 * j), hi = sm.scale(2 * j + 1);
+                s0 += lo * __dp4a(int(q4[j].x & 0x0f0f0f0fu), int(y.x), 0) + hi * __dp4a(int((q4[j].x >> 4) & 0x0f0f0f0fu), int(y.z), 0);
+                s1 += lo * __dp4a(int(q4[j].y & 0x0f0f0f0fu), int(y.y), 0) + hi * __dp4a(int((q4[j].y >> 4) & 0x0f0f0f0fu), int(y.w), 0);
             }
-            acc[t] = __fmaf_rn(__fmul_rn(yd, xd), float(sumi), acc[t]);
-            if (l < 4) {  // mins lane l: madd of mins (2 l, 2 l + 1) with the 16-bit pair sums of the block sums
-                const int bx = *reinterpret_cast<const int *>(y + 260 + 8 * l);      // bsums[4 l], [4 l + 1]
-                const int by = *reinterpret_cast<const int *>(y + 260 + 8 * l + 4);  // bsums[4 l + 2], [4 l + 3]
-                const int s0 = int(int16_t(int16_t(bx & 0xffff) + int16_t(bx >> 16)));
-                const int s1 = int(int16_t(int16_t(by & 0xffff) + int16_t(by >> 16)));
-                const int prod = (l == 0 ? mn[0] : l == 1 ? mn[2] : l == 2 ? mn[4] : mn[6]) * s0 +
-                                 (l == 0 ? mn[1] : l == 1 ? mn[3] : l == 2 ? mn[5] : mn[7]) * s1;
-                accm[t] = __fmaf_rn(__fmul_rn(-yd, xdmin), float(prod), accm[t]);
-            }
-        }
-    }
-}
-
-// one super-block's weight-side values for a lane
-struct q4k_lane {
-    uint32_t q4[4];
-    float xd, xdmin;
-    int sc[8], mn[8];
-    __device__ __forceinline__ void load(const uint8_t * x, int l) {
-        const uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(x));  // d, dmin, 12 scale bytes (144 i is 16-byte aligned)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) q4[j] = __ldg(reinterpret_cast<const uint32_t *>(x + 16 + 32 * j) + l);
-        xd = f16_bits_to_f32(uint16_t(hdr.x & 0xffffu)), xdmin = f16_bits_to_f32(uint16_t(hdr.x >> 16));
-        scales_mins(hdr.y, hdr.z, hdr.w, sc, mn);
-    }
-    __device__ __forceinline__ int min_pair(int l, int s0, int s1) const {  // madd of mins (2 l, 2 l + 1) with the pair sums
-        return (l == 0 ? mn[0] : l == 1 ? mn[2] : l == 2 ? mn[4] : mn[6]) * s0 +
-               (l == 0 ? mn[1] : l == 1 ? mn[3] : l == 2 ? mn[5] : mn[7]) * s1;
-    }
-};
-
-// the gate row and the up row of one output against the window, in one pass over the activations (both rows read the
-// same Q8_K words): per window row the lane's accumulators (g, u) and, on lanes 0..3, the mins lanes (gm, um)
-template <int NT>
-__device__ __forceinline__ void rows_dot(const uint8_t * __restrict__ grow, const uint8_t * __restrict__ urow, int nb,
-                                         const uint8_t * act_sm, int l, float (&g)[NT], float (&u)[NT], float (&gm)[NT],
-                                         float (&um)[NT]) {
-#pragma unroll
-    for (int t = 0; t < NT; ++t) g[t] = 0.0f, u[t] = 0.0f, gm[t] = 0.0f, um[t] = 0.0f;
-    for (int i = 0; i < nb; ++i) {
-        q4k_lane wg, wu;
-        wg.load(grow + 144 * i, l);
-        wu.load(urow + 144 * i, l);
-#pragma unroll
-        for (int t = 0; t < NT; ++t) {
-            const uint8_t * y = act_sm + (size_t(t) * nb + i) * 292;
-            const float yd = *reinterpret_cast<const float *>(y);
-            int sg = 0, su = 0;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int ylo = *reinterpret_cast<const int *>(y + 4 + 64 * j + 4 * l);
-                const int yhi = *reinterpret_cast<const int *>(y + 4 + 64 * j + 32 + 4 * l);
-                sg += wg.sc[2 * j] * __dp4a(int(wg.q4[j] & 0x0f0f0f0fu), ylo, 0) +
-                      wg.sc[2 * j + 1] * __dp4a(int((wg.q4[j] >> 4) & 0x0f0f0f0fu), yhi, 0);
-                su += wu.sc[2 * j] * __dp4a(int(wu.q4[j] & 0x0f0f0f0fu), ylo, 0) +
-                      wu.sc[2 * j + 1] * __dp4a(int((wu.q4[j] >> 4) & 0x0f0f0f0fu), yhi, 0);
-            }
-            g[t] = __fmaf_rn(__fmul_rn(yd, wg.xd), float(sg), g[t]);
-            u[t] = __fmaf_rn(__fmul_rn(yd, wu.xd), float(su), u[t]);
-            if (l < 4) {  // mins lane l: the 16-bit pair sums of the block sums (hadd_epi16), then madd with the mins
-                const int bx = *reinterpret_cast<const int *>(y + 260 + 8 * l);      // bsums[4 l], [4 l + 1]
-                const int by = *reinterpret_cast<const int *>(y + 260 + 8 * l + 4);  // bsums[4 l + 2], [4 l + 3]
-                const int s0 = int(int16_t(int16_t(bx & 0xffff) + int16_t(bx >> 16)));
-                const int s1 = int(int16_t(int16_t(by & 0xffff) + int16_t(by >> 16)));
-                gm[t] = __fmaf_rn(__fmul_rn(-yd, wg.xdmin), float(wg.min_pair(l, s0, s1)), gm[t]);
-                um[t] = __fmaf_rn(__fmul_rn(-yd, wu.xdmin), float(wu.min_pair(l, s0, s1)), um[t]);
-            }
+            const float yd = d_sm[b], d = __fmul_rn(yd, xd);
+            acc[t][0] = __fmaf_rn(d, float(s0), acc[t][0]);
+            acc[t][1] = __fmaf_rn(d, float(s1), acc[t][1]);
+            // mins lane k: madd of mins (2 k, 2 k + 1) with the 16-bit pair sums of the block sums (hadd_epi16)
+            const int2 bs = bs_sm[b * 4 + k];
+            accm[t] = __fmaf_rn(__fmul_rn(-yd, xdmin), float(mn0 * bs.x + mn1 * bs.y), accm[t]);
         }
     }
 }
@@ -138,42 +84,56 @@ __global__ void __launch_bounds__(kWarps * 32)
     gate_up_q4_k_kernel(const uint8_t * __restrict__ gate, const uint8_t * __restrict__ up, int64_t row_bytes, int nb,
                         const uint8_t * __restrict__ act, int64_t act_stride, float * __restrict__ ff, int64_t ff_stride,
                         float * __restrict__ gu, int64_t r0, int64_t r1) {
-    extern __shared__ __align__(16) uint8_t act_sm[];  // [NT][nb][292]
+    // the window's Q8_K blocks, rearranged: codes [NT nb][256] (per nibble group and lane: the low nibbles' eight codes,
+    // then the high nibbles' eight), pair sums of the block sums [NT nb][4] x 2, scales [NT nb]
+    extern __shared__ __align__(16) uint8_t act_sm[];
+    uint8_t * codes_sm = act_sm;
+    int2 * bs_sm = reinterpret_cast<int2 *>(act_sm + size_t(NT) * nb * 256);
+    float * d_sm = reinterpret_cast<float *>(act_sm + size_t(NT) * nb * 288);
     load_exp2_table();
     for (int i = threadIdx.x; i < NT * nb * 73; i += blockDim.x) {
-        const int t = i / (nb * 73), k = i - t * nb * 73;
-        reinterpret_cast<uint32_t *>(act_sm)[i] = __ldg(reinterpret_cast<const uint32_t *>(act + int64_t(t) * act_stride) + k);
+        const int b = i / 73, word = i - b * 73;
+        const int t = b / nb, blk = b - t * nb;
+        const uint32_t w = __ldg(reinterpret_cast<const uint32_t *>(act + int64_t(t) * act_stride) + blk * 73 + word);
+        if (word == 0) {
+            d_sm[b] = __uint_as_float(w);
+        } else if (word <= 64) {
+            // code word c: nibble group c / 16, low / high half (c % 16) / 8, word (c % 8) of the half's 32 bytes = lane
+            // (c % 8) / 2, its word (c % 2)
+            const int c = word - 1;
+            reinterpret_cast<uint32_t *>(codes_sm)[b * 64 + (c >> 4) * 16 + ((c & 7) >> 1) * 4 + ((c >> 3) & 1) * 2 + (c & 1)] = w;
+        } else {
+            // block sums 2 s, 2 s + 1 -> their 16-bit sum; mins lane k takes sums 2 k (x) and 2 k + 1 (y)
+            const int s = word - 65;
+            reinterpret_cast<int *>(bs_sm)[b * 8 + s] = int(int16_t(int16_t(w & 0xffffu) + int16_t(w >> 16)));
+        }
     }
     __syncthreads();
-    const int lane = threadIdx.x & 31, l = lane & 7, sub = lane >> 3;
+    // four lanes a row; lanes 0..15 the quad's gate rows, lanes 16..31 its up rows
+    const int lane = threadIdx.x & 31, k = lane & 3, sub = (lane >> 2) & 3, mat = lane >> 4;
+    const uint8_t * mine = mat == 0 ? gate : up;
     const int64_t quad = int64_t(blockIdx.x) * kWarps + (threadIdx.x >> 5), n_quads = int64_t(gridDim.x) * kWarps;
     for (int64_t r4 = r0 + 4 * quad; r4 < r1; r4 += 4 * n_quads) {
         const int64_t r = r4 + sub;
         const bool live = r < r1;
         const int64_t rr = live ? r : r1 - 1;  // every lane takes part in the shuffles
-        float g[NT], u[NT], gm[NT], um[NT];
-        // measured at 2 x 131072 rows of 2560 columns: one pass per matrix 0.125 / 0.250 / 0.760 ms at windows of
-        // 1 / 3 / 8 rows, both matrices in one pass over the activations 0.144 / 0.300 / 0.580 ms
-        if constexpr (NT >= 6) {
-            rows_dot<NT>(gate + rr * row_bytes, up + rr * row_bytes, nb, act_sm, l, g, u, gm, um);
-        } else {
-            row_dot<NT>(gate + rr * row_bytes, nb, act_sm, l, g, gm);
-            row_dot<NT>(up + rr * row_bytes, nb, act_sm, l, u, um);
-        }
+        float acc[NT][2], accm[NT];
+        row_dot<NT>(mine + rr * row_bytes, nb, codes_sm, bs_sm, d_sm, k, acc, accm);
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
-            // hsum_float_8: lane i + 4 onto lane i, lanes 2, 3 onto 0, 1, lane 1 onto lane 0; the mins' four lanes likewise
-            float a = g[t], b = u[t], am = gm[t], bm = um[t];
-            a = __fadd_rn(__shfl_down_sync(kFull, a, 4, 8), a), b = __fadd_rn(__shfl_down_sync(kFull, b, 4, 8), b);
-            a = __fadd_rn(a, __shfl_down_sync(kFull, a, 2, 8)), b = __fadd_rn(b, __shfl_down_sync(kFull, b, 2, 8));
-            a = __fadd_rn(a, __shfl_down_sync(kFull, a, 1, 8)), b = __fadd_rn(b, __shfl_down_sync(kFull, b, 1, 8));
-            am = __fadd_rn(am, __shfl_down_sync(kFull, am, 2, 8)), bm = __fadd_rn(bm, __shfl_down_sync(kFull, bm, 2, 8));
-            am = __fadd_rn(am, __shfl_down_sync(kFull, am, 1, 8)), bm = __fadd_rn(bm, __shfl_down_sync(kFull, bm, 1, 8));
-            if (l == 0 && live) {
-                const float gs = __fadd_rn(a, am), us = __fadd_rn(b, bm);
-                ff[int64_t(t) * ff_stride + r] = __fmul_rn(__fdiv_rn(gs, __fadd_rn(1.0f, exact_expf(-gs))), us);
+            // hsum_float_8 with r_l on lane l / 2: r_l + r_(l + 4) (two lanes up), lanes 2, 3 onto 0, 1 (one lane up),
+            // lane 1 onto lane 0 (the lane's own pair); the mins' four lanes likewise
+            float a = acc[t][0], b = acc[t][1], m = accm[t];
+            a = __fadd_rn(__shfl_down_sync(kFull, a, 2, 4), a), b = __fadd_rn(__shfl_down_sync(kFull, b, 2, 4), b);
+            a = __fadd_rn(a, __shfl_down_sync(kFull, a, 1, 4)), b = __fadd_rn(b, __shfl_down_sync(kFull, b, 1, 4));
+            m = __fadd_rn(m, __shfl_down_sync(kFull, m, 2, 4));
+            m = __fadd_rn(m, __shfl_down_sync(kFull, m, 1, 4));
+            const float dot = __fadd_rn(__fadd_rn(a, b), m);
+            const float us = __shfl_down_sync(kFull, dot, 16);  // the up row's sits 16 lanes above the gate row's
+            if (mat == 0 && k == 0 && live) {
+                ff[int64_t(t) * ff_stride + r] = __fmul_rn(__fdiv_rn(dot, __fadd_rn(1.0f, exact_expf(-dot))), us);
                 if (gu != nullptr) {
-                    gu[int64_t(t) * ff_stride + r] = gs;
+                    gu[int64_t(t) * ff_stride + r] = dot;
                     gu[(int64_t(NT) + t) * ff_stride + r] = us;
                 }
             }
