@@ -10,7 +10,7 @@
 // 32-byte sector) and keeps AVX2 lanes 2 k, 2 k + 1 and mins lane k; a warp takes four (gate, up) row pairs, the gate
 // rows on lanes 0..15 and the up rows on lanes 16..31; the horizontal sums are shuffle steps in the AVX2 order.
 // (With eight lanes a row every lane repeated the scale unpacking and header decode for half the weights: 0.115 /
-// 0.244 / 0.578 ms against this form's 0.089 / 0.160 / 0.351 ms at 2 x 131072 rows of 2560 columns and windows of
+// 0.244 / 0.578 ms against this form's 0.072 / 0.138 / 0.283 ms at 2 x 131072 rows of 2560 columns and windows of
 // 1 / 3 / 8 rows.)
 //
 // HBM-bound on the weights at the window sizes decode uses: 2 x 1440 bytes per output row at 2560 columns, read once
@@ -21,7 +21,23 @@
 namespace fnb {
 namespace {
 
-constexpr int kWarps = 8;
+#ifndef FNB_GU_Q4K_WARPS
+#define FNB_GU_Q4K_WARPS 8
+#endif
+#ifndef FNB_GU_Q4K_GRID
+#define FNB_GU_Q4K_GRID 8
+#endif
+#ifndef FNB_GU_Q4K_UNROLL
+#define FNB_GU_Q4K_UNROLL 2
+#endif
+
+constexpr int kWarps = FNB_GU_Q4K_WARPS;
+// Measured at 2 x 131072 rows of 2560 columns, windows of 1 / 3 / 8 rows: 32 CTAs per SM and one super-block per trip
+// 0.089 / 0.158 / 0.351 ms; two super-blocks per trip (their loads issued together) 0.080 / 0.154 ms; 8 CTAs per SM
+// (each CTA rearranges the window once) 0.082 / 0.144 ms; both 0.072 / 0.138 / 0.283 ms; 4 CTAs per SM 0.070 / 0.152 /
+// 0.275 ms; four warps a CTA or five super-blocks per trip were slower.
+constexpr int kGridPerSm = FNB_GU_Q4K_GRID;
+constexpr int kBlockUnroll = FNB_GU_Q4K_UNROLL;
 constexpr int kMaxT = 8;
 
 // the eight six-bit scales and eight mins from the 12 packed bytes, four to a word, as ggml unpacks them for its
@@ -47,6 +63,7 @@ __device__ __forceinline__ void row_dot(const uint8_t * __restrict__ row, int nb
                                         const float * d_sm, int k, float (&acc)[NT][2], float (&accm)[NT]) {
 #pragma unroll
     for (int t = 0; t < NT; ++t) acc[t][0] = 0.0f, acc[t][1] = 0.0f, accm[t] = 0.0f;
+#pragma unroll kBlockUnroll
     for (int i = 0; i < nb; ++i) {
         const uint8_t * x = row + 144 * i;
         const uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(x));  // d, dmin, 12 scale bytes (144 i is 16-byte aligned)
@@ -147,7 +164,7 @@ int32_t launch_nt(const uint8_t * gate, const uint8_t * up, int64_t row_bytes, i
     const size_t smem = size_t(NT) * nb * 292;
     if (smem > 47 * 1024) return FNB_REJECTED;  // the window's activations must fit the default shared-memory limit
     const int64_t quads = (r1 - r0 + 3) / 4;
-    const int grid = grid_for((quads + kWarps - 1) / kWarps, 32);
+    const int grid = grid_for((quads + kWarps - 1) / kWarps, kGridPerSm);
     gate_up_q4_k_kernel<NT><<<grid, kWarps * 32, smem, s>>>(gate, up, row_bytes, nb, act, act_stride, ff, ff_stride, gu, r0, r1);
     return launch_status();
 }
