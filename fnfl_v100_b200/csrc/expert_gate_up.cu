@@ -58,18 +58,35 @@ struct scales_mins {
 // One weight row against the window.  Lane k of the row's four stands for the AVX2 kernel's lanes 2 k and 2 k + 1
 // (acc[t][0 / 1]: bytes 8 k .. 8 k + 7 of every 32-byte nibble group, one 64-bit load, four lanes one sector) and for
 // its mins lane k (accm[t]).
-template <int NT>
+// Q5: ggml Q5_K rows (176-byte super-blocks: d, dmin, 12 scale bytes, qh[32], qs[128]; value 64 j + b is the low
+// nibble of qs[32 j + b] plus 16 x bit 2 j of qh[b], value 64 j + 32 + b the high nibble plus 16 x bit 2 j + 1) through
+// the same eight lanes (cpu_kq_avx2.cpp:226-290 q5k_dot); there the mins are ONE scalar per (row, t), accm[t] on every
+// lane: summs += dmin x (the eight mins x pair sums, added as integers), a fused multiply-add under the reference's
+// flags.
+template <int NT, bool Q5>
 __device__ __forceinline__ void row_dot(const uint8_t * __restrict__ row, int nb, const uint8_t * codes_sm, const int2 * bs_sm,
                                         const float * d_sm, int k, float (&acc)[NT][2], float (&accm)[NT]) {
 #pragma unroll
     for (int t = 0; t < NT; ++t) acc[t][0] = 0.0f, acc[t][1] = 0.0f, accm[t] = 0.0f;
 #pragma unroll kBlockUnroll
     for (int i = 0; i < nb; ++i) {
-        const uint8_t * x = row + 144 * i;
-        const uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(x));  // d, dmin, 12 scale bytes (144 i is 16-byte aligned)
-        uint2 q4[4];
+        const uint8_t * x = row + (Q5 ? 176 : 144) * i;
+        const uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(x));  // d, dmin, 12 scale bytes (blocks are 16-byte aligned)
+        uint2 q4[4], qh = make_uint2(0u, 0u);
+        if (Q5) qh = __ldg(reinterpret_cast<const uint2 *>(x + 16) + k);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) q4[j] = __ldg(reinterpret_cast<const uint2 *>(x + 16 + 32 * j) + k);
+        for (int j = 0; j < 4; ++j) q4[j] = __ldg(reinterpret_cast<const uint2 *>(x + (Q5 ? 48 : 16) + 32 * j) + k);
+        // the lane's eight low-nibble and eight high-nibble values of each nibble group, four to a word
+        uint2 vlo[4], vhi[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            vlo[j] = make_uint2(q4[j].x & 0x0f0f0f0fu, q4[j].y & 0x0f0f0f0fu);
+            vhi[j] = make_uint2((q4[j].x >> 4) & 0x0f0f0f0fu, (q4[j].y >> 4) & 0x0f0f0f0fu);
+            if (Q5) {
+                vlo[j].x |= ((qh.x >> (2 * j)) & 0x01010101u) << 4, vlo[j].y |= ((qh.y >> (2 * j)) & 0x01010101u) << 4;
+                vhi[j].x |= ((qh.x >> (2 * j + 1)) & 0x01010101u) << 4, vhi[j].y |= ((qh.y >> (2 * j + 1)) & 0x01010101u) << 4;
+            }
+        }
         const float xd = f16_bits_to_f32(uint16_t(hdr.x & 0xffffu)), xdmin = f16_bits_to_f32(uint16_t(hdr.x >> 16));
         const scales_mins sm(hdr.y, hdr.z, hdr.w);
         const uint32_t mp = sm.min_pair(k);
@@ -83,22 +100,27 @@ __device__ __forceinline__ void row_dot(const uint8_t * __restrict__ row, int nb
                 // the lane's codes of nibble group j: low nibbles' eight, then high nibbles' eight (stored that way)
                 const uint4 y = *reinterpret_cast<const uint4 *>(codes_sm + size_t(b) * 256 + 64 * j + 16 * k);
                 const int lo = sm.scale(2 * j), hi = sm.scale(2 * j + 1);
-                s0 += lo * __dp4a(int(q4[j].x & 0x0f0f0f0fu), int(y.x), 0) + hi * __dp4a(int((q4[j].x >> 4) & 0x0f0f0f0fu), int(y.z), 0);
-                s1 += lo * __dp4a(int(q4[j].y & 0x0f0f0f0fu), int(y.y), 0) + hi * __dp4a(int((q4[j].y >> 4) & 0x0f0f0f0fu), int(y.w), 0);
+                s0 += lo * __dp4a(int(vlo[j].x), int(y.x), 0) + hi * __dp4a(int(vhi[j].x), int(y.z), 0);
+                s1 += lo * __dp4a(int(vlo[j].y), int(y.y), 0) + hi * __dp4a(int(vhi[j].y), int(y.w), 0);
             }
             const float yd = d_sm[b], d = __fmul_rn(yd, xd);
             acc[t][0] = __fmaf_rn(d, float(s0), acc[t][0]);
             acc[t][1] = __fmaf_rn(d, float(s1), acc[t][1]);
             // mins lane k: madd of mins (2 k, 2 k + 1) with the 16-bit pair sums of the block sums (hadd_epi16)
             const int2 bs = bs_sm[b * 4 + k];
-            accm[t] = __fmaf_rn(__fmul_rn(-yd, xdmin), float(mn0 * bs.x + mn1 * bs.y), accm[t]);
+            int prod = mn0 * bs.x + mn1 * bs.y;
+            if (Q5) {  // all eight products, on every lane of the row
+                prod += __shfl_xor_sync(kFull, prod, 1, 4);
+                prod += __shfl_xor_sync(kFull, prod, 2, 4);
+            }
+            accm[t] = __fmaf_rn(__fmul_rn(-yd, xdmin), float(prod), accm[t]);
         }
     }
 }
 
-template <int NT>
+template <int NT, bool Q5>
 __global__ void __launch_bounds__(kWarps * 32)
-    gate_up_q4_k_kernel(const uint8_t * __restrict__ gate, const uint8_t * __restrict__ up, int64_t row_bytes, int nb,
+    gate_up_kq_kernel(const uint8_t * __restrict__ gate, const uint8_t * __restrict__ up, int64_t row_bytes, int nb,
                         const uint8_t * __restrict__ act, int64_t act_stride, float * __restrict__ ff, int64_t ff_stride,
                         float * __restrict__ gu, int64_t r0, int64_t r1) {
     // the window's Q8_K blocks, rearranged: codes [NT nb][256] (per nibble group and lane: the low nibbles' eight codes,
@@ -135,7 +157,7 @@ __global__ void __launch_bounds__(kWarps * 32)
         const bool live = r < r1;
         const int64_t rr = live ? r : r1 - 1;  // every lane takes part in the shuffles
         float acc[NT][2], accm[NT];
-        row_dot<NT>(mine + rr * row_bytes, nb, codes_sm, bs_sm, d_sm, k, acc, accm);
+        row_dot<NT, Q5>(mine + rr * row_bytes, nb, codes_sm, bs_sm, d_sm, k, acc, accm);
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
             // hsum_float_8 with r_l on lane l / 2: r_l + r_(l + 4) (two lanes up), lanes 2, 3 onto 0, 1 (one lane up),
@@ -143,8 +165,10 @@ __global__ void __launch_bounds__(kWarps * 32)
             float a = acc[t][0], b = acc[t][1], m = accm[t];
             a = __fadd_rn(__shfl_down_sync(kFull, a, 2, 4), a), b = __fadd_rn(__shfl_down_sync(kFull, b, 2, 4), b);
             a = __fadd_rn(a, __shfl_down_sync(kFull, a, 1, 4)), b = __fadd_rn(b, __shfl_down_sync(kFull, b, 1, 4));
-            m = __fadd_rn(m, __shfl_down_sync(kFull, m, 2, 4));
-            m = __fadd_rn(m, __shfl_down_sync(kFull, m, 1, 4));
+            if (!Q5) {  // Q4_K's four mins lanes: (m0 + m2) + (m1 + m3); Q5_K's mins are one scalar already
+                m = __fadd_rn(m, __shfl_down_sync(kFull, m, 2, 4));
+                m = __fadd_rn(m, __shfl_down_sync(kFull, m, 1, 4));
+            }
             const float dot = __fadd_rn(__fadd_rn(a, b), m);
             const float us = __shfl_down_sync(kFull, dot, 16);  // the up row's sits 16 lanes above the gate row's
             if (mat == 0 && k == 0 && live) {
@@ -158,28 +182,30 @@ __global__ void __launch_bounds__(kWarps * 32)
     }
 }
 
-template <int NT>
+template <int NT, bool Q5>
 int32_t launch_nt(const uint8_t * gate, const uint8_t * up, int64_t row_bytes, int nb, const uint8_t * act, int64_t act_stride,
                   float * ff, int64_t ff_stride, float * gu, int64_t r0, int64_t r1, cudaStream_t s) {
     const size_t smem = size_t(NT) * nb * 292;
     if (smem > 47 * 1024) return FNB_REJECTED;  // the window's activations must fit the default shared-memory limit
     const int64_t quads = (r1 - r0 + 3) / 4;
     const int grid = grid_for((quads + kWarps - 1) / kWarps, kGridPerSm);
-    gate_up_q4_k_kernel<NT><<<grid, kWarps * 32, smem, s>>>(gate, up, row_bytes, nb, act, act_stride, ff, ff_stride, gu, r0, r1);
+    gate_up_kq_kernel<NT, Q5><<<grid, kWarps * 32, smem, s>>>(gate, up, row_bytes, nb, act, act_stride, ff, ff_stride, gu, r0, r1);
     return launch_status();
 }
 
 }  // namespace
 }  // namespace fnb
 
-extern "C" int32_t fnb_expert_gate_up_rows_q4_k(const void * gate, const void * up, int64_t row_bytes, int32_t n,
-                                                const void * act, int64_t act_stride, int32_t nt, float * ff,
-                                                int64_t ff_stride, float * gu, int64_t r0, int64_t r1, void * stream) {
-    using namespace fnb;
+namespace fnb {
+namespace {
+
+template <bool Q5>
+int32_t gate_up_rows(const void * gate, const void * up, int64_t row_bytes, int32_t n, const void * act, int64_t act_stride,
+                     int32_t nt, float * ff, int64_t ff_stride, float * gu, int64_t r0, int64_t r1, void * stream) {
     if (!ok_ptr(gate, 16) || !ok_ptr(up, 16) || !ok_ptr(act, 4) || !ok_ptr(ff, 4) || !ok_opt(gu, 4)) return FNB_REJECTED;
     if (n < 256 || n > 16384 || n % 256 != 0 || nt < 1 || nt > 64 || r0 < 0 || r1 <= r0 || r1 - r0 > INT32_MAX) return FNB_REJECTED;
     const int nb = n / 256;
-    if (row_bytes != int64_t(nb) * 144 || act_stride < int64_t(nb) * 292 || act_stride % 4 != 0 || ff_stride < r1) return FNB_REJECTED;
+    if (row_bytes != int64_t(nb) * (Q5 ? 176 : 144) || act_stride < int64_t(nb) * 292 || act_stride % 4 != 0 || ff_stride < r1) return FNB_REJECTED;
     const cudaStream_t s = static_cast<cudaStream_t>(stream);
     const uint8_t * gp = static_cast<const uint8_t *>(gate);
     const uint8_t * upp = static_cast<const uint8_t *>(up);
@@ -192,16 +218,31 @@ extern "C" int32_t fnb_expert_gate_up_rows_q4_k(const void * gate, const void * 
         if (gu != nullptr && nt > kMaxT) return FNB_REJECTED;
         int32_t st;
         switch (m) {
-            case 1: st = launch_nt<1>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
-            case 2: st = launch_nt<2>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
-            case 3: st = launch_nt<3>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
-            case 4: st = launch_nt<4>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
-            case 5: st = launch_nt<5>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
-            case 6: st = launch_nt<6>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
-            case 7: st = launch_nt<7>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
-            default: st = launch_nt<8>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
+            case 1: st = launch_nt<1, Q5>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
+            case 2: st = launch_nt<2, Q5>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
+            case 3: st = launch_nt<3, Q5>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
+            case 4: st = launch_nt<4, Q5>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
+            case 5: st = launch_nt<5, Q5>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
+            case 6: st = launch_nt<6, Q5>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
+            case 7: st = launch_nt<7, Q5>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
+            default: st = launch_nt<8, Q5>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
         }
         if (st != FNB_OK) return st;
     }
     return FNB_OK;
+}
+
+}  // namespace
+}  // namespace fnb
+
+extern "C" int32_t fnb_expert_gate_up_rows_q4_k(const void * gate, const void * up, int64_t row_bytes, int32_t n,
+                                                const void * act, int64_t act_stride, int32_t nt, float * ff,
+                                                int64_t ff_stride, float * gu, int64_t r0, int64_t r1, void * stream) {
+    return fnb::gate_up_rows<false>(gate, up, row_bytes, n, act, act_stride, nt, ff, ff_stride, gu, r0, r1, stream);
+}
+
+extern "C" int32_t fnb_expert_gate_up_rows_q5_k(const void * gate, const void * up, int64_t row_bytes, int32_t n,
+                                                const void * act, int64_t act_stride, int32_t nt, float * ff,
+                                                int64_t ff_stride, float * gu, int64_t r0, int64_t r1, void * stream) {
+    return fnb::gate_up_rows<true>(gate, up, row_bytes, n, act, act_stride, nt, ff, ff_stride, gu, r0, r1, stream);
 }

@@ -20,6 +20,7 @@ OPS = ("get_rows_q4_k", "get_rows_iq3_xxs", "rms_norm", "rms_norm_heads", "rope_
        "rope_kv8", "quantize_q8_1", "rms_norm_q8_1", "embed_iq3_s", "kv_read_q8_0", "kv_read_kv8",
        "expert_down_q5_1_nt1", "expert_down_q5_1_nt3", "expert_down_q5_1_nt8", "expert_down_q8_0_nt1", "expert_down_q8_0_nt3", "quantize_q8_k",
        "expert_gate_up_q4_k_nt1", "expert_gate_up_q4_k_nt3", "expert_gate_up_q4_k_nt8",
+       "expert_gate_up_q5_k_nt1", "expert_gate_up_q5_k_nt3", "expert_gate_up_q5_k_nt8",
        "expert_gate_up_iq3_xxs_nt1", "expert_gate_up_iq3_xxs_nt3", "expert_gate_up_iq3_xxs_nt8")
 
 
@@ -83,6 +84,13 @@ def make_case(op: str, T: int, dev, gen, c: ChainConfig):
         act = ops.quantize_q8_k(N(gen, (nt, n), 1.0, dev))
         out = torch.empty((nt, rows), dtype=torch.float32, device=dev)
         return (lambda: ops.expert_gate_up_rows_q4_k(gate, up, act, n, out=out)), rows * (2 * n // 256 * 144 + nt * 4) + nt * n // 256 * 292
+    if op.startswith("expert_gate_up_q5_k"):
+        nt, n, rows = int(op.rsplit("nt", 1)[1]), 2560, 2 * T
+        gate = synth.torch_table("q5_k", gen, rows, n, dev, 1e-5, 2e-4)
+        up = synth.torch_table("q5_k", gen, rows, n, dev, 1e-5, 2e-4)
+        act = ops.quantize_q8_k(N(gen, (nt, n), 1.0, dev))
+        out = torch.empty((nt, rows), dtype=torch.float32, device=dev)
+        return (lambda: ops.expert_gate_up_rows_q5_k(gate, up, act, n, out=out)), rows * (2 * n // 256 * 176 + nt * 4) + nt * n // 256 * 292
     if op.startswith("expert_gate_up_iq3_xxs"):
         nt, n, rows = int(op.rsplit("nt", 1)[1]), 2560, 2 * T
         gate = synth.torch_table("iq3_xxs", gen, rows, n, dev, 5e-5, 4e-4)

@@ -28,6 +28,15 @@ def q4_k_table(g: np.random.Generator, n_rows: int, cols: int, d_lo: float = 1e-
     return t.reshape(n_rows, nsb * 144)
 
 
+def q5_k_table(g: np.random.Generator, n_rows: int, cols: int, d_lo: float = 1e-3, d_hi: float = 1e-2) -> np.ndarray:
+    """uint8 [n_rows][cols/256*176]: uniform bytes (6-bit scales/mins, high bits, nibbles), fp16 d and dmin ~ U(d_lo, d_hi)."""
+    nsb = cols // 256
+    t = g.integers(0, 256, size=(n_rows, nsb, 176), dtype=np.uint8)
+    dm = _f16_bits(g.uniform(d_lo, d_hi, size=(n_rows, nsb, 2)))
+    t[:, :, 0:4] = dm.view(np.uint8).reshape(n_rows, nsb, 4)
+    return t.reshape(n_rows, nsb * 176)
+
+
 def iq3_xxs_table(g: np.random.Generator, n_rows: int, cols: int, d_lo: float = 1e-3, d_hi: float = 1e-2) -> np.ndarray:
     """uint8 [n_rows][cols/256*98]: uniform codebook indices, sign bits and 4-bit scales, fp16 d ~ U(d_lo, d_hi) > 0."""
     nsb = cols // 256
@@ -88,7 +97,7 @@ def torch_normal(gen, shape, scale: float, device):
 def torch_table(fmt: str, gen, n_rows: int, cols: int, device, d_lo: float = 1e-3, d_hi: float = 1e-2):
     """Device form of q4_k_table / iq3_xxs_table / an IQ3_S table (same distributions, torch's generator)."""
     import torch
-    bv, bb, nd = {"q4_k": (256, 144, 2), "iq3_xxs": (256, 98, 1), "iq3_s": (256, 110, 1)}[fmt]
+    bv, bb, nd = {"q4_k": (256, 144, 2), "q5_k": (256, 176, 2), "iq3_xxs": (256, 98, 1), "iq3_s": (256, 110, 1)}[fmt]
     nsb = cols // bv
     t = torch.randint(0, 256, (n_rows, nsb, bb), dtype=torch.uint8, device=device, generator=gen)
     d = torch.empty((n_rows, nsb, nd), dtype=torch.float32, device=device).uniform_(d_lo, d_hi, generator=gen)

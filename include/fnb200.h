@@ -306,6 +306,16 @@ int32_t fnb_expert_gate_up_rows_q4_k(const void * gate, const void * up, int64_t
                                      int64_t r1, void * stream);
 
 /*
+ * The same mat-vec with ggml Q5_K weights (n / 256 super-blocks of 176 bytes a row: row_bytes = n / 256 * 176): replaces
+ * fn::experts::cpu::kq_gu_rows for fmt q5_k (cpu_kq_avx2.cpp:226-290 q5k_dot, :362-380) and returns the SAME BITS - the
+ * Q4_K lane structure over 5-bit values, the mins as one scalar fused multiply-add a super-block.  Arguments and limits
+ * as fnb_expert_gate_up_rows_q4_k.
+ */
+int32_t fnb_expert_gate_up_rows_q5_k(const void * gate, const void * up, int64_t row_bytes, int32_t n, const void * act,
+                                     int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, float * gu, int64_t r0,
+                                     int64_t r1, void * stream);
+
+/*
  * The same mat-vec with ggml IQ3_XXS weights (n / 256 super-blocks of 98 bytes a row, rows back to back:
  * row_bytes = n / 256 * 98): replaces fn::experts::cpu::iq_gu_rows for fmt iq3_xxs (fn/kernels/experts/cpu_kernels.h:67;
  * cpu_iq_avx2.cpp:256-271, :305-337, :429-445) and returns the SAME BITS - eight int32 lanes a super-block of

@@ -81,6 +81,12 @@ inline bool gate_up_rows_q4_k(const uint8_t * gate, const uint8_t * up, int32_t 
     return fnb_expert_gate_up_rows_q4_k(gate, up, int64_t(n / 256) * 144, n, act, act_stride, nt, ff, ff_stride, nullptr, r0,
                                         r1, stream) == FNB_OK;
 }
+// the same for fmt q5_k (176-byte super-blocks)
+inline bool gate_up_rows_q5_k(const uint8_t * gate, const uint8_t * up, int32_t n, const void * act, int64_t act_stride,
+                              int32_t nt, float * ff, int64_t ff_stride, int64_t r0, int64_t r1, void * stream) {
+    return fnb_expert_gate_up_rows_q5_k(gate, up, int64_t(n / 256) * 176, n, act, act_stride, nt, ff, ff_stride, nullptr, r0,
+                                        r1, stream) == FNB_OK;
+}
 // the same for fmt iq3_xxs (fn::experts::cpu::iq_gu_rows, same bits); IQ3_XXS rows of n / 256 x 98 bytes back to back
 inline bool gate_up_rows_iq3_xxs(const uint8_t * gate, const uint8_t * up, int32_t n, const void * act, int64_t act_stride,
                                  int32_t nt, float * ff, int64_t ff_stride, int64_t r0, int64_t r1, void * stream) {

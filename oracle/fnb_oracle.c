@@ -578,6 +578,68 @@ void fnbo_expert_gu_rows_q4_k(const uint8_t * gate, const uint8_t * up, int64_t 
     }
 }
 
+/* ---- the same rows with Q5_K weights (fn/kernels/experts/cpu_kq_avx2.cpp:226-290 q5k_dot, ggml's
+ * ggml_vec_dot_q5_K_q8_K with the weight side hoisted).  Block: fp16 d, dmin, 12 scale bytes, qh[32], qs[128]; value
+ * 64 j + b is (qs[32 j + b] & 15) + 16 bit 2 j of qh[b], value 64 j + 32 + b is (qs[32 j + b] >> 4) + 16 bit 2 j + 1.
+ * Eight int32 lanes as for Q4_K; the mins are ONE scalar: summs += dmin x (sum over eight of min x 16-bit pair sum of
+ * the block sums), which the reference's flags compile to a fused multiply-add; result hsum_float_8(acc) + summs. */
+static float fnbo_q5k_dot(const uint8_t * row, int nb, const uint8_t * act) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float summs = 0.f;
+    for (int i = 0; i < nb; ++i) {
+        const uint8_t * x = row + 176 * i;
+        const uint8_t * y = act + 292 * i;
+        uint16_t dh, mh;
+        memcpy(&dh, x, 2), memcpy(&mh, x + 2, 2);
+        const float xd = fnbo_f16_to_f32(dh), xdmin = fnbo_f16_to_f32(mh);
+        uint8_t sc[8], mn[8];
+        for (int j = 0; j < 8; ++j) o_scale_min_k4(j, x + 4, &sc[j], &mn[j]);
+        const uint8_t * qh = x + 16;
+        const uint8_t * qs = x + 48;
+        float yd;
+        memcpy(&yd, y, 4);
+        const int8_t * q8 = (const int8_t *) (y + 4);
+        int16_t bsums[16];
+        memcpy(bsums, y + 260, 32);
+        const float d = yd * xd, dmin = -yd * xdmin;
+        int32_t msum = 0;
+        for (int k = 0; k < 8; ++k) msum += (int32_t) mn[k] * (int16_t) (bsums[2 * k] + bsums[2 * k + 1]);
+        summs = fmaf(dmin, (float) msum, summs);
+        for (int l = 0; l < 8; ++l) {
+            int32_t sumi = 0;
+            for (int j = 0; j < 4; ++j) {
+                int32_t lo = 0, hi = 0;
+                for (int b = 4 * l; b < 4 * l + 4; ++b) {
+                    const int v0 = (qs[32 * j + b] & 15) + (((qh[b] >> (2 * j)) & 1) << 4);
+                    const int v1 = (qs[32 * j + b] >> 4) + (((qh[b] >> (2 * j + 1)) & 1) << 4);
+                    lo += v0 * (int32_t) q8[64 * j + b];
+                    hi += v1 * (int32_t) q8[64 * j + 32 + b];
+                }
+                sumi += (int32_t) sc[2 * j] * lo + (int32_t) sc[2 * j + 1] * hi;
+            }
+            acc[l] = fmaf(d, (float) sumi, acc[l]);
+        }
+    }
+    return fnbo_hsum8(acc) + summs;
+}
+
+void fnbo_expert_gu_rows_q5_k(const uint8_t * gate, const uint8_t * up, int64_t row_bytes, int32_t n, const uint8_t * act,
+                              int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, float * gu, int64_t r0,
+                              int64_t r1) {
+    const int nb = n / 256;
+    for (int64_t r = r0; r < r1; ++r) {
+        for (int t = 0; t < nt; ++t) {
+            const float g = fnbo_q5k_dot(gate + r * row_bytes, nb, act + (int64_t) t * act_stride);
+            const float u = fnbo_q5k_dot(up + r * row_bytes, nb, act + (int64_t) t * act_stride);
+            ff[(int64_t) t * ff_stride + r] = (g / (1.0f + o_expf(-g))) * u;
+            if (gu != NULL) {
+                gu[(int64_t) t * ff_stride + r] = g;
+                gu[((int64_t) nt + t) * ff_stride + r] = u;
+            }
+        }
+    }
+}
+
 /* ---- the same rows with IQ3_XXS weights (fn/kernels/experts/cpu_iq_avx2.cpp:256-271 fmt32<18>::decode, :305-337
  * row_dot, :429-445 gu_rows).  Per super-block eight int32 lanes: lane l collects, over the block's eight groups of 32
  * values, (2 s + 1) x the sum of four codebook bytes of the group's index byte l times the sign-applied Q8_K codes

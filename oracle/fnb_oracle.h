@@ -96,6 +96,13 @@ void fnbo_expert_gu_rows_q4_k(const uint8_t * gate, const uint8_t * up, int64_t 
                               int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, float * gu, int64_t r0,
                               int64_t r1);
 
+/* The same with ggml Q5_K weights (n / 256 super-blocks of 176 bytes a row): fn/kernels/experts/cpu_kq_avx2.cpp:226-290
+ * q5k_dot - the Q4_K lane structure over 5-bit values (high bits from qh), the mins as one scalar fused multiply-add a
+ * super-block, hsum_float_8(acc) + summs. */
+void fnbo_expert_gu_rows_q5_k(const uint8_t * gate, const uint8_t * up, int64_t row_bytes, int32_t n, const uint8_t * act,
+                              int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, float * gu, int64_t r0,
+                              int64_t r1);
+
 /* The same with ggml IQ3_XXS weights (n / 256 super-blocks of 98 bytes a row): the reference's AVX2 row kernel lane for
  * lane (fn/kernels/experts/cpu_iq_avx2.cpp:256-271, :305-337, :429-445) - eight int32 lanes a super-block of
  * (2 s + 1) x codebook bytes x sign-applied Q8_K codes, one fused multiply-add a super-block with (x.d y.d), ggml's

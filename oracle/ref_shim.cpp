@@ -85,6 +85,15 @@ void ref_kq_gu_rows_q4_k(const uint8_t * gate, const uint8_t * up, int64_t row_b
     fn::experts::cpu::kq_gu_rows(fn::experts::fmt::q4_k, gate, up, size_t(row_bytes), n, a, nt, o, r0, r1);
 }
 
+// the same rows for Q5_K weights (fn/kernels/experts/cpu_kq_avx2.cpp:226-290 through kq_gu_rows)
+void ref_kq_gu_rows_q5_k(const uint8_t * gate, const uint8_t * up, int64_t row_bytes, int32_t n, const uint8_t * act,
+                         int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, int32_t r0, int32_t r1) {
+    const void * a[64];
+    float * o[64];
+    for (int t = 0; t < nt && t < 64; ++t) a[t] = act + int64_t(t) * act_stride, o[t] = ff + int64_t(t) * ff_stride;
+    fn::experts::cpu::kq_gu_rows(fn::experts::fmt::q5_k, gate, up, size_t(row_bytes), n, a, nt, o, r0, r1);
+}
+
 // the same rows for IQ3_XXS weights (fn/kernels/experts/cpu_iq_avx2.cpp:429-445 through iq_gu_rows)
 void ref_iq_gu_rows_iq3_xxs(const uint8_t * gate, const uint8_t * up, int64_t row_bytes, int32_t n, const uint8_t * act,
                             int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, int32_t r0, int32_t r1) {

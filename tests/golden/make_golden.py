@@ -152,6 +152,21 @@ def gate_up_rows() -> None:
     print("gate_up_rows.npz", os.path.getsize(os.path.join(HERE, "gate_up_rows.npz")), "bytes; |ff| max", float(np.abs(ff).max()))
 
 
+def gate_up_rows_q5_k() -> None:
+    """The same for Q5_K rows (fn::experts::cpu::kq_gu_rows, fmt q5_k).  Same libm note as above."""
+    from fnfl_v100_b200 import synth
+    g = synth.rng(0x5135)
+    n, rows, nt = 2560, 45, 5
+    gate, up = synth.q5_k_table(g, rows, n, 1e-5, 1e-4), synth.q5_k_table(g, rows, n, 1e-5, 1e-4)
+    act = O.quantize_q8_k(synth.normal(g, (nt, n), 1.0), "ggml").reshape(nt, -1)
+    ff = O.expert_gu_rows_q5_k(gate, up, act, n, use_ref=True)
+    O.use_libm(False)
+    assert np.array_equal(ff.view(np.uint32), O.expert_gu_rows_q5_k(gate, up, act, n).view(np.uint32)), "libm is not the generic build"
+    path = os.path.join(HERE, "gate_up_rows_q5_k.npz")
+    np.savez_compressed(path, gate=gate, up=up, act=act, ff=ff)
+    print("gate_up_rows_q5_k.npz", os.path.getsize(path), "bytes; |ff| max", float(np.abs(ff).max()))
+
+
 def gate_up_rows_iq3_xxs() -> None:
     """The same for IQ3_XXS rows (fn::experts::cpu::iq_gu_rows, fmt iq3_xxs), and once more with one activation code in
     ten set to -128, which the reference's sign step (_mm256_sign_epi8) leaves as it is.  Same libm note as above."""
@@ -180,6 +195,7 @@ def main() -> None:
     down_rows()
     q8_k()
     gate_up_rows()
+    gate_up_rows_q5_k()
     gate_up_rows_iq3_xxs()
     r = O.ref()
     x = stress_blocks()

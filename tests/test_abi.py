@@ -89,6 +89,11 @@ def test_rejections_enqueue_nothing(lib):
     dbg = list(okg)
     dbg[6], dbg[9] = 9, A16
     assert lib.fnb_expert_gate_up_rows_q4_k(*dbg) == R
+    ok5 = (A16, A16, 1760, 2560, A16, 2920, 3, A16, 640, None, 0, 640, None)
+    for i, bad in ((3, 2500), (2, 1440), (6, 0), (6, 65), (11, 0), (8, 100), (0, ODD), (4, None)):
+        a = list(ok5)
+        a[i] = bad
+        assert lib.fnb_expert_gate_up_rows_q5_k(*a) == R, (i, bad)
     # the IQ3_XXS form: an odd number of super-blocks a row (rows off 4-byte boundaries), rows not back to back
     ok3 = (A16, A16, 980, 2560, A16, 2920, 3, A16, 640, None, 0, 640, None)
     for i, bad in ((3, 2304), (2, 984), (6, 0), (6, 65), (11, 0), (8, 100), (0, ODD), (4, None), (5, 2916)):

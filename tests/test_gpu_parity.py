@@ -352,6 +352,34 @@ def test_expert_gate_up_rows_bit_exact(dev, oracle, n, rows, nt):
     assert np.abs(want[:, r0:r1]).max() < 1e3 and np.abs(wgu[0][:, r0:r1]).std() > 0.3   # gates of order one: the GLU is exercised
 
 
+def test_expert_gate_up_rows_q5_k_equal_the_reference_avx2_kernel_on_golden(dev):
+    gold = np.load(os.path.join(GOLD, "gate_up_rows_q5_k.npz"))
+    got = ops.expert_gate_up_rows_q5_k(to_dev(gold["gate"], dev), to_dev(gold["up"], dev), to_dev(gold["act"], dev), 2560)
+    assert np.array_equal(bits(got.cpu().numpy()), bits(gold["ff"]))
+
+
+@pytest.mark.parametrize("n,rows,nt", [(2560, 320, 1), (2560, 999, 3), (2560, 130, 8), (256, 37, 2), (1024, 65, 13)])
+def test_expert_gate_up_rows_q5_k_bit_exact(dev, oracle, n, rows, nt):
+    """As the Q4_K test, with Q5_K rows: the high bits from qh and the mins as one scalar per (row, window row)."""
+    g = synth.rng(34)
+    x = synth.normal(g, (nt, n), 1.0)
+    act = ops.quantize_q8_k(to_dev(x, dev))
+    d_hi = 1.5e-4 * (2560 / n) ** 0.5
+    gate, up = synth.q5_k_table(g, rows, n, d_hi / 10, d_hi), synth.q5_k_table(g, rows, n, d_hi / 10, d_hi)
+    r0, r1 = 2, rows - 1
+    out = torch.full((nt, rows), float("nan"), dtype=torch.float32, device=dev)
+    gu = torch.zeros((2, nt, rows), dtype=torch.float32, device=dev) if nt <= 8 else None
+    ops.expert_gate_up_rows_q5_k(to_dev(gate, dev), to_dev(up, dev), act, n, r0=r0, r1=r1, out=out, gu=gu)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    want, wgu = oracle.expert_gu_rows_q5_k(gate, up, act.cpu().numpy(), n, r0=r0, r1=r1, want_gu=True)
+    assert np.array_equal(bits(got[:, r0:r1]), bits(want[:, r0:r1]))
+    assert np.isnan(got[:, :r0]).all() and np.isnan(got[:, r1:]).all()
+    if gu is not None:
+        assert np.array_equal(bits(gu.cpu().numpy()[:, :, r0:r1]), bits(wgu[:, :, r0:r1]))
+    assert np.abs(want[:, r0:r1]).max() < 1e4 and np.abs(wgu[0][:, r0:r1]).std() > 0.3
+
+
 def test_expert_gate_up_rows_iq3_xxs_equal_the_reference_avx2_kernel_on_golden(dev):
     """The reference's own iq_gu_rows outputs, also for a window holding -128 codes (the kernel's other sign path)."""
     gold = np.load(os.path.join(GOLD, "gate_up_rows_iq3_xxs.npz"))

@@ -145,6 +145,13 @@ def test_q8_k_matches_ggml_and_the_reference_avx2_form(oracle):
     assert np.array_equal(oracle.quantize_q8_k(gold["x"]), gold["blocks"])
 
 
+def test_expert_gate_up_rows_q5_k_match_the_reference_avx2_kernel(oracle):
+    """tests/golden/gate_up_rows_q5_k.npz: ff of the reference's own kq_gu_rows (fmt q5_k, GLU included)."""
+    gold = np.load(os.path.join(GOLD, "gate_up_rows_q5_k.npz"))
+    got = oracle.expert_gu_rows_q5_k(gold["gate"], gold["up"], gold["act"], 2560)
+    assert np.array_equal(got.view(np.uint32), gold["ff"].view(np.uint32))
+
+
 def test_expert_gate_up_rows_iq3_xxs_match_the_reference_avx2_kernel(oracle):
     """tests/golden/gate_up_rows_iq3_xxs.npz: ff of the reference's own iq_gu_rows (fmt iq3_xxs, GLU included), also for
     activations holding -128 codes, which its sign step leaves as they are; the restatement reproduces every bit."""
