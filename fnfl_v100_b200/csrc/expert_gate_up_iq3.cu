@@ -31,6 +31,7 @@
 
 #include "common.cuh"
 #include "exact_math.cuh"
+#include "stage_span.cuh"
 
 #ifndef FNB_GU_IQ3_GRID
 #define FNB_GU_IQ3_GRID 1
@@ -81,35 +82,13 @@ __device__ __forceinline__ const uint8_t * chunk_src(const uint8_t * mat, int64_
     return mat + (r < r1 ? r : r1 - 1) * row_bytes + int64_t(chunk) * (kChunkBlocks * 98);
 }
 
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const uint8_t * src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_4(uint32_t dst, const uint8_t * src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
-}
-
-// `bytes` (a multiple of 4) from src (4-byte aligned) into a slot, at src's own offset within 16 bytes
-__device__ __forceinline__ void stage_slot(uint32_t slot_sm, const uint8_t * src, int bytes, int lane) {
-    const int phase = int(reinterpret_cast<uintptr_t>(src) & 15);
-    const uint32_t dst = slot_sm + phase;
-    const int head = (16 - phase) & 15;  // bytes is at least 196, so the head is whole
-    const int body = (bytes - head) >> 4, tail = (bytes - head) & 15;
-    for (int c = lane; c < body; c += 32) cp_async_16(dst + head + 16 * c, src + head + 16 * c);
-    if (lane < (head >> 2)) {
-        cp_async_4(dst + 4 * lane, src + 4 * lane);
-    } else if (lane >= 8 && lane - 8 < (tail >> 2)) {
-        const int o = head + 16 * body + 4 * (lane - 8);
-        cp_async_4(dst + o, src + o);
-    }
-}
-
 __device__ __forceinline__ void stage_unit(uint32_t buf_sm, const uint8_t * __restrict__ gate, const uint8_t * __restrict__ up,
                                            int64_t row_bytes, int64_t r4, int64_t r1, int chunk, int bytes, int lane) {
 #pragma unroll
     for (int slot = 0; slot < 8; ++slot) {
-        stage_slot(buf_sm + slot * kSlotBytes, chunk_src(slot < 4 ? gate : up, row_bytes, r4 + (slot & 3), r1, chunk), bytes, lane);
+        stage_span(buf_sm + slot * kSlotBytes, chunk_src(slot < 4 ? gate : up, row_bytes, r4 + (slot & 3), r1, chunk), bytes, lane);
     }
-    asm volatile("cp.async.commit_group;" ::: "memory");
+    cp_async_commit();
 }
 
 // rows of up to ten super-blocks: the quad's four gate rows are one contiguous span of the matrix, its up rows another
@@ -117,9 +96,9 @@ __device__ __forceinline__ void stage_unit_whole(uint32_t buf_sm, const uint8_t 
                                                  const uint8_t * __restrict__ up, int64_t row_bytes, int64_t r4, int64_t r1,
                                                  int lane) {
     const int rows = r1 - r4 < 4 ? int(r1 - r4) : 4;  // a ragged last quad leaves its missing rows' bytes as they were
-    stage_slot(buf_sm, gate + r4 * row_bytes, rows * int(row_bytes), lane);
-    stage_slot(buf_sm + kSpanBytes, up + r4 * row_bytes, rows * int(row_bytes), lane);
-    asm volatile("cp.async.commit_group;" ::: "memory");
+    stage_span(buf_sm, gate + r4 * row_bytes, rows * int(row_bytes), lane);
+    stage_span(buf_sm + kSpanBytes, up + r4 * row_bytes, rows * int(row_bytes), lane);
+    cp_async_commit();
 }
 
 // one staged unit (n_blk super-blocks of the lane's row, x) against the window: acc[t][0 / 1] are AVX2 lanes 2 k, 2 k + 1

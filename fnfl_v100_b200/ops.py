@@ -363,7 +363,8 @@ def expert_down_rows(fmt: str, w: torch.Tensor, act: torch.Tensor, n: int, r0: i
     if out is None:
         out = torch.zeros((nt, rows), dtype=torch.float32, device=w.device)
     _dev(out, torch.float32, "out")
-    fn = {"q5_1": _lib.lib().fnb_expert_down_rows_q5_1, "q8_0": _lib.lib().fnb_expert_down_rows_q8_0}[fmt]
+    fn = {"q5_1": _lib.lib().fnb_expert_down_rows_q5_1, "q8_0": _lib.lib().fnb_expert_down_rows_q8_0,
+          "iq4_nl": _lib.lib().fnb_expert_down_rows_iq4_nl}[fmt]
     _check(fn(_ptr(w), w.shape[1], n, _ptr(act), act.shape[1], nt, _ptr(out), out.shape[1], r0, r1, _stream()),
            "expert_down_rows_" + fmt)
     return out

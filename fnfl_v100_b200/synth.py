@@ -67,6 +67,14 @@ def q5_1_rows(g: np.random.Generator, rows: int, n: int, d_lo: float = 1e-3, d_h
     return t.reshape(rows, nb * 24)
 
 
+def iq4_nl_rows(g: np.random.Generator, rows: int, n: int, d_lo: float = 1e-3, d_hi: float = 1e-2) -> np.ndarray:
+    """Random valid ggml IQ4_NL rows: uint8 [rows][n/32*18] (fp16 d ~ U(d_lo, d_hi), random nibbles)."""
+    nb = n // 32
+    t = g.integers(0, 256, (rows, nb, 18)).astype(np.uint8)
+    t[:, :, 0:2] = g.uniform(d_lo, d_hi, (rows, nb)).astype(np.float16).view(np.uint8).reshape(rows, nb, 2)
+    return t.reshape(rows, nb * 18)
+
+
 def norm_weight(g: np.random.Generator, cols: int) -> np.ndarray:
     """1 + N(0, 0.1), the RMSNorm weight of the first configuration."""
     return (1.0 + 0.1 * g.standard_normal(cols)).astype(np.float32)

@@ -353,6 +353,18 @@ int32_t fnb_expert_down_rows_q8_0(const void * w, int64_t row_bytes, int32_t n, 
                                   int32_t nt, float * out, int64_t out_stride, int64_t r0, int64_t r1, void * stream);
 
 /*
+ * The same mat-vec with ggml IQ4_NL weights (18-byte blocks: fp16 d, 16 nibble bytes indexing kvalues_iq4nl) against
+ * Q8_0 activations: fn::experts::cpu::iq4nl_down_rows (fn/kernels/experts/cpu_kernels.h:73; cpu_iq_avx2.cpp:481-514,
+ * :571-578), same bits - eight accumulators, one fused multiply-add per block and lane with the product of the two block
+ * scales, |w| times the code with w's sign applied (a -128 code stays -128, as _mm256_sign_epi8 leaves it), that file's
+ * hsum8 order.  n a multiple of 64 up to 8192 (rows on 4-byte boundaries, blocks in pairs); row_bytes = n / 32 * 18;
+ * w 16-byte, act 2-byte, out 4-byte aligned; act_stride even.  Uses more than the default shared memory:
+ * fnb_prepare_device covers it.
+ */
+int32_t fnb_expert_down_rows_iq4_nl(const void * w, int64_t row_bytes, int32_t n, const void * act, int64_t act_stride,
+                                    int32_t nt, float * out, int64_t out_stride, int64_t r0, int64_t r1, void * stream);
+
+/*
  * Host-side check before upload: 0 when every id is in [0, n_vocab), else 1 + the index of the first bad id.
  * Replaces fn::embed::check_tokens (fn/kernels/embed/embed.h:56).
  */

@@ -109,6 +109,11 @@ inline bool down_rows_q8_0(const uint8_t * w, int32_t n, const void * act, int64
                            int64_t out_stride, int64_t r0, int64_t r1, void * stream) {
     return fnb_expert_down_rows_q8_0(w, int64_t(n / 32) * 34, n, act, act_stride, nt, out, out_stride, r0, r1, stream) == FNB_OK;
 }
+// fmt iq4_nl (fn::experts::cpu::iq4nl_down_rows, same bits): IQ4_NL weight rows against Q8_0 activation rows
+inline bool down_rows_iq4_nl(const uint8_t * w, int32_t n, const void * act, int64_t act_stride, int32_t nt, float * out,
+                             int64_t out_stride, int64_t r0, int64_t r1, void * stream) {
+    return fnb_expert_down_rows_iq4_nl(w, int64_t(n / 32) * 18, n, act, act_stride, nt, out, out_stride, r0, r1, stream) == FNB_OK;
+}
 
 }  // namespace experts
 

@@ -461,6 +461,24 @@ void fnbo_expert_down_rows(int32_t fmt, const uint8_t * w, int64_t row_bytes, in
                     xd = fnbo_f16_to_f32(dh);
                     summs = fmaf(fnbo_f16_to_f32(mh), fnbo_f16_to_f32(ys), summs);
                     scale = xd * fnbo_f16_to_f32(yd);
+                } else if (fmt == 2) { /* IQ4_NL {d fp16; 16 nibble bytes -> kvalues_iq4nl} x Q8_0: cpu_iq_avx2.cpp:481-514 */
+                    static const int8_t kvalues[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+                    const uint8_t * b = row + ib * 18;
+                    uint16_t dh, yd;
+                    memcpy(&dh, b, 2);
+                    const uint8_t * y = a + ib * 34;
+                    memcpy(&yd, y, 2);
+                    qy = (const int8_t *) (y + 2);
+                    /* the kernel multiplies |w| by the code with w's sign applied (_mm256_sign_epi8: two's complement,
+                     * -128 stays -128); stated here as w' x code with w' = w unless the code is -128 and w < 0 */
+                    for (int i = 0; i < 16; ++i) {
+                        qx[i] = kvalues[b[2 + i] & 15];
+                        qx[i + 16] = kvalues[b[2 + i] >> 4];
+                    }
+                    for (int i = 0; i < 32; ++i) {
+                        if (qy[i] == -128 && qx[i] < 0) qx[i] = -qx[i];
+                    }
+                    scale = fnbo_f16_to_f32(dh) * fnbo_f16_to_f32(yd);
                 } else { /* Q8_0 {d fp16; qs[32]} x Q8_0 */
                     const uint8_t * b = row + ib * 34;
                     uint16_t dh, yd;
@@ -476,6 +494,11 @@ void fnbo_expert_down_rows(int32_t fmt, const uint8_t * w, int64_t row_bytes, in
                     for (int i = 0; i < 4; ++i) s += qx[4 * j + i] * (int) qy[4 * j + i];
                     acc[j] = fmaf((float) s, scale, acc[j]);
                 }
+            }
+            if (fmt == 2) { /* the IQ file's hsum8 (:187-193): lane i + 4 onto lane i, then two horizontal adds */
+                const float s0 = acc[0] + acc[4], s1 = acc[1] + acc[5], s2 = acc[2] + acc[6], s3 = acc[3] + acc[7];
+                out[(int64_t) t * out_stride + r] = (s0 + s1) + (s2 + s3);
+                continue;
             }
             out[(int64_t) t * out_stride + r] = fnbo_hsum8(acc) + summs;
         }

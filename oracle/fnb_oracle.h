@@ -115,7 +115,9 @@ void fnbo_expert_gu_rows_iq3_xxs(const uint8_t * gate, const uint8_t * up, int64
  * ggml's Q5_1 weights against Q8_1 activations (fmt 0) or Q8_0 weights against Q8_0 activations (fmt 1).  Follows the
  * reference's CPU kernels lane for lane (fn/kernels/experts/cpu_kq_avx2.cpp:293-344, :382-394): eight F32 accumulators
  * per (row, t), accumulator j taking bytes 4 j .. 4 j + 3 of every block by one fused multiply-add per block, reduced
- * once at the end in hsum_float_8's order (:103-109).  w: rows of n / 32 blocks, row r at w + r row_bytes; act: nt rows of
+ * once at the end in hsum_float_8's order (:103-109).  fmt 2: ggml IQ4_NL weights (18-byte blocks: fp16 d, 16 nibble
+ * bytes indexing kvalues_iq4nl) against Q8_0 activations, fn/kernels/experts/cpu_iq_avx2.cpp:481-514: |w| times the
+ * code with w's sign applied (a -128 code stays -128), reduced in that file's hsum8 order (:187-193).  w: rows of n / 32 blocks, row r at w + r row_bytes; act: nt rows of
  * n / 32 activation blocks, row t at act + t act_stride; out[t * out_stride + r] for r in [r0, r1). */
 void fnbo_expert_down_rows(int32_t fmt, const uint8_t * w, int64_t row_bytes, int32_t n, const uint8_t * act,
                            int64_t act_stride, int32_t nt, float * out, int64_t out_stride, int64_t r0, int64_t r1);

@@ -313,13 +313,13 @@ def quantize_q8_k(x: np.ndarray, which: str = "oracle") -> np.ndarray:
     return out.reshape(-1, Q8_K_BYTES)
 
 
-DOWN_FMT = {"q5_1": (0, 24, Q8_1_BYTES), "q8_0": (1, Q8_0_BYTES, Q8_0_BYTES)}   # code, weight block, activation block
+DOWN_FMT = {"q5_1": (0, 24, Q8_1_BYTES), "q8_0": (1, Q8_0_BYTES, Q8_0_BYTES), "iq4_nl": (2, 18, Q8_0_BYTES)}   # code, weight block, activation block
 
 
 def expert_down_rows(fmt: str, w: np.ndarray, act: np.ndarray, n: int, r0: int = 0, r1: int | None = None,
                      use_ref: bool = False) -> np.ndarray:
     """out[t][r] = weight row r . act[t]: w uint8 [rows][n/32 * weight block], act uint8 [nt][n/32 * activation block]
-    (Q8_1 blocks for "q5_1" weights, Q8_0 blocks for "q8_0").  use_ref: the reference's own AVX2 kernel."""
+    (Q8_1 blocks for "q5_1" weights, Q8_0 blocks for "q8_0" and "iq4_nl").  use_ref: the reference's own AVX2 kernel."""
     code, wb, ab = DOWN_FMT[fmt]
     w, act = np.ascontiguousarray(w, np.uint8), np.ascontiguousarray(act, np.uint8)
     rows, nt = w.shape[0], act.shape[0]

@@ -113,6 +113,10 @@ void ref_kq_down_rows(int32_t f, const uint8_t * w, int64_t row_bytes, int32_t n
     const void * a[64];
     float * o[64];
     for (int t = 0; t < nt && t < 64; ++t) a[t] = act + int64_t(t) * act_stride, o[t] = out + int64_t(t) * out_stride;
+    if (f == 2) {  // IQ4_NL x Q8_0 (fn/kernels/experts/cpu_iq_avx2.cpp:571-578)
+        fn::experts::cpu::iq4nl_down_rows(w, size_t(row_bytes), n, a, nt, o, r0, r1);
+        return;
+    }
     fn::experts::cpu::kq_down_rows(f == 0 ? fn::experts::fmt::q5_1 : fn::experts::fmt::q8_0, w, size_t(row_bytes), n, a, nt,
                                    o, r0, r1);
 }

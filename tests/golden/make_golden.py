@@ -111,6 +111,22 @@ def down_rows() -> None:
     print("down_rows.npz", os.path.getsize(os.path.join(HERE, "down_rows.npz")), "bytes")
 
 
+def down_rows_iq4_nl() -> None:
+    """The reference's own AVX2 IQ4_NL down mat-vec (fn::experts::cpu::iq4nl_down_rows) on seeded weights and Q8_0
+    activations; the second case's activations are random blocks, -128 codes among them (its sign step leaves them)."""
+    from fnfl_v100_b200 import synth
+    g = synth.rng(0x344e4c)
+    rec = {}
+    for key, n, rows, nt in (("quantised", 640, 67, 5), ("random", 128, 19, 8)):
+        w = synth.iq4_nl_rows(g, rows, n)
+        act = O.quantize_q8_0(synth.normal(g, (nt, n), 2.0)).reshape(nt, -1) if key == "quantised" else synth.q8_0_table(g, nt, n)
+        rec[f"{key}_{n}|w"], rec[f"{key}_{n}|act"] = w, act
+        rec[f"{key}_{n}|out"] = O.expert_down_rows("iq4_nl", w, act, n, use_ref=True)
+    assert (rec["random_128|act"].reshape(8, -1, 34)[:, :, 2:] == 0x80).sum() > 0
+    np.savez_compressed(os.path.join(HERE, "down_rows_iq4_nl.npz"), **rec)
+    print("down_rows_iq4_nl.npz", os.path.getsize(os.path.join(HERE, "down_rows_iq4_nl.npz")), "bytes")
+
+
 def q8_k() -> None:
     """ggml's quantize_row_q8_K_ref and the reference's AVX2 quantize_q8_k on stress blocks (ties between +a and -a in
     both orders, zeros, tiny and huge magnitudes, constant blocks, half steps) and random ones; the two must agree."""
@@ -193,6 +209,7 @@ def main() -> None:
     O.build(with_ref=True)
     model_file()
     down_rows()
+    down_rows_iq4_nl()
     q8_k()
     gate_up_rows()
     gate_up_rows_q5_k()

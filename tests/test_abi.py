@@ -94,6 +94,12 @@ def test_rejections_enqueue_nothing(lib):
         a = list(ok5)
         a[i] = bad
         assert lib.fnb_expert_gate_up_rows_q5_k(*a) == R, (i, bad)
+    # IQ4_NL down rows: an odd number of blocks a row, rows not back to back, a window of 0 rows, short out rows
+    ok4 = (A16, 360, 640, A16, 680, 3, A16, 2560, 0, 2560, None)
+    for i, bad in ((2, 672), (1, 364), (5, 0), (5, 65), (9, 0), (7, 100), (0, None), (4, 678), (4, 681)):
+        a = list(ok4)
+        a[i] = bad
+        assert lib.fnb_expert_down_rows_iq4_nl(*a) == R, (i, bad)
     # the IQ3_XXS form: an odd number of super-blocks a row (rows off 4-byte boundaries), rows not back to back
     ok3 = (A16, A16, 980, 2560, A16, 2920, 3, A16, 640, None, 0, 640, None)
     for i, bad in ((3, 2304), (2, 984), (6, 0), (6, 65), (11, 0), (8, 100), (0, ODD), (4, None), (5, 2916)):

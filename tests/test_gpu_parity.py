@@ -421,31 +421,34 @@ def test_expert_gate_up_rows_iq3_xxs_bit_exact(dev, oracle, n, rows, nt, m128):
     assert np.abs(want[:, r0:r1]).max() < 1e3 and np.abs(wgu[0][:, r0:r1]).std() > 0.3   # gates of order one: the GLU is exercised
 
 
-def test_expert_ffn_for_a_decode_window_stage_by_stage(dev, oracle):
+@pytest.mark.parametrize("fmt", ["q4_k", "q5_k", "iq3_xxs"])
+def test_expert_ffn_for_a_decode_window_stage_by_stage(dev, oracle, fmt):
     """One routed expert for a window of three rows, every hand-over on the device: RMSNorm -> Q8_K -> gate / up mat-vec
-    with the GLU (Q4_K) -> Q8_1 -> down mat-vec (Q5_1).  Each stage is checked bit for bit against the oracle applied to
-    the previous stage's device output, and the end against the all-CPU chain."""
+    with the GLU (Q4_K, Q5_K or IQ3_XXS) -> Q8_1 -> down mat-vec (Q5_1).  Each stage is checked bit for bit against the
+    oracle applied to the previous stage's device output, and the end against the all-CPU chain."""
     g = synth.rng(77)
     nt, d_model, d_ff = 3, 2560, 640
     x, w = synth.normal(g, (nt, d_model), 1.0), synth.norm_weight(g, d_model)
-    gate, up = synth.q4_k_table(g, d_ff, d_model, 1e-5, 3e-4), synth.q4_k_table(g, d_ff, d_model, 1e-5, 3e-4)
+    table, d_lo, d_hi = {"q4_k": (synth.q4_k_table, 1e-5, 3e-4), "q5_k": (synth.q5_k_table, 1e-5, 1.5e-4),
+                         "iq3_xxs": (synth.iq3_xxs_table, 5e-5, 4e-4)}[fmt]
+    gate, up = table(g, d_ff, d_model, d_lo, d_hi), table(g, d_ff, d_model, d_lo, d_hi)
     down = synth.q5_1_rows(g, d_model, d_ff)
     D = lambda a: to_dev(a, dev)  # noqa: E731
     normed = ops.rms_norm(D(x), D(w), 1e-6)
     q8k = ops.quantize_q8_k(normed)
-    ff = ops.expert_gate_up_rows_q4_k(D(gate), D(up), q8k, d_model)
+    ff = ops.expert_gate_up_rows(fmt, D(gate), D(up), q8k, d_model)
     q81 = ops.quantize_q8_1(ff)
     out = ops.expert_down_rows("q5_1", D(down), q81, d_ff)
     torch.cuda.synchronize()
     H = lambda t: t.cpu().numpy()  # noqa: E731
     assert ulp_diff(H(normed), oracle.rms_norm(x, w, 1e-6)).max() <= 2
     assert np.array_equal(H(q8k).reshape(-1, 292), oracle.quantize_q8_k(H(normed)))
-    assert np.array_equal(bits(H(ff)), bits(oracle.expert_gu_rows_q4_k(gate, up, H(q8k), d_model)))
+    assert np.array_equal(bits(H(ff)), bits(oracle.expert_gu_rows(fmt, gate, up, H(q8k), d_model)))
     assert np.array_equal(H(q81).reshape(-1), oracle.quantize_q8_1(H(ff)).reshape(-1))
     assert np.array_equal(bits(H(out)), bits(oracle.expert_down_rows("q5_1", down, H(q81).reshape(nt, -1), d_ff)))
     # the all-CPU chain (its RMSNorm sums in another order: the device result may sit an ulp away, and a code with it)
     c_norm = oracle.rms_norm(x, w, 1e-6)
-    c_ff = oracle.expert_gu_rows_q4_k(gate, up, oracle.quantize_q8_k(c_norm).reshape(nt, -1), d_model)
+    c_ff = oracle.expert_gu_rows(fmt, gate, up, oracle.quantize_q8_k(c_norm).reshape(nt, -1), d_model)
     c_out = oracle.expert_down_rows("q5_1", down, oracle.quantize_q8_1(c_ff).reshape(nt, -1), d_ff)
     assert np.abs(H(out) - c_out).max() <= 1e-3 * np.abs(c_out).max()
 
@@ -492,6 +495,56 @@ def test_expert_down_rows_q8_0_bit_exact(dev, oracle, n, rows, nt):
     got = ops.expert_down_rows("q8_0", to_dev(w, dev), act, n).cpu().numpy()
     want = oracle.expert_down_rows("q8_0", w, act.cpu().numpy().reshape(nt, -1), n)
     assert np.array_equal(bits(got), bits(want))
+
+
+def test_expert_down_rows_iq4_nl_equal_the_reference_avx2_kernel_on_golden(dev):
+    gold = np.load(os.path.join(GOLD, "down_rows_iq4_nl.npz"))
+    for key in sorted({k.split("|")[0] for k in gold.files}):
+        n = int(key.rsplit("_", 1)[1])
+        got = ops.expert_down_rows("iq4_nl", to_dev(gold[key + "|w"], dev), to_dev(gold[key + "|act"], dev), n).cpu().numpy()
+        assert np.array_equal(bits(got), bits(gold[key + "|out"])), key
+
+
+@pytest.mark.parametrize("n,rows,nt,raw", [(640, 2560, 1, False), (640, 777, 5, False), (64, 40, 2, True), (2048, 129, 11, False),
+                                           (320, 1001, 3, True), (8192, 21, 8, False)])
+def test_expert_down_rows_iq4_nl_bit_exact(dev, oracle, n, rows, nt, raw):
+    """IQ4_NL weights against Q8_0 blocks: the ones fnb_quantize_q8_0 writes, or (raw) random blocks with -128 codes
+    among them; rows outside [r0, r1) stay untouched; every row offset within 16 bytes (320 columns: 180-byte rows)."""
+    g = synth.rng(36)
+    if raw:
+        act = to_dev(synth.q8_0_table(g, nt, n), dev)
+    else:
+        act = ops.quantize_q8_0(to_dev(synth.normal(g, (nt, n), 2.0), dev)).reshape(nt, -1)
+    w = synth.iq4_nl_rows(g, rows, n)
+    r0, r1 = 3, rows - 2
+    out = torch.full((nt, rows), float("nan"), dtype=torch.float32, device=dev)
+    ops.expert_down_rows("iq4_nl", to_dev(w, dev), act, n, r0=r0, r1=r1, out=out)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    want = oracle.expert_down_rows("iq4_nl", w, act.cpu().numpy().reshape(nt, -1), n, r0=r0, r1=r1)
+    assert np.array_equal(bits(got[:, r0:r1]), bits(want[:, r0:r1]))
+    assert np.isnan(got[:, :r0]).all() and np.isnan(got[:, r1:]).all()
+
+
+def test_expert_ffn_in_the_iq_formats_stage_by_stage(dev, oracle):
+    """The IQ-format expert for a window of three rows, every hand-over on the device: RMSNorm -> Q8_K -> IQ3_XXS gate / up
+    with the GLU -> Q8_0 -> IQ4_NL down; each stage bit for bit against the oracle on the previous stage's device output."""
+    g = synth.rng(78)
+    nt, d_model, d_ff = 3, 2560, 640
+    x, w = synth.normal(g, (nt, d_model), 1.0), synth.norm_weight(g, d_model)
+    gate, up = synth.iq3_xxs_table(g, d_ff, d_model, 5e-5, 4e-4), synth.iq3_xxs_table(g, d_ff, d_model, 5e-5, 4e-4)
+    down = synth.iq4_nl_rows(g, d_model, d_ff)
+    D = lambda a: to_dev(a, dev)  # noqa: E731
+    H = lambda t: t.cpu().numpy()  # noqa: E731
+    q8k = ops.quantize_q8_k(ops.rms_norm(D(x), D(w), 1e-6))
+    ff = ops.expert_gate_up_rows("iq3_xxs", D(gate), D(up), q8k, d_model)
+    q80 = ops.quantize_q8_0(ff).reshape(nt, -1)
+    out = ops.expert_down_rows("iq4_nl", D(down), q80, d_ff)
+    torch.cuda.synchronize()
+    assert np.array_equal(bits(H(ff)), bits(oracle.expert_gu_rows("iq3_xxs", gate, up, H(q8k), d_model)))
+    assert np.array_equal(H(q80).reshape(-1), oracle.quantize_q8_0(H(ff)).reshape(-1))
+    assert np.array_equal(bits(H(out)), bits(oracle.expert_down_rows("iq4_nl", down, H(q80), d_ff)))
+    assert np.abs(H(out)).max() > 1e-3
 
 
 # ---- get_rows ----------------------------------------------------------------------------------------------------------

@@ -139,6 +139,15 @@ def test_expert_down_rows_match_the_reference_avx2_kernel(oracle):
         assert np.array_equal(part[:, 3:8].view(np.uint32), want[:, 3:8].view(np.uint32)) and not part[:, :3].any()
 
 
+def test_expert_down_rows_iq4_nl_match_the_reference_avx2_kernel(oracle):
+    """tests/golden/down_rows_iq4_nl.npz: outputs of the reference's own iq4nl_down_rows, one case with -128 codes."""
+    gold = np.load(os.path.join(GOLD, "down_rows_iq4_nl.npz"))
+    for key in sorted({k.split("|")[0] for k in gold.files}):
+        n = int(key.rsplit("_", 1)[1])
+        got = oracle.expert_down_rows("iq4_nl", gold[key + "|w"], gold[key + "|act"], n)
+        assert np.array_equal(got.view(np.uint32), gold[key + "|out"].view(np.uint32)), key
+
+
 def test_q8_k_matches_ggml_and_the_reference_avx2_form(oracle):
     """tests/golden/q8_k.npz: blocks from ggml's quantize_row_q8_K_ref, equal to the reference's AVX2 quantize_q8_k."""
     gold = np.load(os.path.join(GOLD, "q8_k.npz"))
