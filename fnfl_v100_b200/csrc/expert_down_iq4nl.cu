@@ -20,11 +20,18 @@
 #ifndef FNB_DOWN_IQ4_GRID
 #define FNB_DOWN_IQ4_GRID 4
 #endif
+#ifndef FNB_DOWN_IQ4_UNROLL
+#define FNB_DOWN_IQ4_UNROLL 1
+#endif
+#ifndef FNB_DOWN_IQ4_WARPS
+#define FNB_DOWN_IQ4_WARPS 8
+#endif
 
 namespace fnb {
 namespace {
 
-constexpr int kMaxWarps = 8;
+constexpr int kMaxWarps = FNB_DOWN_IQ4_WARPS;
+constexpr int kPairUnroll = FNB_DOWN_IQ4_UNROLL;
 constexpr int kMaxT = 8;
 constexpr int kRowsPerWarp = 8;
 constexpr size_t kSmemLimit = 200 * 1024;
@@ -67,8 +74,8 @@ __device__ __forceinline__ int dot_sign_applied(uint32_t w, uint32_t y) {
 
 // two blocks (36 bytes, 4-byte aligned) of the lane's row: words 0 .. 8 = d0 | 16 nibble bytes | d1 | 16 nibble bytes
 template <int NT, bool WRAP>
-__device__ __forceinline__ void dot_pair(const uint32_t * x, const uint2 * codes_sm, const float * d_sm, int nb, int ib, int k,
-                                         float (&acc)[NT][2]) {
+__device__ __forceinline__ void dot_pair(const uint32_t * x, const uint2 * yk, const float * dk, int nb, int k,
+                                         float (&acc)[NT][2]) {  // yk, dk: the lane's codes and the scales of this pair, row 0
     const uint32_t w0 = x[0], w4 = x[4];
     const uint32_t qa = __funnelshift_r(x[k], x[k + 1], 16);  // block ib: bytes 2 + 4 k .. 5 + 4 k
     const uint32_t qb = x[5 + k];                             // block ib + 1: bytes 20 + 4 k ..
@@ -78,9 +85,8 @@ __device__ __forceinline__ void dot_pair(const uint32_t * x, const uint2 * codes
     decode8(qb, blo, bhi);
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
-        const int b = t * nb + ib;
-        const uint2 ya = codes_sm[b * 4 + k], yb = codes_sm[(b + 1) * 4 + k];  // codes 4 k .. and 16 + 4 k ..
-        const float sa = __fmul_rn(da, d_sm[b]), sb = __fmul_rn(db, d_sm[b + 1]);
+        const uint2 ya = yk[t * nb * 4], yb = yk[t * nb * 4 + 4];  // codes 4 k .. and 16 + 4 k .. of the two blocks
+        const float sa = __fmul_rn(da, dk[t * nb]), sb = __fmul_rn(db, dk[t * nb + 1]);
         int pa0, pa1, pb0, pb1;
         if (WRAP) {
             pa0 = dot_sign_applied(alo, ya.x), pa1 = dot_sign_applied(ahi, ya.y);
@@ -130,7 +136,10 @@ __device__ __forceinline__ void run_warp(const uint8_t * __restrict__ w, int64_t
         float acc[NT][2];
 #pragma unroll
         for (int t = 0; t < NT; ++t) acc[t][0] = 0.0f, acc[t][1] = 0.0f;
-        for (int ib = 0; ib < nb; ib += 2, x += 9) dot_pair<NT, WRAP>(x, codes_sm, d_sm, nb, ib, k, acc);
+#pragma unroll kPairUnroll
+        const uint2 * yk = codes_sm + k;
+        const float * dk = d_sm;
+        for (int ib = 0; ib < nb; ib += 2, x += 9, yk += 8, dk += 2) dot_pair<NT, WRAP>(x, yk, dk, nb, k, acc);
         __syncwarp();  // every lane is done with the buffer the next trip's copies overwrite
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
