@@ -1,7 +1,7 @@
 // The routed experts' gate / up mat-vec for a decode window with the GLU fused,
 //     ff[t][r] = silu(g) u,   g = gate row r . act[t],  u = up row r . act[t],   t < nt,  r in [r0, r1)
-// with ggml IQ3_XXS weights against Q8_K activations (fnb_quantize_q8_k).  Replaces fn::experts::cpu::iq_gu_rows for
-// fmt iq3_xxs (fn/kernels/experts/cpu_kernels.h:67; cpu_iq_avx2.cpp:256-271 decode, :305-337 row_dot, :429-445 gu_rows)
+// with ggml IQ3_XXS or IQ3_S weights against Q8_K activations (fnb_quantize_q8_k).  Replaces fn::experts::cpu::iq_gu_rows
+// for fmt iq3_xxs and iq3_s (IQ3_S: cpu_iq_avx2.cpp:273-290, described at `shape` below; IQ3_XXS: fn/kernels/experts/cpu_kernels.h:67; cpu_iq_avx2.cpp:256-271 decode, :305-337 row_dot, :429-445 gu_rows)
 // and returns the SAME BITS: the AVX2 kernel keeps, per (row, t), eight int32 lanes a super-block - lane l collects,
 // over the block's eight groups of 32 values, (2 s + 1) x the four codebook bytes of the group's index byte l times the
 // sign-applied Q8_K codes 32 g + 4 l .. - adds them as floats by one fused multiply-add per super-block and lane with
@@ -43,21 +43,35 @@ namespace {
 constexpr int kMaxWarps = 12;
 constexpr int kMaxT = 8;
 constexpr int kWholeRowBlocks = 10;                  // rows of up to ten super-blocks (2560 columns) are staged whole,
-constexpr int kChunkBlocks = 8;                      // longer ones eight super-blocks (784 = 49 x 16 bytes) at a time
-constexpr int kSlotBytes = 1008;                     // ten blocks, 12 bytes of source offset, rounded up to 16
-constexpr int kUnitBytes = 8 * kSlotBytes;           // four gate rows, then four up rows
-constexpr int kWarpStage = 2 * kUnitBytes;           // two units: the one computed on and the one in flight
+constexpr int kChunkBlocks = 8;                      // longer ones eight super-blocks (a multiple of 16 bytes) at a time
 constexpr int kGridCopies = 32;                      // the codebook once per bank
-constexpr int kGridBytes = 256 * kGridCopies * 4;
 constexpr int kSignCopies = 16;                      // 8-byte entries: a half-warp's lookups fill the 32 banks
-constexpr int kSignBytes = 128 * kSignCopies * 8;
-constexpr int kTableBytes = kGridBytes + kSignBytes;
-constexpr int kSpanBytes = 4 * kWholeRowBlocks * 98 + 16;  // four whole rows, back to back as in global memory
-constexpr size_t kSmemLimit = 225 * 1024;            // one CTA an SM (227 KB less the static arrays)
+
+// S: ggml IQ3_S rows (110-byte super-blocks: d, qs[64], qh[8], signs[32], scales[4]; 512-entry codebook, plain sign
+// bits, one 4-bit scale per 32 values) instead of IQ3_XXS (98 bytes: d, qs[64], eight words of 4 x 7-bit sign index +
+// 4-bit scale; 256-entry codebook)
+template <bool S>
+struct shape {
+    static constexpr int kBlock = S ? 110 : 98;
+    // a slot: ten blocks and 12 bytes of source offset, rounded up so that the eight slots start in different banks
+    static constexpr int kSlot = S ? 1136 : 1008;
+    static constexpr int kUnit = 8 * kSlot;           // four gate rows, then four up rows
+    static constexpr int kWarpStage = 2 * kUnit;      // two units: the one computed on and the one in flight
+    static constexpr int kSpan = 4 * kWholeRowBlocks * kBlock + 16;  // four whole rows, back to back as in global memory
+    static constexpr int kGridEntries = S ? 512 : 256;
+    static constexpr int kGridBytes = kGridEntries * kGridCopies * 4;
+    static constexpr int kSignBytes = S ? 0 : 128 * kSignCopies * 8;  // IQ3_S's sign bits need no table
+    static constexpr int kTableBytes = kGridBytes + kSignBytes;
+    static_assert(2 * kSpan <= kUnit, "two spans fit a unit");
+};
+constexpr size_t kSmemLimit = 224 * 1024;            // one CTA an SM (227 KB less the static arrays)
 constexpr int kGridPerSm = FNB_GU_IQ3_GRID;
 
 __constant__ uint16_t c_grid_packed[256] = {
 #include "iq3xxs_grid_packed.inc"
+};
+__constant__ uint16_t c_grid3s_packed[512] = {
+#include "iq3s_grid_packed.inc"
 };
 
 // 0xFF in byte j where bit j of a 4-bit sign field is set: the field times 0x10204080 puts bit j at the top of byte j,
@@ -78,40 +92,47 @@ __device__ __forceinline__ int signed_codes(uint32_t y, uint32_t mff) {
 }
 
 // where row r's chunk of a matrix starts; a ragged last quad re-reads the last row (its results are not stored)
+template <bool S>
 __device__ __forceinline__ const uint8_t * chunk_src(const uint8_t * mat, int64_t row_bytes, int64_t r, int64_t r1, int chunk) {
-    return mat + (r < r1 ? r : r1 - 1) * row_bytes + int64_t(chunk) * (kChunkBlocks * 98);
+    return mat + (r < r1 ? r : r1 - 1) * row_bytes + int64_t(chunk) * (kChunkBlocks * shape<S>::kBlock);
 }
 
+template <bool S>
 __device__ __forceinline__ void stage_unit(uint32_t buf_sm, const uint8_t * __restrict__ gate, const uint8_t * __restrict__ up,
                                            int64_t row_bytes, int64_t r4, int64_t r1, int chunk, int bytes, int lane) {
 #pragma unroll
     for (int slot = 0; slot < 8; ++slot) {
-        stage_span(buf_sm + slot * kSlotBytes, chunk_src(slot < 4 ? gate : up, row_bytes, r4 + (slot & 3), r1, chunk), bytes, lane);
+        stage_span(buf_sm + slot * shape<S>::kSlot, chunk_src<S>(slot < 4 ? gate : up, row_bytes, r4 + (slot & 3), r1, chunk), bytes,
+                   lane);
     }
     cp_async_commit();
 }
 
 // rows of up to ten super-blocks: the quad's four gate rows are one contiguous span of the matrix, its up rows another
+template <bool S>
 __device__ __forceinline__ void stage_unit_whole(uint32_t buf_sm, const uint8_t * __restrict__ gate,
                                                  const uint8_t * __restrict__ up, int64_t row_bytes, int64_t r4, int64_t r1,
                                                  int lane) {
     const int rows = r1 - r4 < 4 ? int(r1 - r4) : 4;  // a ragged last quad leaves its missing rows' bytes as they were
     stage_span(buf_sm, gate + r4 * row_bytes, rows * int(row_bytes), lane);
-    stage_span(buf_sm + kSpanBytes, up + r4 * row_bytes, rows * int(row_bytes), lane);
+    stage_span(buf_sm + shape<S>::kSpan, up + r4 * row_bytes, rows * int(row_bytes), lane);
     cp_async_commit();
 }
 
 // one staged unit (n_blk super-blocks of the lane's row, x) against the window: acc[t][0 / 1] are AVX2 lanes 2 k, 2 k + 1
-template <int NT, bool WRAP>
+template <int NT, bool WRAP, bool S>
 __device__ __forceinline__ void dot_unit(const uint8_t * x, int n_blk, const uint8_t * codes_sm, const float * d_sm, int nb,
                                          int blk0, int k, const uint32_t * grid_lane, const uint2 * sign_lane, float (&acc)[NT][2]) {
     const int sh7 = 7 * k;
 #pragma unroll 1
-    for (int i = 0; i < n_blk; ++i, x += 98) {
-        // lane k holds the sign / scale words of groups k and k + 4 (2-byte aligned); each group's reaches the row's
-        // four lanes by a shuffle
-        const uint16_t * pw = reinterpret_cast<const uint16_t *>(x + 66 + 4 * k);
-        const uint32_t own_lo = uint32_t(pw[0]) | (uint32_t(pw[1]) << 16), own_hi = uint32_t(pw[8]) | (uint32_t(pw[9]) << 16);
+    for (int i = 0; i < n_blk; ++i, x += shape<S>::kBlock) {
+        // IQ3_XXS: lane k holds the sign / scale words of groups k and k + 4 (2-byte aligned); each group's reaches the
+        // row's four lanes by a shuffle
+        uint32_t own_lo = 0, own_hi = 0;
+        if (!S) {
+            const uint16_t * pw = reinterpret_cast<const uint16_t *>(x + 66 + 4 * k);
+            own_lo = uint32_t(pw[0]) | (uint32_t(pw[1]) << 16), own_hi = uint32_t(pw[8]) | (uint32_t(pw[9]) << 16);
+        }
         const float dx = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(x));
         int a0[NT], a1[NT];
 #pragma unroll
@@ -120,12 +141,25 @@ __device__ __forceinline__ void dot_unit(const uint8_t * x, int n_blk, const uin
         uint4 y4[NT];
 #pragma unroll
         for (int grp = 0; grp < 8; ++grp) {
-            const uint32_t w = __shfl_sync(kFull, grp < 4 ? own_lo : own_hi, grp & 3, 4);
             const uint32_t h = *reinterpret_cast<const uint16_t *>(x + 2 + 8 * grp + 2 * k);  // index bytes 2 k, 2 k + 1
-            const uint32_t c0 = grid_lane[(h & 0xffu) * kGridCopies], c1 = grid_lane[(h >> 8) * kGridCopies];
-            const uint2 sg = sign_lane[((w >> sh7) & 127u) * kSignCopies];  // the group's sign index k
-            const uint32_t m0 = sg.x, m1 = sg.y;
-            const int sc = int(2u * (w >> 28) + 1u);
+            uint32_t e0 = h & 0xffu, e1 = h >> 8, m0, m1;
+            int sc;
+            if (S) {
+                // ninth index bits 2 k, 2 k + 1 of the group's qh byte; sign byte k of the group's four (bit i: value
+                // 8 k + i); the group's nibble of the scale byte it shares with its neighbour
+                const uint32_t hb = uint32_t(x[66 + grp]) >> (2 * k);
+                e0 |= (hb & 1u) << 8, e1 |= (hb & 2u) << 7;
+                const uint32_t sb = x[74 + 4 * grp + k];
+                m0 = spread_msb((sb & 15u) * 0x10204080u), m1 = spread_msb((sb >> 4) * 0x10204080u);
+                const uint32_t s = x[106 + (grp >> 1)];
+                sc = int(2u * ((grp & 1) ? s >> 4 : s & 15u) + 1u);
+            } else {
+                const uint32_t w = __shfl_sync(kFull, grp < 4 ? own_lo : own_hi, grp & 3, 4);
+                const uint2 sg = sign_lane[((w >> sh7) & 127u) * kSignCopies];  // the group's sign index k
+                m0 = sg.x, m1 = sg.y;
+                sc = int(2u * (w >> 28) + 1u);
+            }
+            const uint32_t c0 = grid_lane[e0 * kGridCopies], c1 = grid_lane[e1 * kGridCopies];
             const int v0 = WRAP ? int(c0) : signed_grid(c0, m0), v1 = WRAP ? int(c1) : signed_grid(c1, m1);
 #pragma unroll
             for (int t = 0; t < NT; ++t) {
@@ -150,7 +184,7 @@ __device__ __forceinline__ void dot_unit(const uint8_t * x, int n_blk, const uin
     }
 }
 
-template <int NT, bool WRAP>
+template <int NT, bool WRAP, bool S>
 __device__ __forceinline__ void run_warp(const uint8_t * __restrict__ gate, const uint8_t * __restrict__ up, int64_t row_bytes,
                                          int nb, const uint8_t * codes_sm, const float * d_sm, uint8_t * stage,
                                          const uint32_t * grid_sm, const uint2 * sign_sm, float * __restrict__ ff,
@@ -168,9 +202,9 @@ __device__ __forceinline__ void run_warp(const uint8_t * __restrict__ gate, cons
     const uint8_t * mine = mat == 0 ? gate : up;
     int c = 0, trip = 0;
     if (whole) {
-        stage_unit_whole(stage_sm, gate, up, row_bytes, r0 + 4 * q, r1, lane);
+        stage_unit_whole<S>(stage_sm, gate, up, row_bytes, r0 + 4 * q, r1, lane);
     } else {
-        stage_unit(stage_sm, gate, up, row_bytes, r0 + 4 * q, r1, 0, blocks_of(0) * 98, lane);
+        stage_unit<S>(stage_sm, gate, up, row_bytes, r0 + 4 * q, r1, 0, blocks_of(0) * shape<S>::kBlock, lane);
     }
     float acc[NT][2];
 #pragma unroll
@@ -181,11 +215,11 @@ __device__ __forceinline__ void run_warp(const uint8_t * __restrict__ gate, cons
         if (cn == n_chunks) cn = 0, qn = q + stride;
         const bool more = qn < n_quads;
         if (more) {
-            const uint32_t next_sm = stage_sm + uint32_t((trip + 1) & 1) * kUnitBytes;
+            const uint32_t next_sm = stage_sm + uint32_t((trip + 1) & 1) * shape<S>::kUnit;
             if (whole) {
-                stage_unit_whole(next_sm, gate, up, row_bytes, r0 + 4 * qn, r1, lane);
+                stage_unit_whole<S>(next_sm, gate, up, row_bytes, r0 + 4 * qn, r1, lane);
             } else {
-                stage_unit(next_sm, gate, up, row_bytes, r0 + 4 * qn, r1, cn, blocks_of(cn) * 98, lane);
+                stage_unit<S>(next_sm, gate, up, row_bytes, r0 + 4 * qn, r1, cn, blocks_of(cn) * shape<S>::kBlock, lane);
             }
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
@@ -194,15 +228,15 @@ __device__ __forceinline__ void run_warp(const uint8_t * __restrict__ gate, cons
         __syncwarp();
         const int64_t r = r0 + 4 * q + sub;
         {
-            const uint8_t * x = stage + (trip & 1) * kUnitBytes;
+            const uint8_t * x = stage + (trip & 1) * shape<S>::kUnit;
             if (whole) {
                 const uintptr_t src = reinterpret_cast<uintptr_t>(mine + (r0 + 4 * q) * row_bytes);
-                x += mat * kSpanBytes + (src & 15) + sub * int(row_bytes);
+                x += mat * shape<S>::kSpan + (src & 15) + sub * int(row_bytes);
             } else {
-                const uintptr_t src = reinterpret_cast<uintptr_t>(chunk_src(mine, row_bytes, r, r1, c));
-                x += (4 * mat + sub) * kSlotBytes + (src & 15);
+                const uintptr_t src = reinterpret_cast<uintptr_t>(chunk_src<S>(mine, row_bytes, r, r1, c));
+                x += (4 * mat + sub) * shape<S>::kSlot + (src & 15);
             }
-            dot_unit<NT, WRAP>(x, blocks_of(c), codes_sm, d_sm, nb, c * chunk_blocks, k, grid_sm + lane,
+            dot_unit<NT, WRAP, S>(x, blocks_of(c), codes_sm, d_sm, nb, c * chunk_blocks, k, grid_sm + lane,
                                sign_sm + (lane & (kSignCopies - 1)), acc);
         }
         __syncwarp();  // every lane is done with the buffer the next trip's copies overwrite
@@ -214,7 +248,7 @@ __device__ __forceinline__ void run_warp(const uint8_t * __restrict__ gate, cons
                 float a = acc[t][0], b = acc[t][1];
                 a = __fadd_rn(__shfl_down_sync(kFull, a, 2, 4), a), b = __fadd_rn(__shfl_down_sync(kFull, b, 2, 4), b);
                 a = __fadd_rn(a, __shfl_down_sync(kFull, a, 1, 4)), b = __fadd_rn(b, __shfl_down_sync(kFull, b, 1, 4));
-                const float dot = __fmul_rn(0.25f, __fadd_rn(a, b));
+                const float dot = __fmul_rn(S ? 1.0f : 0.25f, __fadd_rn(a, b));  // the format's K, applied to the reduced sum
                 const float us = __shfl_down_sync(kFull, dot, 16);  // the up row's sits 16 lanes above the gate row's
                 if (mat == 0 && k == 0 && r < r1) {
                     ff[int64_t(t) * ff_stride + r] = __fmul_rn(__fdiv_rn(dot, __fadd_rn(1.0f, exact_expf(-dot))), us);
@@ -231,27 +265,28 @@ __device__ __forceinline__ void run_warp(const uint8_t * __restrict__ gate, cons
     }
 }
 
-template <int NT>
+template <int NT, bool S>
 __global__ void __launch_bounds__(kMaxWarps * 32)
-    gate_up_iq3_xxs_kernel(const uint8_t * __restrict__ gate, const uint8_t * __restrict__ up, int64_t row_bytes, int nb,
+    gate_up_iq3_kernel(const uint8_t * __restrict__ gate, const uint8_t * __restrict__ up, int64_t row_bytes, int nb,
                            const uint8_t * __restrict__ act, int64_t act_stride, int act_bytes, float * __restrict__ ff,
                            int64_t ff_stride, float * __restrict__ gu, int64_t r0, int64_t r1) {
     // the codebook copies, the sign masks' copies, the window's codes [NT][nb][256] and scales [NT][nb], then each
     // warp's two units
     extern __shared__ __align__(16) uint8_t smem[];
-    __shared__ uint32_t s_grid[256];  // the codebook's four magnitudes per entry as bytes
+    __shared__ uint32_t s_grid[shape<S>::kGridEntries];  // the codebook's four magnitudes per entry as bytes
     uint32_t * grid_sm = reinterpret_cast<uint32_t *>(smem);
-    uint2 * sign_sm = reinterpret_cast<uint2 *>(smem + kGridBytes);
-    uint8_t * codes_sm = smem + kTableBytes;
+    uint2 * sign_sm = reinterpret_cast<uint2 *>(smem + shape<S>::kGridBytes);
+    uint8_t * codes_sm = smem + shape<S>::kTableBytes;
     float * d_sm = reinterpret_cast<float *>(codes_sm + size_t(NT) * nb * 256);
     load_exp2_table();
-    for (int i = threadIdx.x; i < 256; i += blockDim.x) {
-        const uint32_t c = c_grid_packed[i];
+    for (int i = threadIdx.x; i < shape<S>::kGridEntries; i += blockDim.x) {
+        const uint32_t c = S ? c_grid3s_packed[i] : c_grid_packed[i];  // four 3-bit levels
         uint32_t w = 0;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const uint32_t lvl = (c >> (3 * j)) & 7u;
-            w |= (lvl == 7u ? 62u : 4u + 8u * lvl) << (8 * j);
+            // IQ3_S: 1, 3 .. 15; IQ3_XXS: 4, 12 .. 52, 62
+            w |= (S ? 2u * lvl + 1u : (lvl == 7u ? 62u : 4u + 8u * lvl)) << (8 * j);
         }
         s_grid[i] = w;
     }
@@ -272,29 +307,29 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
         }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < 256 * kGridCopies; i += blockDim.x) grid_sm[i] = s_grid[i / kGridCopies];
-    for (int i = threadIdx.x; i < 128 * kSignCopies; i += blockDim.x) {
+    for (int i = threadIdx.x; i < shape<S>::kGridEntries * kGridCopies; i += blockDim.x) grid_sm[i] = s_grid[i / kGridCopies];
+    for (int i = threadIdx.x; i < (S ? 0 : 128 * kSignCopies); i += blockDim.x) {
         // sign index s7: values 0 .. 6 of its eight take bits 0 .. 6, value 7 their parity (ksigns_iq2xs)
         const uint32_t s7 = uint32_t(i) / kSignCopies;
         sign_sm[i] = make_uint2(spread_msb((s7 & 15u) * 0x10204080u),
                                 spread_msb((s7 >> 4) * 0x10204080u + (uint32_t(__popc(s7)) << 31)));
     }
     const int wrap = __syncthreads_or(has_m128);
-    uint8_t * stage = smem + kTableBytes + act_bytes + size_t(threadIdx.x >> 5) * kWarpStage;
+    uint8_t * stage = smem + shape<S>::kTableBytes + act_bytes + size_t(threadIdx.x >> 5) * shape<S>::kWarpStage;
     if (wrap) {
-        run_warp<NT, true>(gate, up, row_bytes, nb, codes_sm, d_sm, stage, grid_sm, sign_sm, ff, ff_stride, gu, r0, r1);
+        run_warp<NT, true, S>(gate, up, row_bytes, nb, codes_sm, d_sm, stage, grid_sm, sign_sm, ff, ff_stride, gu, r0, r1);
     } else {
-        run_warp<NT, false>(gate, up, row_bytes, nb, codes_sm, d_sm, stage, grid_sm, sign_sm, ff, ff_stride, gu, r0, r1);
+        run_warp<NT, false, S>(gate, up, row_bytes, nb, codes_sm, d_sm, stage, grid_sm, sign_sm, ff, ff_stride, gu, r0, r1);
     }
 }
 
-template <int NT>
+template <int NT, bool S>
 bool ensure_configured() {
     static std::atomic<bool> configured[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
     if (!configured[dev].load(std::memory_order_acquire)) {
-        if (cudaFuncSetAttribute(gate_up_iq3_xxs_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemLimit)) !=
+        if (cudaFuncSetAttribute(gate_up_iq3_kernel<NT, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemLimit)) !=
             cudaSuccess) {
             return false;
         }
@@ -304,51 +339,51 @@ bool ensure_configured() {
 }
 
 // window rows one launch can hold for nb super-blocks a row (their codes and scales and at least two warps' buffers)
-inline int window_rows(int nb) {
-    const size_t per_t = size_t(nb) * 260, room = kSmemLimit - kTableBytes - 2 * size_t(kWarpStage) - 16;
+template <bool S>
+int window_rows(int nb) {
+    const size_t per_t = size_t(nb) * 260, room = kSmemLimit - shape<S>::kTableBytes - 2 * size_t(shape<S>::kWarpStage) - 16;
     const size_t m = room / per_t;
     return int(m > size_t(kMaxT) ? size_t(kMaxT) : m);
 }
 
-template <int NT>
+template <int NT, bool S>
 int32_t launch_nt(const uint8_t * gate, const uint8_t * up, int64_t row_bytes, int nb, const uint8_t * act, int64_t act_stride,
                   float * ff, int64_t ff_stride, float * gu, int64_t r0, int64_t r1, cudaStream_t s) {
     const size_t act_bytes = (size_t(NT) * nb * 260 + 15) & ~size_t(15);
-    if (kTableBytes + act_bytes + kWarpStage > kSmemLimit) return FNB_REJECTED;
-    int warps = int((kSmemLimit - kTableBytes - act_bytes) / kWarpStage);  // one CTA an SM, as many warps as fit
+    constexpr size_t tables = shape<S>::kTableBytes, per_warp = shape<S>::kWarpStage;
+    if (tables + act_bytes + per_warp > kSmemLimit) return FNB_REJECTED;
+    int warps = int((kSmemLimit - tables - act_bytes) / per_warp);  // one CTA an SM, as many warps as fit
     warps = warps > kMaxWarps ? kMaxWarps : warps;
-    if (!ensure_configured<NT>()) return FNB_LAUNCH_FAILED;
-    const size_t smem = kTableBytes + act_bytes + size_t(warps) * kWarpStage;
+    if (!ensure_configured<NT, S>()) return FNB_LAUNCH_FAILED;
+    const size_t smem = tables + act_bytes + size_t(warps) * per_warp;
     const int64_t quads = (r1 - r0 + 3) / 4;
     const int grid = grid_for((quads + warps - 1) / warps, kGridPerSm);
-    gate_up_iq3_xxs_kernel<NT><<<grid, warps * 32, smem, s>>>(gate, up, row_bytes, nb, act, act_stride, int(act_bytes), ff,
+    gate_up_iq3_kernel<NT, S><<<grid, warps * 32, smem, s>>>(gate, up, row_bytes, nb, act, act_stride, int(act_bytes), ff,
                                                                 ff_stride, gu, r0, r1);
     return launch_status();
 }
 
-}  // namespace
-
-bool expert_gate_up_prepare_device() {
-    return ensure_configured<1>() && ensure_configured<2>() && ensure_configured<3>() && ensure_configured<4>() &&
-           ensure_configured<5>() && ensure_configured<6>() && ensure_configured<7>() && ensure_configured<8>();
+template <bool S>
+bool prepare_fmt() {
+    return ensure_configured<1, S>() && ensure_configured<2, S>() && ensure_configured<3, S>() && ensure_configured<4, S>() &&
+           ensure_configured<5, S>() && ensure_configured<6, S>() && ensure_configured<7, S>() && ensure_configured<8, S>();
 }
 
-}  // namespace fnb
-
-extern "C" int32_t fnb_expert_gate_up_rows_iq3_xxs(const void * gate, const void * up, int64_t row_bytes, int32_t n,
-                                                   const void * act, int64_t act_stride, int32_t nt, float * ff,
-                                                   int64_t ff_stride, float * gu, int64_t r0, int64_t r1, void * stream) {
-    using namespace fnb;
+template <bool S>
+int32_t gate_up_rows(const void * gate, const void * up, int64_t row_bytes, int32_t n, const void * act, int64_t act_stride,
+                     int32_t nt, float * ff, int64_t ff_stride, float * gu, int64_t r0, int64_t r1, void * stream) {
     if (!ok_ptr(gate, 16) || !ok_ptr(up, 16) || !ok_ptr(act, 4) || !ok_ptr(ff, 4) || !ok_opt(gu, 4)) return FNB_REJECTED;
-    // an even number of 98-byte super-blocks a row: rows on 4-byte boundaries, which the copies into shared memory need
+    // an even number of super-blocks a row: rows on 4-byte boundaries, which the copies into shared memory need
     if (n < 512 || n > 16384 || n % 512 != 0 || nt < 1 || nt > 64 || r0 < 0 || r1 <= r0 || r1 - r0 > INT32_MAX) return FNB_REJECTED;
     const int nb = n / 256;
-    if (row_bytes != int64_t(nb) * 98 || act_stride < int64_t(nb) * 292 || act_stride % 4 != 0 || ff_stride < r1) return FNB_REJECTED;
+    if (row_bytes != int64_t(nb) * shape<S>::kBlock || act_stride < int64_t(nb) * 292 || act_stride % 4 != 0 || ff_stride < r1) {
+        return FNB_REJECTED;
+    }
     const cudaStream_t s = static_cast<cudaStream_t>(stream);
     const uint8_t * gp = static_cast<const uint8_t *>(gate);
     const uint8_t * upp = static_cast<const uint8_t *>(up);
     const uint8_t * a = static_cast<const uint8_t *>(act);
-    const int max_t = window_rows(nb);
+    const int max_t = window_rows<S>(nb);
     if (max_t < 1) return FNB_REJECTED;
     // g and u of a later pass would need their own [2][m] planes: the debug output is for windows of one pass
     if (gu != nullptr && nt > max_t) return FNB_REJECTED;
@@ -358,16 +393,34 @@ extern "C" int32_t fnb_expert_gate_up_rows_iq3_xxs(const void * gate, const void
         float * ft = ff + int64_t(t0) * ff_stride;
         int32_t st;
         switch (m) {
-            case 1: st = launch_nt<1>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
-            case 2: st = launch_nt<2>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
-            case 3: st = launch_nt<3>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
-            case 4: st = launch_nt<4>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
-            case 5: st = launch_nt<5>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
-            case 6: st = launch_nt<6>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
-            case 7: st = launch_nt<7>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
-            default: st = launch_nt<8>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
+            case 1: st = launch_nt<1, S>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
+            case 2: st = launch_nt<2, S>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
+            case 3: st = launch_nt<3, S>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
+            case 4: st = launch_nt<4, S>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
+            case 5: st = launch_nt<5, S>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
+            case 6: st = launch_nt<6, S>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
+            case 7: st = launch_nt<7, S>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
+            default: st = launch_nt<8, S>(gp, upp, row_bytes, nb, at, act_stride, ft, ff_stride, gu, r0, r1, s); break;
         }
         if (st != FNB_OK) return st;
     }
     return FNB_OK;
+}
+
+}  // namespace
+
+bool expert_gate_up_prepare_device() { return prepare_fmt<false>() && prepare_fmt<true>(); }
+
+}  // namespace fnb
+
+extern "C" int32_t fnb_expert_gate_up_rows_iq3_xxs(const void * gate, const void * up, int64_t row_bytes, int32_t n,
+                                                   const void * act, int64_t act_stride, int32_t nt, float * ff,
+                                                   int64_t ff_stride, float * gu, int64_t r0, int64_t r1, void * stream) {
+    return fnb::gate_up_rows<false>(gate, up, row_bytes, n, act, act_stride, nt, ff, ff_stride, gu, r0, r1, stream);
+}
+
+extern "C" int32_t fnb_expert_gate_up_rows_iq3_s(const void * gate, const void * up, int64_t row_bytes, int32_t n,
+                                                 const void * act, int64_t act_stride, int32_t nt, float * ff,
+                                                 int64_t ff_stride, float * gu, int64_t r0, int64_t r1, void * stream) {
+    return fnb::gate_up_rows<true>(gate, up, row_bytes, n, act, act_stride, nt, ff, ff_stride, gu, r0, r1, stream);
 }

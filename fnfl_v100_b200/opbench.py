@@ -22,6 +22,7 @@ OPS = ("get_rows_q4_k", "get_rows_iq3_xxs", "rms_norm", "rms_norm_heads", "rope_
        "expert_down_iq4_nl_nt1", "expert_down_iq4_nl_nt3", "expert_down_iq4_nl_nt8",
        "expert_gate_up_q4_k_nt1", "expert_gate_up_q4_k_nt3", "expert_gate_up_q4_k_nt8",
        "expert_gate_up_q5_k_nt1", "expert_gate_up_q5_k_nt3", "expert_gate_up_q5_k_nt8",
+       "expert_gate_up_iq3_s_nt1", "expert_gate_up_iq3_s_nt3", "expert_gate_up_iq3_s_nt8",
        "expert_gate_up_iq3_xxs_nt1", "expert_gate_up_iq3_xxs_nt3", "expert_gate_up_iq3_xxs_nt8")
 
 
@@ -100,6 +101,13 @@ def make_case(op: str, T: int, dev, gen, c: ChainConfig):
         act = ops.quantize_q8_k(N(gen, (nt, n), 1.0, dev))
         out = torch.empty((nt, rows), dtype=torch.float32, device=dev)
         return (lambda: ops.expert_gate_up_rows_q5_k(gate, up, act, n, out=out)), rows * (2 * n // 256 * 176 + nt * 4) + nt * n // 256 * 292
+    if op.startswith("expert_gate_up_iq3_s"):
+        nt, n, rows = int(op.rsplit("nt", 1)[1]), 2560, 2 * T
+        gate = synth.torch_table("iq3_s", gen, rows, n, dev, 2e-5, 3e-4)
+        up = synth.torch_table("iq3_s", gen, rows, n, dev, 2e-5, 3e-4)
+        act = ops.quantize_q8_k(N(gen, (nt, n), 1.0, dev))
+        out = torch.empty((nt, rows), dtype=torch.float32, device=dev)
+        return (lambda: ops.expert_gate_up_rows("iq3_s", gate, up, act, n, out=out)), rows * (2 * n // 256 * 110 + nt * 4) + nt * n // 256 * 292
     if op.startswith("expert_gate_up_iq3_xxs"):
         nt, n, rows = int(op.rsplit("nt", 1)[1]), 2560, 2 * T
         gate = synth.torch_table("iq3_xxs", gen, rows, n, dev, 5e-5, 4e-4)

@@ -46,6 +46,15 @@ def iq3_xxs_table(g: np.random.Generator, n_rows: int, cols: int, d_lo: float = 
     return t.reshape(n_rows, nsb * 98)
 
 
+def iq3_s_table(g: np.random.Generator, n_rows: int, cols: int, d_lo: float = 1e-3, d_hi: float = 1e-2) -> np.ndarray:
+    """uint8 [n_rows][cols/256*110]: uniform indices, high bits, sign bits and 4-bit scales, fp16 d ~ U(d_lo, d_hi)."""
+    nsb = cols // 256
+    t = g.integers(0, 256, size=(n_rows, nsb, 110), dtype=np.uint8)
+    d = _f16_bits(g.uniform(d_lo, d_hi, size=(n_rows, nsb, 1)))
+    t[:, :, 0:2] = d.view(np.uint8).reshape(n_rows, nsb, 2)
+    return t.reshape(n_rows, nsb * 110)
+
+
 def q8_0_table(g: np.random.Generator, n_rows: int, cols: int) -> np.ndarray:
     nb = cols // 32
     t = g.integers(0, 256, size=(n_rows, nb, 34), dtype=np.uint8)

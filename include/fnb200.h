@@ -330,6 +330,15 @@ int32_t fnb_expert_gate_up_rows_iq3_xxs(const void * gate, const void * up, int6
                                         int64_t r1, void * stream);
 
 /*
+ * And with ggml IQ3_S weights (110-byte super-blocks: row_bytes = n / 256 * 110): fn::experts::cpu::iq_gu_rows for fmt
+ * iq3_s (cpu_iq_avx2.cpp:273-290 through the same row kernel), same bits - 9-bit codebook indices, plain sign bits, one
+ * 4-bit scale per 32 values, K = 1.  Arguments and limits as fnb_expert_gate_up_rows_iq3_xxs.
+ */
+int32_t fnb_expert_gate_up_rows_iq3_s(const void * gate, const void * up, int64_t row_bytes, int32_t n, const void * act,
+                                      int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, float * gu, int64_t r0,
+                                      int64_t r1, void * stream);
+
+/*
  * The consumer of the Q8_1 blocks fnb_swiglu_q8_1 writes: the routed experts' down mat-vec for a decode window,
  * out[t * out_stride + r] = weight row r . act[t] for t < nt and r in [r0, r1).  Weights are ggml Q5_1 rows (n / 32
  * blocks of 24 bytes: fp16 d, fp16 m, 32 high bits, 16 nibble bytes; value = d q + m), rows back to back

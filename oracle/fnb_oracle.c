@@ -721,3 +721,57 @@ void fnbo_expert_gu_rows_iq3_xxs(const uint8_t * gate, const uint8_t * up, int64
         }
     }
 }
+
+/* ---- and with IQ3_S weights (cpu_iq_avx2.cpp:273-290 fmt32<21>::decode through the same row_dot): 9-bit codebook
+ * indices (qs byte | qh bit), sign bit i of a group's four sign bytes for value i, one 4-bit scale per 32 values
+ * (2 s + 1), K = 1: x.d y.d per super-block, ggml's hsum_float_8 order. */
+static float fnbo_iq3s_dot(const uint8_t * row, int nb, const uint8_t * act) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int i = 0; i < nb; ++i) {
+        const uint8_t * x = row + 110 * i;
+        const uint8_t * y = act + 292 * i;
+        uint16_t dh;
+        memcpy(&dh, x, 2);
+        float yd;
+        memcpy(&yd, y, 4);
+        const int8_t * q8 = (const int8_t *) (y + 4);
+        int32_t acci[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int g = 0; g < 8; ++g) {
+            uint32_t signs;
+            memcpy(&signs, x + 74 + 4 * g, 4);
+            const unsigned s = x[106 + g / 2];
+            const int32_t sc = 2 * (int32_t) ((g & 1) ? s >> 4 : s & 15u) + 1;
+            for (int l = 0; l < 8; ++l) {
+                const unsigned code = o_grid3s_packed[x[2 + 8 * g + l] | (((x[66 + g] >> l) & 1u) << 8)];
+                int32_t sum = 0;
+                for (int b = 0; b < 4; ++b) {
+                    const int32_t mag = 2 * (int32_t) ((code >> (3 * b)) & 7u) + 1;
+                    const int8_t yv = q8[32 * g + 4 * l + b];
+                    const int8_t ys = (signs >> (4 * l + b)) & 1u ? (int8_t) (0u - (unsigned) yv) : yv;
+                    sum += mag * (int32_t) ys;
+                }
+                acci[l] += sc * sum;
+            }
+        }
+        const float dxy = fnbo_f16_to_f32(dh) * yd;
+        for (int l = 0; l < 8; ++l) acc[l] = fmaf(dxy, (float) acci[l], acc[l]);
+    }
+    return 1.0f * fnbo_hsum8(acc);
+}
+
+void fnbo_expert_gu_rows_iq3_s(const uint8_t * gate, const uint8_t * up, int64_t row_bytes, int32_t n, const uint8_t * act,
+                               int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, float * gu, int64_t r0,
+                               int64_t r1) {
+    const int nb = n / 256;
+    for (int64_t r = r0; r < r1; ++r) {
+        for (int t = 0; t < nt; ++t) {
+            const float g = fnbo_iq3s_dot(gate + r * row_bytes, nb, act + (int64_t) t * act_stride);
+            const float u = fnbo_iq3s_dot(up + r * row_bytes, nb, act + (int64_t) t * act_stride);
+            ff[(int64_t) t * ff_stride + r] = (g / (1.0f + o_expf(-g))) * u;
+            if (gu != NULL) {
+                gu[(int64_t) t * ff_stride + r] = g;
+                gu[((int64_t) nt + t) * ff_stride + r] = u;
+            }
+        }
+    }
+}

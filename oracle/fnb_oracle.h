@@ -111,6 +111,12 @@ void fnbo_expert_gu_rows_iq3_xxs(const uint8_t * gate, const uint8_t * up, int64
                                  int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, float * gu, int64_t r0,
                                  int64_t r1);
 
+/* And with ggml IQ3_S weights (110-byte super-blocks; cpu_iq_avx2.cpp:273-290 through the same row kernel): 9-bit
+ * codebook indices, plain sign bits, one 4-bit scale per 32 values, K = 1. */
+void fnbo_expert_gu_rows_iq3_s(const uint8_t * gate, const uint8_t * up, int64_t row_bytes, int32_t n, const uint8_t * act,
+                               int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, float * gu, int64_t r0,
+                               int64_t r1);
+
 /* The consumer of the 8-bit activations: the routed experts' down mat-vec, out[t][r] = weight row r . act[t], with
  * ggml's Q5_1 weights against Q8_1 activations (fmt 0) or Q8_0 weights against Q8_0 activations (fmt 1).  Follows the
  * reference's CPU kernels lane for lane (fn/kernels/experts/cpu_kq_avx2.cpp:293-344, :382-394): eight F32 accumulators

@@ -268,11 +268,12 @@ def kv8_dequantize(codes: np.ndarray, scales: np.ndarray) -> np.ndarray:
 def expert_gu_rows(fmt: str, gate: np.ndarray, up: np.ndarray, act: np.ndarray, n: int, r0: int = 0, r1: int | None = None,
                    use_ref: bool = False, want_gu: bool = False):
     """ff[t][r] = silu(gate row r . act[t]) * (up row r . act[t]): weight rows uint8 [rows][n/256*block bytes] of
-    fmt "q4_k" (144), "q5_k" (176) or "iq3_xxs" (98) against Q8_K activations uint8 [nt][n/256*292].  use_ref: the reference's own
+    fmt "q4_k" (144), "q5_k" (176), "iq3_xxs" (98) or "iq3_s" (110) against Q8_K activations uint8 [nt][n/256*292].  use_ref: the reference's own
     AVX2 kernel (its libm's expf)."""
     ref_fn, own_fn = {"q4_k": ("ref_kq_gu_rows_q4_k", "fnbo_expert_gu_rows_q4_k"),
                       "q5_k": ("ref_kq_gu_rows_q5_k", "fnbo_expert_gu_rows_q5_k"),
-                      "iq3_xxs": ("ref_iq_gu_rows_iq3_xxs", "fnbo_expert_gu_rows_iq3_xxs")}[fmt]
+                      "iq3_xxs": ("ref_iq_gu_rows_iq3_xxs", "fnbo_expert_gu_rows_iq3_xxs"),
+                      "iq3_s": ("ref_iq_gu_rows_iq3_s", "fnbo_expert_gu_rows_iq3_s")}[fmt]
     gate, up, act = (np.ascontiguousarray(a, np.uint8) for a in (gate, up, act))
     rows, nt = gate.shape[0], act.shape[0]
     r1 = rows if r1 is None else r1

@@ -103,6 +103,15 @@ void ref_iq_gu_rows_iq3_xxs(const uint8_t * gate, const uint8_t * up, int64_t ro
     fn::experts::cpu::iq_gu_rows(fn::experts::fmt::iq3_xxs, gate, up, size_t(row_bytes), n, a, nt, o, r0, r1);
 }
 
+// and for IQ3_S weights
+void ref_iq_gu_rows_iq3_s(const uint8_t * gate, const uint8_t * up, int64_t row_bytes, int32_t n, const uint8_t * act,
+                          int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, int32_t r0, int32_t r1) {
+    const void * a[64];
+    float * o[64];
+    for (int t = 0; t < nt && t < 64; ++t) a[t] = act + int64_t(t) * act_stride, o[t] = ff + int64_t(t) * ff_stride;
+    fn::experts::cpu::iq_gu_rows(fn::experts::fmt::iq3_s, gate, up, size_t(row_bytes), n, a, nt, o, r0, r1);
+}
+
 // Q8_K activations: the reference's AVX2 form (fn/kernels/experts/cpu_iq_avx2.cpp:583-646); ggml's scalar form
 // quantize_row_q8_K_ref is exported by ggml-quants.c itself
 void ref_quantize_q8_k_avx2(const float * x, void * y, int64_t k) { fn::experts::cpu::quantize_q8_k(x, y, k); }

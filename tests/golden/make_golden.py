@@ -205,6 +205,26 @@ def gate_up_rows_iq3_xxs() -> None:
     print("gate_up_rows_iq3_xxs.npz", os.path.getsize(path), "bytes; |ff| max", float(np.abs(ff).max()))
 
 
+def gate_up_rows_iq3_s() -> None:
+    """The same for IQ3_S rows (fn::experts::cpu::iq_gu_rows, fmt iq3_s), also with -128 codes.  Same libm note."""
+    from fnfl_v100_b200 import synth
+    g = synth.rng(0x4953)
+    n, rows, nt = 2560, 45, 5
+    gate, up = synth.iq3_s_table(g, rows, n, 2e-5, 3e-4), synth.iq3_s_table(g, rows, n, 2e-5, 3e-4)
+    act = O.quantize_q8_k(synth.normal(g, (nt, n), 1.0), "ggml").reshape(nt, -1)
+    act_m128 = act.copy()
+    codes = act_m128.reshape(nt, -1, 292)[:, :, 4:260]
+    codes[g.integers(0, 10, size=codes.shape) == 0] = 0x80
+    ff = O.expert_gu_rows("iq3_s", gate, up, act, n, use_ref=True)
+    ff_m128 = O.expert_gu_rows("iq3_s", gate, up, act_m128, n, use_ref=True)
+    O.use_libm(False)
+    for a, f in ((act, ff), (act_m128, ff_m128)):
+        assert np.array_equal(f.view(np.uint32), O.expert_gu_rows("iq3_s", gate, up, a, n).view(np.uint32)), "libm is not the generic build"
+    path = os.path.join(HERE, "gate_up_rows_iq3_s.npz")
+    np.savez_compressed(path, gate=gate, up=up, act=act, ff=ff, act_m128=act_m128, ff_m128=ff_m128)
+    print("gate_up_rows_iq3_s.npz", os.path.getsize(path), "bytes; |ff| max", float(np.abs(ff).max()))
+
+
 def main() -> None:
     O.build(with_ref=True)
     model_file()
@@ -214,6 +234,7 @@ def main() -> None:
     gate_up_rows()
     gate_up_rows_q5_k()
     gate_up_rows_iq3_xxs()
+    gate_up_rows_iq3_s()
     r = O.ref()
     x = stress_blocks()
     n = x.shape[0]

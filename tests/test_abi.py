@@ -106,6 +106,11 @@ def test_rejections_enqueue_nothing(lib):
         a = list(ok3)
         a[i] = bad
         assert lib.fnb_expert_gate_up_rows_iq3_xxs(*a) == R, (i, bad)
+    ok3s = (A16, A16, 1100, 2560, A16, 2920, 3, A16, 640, None, 0, 640, None)
+    for i, bad in ((3, 2304), (2, 980), (6, 0), (11, 0), (0, ODD)):
+        a = list(ok3s)
+        a[i] = bad
+        assert lib.fnb_expert_gate_up_rows_iq3_s(*a) == R, (i, bad)
     dbg3 = list(ok3)
     dbg3[6], dbg3[9] = 9, A16
     assert lib.fnb_expert_gate_up_rows_iq3_xxs(*dbg3) == R

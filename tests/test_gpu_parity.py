@@ -421,7 +421,42 @@ def test_expert_gate_up_rows_iq3_xxs_bit_exact(dev, oracle, n, rows, nt, m128):
     assert np.abs(want[:, r0:r1]).max() < 1e3 and np.abs(wgu[0][:, r0:r1]).std() > 0.3   # gates of order one: the GLU is exercised
 
 
-@pytest.mark.parametrize("fmt", ["q4_k", "q5_k", "iq3_xxs"])
+def test_expert_gate_up_rows_iq3_s_equal_the_reference_avx2_kernel_on_golden(dev):
+    gold = np.load(os.path.join(GOLD, "gate_up_rows_iq3_s.npz"))
+    gate, up = to_dev(gold["gate"], dev), to_dev(gold["up"], dev)
+    for act, want in ((gold["act"], gold["ff"]), (gold["act_m128"], gold["ff_m128"])):
+        got = ops.expert_gate_up_rows("iq3_s", gate, up, to_dev(act, dev), 2560)
+        assert np.array_equal(bits(got.cpu().numpy()), bits(want))
+
+
+@pytest.mark.parametrize("n,rows,nt,m128", [(2560, 320, 1, False), (2560, 999, 3, True), (2048, 130, 8, False),
+                                            (512, 37, 2, True), (5632, 41, 13, False), (16384, 9, 7, False)])
+def test_expert_gate_up_rows_iq3_s_bit_exact(dev, oracle, n, rows, nt, m128):
+    """As the IQ3_XXS test, with IQ3_S rows (9-bit indices, plain sign bits, a scale per 32 values)."""
+    g = synth.rng(37)
+    act = ops.quantize_q8_k(to_dev(synth.normal(g, (nt, n), 1.0), dev))
+    if m128:
+        a = act.cpu().numpy().reshape(nt, -1, 292)
+        codes = a[:, :, 4:260]
+        codes[g.integers(0, 7, size=codes.shape) == 0] = 0x80
+        act = to_dev(a.reshape(nt, -1), dev)
+    d_hi = 3e-4 * (2560 / n) ** 0.5
+    gate, up = synth.iq3_s_table(g, rows, n, d_hi / 15, d_hi), synth.iq3_s_table(g, rows, n, d_hi / 15, d_hi)
+    r0, r1 = 2, rows - 1
+    out = torch.full((nt, rows), float("nan"), dtype=torch.float32, device=dev)
+    gu = torch.zeros((2, nt, rows), dtype=torch.float32, device=dev) if nt <= 8 else None
+    ops.expert_gate_up_rows("iq3_s", to_dev(gate, dev), to_dev(up, dev), act, n, r0=r0, r1=r1, out=out, gu=gu)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    want, wgu = oracle.expert_gu_rows("iq3_s", gate, up, act.cpu().numpy(), n, r0=r0, r1=r1, want_gu=True)
+    assert np.array_equal(bits(got[:, r0:r1]), bits(want[:, r0:r1]))
+    assert np.isnan(got[:, :r0]).all() and np.isnan(got[:, r1:]).all()
+    if gu is not None:
+        assert np.array_equal(bits(gu.cpu().numpy()[:, :, r0:r1]), bits(wgu[:, :, r0:r1]))
+    assert np.abs(wgu[0][:, r0:r1]).std() > 0.3
+
+
+@pytest.mark.parametrize("fmt", ["q4_k", "q5_k", "iq3_xxs", "iq3_s"])
 def test_expert_ffn_for_a_decode_window_stage_by_stage(dev, oracle, fmt):
     """One routed expert for a window of three rows, every hand-over on the device: RMSNorm -> Q8_K -> gate / up mat-vec
     with the GLU (Q4_K, Q5_K or IQ3_XXS) -> Q8_1 -> down mat-vec (Q5_1).  Each stage is checked bit for bit against the
@@ -430,7 +465,7 @@ def test_expert_ffn_for_a_decode_window_stage_by_stage(dev, oracle, fmt):
     nt, d_model, d_ff = 3, 2560, 640
     x, w = synth.normal(g, (nt, d_model), 1.0), synth.norm_weight(g, d_model)
     table, d_lo, d_hi = {"q4_k": (synth.q4_k_table, 1e-5, 3e-4), "q5_k": (synth.q5_k_table, 1e-5, 1.5e-4),
-                         "iq3_xxs": (synth.iq3_xxs_table, 5e-5, 4e-4)}[fmt]
+                         "iq3_xxs": (synth.iq3_xxs_table, 5e-5, 4e-4), "iq3_s": (synth.iq3_s_table, 2e-5, 3e-4)}[fmt]
     gate, up = table(g, d_ff, d_model, d_lo, d_hi), table(g, d_ff, d_model, d_lo, d_hi)
     down = synth.q5_1_rows(g, d_model, d_ff)
     D = lambda a: to_dev(a, dev)  # noqa: E731

@@ -174,6 +174,14 @@ def test_expert_gate_up_rows_iq3_xxs_match_the_reference_avx2_kernel(oracle):
     assert not np.array_equal(gold["ff"], gold["ff_m128"])
 
 
+def test_expert_gate_up_rows_iq3_s_match_the_reference_avx2_kernel(oracle):
+    """tests/golden/gate_up_rows_iq3_s.npz: ff of the reference's own iq_gu_rows (fmt iq3_s), also with -128 codes."""
+    gold = np.load(os.path.join(GOLD, "gate_up_rows_iq3_s.npz"))
+    for act, want in ((gold["act"], gold["ff"]), (gold["act_m128"], gold["ff_m128"])):
+        got = oracle.expert_gu_rows("iq3_s", gold["gate"], gold["up"], act, 2560)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
 def test_expert_gate_up_rows_match_the_reference_avx2_kernel(oracle):
     """tests/golden/gate_up_rows.npz: ff of the reference's own kq_gu_rows (fmt q4_k, GLU included); the scalar
     restatement reproduces every bit, also on a sub-range of rows."""
