@@ -1,7 +1,8 @@
 // The routed experts' gate / up mat-vec for a decode window with the GLU fused,
 //     ff[t][r] = silu(g) u,   g = gate row r . act[t],  u = up row r . act[t],   t < nt,  r in [r0, r1)
 // with ggml IQ3_XXS or IQ3_S weights against Q8_K activations (fnb_quantize_q8_k).  Replaces fn::experts::cpu::iq_gu_rows
-// for fmt iq3_xxs and iq3_s (IQ3_S: cpu_iq_avx2.cpp:273-290, described at `shape` below; IQ3_XXS: fn/kernels/experts/cpu_kernels.h:67; cpu_iq_avx2.cpp:256-271 decode, :305-337 row_dot, :429-445 gu_rows)
+// for fmt iq3_xxs and iq3_s (fn/kernels/experts/cpu_kernels.h:67; cpu_iq_avx2.cpp:256-271 and :273-290 decode, :305-337
+// row_dot, :429-445 gu_rows; IQ3_S's differences are listed at `shape` below, the text here describes IQ3_XXS)
 // and returns the SAME BITS: the AVX2 kernel keeps, per (row, t), eight int32 lanes a super-block - lane l collects,
 // over the block's eight groups of 32 values, (2 s + 1) x the four codebook bytes of the group's index byte l times the
 // sign-applied Q8_K codes 32 g + 4 l .. - adds them as floats by one fused multiply-add per super-block and lane with
