@@ -89,6 +89,8 @@ SIGNATURES = {
     "fnb_expert_gate_up_rows_iq3_xxs": (_I32, [_P, _P, _I64, _I32, _P, _I64, _I32, _P, _I64, _P, _I64, _I64, _P]),
     "fnb_expert_down_rows_q5_1": (_I32, [_P, _I64, _I32, _P, _I64, _I32, _P, _I64, _I64, _I64, _P]),
     "fnb_expert_down_rows_q8_0": (_I32, [_P, _I64, _I32, _P, _I64, _I32, _P, _I64, _I64, _I64, _P]),
+    "fnb_quantize_act_q": (_I32, [_P, _P, _P, _I64, _I32, _P]),
+    "fnb_expert_down_rows_q2_0": (_I32, [_P, _I64, _I32, _P, _I64, _P, _I64, _I32, _P, _I64, _I64, _I64, _P]),
     "fnb_expert_down_rows_iq4_nl": (_I32, [_P, _I64, _I32, _P, _I64, _I32, _P, _I64, _I64, _I64, _P]),
     "fnb_check_tokens": (_I64, [_P, _I64, _I64]),
     "fnb_prepare_device": (_I32, []),

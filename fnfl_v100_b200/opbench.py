@@ -19,6 +19,7 @@ from .chain import ChainConfig
 OPS = ("get_rows_q4_k", "get_rows_iq3_xxs", "rms_norm", "rms_norm_heads", "rope_kv", "swiglu_q8_1", "swiglu_act",
        "rope_kv8", "quantize_q8_1", "rms_norm_q8_1", "embed_iq3_s", "kv_read_q8_0", "kv_read_kv8",
        "expert_down_q5_1_nt1", "expert_down_q5_1_nt3", "expert_down_q5_1_nt8", "expert_down_q8_0_nt1", "expert_down_q8_0_nt3", "quantize_q8_k",
+       "expert_down_q2_0_nt1", "expert_down_q2_0_nt3", "expert_down_q2_0_nt8", "quantize_act_q",
        "expert_down_iq4_nl_nt1", "expert_down_iq4_nl_nt3", "expert_down_iq4_nl_nt8",
        "expert_gate_up_q4_k_nt1", "expert_gate_up_q4_k_nt3", "expert_gate_up_q4_k_nt8",
        "expert_gate_up_q5_k_nt1", "expert_gate_up_q5_k_nt3", "expert_gate_up_q5_k_nt8",
@@ -75,6 +76,17 @@ def make_case(op: str, T: int, dev, gen, c: ChainConfig):
         act = ops.quantize_q8_0(N(gen, (nt, n), 0.5, dev)).reshape(nt, -1)
         out = torch.empty((nt, rows), dtype=torch.float32, device=dev)
         return (lambda: ops.expert_down_rows("q8_0", w, act, n, out=out)), rows * (n // 32 * 34 + nt * 4) + nt * n // 32 * 34
+    if op == "quantize_act_q":
+        x = N(gen, (T, 640), 1.0, dev)
+        return (lambda: ops.quantize_act_q(x)), T * 640 * 4 + T * 640 + T * 20 * 4
+    if op.startswith("expert_down_q2_0"):
+        nt, n, rows = int(op.rsplit("nt", 1)[1]), 640, 32 * T
+        w = torch.randint(0, 256, (rows, n // 64, 18), dtype=torch.uint8, device=dev, generator=gen)
+        w.view(torch.float16).reshape(rows, n // 64, 9)[..., 0] = 0.01
+        w = w.reshape(rows, n // 64 * 18)
+        codes, scales = ops.quantize_act_q(N(gen, (nt, n), 0.5, dev))
+        out = torch.empty((nt, rows), dtype=torch.float32, device=dev)
+        return (lambda: ops.expert_down_rows_q2_0(w, codes, scales, n, out=out)), rows * (n // 64 * 18 + nt * 4) + nt * n * 9 // 8
     if op.startswith("expert_down_iq4_nl"):
         nt, n, rows = int(op.rsplit("nt", 1)[1]), 640, 16 * T
         w = torch.randint(0, 256, (rows, n // 32, 18), dtype=torch.uint8, device=dev, generator=gen)

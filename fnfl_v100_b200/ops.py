@@ -371,6 +371,35 @@ def expert_down_rows(fmt: str, w: torch.Tensor, act: torch.Tensor, n: int, r0: i
     return out
 
 
+def quantize_act_q(x: torch.Tensor):
+    """The reference's planar 32-value activation (fn::experts::cpu::quantize_act_q): (codes int8 [rows][n], chunk scales
+    F32 [rows][n/32]) of x F32 [rows][n]."""
+    _dev(x, torch.float32, "x")
+    rows, n = x.shape
+    codes = torch.empty((rows, n), dtype=torch.int8, device=x.device)
+    scales = torch.empty((rows, n // 32), dtype=torch.float32, device=x.device)
+    _check(_lib.lib().fnb_quantize_act_q(_ptr(x), _ptr(codes), _ptr(scales), rows, n, _stream()), "quantize_act_q")
+    return codes, scales
+
+
+def expert_down_rows_q2_0(w: torch.Tensor, codes: torch.Tensor, scales: torch.Tensor, n: int, r0: int = 0,
+                          r1: int | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t][r] = Q2_0 weight row r (uint8 [rows][n/64*18]) . planar activation row t (fn::experts::cpu::q2_down_rows,
+    bit for bit).  Returns F32 [nt][rows] (columns r0 .. r1 - 1 written)."""
+    _dev(w, torch.uint8, "w")
+    _dev(codes, torch.int8, "codes")
+    _dev(scales, torch.float32, "scales")
+    rows, nt = w.shape[0], codes.shape[0]
+    r1 = rows if r1 is None else r1
+    if out is None:
+        out = torch.zeros((nt, rows), dtype=torch.float32, device=w.device)
+    _dev(out, torch.float32, "out")
+    _check(_lib.lib().fnb_expert_down_rows_q2_0(_ptr(w), w.shape[1], n, _ptr(codes), codes.shape[1], _ptr(scales),
+                                                scales.shape[1], nt, _ptr(out), out.shape[1], r0, r1, _stream()),
+           "expert_down_rows_q2_0")
+    return out
+
+
 def expert_down_rows_q5_1(w, act, n, r0=0, r1=None, out=None):
     return expert_down_rows("q5_1", w, act, n, r0, r1, out)
 

@@ -84,6 +84,14 @@ def iq4_nl_rows(g: np.random.Generator, rows: int, n: int, d_lo: float = 1e-3, d
     return t.reshape(rows, nb * 18)
 
 
+def q2_0_rows(g: np.random.Generator, rows: int, n: int, d_lo: float = 1e-3, d_hi: float = 1e-2) -> np.ndarray:
+    """Random valid Q2_0 rows of the reference engine: uint8 [rows][n/64*18] (fp16 d ~ U(d_lo, d_hi), random 2-bit codes)."""
+    nb = n // 64
+    t = g.integers(0, 256, (rows, nb, 18)).astype(np.uint8)
+    t[:, :, 0:2] = g.uniform(d_lo, d_hi, (rows, nb)).astype(np.float16).view(np.uint8).reshape(rows, nb, 2)
+    return t.reshape(rows, nb * 18)
+
+
 def norm_weight(g: np.random.Generator, cols: int) -> np.ndarray:
     """1 + N(0, 0.1), the RMSNorm weight of the first configuration."""
     return (1.0 + 0.1 * g.standard_normal(cols)).astype(np.float32)

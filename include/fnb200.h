@@ -374,6 +374,27 @@ int32_t fnb_expert_down_rows_iq4_nl(const void * w, int64_t row_bytes, int32_t n
                                     int32_t nt, float * out, int64_t out_stride, int64_t r0, int64_t r1, void * stream);
 
 /*
+ * The reference engine's planar 32-value activation: per chunk of 32 values s = amax / 127 and codes
+ * trunc(x / s +- 0.5) in +-127 (half away from zero; inv = 1 / s is what multiplies).  codes int8 [rows][n], scales F32
+ * [rows][n / 32], both dense.  Replaces fn::experts::cpu::quantize_act_q (fn/kernels/experts/cpu_kernels.h:45-62;
+ * cpu_q2_avx2.cpp:180-226) for codes and scales, same bits on finite inputs.  n a multiple of 32; x, codes 16-byte aligned.
+ */
+int32_t fnb_quantize_act_q(const float * x, int8_t * codes, float * scales, int64_t rows, int32_t n, void * stream);
+
+/*
+ * The down mat-vec with the reference engine's Q2_0 weights (64-weight blocks of 18 bytes: fp16 d, 16 bytes of 2-bit
+ * codes, value 4 i + k at bits 2 k of byte i, weight d (c - 1); rows back to back, row_bytes = n / 64 * 18) against the
+ * planar activation fnb_quantize_act_q writes (row t's codes at codes + t codes_stride, its chunk scales at
+ * scales + t scales_stride): replaces fn::experts::cpu::q2_down_rows (cpu_kernels.h:78-81; cpu_q2_avx2.cpp:62-146),
+ * same bits - per pair of blocks eight lanes of sum(c q) - sum(q) in integers, times the chunk scale, one fused
+ * multiply-add by d, an output reduced as ((x0 + x1) + (x2 + x3)) + ((x4 + x5) + (x6 + x7)).  n a multiple of 128 up to
+ * 8192; codes 16-byte aligned, codes_stride a multiple of 16; other arguments as fnb_expert_down_rows_q5_1.
+ */
+int32_t fnb_expert_down_rows_q2_0(const void * w, int64_t row_bytes, int32_t n, const int8_t * codes, int64_t codes_stride,
+                                  const float * scales, int64_t scales_stride, int32_t nt, float * out, int64_t out_stride,
+                                  int64_t r0, int64_t r1, void * stream);
+
+/*
  * Host-side check before upload: 0 when every id is in [0, n_vocab), else 1 + the index of the first bad id.
  * Replaces fn::embed::check_tokens (fn/kernels/embed/embed.h:56).
  */

@@ -120,6 +120,15 @@ inline bool down_rows_iq4_nl(const uint8_t * w, int32_t n, const void * act, int
                              int64_t out_stride, int64_t r0, int64_t r1, void * stream) {
     return fnb_expert_down_rows_iq4_nl(w, int64_t(n / 32) * 18, n, act, act_stride, nt, out, out_stride, r0, r1, stream) == FNB_OK;
 }
+// Q2_0 weights against the planar activation (fn::experts::cpu::quantize_act_q, q2_down_rows; same bits)
+inline bool quantize_act_q(const float * x, int8_t * codes, float * scales, int64_t rows, int32_t n, void * stream) {
+    return fnb_quantize_act_q(x, codes, scales, rows, n, stream) == FNB_OK;
+}
+inline bool down_rows_q2_0(const uint8_t * w, int32_t n, const int8_t * codes, const float * scales, int32_t nt, float * out,
+                           int64_t out_stride, int64_t r0, int64_t r1, void * stream) {
+    return fnb_expert_down_rows_q2_0(w, int64_t(n / 64) * 18, n, codes, n, scales, n / 32, nt, out, out_stride, r0, r1, stream) ==
+           FNB_OK;
+}
 
 }  // namespace experts
 

@@ -544,6 +544,68 @@ void fnbo_quantize_row_q8_k(const float * x, void * vy, int64_t k) {
     }
 }
 
+/* ---- the reference's planar 32-value activation and its Q2_0 down rows (fn/kernels/experts/cpu_q2_avx2.cpp:180-226
+ * quantize_act_q, :62-96 row_bp, :98-102 reduce1).  Quantiser: s = amax / 127, inv = 1 / s (both 0 for an all-zero
+ * chunk), code = trunc(x inv +- 0.5) (half away from zero) clamped to +-127.  Q2_0: 64-weight blocks of 18 bytes (fp16
+ * d, 16 code bytes: value 4 i + k at bits 2 k of byte i, weight d (c - 1)), taken in pairs.  Per pair eight lanes: lane
+ * 4 h + m is block h's values 16 m .. 16 m + 15: sum(c q) - sum(q) exactly in integers, converted, TIMES the chunk
+ * scale (one multiply), then one fused multiply-add by d into the lane; an output is
+ * ((x0 + x1) + (x2 + x3)) + ((x4 + x5) + (x6 + x7)). ---- */
+void fnbo_quantize_act_q(const float * x, int64_t n, int8_t * q, float * scale) {
+    for (int64_t k = 0; k < n / 32; ++k) {
+        const float * xb = x + 32 * k;
+        float amax = 0.0f;
+        for (int j = 0; j < 32; ++j) {
+            const float a = fabsf(xb[j]);
+            if (a > amax) amax = a;
+        }
+        const float s = amax > 0.f ? amax / 127.f : 0.f;
+        const float inv = s > 0.f ? 1.f / s : 0.f;
+        for (int j = 0; j < 32; ++j) {
+            const float t = xb[j] * inv;
+            const float r = t + (t >= 0.f ? 0.5f : -0.5f);
+            int32_t v = (r > -2147483648.0f && r < 2147483648.0f) ? (int32_t) r : INT32_MIN; /* cvttps */
+            v = v < -127 ? -127 : v > 127 ? 127 : v;
+            q[32 * k + j] = (int8_t) v;
+        }
+        scale[k] = s;
+    }
+}
+
+void fnbo_expert_down_rows_q2_0(const uint8_t * w, int64_t row_bytes, int32_t n, const int8_t * q, int64_t q_stride,
+                                const float * scale, int64_t scale_stride, int32_t nt, float * out, int64_t out_stride,
+                                int64_t r0, int64_t r1) {
+    const int npairs = n / 128;
+    for (int64_t r = r0; r < r1; ++r) {
+        const uint8_t * row = w + r * row_bytes;
+        for (int t = 0; t < nt; ++t) {
+            const int8_t * qt = q + (int64_t) t * q_stride;
+            const float * st = scale + (int64_t) t * scale_stride;
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int p = 0; p < npairs; ++p) {
+                for (int h = 0; h < 2; ++h) {
+                    const uint8_t * blk = row + 36 * p + 18 * h;
+                    uint16_t dh;
+                    memcpy(&dh, blk, 2);
+                    const float d = fnbo_f16_to_f32(dh);
+                    for (int m = 0; m < 4; ++m) {
+                        int32_t dot = 0, sum = 0;
+                        for (int v = 0; v < 16; ++v) {
+                            const int idx = 16 * m + v; /* value idx of the block: byte idx / 4, bits 2 (idx % 4) */
+                            const int c = (blk[2 + idx / 4] >> (2 * (idx % 4))) & 3;
+                            const int qv = qt[128 * p + 64 * h + idx];
+                            dot += c * qv, sum += qv;
+                        }
+                        const float val = (float) (dot - sum) * st[4 * p + 2 * h + m / 2];
+                        acc[4 * h + m] = fmaf(d, val, acc[4 * h + m]);
+                    }
+                }
+            }
+            out[(int64_t) t * out_stride + r] = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
+        }
+    }
+}
+
 /* ---- the routed experts' gate / up rows over Q8_K (fn/kernels/experts/cpu_kq_avx2.cpp:166-224, :362-380) ------------*/
 static float fnbo_q4k_dot(const uint8_t * row, int nb, const uint8_t * act) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};

@@ -128,6 +128,14 @@ void fnbo_expert_gu_rows_iq3_s(const uint8_t * gate, const uint8_t * up, int64_t
 void fnbo_expert_down_rows(int32_t fmt, const uint8_t * w, int64_t row_bytes, int32_t n, const uint8_t * act,
                            int64_t act_stride, int32_t nt, float * out, int64_t out_stride, int64_t r0, int64_t r1);
 
+/* The reference's planar 32-value activation (fn/kernels/experts/cpu_q2_avx2.cpp:180-226): per chunk of 32 values
+ * s = amax / 127, codes trunc(x / s +- 0.5) in +-127 (half away from zero), and the down mat-vec of its Q2_0 weights
+ * (64-weight blocks of 18 bytes, weight d (c - 1); :62-102): out[t][r] for r in [r0, r1), n a multiple of 128. */
+void fnbo_quantize_act_q(const float * x, int64_t n, int8_t * q, float * scale);
+void fnbo_expert_down_rows_q2_0(const uint8_t * w, int64_t row_bytes, int32_t n, const int8_t * q, int64_t q_stride,
+                                const float * scale, int64_t scale_stride, int32_t nt, float * out, int64_t out_stride,
+                                int64_t r0, int64_t r1);
+
 #ifdef __cplusplus
 }
 #endif

@@ -317,6 +317,41 @@ def quantize_q8_k(x: np.ndarray, which: str = "oracle") -> np.ndarray:
 DOWN_FMT = {"q5_1": (0, 24, Q8_1_BYTES), "q8_0": (1, Q8_0_BYTES, Q8_0_BYTES), "iq4_nl": (2, 18, Q8_0_BYTES)}   # code, weight block, activation block
 
 
+def quantize_act_q(x: np.ndarray, use_ref: bool = False):
+    """The reference's planar 32-value activation: (codes int8 [rows][n], chunk scales f32 [rows][n/32]) of x [rows][n].
+    use_ref: the reference's own AVX2 quantiser (n <= 640, a multiple of 128)."""
+    x = _f32(x)
+    rows, n = x.shape
+    q, s = np.zeros((rows, n), np.int8), np.zeros((rows, n // 32), np.float32)
+    for r in range(rows):
+        if use_ref:
+            ref().ref_quantize_act_q(_p(x[r]), C.c_int32(n), _p(q[r]), _p(s[r]))
+        else:
+            lib().fnbo_quantize_act_q(_p(x[r]), C.c_int64(n), _p(q[r]), _p(s[r]))
+    return q, s
+
+
+def expert_down_rows_q2_0(w: np.ndarray, n: int, q: np.ndarray = None, scale: np.ndarray = None, r0: int = 0,
+                          r1: int | None = None, x: np.ndarray = None) -> np.ndarray:
+    """out[t][r] = Q2_0 weight row r (uint8 [rows][n/64*18]) . planar activation row t (codes q, chunk scales scale).
+    With x (F32 [nt][n], nt <= 8, n <= 640) instead: the reference's own quantiser and AVX2 rows."""
+    w = np.ascontiguousarray(w, np.uint8)
+    rows = w.shape[0]
+    r1 = rows if r1 is None else r1
+    if x is not None:
+        x = _f32(x)
+        out = np.zeros((x.shape[0], rows), np.float32)
+        ref().ref_q2_down_rows(_p(w), C.c_int64(w.shape[1]), C.c_int32(n), _p(x), C.c_int32(x.shape[0]), _p(out),
+                               C.c_int64(rows), C.c_int32(r0), C.c_int32(r1))
+        return out
+    q, scale = np.ascontiguousarray(q, np.int8), _f32(scale)
+    out = np.zeros((q.shape[0], rows), np.float32)
+    lib().fnbo_expert_down_rows_q2_0(_p(w), C.c_int64(w.shape[1]), C.c_int32(n), _p(q), C.c_int64(q.shape[1]), _p(scale),
+                                     C.c_int64(scale.shape[1]), C.c_int32(q.shape[0]), _p(out), C.c_int64(rows),
+                                     C.c_int64(r0), C.c_int64(r1))
+    return out
+
+
 def expert_down_rows(fmt: str, w: np.ndarray, act: np.ndarray, n: int, r0: int = 0, r1: int | None = None,
                      use_ref: bool = False) -> np.ndarray:
     """out[t][r] = weight row r . act[t]: w uint8 [rows][n/32 * weight block], act uint8 [nt][n/32 * activation block]

@@ -112,6 +112,27 @@ void ref_iq_gu_rows_iq3_s(const uint8_t * gate, const uint8_t * up, int64_t row_
     fn::experts::cpu::iq_gu_rows(fn::experts::fmt::iq3_s, gate, up, size_t(row_bytes), n, a, nt, o, r0, r1);
 }
 
+// the planar 32-value activation (fn/kernels/experts/cpu_q2_avx2.cpp:180-226): codes and chunk scales of n <= 640 values
+void ref_quantize_act_q(const float * x, int32_t n, int8_t * q, float * scale) {
+    fn::experts::cpu::act_q a;
+    fn::experts::cpu::quantize_act_q(x, n, a);
+    for (int i = 0; i < n; ++i) q[i] = a.q[i];
+    for (int i = 0; i < n / 32; ++i) scale[i] = a.scale[i];
+}
+
+// Q2_0 down rows (:150-178) of nt <= 8 activation rows given as floats (quantised by the reference's own quantiser)
+void ref_q2_down_rows(const uint8_t * w, int64_t row_bytes, int32_t n, const float * x, int32_t nt, float * out,
+                      int64_t out_stride, int32_t r0, int32_t r1) {
+    static fn::experts::cpu::act_q acts[8];
+    const fn::experts::cpu::act_q * a[8];
+    float * o[8];
+    for (int t = 0; t < nt && t < 8; ++t) {
+        fn::experts::cpu::quantize_act_q(x + int64_t(t) * n, n, acts[t]);
+        a[t] = &acts[t], o[t] = out + int64_t(t) * out_stride;
+    }
+    fn::experts::cpu::q2_down_rows(w, size_t(row_bytes), n / 64, a, nt, o, r0, r1);
+}
+
 // Q8_K activations: the reference's AVX2 form (fn/kernels/experts/cpu_iq_avx2.cpp:583-646); ggml's scalar form
 // quantize_row_q8_K_ref is exported by ggml-quants.c itself
 void ref_quantize_q8_k_avx2(const float * x, void * y, int64_t k) { fn::experts::cpu::quantize_q8_k(x, y, k); }

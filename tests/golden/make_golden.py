@@ -127,6 +127,23 @@ def down_rows_iq4_nl() -> None:
     print("down_rows_iq4_nl.npz", os.path.getsize(os.path.join(HERE, "down_rows_iq4_nl.npz")), "bytes")
 
 
+def down_rows_q2_0() -> None:
+    """The reference's own planar activation quantiser and Q2_0 down rows (fn::experts::cpu::quantize_act_q,
+    q2_down_rows) on seeded inputs: an all-zero chunk, a large outlier and exact half steps among them."""
+    from fnfl_v100_b200 import synth
+    g = synth.rng(0x5132)
+    n, rows, nt = 640, 67, 5
+    x = synth.normal(g, (nt, n), 2.0)
+    x[0, :32] = 0.0
+    x[1, 7] = 1e3
+    x[2, 64:96] = np.arange(32, dtype=np.float32) * 0.5 - 8.0   # amax 8: x / s = 127 x / 8 lands on .5 steps
+    w = synth.q2_0_rows(g, rows, n)
+    q, s = O.quantize_act_q(x, use_ref=True)
+    out = O.expert_down_rows_q2_0(w, n, x=x)
+    np.savez_compressed(os.path.join(HERE, "down_rows_q2_0.npz"), x=x, w=w, codes=q, scales=s, out=out)
+    print("down_rows_q2_0.npz", os.path.getsize(os.path.join(HERE, "down_rows_q2_0.npz")), "bytes")
+
+
 def q8_k() -> None:
     """ggml's quantize_row_q8_K_ref and the reference's AVX2 quantize_q8_k on stress blocks (ties between +a and -a in
     both orders, zeros, tiny and huge magnitudes, constant blocks, half steps) and random ones; the two must agree."""
@@ -230,6 +247,7 @@ def main() -> None:
     model_file()
     down_rows()
     down_rows_iq4_nl()
+    down_rows_q2_0()
     q8_k()
     gate_up_rows()
     gate_up_rows_q5_k()

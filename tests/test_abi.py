@@ -100,6 +100,14 @@ def test_rejections_enqueue_nothing(lib):
         a = list(ok4)
         a[i] = bad
         assert lib.fnb_expert_down_rows_iq4_nl(*a) == R, (i, bad)
+    # Q2_0 down rows: n not whole pairs of 64-weight blocks, rows not back to back, codes rows off 16 bytes, no scales
+    okq = (A16, 180, 640, A16, 640, A16, 20, 3, A16, 2560, 0, 2560, None)
+    for i, bad in ((2, 576), (1, 184), (4, 648), (4, 624), (6, 19), (5, None), (7, 0), (11, 0), (9, 100)):
+        a = list(okq)
+        a[i] = bad
+        assert lib.fnb_expert_down_rows_q2_0(*a) == R, (i, bad)
+    assert lib.fnb_quantize_act_q(A16, A16, A16, 4, 48, None) == R
+    assert lib.fnb_quantize_act_q(A16, ODD, A16, 4, 64, None) == R
     # the IQ3_XXS form: an odd number of super-blocks a row (rows off 4-byte boundaries), rows not back to back
     ok3 = (A16, A16, 980, 2560, A16, 2920, 3, A16, 640, None, 0, 640, None)
     for i, bad in ((3, 2304), (2, 984), (6, 0), (6, 65), (11, 0), (8, 100), (0, ODD), (4, None), (5, 2916)):

@@ -561,6 +561,46 @@ def test_expert_down_rows_iq4_nl_bit_exact(dev, oracle, n, rows, nt, raw):
     assert np.isnan(got[:, :r0]).all() and np.isnan(got[:, r1:]).all()
 
 
+def test_planar_activation_and_q2_0_down_rows_equal_the_reference_on_golden(dev):
+    gold = np.load(os.path.join(GOLD, "down_rows_q2_0.npz"))
+    codes, scales = ops.quantize_act_q(to_dev(gold["x"], dev))
+    assert np.array_equal(codes.cpu().numpy(), gold["codes"]) and np.array_equal(bits(scales.cpu().numpy()), bits(gold["scales"]))
+    got = ops.expert_down_rows_q2_0(to_dev(gold["w"], dev), codes, scales, 640).cpu().numpy()
+    assert np.array_equal(bits(got), bits(gold["out"]))
+
+
+@pytest.mark.parametrize("n,rows,nt", [(640, 2560, 1), (640, 777, 5), (128, 40, 2), (2048, 129, 11), (384, 1001, 3),
+                                       (8192, 21, 8)])
+def test_q2_0_down_rows_bit_exact(dev, oracle, n, rows, nt):
+    """Planar activation on the device (codes and scales equal the oracle's), Q2_0 rows against it; rows outside
+    [r0, r1) stay untouched."""
+    g = synth.rng(38)
+    x = synth.normal(g, (nt, n), 2.0)
+    x[0, :32] = 0.0
+    codes, scales = ops.quantize_act_q(to_dev(x, dev))
+    wq, ws = oracle.quantize_act_q(x)
+    assert np.array_equal(codes.cpu().numpy(), wq) and np.array_equal(bits(scales.cpu().numpy()), bits(ws))
+    w = synth.q2_0_rows(g, rows, n)
+    r0, r1 = 3, rows - 2
+    out = torch.full((nt, rows), float("nan"), dtype=torch.float32, device=dev)
+    ops.expert_down_rows_q2_0(to_dev(w, dev), codes, scales, n, r0=r0, r1=r1, out=out)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    want = oracle.expert_down_rows_q2_0(w, n, wq, ws, r0=r0, r1=r1)
+    assert np.array_equal(bits(got[:, r0:r1]), bits(want[:, r0:r1]))
+    assert np.isnan(got[:, :r0]).all() and np.isnan(got[:, r1:]).all()
+
+
+def test_quantize_act_q_ragged_grid(dev, oracle):
+    """Row counts whose last warp is partly past the end."""
+    g = synth.rng(39)
+    for rows, n in ((1, 32), (3, 96), (7, 160), (1001, 64)):
+        x = synth.normal(g, (rows, n), 1.0)
+        codes, scales = ops.quantize_act_q(to_dev(x, dev))
+        wq, ws = oracle.quantize_act_q(x)
+        assert np.array_equal(codes.cpu().numpy(), wq) and np.array_equal(bits(scales.cpu().numpy()), bits(ws)), (rows, n)
+
+
 def test_expert_ffn_in_the_iq_formats_stage_by_stage(dev, oracle):
     """The IQ-format expert for a window of three rows, every hand-over on the device: RMSNorm -> Q8_K -> IQ3_XXS gate / up
     with the GLU -> Q8_0 -> IQ4_NL down; each stage bit for bit against the oracle on the previous stage's device output."""

@@ -148,6 +148,18 @@ def test_expert_down_rows_iq4_nl_match_the_reference_avx2_kernel(oracle):
         assert np.array_equal(got.view(np.uint32), gold[key + "|out"].view(np.uint32)), key
 
 
+def test_planar_activation_and_q2_0_down_rows_match_the_reference(oracle):
+    """tests/golden/down_rows_q2_0.npz: codes and scales of the reference's quantize_act_q and outputs of its
+    q2_down_rows; the restatements reproduce every bit, also on a sub-range of rows."""
+    gold = np.load(os.path.join(GOLD, "down_rows_q2_0.npz"))
+    q, s = oracle.quantize_act_q(gold["x"])
+    assert np.array_equal(q, gold["codes"]) and np.array_equal(s.view(np.uint32), gold["scales"].view(np.uint32))
+    out = oracle.expert_down_rows_q2_0(gold["w"], 640, q, s)
+    assert np.array_equal(out.view(np.uint32), gold["out"].view(np.uint32))
+    part = oracle.expert_down_rows_q2_0(gold["w"], 640, q, s, r0=3, r1=8)
+    assert np.array_equal(part[:, 3:8].view(np.uint32), gold["out"][:, 3:8].view(np.uint32)) and not part[:, :3].any()
+
+
 def test_q8_k_matches_ggml_and_the_reference_avx2_form(oracle):
     """tests/golden/q8_k.npz: blocks from ggml's quantize_row_q8_K_ref, equal to the reference's AVX2 quantize_q8_k."""
     gold = np.load(os.path.join(GOLD, "q8_k.npz"))
