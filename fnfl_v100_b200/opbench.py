@@ -78,7 +78,8 @@ def make_case(op: str, T: int, dev, gen, c: ChainConfig):
         return (lambda: ops.expert_down_rows("q8_0", w, act, n, out=out)), rows * (n // 32 * 34 + nt * 4) + nt * n // 32 * 34
     if op == "quantize_act_q":
         x = N(gen, (T, 640), 1.0, dev)
-        return (lambda: ops.quantize_act_q(x)), T * 640 * 4 + T * 640 + T * 20 * 4
+        codes, scales = ops.quantize_act_q(x)
+        return (lambda: ops.quantize_act_q(x, codes, scales)), T * 640 * 4 + T * 640 + T * 20 * 4
     if op.startswith("expert_down_q2_0"):
         nt, n, rows = int(op.rsplit("nt", 1)[1]), 640, 32 * T
         w = torch.randint(0, 256, (rows, n // 64, 18), dtype=torch.uint8, device=dev, generator=gen)

@@ -371,13 +371,17 @@ def expert_down_rows(fmt: str, w: torch.Tensor, act: torch.Tensor, n: int, r0: i
     return out
 
 
-def quantize_act_q(x: torch.Tensor):
+def quantize_act_q(x: torch.Tensor, codes: torch.Tensor | None = None, scales: torch.Tensor | None = None):
     """The reference's planar 32-value activation (fn::experts::cpu::quantize_act_q): (codes int8 [rows][n], chunk scales
     F32 [rows][n/32]) of x F32 [rows][n]."""
     _dev(x, torch.float32, "x")
     rows, n = x.shape
-    codes = torch.empty((rows, n), dtype=torch.int8, device=x.device)
-    scales = torch.empty((rows, n // 32), dtype=torch.float32, device=x.device)
+    if codes is None:
+        codes = torch.empty((rows, n), dtype=torch.int8, device=x.device)
+    if scales is None:
+        scales = torch.empty((rows, n // 32), dtype=torch.float32, device=x.device)
+    _dev(codes, torch.int8, "codes")
+    _dev(scales, torch.float32, "scales")
     _check(_lib.lib().fnb_quantize_act_q(_ptr(x), _ptr(codes), _ptr(scales), rows, n, _stream()), "quantize_act_q")
     return codes, scales
 
