@@ -745,6 +745,18 @@ def test_first_calls_can_be_captured_after_prepare_device(dev, oracle):
         x, w = synth.normal(g, (9, 2048)), synth.norm_weight(g, 2048)
         dg, du, dx, dw = (torch.from_numpy(a).to(dev) for a in (gate, up, x, w))
         out = torch.empty((64, 16 * 36), dtype=torch.uint8, device=dev)
+        # the experts' kernels that raise their shared-memory limit: IQ3_XXS gate / up, IQ4_NL and Q2_0 down
+        n, ff_rows = 2560, 24
+        wg, wu = synth.iq3_xxs_table(g, ff_rows, n, 5e-5, 4e-4), synth.iq3_xxs_table(g, ff_rows, n, 5e-5, 4e-4)
+        q8k = O.quantize_q8_k(synth.normal(g, (2, n), 1.0)).reshape(2, -1)
+        w4, a80 = synth.iq4_nl_rows(g, 40, 640), O.quantize_q8_0(synth.normal(g, (2, 640), 2.0)).reshape(2, -1)
+        w2 = synth.q2_0_rows(g, 40, 640)
+        qc, qs = O.quantize_act_q(synth.normal(g, (2, 640), 2.0))
+        D = lambda a: torch.from_numpy(a).to(dev)
+        dwg, dwu, dq8k, dw4, da80, dw2, dqc, dqs = (D(a) for a in (wg, wu, q8k, w4, a80, w2, qc, qs))
+        ff = torch.zeros((2, ff_rows), dtype=torch.float32, device=dev)
+        o4 = torch.zeros((2, 40), dtype=torch.float32, device=dev)
+        o2 = torch.zeros((2, 40), dtype=torch.float32, device=dev)
         ops.prepare_device()
         torch.cuda.synchronize()
         s = torch.cuda.Stream(dev)
@@ -753,8 +765,15 @@ def test_first_calls_can_be_captured_after_prepare_device(dev, oracle):
             with torch.cuda.graph(graph, stream=s):
                 ops.swiglu_q8_1(dg, du, out=out)          # first call of this kernel in the process
                 blocks = ops.rms_norm_quant(dx, dw, 1e-6, "q8_1")
+                ops.expert_gate_up_rows("iq3_xxs", dwg, dwu, dq8k, n, out=ff)
+                ops.expert_down_rows("iq4_nl", dw4, da80, 640, out=o4)
+                ops.expert_down_rows_q2_0(dw2, dqc, dqs, 640, out=o2)
         graph.replay()
         torch.cuda.synchronize()
+        bits = lambda a: np.ascontiguousarray(a).view(np.uint32)
+        assert np.array_equal(bits(ff.cpu().numpy()), bits(O.expert_gu_rows("iq3_xxs", wg, wu, q8k, n)))
+        assert np.array_equal(bits(o4.cpu().numpy()), bits(O.expert_down_rows("iq4_nl", w4, a80, 640)))
+        assert np.array_equal(bits(o2.cpu().numpy()), bits(O.expert_down_rows_q2_0(w2, 640, qc, qs)))
         want = O.swiglu_q8_1(gate, up)
         assert np.array_equal(out.cpu().numpy().reshape(-1), want.reshape(-1))
         again = ops.rms_norm_quant(dx, dw, 1e-6, "q8_1")       # the same launch outside a capture
