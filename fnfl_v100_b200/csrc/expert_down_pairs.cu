@@ -37,7 +37,13 @@ namespace {
 
 constexpr int kMaxWarps = FNB_DOWN_IQ4_WARPS;
 constexpr int kMaxT = 8;
-constexpr int kRowsPerWarp = 8;
+#ifndef FNB_DOWN_PAIRS_PASSES
+#define FNB_DOWN_PAIRS_PASSES 2
+#endif
+// a staged unit is this many groups of eight rows (more bytes per copy, fewer trips).  Windows of 1 / 3 rows, 640 columns:
+// Q2_0 0.123 / 0.236 ms with one group, 0.117 / 0.234 with two, 0.123 / 0.234 with four; IQ4_NL 0.138 / 0.197, 0.138 /
+// 0.187, 0.152 / 0.216
+constexpr int kPasses = FNB_DOWN_PAIRS_PASSES;  // where shared memory allows; else one group
 constexpr size_t kSmemLimit = 200 * 1024;
 constexpr int kGridPerSm = FNB_DOWN_IQ4_GRID;
 
@@ -135,19 +141,19 @@ __device__ __forceinline__ void dot_pair_q2(const uint32_t * x, const q2_image *
 
 template <int NT, bool WRAP, bool Q2>
 __device__ __forceinline__ void run_warp(const uint8_t * __restrict__ w, int64_t row_bytes, int nb, const uint2 * codes_sm,
-                                         const float * d_sm, uint8_t * stage, int unit_bytes, float * __restrict__ out,
+                                         const float * d_sm, uint8_t * stage, int unit_bytes, int unit_rows, float * __restrict__ out,
                                          int64_t out_stride, int64_t r0, int64_t r1) {
     const int lane = threadIdx.x & 31, k = lane & 3, sub = lane >> 2;
     const int warps = blockDim.x >> 5;
-    const int64_t n_units = (r1 - r0 + kRowsPerWarp - 1) / kRowsPerWarp, stride = int64_t(gridDim.x) * warps;
+    const int64_t n_units = (r1 - r0 + unit_rows - 1) / unit_rows, stride = int64_t(gridDim.x) * warps;
     int64_t u = int64_t(blockIdx.x) * warps + (threadIdx.x >> 5);
     if (u >= n_units) return;
     const uint32_t stage_sm = uint32_t(__cvta_generic_to_shared(stage));
     // a unit's rows are one run of the matrix; a ragged last unit copies the rows there are and leaves the others'
     // bytes as they were (their results are not stored)
     const auto issue = [&](int64_t unit, int buf) {
-        const int64_t first = r0 + unit * kRowsPerWarp;
-        const int rows = r1 - first < kRowsPerWarp ? int(r1 - first) : kRowsPerWarp;
+        const int64_t first = r0 + unit * unit_rows;
+        const int rows = r1 - first < unit_rows ? int(r1 - first) : unit_rows;
         stage_span(stage_sm + uint32_t(buf) * unit_bytes, w + first * row_bytes, rows * int(row_bytes), lane);
         cp_async_commit();
     };
@@ -162,10 +168,13 @@ __device__ __forceinline__ void run_warp(const uint8_t * __restrict__ w, int64_t
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncwarp();
-        const int64_t first = r0 + u * kRowsPerWarp, r = first + sub;
+        const int64_t first = r0 + u * unit_rows;
         const uintptr_t src = reinterpret_cast<uintptr_t>(w + first * row_bytes);
-        const uint32_t * x =
-            reinterpret_cast<const uint32_t *>(stage + size_t(trip & 1) * unit_bytes + (src & 15) + size_t(sub) * row_bytes);
+#pragma unroll 1
+        for (int pass = 0; pass < unit_rows / 8; ++pass) {
+        const int64_t r = first + 8 * pass + sub;
+        const uint32_t * x = reinterpret_cast<const uint32_t *>(stage + size_t(trip & 1) * unit_bytes + (src & 15) +
+                                                                size_t(8 * pass + sub) * row_bytes);
         float acc[NT][2];
 #pragma unroll
         for (int t = 0; t < NT; ++t) acc[t][0] = 0.0f, acc[t][1] = 0.0f;
@@ -177,7 +186,6 @@ __device__ __forceinline__ void run_warp(const uint8_t * __restrict__ w, int64_t
             const float * dk = d_sm;
             for (int ib = 0; ib < nb; ib += 2, x += 9, yk += 8, dk += 2) dot_pair<NT, WRAP>(x, yk, dk, nb, k, acc);
         }
-        __syncwarp();  // every lane is done with the buffer the next trip's copies overwrite
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
             // hsum8 of the reference's IQ kernels: lane l + 4 onto lane l (this lane's own pair), then s0 + s1 and
@@ -195,6 +203,8 @@ __device__ __forceinline__ void run_warp(const uint8_t * __restrict__ w, int64_t
             }
             if (k == 0 && r < r1) out[int64_t(t) * out_stride + r] = s;
         }
+        }
+        __syncwarp();  // every lane is done with the buffer the next trip's copies overwrite
         if (!more) break;
         u = un;
     }
@@ -205,7 +215,7 @@ template <int NT, bool Q2>
 __global__ void __launch_bounds__(kMaxWarps * 32)
     down_pairs_kernel(const uint8_t * __restrict__ w, int64_t row_bytes, int nb, const uint8_t * __restrict__ act,
                       int64_t act_stride, const float * __restrict__ scales, int64_t scale_stride, int act_bytes,
-                      int unit_bytes, float * __restrict__ out, int64_t out_stride, int64_t r0, int64_t r1) {
+                      int unit_bytes, int unit_rows, float * __restrict__ out, int64_t out_stride, int64_t r0, int64_t r1) {
     // the window's Q8_0 blocks rearranged: per block and lane k the code words k and 4 + k as one 8-byte entry
     // [NT nb][4], then the scales widened to F32 [NT nb]; then each warp's two units
     extern __shared__ __align__(16) uint8_t smem[];
@@ -244,9 +254,9 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
     const int wrap = __syncthreads_or(has_m128);
     uint8_t * stage = smem + act_bytes + size_t(threadIdx.x >> 5) * 2 * unit_bytes;
     if (wrap) {
-        run_warp<NT, true, Q2>(w, row_bytes, nb, codes_sm, d_sm, stage, unit_bytes, out, out_stride, r0, r1);
+        run_warp<NT, true, Q2>(w, row_bytes, nb, codes_sm, d_sm, stage, unit_bytes, unit_rows, out, out_stride, r0, r1);
     } else {
-        run_warp<NT, false, Q2>(w, row_bytes, nb, codes_sm, d_sm, stage, unit_bytes, out, out_stride, r0, r1);
+        run_warp<NT, false, Q2>(w, row_bytes, nb, codes_sm, d_sm, stage, unit_bytes, unit_rows, out, out_stride, r0, r1);
     }
 }
 
@@ -269,17 +279,23 @@ template <int NT, bool Q2>
 int32_t launch_nt(const uint8_t * w, int64_t row_bytes, int nb, const uint8_t * act, int64_t act_stride, const float * scales,
                   int64_t scale_stride, float * out, int64_t out_stride, int64_t r0, int64_t r1, cudaStream_t s) {
     const size_t act_bytes = Q2 ? size_t(NT) * nb * 4 * sizeof(q2_image) : (size_t(NT) * nb * 36 + 15) & ~size_t(15);
-    const size_t unit_bytes = (size_t(kRowsPerWarp) * row_bytes + 16 + 15) & ~size_t(15);
+    // kPasses groups of eight rows a unit where that still leaves four warps for two CTAs an SM, else one group
+    int unit_rows = 8 * kPasses;
+    size_t unit_bytes = (size_t(unit_rows) * row_bytes + 16 + 15) & ~size_t(15);
+    if (act_bytes + 4 * 2 * unit_bytes > kSmemLimit / 2) {
+        unit_rows = 8;
+        unit_bytes = (size_t(unit_rows) * row_bytes + 16 + 15) & ~size_t(15);
+    }
     if (act_bytes + 2 * unit_bytes > kSmemLimit) return FNB_REJECTED;
     int warps = int((kSmemLimit / 2 - act_bytes) / (2 * unit_bytes));  // two CTAs an SM where that leaves four warps each
     if (warps < 4) warps = int((kSmemLimit - act_bytes) / (2 * unit_bytes));
     warps = warps > kMaxWarps ? kMaxWarps : warps;
     if (!ensure_configured<NT, Q2>()) return FNB_LAUNCH_FAILED;
     const size_t smem = act_bytes + size_t(warps) * 2 * unit_bytes;
-    const int64_t units = (r1 - r0 + kRowsPerWarp - 1) / kRowsPerWarp;
+    const int64_t units = (r1 - r0 + unit_rows - 1) / unit_rows;
     const int grid = grid_for((units + warps - 1) / warps, kGridPerSm);
     down_pairs_kernel<NT, Q2><<<grid, warps * 32, smem, s>>>(w, row_bytes, nb, act, act_stride, scales, scale_stride,
-                                                              int(act_bytes), int(unit_bytes), out, out_stride, r0, r1);
+                                                              int(act_bytes), int(unit_bytes), unit_rows, out, out_stride, r0, r1);
     return launch_status();
 }
 
