@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("FNB200_LIB") or os.path.join(HERE, "libfnb200.so")   # FNB200_LIB: load another build
 
 OK, REJECTED, LAUNCH_FAILED = 0, 1, 2
-ERR_TOKEN, ERR_SLOT = 1, 2
+ERR_TOKEN, ERR_SLOT, ERR_TIMEOUT = 1, 2, 4
 
 
 class RopeKvArgs(C.Structure):
@@ -64,14 +64,14 @@ SIGNATURES = {
     "fnb_status_name": (C.c_char_p, [_I32]),
     "fnb_rms_norm_f32": (_I32, [_P, _P, _F, _P, _I64, _I32, _P]),
     "fnb_rms_norm_heads_f32": (_I32, [_P, _P, _F, _P, _I64, _I32, _I32, _P]),
-    "fnb_swiglu_q8_1": (_I32, [_P, _P, _P, _P, _I64, _I32, _P]),
-    "fnb_swiglu_act": (_I32, [_P, _P, _P, _P, _P, _I64, _I32, _P]),
-    "fnb_quantize_q8_1": (_I32, [_P, _P, _I64, _I32, _P]),
-    "fnb_quantize_q8_0": (_I32, [_P, _P, _I64, _I32, _P]),
-    "fnb_act_quantize": (_I32, [_P, _P, _P, _I64, _I32, _P]),
-    "fnb_rms_norm_q8_1": (_I32, [_P, _P, _F, _P, _P, _I64, _I32, _P]),
-    "fnb_rms_norm_q8_0": (_I32, [_P, _P, _F, _P, _P, _I64, _I32, _P]),
-    "fnb_rms_norm_act": (_I32, [_P, _P, _F, _P, _P, _P, _I64, _I32, _P]),
+    "fnb_swiglu_q8_1": (_I32, [_P, _P, _P, _P, _I64, _I32, _P, _P]),
+    "fnb_swiglu_act": (_I32, [_P, _P, _P, _P, _P, _I64, _I32, _P, _P]),
+    "fnb_quantize_q8_1": (_I32, [_P, _P, _I64, _I32, _P, _P]),
+    "fnb_quantize_q8_0": (_I32, [_P, _P, _I64, _I32, _P, _P]),
+    "fnb_act_quantize": (_I32, [_P, _P, _P, _I64, _I32, _P, _P]),
+    "fnb_rms_norm_q8_1": (_I32, [_P, _P, _F, _P, _P, _I64, _I32, _P, _P]),
+    "fnb_rms_norm_q8_0": (_I32, [_P, _P, _F, _P, _P, _I64, _I32, _P, _P]),
+    "fnb_rms_norm_act": (_I32, [_P, _P, _F, _P, _P, _P, _I64, _I32, _P, _P]),
     "fnb_rope_neox_q8_0_append": (_I32, [C.POINTER(RopeKvArgs), _P]),
     "fnb_rope_neox_kv8_append": (_I32, [C.POINTER(RopeKv8Args), _P]),
     "fnb_rope_theta_scale": (_F, [_F, _I32]),
@@ -99,9 +99,6 @@ SIGNATURES = {
     "fnb_gguf_n_tensors": (_I64, [_P]),
     "fnb_gguf_find": (_I32, [_P, C.c_char_p, C.POINTER(GgufTensor)]),
     "fnb_gguf_read_rows": (_I32, [_P, C.POINTER(GgufTensor), _I64, _I64, _P]),
-    "fnb_selftest_glu_math": (_I32, [C.c_uint64, C.c_uint64, _P, _P]),
-    "fnb_selftest_kv8_math": (_I32, [C.c_uint64, C.c_uint64, _P, _P]),
-    "fnb_selftest_expf": (_I32, [_P, _P]),
 }
 
 _lib = None

@@ -1,7 +1,7 @@
 // Library identity and status names.
 #include "common.cuh"
 
-extern "C" int32_t fnb_version(void) { return 100; }  // 0.1.0
+extern "C" int32_t fnb_version(void) { return 200; }  // 0.2.0
 
 extern "C" const char * fnb_status_name(int32_t status) {
     switch (status) {

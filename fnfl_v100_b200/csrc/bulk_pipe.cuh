@@ -2,8 +2,13 @@
 // cp.async.bulk global -> shared copy that signals them.  Every kernel here reads only its own GPU's memory and
 // every copy is issued by one CTA for itself (no cluster-wide forms).
 //
-// Waits are bounded: a wait that does not complete within kSpinLimit polls records FNB_ERR_TIMEOUT in the
-// caller's error word and returns false, and the kernel unwinds instead of spinning forever.
+// Waits are bounded: a wait that does not complete within its poll limit records FNB_ERR_TIMEOUT in the caller's
+// error word and returns false, and the kernel unwinds instead of spinning forever.  Two limits: the waits of the
+// data path (mbar_wait) use kPrimarySpinLimit, the waits a producer makes while unwinding - for the copies it has
+// already issued into its shared memory to land before the CTA exits - use kSpinLimit.  They are the same number
+// in the product; a build that defines FNB_PRIMARY_SPIN_LIMIT as a few polls makes the data path give up at once
+// while the unwinding stays patient, which is how the give-up path is exercised on a GPU without leaving a copy in
+// flight.
 #pragma once
 
 #include "common.cuh"
@@ -13,6 +18,10 @@ namespace fnb {
 // A failed poll suspends the thread for up to kPollNs, so the hint is also the granularity with which a waiter
 // notices completion: 2 us made a latency-sensitive pipeline (consumers faster than memory) three times slower.
 constexpr uint32_t kSpinLimit = 1u << 24;  // polls of at most kPollNs each: about a second in the worst case
+#ifndef FNB_PRIMARY_SPIN_LIMIT
+#define FNB_PRIMARY_SPIN_LIMIT (1u << 24)
+#endif
+constexpr uint32_t kPrimarySpinLimit = FNB_PRIMARY_SPIN_LIMIT;
 #ifndef FNB_POLL_NS
 #define FNB_POLL_NS 64
 #endif
@@ -45,10 +54,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t * bar, uint32_t parity) {
 }
 // bounded wait for the phase with the given parity; false (and FNB_ERR_TIMEOUT in *err) when it gives up
 __device__ __forceinline__ bool mbar_wait(uint64_t * bar, uint32_t parity, uint32_t * err) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    for (uint32_t i = 0; i < kPrimarySpinLimit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
     }
     if (err != nullptr) atomicOr(err, FNB_ERR_TIMEOUT);
+    return false;
+}
+// the unwinding wait: the producer's last look at a stage it has issued a copy into (always the full limit)
+__device__ __forceinline__ bool mbar_wait_landed(uint64_t * bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+    }
     return false;
 }
 

@@ -11,6 +11,14 @@
 // row each.  A lane owns whole blocks (block b = lane, lane + 32, ...), reads them in rotated 16-byte chunks
 // (conflict-free), and RELEASES THE STAGE AS SOON AS THE ROW IS IN REGISTERS, so nearly the whole ring is in flight.
 // amax, code sums and block headers are in-lane; only the row's sum of squares crosses lanes (one 5-step butterfly).
+//
+// Tiles go to the consumer groups in turn (tile i of a CTA to group i mod groups) and stage i mod stages holds it.
+// A group's parity waits on a stage are only sound while the ring is at least as deep as the number of groups
+// taking tiles (then the fill a group waits for is at most one phase past the last one the producer's own order
+// guarantees consumed); wide rows leave room for fewer stages than there are groups, so the launcher then runs
+// only `stages` groups and the other warps idle.
+// All barrier waits are bounded; a wait that gives up sets FNB_ERR_TIMEOUT in the caller's error word (when one is
+// given), consumers return and the producer stays until every copy it issued has landed.
 #include <atomic>
 
 #include "bulk_pipe.cuh"
@@ -42,7 +50,8 @@ __device__ __forceinline__ double sq4(double acc, float4 v) {
 template <out_fmt F, int BPL, bool F32OUT>
 __global__ void __launch_bounds__(kThreads, 1)
     rms_norm_quant_kernel(const float * __restrict__ x, const float * __restrict__ w, float eps, uint8_t * __restrict__ out,
-                          float * __restrict__ scales, float * __restrict__ out_f32, int64_t rows, int cols, int stages) {
+                          float * __restrict__ scales, float * __restrict__ out_f32, int64_t rows, int cols, int stages,
+                          int groups, uint32_t * err) {
     constexpr int BB = block_bytes<F>();
     extern __shared__ __align__(128) uint8_t smem[];
     const int nb = cols / 32;                            // blocks per row
@@ -76,7 +85,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         bool ok = true;
         for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
             const int s = it % stages;
-            if (it >= stages && !mbar_wait(&empty[s], (uint32_t(it / stages) & 1u) ^ 1u, nullptr)) {
+            if (it >= stages && !mbar_wait(&empty[s], (uint32_t(it / stages) & 1u) ^ 1u, err)) {
                 ok = false;
                 break;
             }
@@ -86,27 +95,29 @@ __global__ void __launch_bounds__(kThreads, 1)
             bulk_g2s(data + size_t(s) * tile_bytes, x + r0 * cols, bytes, &full[s], policy);
             mbar_arrive(&full[s]);
         }
-        if (!ok) {
-            for (int j = 1; j <= stages && j <= it; ++j) {
-                const int its = it - j;
-                mbar_wait(&full[its % stages], uint32_t(its / stages) & 1u, nullptr);
-            }
+        // the producer leaves last: every copy it issued has landed before the CTA's shared memory is released
+        (void) ok;
+        for (int j = 1; j <= stages && j <= it; ++j) {
+            const int its = it - j;
+            mbar_wait_landed(&full[its % stages], uint32_t(its / stages) & 1u);
         }
         return;
     }
 
     const int grp = wid / kGroupWarps, gw = wid - grp * kGroupWarps;
+    if (grp >= groups) return;  // a ring shallower than kGroups is shared by `groups` groups only
     uint8_t * my_out = outs + size_t(wid) * row_out_pad;
 
     int it = 0;
     for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
-        if (it % kGroups != grp) continue;
+        if (it % groups != grp) continue;
         const int s = it % stages;
         const uint32_t fill = uint32_t(it / stages);
         // successive fills of a stage go to different groups: wait for the previous fill to have been consumed before
-        // trusting the parity of this one (a parity wait is only meaningful at most one phase ahead)
-        if (fill > 0 && !mbar_wait(&empty[s], (fill - 1u) & 1u, nullptr)) return;
-        if (!mbar_wait(&full[s], fill & 1u, nullptr)) return;
+        // trusting the parity of this one (a parity wait is only meaningful at most one phase ahead; stages >= groups
+        // keeps the empty barrier itself within one phase of this group's view)
+        if (fill > 0 && !mbar_wait(&empty[s], (fill - 1u) & 1u, err)) return;
+        if (!mbar_wait(&full[s], fill & 1u, err)) return;
         const int64_t row = tile * kGroupWarps + gw;
         const bool live = row < rows;
         const uint8_t * src = data + size_t(s) * tile_bytes + size_t(live ? gw : 0) * row_bytes;
@@ -228,7 +239,7 @@ bool prepare_fmt() {
 
 template <out_fmt F, int BPL, bool F32OUT>
 int32_t launch_one(const float * x, const float * w, float eps, uint8_t * out, float * scales, float * out_f32, int64_t rows,
-                   int32_t cols, cudaStream_t s) {
+                   int32_t cols, uint32_t * err, cudaStream_t s) {
     constexpr int BB = block_bytes<F>();
     const size_t tile = size_t(cols) * 4 * kGroupWarps;
     const size_t row_out_pad = (size_t(cols / 32) * BB + 15) & ~size_t(15);
@@ -241,14 +252,16 @@ int32_t launch_one(const float * x, const float * w, float eps, uint8_t * out, f
     if (!ensure_configured<F, BPL, F32OUT>()) return FNB_LAUNCH_FAILED;
     const int64_t n_tiles = (rows + kGroupWarps - 1) / kGroupWarps;
     const int grid = int(n_tiles < kSmCount ? n_tiles : kSmCount);
-    rms_norm_quant_kernel<F, BPL, F32OUT><<<grid, kThreads, smem, s>>>(x, w, eps, out, scales, out_f32, rows, cols, stages);
+    const int groups = stages < kGroups ? stages : kGroups;
+    rms_norm_quant_kernel<F, BPL, F32OUT><<<grid, kThreads, smem, s>>>(x, w, eps, out, scales, out_f32, rows, cols, stages,
+                                                                       groups, err);
     return launch_status();
 }
 
 template <out_fmt F>
 int32_t launch(const float * x, const float * w, float eps, void * out, float * scales, float * out_f32, int64_t rows,
-               int32_t cols, cudaStream_t s) {
-    if (!ok_ptr(x, 16) || !ok_opt(w, 16) || !ok_ptr(out, 16) || !ok_opt(out_f32, 16)) return FNB_REJECTED;
+               int32_t cols, uint32_t * err, cudaStream_t s) {
+    if (!ok_ptr(x, 16) || !ok_opt(w, 16) || !ok_ptr(out, 16) || !ok_opt(out_f32, 16) || !ok_opt(err, 4)) return FNB_REJECTED;
     if (F == out_fmt::act && !ok_ptr(scales, 8)) return FNB_REJECTED;
     if (rows < 1 || rows > INT32_MAX || cols < 32 || cols > 4096 || cols % 32 != 0 || !(eps >= 0.0f)) return FNB_REJECTED;
     uint8_t * o = static_cast<uint8_t *>(out);
@@ -256,8 +269,8 @@ int32_t launch(const float * x, const float * w, float eps, void * out, float * 
     const bool f = out_f32 != nullptr;
 #define FNB_CASE(B)                                                                                   \
     case B:                                                                                           \
-        return f ? launch_one<F, B, true>(x, w, eps, o, scales, out_f32, rows, cols, s)               \
-                 : launch_one<F, B, false>(x, w, eps, o, scales, nullptr, rows, cols, s);
+        return f ? launch_one<F, B, true>(x, w, eps, o, scales, out_f32, rows, cols, err, s)          \
+                 : launch_one<F, B, false>(x, w, eps, o, scales, nullptr, rows, cols, err, s);
     switch (bpl) {
         FNB_CASE(1)
         FNB_CASE(2)
@@ -277,16 +290,19 @@ bool rms_norm_quant_prepare_device() {
 }  // namespace fnb
 
 extern "C" int32_t fnb_rms_norm_q8_1(const float * x, const float * w, float eps, void * out_q8_1, float * out_f32,
-                                     int64_t rows, int32_t cols, void * stream) {
-    return fnb::launch<fnb::out_fmt::q8_1>(x, w, eps, out_q8_1, nullptr, out_f32, rows, cols, static_cast<cudaStream_t>(stream));
+                                     int64_t rows, int32_t cols, uint32_t * err, void * stream) {
+    return fnb::launch<fnb::out_fmt::q8_1>(x, w, eps, out_q8_1, nullptr, out_f32, rows, cols, err,
+                                          static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int32_t fnb_rms_norm_q8_0(const float * x, const float * w, float eps, void * out_q8_0, float * out_f32,
-                                     int64_t rows, int32_t cols, void * stream) {
-    return fnb::launch<fnb::out_fmt::q8_0>(x, w, eps, out_q8_0, nullptr, out_f32, rows, cols, static_cast<cudaStream_t>(stream));
+                                     int64_t rows, int32_t cols, uint32_t * err, void * stream) {
+    return fnb::launch<fnb::out_fmt::q8_0>(x, w, eps, out_q8_0, nullptr, out_f32, rows, cols, err,
+                                          static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int32_t fnb_rms_norm_act(const float * x, const float * w, float eps, int8_t * codes, float * scales,
-                                    float * out_f32, int64_t rows, int32_t cols, void * stream) {
-    return fnb::launch<fnb::out_fmt::act>(x, w, eps, codes, scales, out_f32, rows, cols, static_cast<cudaStream_t>(stream));
+                                    float * out_f32, int64_t rows, int32_t cols, uint32_t * err, void * stream) {
+    return fnb::launch<fnb::out_fmt::act>(x, w, eps, codes, scales, out_f32, rows, cols, err,
+                                          static_cast<cudaStream_t>(stream));
 }

@@ -202,12 +202,14 @@ __global__ void __launch_bounds__(kThreads, 1) rope_kv_pipe_kernel(const rope_ke
             __syncwarp();
             if (lane == 0) mbar_arrive(&full[s]);
         }
-        if (!ok && pw == 0) {
-            // unwinding after a timed-out wait: let the copies already issued into this CTA's shared memory land
-            // (bounded) before the CTA exits and the memory is handed to another CTA
+        // The copying producer leaves last: every copy it issued into this CTA's shared memory has landed (bounded)
+        // before the CTA can exit and the memory be handed to another CTA.  After a normal run these waits pass at
+        // once; after a wait that gave up, here or in a consumer, they are what keeps the exit safe.
+        (void) ok;
+        if (pw == 0 && lane == 0) {
             for (int j = 1; j <= stages && j <= it; ++j) {
                 const int its = it - j;
-                mbar_wait(&full[its % stages], uint32_t(its / stages) & 1u, nullptr);
+                mbar_wait_landed(&full[its % stages], uint32_t(its / stages) & 1u);
             }
         }
         return;
@@ -404,36 +406,6 @@ bool launch_one(const rope_kernel_args & a, cudaStream_t s) {
     return true;
 }
 
-// Self-check of kv8_rule's written-out division against __fdiv_rn: every positive finite FP16 scale (i mod 31743)
-// with pseudo-random x of magnitude up to 300 s; counts codes that differ.
-__global__ void kv8_selftest_kernel(uint64_t n, uint64_t seed, unsigned long long * mismatches) {
-    unsigned long long bad = 0;
-    for (uint64_t i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += uint64_t(gridDim.x) * blockDim.x) {
-        uint64_t z = (i + seed) * 0x9E3779B97F4A7C15ull;  // splitmix64 finaliser
-        z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
-        z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
-        z ^= z >> 31;
-        const float s = f16_bits_to_f32(uint16_t(1u + uint32_t(i % 31743u)));  // 0x0001 .. 0x7BFF
-        // x = s * m with m log-uniform in [2^-12, 300), half of them pushed onto exact k + 0.5 multiples of s
-        const float mant = __uint_as_float(0x3f800000u | (uint32_t(z) & 0x7fffffu));
-        float m = mant * exp2f(float(int((z >> 24) % 21u)) - 12.0f);
-        if (z & (1ull << 60)) m = floorf(fminf(m, 200.0f)) + 0.5f;
-        float x = __fmul_rn(s, m);
-        if (z & (1ull << 61)) x = -x;
-        kv8_rule rule(__fmul_rn(s, 127.0f));  // amax that maps back onto the scale (or its neighbour)
-        rule.sb = 0, rule.s = s;
-        rule.fast = s >= 0x1p-24f && s <= 65504.0f;
-        float r0;
-        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(s));
-        rule.r = __fmaf_rn(r0, __fmaf_rn(-s, r0, 1.0f), r0);
-        const int fast = rule.code(x);
-        const int ref = max(-127, min(127, __float2int_rn(__fdiv_rn(x, s))));
-        bad += fast != ref;
-        bad += rule.code4(make_float4(x, -x, x, -x)) != pack4(ref, -ref, ref, -ref);  // the form the kernel calls
-    }
-    if (bad != 0) atomicAdd(mismatches, bad);
-}
-
 }  // namespace
 
 bool rope_kv_pipe_try_launch(const rope_kernel_args & a, int head_dim, kv_fmt fmt, cudaStream_t s) {
@@ -453,9 +425,3 @@ bool rope_prepare_device() {
 }
 
 }  // namespace fnb
-
-extern "C" int32_t fnb_selftest_kv8_math(uint64_t n, uint64_t seed, unsigned long long * mismatches, void * stream) {
-    if (!fnb::ok_ptr(mismatches, 8) || n == 0) return FNB_REJECTED;
-    fnb::kv8_selftest_kernel<<<fnb::kSmCount * 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(n, seed, mismatches);
-    return fnb::launch_status();
-}

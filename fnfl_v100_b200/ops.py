@@ -15,7 +15,7 @@ import torch
 from . import _lib
 
 Q8_0_BLOCK, Q8_1_BLOCK, Q4_K_BLOCK, IQ3_XXS_BLOCK = 34, 36, 144, 98
-ERR_TOKEN, ERR_SLOT = _lib.ERR_TOKEN, _lib.ERR_SLOT
+ERR_TOKEN, ERR_SLOT, ERR_TIMEOUT = _lib.ERR_TOKEN, _lib.ERR_SLOT, _lib.ERR_TIMEOUT
 
 _TABLE_BLOCK = {"q4_k": (256, Q4_K_BLOCK), "iq3_xxs": (256, IQ3_XXS_BLOCK), "q8_0": (32, Q8_0_BLOCK)}
 
@@ -32,6 +32,25 @@ def _dev(t: torch.Tensor, dtype: torch.dtype, name: str) -> torch.Tensor:
     if not (isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == dtype and t.is_contiguous()):
         raise ValueError(f"{name}: expected a contiguous CUDA tensor of {dtype}")
     return t
+
+
+def _same_device(*tensors) -> torch.device:
+    """Every tensor of a call lives on one device, which becomes the current device for the launch."""
+    devs = {t.device for t in tensors if t is not None}
+    if len(devs) != 1:
+        raise ValueError("tensors of one call must live on one CUDA device")
+    return devs.pop()
+
+
+def _numel(t: torch.Tensor | None, n: int, name: str) -> None:
+    if t is not None and t.numel() != n:
+        raise ValueError(f"{name}: expected {n} elements, got {t.numel()}")
+
+
+def _err(err: torch.Tensor | None) -> torch.Tensor | None:
+    if err is not None:
+        _dev(err, torch.int32, "err")
+    return err
 
 
 def _check(status: int, what: str) -> None:
@@ -77,27 +96,30 @@ def rms_norm_heads(x: torch.Tensor, w: torch.Tensor | None, eps: float = 1e-6, o
 
 
 def rms_norm_quant(x: torch.Tensor, w: torch.Tensor | None, eps: float = 1e-6, fmt: str = "q8_1",
-                   out_f32: torch.Tensor | None = None):
+                   out_f32: torch.Tensor | None = None, err: torch.Tensor | None = None):
     """RMSNorm fused with requantisation of its output.  fmt "q8_1" / "q8_0": returns uint8 blocks [rows][cols/32*B];
     fmt "act": returns (codes int8 [rows][cols], scales F32 [rows][cols/32][2])."""
     _dev(x, torch.float32, "x")
+    rows, cols = _rows_cols(x)
     if w is not None:
         _dev(w, torch.float32, "w")
+        _numel(w, cols, "w")
     if out_f32 is not None:
         _dev(out_f32, torch.float32, "out_f32")
-    rows, cols = _rows_cols(x)
+        _numel(out_f32, rows * cols, "out_f32")
     L = _lib.lib()
-    if fmt == "act":
-        codes = torch.empty((rows, cols), dtype=torch.int8, device=x.device)
-        scales = torch.empty((rows, cols // 32, 2), dtype=torch.float32, device=x.device)
-        _check(L.fnb_rms_norm_act(_ptr(x), _ptr(w), eps, _ptr(codes), _ptr(scales), _ptr(out_f32), rows, cols, _stream()),
-               "rms_norm_act")
-        return codes, scales
-    bb = {"q8_1": Q8_1_BLOCK, "q8_0": Q8_0_BLOCK}[fmt]
-    out = torch.empty((rows, cols // 32 * bb), dtype=torch.uint8, device=x.device)
-    fn = L.fnb_rms_norm_q8_1 if fmt == "q8_1" else L.fnb_rms_norm_q8_0
-    _check(fn(_ptr(x), _ptr(w), eps, _ptr(out), _ptr(out_f32), rows, cols, _stream()), "rms_norm_" + fmt)
-    return out
+    with torch.cuda.device(_same_device(x, w, out_f32, _err(err))):
+        if fmt == "act":
+            codes = torch.empty((rows, cols), dtype=torch.int8, device=x.device)
+            scales = torch.empty((rows, cols // 32, 2), dtype=torch.float32, device=x.device)
+            _check(L.fnb_rms_norm_act(_ptr(x), _ptr(w), eps, _ptr(codes), _ptr(scales), _ptr(out_f32), rows, cols,
+                                      _ptr(err), _stream()), "rms_norm_act")
+            return codes, scales
+        bb = {"q8_1": Q8_1_BLOCK, "q8_0": Q8_0_BLOCK}[fmt]
+        out = torch.empty((rows, cols // 32 * bb), dtype=torch.uint8, device=x.device)
+        fn = L.fnb_rms_norm_q8_1 if fmt == "q8_1" else L.fnb_rms_norm_q8_0
+        _check(fn(_ptr(x), _ptr(w), eps, _ptr(out), _ptr(out_f32), rows, cols, _ptr(err), _stream()), "rms_norm_" + fmt)
+        return out
 
 
 # ---- SwiGLU + requantisation --------------------------------------------------------------------------------
@@ -108,48 +130,60 @@ def _rows_cols(x: torch.Tensor) -> tuple[int, int]:
 
 
 def swiglu_q8_1(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor | None = None,
-                out_f32: torch.Tensor | None = None) -> torch.Tensor:
+                out_f32: torch.Tensor | None = None, err: torch.Tensor | None = None) -> torch.Tensor:
     """silu(gate) * up -> ggml Q8_1 blocks, uint8 [rows][cols / 32 * 36]; replaces fn::experts::glu_finish."""
     _dev(gate, torch.float32, "gate")
     _dev(up, torch.float32, "up")
     if up.shape != gate.shape:
         raise ValueError("gate and up must have one shape")
     rows, cols = _rows_cols(gate)
-    if out is None:
-        out = torch.empty((rows, cols // 32 * Q8_1_BLOCK), dtype=torch.uint8, device=gate.device)
-    _dev(out, torch.uint8, "out")
-    if out_f32 is not None:
-        _dev(out_f32, torch.float32, "out_f32")
-    _check(_lib.lib().fnb_swiglu_q8_1(_ptr(gate), _ptr(up), _ptr(out), _ptr(out_f32), rows, cols, _stream()),
-           "swiglu_q8_1")
+    with torch.cuda.device(_same_device(gate, up, out, out_f32, _err(err))):
+        if out is None:
+            out = torch.empty((rows, cols // 32 * Q8_1_BLOCK), dtype=torch.uint8, device=gate.device)
+        _dev(out, torch.uint8, "out")
+        _numel(out, rows * (cols // 32) * Q8_1_BLOCK, "out")
+        if out_f32 is not None:
+            _dev(out_f32, torch.float32, "out_f32")
+            _numel(out_f32, rows * cols, "out_f32")
+        _check(_lib.lib().fnb_swiglu_q8_1(_ptr(gate), _ptr(up), _ptr(out), _ptr(out_f32), rows, cols, _ptr(err),
+                                          _stream()), "swiglu_q8_1")
     return out
 
 
-def swiglu_act(gate: torch.Tensor, up: torch.Tensor, out_f32: torch.Tensor | None = None):
+def swiglu_act(gate: torch.Tensor, up: torch.Tensor, out_f32: torch.Tensor | None = None,
+               err: torch.Tensor | None = None):
     """silu(gate) * up -> the reference's activation format: (codes int8 [rows][cols], scales F32 [rows][cols/32][2])."""
     _dev(gate, torch.float32, "gate")
     _dev(up, torch.float32, "up")
+    if up.shape != gate.shape:
+        raise ValueError("gate and up must have one shape")
     rows, cols = _rows_cols(gate)
-    codes = torch.empty((rows, cols), dtype=torch.int8, device=gate.device)
-    scales = torch.empty((rows, cols // 32, 2), dtype=torch.float32, device=gate.device)
-    _check(_lib.lib().fnb_swiglu_act(_ptr(gate), _ptr(up), _ptr(codes), _ptr(scales), _ptr(out_f32), rows, cols,
-                                     _stream()), "swiglu_act")
+    if out_f32 is not None:
+        _dev(out_f32, torch.float32, "out_f32")
+        _numel(out_f32, rows * cols, "out_f32")
+    with torch.cuda.device(_same_device(gate, up, out_f32, _err(err))):
+        codes = torch.empty((rows, cols), dtype=torch.int8, device=gate.device)
+        scales = torch.empty((rows, cols // 32, 2), dtype=torch.float32, device=gate.device)
+        _check(_lib.lib().fnb_swiglu_act(_ptr(gate), _ptr(up), _ptr(codes), _ptr(scales), _ptr(out_f32), rows, cols,
+                                         _ptr(err), _stream()), "swiglu_act")
     return codes, scales
 
 
-def quantize_q8_1(x: torch.Tensor) -> torch.Tensor:
+def quantize_q8_1(x: torch.Tensor, err: torch.Tensor | None = None) -> torch.Tensor:
     _dev(x, torch.float32, "x")
     rows, cols = _rows_cols(x)
-    out = torch.empty((rows, cols // 32 * Q8_1_BLOCK), dtype=torch.uint8, device=x.device)
-    _check(_lib.lib().fnb_quantize_q8_1(_ptr(x), _ptr(out), rows, cols, _stream()), "quantize_q8_1")
+    with torch.cuda.device(_same_device(x, _err(err))):
+        out = torch.empty((rows, cols // 32 * Q8_1_BLOCK), dtype=torch.uint8, device=x.device)
+        _check(_lib.lib().fnb_quantize_q8_1(_ptr(x), _ptr(out), rows, cols, _ptr(err), _stream()), "quantize_q8_1")
     return out
 
 
-def quantize_q8_0(x: torch.Tensor) -> torch.Tensor:
+def quantize_q8_0(x: torch.Tensor, err: torch.Tensor | None = None) -> torch.Tensor:
     _dev(x, torch.float32, "x")
     rows, cols = _rows_cols(x)
-    out = torch.empty((rows, cols // 32 * Q8_0_BLOCK), dtype=torch.uint8, device=x.device)
-    _check(_lib.lib().fnb_quantize_q8_0(_ptr(x), _ptr(out), rows, cols, _stream()), "quantize_q8_0")
+    with torch.cuda.device(_same_device(x, _err(err))):
+        out = torch.empty((rows, cols // 32 * Q8_0_BLOCK), dtype=torch.uint8, device=x.device)
+        _check(_lib.lib().fnb_quantize_q8_0(_ptr(x), _ptr(out), rows, cols, _ptr(err), _stream()), "quantize_q8_0")
     return out
 
 
@@ -162,13 +196,15 @@ def quantize_q8_k(x: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def act_quantize(x: torch.Tensor):
+def act_quantize(x: torch.Tensor, err: torch.Tensor | None = None):
     """fn::act::quantize: F32 [rows][k] -> (codes int8 [rows][k], scales F32 [rows][k/32][2])."""
     _dev(x, torch.float32, "x")
     rows, cols = _rows_cols(x)
-    codes = torch.empty((rows, cols), dtype=torch.int8, device=x.device)
-    scales = torch.empty((rows, cols // 32, 2), dtype=torch.float32, device=x.device)
-    _check(_lib.lib().fnb_act_quantize(_ptr(x), _ptr(codes), _ptr(scales), rows, cols, _stream()), "act_quantize")
+    with torch.cuda.device(_same_device(x, _err(err))):
+        codes = torch.empty((rows, cols), dtype=torch.int8, device=x.device)
+        scales = torch.empty((rows, cols // 32, 2), dtype=torch.float32, device=x.device)
+        _check(_lib.lib().fnb_act_quantize(_ptr(x), _ptr(codes), _ptr(scales), rows, cols, _ptr(err), _stream()),
+               "act_quantize")
     return codes, scales
 
 

@@ -74,11 +74,15 @@ int32_t fnb_rms_norm_heads_f32(const float * x, const float * w, float eps, floa
  * (fn/kernels/experts/experts.h:45-47).  expf is evaluated exactly as glibc 2.39's non-FMA expf.
  * As with the rope entry points, the first call of each SwiGLU / requantiser variant on a device raises its
  * kernel's dynamic shared-memory limit (cudaFuncSetAttribute): make that first call outside a stream capture.
+ * err (optional device error word, 4-byte aligned; the same for every SwiGLU / requantiser / fused-norm entry point
+ * below): these kernels stage their input through a ring of shared-memory stages filled by bulk copies and every
+ * wait on that ring is bounded; a wait that gives up sets FNB_ERR_TIMEOUT in *err, the launch ends by itself and
+ * its outputs are incomplete.  With err null such a launch ends the same way, unreported.
  * Replaces fn::experts::glu_finish (fn/kernels/experts/experts.h:273-277, experts.cu:716-729) and the GLU
  * epilogues glu_out / glu_run (experts_gu.cuh:308-340, experts_dev.cuh:196-213).
  */
 int32_t fnb_swiglu_q8_1(const float * gate, const float * up, void * out_q8_1, float * out_f32, int64_t rows,
-                        int32_t cols, void * stream);
+                        int32_t cols, uint32_t * err, void * stream);
 
 /*
  * The same GLU into the reference's own activation format: int8 codes [rows][cols] and F32 {d, s} pairs
@@ -87,7 +91,7 @@ int32_t fnb_swiglu_q8_1(const float * gate, const float * up, void * out_q8_1, f
  * Bitwise drop-in for fn::experts::glu_finish's outputs.
  */
 int32_t fnb_swiglu_act(const float * gate, const float * up, int8_t * codes, float * scales, float * out_f32,
-                       int64_t rows, int32_t cols, void * stream);
+                       int64_t rows, int32_t cols, uint32_t * err, void * stream);
 
 /*
  * Stand-alone requantisers of F32 [rows][cols] (cols a multiple of 32): ggml Q8_1 blocks, ggml Q8_0 blocks, and
@@ -95,9 +99,9 @@ int32_t fnb_swiglu_act(const float * gate, const float * up, int8_t * codes, flo
  * (fn/kernels/act/act.h:57-66, act.cu:17-49); the Q8 forms replace the CPU quantize_q8_1 / quantize_q8_0 of
  * the expert miss path (fn/kernels/experts/experts_cpu.cpp:359-367) with ggml's reference rounding rule.
  */
-int32_t fnb_quantize_q8_1(const float * x, void * out_q8_1, int64_t rows, int32_t cols, void * stream);
-int32_t fnb_quantize_q8_0(const float * x, void * out_q8_0, int64_t rows, int32_t cols, void * stream);
-int32_t fnb_act_quantize(const float * x, int8_t * codes, float * scales, int64_t rows, int32_t cols,
+int32_t fnb_quantize_q8_1(const float * x, void * out_q8_1, int64_t rows, int32_t cols, uint32_t * err, void * stream);
+int32_t fnb_quantize_q8_0(const float * x, void * out_q8_0, int64_t rows, int32_t cols, uint32_t * err, void * stream);
+int32_t fnb_act_quantize(const float * x, int8_t * codes, float * scales, int64_t rows, int32_t cols, uint32_t * err,
                          void * stream);
 
 /*
@@ -109,11 +113,11 @@ int32_t fnb_act_quantize(const float * x, int8_t * codes, float * scales, int64_
  * First call per device and variant sets a kernel attribute (see fnb_swiglu_q8_1).
  */
 int32_t fnb_rms_norm_q8_1(const float * x, const float * w, float eps, void * out_q8_1, float * out_f32, int64_t rows,
-                          int32_t cols, void * stream);
+                          int32_t cols, uint32_t * err, void * stream);
 int32_t fnb_rms_norm_q8_0(const float * x, const float * w, float eps, void * out_q8_0, float * out_f32, int64_t rows,
-                          int32_t cols, void * stream);
+                          int32_t cols, uint32_t * err, void * stream);
 int32_t fnb_rms_norm_act(const float * x, const float * w, float eps, int8_t * codes, float * scales, float * out_f32,
-                         int64_t rows, int32_t cols, void * stream);
+                         int64_t rows, int32_t cols, uint32_t * err, void * stream);
 
 /*
  * Optional per-head RMSNorm, NeoX partial-rotary RoPE, and Q8_0 quantise-and-append of K and V into the cache.
@@ -399,27 +403,6 @@ int32_t fnb_expert_down_rows_q2_0(const void * w, int64_t row_bytes, int32_t n, 
  * Replaces fn::embed::check_tokens (fn/kernels/embed/embed.h:56).
  */
 int64_t fnb_check_tokens(const int32_t * ids_host, int64_t rows, int64_t n_vocab);
-
-/*
- * Diagnostic with no counterpart in the reference: runs the SwiGLU fast path (branch-free expf and the written-out
- * IEEE division) and the generic path on n pseudo-random (gate, up) pairs covering the fast path's whole domain and
- * adds the number of results whose bits differ to *mismatches (device memory, 8-byte aligned, caller-zeroed).
- */
-int32_t fnb_selftest_glu_math(uint64_t n, uint64_t seed, unsigned long long * mismatches, void * stream);
-
-/*
- * Diagnostic with no counterpart in the reference: the KV8 rule's written-out division by the group scale against
- * __fdiv_rn, over every positive finite FP16 scale and n pseudo-random values (half of them on exact half steps);
- * adds the number of differing codes to *mismatches.
- */
-int32_t fnb_selftest_kv8_math(uint64_t n, uint64_t seed, unsigned long long * mismatches, void * stream);
-
-/*
- * Diagnostic with no counterpart in the reference: for EVERY float |x| < 88 (both signs, 2 x 0x42b00000 inputs)
- * compares the SwiGLU fast path's e^x (reduction as defined, cubic as a fused Horner chain, 8 FP64 operations) with the
- * operation-for-operation evaluation of the definition (12) and adds the number of differing results to *mismatches.
- */
-int32_t fnb_selftest_expf(unsigned long long * mismatches, void * stream);
 
 /*
  * Optional, once per device (the current one): performs the one-time kernel attribute set-up (cudaFuncSetAttribute for

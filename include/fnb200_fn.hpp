@@ -48,15 +48,18 @@ struct out_view {  // fn::act::out_view: codes int8 [rows][k], scales F32 [rows]
     float * scales = nullptr;
     int32_t rows = 0;
     int32_t k = 0;
+    uint32_t * err = nullptr;  // not in fn::act::out_view: optional device error word (FNB_ERR_TIMEOUT)
 };
 inline bool quantize(const float * x, const out_view & o, void * stream) {
-    return fnb_act_quantize(x, o.codes, o.scales, o.rows, o.k, stream) == FNB_OK;
+    return fnb_act_quantize(x, o.codes, o.scales, o.rows, o.k, o.err, stream) == FNB_OK;
 }
-inline bool quantize_q8_1(const float * x, void * blocks, int64_t rows, int32_t k, void * stream) {
-    return fnb_quantize_q8_1(x, blocks, rows, k, stream) == FNB_OK;
+inline bool quantize_q8_1(const float * x, void * blocks, int64_t rows, int32_t k, void * stream,
+                          uint32_t * err = nullptr) {
+    return fnb_quantize_q8_1(x, blocks, rows, k, err, stream) == FNB_OK;
 }
-inline bool quantize_q8_0(const float * x, void * blocks, int64_t rows, int32_t k, void * stream) {
-    return fnb_quantize_q8_0(x, blocks, rows, k, stream) == FNB_OK;
+inline bool quantize_q8_0(const float * x, void * blocks, int64_t rows, int32_t k, void * stream,
+                          uint32_t * err = nullptr) {
+    return fnb_quantize_q8_0(x, blocks, rows, k, err, stream) == FNB_OK;
 }
 
 }  // namespace act
@@ -64,14 +67,15 @@ inline bool quantize_q8_0(const float * x, void * blocks, int64_t rows, int32_t 
 namespace experts {  // SwiGLU + requantisation: fn::experts::glu_finish
 
 // gs, us: F32 [n][cols] gate and up sums; the GLU leaves in the reference's activation format
+// (err, not in the reference's signature: optional device error word for FNB_ERR_TIMEOUT)
 inline bool glu_finish(const float * gs, const float * us, int64_t n, int32_t cols, int8_t * codes, float * scales,
-                       void * stream) {
-    return fnb_swiglu_act(gs, us, codes, scales, nullptr, n, cols, stream) == FNB_OK;
+                       void * stream, uint32_t * err = nullptr) {
+    return fnb_swiglu_act(gs, us, codes, scales, nullptr, n, cols, err, stream) == FNB_OK;
 }
 // the same GLU as ggml Q8_1 blocks [n][cols / 32]; glu_f32 (optional) receives the F32 GLU the codes were made from
 inline bool glu_finish_q8_1(const float * gs, const float * us, int64_t n, int32_t cols, void * blocks, float * glu_f32,
-                            void * stream) {
-    return fnb_swiglu_q8_1(gs, us, blocks, glu_f32, n, cols, stream) == FNB_OK;
+                            void * stream, uint32_t * err = nullptr) {
+    return fnb_swiglu_q8_1(gs, us, blocks, glu_f32, n, cols, err, stream) == FNB_OK;
 }
 
 // the experts' gate / up mat-vec with the GLU over a decode window (fn::experts::cpu::kq_gu_rows for fmt q4_k, same

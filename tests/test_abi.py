@@ -67,12 +67,13 @@ def test_rejections_enqueue_nothing(lib):
     assert lib.fnb_rms_norm_f32(A16, A16, -1.0, A16, 4, 2048, None) == R
     assert lib.fnb_rms_norm_heads_f32(A16, A16, 1e-6, A16, 4, 0, 256, None) == R
     # swiglu / requantisers: cols must be a multiple of 32, pointers 16-byte aligned
-    assert lib.fnb_swiglu_q8_1(A16, A16, A16, None, 8, 48, None) == R
-    assert lib.fnb_swiglu_q8_1(A16, None, A16, None, 8, 512, None) == R
-    assert lib.fnb_swiglu_q8_1(A16, A16, ODD, None, 8, 512, None) == R
-    assert lib.fnb_swiglu_act(A16, A16, A16, None, None, 8, 512, None) == R
-    assert lib.fnb_quantize_q8_1(A16, A16, -3, 512, None) == R
-    assert lib.fnb_quantize_q8_0(None, A16, 3, 512, None) == R
+    assert lib.fnb_swiglu_q8_1(A16, A16, A16, None, 8, 48, None, None) == R
+    assert lib.fnb_swiglu_q8_1(A16, None, A16, None, 8, 512, None, None) == R
+    assert lib.fnb_swiglu_q8_1(A16, A16, ODD, None, 8, 512, None, None) == R
+    assert lib.fnb_swiglu_q8_1(A16, A16, A16, None, 8, 512, A16 + 2, None) == R   # the error word needs 4-byte alignment
+    assert lib.fnb_swiglu_act(A16, A16, A16, None, None, 8, 512, None, None) == R
+    assert lib.fnb_quantize_q8_1(A16, A16, -3, 512, None, None) == R
+    assert lib.fnb_quantize_q8_0(None, A16, 3, 512, None, None) == R
     assert lib.fnb_quantize_q8_k(A16, A16, 4, 300, None) == R      # cols not a multiple of 256
     assert lib.fnb_quantize_q8_k(ODD, A16, 4, 512, None) == R
     assert lib.fnb_quantize_q8_k(A16, None, 4, 512, None) == R
@@ -135,7 +136,7 @@ def test_rejections_enqueue_nothing(lib):
         setattr(kb, field, bad)
         assert lib.fnb_kv_read_f32(C.byref(kb), None) == R, field
     assert lib.fnb_kv_read_f32(None, None) == R
-    assert lib.fnb_act_quantize(A16, A16, ODD + 2, 3, 512, None) == R       # scales need 8-byte alignment
+    assert lib.fnb_act_quantize(A16, A16, ODD + 2, 3, 512, None, None) == R       # scales need 8-byte alignment
     # get_rows
     assert lib.fnb_get_rows_q4_k(A16, 100, A16, A16, None, 8, 2000, None) == R
     assert lib.fnb_get_rows_q4_k(A16, 0, A16, A16, None, 8, 2048, None) == R
@@ -170,7 +171,8 @@ def test_embed_layout_rejections(lib):
     none = _lib.EmbedArgs(**{**ok, "own": None, "full": None, "streams": None})
     assert lib.fnb_embed_rows(C.byref(none), None) == R
     # fused norm + requant
-    assert lib.fnb_rms_norm_q8_1(A16, A16, 1e-6, A16, None, 4, 2040, None) == R
-    assert lib.fnb_rms_norm_q8_0(A16, A16, 1e-6, None, None, 4, 2048, None) == R
-    assert lib.fnb_rms_norm_act(A16, A16, 1e-6, A16, None, None, 4, 2048, None) == R
-    assert lib.fnb_rms_norm_q8_1(A16, A16, 1e-6, A16, None, 4, 8192, None) == R
+    assert lib.fnb_rms_norm_q8_1(A16, A16, 1e-6, A16, None, 4, 2040, None, None) == R
+    assert lib.fnb_rms_norm_q8_0(A16, A16, 1e-6, None, None, 4, 2048, None, None) == R
+    assert lib.fnb_rms_norm_act(A16, A16, 1e-6, A16, None, None, 4, 2048, None, None) == R
+    assert lib.fnb_rms_norm_q8_1(A16, A16, 1e-6, A16, None, 4, 8192, None, None) == R
+    assert lib.fnb_rms_norm_q8_1(A16, A16, 1e-6, A16, None, 4, 2048, A16 + 2, None) == R

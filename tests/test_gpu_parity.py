@@ -785,36 +785,33 @@ def test_first_calls_can_be_captured_after_prepare_device(dev, oracle):
     assert r.returncode == 0 and "captured-first-call ok" in r.stdout, r.stdout + r.stderr
 
 
-def test_glu_fast_path_equals_generic_path_on_its_whole_domain(dev):
+def test_glu_fast_path_equals_generic_path_on_its_whole_domain(dev, selftest_lib):
     """2^28 pseudo-random (gate, up) pairs over |gate| in [2^-40, 64): the branch-free expf and the written-out
     division must give the same bits as the generic path (special-case aware expf, __fdiv_rn)."""
     import ctypes as C
-    from fnfl_v100_b200 import _lib
     bad = torch.zeros(1, dtype=torch.int64, device=dev)
-    st = _lib.lib().fnb_selftest_glu_math(1 << 28, 12345, C.c_void_p(bad.data_ptr()),
+    st = selftest_lib.fnbt_selftest_glu_math(1 << 28, 12345, C.c_void_p(bad.data_ptr()),
                                           C.c_void_p(torch.cuda.current_stream().cuda_stream))
     assert st == 0
     torch.cuda.synchronize()
     assert int(bad.item()) == 0
 
 
-def test_fused_expf_equals_the_definition_for_every_float(dev):
+def test_fused_expf_equals_the_definition_for_every_float(dev, selftest_lib):
     """All 2 x 0x42b00000 floats |x| < 88: the 8-operation evaluation rounds to the same float as the 12-operation one."""
     import ctypes as C
-    from fnfl_v100_b200 import _lib
     bad = torch.zeros(1, dtype=torch.int64, device=dev)
-    st = _lib.lib().fnb_selftest_expf(C.c_void_p(bad.data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    st = selftest_lib.fnbt_selftest_expf(C.c_void_p(bad.data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream))
     assert st == 0
     torch.cuda.synchronize()
     assert int(bad.item()) == 0
 
 
-def test_kv8_written_out_division_equals_ieee_division(dev):
+def test_kv8_written_out_division_equals_ieee_division(dev, selftest_lib):
     """Every positive finite FP16 scale x 2^27 pseudo-random values (half on exact half steps): same codes as __fdiv_rn."""
     import ctypes as C
-    from fnfl_v100_b200 import _lib
     bad = torch.zeros(1, dtype=torch.int64, device=dev)
-    st = _lib.lib().fnb_selftest_kv8_math(1 << 27, 777, C.c_void_p(bad.data_ptr()),
+    st = selftest_lib.fnbt_selftest_kv8_math(1 << 27, 777, C.c_void_p(bad.data_ptr()),
                                           C.c_void_p(torch.cuda.current_stream().cuda_stream))
     assert st == 0
     torch.cuda.synchronize()
