@@ -6,19 +6,32 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
         bench.py --gpus N --steps K --warmup W
 
-A step is one pass of the chain over T = 65536 tokens per GPU (weak scaling: every rank owns T token rows of a
-longer prompt; the path has no collective).  Rank 0 prints ONE JSON line:
-  value        whole-job tokens/s, inputs resident in HBM, CUDA events, max over ranks
-  ops          per fused op: ms per launch, effective GB/s (algorithmic bytes), fraction of the measured HBM peak
-  roofline     the dominant kernel (SwiGLU + Q8_1) against the measured HBM copy bandwidth
-  e2e          the same metric through the host-buffer pipeline (pinned host inputs in, results out, copies timed)
-  cpu_baseline the CPU oracle (a port of the reference's CPU definition) on a bounded sample, all host threads
-`--impl reference` times only that CPU path and prints the same line shape with "impl": "reference".
+The job is ONE prefill chunk of T = 65536 tokens.  With N GPUs it is partitioned by token rows: rank r holds rows
+shard.row_range(T, r, N) of every per-row tensor and appends its own range of cache cells; the table and the norm
+weights are replicated; the data path has no collective (strong scaling).  A step is one pass of the chain over the
+job, replayed from a CUDA graph of the rank's five launches.  Rank 0 prints ONE JSON line:
+
+  value         whole-job tokens/s: T x K / (device time of K graph replays, CUDA events, max over ranks)
+  step          median / p90 / mean of the K replays
+  ops           per fused op, replayed alone from its own graph: median / p90 / mean ms, GB/s of the algorithmic
+                bytes, fraction of the measured and of the nominal HBM peak.  At N = 1 also the configurations the
+                chain does not run at their stated sizes (get_rows IQ3_XXS at T, RoPE + KV at 4096 tokens with
+                random offsets, SwiGLU + Q8_1 at 40960 rows, RMSNorm at 512 rows), cold (inputs rotated over more
+                bytes than L2 holds) and hot
+  roofline      the dominant kernel (SwiGLU + Q8_1) against the measured HBM copy bandwidth
+  sustained     at least a second of back-to-back chain steps (outside value) with the clocks sampled meanwhile
+  e2e           the same metric through the host-buffer pipeline (pinned host inputs in, results out, copies timed),
+                and the same copies without the kernels (the ceiling the host link sets)
+  gather_ms,    N > 1: all-gather of the quantised outputs (Q8_1 activations, K / V cells), timed beside value; rank 0
+  shard_check   recomputes a sample of every other rank's rows and compares it with the gathered bytes
+  cpu_baseline  N = 1: the CPU oracle (a port of the reference's CPU definition) on a bounded sample, all host threads
+`--impl reference` times only that CPU path on the whole job and prints the same line shape with "impl": "reference".
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import subprocess
 import sys
@@ -28,9 +41,11 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-METRIC = "fused row-wise chain throughput at T=65536 tokens per GPU (per-op GB/s and fraction of HBM peak in ops)"
+METRIC = "fused row-wise chain throughput at T=65536 tokens (per-op GB/s and fraction of HBM peak in ops)"
 UNIT = "tokens/s"
 FALLBACK_HBM_GBS = 6650.0
+NOMINAL_HBM_GBS = 8000.0
+L2_BYTES = 126 * 1024 * 1024
 
 
 def hbm_peak():
@@ -50,16 +65,36 @@ def ncu_traffic(kernel: str):
         return None
 
 
+def job_config(args) -> dict:
+    """The workload, spelled identically by both arms."""
+    from fnfl_v100_b200.chain import ChainConfig
+    c = ChainConfig(tokens=args.tokens)
+    return {"workload": "fused-op chain of one prefill chunk: get_rows(Q4_K) -> RMSNorm -> Q/K head norm + NeoX RoPE + "
+                        "Q8_0 KV append -> RMSNorm -> SwiGLU + Q8_1",
+            "tokens": args.tokens, "hidden": c.hidden, "q_heads": c.n_q_heads, "kv_heads": c.n_kv_heads,
+            "head_dim": c.head_dim, "n_rot": c.n_rot, "experts_per_token": c.top_k, "expert_inter": c.inter,
+            "n_vocab": c.n_vocab, "cache_slots": c.cache_slots, "depth": c.depth, "shards": args.gpus,
+            "sharding": "contiguous token-row ranges, no collective on the data path",
+            "l2": "every step streams more than the 126 MB L2 per GPU between two launches of the same kernel; "
+                  "no flush needed"}
+
+
+def stats(ms: list) -> dict:
+    s = sorted(ms)
+    n = len(s)
+    return {"median_ms": s[n // 2] if n % 2 else 0.5 * (s[n // 2 - 1] + s[n // 2]),
+            "p90_ms": s[min(n - 1, int(math.ceil(0.9 * n)) - 1)], "mean_ms": sum(s) / n, "min_ms": s[0], "n": n}
+
+
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi.  It is started before the warm-up steps
-    (nvidia-smi takes tens of milliseconds to produce its first line); the samples that arrive between begin() and
-    end() are the timed region's.  A region shorter than the sampling period falls back to the samples taken while
-    the same kernels were running in warm-up, and says so in `window`."""
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi (read-only queries) from before the warm-up
+    on; window(t0, t1) summarises the samples taken inside a wall-clock window.  A window shorter than the sampling
+    period falls back to every sample taken so far, and says so."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap,power.draw")
 
     def __init__(self, index: int):
-        self.rows, self.proc, self.t0, self.t1 = [], None, None, None
+        self.rows, self.proc = [], None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.Q,
                                           "--format=csv,noheader,nounits", "-lms", "10"],
@@ -73,61 +108,64 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
 
-    def begin(self):
-        self.t0 = time.time()
-
-    def end(self):
-        self.t1 = time.time()
-
-    def stop(self) -> dict:
+    def window(self, t0: float, t1: float) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
-        time.sleep(0.03)  # let the line that was sampled during the region arrive
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            pass
-        ok = [(t, r) for t, r in self.rows if len(r) >= 6 and r[0].isdigit()]
-        inside = [r for t, r in ok if self.t0 is not None and self.t0 <= t <= (self.t1 or t) + 0.02]
-        window = "timed region"
+        time.sleep(0.03)  # let the line that was sampled during the window arrive
+        ok = [(t, r) for t, r in list(self.rows) if len(r) >= 6 and r[0].isdigit()]
+        inside, where = [r for t, r in ok if t0 <= t <= t1 + 0.02], "the window itself"
         if not inside:
-            inside, window = [r for t, r in ok if self.t0 is None or t <= (self.t1 or t) + 0.02], "warm-up + timed region"
+            inside, where = [r for t, r in ok if t <= t1 + 0.02], "everything sampled up to the window's end"
         sm = sorted(int(r[0]) for r in inside)
         mx = [int(r[1]) for r in inside if r[1].isdigit()]
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         reasons = sorted({n for r in inside for n, v in zip(names, r[2:6]) if v.lower() == "active"})
+        watts = [float(r[6]) for r in inside if len(r) > 6 and r[6].replace(".", "", 1).isdigit()]
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(sm), "window": window}
+                "reasons": reasons, "samples": len(sm), "window": where,
+                "power_w_max": max(watts) if watts else None}
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
 
 
 # ---- the CPU arm ---------------------------------------------------------------------------------------------
 
 class CpuChain:
-    """The oracle's chain on `tokens` tokens (full row widths), rows split over host threads."""
+    """The oracle's chain on rows [0, tokens) of the job (full row widths, the full table), rows split over host
+    threads.  Inputs are the job's own counter-based rows, generated on the host."""
 
     def __init__(self, tokens: int, libm: bool = True):
         import ctypes as C
         import numpy as np
+        import torch
         from fnfl_v100_b200 import synth
         from fnfl_v100_b200.chain import ChainConfig
         from oracle import oracle as O
         O.use_libm(libm)
         self.O, self.C, self.tokens = O, C, tokens
         c = self.c = ChainConfig(tokens=tokens)
-        g = synth.rng(5)
-        self.vocab = 4096                               # rows actually touched; the decode cost per row is the same
+        g = synth.rng(c.seed_case)
+        seed = synth.SEED_BASE + c.seed_case
+        self.vocab = c.n_vocab
         self.table = synth.q4_k_table(g, self.vocab, c.hidden)
-        self.ids = g.integers(0, self.vocab, tokens).astype(np.int32)
         self.w1, self.w2 = synth.norm_weight(g, c.hidden), synth.norm_weight(g, c.hidden)
         self.wq, self.wk = synth.norm_weight(g, c.head_dim), synth.norm_weight(g, c.head_dim)
-        self.q = synth.normal(g, (tokens, c.n_q_heads, c.head_dim))
-        self.k = synth.normal(g, (tokens, c.n_kv_heads, c.head_dim))
-        self.v = synth.normal(g, (tokens, c.n_kv_heads, c.head_dim))
-        self.gate = synth.normal(g, (tokens * c.top_k, c.inter), 0.5)
-        self.up = synth.normal(g, (tokens * c.top_k, c.inter), 0.5)
+        torch.set_num_threads(os.cpu_count() or 1)
+        N = lambda sid, rows, cols, sc: synth.counter_normal(seed, sid, 0, rows, cols, sc, "cpu").numpy()  # noqa: E731
+        self.ids = synth.counter_ids(seed, 0, 0, tokens, c.n_vocab, "cpu").numpy()
+        self.q = N(1, tokens, c.n_q_heads * c.head_dim, 1.0).reshape(tokens, c.n_q_heads, c.head_dim)
+        self.k = N(2, tokens, c.n_kv_heads * c.head_dim, 1.0).reshape(tokens, c.n_kv_heads, c.head_dim)
+        self.v = N(3, tokens, c.n_kv_heads * c.head_dim, 1.0).reshape(tokens, c.n_kv_heads, c.head_dim)
+        self.gate = N(4, tokens * c.top_k, c.inter, 0.5)
+        self.up = N(5, tokens * c.top_k, c.inter, 0.5)
         self.pos = (c.depth + np.arange(tokens)).astype(np.int32)
-        self.slot = np.arange(tokens).astype(np.int32)
+        self.slot = np.arange(tokens).astype(np.int32)          # a cache of `tokens` cells: the cells this job appends
         self.ts = O.theta_scale(c.freq_base, c.n_rot)
         self.kc = np.zeros((tokens, c.n_kv_heads, 272), np.uint8)
         self.vc = np.zeros_like(self.kc)
@@ -161,22 +199,18 @@ class CpuChain:
         return time.perf_counter() - t0
 
 
-def _cpu_sample_size(threads: int, target_s: float, cap: int) -> int:
-    probe = CpuChain(256)
-    probe.run(threads)
-    per_tok = probe.run(threads) / 256
-    n = int(min(cap, max(256, target_s / per_tok)))
-    return n - n % 64
+CPU_BUILD = "oracle built -O3 -ffp-contract=off (no -march=native), host libm expf / sinf / cosf"
 
 
-def cpu_baseline(threads: int) -> dict:
-    sample = _cpu_sample_size(threads, 1.0, 16384)
+def cpu_baseline(threads: int, job_tokens: int) -> dict:
+    """A bounded sample (about 10-30 s of CPU work with its set-up) of the same job on all host threads."""
+    sample = min(16384, job_tokens)
     ch = CpuChain(sample)
     ch.run(threads)
     best = min(ch.run(threads) for _ in range(5))
     return {"value": sample / best, "unit": UNIT, "cores": threads, "kind": "port",
-            "sample": f"{sample} tokens of the same chain (full row widths), best of 5 passes ({best:.3f} s); "
-                      "oracle built -O2 -ffp-contract=off, host libm expf/sinf/cosf, rows split over host threads"}
+            "sample": f"rows [0, {sample}) of the job (full row widths, the full {ch.vocab}-row table), best of 5 "
+                      f"passes ({best:.3f} s); {CPU_BUILD}, rows split over {threads} host threads"}
 
 
 def run_reference(args) -> None:
@@ -187,19 +221,20 @@ def run_reference(args) -> None:
     if not os.path.exists(O.ORACLE_SO):
         O.build(with_ref=False)
     threads = os.cpu_count() or 1
-    sample = _cpu_sample_size(threads, 1.0, 16384)
-    ch = CpuChain(sample)
-    for _ in range(args.warmup):
+    T = args.tokens
+    ch = CpuChain(T)
+    for _ in range(max(1, args.warmup)):
         ch.run(threads)
-    dt = sum(ch.run(threads) for _ in range(args.steps))
-    tps = sample * args.steps / dt
-    desc = (f"{sample} tokens per step of the same chain on the host cores (the reference has no CPU code for the "
-            "whole path in its tree: this is the oracle port, -O2 -ffp-contract=off, host libm)")
+    dts = [ch.run(threads) for _ in range(args.steps)]
+    dt = sum(dts)
+    tps = T * args.steps / dt
+    desc = (f"the whole job ({T} tokens) per step on {threads} host threads; the reference ships no CPU code for the "
+            f"whole path, so this is the oracle port: {CPU_BUILD}")
     emit({
         "impl": "reference", "metric": METRIC, "value": tps, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded)",
-        "config": {"workload": "fused-op chain, hidden 2048, 16 Q / 2 KV heads x 256, 10 experts x 512", "sample": desc},
+        "warmup": max(1, args.warmup), "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded, counter-based rows)",
+        "config": job_config(args), "step": stats([d * 1e3 for d in dts]),
         "cpu_baseline": {"value": tps, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
         "e2e": {"value": tps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -208,10 +243,128 @@ def run_reference(args) -> None:
 
 # ---- the GPU arm -----------------------------------------------------------------------------------------------
 
+def capture(fn):
+    """`fn` (launches only, no allocation) recorded into a CUDA graph; one warm call first."""
+    import torch
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        fn()
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    return g
+
+
+def time_replays(graphs: list, k: int, warm: int = 3) -> list:
+    """ms of each of k replays (graphs taken in turn), an event on either side of every replay."""
+    import torch
+    cur = torch.cuda.current_stream()
+    for i in range(max(warm, len(graphs))):
+        graphs[i % len(graphs)].replay()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(k + 1)]
+    torch.cuda.synchronize()
+    ev[0].record(cur)
+    for i in range(k):
+        graphs[i % len(graphs)].replay()
+        ev[i + 1].record(cur)
+    torch.cuda.synchronize()
+    return [ev[i].elapsed_time(ev[i + 1]) for i in range(k)]
+
+
+def op_report(ms: list, nbytes: int, peak: float) -> dict:
+    st = stats(ms)
+    gbs = nbytes / (st["median_ms"] * 1e-3) / 1e9
+    return {"median_ms": round(st["median_ms"], 5), "p90_ms": round(st["p90_ms"], 5), "mean_ms": round(st["mean_ms"], 5),
+            "bytes": nbytes, "gbs": round(gbs, 1), "frac_of_measured_peak": round(gbs / peak, 4),
+            "frac_of_nominal_8tbs": round(gbs / NOMINAL_HBM_GBS, 4)}
+
+
+def extra_configs(dev, k: int, peak: float) -> dict:
+    """The stated configurations the chain does not run at their own sizes, each replayed from graphs: cold (instances
+    rotated so that more bytes than L2 holds pass between two replays of one instance) and hot (one instance)."""
+    import torch
+    from fnfl_v100_b200 import ops, synth
+    from fnfl_v100_b200.chain import ChainConfig
+    c = ChainConfig()
+    out = {}
+
+    def rotate(make, nbytes: int):
+        n_inst = max(2, int(math.ceil(2.5 * L2_BYTES / nbytes)))
+        return [make(i) for i in range(n_inst)], n_inst
+
+    def both(name, make, nbytes, note):
+        fns, n_inst = rotate(make, nbytes)
+        graphs = [capture(f) for f in fns]
+        r = {"cold": op_report(time_replays(graphs, k), nbytes, peak), "hot": op_report(time_replays(graphs[:1], k), nbytes, peak),
+             "instances_rotated": n_inst, "what": note}
+        out[name] = r
+
+    seed = synth.SEED_BASE
+    # configuration 4, the other table format, at T = 65536 (one launch streams 589 MB: cold by construction)
+    gen = synth.torch_gen(dev, 4)
+    T = 65536
+    table = synth.torch_table("iq3_xxs", gen, c.n_vocab, c.hidden, dev)
+    ids = synth.counter_ids(seed + 4, 0, 0, T, c.n_vocab, dev)
+    rows_out = torch.empty((T, c.hidden), dtype=torch.float32, device=dev)
+    err = ops.new_err(dev)
+    nb = T * (ops.table_row_bytes("iq3_xxs", c.hidden) + 4 + c.hidden * 4)
+    g = capture(lambda: ops.get_rows("iq3_xxs", table, ids, c.hidden, out=rows_out, err=err))
+    out["get_rows_iq3_xxs_T65536"] = {"cold": op_report(time_replays([g], k), nb, peak),
+                                      "what": "configuration 4, IQ3_XXS table [151936][2048], 65536 uniform ids"}
+    del table, rows_out, g
+
+    # configuration 2: 4096 tokens, positions = offset ~ U[0, 258048) + t, cache of 262144 slots
+    T2 = 4096
+    kc, vc = ops.new_kv_cache(c.cache_slots, c.n_kv_heads, c.head_dim, dev), ops.new_kv_cache(c.cache_slots, c.n_kv_heads, c.head_dim, dev)
+    ts = ops.theta_scale(c.freq_base, c.n_rot)
+    rg = synth.rng(2)
+
+    def make_rope(i):
+        q = synth.counter_normal(seed + 2, 10 + 3 * i, 0, T2, c.n_q_heads * c.head_dim, 1.0, dev).view(T2, c.n_q_heads, c.head_dim)
+        kk = synth.counter_normal(seed + 2, 11 + 3 * i, 0, T2, c.n_kv_heads * c.head_dim, 1.0, dev).view(T2, c.n_kv_heads, c.head_dim)
+        v = synth.counter_normal(seed + 2, 12 + 3 * i, 0, T2, c.n_kv_heads * c.head_dim, 1.0, dev).view(T2, c.n_kv_heads, c.head_dim)
+        pos = torch.from_numpy(synth.positions(rg, T2)).to(dev)
+        q_out = torch.empty_like(q)
+        return lambda: ops.rope_neox_q8_0_append(q, kk, v, pos, n_rot=c.n_rot, theta_scale=ts, k_cache=kc, v_cache=vc,
+                                                 q_out=q_out, err=err)
+    cell = c.head_dim // 32 * ops.Q8_0_BLOCK
+    nb2 = T2 * (2 * c.n_q_heads * c.head_dim * 4 + 2 * c.n_kv_heads * c.head_dim * 4 + 2 * c.n_kv_heads * cell + 4)
+    both("rope_kv_q8_0_T4096", make_rope, nb2, "configuration 2: Q [4096][16][256], K / V [4096][2][256], no head norm, "
+                                               "offsets U[0, 258048)")
+
+    # configuration 3: 40960 rows of 512
+    R3 = 40960
+
+    def make_glu(i):
+        gate = synth.counter_normal(seed + 3, 2 * i, 0, R3, c.inter, 0.5, dev)
+        up = synth.counter_normal(seed + 3, 2 * i + 1, 0, R3, c.inter, 0.5, dev)
+        act = torch.empty((R3, c.inter // 32 * ops.Q8_1_BLOCK), dtype=torch.uint8, device=dev)
+        return lambda: ops.swiglu_q8_1(gate, up, out=act, err=err)
+    both("swiglu_q8_1_R40960", make_glu, R3 * (2 * c.inter * 4 + c.inter // 32 * ops.Q8_1_BLOCK),
+         "configuration 3: gate, up [40960][512]")
+
+    # configuration 1: 512 rows of 2048 (plumbing size: launch-bound)
+    R1 = 512
+    w = 1.0 + 0.1 * synth.counter_normal(seed + 1, 0, 0, 1, c.hidden, 1.0, dev).view(-1)
+
+    def make_norm(i):
+        x = synth.counter_normal(seed + 1, 1 + i, 0, R1, c.hidden, 1.0, dev)
+        y = torch.empty_like(x)
+        return lambda: ops.rms_norm(x, w, c.eps, out=y)
+    both("rms_norm_R512", make_norm, 2 * R1 * c.hidden * 4 + c.hidden * 4, "configuration 1: x [512][2048]")
+    if int(err.item()) != 0:
+        raise RuntimeError("device error word %d in the extra configurations" % int(err.item()))
+    return out
+
+
 def run_ours(args) -> None:
     import torch
     import torch.distributed as dist
     import fnfl_v100_b200 as fnb
+    from fnfl_v100_b200 import ops, shard
     from fnfl_v100_b200.chain import ChainConfig, PrefillChain
     from fnfl_v100_b200.host_pipeline import HostChunkPipeline
 
@@ -225,8 +378,7 @@ def run_ours(args) -> None:
     dev = torch.device("cuda", local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # rank 0 prints exactly one JSON line on stdout: whatever NCCL logs (its version banner at the VERSION and
-        # WARN levels, everything at INFO) goes to stderr
+        # rank 0 prints exactly one JSON line on stdout: whatever NCCL logs goes to stderr
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
 
@@ -235,115 +387,243 @@ def run_ours(args) -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    def max_over_ranks(values: list) -> list:
+        t = torch.tensor(values, dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(x) for x in t]
+
     T = args.tokens
-    cfg = ChainConfig(tokens=T)
-    chain = PrefillChain(cfg, dev, first_token=0)
+    lo, hi = shard.row_range(T, rank, world)
+    Tl = hi - lo
+    cfg = ChainConfig(tokens=Tl)
+    sampler = ClockSampler(local) if rank == 0 else None
+    ops.prepare_device()
+    chain = PrefillChain(cfg, dev, first_token=lo)
     bpt = cfg.bytes_per_token()
     stages = PrefillChain.STAGES
     peak, peak_kind = hbm_peak()
-
-    sampler = ClockSampler(local) if rank == 0 else None
-    for _ in range(max(args.warmup, 3)):
-        chain.step()
-    barrier()
-    K = args.steps
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(stages) + 1)] for _ in range(K)]
     cur = torch.cuda.current_stream()
+    W, K = max(args.warmup, 3), args.steps
+
+    # ---- the timed region: K replays of the step graph ----
+    step_graph = chain.capture()
+    for _ in range(W):
+        step_graph.replay()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(K + 1)]
     barrier()
-    if sampler:
-        sampler.begin()
-    for k in range(K):
-        ev[k][0].record(cur)
-        for i, name in enumerate(stages):
-            getattr(chain, name)()
-            ev[k][i + 1].record(cur)
+    t_begin = time.time()
+    ev[0].record(cur)
+    for i in range(K):
+        step_graph.replay()
+        ev[i + 1].record(cur)
     barrier()
-    if sampler:
-        sampler.end()
-    total_ms = ev[0][0].elapsed_time(ev[K - 1][len(stages)])
-    stage_ms = [sum(ev[k][i].elapsed_time(ev[k][i + 1]) for k in range(K)) / K for i in range(len(stages))]
-    clocks = sampler.stop() if sampler else None
+    t_end = time.time()
+    total_ms = ev[0].elapsed_time(ev[K])
+    step_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(K)]
+    clocks = sampler.window(t_begin, t_end) if sampler else None
     if int(chain.err.item()) != 0:
         raise SystemExit("bench.py: the chain reported a device error word of %d" % int(chain.err.item()))
+    total_ms, = max_over_ranks([total_ms])
+    step_stats = stats(step_ms)
+    step_stats = dict(zip(step_stats, max_over_ranks([float(v) for v in step_stats.values()])))
 
-    t = torch.tensor([total_ms] + stage_ms, dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, stage_ms = float(t[0]), [float(x) for x in t[1:]]
+    # ---- every stage alone, replayed from its own graph ----
+    stage_ms = {}
+    for name in stages:
+        g = capture(getattr(chain, name))
+        stage_ms[name] = time_replays([g], K, W)
+        del g
+    flat = max_over_ranks([v for name in stages for v in (stats(stage_ms[name])["median_ms"], stats(stage_ms[name])["p90_ms"],
+                                                          stats(stage_ms[name])["mean_ms"])])
+    ops_report = {}
+    for i, name in enumerate(stages):
+        med, p90, mean = flat[3 * i:3 * i + 3]
+        nbytes = bpt[name] * math.ceil(T / world)            # the largest shard's bytes against the slowest rank's time
+        gbs = nbytes / (med * 1e-3) / 1e9
+        ops_report[name] = {"median_ms": round(med, 5), "p90_ms": round(p90, 5), "mean_ms": round(mean, 5),
+                            "bytes": nbytes, "gbs": round(gbs, 1), "frac_of_measured_peak": round(gbs / peak, 4),
+                            "frac_of_nominal_8tbs": round(gbs / NOMINAL_HBM_GBS, 4),
+                            "l2": "cold: one launch streams more than twice the L2" if nbytes > 2 * L2_BYTES else
+                                  "the launch's bytes could partly sit in L2 between replays"}
 
-    # end to end from pinned host memory (chunks of 8192 tokens over three streams)
-    e2e_steps = max(1, min(args.e2e_steps, K))
+    # ---- sustained: at least a second of back-to-back steps, stage events on the last hundred ----
+    n_sus = max(100, int(math.ceil(args.sustain_s * 1e3 / (total_ms / K)))) if args.sustain_s > 0 else 0
+    n_ev = min(100, n_sus)
+    sev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(stages) + 1)] for _ in range(n_ev)]
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    ts0 = time.time()
+    s0.record(cur)
+    for i in range(n_sus):
+        j = i - (n_sus - n_ev)
+        if j < 0:
+            step_graph.replay()
+            continue
+        sev[j][0].record(cur)
+        for si, name in enumerate(stages):
+            getattr(chain, name)()
+            sev[j][si + 1].record(cur)
+    s1.record(cur)
+    torch.cuda.synchronize()
+    ts1 = time.time()
+    sus_clocks = sampler.window(ts0 + 0.5 * (ts1 - ts0), ts1) if sampler else None
+    sustained = None
+    if rank == 0 and n_sus > 0:
+        mhz = (sus_clocks or {}).get("sm_mhz")
+        per = {}
+        for si, name in enumerate(stages):
+            ms = stats([sev[j][si].elapsed_time(sev[j][si + 1]) for j in range(n_ev)])["median_ms"]
+            gbs = bpt[name] * Tl / (ms * 1e-3) / 1e9
+            per[name] = {"median_ms": round(ms, 5), "gbs": round(gbs, 1), "frac_of_measured_peak": round(gbs / peak, 4),
+                         "ms_x_sm_mhz": round(ms * mhz, 2) if mhz else None}
+        sustained = {"steps": n_sus, "seconds": round(s0.elapsed_time(s1) * 1e-3, 3),
+                     "ms_per_step": round(s0.elapsed_time(s1) / n_sus, 5),
+                     "stages_last_%d_steps" % n_ev: per, "clocks_second_half": sus_clocks,
+                     "note": "rank 0's shard; graph replays, then eager launches with an event between stages"}
+
+    # ---- the stated configurations the chain does not run at their own sizes (one GPU only) ----
+    extras = None
+    if world == 1 and not args.no_extras:
+        try:
+            extras = extra_configs(dev, K, peak)
+        except Exception as e:  # the headline does not depend on them
+            extras = {"error": repr(e)}
+
+    # ---- end to end from pinned host memory ----
     e2e = None
     if not args.no_e2e:
-        pipe = HostChunkPipeline(cfg, dev, chunk=min(8192, T), source=chain)
-        pipe.step()
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(cur)
-        for _ in range(e2e_steps):
-            pipe.step()
-        e1.record(cur)
-        barrier()
-        e2e_ms = torch.tensor([e0.elapsed_time(e1) / e2e_steps], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
-        e2e_ms = float(e2e_ms)
+        chunk = min(8192, max(256, (Tl // 4) // 256 * 256))
+        while Tl % chunk != 0:
+            chunk //= 2
+        pipe = HostChunkPipeline(cfg, dev, chunk=chunk, source=chain)
+        e2e_steps = max(1, min(args.e2e_steps, K))
+
+        def timed(fn, n):
+            fn()
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(cur)
+            for _ in range(n):
+                fn()
+            b.record(cur)
+            barrier()
+            return max_over_ranks([a.elapsed_time(b) / n])[0]
+
+        e2e_ms = timed(pipe.step, e2e_steps)
+        copy_ms = timed(lambda: pipe.step(copies_only=True), e2e_steps)
         if int(pipe.h_err.item()) != 0:
             raise SystemExit("bench.py: the host pipeline reported a device error word of %d" % int(pipe.h_err.item()))
-        e2e = {"value": T * world / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": pipe.h2d_bytes,
-               "d2h_bytes_per_step": pipe.d2h_bytes, "ms_per_step": e2e_ms, "chunk_tokens": pipe.chunk,
-               "launches_per_step": pipe.launches_per_step}
+        h2d, d2h = max_over_ranks([float(pipe.h2d_bytes), float(pipe.d2h_bytes)])
+        e2e = {"value": T / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+               "bytes_are": "per GPU (the largest shard)", "ms_per_step": e2e_ms, "chunk_tokens": pipe.chunk,
+               "launches_per_step": pipe.launches_per_step * world,
+               "copies_only_ms_per_step": copy_ms, "copies_only_value": T / (copy_ms * 1e-3),
+               "frac_of_copies_only": copy_ms / e2e_ms,
+               "host_link_gbs_per_gpu": (h2d + d2h) / (copy_ms * 1e-3) / 1e9}
+        del pipe
 
-    # optional final gather of the quantised outputs over NVLink (not part of the timed chain)
-    gather_ms = None
-    if world > 1 and args.gather:
-        from fnfl_v100_b200 import shard
+    # ---- N > 1: gather of the quantised outputs, timed beside value, and the cross-rank check ----
+    gather_ms, shard_check = None, None
+    if world > 1:
+        k_cells, v_cells = chain.kv_cells()
         g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        full_act = shard.gather_rows(chain.act, T * cfg.top_k)       # warm (communicator set-up)
+        del full_act
         barrier()
         g0.record(cur)
-        full = shard.gather_rows(chain.act, T * cfg.top_k * world)
+        full_act = shard.gather_rows(chain.act, T * cfg.top_k)
+        full_k = shard.gather_rows(k_cells, T)
+        full_v = shard.gather_rows(v_cells, T)
         g1.record(cur)
         barrier()
-        gather_ms = g0.elapsed_time(g1)
-        del full
+        gather_ms, = max_over_ranks([g0.elapsed_time(g1)])
+        if rank == 0:
+            n_check, bad, checked = 256, 0, 0
+            for r in range(1, world):
+                rlo, rhi = shard.row_range(T, r, world)
+                n = min(n_check, rhi - rlo)
+                s = rlo + (rhi - rlo - n) // 2
+                part = PrefillChain(ChainConfig(tokens=n), dev, first_token=s, shared=chain)
+                part.step()
+                torch.cuda.synchronize()
+                pk, pv = part.kv_cells()
+                bad += int((part.act != full_act[s * cfg.top_k:(s + n) * cfg.top_k]).sum())
+                bad += int((pk != full_k[s:s + n]).sum()) + int((pv != full_v[s:s + n]).sum())
+                bad += int(part.err.item() != 0)
+                checked += n
+            shard_check = {"mismatches": bad, "rows_checked": checked,
+                           "what": "rank 0 regenerates %d rows from the middle of every other rank's range, runs the chain "
+                                   "on them and compares Q8_1 bytes and K / V cells with the gathered ones" % n_check}
+        gathered_bytes = int(full_act.numel() + full_k.numel() + full_v.numel())
+        del full_act, full_k, full_v
+
+    # ---- N > 1: the replicated form (every rank the whole job), for comparison with earlier records ----
+    replicas = None
+    if world > 1 and not args.no_replicas:
+        del chain, step_graph
+        torch.cuda.empty_cache()
+        rep = PrefillChain(ChainConfig(tokens=T), dev, first_token=0)
+        rg = rep.capture()
+        for _ in range(W):
+            rg.replay()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        a.record(cur)
+        for _ in range(K):
+            rg.replay()
+        b.record(cur)
+        barrier()
+        rep_ms, = max_over_ranks([a.elapsed_time(b)])
+        replicas = {"value": T * world * K / (rep_ms * 1e-3), "unit": UNIT, "tokens_per_gpu": T, "ms_per_step": rep_ms / K,
+                    "note": "REPLICAS, not a partition: every rank runs the whole job on its own copy (weak scaling); "
+                            "not the headline"}
 
     if rank == 0:
-        ops_report = {}
-        for name, ms in zip(stages, stage_ms):
-            gbs = bpt[name] * T / (ms * 1e-3) / 1e9
-            ops_report[name] = {"ms": round(ms, 4), "gbs": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak, 4),
-                                "bytes": bpt[name] * T}
         dom = "swiglu_q8_1"
-        dom_bytes = bpt[dom] * T
-        dom_ms = stage_ms[stages.index(dom)]
-        achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
+        dom_bytes = ops_report[dom]["bytes"]
+        achieved = dom_bytes / (ops_report[dom]["mean_ms"] * 1e-3) / 1e9
         traffic = ncu_traffic("glu_quant_kernel")
+        chain_bytes = sum(bpt.values()) * T
+        ms_per_step = total_ms / K
         line = {
-            "metric": METRIC, "value": T * world * K / (total_ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K,
-            "warmup": max(args.warmup, 3), "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded)",
-            "config": {"workload": "fused-op chain: get_rows(Q4_K) -> RMSNorm -> Q/K head norm + NeoX RoPE + Q8_0 KV "
-                                   "append -> RMSNorm -> SwiGLU + Q8_1",
-                       "tokens_per_gpu": T, "hidden": cfg.hidden, "q_heads": cfg.n_q_heads, "kv_heads": cfg.n_kv_heads,
-                       "head_dim": cfg.head_dim, "n_rot": cfg.n_rot, "experts_per_token": cfg.top_k,
-                       "expert_inter": cfg.inter, "n_vocab": cfg.n_vocab, "cache_slots": cfg.cache_slots,
-                       "depth": cfg.depth, "sharding": f"token rows, {world} shard(s), no collective",
-                       "l2": "every stage streams more than the 126 MB L2 per launch; no flush needed"},
-            "chain_gbs": sum(bpt.values()) * T / (total_ms / K * 1e-3) / 1e9,
-            "chain_frac_of_hbm_peak": sum(bpt.values()) * T / (total_ms / K * 1e-3) / 1e9 / peak,
+            "metric": METRIC, "value": T * K / (total_ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K,
+            "warmup": W, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded, counter-based rows)",
+            "config": job_config(args),
+            "tokens_per_gpu": math.ceil(T / world),
+            "timing": "CUDA-graph replays (%d warm, %d timed), CUDA events on the launching stream, max over ranks" % (W, K),
+            "step": {k: round(v, 5) for k, v in step_stats.items()},
+            "chain_gbs": chain_bytes / (ms_per_step * 1e-3) / 1e9,
+            "chain_frac_of_measured_peak_x_gpus": chain_bytes / (ms_per_step * 1e-3) / 1e9 / (peak * world),
+            "chain_frac_of_nominal_8tbs_x_gpus": chain_bytes / (ms_per_step * 1e-3) / 1e9 / (NOMINAL_HBM_GBS * world),
             "ops": ops_report,
+            "configs": extras,
             "roofline": {"kernel": "glu_quant_kernel (SwiGLU + Q8_1)", "bound": "hbm", "achieved": achieved,
                          "peak": peak, "peak_source": peak_kind, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": traffic, "algorithmic_bytes": dom_bytes},
+                         "frac_of_nominal_8tbs": achieved / NOMINAL_HBM_GBS,
+                         "traffic": traffic * dom_bytes / (bpt[dom] * 65536) if traffic else None,
+                         "algorithmic_bytes": dom_bytes,
+                         "how": "mean of the kernel's %d graph replays alone (ops.swiglu_q8_1.mean_ms); its time inside a "
+                                "long run of the chain is sustained.stages_*.swiglu_q8_1" % K},
+            "sustained": sustained,
             "e2e": e2e,
             "gpu_launches": 5 * K * world,
             "clocks": clocks,
         }
-        if gather_ms is not None:
+        if world > 1:
             line["gather_ms"] = gather_ms
+            line["gather_bytes"] = gathered_bytes
+            line["shard_check"] = shard_check
+            line["replicas"] = replicas
         if world == 1 and not args.no_cpu:
-            line["cpu_baseline"] = cpu_baseline(os.cpu_count() or 1)
+            try:
+                line["cpu_baseline"] = cpu_baseline(os.cpu_count() or 1, T)
+            except Exception as e:
+                line["cpu_baseline"] = {"error": repr(e)}
         emit(line)
+    if sampler:
+        sampler.stop()
     if world > 1:
         dist.destroy_process_group()
 
@@ -375,13 +655,15 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--tokens", type=int, default=65536, help="token rows per GPU")
+    ap.add_argument("--warmup", type=int, default=3, help="warm-up steps (at least 3 are run)")
+    ap.add_argument("--tokens", type=int, default=65536, help="token rows of the whole job (partitioned over the GPUs)")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--e2e-steps", type=int, default=3)
-    ap.add_argument("--gather", action="store_true", help="also time an all-gather of the Q8_1 outputs (N > 1)")
+    ap.add_argument("--sustain-s", type=float, default=1.2, help="length of the sustained leg in seconds (0: skip it)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler runs)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the stated configurations outside the chain")
+    ap.add_argument("--no-replicas", action="store_true", help="N > 1: skip the replicated (weak) form")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

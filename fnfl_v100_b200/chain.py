@@ -9,6 +9,11 @@ Only get_rows -> RMSNorm is truly chained; the tensors a dense product would pro
 seeded synthetic inputs, because contractions are outside this path.  Five launches per step, no host
 synchronisation, no allocation after construction, so a step can be captured in a CUDA graph and replayed,
 which is how the reference's prompt path replays its unit graphs.
+
+Sharding: a chain object holds rows [first_token, first_token + tokens) of ONE job.  Per-row inputs (ids, q, k, v,
+gate, up) are counter-based functions of the job's row index (synth.counter_*), positions are depth + row and the
+cache cell of a row is its position, so shards of a job compute exactly the rows the unsharded job computes and
+append disjoint cell ranges; the small shared state (table, norm weights) is generated from one seed on every GPU.
 """
 from __future__ import annotations
 
@@ -21,7 +26,7 @@ from . import ops, synth
 
 @dataclass
 class ChainConfig:
-    tokens: int = 65536          # rows of this GPU's shard
+    tokens: int = 65536          # rows this object holds (the whole job, or one shard of it)
     hidden: int = 2048
     n_q_heads: int = 16
     n_kv_heads: int = 2
@@ -55,31 +60,46 @@ class PrefillChain:
 
     STAGES = ("get_rows", "rms_norm_attn", "rope_kv", "rms_norm_ffn", "swiglu_q8_1")
 
-    def __init__(self, cfg: ChainConfig, device, first_token: int = 0):
+    SHARED = ("table", "w_attn", "w_ffn", "w_q", "w_k")   # replicated on every GPU
+
+    def __init__(self, cfg: ChainConfig, device, first_token: int = 0, shared: "PrefillChain | None" = None):
+        """rows [first_token, first_token + cfg.tokens) of the job; `shared` lends its table and norm weights (a
+        second shard on the same GPU) instead of generating them again."""
         self.cfg, self.device = cfg, torch.device(device)
         c, dev, T = cfg, self.device, cfg.tokens
-        gen = synth.torch_gen(dev, c.seed_case)
-        self.table = synth.torch_table(c.table_fmt, gen, c.n_vocab, c.hidden, dev)
-        self.ids = torch.randint(0, c.n_vocab, (T,), dtype=torch.int32, device=dev, generator=gen)
-        # positions are contiguous per shard: depth + the shard's first token + t
+        self.first_token = first_token
+        if shared is None:
+            # state every shard replicates: one seed, the same bits on every GPU of one model
+            gen = synth.torch_gen(dev, c.seed_case)
+            self.table = synth.torch_table(c.table_fmt, gen, c.n_vocab, c.hidden, dev)
+            self.w_attn = 1.0 + 0.1 * synth.torch_normal(gen, (c.hidden,), 1.0, dev)
+            self.w_ffn = 1.0 + 0.1 * synth.torch_normal(gen, (c.hidden,), 1.0, dev)
+            self.w_q = 1.0 + 0.1 * synth.torch_normal(gen, (c.head_dim,), 1.0, dev)
+            self.w_k = 1.0 + 0.1 * synth.torch_normal(gen, (c.head_dim,), 1.0, dev)
+        else:
+            for n in self.SHARED:
+                setattr(self, n, getattr(shared, n))
+        # per-row inputs: functions of the job's row index, so any shard regenerates exactly its rows
+        seed, lo, hi = synth.SEED_BASE + c.seed_case, first_token, first_token + T
+        self.ids = synth.counter_ids(seed, 0, lo, hi, c.n_vocab, dev)
         self.pos = (c.depth + first_token + torch.arange(T, device=dev, dtype=torch.int64)).to(torch.int32)
-        self.w_attn = 1.0 + 0.1 * synth.torch_normal(gen, (c.hidden,), 1.0, dev)
-        self.w_ffn = 1.0 + 0.1 * synth.torch_normal(gen, (c.hidden,), 1.0, dev)
-        self.w_q = 1.0 + 0.1 * synth.torch_normal(gen, (c.head_dim,), 1.0, dev)
-        self.w_k = 1.0 + 0.1 * synth.torch_normal(gen, (c.head_dim,), 1.0, dev)
-        self.q = synth.torch_normal(gen, (T, c.n_q_heads, c.head_dim), 1.0, dev)
-        self.k = synth.torch_normal(gen, (T, c.n_kv_heads, c.head_dim), 1.0, dev)
-        self.v = synth.torch_normal(gen, (T, c.n_kv_heads, c.head_dim), 1.0, dev)
-        self.gate = synth.torch_normal(gen, (T * c.top_k, c.inter), 0.5, dev)
-        self.up = synth.torch_normal(gen, (T * c.top_k, c.inter), 0.5, dev)
+        qw, kw = c.n_q_heads * c.head_dim, c.n_kv_heads * c.head_dim
+        self.q = synth.counter_normal(seed, 1, lo, hi, qw, 1.0, dev).view(T, c.n_q_heads, c.head_dim)
+        self.k = synth.counter_normal(seed, 2, lo, hi, kw, 1.0, dev).view(T, c.n_kv_heads, c.head_dim)
+        self.v = synth.counter_normal(seed, 3, lo, hi, kw, 1.0, dev).view(T, c.n_kv_heads, c.head_dim)
+        self.gate = synth.counter_normal(seed, 4, lo * c.top_k, hi * c.top_k, c.inter, 0.5, dev)
+        self.up = synth.counter_normal(seed, 5, lo * c.top_k, hi * c.top_k, c.inter, 0.5, dev)
         self.theta_scale = ops.theta_scale(c.freq_base, c.n_rot)
         # outputs
         self.hidden = torch.empty((T, c.hidden), dtype=torch.float32, device=dev)
         self.normed_attn = torch.empty_like(self.hidden)
         self.normed_ffn = torch.empty_like(self.hidden)
         self.q_out = torch.empty_like(self.q)
-        self.k_cache = ops.new_kv_cache(c.cache_slots, c.n_kv_heads, c.head_dim, dev)
-        self.v_cache = ops.new_kv_cache(c.cache_slots, c.n_kv_heads, c.head_dim, dev)
+        if shared is None:
+            self.k_cache = ops.new_kv_cache(c.cache_slots, c.n_kv_heads, c.head_dim, dev)
+            self.v_cache = ops.new_kv_cache(c.cache_slots, c.n_kv_heads, c.head_dim, dev)
+        else:  # shards on one GPU append disjoint cells of one cache
+            self.k_cache, self.v_cache = shared.k_cache, shared.v_cache
         self.act = torch.empty((T * c.top_k, c.inter // 32 * ops.Q8_1_BLOCK), dtype=torch.uint8, device=dev)
         self.err = ops.new_err(dev)
 
@@ -100,7 +120,7 @@ class PrefillChain:
         ops.rms_norm(self.hidden, self.w_ffn, self.cfg.eps, out=self.normed_ffn)
 
     def swiglu_q8_1(self):
-        ops.swiglu_q8_1(self.gate, self.up, out=self.act)
+        ops.swiglu_q8_1(self.gate, self.up, out=self.act, err=self.err)
 
     def step(self):
         for name in self.STAGES:
@@ -123,7 +143,7 @@ class PrefillChain:
 
     def kv_cells(self):
         """The cells this shard appended: (K, V) uint8 [tokens][n_kv][cell bytes]."""
-        lo = int(self.pos[0].item())
+        lo = self.cfg.depth + self.first_token
         return self.k_cache[lo:lo + self.cfg.tokens], self.v_cache[lo:lo + self.cfg.tokens]
 
     def describe(self) -> dict:

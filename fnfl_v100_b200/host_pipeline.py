@@ -39,8 +39,9 @@ class HostChunkPipeline:
         for _ in range(2):
             s = PrefillChain.__new__(PrefillChain)
             s.cfg, s.device = ccfg, self.device
-            for n in ("table", "w_attn", "w_ffn", "w_q", "w_k", "k_cache", "v_cache", "err", "theta_scale"):
+            for n in PrefillChain.SHARED + ("k_cache", "v_cache", "err", "theta_scale"):
                 setattr(s, n, getattr(src, n))
+            s.first_token = src.first_token
             dev = self.device
             Tc = self.chunk
             s.ids = torch.empty(Tc, dtype=torch.int32, device=dev)
@@ -67,8 +68,10 @@ class HostChunkPipeline:
         self.h2d_bytes = sum(row_in.values()) * T
         self.d2h_bytes = T * (c.top_k * c.inter // 32 * ops.Q8_1_BLOCK + 2 * c.n_kv_heads * cell) + 4
 
-    def step(self) -> None:
-        """One pass over all T tokens from and to host memory; returns with work enqueued (no sync)."""
+    def step(self, copies_only: bool = False) -> None:
+        """One pass over all T tokens from and to host memory; returns with work enqueued (no sync).
+        copies_only: the same copies on the same streams with the kernels left out - the ceiling the host link
+        and the host's memory system set for this pipeline."""
         c, Tc = self.cfg, self.chunk
         cur = torch.cuda.current_stream(self.device)
         self.s_in.wait_stream(cur)
@@ -86,7 +89,8 @@ class HostChunkPipeline:
             cur.wait_event(self.ev_in[b])
             if ci >= 2:
                 cur.wait_event(self.ev_out[b])                   # the slot's previous outputs reached the host
-            s.step()
+            if not copies_only:
+                s.step()
             self.ev_done[b].record(cur)
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(self.ev_done[b])

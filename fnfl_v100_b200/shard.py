@@ -34,6 +34,10 @@ def gather_rows(local, total_rows: int, group=None):
     sizes = shard_sizes(total_rows, world)
     if local.shape[0] != sizes[dist.get_rank(group)]:
         raise ValueError("gather_rows: local shard does not match row_range")
+    if min(sizes) == max(sizes):  # equal shards: one collective straight into the result
+        out = torch.empty((total_rows,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(out, local.contiguous(), group=group)
+        return out
     biggest = max(sizes)
     padded = local
     if local.shape[0] != biggest:

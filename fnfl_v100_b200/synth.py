@@ -128,3 +128,61 @@ def torch_table(fmt: str, gen, n_rows: int, cols: int, device, d_lo: float = 1e-
     d = torch.empty((n_rows, nsb, nd), dtype=torch.float32, device=device).uniform_(d_lo, d_hi, generator=gen)
     t[:, :, 0:2 * nd] = d.to(torch.float16).view(torch.uint8).reshape(n_rows, nsb, 2 * nd)
     return t.reshape(n_rows, nsb * bb)
+
+
+# ---- counter-based device inputs: any rank can regenerate any row of the job -------------------------------------
+# Element (row, col) of stream `sid` is a pure function of (seed, sid, row * cols + col): a splitmix64 finaliser of
+# the counter gives two 24-bit uniforms, Box-Muller (F32, on the device) gives one normal.  A shard that holds rows
+# [lo, hi) of the job generates exactly the values the unsharded job holds in those rows, so a partitioned run can
+# be compared with the whole one byte for byte, and one rank can recompute another rank's slice.
+
+_M64 = (1 << 64) - 1
+
+
+def _s64(v: int) -> int:
+    """An unsigned 64-bit constant as the signed value torch's int64 arithmetic wraps to."""
+    v &= _M64
+    return v - (1 << 64) if v >> 63 else v
+
+
+def _lsr(x, n: int):
+    """Logical right shift of an int64 tensor (torch's >> is arithmetic)."""
+    return (x >> n) & ((1 << (64 - n)) - 1)
+
+
+def _mix64(x):
+    x = (x ^ _lsr(x, 30)) * _s64(0xBF58476D1CE4E5B9)
+    x = (x ^ _lsr(x, 27)) * _s64(0x94D049BB133111EB)
+    return x ^ _lsr(x, 31)
+
+
+def _counter_bits(seed: int, sid: int, lo: int, n: int, device):
+    import torch
+    idx = torch.arange(lo, lo + n, dtype=torch.int64, device=device)
+    key = _s64((seed * 0x9E3779B97F4A7C15 + sid * 0xD1B54A32D192ED03) & _M64)
+    return _mix64((idx + key) * _s64(0x9E3779B97F4A7C15))
+
+
+def counter_normal(seed: int, sid: int, row_lo: int, row_hi: int, cols: int, scale: float, device, out=None):
+    """F32 [row_hi - row_lo][cols] ~ N(0, scale^2): rows row_lo .. row_hi - 1 of stream `sid`."""
+    import math
+    import torch
+    rows = row_hi - row_lo
+    if out is None:
+        out = torch.empty((rows, cols), dtype=torch.float32, device=device)
+    flat = out.view(-1)
+    step = max(1, (1 << 25) // cols)                      # rows per pass: bounded temporaries
+    for r in range(0, rows, step):
+        n = min(step, rows - r) * cols
+        z = _counter_bits(seed, sid, (row_lo + r) * cols, n, device)
+        u1 = (_lsr(z, 40).to(torch.float32) + 0.5) * (1.0 / (1 << 24))          # (0, 1)
+        u2 = ((z >> 16) & 0xFFFFFF).to(torch.float32) * (1.0 / (1 << 24))        # [0, 1)
+        torch.mul(torch.sqrt(-2.0 * torch.log(u1)), torch.cos((2.0 * math.pi) * u2) * scale, out=flat[r * cols:r * cols + n])
+    return out
+
+
+def counter_ids(seed: int, sid: int, row_lo: int, row_hi: int, n_vocab: int, device):
+    """I32 [row_hi - row_lo] uniform in [0, n_vocab): token ids of rows row_lo .. row_hi - 1."""
+    import torch
+    z = _counter_bits(seed, sid, row_lo, row_hi - row_lo, device)
+    return (_lsr(z, 11) % n_vocab).to(torch.int32)

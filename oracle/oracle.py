@@ -26,13 +26,25 @@ ERR_SLOT = 2
 Q8_0_BYTES, Q8_1_BYTES, Q4_K_BYTES, IQ3_XXS_BYTES = 34, 36, 144, 98
 
 
-def build(with_ref: bool | None = None) -> None:
-    """Compile the oracle (and the reference build when the reference tree is present)."""
-    ref_root = os.environ.get("FNB_REFERENCE", "/root/reference")
+def reference_root(reference: str | None = None) -> str | None:
+    """Where the reference tree is: the argument, else the FNB_REFERENCE environment variable, else a directory named
+    `reference` beside this repository; None when there is none (then only the oracle itself is built)."""
+    for cand in (reference, os.environ.get("FNB_REFERENCE"),
+                 os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "ggml", "src")):
+            return cand
+    return None
+
+
+def build(with_ref: bool | None = None, reference: str | None = None) -> None:
+    """Compile the oracle, and the reference's own sources where they lie when a reference tree is found."""
+    ref_root = reference_root(reference)
     if with_ref is None:
-        with_ref = os.path.isdir(os.path.join(ref_root, "ggml", "src"))
-    targets = ["all"] + (["ref", "ref-gguf"] if with_ref else [])
-    subprocess.run(["make", "-C", _HERE, "REFERENCE=" + ref_root] + targets, check=True, capture_output=True)
+        with_ref = ref_root is not None
+    if with_ref and ref_root is None:
+        raise FileNotFoundError("no reference tree: pass reference=... or set FNB_REFERENCE")
+    cmd = ["make", "-C", _HERE, "all"] + (["ref", "ref-gguf", "REFERENCE=" + ref_root] if with_ref else [])
+    subprocess.run(cmd, check=True, capture_output=True)
 
 
 class _RopeArgs(C.Structure):
@@ -75,7 +87,9 @@ _ref_gguf = None
 
 def build_ref_gguf() -> None:
     """Compile the reference's GGUF writer / reader (ggml/src/gguf.cpp with the ggml core) where it lies."""
-    ref_root = os.environ.get("FNB_REFERENCE", "/root/reference")
+    ref_root = reference_root()
+    if ref_root is None:
+        raise FileNotFoundError("no reference tree: set FNB_REFERENCE")
     subprocess.run(["make", "-C", _HERE, "REFERENCE=" + ref_root, "ref-gguf"], check=True, capture_output=True)
 
 

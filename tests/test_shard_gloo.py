@@ -76,6 +76,12 @@ def test_two_ranks_gather_equals_unsharded():
     assert res[0][2] == (37, 512) and res[0][3] == (37, 16 * 36)
 
 
+def test_two_ranks_gather_of_equal_shards():
+    res = _run(rows=64, fail_rank=-1, port=29675)     # equal shards take the single-collective path
+    assert [r[1] for r in res] == ["ok", "ok"]
+    assert res[0][2] == (64, 512) and res[0][3] == (64, 16 * 36)
+
+
 def test_failure_on_one_rank_skips_the_gather_on_all():
     res = _run(rows=16, fail_rank=1, port=29673)
     assert [r[1] for r in res] == ["skipped", "skipped"]
