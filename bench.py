@@ -13,7 +13,7 @@ job, replayed from a CUDA graph of the rank's five launches.  Rank 0 prints ONE 
 
   value         whole-job tokens/s: T x K / (device time of K graph replays, CUDA events, max over ranks)
   step          median / p90 / mean of the K replays
-  ops           per fused op, replayed alone from its own graph: median / p90 / mean ms, GB/s of the algorithmic
+  ops           per fused op, replayed alone from its own graph (after a short idle): median / p90 / mean ms, GB/s of the algorithmic
                 bytes, fraction of the measured and of the nominal HBM peak.  At N = 1 also the configurations the
                 chain does not run at their stated sizes (get_rows IQ3_XXS at T, RoPE + KV at 4096 tokens with
                 random offsets, SwiGLU + Q8_1 at 40960 rows, RMSNorm at 512 rows), cold (inputs rotated over more
@@ -282,7 +282,7 @@ def op_report(ms: list, nbytes: int, peak: float) -> dict:
             "frac_of_nominal_8tbs": round(gbs / NOMINAL_HBM_GBS, 4)}
 
 
-def extra_configs(dev, k: int, peak: float) -> dict:
+def extra_configs(dev, k: int, peak: float, rest_s: float) -> dict:
     """The stated configurations the chain does not run at their own sizes, each replayed from graphs: cold (instances
     rotated so that more bytes than L2 holds pass between two replays of one instance) and hot (one instance)."""
     import torch
@@ -298,6 +298,7 @@ def extra_configs(dev, k: int, peak: float) -> dict:
     def both(name, make, nbytes, note):
         fns, n_inst = rotate(make, nbytes)
         graphs = [capture(f) for f in fns]
+        time.sleep(rest_s)
         r = {"cold": op_report(time_replays(graphs, k), nbytes, peak), "hot": op_report(time_replays(graphs[:1], k), nbytes, peak),
              "instances_rotated": n_inst, "what": note}
         out[name] = r
@@ -431,6 +432,7 @@ def run_ours(args) -> None:
     # ---- every stage alone, replayed from its own graph ----
     stage_ms = {}
     for name in stages:
+        time.sleep(args.rest_s)          # each leg alone: let the board's power controller forget the previous one
         g = capture(getattr(chain, name))
         stage_ms[name] = time_replays([g], K, W)
         del g
@@ -446,6 +448,14 @@ def run_ours(args) -> None:
                             "frac_of_nominal_8tbs": round(gbs / NOMINAL_HBM_GBS, 4),
                             "l2": "cold: one launch streams more than twice the L2" if nbytes > 2 * L2_BYTES else
                                   "the launch's bytes could partly sit in L2 between replays"}
+
+    # ---- the stated configurations the chain does not run at their own sizes (one GPU only) ----
+    extras = None
+    if world == 1 and not args.no_extras:
+        try:
+            extras = extra_configs(dev, K, peak, args.rest_s)
+        except Exception as e:  # the headline does not depend on them
+            extras = {"error": repr(e)}
 
     # ---- sustained: at least a second of back-to-back steps, stage events on the last hundred ----
     n_sus = max(100, int(math.ceil(args.sustain_s * 1e3 / (total_ms / K)))) if args.sustain_s > 0 else 0
@@ -481,14 +491,6 @@ def run_ours(args) -> None:
                      "ms_per_step": round(s0.elapsed_time(s1) / n_sus, 5),
                      "stages_last_%d_steps" % n_ev: per, "clocks_second_half": sus_clocks,
                      "note": "rank 0's shard; graph replays, then eager launches with an event between stages"}
-
-    # ---- the stated configurations the chain does not run at their own sizes (one GPU only) ----
-    extras = None
-    if world == 1 and not args.no_extras:
-        try:
-            extras = extra_configs(dev, K, peak)
-        except Exception as e:  # the headline does not depend on them
-            extras = {"error": repr(e)}
 
     # ---- end to end from pinned host memory ----
     e2e = None
@@ -660,6 +662,9 @@ def main() -> None:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--sustain-s", type=float, default=1.2, help="length of the sustained leg in seconds (0: skip it)")
+    ap.add_argument("--rest-s", type=float, default=0.3,
+                    help="idle time before each per-op leg (outside every timed region), so that a kernel timed alone "
+                         "is not timed under the power cap its predecessor drove the board into")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler runs)")
     ap.add_argument("--no-extras", action="store_true", help="skip the stated configurations outside the chain")

@@ -68,6 +68,13 @@ __device__ __forceinline__ bool mbar_wait_landed(uint64_t * bar, uint32_t parity
     return false;
 }
 
+// barrier among the first `threads` threads of the CTA (whole warps) on hardware barrier `id` (1 .. 15; 0 is
+// __syncthreads'): lets the consumer warps wait for state only they need while the producer already streams
+template <int ID>
+__device__ __forceinline__ void named_barrier(int threads) {
+    asm volatile("bar.sync %0, %1;" ::"n"(ID), "r"(threads) : "memory");
+}
+
 // L2 policy for data that is read once: evict first
 __device__ __forceinline__ uint64_t l2_evict_first_policy() {
     uint64_t p;

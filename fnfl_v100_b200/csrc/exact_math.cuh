@@ -48,23 +48,6 @@ __device__ __forceinline__ float expf_steps(float x) {
     return __double2float_rn(y);
 }
 
-// double(x) for a NORMAL float (not zero, subnormal, infinite or NaN).  FNB_GLU_WIDEN_INT builds it from the bits
-// with integer operations (the 31 magnitude bits shifted into place by a 32 x 32 -> 64 multiply, exponent rebiased,
-// sign put back) instead of the conversion instruction, which runs on the quarter-rate conversion pipe.
-#ifndef FNB_GLU_WIDEN_INT
-#define FNB_GLU_WIDEN_INT 0
-#endif
-__device__ __forceinline__ double widen_normal(float x) {
-#if FNB_GLU_WIDEN_INT
-    const uint32_t b = __float_as_uint(x);
-    const unsigned long long m = (unsigned long long) (b << 1) * 0x10000000ull;  // (b & 0x7fffffff) << 29
-    const uint32_t hi = uint32_t(m >> 32) + 0x38000000u + (b & 0x80000000u);
-    return __hiloint2double(int(hi), int(uint32_t(m)));
-#else
-    return double(x);
-#endif
-}
-
 // The same function in 8 FP64 operations: the reduction as above (so k and r are the definition's), the cubic as
 // a fused Horner chain.  The two doubles differ by at most 2 units in the last place and the FLOAT they round to is
 // the same for EVERY float |x| < 88: checked by enumerating all 2 x 0x42b00000 inputs, on the CPU
@@ -73,7 +56,7 @@ __device__ __forceinline__ double widen_normal(float x) {
 // NEG: returns -e^x (the sign rides on the last product: rounding is symmetric, so it is exactly the negated result)
 template <bool NEG>
 __device__ __forceinline__ float expf_core_signed(float x) {
-    const double z = __dmul_rn(c_exp_k[0], widen_normal(x));
+    const double z = __dmul_rn(c_exp_k[0], double(x));
     double kd = __dadd_rn(z, c_exp_k[1]);
     const unsigned long long ki = (unsigned long long) __double_as_longlong(kd);
     kd = __dsub_rn(kd, c_exp_k[1]);

@@ -60,7 +60,7 @@ __global__ void __launch_bounds__(kWarps * 32) quantize_q8_k_kernel(const float 
                     const int bits = __float_as_int(__fadd_rn(__fmul_rn(iscale, c[e]), 12582912.0f));
                     code[e] = min(127, (bits & 0x007fffff) - 0x00400000);  // the reference stores the low byte
                 }
-                mine[1 + j + 8 * q] = pack4(code[0], code[1], code[2], code[3]);
+                mine[1 + j + 8 * q] = pack4_low_bytes(code[0], code[1], code[2], code[3]);
             }
             d = __fdiv_rn(1.0f, iscale);
         } else {

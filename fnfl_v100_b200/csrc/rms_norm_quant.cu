@@ -9,7 +9,8 @@
 // HBM-bound: 4 bytes read and 1.06 - 1.25 written per value.  Same pipeline shape as the SwiGLU kernel: one producer
 // lane streams tiles of four rows (one bulk copy per tile) into a ring of shared-memory stages; consumer warps take a
 // row each.  A lane owns whole blocks (block b = lane, lane + 32, ...), reads them in rotated 16-byte chunks
-// (conflict-free), and RELEASES THE STAGE AS SOON AS THE ROW IS IN REGISTERS, so nearly the whole ring is in flight.
+// (conflict-free), and RELEASES THE STAGE AS SOON AS THE ROW IS IN REGISTERS (the release is made to depend on every
+// loaded value), so nearly the whole ring is in flight.
 // amax, code sums and block headers are in-lane; only the row's sum of squares crosses lanes (one 5-step butterfly).
 //
 // Tiles go to the consumer groups in turn (tile i of a CTA to group i mod groups) and stage i mod stages holds it.
@@ -72,8 +73,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         mbar_init_fence();
     }
-    for (int i = threadIdx.x; i < cols; i += blockDim.x) wsm[i] = w != nullptr ? __ldg(w + i) : 1.0f;
-    __syncthreads();
+    __syncthreads();  // nothing slow before this point: the producer starts streaming at once
 
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int64_t n_tiles = (rows + kGroupWarps - 1) / kGroupWarps;
@@ -104,6 +104,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         return;
     }
 
+    // the weights reach shared memory while the first tiles are in flight (every consumer warp helps, then the idle
+    // groups leave)
+    for (int i = threadIdx.x; i < cols; i += kConsumerWarps * 32) wsm[i] = w != nullptr ? __ldg(w + i) : 1.0f;
+    named_barrier<1>(kConsumerWarps * 32);
     const int grp = wid / kGroupWarps, gw = wid - grp * kGroupWarps;
     if (grp >= groups) return;  // a ring shallower than kGroups is shared by `groups` groups only
     uint8_t * my_out = outs + size_t(wid) * row_out_pad;
@@ -132,9 +136,25 @@ __global__ void __launch_bounds__(kThreads, 1)
                 v[k][j] = b < nb ? *reinterpret_cast<const float4 *>(src + 128 * b + 16 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
+        // The stage is handed back as soon as the row is in registers - and no sooner: the arrive is predicated on a
+        // cheap value computed from EVERY loaded register (a packed F32 sum; no addition yields the all-ones pattern,
+        // so the predicate is always true), which keeps it behind the completion of all the loads above in any
+        // schedule, instead of resting on the ordering of a release that follows loads nothing has consumed yet.
+        f32x2 touch[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll
+        for (int k = 0; k < BPL; ++k) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                touch[j & 3] = add2(touch[j & 3], pk(v[k][j].x, v[k][j].y));
+                touch[j & 3] = add2(touch[j & 3], pk(v[k][j].z, v[k][j].w));
+            }
+        }
+        float t_lo, t_hi;
+        unpk(add2(add2(touch[0], touch[1]), add2(touch[2], touch[3])), t_lo, t_hi);
+        const bool landed = __float_as_uint(__fadd_rn(t_lo, t_hi)) != 0xffffffffu;
         __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[s]);  // the row is in registers: the stage can be refilled
-        if (!live) continue;                    // uniform over the warp
+        if (lane == 0 && landed) mbar_arrive(&empty[s]);  // the row is in registers: the stage can be refilled
+        if (!live) continue;                              // uniform over the warp
 
         // four independent chains (a double tree sum differs from the sequential one far below the F32 narrowing)
         double a4[4] = {0.0, 0.0, 0.0, 0.0};

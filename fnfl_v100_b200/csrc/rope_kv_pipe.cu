@@ -132,12 +132,7 @@ __global__ void __launch_bounds__(kThreads, 1) rope_kv_pipe_kernel(const rope_ke
         }
         mbar_init_fence();
     }
-    for (int i = threadIdx.x; i < HD; i += blockDim.x) {
-        w_tab[i] = a.q_norm_w != nullptr ? __ldg(a.q_norm_w + i) : 1.0f;
-        w_tab[HD + i] = a.k_norm_w != nullptr ? __ldg(a.k_norm_w + i) : 1.0f;
-        w_tab[2 * HD + i] = 1.0f;
-    }
-    __syncthreads();
+    __syncthreads();  // nothing slow before this point: the producers start streaming at once
 
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int64_t n_tiles = (a.rows + tt - 1) / tt;
@@ -216,6 +211,13 @@ __global__ void __launch_bounds__(kThreads, 1) rope_kv_pipe_kernel(const rope_ke
     }
 
     // ---------------- consumers ----------------
+    // the norm weights reach shared memory while the first tiles are in flight
+    for (int i = threadIdx.x; i < HD; i += kConsumerWarps * 32) {
+        w_tab[i] = a.q_norm_w != nullptr ? __ldg(a.q_norm_w + i) : 1.0f;
+        w_tab[HD + i] = a.k_norm_w != nullptr ? __ldg(a.k_norm_w + i) : 1.0f;
+        w_tab[2 * HD + i] = 1.0f;
+    }
+    named_barrier<1>(kConsumerWarps * 32);
     const int grp = wid / kGroupWarps, gw = wid - grp * kGroupWarps;
     const int sub = lane & 7, rq = lane >> 3;
     uint8_t * my_slot = slots + (wid * 4 + rq) * kSlotBytes;  // this row's cell under assembly
