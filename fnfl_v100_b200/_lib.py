@@ -22,7 +22,7 @@ class RopeKvArgs(C.Structure):
         ("q_norm_w", C.c_void_p), ("k_norm_w", C.c_void_p), ("q_out", C.c_void_p), ("k_cache", C.c_void_p),
         ("v_cache", C.c_void_p), ("k_f32", C.c_void_p), ("err", C.c_void_p), ("rows", C.c_int64),
         ("cache_slots", C.c_int64), ("n_q_heads", C.c_int32), ("n_kv_heads", C.c_int32), ("head_dim", C.c_int32),
-        ("n_rot", C.c_int32), ("theta_scale", C.c_float), ("eps", C.c_float),
+        ("n_rot", C.c_int32), ("theta_scale", C.c_float), ("eps", C.c_float), ("planes", C.c_void_p),
     ]
 
 

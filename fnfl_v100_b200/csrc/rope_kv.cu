@@ -185,7 +185,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32) rope_kv_kernel(const kernel_ar
         }
         __syncthreads();  // the previous token's readers of s_cs are done
         for (int i = threadIdx.x; i < half; i += blockDim.x) {
-            float theta = float(p);
+            float theta = float(a.planes != nullptr ? __ldg(a.planes + 4 * t + rope_plane_of_pair(i)) : p);
             for (int c = 0; c < i; ++c) theta = __fmul_rn(theta, a.theta_scale);
             float sn, cs;
             exact_sincosf(theta, &sn, &cs);
@@ -246,7 +246,8 @@ int32_t launch(const fnb_rope_kv_args * p, uint16_t * k_scale, uint16_t * v_scal
     if (p->n_q_heads < 0 || p->n_q_heads > 256 || p->n_kv_heads < 0 || p->n_kv_heads > 256) return FNB_REJECTED;
     if (p->n_q_heads + p->n_kv_heads < 1) return FNB_REJECTED;
     if (p->n_rot < 0 || p->n_rot > hd || p->n_rot % (2 * epl) != 0) return FNB_REJECTED;
-    if (!ok_ptr(p->pos, 4) || !ok_opt(p->slots, 4) || !ok_opt(p->err, 4)) return FNB_REJECTED;
+    if (!ok_ptr(p->pos, 4) || !ok_opt(p->slots, 4) || !ok_opt(p->err, 4) || !ok_opt(p->planes, 4)) return FNB_REJECTED;
+    if (p->planes != nullptr && p->n_rot != 64) return FNB_REJECTED;  // the plane sections are defined for 32 pairs
     if (!ok_opt(p->q_norm_w, 16) || !ok_opt(p->k_norm_w, 16) || !ok_opt(p->k_f32, 16)) return FNB_REJECTED;
     if (p->n_q_heads > 0 && (!ok_ptr(p->q, 16) || !ok_ptr(p->q_out, 16))) return FNB_REJECTED;
     if (p->n_kv_heads > 0) {
@@ -259,7 +260,7 @@ int32_t launch(const fnb_rope_kv_args * p, uint16_t * k_scale, uint16_t * v_scal
     if (!(p->eps >= 0.0f) || !(p->theta_scale > 0.0f)) return FNB_REJECTED;
 
     kernel_args a;
-    a.q = p->q, a.k = p->k, a.v = p->v, a.pos = p->pos, a.slots = p->slots;
+    a.q = p->q, a.k = p->k, a.v = p->v, a.pos = p->pos, a.slots = p->slots, a.planes = p->planes;
     a.q_norm_w = p->q_norm_w, a.k_norm_w = p->k_norm_w, a.q_out = p->q_out, a.k_f32 = p->k_f32;
     a.k_cache = static_cast<uint8_t *>(p->k_cache), a.v_cache = static_cast<uint8_t *>(p->v_cache);
     a.k_scale = k_scale, a.v_scale = v_scale, a.err = p->err;

@@ -12,6 +12,7 @@ enum class kv_fmt { q8_0, kv8 };
 struct rope_kernel_args {
     const float *q, *k, *v;
     const int32_t *pos, *slots;
+    const int32_t * planes;  // [rows][4] or null: the reference's rotary position planes of image rows
     const float *q_norm_w, *k_norm_w;
     float *q_out, *k_f32;
     uint8_t *k_cache, *v_cache;
@@ -21,6 +22,12 @@ struct rope_kernel_args {
     int32_t n_q, n_kv, n_rot;
     float theta_scale, eps;
 };
+
+// the position plane rotary pair i reads (sections 11, 11, 10, 0 of 32 pairs, interleaved), as the reference's
+// imrope_plane (fn/kernels/qsa/imrope.cuh:15-24)
+__host__ __device__ __forceinline__ int rope_plane_of_pair(int i) {
+    return i % 3 == 1 && i < 33 ? 1 : i % 3 == 2 && i < 30 ? 2 : i % 3 == 0 && i < 33 ? 0 : 3;
+}
 
 // Enqueues the pipelined kernel when the shape suits it and returns true; returns false (nothing enqueued) when
 // the caller should use the row-per-warp kernel instead.

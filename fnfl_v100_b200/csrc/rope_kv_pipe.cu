@@ -179,7 +179,8 @@ __global__ void __launch_bounds__(kThreads, 1) rope_kv_pipe_kernel(const rope_ke
                 if (tk >= live) break;
                 float2 * cs = cs_all + (size_t(s) * tt + tk) * (HD / 2);
                 // lane i walks the chain pos * ts^i: i multiplies to reach its first pair, 32 more for each further one
-                float theta = float(p_of[j]);
+                // (with position planes, n_rot is 64: lane i is pair i and reads its own plane's position)
+                float theta = float(a.planes != nullptr ? __ldg(a.planes + 4 * (t0 + tk) + rope_plane_of_pair(lane)) : p_of[j]);
 #pragma unroll
                 for (int c = 0; c < 31; ++c) theta = c < lane ? __fmul_rn(theta, a.theta_scale) : theta;
                 for (int i = lane; i < half; i += 32) {

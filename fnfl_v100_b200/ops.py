@@ -223,7 +223,7 @@ def new_kv_cache(cache_slots: int, n_kv_heads: int, head_dim: int, device, fmt: 
     return codes, scales
 
 
-def _rope_args(q, k, v, pos, slots, q_norm_w, k_norm_w, q_out, k_cache, v_cache, k_f32, err, n_rot, ts, eps):
+def _rope_args(q, k, v, pos, slots, q_norm_w, k_norm_w, q_out, k_cache, v_cache, k_f32, err, n_rot, ts, eps, planes=None):
     _dev(q, torch.float32, "q")
     _dev(k, torch.float32, "k")
     _dev(v, torch.float32, "v")
@@ -233,16 +233,21 @@ def _rope_args(q, k, v, pos, slots, q_norm_w, k_norm_w, q_out, k_cache, v_cache,
     rows, n_q, hd = q.shape
     if pos.numel() != rows or (slots is not None and slots.numel() != rows):
         raise ValueError("pos / slots: expected [rows]")
+    if planes is not None:
+        _dev(planes, torch.int32, "planes")
+        if planes.numel() != 4 * rows:
+            raise ValueError("planes: expected [rows][4]")
     cache_slots = k_cache.shape[0]
     a = _lib.RopeKvArgs(
         _ptr(q).value, _ptr(k).value, _ptr(v).value, _ptr(pos).value, _ptr(slots).value, _ptr(q_norm_w).value,
         _ptr(k_norm_w).value, _ptr(q_out).value, _ptr(k_cache).value, _ptr(v_cache).value, _ptr(k_f32).value,
-        _ptr(err).value, rows, cache_slots, n_q, k.shape[1], hd, n_rot, ts, eps)
+        _ptr(err).value, rows, cache_slots, n_q, k.shape[1], hd, n_rot, ts, eps, _ptr(planes).value)
     return a
 
 
 def rope_neox_q8_0_append(q, k, v, pos, *, n_rot: int, theta_scale: float, k_cache, v_cache, slots=None,
-                          q_norm_w=None, k_norm_w=None, eps: float = 1e-6, q_out=None, k_f32=None, err=None):
+                          q_norm_w=None, k_norm_w=None, eps: float = 1e-6, q_out=None, k_f32=None, err=None,
+                          planes=None):
     """Per-head norm (optional) + NeoX partial RoPE; Q -> q_out (F32), K/V -> Q8_0 cells at each token's slot.
     Replaces fn::qsa::qsp_kv and the prepare phase of fn::qsa::attn::attend.  Returns q_out."""
     if q_out is None:
@@ -250,14 +255,14 @@ def rope_neox_q8_0_append(q, k, v, pos, *, n_rot: int, theta_scale: float, k_cac
     _dev(k_cache, torch.uint8, "k_cache")
     _dev(v_cache, torch.uint8, "v_cache")
     a = _rope_args(q, k, v, pos, slots, q_norm_w, k_norm_w, q_out, k_cache, v_cache, k_f32, err, n_rot,
-                   theta_scale, eps)
+                   theta_scale, eps, planes)
     _check(_lib.lib().fnb_rope_neox_q8_0_append(C.byref(a), _stream()), "rope_neox_q8_0_append")
     return q_out
 
 
 def rope_neox_kv8_append(q, k, v, pos, *, n_rot: int, theta_scale: float, k_cache, v_cache, k_scale, v_scale,
                          slots=None, q_norm_w=None, k_norm_w=None, eps: float = 1e-6, q_out=None, k_f32=None,
-                         err=None):
+                         err=None, planes=None):
     """The same step into the reference's KV8 format (int8 codes + FP16 scale per 64 values)."""
     if q_out is None:
         q_out = torch.empty_like(q)
@@ -266,7 +271,7 @@ def rope_neox_kv8_append(q, k, v, pos, *, n_rot: int, theta_scale: float, k_cach
     _dev(k_scale, torch.int16, "k_scale")
     _dev(v_scale, torch.int16, "v_scale")
     base = _rope_args(q, k, v, pos, slots, q_norm_w, k_norm_w, q_out, k_cache, v_cache, k_f32, err, n_rot,
-                      theta_scale, eps)
+                      theta_scale, eps, planes)
     a = _lib.RopeKv8Args(base, _ptr(k_scale).value, _ptr(v_scale).value)
     _check(_lib.lib().fnb_rope_neox_kv8_append(C.byref(a), _stream()), "rope_neox_kv8_append")
     return q_out

@@ -136,6 +136,11 @@ int32_t fnb_rms_norm_act(const float * x, const float * w, float eps, int8_t * c
  * device and head_dim): make that first call outside a stream capture.  Shapes whose token tile does not fit in
  * shared memory, or whose n_rot is not a multiple of 64, run a slower row-per-warp kernel with the same results.
  * A bounded in-kernel wait that gives up sets FNB_ERR_TIMEOUT in *err.
+ * planes (optional, n_rot 64 only): the reference's interleaved multi-section rotary positions for image rows
+ * (fn/kernels/qsa/imrope.cuh:15-24, qsa_prompt.h:100-102): row t's rotary pair i takes its position from
+ * planes[4 t + p(i)], p(i) = 1 for i % 3 == 1 below 33, 2 for i % 3 == 2 below 30, 0 for i % 3 == 0 below 33, else 3,
+ * instead of pos[t]; the angle is that position times theta_scale^i by the same F32 product chain.  pos[t] is then
+ * only the cache slot when slots is null.  Text rows hold one integer in all four planes, which is plain NeoX.
  * Replaces fn::qsa::qsp_kv (fn/kernels/qsa/qsa_prompt.h:90-105, qsa_prompt_attn.cu:77-122), the prepare phase
  * of fn::qsa::attn::attend (fn/kernels/qsa/attend.cu:153-260) and fn::draft::dcp_prepare
  * (fn/kernels/draft/draft_prompt.h:44-59).
@@ -161,6 +166,7 @@ typedef struct fnb_rope_kv_args {
     int32_t n_rot;
     float theta_scale;
     float eps;
+    const int32_t * planes; /* optional, device [rows][4]: rotary position planes of image rows (see above); null = text */
 } fnb_rope_kv_args;
 
 int32_t fnb_rope_neox_q8_0_append(const fnb_rope_kv_args * args, void * stream);

@@ -157,6 +157,7 @@ struct qsp_kv_args {
     uint16_t * v_scale = nullptr;
     float * k_f32 = nullptr;          // optional: k after norm and rope, before quantising
     uint32_t * err = nullptr;
+    const int32_t * planes = nullptr; // fn::qsa::qsp_kv_args::planes: device [rows][4] rotary planes of image rows
 };
 inline bool qsp_kv(const qsp_kv_args & a, void * stream) {
     fnb_rope_kv8_args w{};
@@ -165,7 +166,7 @@ inline bool qsp_kv(const qsp_kv_args & a, void * stream) {
     w.base.k_cache = a.k_cache, w.base.v_cache = a.v_cache, w.base.k_f32 = a.k_f32, w.base.err = a.err;
     w.base.rows = a.rows, w.base.cache_slots = a.max_cells;
     w.base.n_q_heads = a.n_q_heads, w.base.n_kv_heads = a.n_kv_heads, w.base.head_dim = a.head_dim;
-    w.base.n_rot = a.n_rot, w.base.theta_scale = a.theta_scale, w.base.eps = a.eps;
+    w.base.n_rot = a.n_rot, w.base.theta_scale = a.theta_scale, w.base.eps = a.eps, w.base.planes = a.planes;
     w.k_scale = a.k_scale, w.v_scale = a.v_scale;
     if ((a.k_scale != nullptr) != (a.v_scale != nullptr)) return false;  // KV8 needs both planes, as the reference
     return (a.k_scale != nullptr ? fnb_rope_neox_kv8_append(&w, stream) : fnb_rope_neox_q8_0_append(&w.base, stream)) ==

@@ -335,6 +335,13 @@ void fnbo_rope_neox_q8_0_append(const fnbo_rope_kv_args * a) {
         }
         float theta = (float) a->pos[t];
         for (int i = 0; i < half; ++i) {
+            if (a->planes) {
+                /* fn/kernels/qsa/imrope.cuh:15-24 (imrope_plane, prompt_rope_pos) and qsa_prompt_attn.cu:56-60: pair i
+                 * starts its chain at its own plane's position and multiplies by theta_scale i times */
+                const int pl = i % 3 == 1 && i < 33 ? 1 : i % 3 == 2 && i < 30 ? 2 : i % 3 == 0 && i < 33 ? 0 : 3;
+                theta = (float) a->planes[4 * t + pl];
+                for (int c = 0; c < i; ++c) theta *= a->theta_scale;
+            }
             cs[2 * i] = o_cosf(theta);
             cs[2 * i + 1] = o_sinf(theta);
             theta *= a->theta_scale;

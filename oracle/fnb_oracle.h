@@ -66,6 +66,7 @@ typedef struct fnbo_rope_kv_args {
     int32_t n_q_heads, n_kv_heads, head_dim, n_rot;
     float theta_scale;       /* powf(freq_base, -2.0f / n_rot) */
     float eps;
+    const int32_t * planes;  /* optional [rows][4]: rotary position planes (fn/kernels/qsa/imrope.cuh:15-24) */
 } fnbo_rope_kv_args;
 
 void fnbo_rope_neox_q8_0_append(const fnbo_rope_kv_args * a);

@@ -45,6 +45,10 @@ def build(with_ref: bool | None = None, reference: str | None = None) -> None:
         raise FileNotFoundError("no reference tree: pass reference=... or set FNB_REFERENCE")
     cmd = ["make", "-C", _HERE, "all"] + (["ref", "ref-gguf", "REFERENCE=" + ref_root] if with_ref else [])
     subprocess.run(cmd, check=True, capture_output=True)
+    if with_ref:
+        # the reference's own GPU launchers for three operations (needs nvcc); a tree whose translation units do not
+        # build for this GPU architecture leaves the library out and the tests that use it skip
+        subprocess.run(["make", "-C", _HERE, "ref-gpu", "REFERENCE=" + ref_root], check=False, capture_output=True)
 
 
 class _RopeArgs(C.Structure):
@@ -53,7 +57,7 @@ class _RopeArgs(C.Structure):
         ("q_norm_w", C.c_void_p), ("k_norm_w", C.c_void_p), ("q_out", C.c_void_p), ("k_cache", C.c_void_p),
         ("v_cache", C.c_void_p), ("k_f32", C.c_void_p), ("err", C.c_void_p), ("rows", C.c_int64),
         ("cache_slots", C.c_int64), ("n_q_heads", C.c_int32), ("n_kv_heads", C.c_int32), ("head_dim", C.c_int32),
-        ("n_rot", C.c_int32), ("theta_scale", C.c_float), ("eps", C.c_float),
+        ("n_rot", C.c_int32), ("theta_scale", C.c_float), ("eps", C.c_float), ("planes", C.c_void_p),
     ]
 
 
@@ -79,6 +83,22 @@ def lib() -> C.CDLL:
 
 def have_ref() -> bool:
     return os.path.exists(REF_SO)
+
+
+REF_GPU_SO = os.path.join(_HERE, "_ref", "libfnb_ref_gpu.so")
+
+
+def ref_gpu():
+    """The reference's own GPU launchers (oracle/ref_gpu_shim.cu), or None when the library was not built."""
+    if not os.path.exists(REF_GPU_SO):
+        return None
+    l = C.CDLL(REF_GPU_SO)
+    P, I = C.c_void_p, C.c_int32
+    l.fnbr_dcp_norm.argtypes, l.fnbr_dcp_norm.restype = [I, P, P, P, P, P, P, P, P, P], I
+    l.fnbr_glu_finish.argtypes, l.fnbr_glu_finish.restype = [P, P, I, P, P, P], I
+    l.fnbr_qsp_kv8.argtypes, l.fnbr_qsp_kv8.restype = [P, P, P, I, I, I, P, P, P, P, I, P, P], I
+    l.fnbr_rope_theta_scale.argtypes, l.fnbr_rope_theta_scale.restype = [], C.c_float
+    return l
 
 
 REF_GGUF_SO = os.path.join(_HERE, "_ref", "libfnb_ref_gguf.so")
@@ -385,7 +405,7 @@ def expert_down_rows(fmt: str, w: np.ndarray, act: np.ndarray, n: int, r0: int =
 
 def rope_kv_append(q, k, v, pos, *, n_rot: int, theta_scale: float, k_cache: np.ndarray, v_cache: np.ndarray,
                    cache_slots: int, slots=None, q_norm_w=None, k_norm_w=None, eps: float = 1e-6,
-                   want_k_f32: bool = False, q_out: np.ndarray | None = None):
+                   want_k_f32: bool = False, q_out: np.ndarray | None = None, planes=None):
     """q [rows][n_q][hd], k/v [rows][n_kv][hd]; caches are uint8 [cache_slots][n_kv][hd/32*34], updated in place.
     Returns (q_out, k_f32 or None, err)."""
     q, k, v = _f32(q), _f32(k), _f32(v)
@@ -400,7 +420,8 @@ def rope_kv_append(q, k, v, pos, *, n_rot: int, theta_scale: float, k_cache: np.
     k_f32 = np.zeros_like(k) if want_k_f32 else None
     err = np.zeros(1, np.uint32)
     a = _RopeArgs(_p(q), _p(k), _p(v), _p(pos), _p(slots), _p(qw), _p(kw), _p(q_out), _p(k_cache), _p(v_cache),
-                  _p(k_f32), _p(err), rows, cache_slots, n_q, n_kv, hd, n_rot, theta_scale, eps)
+                  _p(k_f32), _p(err), rows, cache_slots, n_q, n_kv, hd, n_rot, theta_scale, eps,
+                  _p(None if planes is None else np.ascontiguousarray(planes, np.int32)))
     lib().fnbo_rope_neox_q8_0_append(C.byref(a))
     return q_out, k_f32, int(err[0])
 

@@ -192,6 +192,47 @@ def test_rope_kv_append_matches_oracle(dev, oracle, rows, nq, nkv, hd, n_rot, no
     assert int((kc.numpy() != wkc).sum()) == 0
 
 
+@pytest.mark.parametrize("rows,nq,nkv,hd", [(130, 16, 2, 256), (9, 12, 1, 256), (21, 1, 0, 256), (17, 8, 2, 128)])
+def test_rope_position_planes_match_oracle(dev, oracle, rows, nq, nkv, hd):
+    """Image rows: every rotary pair takes its position from one of four planes (fn/kernels/qsa/imrope.cuh:15-24).  Bit
+    for bit the CPU definition, in the pipelined kernel and (one Q head and no K / V) in the row-per-warp kernel; text
+    rows, whose four planes hold one integer, give exactly what no planes give."""
+    g = synth.rng(6)
+    q, k, v, _, _ = _rope_case(g, rows, nq, nkv, hd, False)
+    planes = g.integers(0, 258048, (rows, 4)).astype(np.int32)
+    pos = (100 + np.arange(rows)).astype(np.int32)            # with planes only the cache slot
+    ts = oracle.theta_scale(1e7, 64)
+    cell = hd // 32 * 34
+
+    def run(pl, rot_pos):
+        kc = Guarded((512, max(nkv, 1), cell), torch.uint8, dev)
+        vc = Guarded((512, max(nkv, 1), cell), torch.uint8, dev)
+        qo = Guarded((rows, nq, hd), torch.float32, dev)
+        err = ops.new_err(dev)
+        D = lambda a: None if a is None else to_dev(a, dev)  # noqa: E731
+        ops.rope_neox_q8_0_append(D(q), D(k), D(v), D(rot_pos), n_rot=64, theta_scale=ts, k_cache=kc.live[:, :nkv],
+                                  v_cache=vc.live[:, :nkv], slots=D(pos), q_out=qo.live, err=err, planes=D(pl))
+        torch.cuda.synchronize()
+        assert int(err.item()) == 0
+        for o in (kc, vc, qo):
+            o.check_guards()
+        return qo.numpy(), kc.numpy()[:, :nkv], vc.numpy()[:, :nkv]
+
+    got_q, got_k, got_v = run(planes, pos)
+    wkc = np.full((512, nkv, cell), POISON, np.uint8)
+    wvc = wkc.copy()
+    want_q, _, werr = oracle.rope_kv_append(q, k, v, pos, n_rot=64, theta_scale=ts, k_cache=wkc, v_cache=wvc,
+                                            cache_slots=512, slots=pos, planes=planes)
+    assert werr == 0
+    assert np.array_equal(bits(got_q), bits(want_q))
+    assert np.array_equal(got_k, wkc) and np.array_equal(got_v, wvc)
+    # a text row: the same integer in all four planes is plain NeoX at that position
+    same = np.repeat(planes[:, :1], 4, axis=1)
+    q_a, k_a, _ = run(same, pos)
+    q_b, k_b, _ = run(None, np.ascontiguousarray(planes[:, 0]))
+    assert np.array_equal(bits(q_a), bits(q_b)) and np.array_equal(k_a, k_b)
+
+
 def test_rope_slot_is_position_by_default_and_bad_slot_is_flagged(dev, oracle):
     g = synth.rng(2)
     q, k, v, _, _ = _rope_case(g, 6, 4, 2, 256, False)
