@@ -258,20 +258,36 @@ def capture(fn):
     return g
 
 
+EVENT_TICK_MS = 0.002048   # the device clock CUDA events read advances in steps of about 2 us on this GPU
+MIN_SAMPLE_MS = 0.4        # a timed sample is at least this long, so that the tick is under 1 % of it
+
+
 def time_replays(graphs: list, k: int, warm: int = 3) -> list:
-    """ms of each of k replays (graphs taken in turn), an event on either side of every replay."""
+    """k samples of the time of one replay in ms (graphs taken in turn).  A sample is a run of back-to-back replays
+    between two events, long enough that the event clock's tick does not show, divided by its length."""
     import torch
     cur = torch.cuda.current_stream()
     for i in range(max(warm, len(graphs))):
         graphs[i % len(graphs)].replay()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(cur)
+    for i in range(8):
+        graphs[i % len(graphs)].replay()
+    b.record(cur)
+    torch.cuda.synchronize()
+    est = max(a.elapsed_time(b) / 8, EVENT_TICK_MS)
+    per = max(1, int(math.ceil(MIN_SAMPLE_MS / est)))
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(k + 1)]
     torch.cuda.synchronize()
     ev[0].record(cur)
+    n = 0
     for i in range(k):
-        graphs[i % len(graphs)].replay()
+        for _ in range(per):
+            graphs[n % len(graphs)].replay()
+            n += 1
         ev[i + 1].record(cur)
     torch.cuda.synchronize()
-    return [ev[i].elapsed_time(ev[i + 1]) for i in range(k)]
+    return [ev[i].elapsed_time(ev[i + 1]) / per for i in range(k)]
 
 
 def op_report(ms: list, nbytes: int, peak: float) -> dict:

@@ -45,6 +45,15 @@ class KvReadArgs(C.Structure):
                 ("n_kv_heads", C.c_int32), ("head_dim", C.c_int32)]
 
 
+class AttendArgs(C.Structure):
+    """fnb_attend_args"""
+    _fields_ = [("q", C.c_void_p), ("gate", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p),
+                ("k_scale", C.c_void_p), ("v_scale", C.c_void_p), ("first_cell", C.c_void_p), ("n_cells", C.c_void_p),
+                ("out", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("err", C.c_void_p),
+                ("cache_slots", C.c_int64), ("range_begin", C.c_int64), ("range_end", C.c_int64), ("rows", C.c_int32),
+                ("n_q_heads", C.c_int32), ("n_kv_heads", C.c_int32), ("head_dim", C.c_int32), ("scale", C.c_float)]
+
+
 class GgufTensor(C.Structure):
     """fnb_gguf_tensor"""
     _fields_ = [("ne", C.c_int64 * 4), ("offset", C.c_int64), ("row_bytes", C.c_int64), ("n_rows", C.c_int64),
@@ -82,6 +91,8 @@ SIGNATURES = {
     "fnb_embed_join": (_I32, [C.POINTER(EmbedArgs), _P, _I32, _P]),
     "fnb_embed_supply": (_I32, [C.POINTER(EmbedArgs), _P, _I64, _I64, _P]),
     "fnb_kv_read_f32": (_I32, [C.POINTER(KvReadArgs), _P]),
+    "fnb_attend_workspace_bytes": (C.c_size_t, [C.POINTER(AttendArgs)]),
+    "fnb_attend": (_I32, [C.POINTER(AttendArgs), _P]),
     "fnb_quantize_q8_k": (_I32, [_P, _P, _I64, _I32, _P]),
     "fnb_expert_gate_up_rows_q4_k": (_I32, [_P, _P, _I64, _I32, _P, _I64, _I32, _P, _I64, _P, _I64, _I64, _P]),
     "fnb_expert_gate_up_rows_q5_k": (_I32, [_P, _P, _I64, _I32, _P, _I64, _I32, _P, _I64, _P, _I64, _I64, _P]),

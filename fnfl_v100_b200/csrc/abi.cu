@@ -18,6 +18,6 @@ extern "C" const char * fnb_status_name(int32_t status) {
 extern "C" int32_t fnb_prepare_device(void) {
     const bool ok = fnb::glu_prepare_device() && fnb::rms_norm_quant_prepare_device() && fnb::rope_prepare_device() &&
                     fnb::expert_down_prepare_device() && fnb::expert_gate_up_prepare_device() &&
-                    fnb::expert_down_iq4nl_prepare_device();
+                    fnb::expert_down_iq4nl_prepare_device() && fnb::attend_prepare_device();
     return ok ? FNB_OK : FNB_LAUNCH_FAILED;
 }

@@ -52,10 +52,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t * bar, uint32_t parity) {
         : "memory");
     return done != 0;
 }
-// bounded wait for the phase with the given parity; false (and FNB_ERR_TIMEOUT in *err) when it gives up
+// one look at the barrier without suspending the thread
+__device__ __forceinline__ bool mbar_test_wait(uint64_t * bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// bounded wait for the phase with the given parity; false (and FNB_ERR_TIMEOUT in *err) when it gives up.  A build
+// with a limit of a few polls looks without suspending (a suspended poll may last as long as the hardware likes,
+// which is long enough for a copy to land), so that its waits really run out.
 __device__ __forceinline__ bool mbar_wait(uint64_t * bar, uint32_t parity, uint32_t * err) {
     for (uint32_t i = 0; i < kPrimarySpinLimit; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (kPrimarySpinLimit < 1024u ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity)) return true;
     }
     if (err != nullptr) atomicOr(err, FNB_ERR_TIMEOUT);
     return false;

@@ -24,7 +24,8 @@ OPS = ("get_rows_q4_k", "get_rows_iq3_xxs", "rms_norm", "rms_norm_heads", "rope_
        "expert_gate_up_q4_k_nt1", "expert_gate_up_q4_k_nt3", "expert_gate_up_q4_k_nt8",
        "expert_gate_up_q5_k_nt1", "expert_gate_up_q5_k_nt3", "expert_gate_up_q5_k_nt8",
        "expert_gate_up_iq3_s_nt1", "expert_gate_up_iq3_s_nt3", "expert_gate_up_iq3_s_nt8",
-       "expert_gate_up_iq3_xxs_nt1", "expert_gate_up_iq3_xxs_nt3", "expert_gate_up_iq3_xxs_nt8")
+       "expert_gate_up_iq3_xxs_nt1", "expert_gate_up_iq3_xxs_nt3", "expert_gate_up_iq3_xxs_nt8",
+       "attend_q8_0_b1", "attend_q8_0_b3", "attend_q8_0_b5", "attend_kv8_b1", "attend_kv8_b5")
 
 
 def hbm_peak() -> float:
@@ -128,6 +129,28 @@ def make_case(op: str, T: int, dev, gen, c: ChainConfig):
         act = ops.quantize_q8_k(N(gen, (nt, n), 1.0, dev))
         out = torch.empty((nt, rows), dtype=torch.float32, device=dev)
         return (lambda: ops.expert_gate_up_rows_iq3_xxs(gate, up, act, n, out=out)), rows * (2 * n // 256 * 98 + nt * 4) + nt * n // 256 * 292
+    if op.startswith("attend_"):
+        # decode rows over T cells of the cache (16 query heads on 2 KV heads of 256): the roofline counts the cache
+        # bytes, which every row of a head's group shares
+        rows, kv8 = int(op.rsplit("_b", 1)[1]), "kv8" in op
+        q = N(gen, (rows, c.n_q_heads, c.head_dim), 1.0, dev)
+        if kv8:
+            kc = torch.randint(-127, 128, (T, c.n_kv_heads, c.head_dim), dtype=torch.int8, device=dev, generator=gen)
+            vc = torch.randint(-127, 128, (T, c.n_kv_heads, c.head_dim), dtype=torch.int8, device=dev, generator=gen)
+            ks = torch.full((T, c.n_kv_heads, c.head_dim // 64), 0.01, dtype=torch.float16, device=dev).view(torch.int16)
+            vs = ks.clone()
+            cell = c.head_dim + c.head_dim // 64 * 2
+        else:
+            def plane():
+                t = torch.randint(0, 256, (T, c.n_kv_heads, c.head_dim // 32, 34), dtype=torch.uint8, device=dev, generator=gen)
+                t.view(torch.float16).reshape(T, c.n_kv_heads, c.head_dim // 32, 17)[..., 0] = 0.01
+                return t.reshape(T, c.n_kv_heads, c.head_dim // 32 * 34)
+            kc, vc, ks, vs = plane(), plane(), None, None
+            cell = c.head_dim // 32 * 34
+        out = torch.empty_like(q)
+        ws = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
+        return (lambda: ops.attend(q, kc, vc, k_scale=ks, v_scale=vs, range_begin=0, range_end=T, out=out, workspace=ws),
+                T * c.n_kv_heads * 2 * cell + 2 * q.numel() * 4)
     if op == "quantize_q8_k":
         x = N(gen, (T, 2560), 1.0, dev)                      # the reference's d_model
         return (lambda: ops.quantize_q8_k(x)), T * 2560 * 4 + T * 2560 // 256 * 292

@@ -309,6 +309,54 @@ def kv_read_f32(cache: torch.Tensor, *, scale: torch.Tensor | None = None, cells
     return out
 
 
+def attend(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, *, range_begin: int, range_end: int,
+           scale: float | None = None, k_scale: torch.Tensor | None = None, v_scale: torch.Tensor | None = None,
+           first_cell: torch.Tensor | None = None, n_cells: torch.Tensor | None = None, gate: torch.Tensor | None = None,
+           out: torch.Tensor | None = None, workspace: torch.Tensor | None = None, err: torch.Tensor | None = None):
+    """Decode attention of q [rows][n_q][hd] over cells [range_begin, range_end) of the cache planes new_kv_cache made
+    (Q8_0, or KV8 codes with k_scale / v_scale): the attention phase of fn::qsa::attn::attend for dense cell ranges.
+    Row t attends first_cell[t] .. + n_cells[t] (int32 device tensors) when given.  `workspace` (uint8) is reused when it
+    is large enough, else allocated.  Returns out [rows][n_q][hd]."""
+    _dev(q, torch.float32, "q")
+    if q.dim() != 3:
+        raise ValueError("q: expected [rows][n_q_heads][head_dim]")
+    rows, n_q, hd = q.shape
+    kv8 = k_scale is not None or v_scale is not None
+    _dev(k_cache, torch.int8 if kv8 else torch.uint8, "k_cache")
+    _dev(v_cache, torch.int8 if kv8 else torch.uint8, "v_cache")
+    if kv8:
+        _dev(k_scale, torch.int16, "k_scale")
+        _dev(v_scale, torch.int16, "v_scale")
+    slots, n_kv = k_cache.shape[0], k_cache.shape[1]
+    if v_cache.shape != k_cache.shape or k_cache.shape[2] != (hd if kv8 else hd // 32 * Q8_0_BLOCK):
+        raise ValueError("k_cache / v_cache: expected the planes of new_kv_cache for this head_dim")
+    for name, t in (("first_cell", first_cell), ("n_cells", n_cells)):
+        if t is not None:
+            _dev(t, torch.int32, name)
+            _numel(t, rows, name)
+    if gate is not None:
+        _dev(gate, torch.float32, "gate")
+        _numel(gate, q.numel(), "gate")
+    with torch.cuda.device(_same_device(q, k_cache, v_cache, k_scale, v_scale, first_cell, n_cells, gate, out, _err(err))):
+        if out is None:
+            out = torch.empty_like(q)
+        _dev(out, torch.float32, "out")
+        _numel(out, q.numel(), "out")
+        a = _lib.AttendArgs(_ptr(q).value, _ptr(gate).value, _ptr(k_cache).value, _ptr(v_cache).value, _ptr(k_scale).value,
+                            _ptr(v_scale).value, _ptr(first_cell).value, _ptr(n_cells).value, _ptr(out).value, None, 0,
+                            _ptr(err).value, slots, range_begin, range_end, rows, n_q, n_kv, hd,
+                            float(scale) if scale is not None else hd ** -0.5)
+        need = int(_lib.lib().fnb_attend_workspace_bytes(C.byref(a)))
+        if need == 0:
+            raise ValueError("attend: shape outside the contract")
+        if workspace is None or workspace.numel() < need:
+            workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+        _dev(workspace, torch.uint8, "workspace")
+        a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel()
+        _check(_lib.lib().fnb_attend(C.byref(a), _stream()), "attend")
+    return out
+
+
 def get_rows(fmt: str, table: torch.Tensor, ids: torch.Tensor, cols: int, out: torch.Tensor | None = None,
              err: torch.Tensor | None = None) -> torch.Tensor:
     """out[t] = dequantised row ids[t] of `table` (uint8 [n_vocab][row_bytes]); replaces fn::embed::embed_rows."""

@@ -291,6 +291,55 @@ typedef struct fnb_kv_read_args {
 int32_t fnb_kv_read_f32(const fnb_kv_read_args * args, void * stream);
 
 /*
+ * Decode attention over the cache the append entry points write: for each of `rows` query rows t and query head h,
+ *   out[t][h] = softmax over the row's cells c of (scale q[t][h] . K[c][g]) applied to V[c][g],  g = h / (n_q_heads / n_kv_heads),
+ * times sigmoid(gate[t][h]) when gate is given (the reference's output gate).  q [rows][n_q_heads][head_dim] F32 is the
+ * q_out of fnb_rope_neox_*_append (normed and roped); K and V are widened from the cache exactly as fnb_kv_read_f32
+ * widens them: Q8_0 cells (k_scale and v_scale null) or KV8 codes with their FP16 scale planes.  Row t attends cells
+ * first_cell[t] .. first_cell[t] + n_cells[t] - 1 (device arrays; null: every row attends the whole range); every row's
+ * cells must lie inside [range_begin, range_end), a host-known bound from which the split over cells is laid out (cells
+ * of the bound outside a row's own range are masked); a row range outside the cache sets FNB_ERR_SLOT and the row
+ * attends nothing; a row with no cell gives zeros.  F32 softmax statistics and accumulators; the products run on the
+ * tensor cores with every operand split into two FP16 halves (K's integer codes exact, each 32-value block's scale
+ * applied in F32), which keeps the reference's bound: max |error| / max |reference| <= 1e-5 per row and head against
+ * an FP64 evaluation over the decoded cache (fn/kernels/qsa/qa2_test.cpp:469-520).  Values whose magnitude exceeds
+ * FP16's range (65504) are outside the contract.
+ * head_dim 128 or 256; rows x (n_q_heads / n_kv_heads) <= 64; q, gate, out, caches 16-byte, scale planes 8-byte aligned.
+ * workspace: device memory of at least fnb_attend_workspace_bytes(args) bytes (16-byte aligned), the partial results of
+ * the split over cells, folded by a second kernel of the same call; its contents need no initialisation and mean
+ * nothing afterwards.  Calls that share a workspace must not overlap on the GPU.  The first call per device and shape
+ * class raises a kernel attribute (fnb_prepare_device covers it).
+ * Replaces the attention phase of fn::qsa::attn::attend for dense contiguous cell ranges (fn/kernels/qsa/attend.h:9-23,
+ * :141; cache decode fn/kernels/qsa/kv_q8.cuh:61-67); the reference's selection format, and its fused prepare phase
+ * (which fnb_rope_neox_*_append covers), are separate.
+ */
+typedef struct fnb_attend_args {
+    const float * q;
+    const float * gate;
+    const void * k_cache;
+    const void * v_cache;
+    const uint16_t * k_scale;
+    const uint16_t * v_scale;
+    const int32_t * first_cell;
+    const int32_t * n_cells;
+    float * out;
+    void * workspace;
+    size_t workspace_bytes;
+    uint32_t * err;
+    int64_t cache_slots;
+    int64_t range_begin;
+    int64_t range_end;
+    int32_t rows;
+    int32_t n_q_heads;
+    int32_t n_kv_heads;
+    int32_t head_dim;
+    float scale; /* the softmax scale, 1 / sqrt(head_dim) in the reference */
+} fnb_attend_args;
+
+size_t fnb_attend_workspace_bytes(const fnb_attend_args * args); /* 0 for a shape outside the contract */
+int32_t fnb_attend(const fnb_attend_args * args, void * stream);
+
+/*
  * F32 rows to ggml Q8_K blocks (292 bytes per 256 values: F32 d, 256 int8 codes, 16 int16 sums of 16 codes), the
  * activation format the routed experts' gate / up mat-vec reads on the reference's CPU tier.  Replaces
  * fn::experts::cpu::quantize_q8_k (fn/kernels/experts/cpu_kernels.h; cpu_iq_avx2.cpp:583-646) and ggml's

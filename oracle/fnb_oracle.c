@@ -13,6 +13,7 @@
 #include "fnb_oracle.h"
 
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "fnb_exact_math.h"
@@ -842,5 +843,47 @@ void fnbo_expert_gu_rows_iq3_s(const uint8_t * gate, const uint8_t * up, int64_t
                 gu[((int64_t) nt + t) * ff_stride + r] = u;
             }
         }
+    }
+}
+
+/* fn/kernels/qsa/attend.h:17-19 (o = softmax(q . K / 16) . V, out = o sigmoid(gate)), every sum in double, the
+ * maximum subtracted before the exponentials: the FP64 statement the reference's qa2-test checks its kernel against
+ * (fn/kernels/qsa/qa2_test.cpp:469-520) */
+void fnbo_attend_f64(const float * q, const float * gate, const float * k, const float * v, const int32_t * first,
+                     const int32_t * count, int32_t rows, int32_t n_q, int32_t n_kv, int32_t hd, double scale, double * out) {
+    const int rep = n_q / n_kv;
+    for (int t = 0; t < rows; ++t) {
+        const int64_t c0 = first[t], n = count[t];
+        double * s = (double *) malloc(sizeof(double) * (size_t) (n > 0 ? n : 1));
+        for (int h = 0; h < n_q; ++h) {
+            const int g = h / rep;
+            const float * qr = q + ((size_t) t * n_q + h) * hd;
+            double * o = out + ((size_t) t * n_q + h) * hd;
+            for (int d = 0; d < hd; ++d) o[d] = 0.0;
+            if (n <= 0) continue;
+            double mx = -INFINITY;
+            for (int64_t c = 0; c < n; ++c) {
+                const float * kr = k + ((size_t) (c0 + c) * n_kv + g) * hd;
+                double acc = 0.0;
+                for (int d = 0; d < hd; ++d) acc += (double) qr[d] * (double) kr[d];
+                s[c] = acc * scale;
+                if (s[c] > mx) mx = s[c];
+            }
+            double l = 0.0;
+            for (int64_t c = 0; c < n; ++c) {
+                s[c] = exp(s[c] - mx);
+                l += s[c];
+            }
+            for (int64_t c = 0; c < n; ++c) {
+                const float * vr = v + ((size_t) (c0 + c) * n_kv + g) * hd;
+                const double p = s[c] / l;
+                for (int d = 0; d < hd; ++d) o[d] += p * (double) vr[d];
+            }
+            if (gate) {
+                const float * gr = gate + ((size_t) t * n_q + h) * hd;
+                for (int d = 0; d < hd; ++d) o[d] *= 1.0 / (1.0 + exp(-(double) gr[d]));
+            }
+        }
+        free(s);
     }
 }

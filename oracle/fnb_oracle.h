@@ -137,6 +137,13 @@ void fnbo_expert_down_rows_q2_0(const uint8_t * w, int64_t row_bytes, int32_t n,
                                 const float * scale, int64_t scale_stride, int32_t nt, float * out, int64_t out_stride,
                                 int64_t r0, int64_t r1);
 
+/* Decode attention in FP64 over already decoded cache rows (the reference's test protocol, fn/kernels/qsa/
+ * qa2_test.cpp:469-520, written from the definition in fn/kernels/qsa/attend.h:9-23): for row t and query head h,
+ * out = softmax_c(scale q . K[c][g]) . V[c][g] over cells first[t] .. first[t] + count[t] - 1, g = h / (n_q / n_kv),
+ * times sigmoid(gate) when gate is given.  k, v: F32 [cells][n_kv][hd] (cell index = absolute cache cell); out: F64. */
+void fnbo_attend_f64(const float * q, const float * gate, const float * k, const float * v, const int32_t * first,
+                     const int32_t * count, int32_t rows, int32_t n_q, int32_t n_kv, int32_t hd, double scale, double * out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -426,6 +426,23 @@ def rope_kv_append(q, k, v, pos, *, n_rot: int, theta_scale: float, k_cache: np.
     return q_out, k_f32, int(err[0])
 
 
+def attend_f64(q, k, v, first, count, scale: float, gate=None) -> np.ndarray:
+    """FP64 attention over decoded cache rows: q [rows][n_q][hd], k / v F32 [cells][n_kv][hd] (absolute cells), row t over
+    cells first[t] .. first[t] + count[t] - 1.  Returns float64 [rows][n_q][hd]."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    rows, n_q, hd = q.shape
+    n_kv = k.shape[1]
+    first = np.ascontiguousarray(first, np.int32)
+    count = np.ascontiguousarray(count, np.int32)
+    g = None if gate is None else _f32(gate)
+    out = np.zeros((rows, n_q, hd), np.float64)
+    l = lib()
+    l.fnbo_attend_f64.restype = None
+    l.fnbo_attend_f64.argtypes = [C.c_void_p] * 6 + [C.c_int32] * 4 + [C.c_double, C.c_void_p]
+    l.fnbo_attend_f64(_p(q), _p(g), _p(k), _p(v), _p(first), _p(count), rows, n_q, n_kv, hd, scale, _p(out))
+    return out
+
+
 def theta_scale(freq_base: float, n_rot: int) -> float:
     """powf(freq_base, -2/n_rot) in F32, as fn/kernels/qsa/attend.cu:830-832 computes it on the host."""
     l = lib()
