@@ -21,11 +21,13 @@
 //     FP16's subnormals), so p . V costs three (the lo x lo term is below 2^-22).
 //   * One warp owns 16 query rows (an m16n8k16 tile row) and all head_dim output columns: its running maximum, sum and
 //     output accumulators never leave registers.  A CTA's four warps take up to four such row tiles; with one or two
-//     row tiles the warps split the CTA's 64-cell tile in halves, each half an independent partial result.
+//     row tiles the warps split the CTA's 64-cell tile four or two ways instead, each part an independent partial
+//     result, so that all four tensor cores work whatever the number of rows.  A warp walks its cells in steps of 16
+//     (two score tiles, one step of the output product), with the online-softmax update per step.
 //   * Cells arrive by 16-byte cp.async into a two-stage ring of raw tiles (the next tile's copies are in flight while
 //     this one is computed); all 128 threads widen a raw tile into the operand tiles (XOR-swizzled rows, so that
 //     ldmatrix is conflict-free), K first, then V into the same shared memory once the scores are done.
-//   * Split over cells (flash decoding): a work unit is (KV head, range of cells); units and tile halves write
+//   * Split over cells (flash decoding): a work unit is (KV head, range of cells); units and tile parts write
 //     (max, sum, unnormalised output) partials into a caller-supplied workspace, and a second small kernel folds them
 //     in a fixed order, divides, gates and writes the rows.  The workspace is the only global memory beyond inputs and
 //     outputs; its size is a function of the shape (fnb_attend_workspace_bytes).
@@ -42,17 +44,17 @@ namespace {
 
 constexpr int kWarps = 4;
 constexpr int kThreads = kWarps * 32;
-constexpr int kSub = 32;   // cells a warp's tensor tile covers
-constexpr int kTile = 64;  // cells a CTA stages at once: two sub-tiles
+constexpr int kStep = 16;  // cells of one step of a warp: two 8-cell score tiles, one k-step of the output product
+constexpr int kTile = 64;  // cells a CTA stages at once: four steps
 constexpr int kMaxM = 64;  // query rows of one KV head's group: rows x (n_q_heads / n_kv_heads)
 constexpr float kPScale = 4096.0f, kPUnscale = 1.0f / 4096.0f;
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct attend_plan {
-    int m, m_tiles, halves;  // query rows per group, their 16-row tiles, partial results a unit writes (1 or 2)
+    int m, m_tiles, parts;   // query rows per group, their 16-row tiles, partial results a unit writes (1, 2 or 4)
     int64_t unit_cells;      // cells per work unit (a multiple of kTile)
     int n_units;             // units per KV head
-    int64_t slots;           // partial results in the workspace: n_kv x n_units x halves
+    int64_t slots;           // partial results in the workspace: n_kv x n_units x parts
 };
 
 // the split the launcher and the workspace size agree on: about two units per SM over all KV heads, never shorter
@@ -61,14 +63,14 @@ inline attend_plan make_plan(int rows, int n_q, int n_kv, int64_t range) {
     attend_plan p;
     p.m = rows * (n_q / n_kv);
     p.m_tiles = (p.m + 15) / 16;
-    p.halves = p.m_tiles <= 2 ? 2 : 1;
+    p.parts = p.m_tiles == 1 ? 4 : p.m_tiles == 2 ? 2 : 1;
     int64_t want = (2 * int64_t(kSmCount) + n_kv - 1) / n_kv;
     int64_t cells = (range + want - 1) / want;
     cells = cells < 256 ? 256 : cells;
     p.unit_cells = (cells + kTile - 1) / kTile * kTile;
     p.n_units = int((range + p.unit_cells - 1) / p.unit_cells);
     if (p.n_units < 1) p.n_units = 1;
-    p.slots = int64_t(n_kv) * p.n_units * p.halves;
+    p.slots = int64_t(n_kv) * p.n_units * p.parts;
     return p;
 }
 inline size_t plan_bytes(const attend_plan & p, int head_dim) { return size_t(p.slots) * p.m * (head_dim + 2) * 4; }
@@ -87,7 +89,7 @@ struct attend_params {
     float * ws_acc;  // [slots][m][head_dim]
     uint32_t * err;
     int64_t cache_slots, range_begin, range_end, unit_cells;
-    int rows, n_q, n_kv, n_rep, m, m_tiles, halves, n_units;
+    int rows, n_q, n_kv, n_rep, m, m_tiles, parts, n_units;
     float scale_log2;  // softmax scale x log2(e)
 };
 
@@ -229,9 +231,10 @@ __global__ void __launch_bounds__(kThreads, 1) attend_kernel(const attend_params
 
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int g = lane >> 2, t4 = lane & 3;
-    // this warp's row tile and the half of the CTA tile it multiplies (both halves when there are 3 or 4 row tiles)
-    const int mt = p.halves == 2 ? (wid % 2) : wid;
-    const int half0 = p.halves == 2 ? wid / 2 : 0, n_half = p.halves == 2 ? 1 : 2;
+    // this warp's row tile and its steps of the CTA tile: one row tile -> a step each, two -> two each, more -> all four
+    const int mt = p.parts == 4 ? 0 : p.parts == 2 ? (wid & 1) : wid;
+    const int part = p.parts == 4 ? wid : p.parts == 2 ? (wid >> 1) : 0;
+    const int n_steps = 4 / p.parts, step0 = part * n_steps;
     const bool mma_warp = mt < p.m_tiles;
     const int r0 = 16 * mt + g, r1 = r0 + 8;  // the two query rows this lane's accumulators belong to
 
@@ -285,15 +288,22 @@ __global__ void __launch_bounds__(kThreads, 1) attend_kernel(const attend_params
         auto issue = [&](int tile, int st) {
             uint8_t * base = smem + L::raw + st * 2 * L::kRawTensor;
             const int64_t c0 = c_begin + int64_t(tile) * kTile;
-            constexpr int kChunks = L::kCell / 16;  // 17 (Q8_0 at 256), 16 (KV8 at 256)
+            // a 256-wide Q8_0 cell is 272 bytes = 17 x 16; a 128-wide one 136 = 17 x 8, only 8-byte aligned
+            constexpr int kPiece = L::kCell % 16 == 0 ? 16 : 8;
+            constexpr int kChunks = L::kCell / kPiece;
 #pragma unroll 1
             for (int i = tid; i < 2 * kTile * kChunks; i += kThreads) {
                 const int tensor = i / (kTile * kChunks), rem = i - tensor * (kTile * kChunks);
                 const int cell = rem / kChunks, ch = rem - cell * kChunks;
                 const int64_t c = c0 + cell;
                 const bool valid = c < c_end;
-                const uint8_t * src = (tensor == 0 ? p.k_cache : p.v_cache) + ((valid ? c : c_begin) * p.n_kv + head) * L::kCell + 16 * ch;
-                cp_async16(base + tensor * L::kRawTensor + cell * L::kCell + 16 * ch, src, valid);
+                const uint8_t * src = (tensor == 0 ? p.k_cache : p.v_cache) + ((valid ? c : c_begin) * p.n_kv + head) * L::kCell + kPiece * ch;
+                uint8_t * dst = base + tensor * L::kRawTensor + cell * L::kCell + kPiece * ch;
+                if (kPiece == 16) {
+                    cp_async16(dst, src, valid);
+                } else {
+                    cp_async8(dst, src, valid);
+                }
             }
             if (KV8) {
                 for (int i = tid; i < 2 * kTile; i += kThreads) {
@@ -347,43 +357,40 @@ __global__ void __launch_bounds__(kThreads, 1) attend_kernel(const attend_params
             }
             __syncthreads();
 
-            // ---- scores, softmax and the P operands, per half of the tile ----
-            uint32_t p_hi[2][2][4], p_lo[2][2][4];  // [half][16-cell step][A fragment]
-            float alpha[2][2];
+            // ---- scores, softmax and the P operands, step by step ----
+            uint32_t p_hi[4][4], p_lo[4][4];  // [step][A fragment]
+            float alpha[4][2];
+            const int lo0 = row_lo[r0], hi0 = row_hi[r0], lo1 = row_lo[r1], hi1 = row_hi[r1];
 #pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                if (hh >= n_half) break;
-                const int cell0 = (half0 + hh) * kSub;  // first cell of this sub-tile within the tile
-                float s[4][4];
+            for (int st4 = 0; st4 < 4; ++st4) {
+                if (st4 >= n_steps) break;
+                const int cell0 = (step0 + st4) * kStep;  // first cell of this step within the tile
+                float s[2][4];
 #pragma unroll
-                for (int n = 0; n < 4; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
+                for (int n = 0; n < 2; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
                 if (mma_warp) {
 #pragma unroll
                     for (int b = 0; b < NB; ++b) {
-                        float part[4][4];
+                        float blk[2][4];
 #pragma unroll
-                        for (int n = 0; n < 4; ++n) part[n][0] = part[n][1] = part[n][2] = part[n][3] = 0.0f;
+                        for (int n = 0; n < 2; ++n) blk[n][0] = blk[n][1] = blk[n][2] = blk[n][3] = 0.0f;
 #pragma unroll
                         for (int kk = 0; kk < 2; ++kk) {
                             const int ks = 2 * b + kk;
-                            uint32_t ah[4], al[4];
+                            uint32_t ah[4], al[4], kb[4];
                             const int arow = 16 * mt + (lane & 15), achunk = 2 * ks + (lane >> 4);
                             ldsm4(ah, s_addr(q_hi + swz<kRow>(arow, achunk)));
                             ldsm4(al, s_addr(q_lo + swz<kRow>(arow, achunk)));
-#pragma unroll
-                            for (int np = 0; np < 2; ++np) {
-                                uint32_t kb[4];
-                                const int krow = cell0 + 16 * np + (lane & 7) + 8 * (lane >> 4), kchunk = 2 * ks + ((lane >> 3) & 1);
-                                ldsm4(kb, s_addr(op + swz<kRow>(krow, kchunk)));
-                                mma16816(part[2 * np], ah, kb[0], kb[1]);
-                                mma16816(part[2 * np], al, kb[0], kb[1]);
-                                mma16816(part[2 * np + 1], ah, kb[2], kb[3]);
-                                mma16816(part[2 * np + 1], al, kb[2], kb[3]);
-                            }
+                            const int krow = cell0 + (lane & 7) + 8 * (lane >> 4), kchunk = 2 * ks + ((lane >> 3) & 1);
+                            ldsm4(kb, s_addr(op + swz<kRow>(krow, kchunk)));
+                            mma16816(blk[0], ah, kb[0], kb[1]);
+                            mma16816(blk[0], al, kb[0], kb[1]);
+                            mma16816(blk[1], ah, kb[2], kb[3]);
+                            mma16816(blk[1], al, kb[2], kb[3]);
                         }
                         // the block's scale of this lane's two cells of each 8-cell tile
 #pragma unroll
-                        for (int n = 0; n < 4; ++n) {
+                        for (int n = 0; n < 2; ++n) {
                             const int c = cell0 + 8 * n + 2 * t4;
                             float d0, d1;
                             if (KV8) {
@@ -393,16 +400,15 @@ __global__ void __launch_bounds__(kThreads, 1) attend_kernel(const attend_params
                                 d0 = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(raw_k + c * L::kCell + 34 * b));
                                 d1 = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(raw_k + (c + 1) * L::kCell + 34 * b));
                             }
-                            s[n][0] = fmaf(part[n][0], d0, s[n][0]), s[n][1] = fmaf(part[n][1], d1, s[n][1]);
-                            s[n][2] = fmaf(part[n][2], d0, s[n][2]), s[n][3] = fmaf(part[n][3], d1, s[n][3]);
+                            s[n][0] = fmaf(blk[n][0], d0, s[n][0]), s[n][1] = fmaf(blk[n][1], d1, s[n][1]);
+                            s[n][2] = fmaf(blk[n][2], d0, s[n][2]), s[n][3] = fmaf(blk[n][3], d1, s[n][3]);
                         }
                     }
                 }
                 // mask, running maximum, probabilities (rows r0 and r1; log2 units)
-                const int lo0 = row_lo[r0], hi0 = row_hi[r0], lo1 = row_lo[r1], hi1 = row_hi[r1];
                 float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-                for (int n = 0; n < 4; ++n) {
+                for (int n = 0; n < 2; ++n) {
 #pragma unroll
                     for (int j = 0; j < 2; ++j) {
                         const int64_t c = tile_c0 + cell0 + 8 * n + 2 * t4 + j;
@@ -416,29 +422,25 @@ __global__ void __launch_bounds__(kThreads, 1) attend_kernel(const attend_params
                 const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
                 // a row with no live cell so far keeps reference 0 (exp2 of -inf is 0; -inf minus -inf is never formed)
                 const float ref0 = mn0 == -INFINITY ? 0.0f : mn0, ref1 = mn1 == -INFINITY ? 0.0f : mn1;
-                alpha[hh][0] = fast_exp2(m_run[0] - ref0), alpha[hh][1] = fast_exp2(m_run[1] - ref1);
+                alpha[st4][0] = fast_exp2(m_run[0] - ref0), alpha[st4][1] = fast_exp2(m_run[1] - ref1);
                 m_run[0] = mn0, m_run[1] = mn1;
-                float sum0 = 0.0f, sum1 = 0.0f;
-                float pr[4][4];
+                float pr[2][4];
 #pragma unroll
-                for (int n = 0; n < 4; ++n) {
+                for (int n = 0; n < 2; ++n) {
                     pr[n][0] = fast_exp2(s[n][0] - ref0), pr[n][1] = fast_exp2(s[n][1] - ref0);
                     pr[n][2] = fast_exp2(s[n][2] - ref1), pr[n][3] = fast_exp2(s[n][3] - ref1);
-                    sum0 += pr[n][0] + pr[n][1], sum1 += pr[n][2] + pr[n][3];
                 }
-                l_run[0] = l_run[0] * alpha[hh][0] + sum0, l_run[1] = l_run[1] * alpha[hh][1] + sum1;
-                // P as A fragments of the two 16-cell steps: hi + lo of p x 2^12
+                l_run[0] = l_run[0] * alpha[st4][0] + ((pr[0][0] + pr[0][1]) + (pr[1][0] + pr[1][1]));
+                l_run[1] = l_run[1] * alpha[st4][1] + ((pr[0][2] + pr[0][3]) + (pr[1][2] + pr[1][3]));
+                // P as the A fragment of the step: hi + lo of p x 2^12
 #pragma unroll
-                for (int kc = 0; kc < 2; ++kc) {
-#pragma unroll
-                    for (int f = 0; f < 4; ++f) {
-                        const int n = 2 * kc + (f >> 1), jb = (f & 1) * 2;  // a0: (g, n), a1: (g + 8, n), a2: (g, n + 1), a3: (g + 8, n + 1)
-                        const float x = pr[n][jb] * kPScale, y = pr[n][jb + 1] * kPScale;
-                        const __half2 hv = __floats2half2_rn(x, y);
-                        const float2 back = __half22float2(hv);
-                        p_hi[hh][kc][f] = h2_bits(hv);
-                        p_lo[hh][kc][f] = h2_bits(__floats2half2_rn(x - back.x, y - back.y));
-                    }
+                for (int f = 0; f < 4; ++f) {
+                    const int n = f >> 1, jb = (f & 1) * 2;  // a0: (g, tile 0), a1: (g + 8, tile 0), a2: (g, tile 1), a3: (g + 8, tile 1)
+                    const float x = pr[n][jb] * kPScale, y = pr[n][jb + 1] * kPScale;
+                    const __half2 hv = __floats2half2_rn(x, y);
+                    const float2 back = __half22float2(hv);
+                    p_hi[st4][f] = h2_bits(hv);
+                    p_lo[st4][f] = h2_bits(__floats2half2_rn(x - back.x, y - back.y));
                 }
             }
             __syncthreads();  // every warp is done with the K operand tile
@@ -471,29 +473,29 @@ __global__ void __launch_bounds__(kThreads, 1) attend_kernel(const attend_params
             // ---- outputs: o = o alpha + (p_hi + p_lo) (v_hi + v_lo) without the lo x lo term ----
             if (mma_warp) {
 #pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    if (hh >= n_half) break;
-                    const int cell0 = (half0 + hh) * kSub;
+                for (int st4 = 0; st4 < 4; ++st4) {
+                    if (st4 >= n_steps) break;
+                    const int cell0 = (step0 + st4) * kStep;
+                    // the maximum seldom moves once a few tiles are in: skip the rescaling when no row of the warp needs it
+                    if (__any_sync(kFull, alpha[st4][0] != 1.0f || alpha[st4][1] != 1.0f)) {
 #pragma unroll
-                    for (int d = 0; d < NT; ++d) {
-                        o[d][0] *= alpha[hh][0], o[d][1] *= alpha[hh][0];
-                        o[d][2] *= alpha[hh][1], o[d][3] *= alpha[hh][1];
+                        for (int d = 0; d < NT; ++d) {
+                            o[d][0] *= alpha[st4][0], o[d][1] *= alpha[st4][0];
+                            o[d][2] *= alpha[st4][1], o[d][3] *= alpha[st4][1];
+                        }
                     }
 #pragma unroll
-                    for (int kc = 0; kc < 2; ++kc) {
-#pragma unroll
-                        for (int dp = 0; dp < NT / 2; ++dp) {
-                            uint32_t bh[4], bl[4];
-                            const int vrow = cell0 + 16 * kc + (lane & 7) + 8 * ((lane >> 3) & 1), vchunk = 2 * dp + (lane >> 4);
-                            ldsm4_t(bh, s_addr(v_hi + swz<kRow>(vrow, vchunk)));
-                            ldsm4_t(bl, s_addr(v_lo + swz<kRow>(vrow, vchunk)));
-                            mma16816(o[2 * dp], p_hi[hh][kc], bh[0], bh[1]);
-                            mma16816(o[2 * dp], p_lo[hh][kc], bh[0], bh[1]);
-                            mma16816(o[2 * dp], p_hi[hh][kc], bl[0], bl[1]);
-                            mma16816(o[2 * dp + 1], p_hi[hh][kc], bh[2], bh[3]);
-                            mma16816(o[2 * dp + 1], p_lo[hh][kc], bh[2], bh[3]);
-                            mma16816(o[2 * dp + 1], p_hi[hh][kc], bl[2], bl[3]);
-                        }
+                    for (int dp = 0; dp < NT / 2; ++dp) {
+                        uint32_t bh[4], bl[4];
+                        const int vrow = cell0 + (lane & 7) + 8 * ((lane >> 3) & 1), vchunk = 2 * dp + (lane >> 4);
+                        ldsm4_t(bh, s_addr(v_hi + swz<kRow>(vrow, vchunk)));
+                        ldsm4_t(bl, s_addr(v_lo + swz<kRow>(vrow, vchunk)));
+                        mma16816(o[2 * dp], p_hi[st4], bh[0], bh[1]);
+                        mma16816(o[2 * dp], p_lo[st4], bh[0], bh[1]);
+                        mma16816(o[2 * dp], p_hi[st4], bl[0], bl[1]);
+                        mma16816(o[2 * dp + 1], p_hi[st4], bh[2], bh[3]);
+                        mma16816(o[2 * dp + 1], p_lo[st4], bh[2], bh[3]);
+                        mma16816(o[2 * dp + 1], p_hi[st4], bl[2], bl[3]);
                     }
                 }
             }
@@ -504,7 +506,7 @@ __global__ void __launch_bounds__(kThreads, 1) attend_kernel(const attend_params
             float l0 = l_run[0], l1 = l_run[1];
             l0 += __shfl_xor_sync(kFull, l0, 1), l0 += __shfl_xor_sync(kFull, l0, 2);
             l1 += __shfl_xor_sync(kFull, l1, 1), l1 += __shfl_xor_sync(kFull, l1, 2);
-            const int64_t slot = (int64_t(head) * p.n_units + u) * p.halves + (p.halves == 2 ? half0 : 0);
+            const int64_t slot = (int64_t(head) * p.n_units + u) * p.parts + part;
             float * ml = p.ws_ml + slot * p.m * 2;
             float * acc = p.ws_acc + slot * p.m * HD;
             if (r0 < p.m) {
@@ -526,27 +528,54 @@ __global__ void __launch_bounds__(kThreads, 1) attend_kernel(const attend_params
 }
 
 // ---- the fold: one CTA a (row, query head), one thread a value ------------------------------------------------------
+// M = max m_j, L = sum l_j 2^(m_j - M), A = sum acc_j 2^(m_j - M) over the row's partials j in slot order.  The weights
+// are formed once per CTA in shared memory (slots in parallel), then every thread streams its column of the partials
+// with independent loads.
+constexpr int kFoldMaxSlots = 4096;
+
 template <int HD>
 __global__ void __launch_bounds__(HD) attend_fold_kernel(const attend_params p) {
+    __shared__ float w_of[kFoldMaxSlots];
+    __shared__ float red[HD / 32];
     const int t = blockIdx.x / p.n_q, h = blockIdx.x - t * p.n_q;
     const int head = h / p.n_rep, row = t * p.n_rep + (h - head * p.n_rep);
-    const int d = threadIdx.x;
-    const int n = p.n_units * p.halves;
+    const int d = threadIdx.x, lane = d & 31, wid = d >> 5;
+    const int n = p.n_units * p.parts;
     const int64_t slot0 = int64_t(head) * n;
-    // M = max m_j, L = sum l_j 2^(m_j - M), A = sum acc_j 2^(m_j - M), in slot order
     float big = -INFINITY;
-    for (int j = 0; j < n; ++j) big = fmaxf(big, __ldg(p.ws_ml + ((slot0 + j) * p.m + row) * 2));
-    float sum = 0.0f, a = 0.0f;
-    if (big != -INFINITY) {
-        for (int j = 0; j < n; ++j) {
-            const float * ml = p.ws_ml + ((slot0 + j) * p.m + row) * 2;
-            const float mj = __ldg(ml);
-            if (mj == -INFINITY) continue;  // a partial with no live cell for this row
-            const float w = fast_exp2(mj - big);
-            sum = fmaf(__ldg(ml + 1), w, sum);
-            a = fmaf(__ldg(p.ws_acc + ((slot0 + j) * p.m + row) * HD + d), w, a);
-        }
+    for (int j = d; j < n; j += HD) {
+        const float mj = __ldg(p.ws_ml + ((slot0 + j) * p.m + row) * 2);
+        w_of[j] = mj;
+        big = fmaxf(big, mj);
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) big = fmaxf(big, __shfl_xor_sync(kFull, big, o));
+    if (lane == 0) red[wid] = big;
+    __syncthreads();
+    big = red[0];
+#pragma unroll
+    for (int i = 1; i < HD / 32; ++i) big = fmaxf(big, red[i]);
+    __syncthreads();
+    // weights (0 for a partial with no live cell for this row, and for every partial of a row with none at all)
+    float part_sum = 0.0f;
+    for (int j = d; j < n; j += HD) {
+        const float mj = w_of[j];
+        const float w = mj == -INFINITY ? 0.0f : fast_exp2(mj - big);
+        w_of[j] = w;
+        part_sum = fmaf(__ldg(p.ws_ml + ((slot0 + j) * p.m + row) * 2 + 1), w, part_sum);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part_sum += __shfl_xor_sync(kFull, part_sum, o);
+    if (lane == 0) red[wid] = part_sum;
+    __syncthreads();
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < HD / 32; ++i) sum += red[i];
+    float a = 0.0f;
+    const float * col = p.ws_acc + (slot0 * p.m + row) * HD + d;
+    const int64_t stride = int64_t(p.m) * HD;
+#pragma unroll 8
+    for (int j = 0; j < n; ++j) a = fmaf(__ldg(col + j * stride), w_of[j], a);
     float y = sum > 0.0f ? a / sum : 0.0f;  // a row with no cell at all gives zeros
     const int64_t at = (int64_t(t) * p.n_q + h) * HD + d;
     if (p.gate != nullptr) y *= 1.0f / (1.0f + expf(-__ldg(p.gate + at)));
@@ -605,6 +634,7 @@ int32_t attend_launch(const fnb_attend_args * a, void * ws, size_t ws_bytes, cud
     if (!ok_opt(a->first_cell, 4) || !ok_opt(a->n_cells, 4) || !ok_opt(a->err, 4)) return FNB_REJECTED;
     if (!(a->scale > 0.0f) || !(a->scale < INFINITY)) return FNB_REJECTED;
     const attend_plan plan = make_plan(a->rows, a->n_q_heads, a->n_kv_heads, a->range_end - a->range_begin);
+    if (plan.n_units * plan.parts > kFoldMaxSlots) return FNB_REJECTED;  // cannot happen with the plan's two units an SM
     if (!ok_ptr(ws, 16) || ws_bytes < plan_bytes(plan, a->head_dim)) return FNB_REJECTED;
 
     attend_params p;
@@ -616,7 +646,7 @@ int32_t attend_launch(const fnb_attend_args * a, void * ws, size_t ws_bytes, cud
     p.ws_acc = p.ws_ml + plan.slots * plan.m * 2;
     p.cache_slots = a->cache_slots, p.range_begin = a->range_begin, p.range_end = a->range_end, p.unit_cells = plan.unit_cells;
     p.rows = a->rows, p.n_q = a->n_q_heads, p.n_kv = a->n_kv_heads, p.n_rep = a->n_q_heads / a->n_kv_heads;
-    p.m = plan.m, p.m_tiles = plan.m_tiles, p.halves = plan.halves, p.n_units = plan.n_units;
+    p.m = plan.m, p.m_tiles = plan.m_tiles, p.parts = plan.parts, p.n_units = plan.n_units;
     p.scale_log2 = a->scale * kLog2e;
     if (a->head_dim == 256) return kv8 ? launch_hd<256, true>(p, s) : launch_hd<256, false>(p, s);
     return kv8 ? launch_hd<128, true>(p, s) : launch_hd<128, false>(p, s);
