@@ -93,6 +93,7 @@ SIGNATURES = {
     "fnb_kv_read_f32": (_I32, [C.POINTER(KvReadArgs), _P]),
     "fnb_attend_workspace_bytes": (C.c_size_t, [C.POINTER(AttendArgs)]),
     "fnb_attend": (_I32, [C.POINTER(AttendArgs), _P]),
+    "fnb_attend_static": (_I32, [C.POINTER(AttendArgs), _P]),
     "fnb_quantize_q8_k": (_I32, [_P, _P, _I64, _I32, _P]),
     "fnb_expert_gate_up_rows_q4_k": (_I32, [_P, _P, _I64, _I32, _P, _I64, _I32, _P, _I64, _P, _I64, _I64, _P]),
     "fnb_expert_gate_up_rows_q5_k": (_I32, [_P, _P, _I64, _I32, _P, _I64, _I32, _P, _I64, _P, _I64, _I64, _P]),

@@ -34,6 +34,7 @@
 //
 // No kernel here waits on another: the fold is a second launch on the same stream.
 #include <atomic>
+#include <cstdio>
 
 #include <cuda_fp16.h>
 
@@ -659,7 +660,53 @@ size_t attend_workspace_bytes(const fnb_attend_args * a) {
 
 }  // namespace fnb
 
+// ---- the same attention for callers with no workspace to give ----------------------------------------------------------
+// Some callers cannot hand in a workspace and cannot get one: an engine that reserves all of its device memory once at
+// load and has nothing left to carve from, a plug-in whose host forbids device allocation on the serving path (an
+// allocation synchronises the whole device and can fail long after start-up).  For them the partial results live in
+// this fixed array, part of the library's image: every GPU that loads the library holds these bytes until the process
+// ends, whether or not this entry point is ever called.
+#define FNB_ATTEND_STATIC_SCRATCH_BYTES (16u << 20)
+static __device__ __align__(256) unsigned char g_attend_scratch[FNB_ATTEND_STATIC_SCRATCH_BYTES];
+
+namespace fnb {
+namespace {
+
+// The array's name is only a host-side handle here: its device address has to be asked for, once per device, with
+// that device current.  nullptr when the runtime refuses.
+void * attend_static_scratch() {
+    static std::atomic<void *> addr_of[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    void * p = addr_of[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
+        if (cudaGetSymbolAddress(&p, g_attend_scratch) != cudaSuccess || p == nullptr) {
+            (void) cudaGetLastError();
+            return nullptr;
+        }
+        addr_of[dev].store(p, std::memory_order_release);
+    }
+    return p;
+}
+
+}  // namespace
+}  // namespace fnb
+
 extern "C" size_t fnb_attend_workspace_bytes(const fnb_attend_args * args) { return fnb::attend_workspace_bytes(args); }
+
+extern "C" int32_t fnb_attend_static(const fnb_attend_args * args, void * stream) {
+    if (args == nullptr) return FNB_REJECTED;
+    const size_t need = fnb::attend_workspace_bytes(args);
+    if (need == 0) return FNB_REJECTED;
+    if (need > size_t(FNB_ATTEND_STATIC_SCRATCH_BYTES)) {
+        fprintf(stderr, "fnb_attend_static: this shape needs %zu bytes of partial results, the built-in scratch holds %u; "
+                        "use fnb_attend with a workspace\n", need, unsigned(FNB_ATTEND_STATIC_SCRATCH_BYTES));
+        return FNB_REJECTED;
+    }
+    void * scratch = fnb::attend_static_scratch();
+    if (scratch == nullptr) return FNB_LAUNCH_FAILED;
+    return fnb::attend_launch(args, scratch, size_t(FNB_ATTEND_STATIC_SCRATCH_BYTES), static_cast<cudaStream_t>(stream));
+}
 
 extern "C" int32_t fnb_attend(const fnb_attend_args * args, void * stream) {
     if (args == nullptr) return FNB_REJECTED;

@@ -340,6 +340,26 @@ size_t fnb_attend_workspace_bytes(const fnb_attend_args * args); /* 0 for a shap
 int32_t fnb_attend(const fnb_attend_args * args, void * stream);
 
 /*
+ * fnb_attend for callers that have no workspace to pass and cannot allocate one.  It has no counterpart in the
+ * reference (whose attention takes a caller-carved workspace, fn/kernels/qsa/attend.h:84-96).  Who needs it: an engine
+ * that reserves all its device memory once at load and has none left to carve from; a plug-in whose host forbids
+ * device allocation on the serving path, where an allocation stalls every stream of the device and may fail long after
+ * start-up.  The partial results of the split over cells go into a fixed 16 MiB array inside the library's device
+ * image instead of args->workspace (workspace and workspace_bytes are ignored): every GPU that loads the library holds
+ * those 16 MiB until the process exits, used or not.  Same arguments, results (bit for bit) and return codes as
+ * fnb_attend otherwise.
+ *   - A shape whose partial results need more than 16 MiB (fnb_attend_workspace_bytes(args) > 16 << 20: very many KV
+ *     heads or rows on a long range) is refused with FNB_REJECTED and one line on stderr; use fnb_attend for those.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *     current, checked); make that first call before any stream capture.  No call allocates or frees anything.
+ *   - All calls share the one array per device and it keeps whatever the last call left there.  Nothing in it has to
+ *     start at zero (every partial a call reads, that call wrote), so nothing is cleared; but two calls that overlap
+ *     on the GPU (different streams, or one stream's graph branches) race on it.  Serialise them, or give all but one a
+ *     workspace of their own through fnb_attend.
+ */
+int32_t fnb_attend_static(const fnb_attend_args * args, void * stream);
+
+/*
  * F32 rows to ggml Q8_K blocks (292 bytes per 256 values: F32 d, 256 int8 codes, 16 int16 sums of 16 codes), the
  * activation format the routed experts' gate / up mat-vec reads on the reference's CPU tier.  Replaces
  * fn::experts::cpu::quantize_q8_k (fn/kernels/experts/cpu_kernels.h; cpu_iq_avx2.cpp:583-646) and ggml's
