@@ -99,6 +99,9 @@ SIGNATURES = {
     "fnb_expert_gate_up_rows_q5_k": (_I32, [_P, _P, _I64, _I32, _P, _I64, _I32, _P, _I64, _P, _I64, _I64, _P]),
     "fnb_expert_gate_up_rows_iq3_s": (_I32, [_P, _P, _I64, _I32, _P, _I64, _I32, _P, _I64, _P, _I64, _I64, _P]),
     "fnb_expert_gate_up_rows_iq3_xxs": (_I32, [_P, _P, _I64, _I32, _P, _I64, _I32, _P, _I64, _P, _I64, _I64, _P]),
+    "fnb_expert_gate_up_rows_iq2_xxs": (_I32, [_P, _P, _I64, _I32, _P, _I64, _I32, _P, _I64, _P, _I64, _I64, _P]),
+    "fnb_expert_gate_up_rows_iq2_xs": (_I32, [_P, _P, _I64, _I32, _P, _I64, _I32, _P, _I64, _P, _I64, _I64, _P]),
+    "fnb_expert_gate_up_rows_iq2_s": (_I32, [_P, _P, _I64, _I32, _P, _I64, _I32, _P, _I64, _P, _I64, _I64, _P]),
     "fnb_expert_down_rows_q5_1": (_I32, [_P, _I64, _I32, _P, _I64, _I32, _P, _I64, _I64, _I64, _P]),
     "fnb_expert_down_rows_q8_0": (_I32, [_P, _I64, _I32, _P, _I64, _I32, _P, _I64, _I64, _I64, _P]),
     "fnb_quantize_act_q": (_I32, [_P, _P, _P, _I64, _I32, _P]),

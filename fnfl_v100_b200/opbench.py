@@ -25,6 +25,7 @@ OPS = ("get_rows_q4_k", "get_rows_iq3_xxs", "rms_norm", "rms_norm_heads", "rope_
        "expert_gate_up_q5_k_nt1", "expert_gate_up_q5_k_nt3", "expert_gate_up_q5_k_nt8",
        "expert_gate_up_iq3_s_nt1", "expert_gate_up_iq3_s_nt3", "expert_gate_up_iq3_s_nt8",
        "expert_gate_up_iq3_xxs_nt1", "expert_gate_up_iq3_xxs_nt3", "expert_gate_up_iq3_xxs_nt8",
+       "expert_gate_up_iq2_xxs_nt1", "expert_gate_up_iq2_xxs_nt3", "expert_gate_up_iq2_xs_nt1", "expert_gate_up_iq2_s_nt1",
        "attend_q8_0_b1", "attend_q8_0_b3", "attend_q8_0_b5", "attend_kv8_b1", "attend_kv8_b5")
 
 
@@ -122,6 +123,19 @@ def make_case(op: str, T: int, dev, gen, c: ChainConfig):
         act = ops.quantize_q8_k(N(gen, (nt, n), 1.0, dev))
         out = torch.empty((nt, rows), dtype=torch.float32, device=dev)
         return (lambda: ops.expert_gate_up_rows("iq3_s", gate, up, act, n, out=out)), rows * (2 * n // 256 * 110 + nt * 4) + nt * n // 256 * 292
+    if op.startswith("expert_gate_up_iq2"):
+        fmt = op[len("expert_gate_up_"):op.rindex("_nt")]
+        nt, n, rows = int(op.rsplit("nt", 1)[1]), 2560, 2 * T
+        bb = {"iq2_xxs": 66, "iq2_xs": 74, "iq2_s": 82}[fmt]
+
+        def rows_of():
+            t = torch.randint(0, 256, (rows, n // 256, bb), dtype=torch.uint8, device=dev, generator=gen)
+            t.view(torch.float16).reshape(rows, n // 256, bb // 2)[..., 0] = 2e-4
+            return t.reshape(rows, n // 256 * bb)
+        gate, up = rows_of(), rows_of()
+        act = ops.quantize_q8_k(N(gen, (nt, n), 1.0, dev))
+        out = torch.empty((nt, rows), dtype=torch.float32, device=dev)
+        return (lambda: ops.expert_gate_up_rows(fmt, gate, up, act, n, out=out)), rows * (2 * n // 256 * bb + nt * 4) + nt * n // 256 * 292
     if op.startswith("expert_gate_up_iq3_xxs"):
         nt, n, rows = int(op.rsplit("nt", 1)[1]), 2560, 2 * T
         gate = synth.torch_table("iq3_xxs", gen, rows, n, dev, 5e-5, 4e-4)

@@ -412,10 +412,11 @@ def embed_supply(fmt: str, table, tok, n_own: int, src, row0: int, *, own=None, 
 def expert_gate_up_rows(fmt: str, gate: torch.Tensor, up: torch.Tensor, act: torch.Tensor, n: int, r0: int = 0,
                         r1: int | None = None, out: torch.Tensor | None = None, gu: torch.Tensor | None = None):
     """ff[t][r] = silu(gate row r . act[t]) * (up row r . act[t]), bit for bit the reference's CPU rows: fmt "q4_k"
-    / "q5_k" (fn::experts::cpu::kq_gu_rows; rows uint8 [rows][n/256*144] / [rows][n/256*176]) or "iq3_xxs" / "iq3_s" (fn::experts::cpu::iq_gu_rows; rows
-    [rows][n/256*98] / [rows][n/256*110]), Q8_K activations uint8 [nt][n/256*292]; returns F32 [nt][rows]."""
+    / "q5_k" (fn::experts::cpu::kq_gu_rows; rows uint8 [rows][n/256*144] / [rows][n/256*176]) or "iq3_xxs" / "iq3_s" /
+    "iq2_xxs" / "iq2_xs" / "iq2_s" (fn::experts::cpu::iq_gu_rows; rows [rows][n/256*98 / 110 / 66 / 74 / 82]), Q8_K activations uint8 [nt][n/256*292]; returns F32 [nt][rows]."""
     entry = {"q4_k": "fnb_expert_gate_up_rows_q4_k", "q5_k": "fnb_expert_gate_up_rows_q5_k", "iq3_xxs": "fnb_expert_gate_up_rows_iq3_xxs",
-             "iq3_s": "fnb_expert_gate_up_rows_iq3_s"}[fmt]
+             "iq3_s": "fnb_expert_gate_up_rows_iq3_s", "iq2_xxs": "fnb_expert_gate_up_rows_iq2_xxs",
+             "iq2_xs": "fnb_expert_gate_up_rows_iq2_xs", "iq2_s": "fnb_expert_gate_up_rows_iq2_s"}[fmt]
     _dev(gate, torch.uint8, "gate")
     _dev(up, torch.uint8, "up")
     _dev(act, torch.uint8, "act")

@@ -55,6 +55,17 @@ def iq3_s_table(g: np.random.Generator, n_rows: int, cols: int, d_lo: float = 1e
     return t.reshape(n_rows, nsb * 110)
 
 
+def iq2_table(fmt: str, g: np.random.Generator, n_rows: int, cols: int, d_lo: float = 1e-3, d_hi: float = 1e-2) -> np.ndarray:
+    """uint8 [n_rows][cols/256*B] for fmt "iq2_xxs" (B = 66), "iq2_xs" (74) or "iq2_s" (82): uniform bytes (every index,
+    sign and scale pattern is a valid block), fp16 d ~ U(d_lo, d_hi)."""
+    bb = {"iq2_xxs": 66, "iq2_xs": 74, "iq2_s": 82}[fmt]
+    nsb = cols // 256
+    t = g.integers(0, 256, size=(n_rows, nsb, bb), dtype=np.uint8)
+    d = _f16_bits(g.uniform(d_lo, d_hi, size=(n_rows, nsb, 1)))
+    t[:, :, 0:2] = d.view(np.uint8).reshape(n_rows, nsb, 2)
+    return t.reshape(n_rows, nsb * bb)
+
+
 def q8_0_table(g: np.random.Generator, n_rows: int, cols: int) -> np.ndarray:
     nb = cols // 32
     t = g.integers(0, 256, size=(n_rows, nb, 34), dtype=np.uint8)

@@ -418,6 +418,24 @@ int32_t fnb_expert_gate_up_rows_iq3_s(const void * gate, const void * up, int64_
                                       int64_t r1, void * stream);
 
 /*
+ * And with the three IQ2 formats (66-, 74- and 82-byte super-blocks: row_bytes = n / 256 * 66 / 74 / 82): fn::experts::cpu::
+ * iq_gu_rows for fmt iq2_xxs, iq2_xs and iq2_s (cpu_iq_avx2.cpp:225-254, :341-414 row_dot_iq2xs, :551-565 the dispatch), same
+ * bits - codebook entries of eight magnitudes (ggml/src/ggml-common.h:605, :672, :803), 7-bit sign indices with their
+ * parity bit (IQ2_XXS, IQ2_XS) or plain sign bits (IQ2_S), a scale per 32 values (IQ2_XXS) or per 16 (IQ2_XS, IQ2_S), the
+ * format's 1/8 folded into d with the pairwise reduction order (IQ2_XXS, IQ2_XS) or on the reduced sum in ggml's order
+ * (IQ2_S).  Arguments and limits as fnb_expert_gate_up_rows_iq3_xxs.
+ */
+int32_t fnb_expert_gate_up_rows_iq2_xxs(const void * gate, const void * up, int64_t row_bytes, int32_t n, const void * act,
+                                        int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, float * gu, int64_t r0,
+                                        int64_t r1, void * stream);
+int32_t fnb_expert_gate_up_rows_iq2_xs(const void * gate, const void * up, int64_t row_bytes, int32_t n, const void * act,
+                                       int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, float * gu, int64_t r0,
+                                       int64_t r1, void * stream);
+int32_t fnb_expert_gate_up_rows_iq2_s(const void * gate, const void * up, int64_t row_bytes, int32_t n, const void * act,
+                                      int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, float * gu, int64_t r0,
+                                      int64_t r1, void * stream);
+
+/*
  * The consumer of the Q8_1 blocks fnb_swiglu_q8_1 writes: the routed experts' down mat-vec for a decode window,
  * out[t * out_stride + r] = weight row r . act[t] for t < nt and r in [r0, r1).  Weights are ggml Q5_1 rows (n / 32
  * blocks of 24 bytes: fp16 d, fp16 m, 32 high bits, 16 nibble bytes; value = d q + m), rows back to back

@@ -103,6 +103,22 @@ inline bool gate_up_rows_iq3_s(const uint8_t * gate, const uint8_t * up, int32_t
     return fnb_expert_gate_up_rows_iq3_s(gate, up, int64_t(n / 256) * 110, n, act, act_stride, nt, ff, ff_stride, nullptr, r0,
                                          r1, stream) == FNB_OK;
 }
+// and for the IQ2 formats (66-, 74-, 82-byte super-blocks), as fn::experts::cpu::iq_gu_rows dispatches them
+inline bool gate_up_rows_iq2_xxs(const uint8_t * gate, const uint8_t * up, int32_t n, const void * act, int64_t act_stride,
+                                 int32_t nt, float * ff, int64_t ff_stride, int64_t r0, int64_t r1, void * stream) {
+    return fnb_expert_gate_up_rows_iq2_xxs(gate, up, int64_t(n / 256) * 66, n, act, act_stride, nt, ff, ff_stride, nullptr, r0,
+                                           r1, stream) == FNB_OK;
+}
+inline bool gate_up_rows_iq2_xs(const uint8_t * gate, const uint8_t * up, int32_t n, const void * act, int64_t act_stride,
+                                int32_t nt, float * ff, int64_t ff_stride, int64_t r0, int64_t r1, void * stream) {
+    return fnb_expert_gate_up_rows_iq2_xs(gate, up, int64_t(n / 256) * 74, n, act, act_stride, nt, ff, ff_stride, nullptr, r0,
+                                          r1, stream) == FNB_OK;
+}
+inline bool gate_up_rows_iq2_s(const uint8_t * gate, const uint8_t * up, int32_t n, const void * act, int64_t act_stride,
+                               int32_t nt, float * ff, int64_t ff_stride, int64_t r0, int64_t r1, void * stream) {
+    return fnb_expert_gate_up_rows_iq2_s(gate, up, int64_t(n / 256) * 82, n, act, act_stride, nt, ff, ff_stride, nullptr, r0,
+                                         r1, stream) == FNB_OK;
+}
 inline bool quantize_q8_k(const float * x, void * blocks, int64_t rows, int32_t k, void * stream) {
     return fnb_quantize_q8_k(x, blocks, rows, k, stream) == FNB_OK;
 }

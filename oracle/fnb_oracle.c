@@ -846,6 +846,109 @@ void fnbo_expert_gu_rows_iq3_s(const uint8_t * gate, const uint8_t * up, int64_t
     }
 }
 
+/* ---- and with the three IQ2 formats (fn/kernels/experts/cpu_iq_avx2.cpp:225-254 fmt32<16> and fmt32<22>, :341-414
+ * row_dot_iq2xs, :305-337 row_dot).  The lane structure is the IQ3 kernels': per super-block eight int32 lanes, lane l of
+ * a 32-value half collecting scale x (four codebook magnitudes times four sign-applied Q8_K codes); a codebook entry
+ * holds EIGHT magnitudes (8, 25 or 43), so it serves two lanes.
+ *   IQ2_XXS (66 bytes): per half four index bytes, then a word of 4 x 7-bit sign index + 4-bit scale s: 2 s + 1.
+ *   IQ2_XS  (74 bytes): 32 x u16 = 9-bit index | 7-bit sign index << 9; scales[8], low nibble for a half's first 16
+ *                       values, high nibble for its last 16; its two accumulators a block add as integers.
+ *   IQ2_S   (82 bytes): qs[32] index low bytes, 32 plain sign bytes, qh[8] (two more index bits a value group),
+ *                       scales[8] as IQ2_XS.
+ * K = 1/8: IQ2_XXS and IQ2_XS fold it into the block's d (d * 0.125f, exact) and reduce pairwise (hsum8: lo + hi halves,
+ * then two horizontal adds); IQ2_S applies it to the reduced sum in ggml's hsum_float_8 order. */
+static const uint16_t o_grid2xxs_packed[256] = {
+#include "../fnfl_v100_b200/csrc/iq2xxs_grid_packed.inc"
+};
+static const uint16_t o_grid2xs_packed[512] = {
+#include "../fnfl_v100_b200/csrc/iq2xs_grid_packed.inc"
+};
+static const uint16_t o_grid2s_packed[1024] = {
+#include "../fnfl_v100_b200/csrc/iq2s_grid_packed.inc"
+};
+
+static float fnbo_hsum8_pairwise(const float * a) {
+    const float s0 = a[0] + a[4], s1 = a[1] + a[5], s2 = a[2] + a[6], s3 = a[3] + a[7];  /* lo + hi */
+    const float h0 = s0 + s1, h1 = s2 + s3;                                               /* hadd */
+    return h0 + h1;                                                                       /* hadd */
+}
+
+/* fmt: 16 IQ2_XXS, 17 IQ2_XS, 22 IQ2_S (ggml's type numbers, as the reference's templates) */
+static float fnbo_iq2_dot(int fmt, const uint8_t * row, int nb, const uint8_t * act) {
+    const int bytes = fmt == 16 ? 66 : fmt == 17 ? 74 : 82;
+    static const int32_t mags[4] = {8, 25, 43, 0};
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int i = 0; i < nb; ++i) {
+        const uint8_t * x = row + (size_t) bytes * i;
+        const uint8_t * y = act + 292 * i;
+        uint16_t dh;
+        memcpy(&dh, x, 2);
+        float yd;
+        memcpy(&yd, y, 4);
+        const int8_t * q8 = (const int8_t *) (y + 4);
+        int32_t acci[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int h = 0; h < 8; ++h) {            /* the eight 32-value halves */
+            for (int k = 0; k < 4; ++k) {        /* a codebook entry: values 8 k .. 8 k + 7 of the half, lanes 2 k, 2 k + 1 */
+                unsigned code, signs;
+                int32_t sc;
+                if (fmt == 16) {
+                    uint32_t w;
+                    memcpy(&w, x + 2 + 8 * h + 4, 4);
+                    code = o_grid2xxs_packed[x[2 + 8 * h + k]];
+                    const unsigned s7 = (w >> (7 * k)) & 127u;
+                    signs = s7 | ((unsigned) (__builtin_popcount(s7) & 1) << 7);
+                    sc = 2 * (int32_t) (w >> 28) + 1;
+                } else if (fmt == 17) {
+                    uint16_t q;
+                    memcpy(&q, x + 2 + 2 * (4 * h + k), 2);
+                    code = o_grid2xs_packed[q & 511u];
+                    const unsigned s7 = q >> 9;
+                    signs = s7 | ((unsigned) (__builtin_popcount(s7) & 1) << 7);
+                    const unsigned sn = x[66 + h];
+                    sc = 2 * (int32_t) (k < 2 ? sn & 15u : sn >> 4) + 1;
+                } else {
+                    code = o_grid2s_packed[x[2 + 4 * h + k] | (((x[66 + h] >> (2 * k)) & 3u) << 8)];
+                    signs = x[34 + 4 * h + k];
+                    const unsigned sn = x[74 + h];
+                    sc = 2 * (int32_t) (k < 2 ? sn & 15u : sn >> 4) + 1;
+                }
+                for (int half = 0; half < 2; ++half) {   /* lanes 2 k and 2 k + 1: four values each */
+                    int32_t sum = 0;
+                    for (int b = 0; b < 4; ++b) {
+                        const int v = 4 * half + b;
+                        const int32_t mag = mags[(code >> (2 * v)) & 3u];
+                        const int8_t yv = q8[32 * h + 8 * k + v];
+                        const int8_t ys = (signs >> v) & 1u ? (int8_t) (0u - (unsigned) yv) : yv;
+                        sum += mag * (int32_t) ys;
+                    }
+                    acci[2 * k + half] += sc * sum;
+                }
+            }
+        }
+        const float dx = fmt == 22 ? fnbo_f16_to_f32(dh) : fnbo_f16_to_f32(dh) * 0.125f;
+        const float dxy = dx * yd;
+        for (int l = 0; l < 8; ++l) acc[l] = fmaf(dxy, (float) acci[l], acc[l]);
+    }
+    return fmt == 22 ? 0.125f * fnbo_hsum8(acc) : fnbo_hsum8_pairwise(acc);
+}
+
+void fnbo_expert_gu_rows_iq2(int32_t fmt, const uint8_t * gate, const uint8_t * up, int64_t row_bytes, int32_t n,
+                             const uint8_t * act, int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, float * gu,
+                             int64_t r0, int64_t r1) {
+    const int nb = n / 256;
+    for (int64_t r = r0; r < r1; ++r) {
+        for (int t = 0; t < nt; ++t) {
+            const float g = fnbo_iq2_dot(fmt, gate + r * row_bytes, nb, act + (int64_t) t * act_stride);
+            const float u = fnbo_iq2_dot(fmt, up + r * row_bytes, nb, act + (int64_t) t * act_stride);
+            ff[(int64_t) t * ff_stride + r] = (g / (1.0f + o_expf(-g))) * u;
+            if (gu != NULL) {
+                gu[(int64_t) t * ff_stride + r] = g;
+                gu[((int64_t) nt + t) * ff_stride + r] = u;
+            }
+        }
+    }
+}
+
 /* fn/kernels/qsa/attend.h:17-19 (o = softmax(q . K / 16) . V, out = o sigmoid(gate)), every sum in double, the
  * maximum subtracted before the exponentials: the FP64 statement the reference's qa2-test checks its kernel against
  * (fn/kernels/qsa/qa2_test.cpp:469-520) */

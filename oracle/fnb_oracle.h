@@ -137,6 +137,11 @@ void fnbo_expert_down_rows_q2_0(const uint8_t * w, int64_t row_bytes, int32_t n,
                                 const float * scale, int64_t scale_stride, int32_t nt, float * out, int64_t out_stride,
                                 int64_t r0, int64_t r1);
 
+/* The experts' gate / up rows with the IQ2 formats; fmt is ggml's type number: 16 IQ2_XXS, 17 IQ2_XS, 22 IQ2_S */
+void fnbo_expert_gu_rows_iq2(int32_t fmt, const uint8_t * gate, const uint8_t * up, int64_t row_bytes, int32_t n,
+                             const uint8_t * act, int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, float * gu,
+                             int64_t r0, int64_t r1);
+
 /* Decode attention in FP64 over already decoded cache rows (the reference's test protocol, fn/kernels/qsa/
  * qa2_test.cpp:469-520, written from the definition in fn/kernels/qsa/attend.h:9-23): for row t and query head h,
  * out = softmax_c(scale q . K[c][g]) . V[c][g] over cells first[t] .. first[t] + count[t] - 1, g = h / (n_q / n_kv),

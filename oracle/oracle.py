@@ -299,11 +299,29 @@ def kv8_dequantize(codes: np.ndarray, scales: np.ndarray) -> np.ndarray:
     return (c * s).reshape(-1)
 
 
+IQ2_TYPE = {"iq2_xxs": 16, "iq2_xs": 17, "iq2_s": 22}   # ggml's type numbers, as the reference's templates use them
+
+
 def expert_gu_rows(fmt: str, gate: np.ndarray, up: np.ndarray, act: np.ndarray, n: int, r0: int = 0, r1: int | None = None,
                    use_ref: bool = False, want_gu: bool = False):
     """ff[t][r] = silu(gate row r . act[t]) * (up row r . act[t]): weight rows uint8 [rows][n/256*block bytes] of
-    fmt "q4_k" (144), "q5_k" (176), "iq3_xxs" (98) or "iq3_s" (110) against Q8_K activations uint8 [nt][n/256*292].  use_ref: the reference's own
+    fmt "q4_k" (144), "q5_k" (176), "iq3_xxs" (98), "iq3_s" (110), "iq2_xxs" (66), "iq2_xs" (74) or "iq2_s" (82) against Q8_K activations uint8 [nt][n/256*292].  use_ref: the reference's own
     AVX2 kernel (its libm's expf)."""
+    gate, up, act = (np.ascontiguousarray(a, np.uint8) for a in (gate, up, act))
+    if fmt in IQ2_TYPE:    # one entry point for the three IQ2 formats, told apart by ggml's type number
+        rows, nt = gate.shape[0], act.shape[0]
+        r1 = rows if r1 is None else r1
+        ff = np.zeros((nt, rows), np.float32)
+        ty = C.c_int32(IQ2_TYPE[fmt])
+        if use_ref:
+            ref().ref_iq_gu_rows_iq2(ty, _p(gate), _p(up), C.c_int64(gate.shape[1]), C.c_int32(n), _p(act),
+                                     C.c_int64(act.shape[1]), C.c_int32(nt), _p(ff), C.c_int64(rows), C.c_int32(r0), C.c_int32(r1))
+            return ff
+        gu = np.zeros((2, nt, rows), np.float32) if want_gu else None
+        lib().fnbo_expert_gu_rows_iq2(ty, _p(gate), _p(up), C.c_int64(gate.shape[1]), C.c_int32(n), _p(act),
+                                      C.c_int64(act.shape[1]), C.c_int32(nt), _p(ff), C.c_int64(rows), _p(gu), C.c_int64(r0),
+                                      C.c_int64(r1))
+        return (ff, gu) if want_gu else ff
     ref_fn, own_fn = {"q4_k": ("ref_kq_gu_rows_q4_k", "fnbo_expert_gu_rows_q4_k"),
                       "q5_k": ("ref_kq_gu_rows_q5_k", "fnbo_expert_gu_rows_q5_k"),
                       "iq3_xxs": ("ref_iq_gu_rows_iq3_xxs", "fnbo_expert_gu_rows_iq3_xxs"),

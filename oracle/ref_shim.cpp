@@ -112,6 +112,17 @@ void ref_iq_gu_rows_iq3_s(const uint8_t * gate, const uint8_t * up, int64_t row_
     fn::experts::cpu::iq_gu_rows(fn::experts::fmt::iq3_s, gate, up, size_t(row_bytes), n, a, nt, o, r0, r1);
 }
 
+// and for the three IQ2 formats (fmt: ggml's type number 16 IQ2_XXS, 17 IQ2_XS, 22 IQ2_S)
+void ref_iq_gu_rows_iq2(int32_t fmt, const uint8_t * gate, const uint8_t * up, int64_t row_bytes, int32_t n,
+                        const uint8_t * act, int64_t act_stride, int32_t nt, float * ff, int64_t ff_stride, int32_t r0,
+                        int32_t r1) {
+    const void * a[64];
+    float * o[64];
+    for (int t = 0; t < nt && t < 64; ++t) a[t] = act + int64_t(t) * act_stride, o[t] = ff + int64_t(t) * ff_stride;
+    const fn::experts::fmt f = fmt == 16 ? fn::experts::fmt::iq2_xxs : fmt == 17 ? fn::experts::fmt::iq2_xs : fn::experts::fmt::iq2_s;
+    fn::experts::cpu::iq_gu_rows(f, gate, up, size_t(row_bytes), n, a, nt, o, r0, r1);
+}
+
 // the planar 32-value activation (fn/kernels/experts/cpu_q2_avx2.cpp:180-226): codes and chunk scales of n <= 640 values
 void ref_quantize_act_q(const float * x, int32_t n, int8_t * q, float * scale) {
     fn::experts::cpu::act_q a;

@@ -242,6 +242,33 @@ def gate_up_rows_iq3_s() -> None:
     print("gate_up_rows_iq3_s.npz", os.path.getsize(path), "bytes; |ff| max", float(np.abs(ff).max()))
 
 
+def gate_up_rows_iq2() -> None:
+    """The same for the three IQ2 formats (fn::experts::cpu::iq_gu_rows, fmt iq2_xxs / iq2_xs / iq2_s), each also with -128
+    codes.  Same libm note."""
+    from fnfl_v100_b200 import synth
+    out = {}
+    for fmt, seed, d_hi in (("iq2_xxs", 0x4932, 2.5e-4), ("iq2_xs", 0x4958, 2.5e-4), ("iq2_s", 0x4953 + 1, 2.5e-4)):
+        g = synth.rng(seed)
+        n, rows, nt = 2560, 33, 5
+        gate, up = synth.iq2_table(fmt, g, rows, n, d_hi / 8, d_hi), synth.iq2_table(fmt, g, rows, n, d_hi / 8, d_hi)
+        act = O.quantize_q8_k(synth.normal(g, (nt, n), 1.0), "ggml").reshape(nt, -1)
+        act_m128 = act.copy()
+        codes = act_m128.reshape(nt, -1, 292)[:, :, 4:260]
+        codes[g.integers(0, 10, size=codes.shape) == 0] = 0x80
+        O.use_libm(True)
+        ff = O.expert_gu_rows(fmt, gate, up, act, n, use_ref=True)
+        ff_m128 = O.expert_gu_rows(fmt, gate, up, act_m128, n, use_ref=True)
+        O.use_libm(False)
+        for a, f in ((act, ff), (act_m128, ff_m128)):
+            assert np.array_equal(f.view(np.uint32), O.expert_gu_rows(fmt, gate, up, a, n).view(np.uint32)), fmt + ": restatement differs"
+        for k, v in dict(gate=gate, up=up, act=act, ff=ff, act_m128=act_m128, ff_m128=ff_m128).items():
+            out[fmt + "_" + k] = v
+        print(fmt, "|ff| max", float(np.abs(ff).max()), "g std", float(np.std(O.expert_gu_rows(fmt, gate, up, act, n, want_gu=True)[1][0])))
+    path = os.path.join(HERE, "gate_up_rows_iq2.npz")
+    np.savez_compressed(path, **out)
+    print("gate_up_rows_iq2.npz", os.path.getsize(path), "bytes")
+
+
 def main() -> None:
     O.build(with_ref=True)
     model_file()
@@ -253,6 +280,7 @@ def main() -> None:
     gate_up_rows_q5_k()
     gate_up_rows_iq3_xxs()
     gate_up_rows_iq3_s()
+    gate_up_rows_iq2()
     r = O.ref()
     x = stress_blocks()
     n = x.shape[0]

@@ -497,6 +497,45 @@ def test_expert_gate_up_rows_iq3_s_bit_exact(dev, oracle, n, rows, nt, m128):
     assert np.abs(wgu[0][:, r0:r1]).std() > 0.3
 
 
+@pytest.mark.parametrize("fmt", ["iq2_xxs", "iq2_xs", "iq2_s"])
+def test_expert_gate_up_rows_iq2_equal_the_reference_avx2_kernel_on_golden(dev, fmt):
+    """The reference's own iq_gu_rows outputs for the three IQ2 formats, also for a window holding -128 codes."""
+    gold = np.load(os.path.join(GOLD, "gate_up_rows_iq2.npz"))
+    gate, up = to_dev(gold[fmt + "_gate"], dev), to_dev(gold[fmt + "_up"], dev)
+    for act, want in ((gold[fmt + "_act"], gold[fmt + "_ff"]), (gold[fmt + "_act_m128"], gold[fmt + "_ff_m128"])):
+        got = ops.expert_gate_up_rows(fmt, gate, up, to_dev(act, dev), 2560)
+        assert np.array_equal(bits(got.cpu().numpy()), bits(want))
+
+
+@pytest.mark.parametrize("fmt", ["iq2_xxs", "iq2_xs", "iq2_s"])
+@pytest.mark.parametrize("n,rows,nt,m128", [(2560, 320, 1, False), (2560, 999, 3, True), (2048, 130, 8, False),
+                                            (512, 37, 2, True), (5632, 41, 13, False), (16384, 9, 7, False)])
+def test_expert_gate_up_rows_iq2_bit_exact(dev, oracle, fmt, n, rows, nt, m128):
+    """As the IQ3 tests, with IQ2 rows: eight-magnitude codebook entries, a scale per 16 or 32 values, both reduction
+    orders.  Rows staged whole and in chunks, every row alignment, windows of several passes, -128 codes."""
+    g = synth.rng(39)
+    act = ops.quantize_q8_k(to_dev(synth.normal(g, (nt, n), 1.0), dev))
+    if m128:
+        a = act.cpu().numpy().reshape(nt, -1, 292)
+        codes = a[:, :, 4:260]
+        codes[g.integers(0, 7, size=codes.shape) == 0] = 0x80
+        act = to_dev(a.reshape(nt, -1), dev)
+    d_hi = 2.5e-4 * (2560 / n) ** 0.5
+    gate, up = synth.iq2_table(fmt, g, rows, n, d_hi / 8, d_hi), synth.iq2_table(fmt, g, rows, n, d_hi / 8, d_hi)
+    r0, r1 = 2, rows - 1
+    out = torch.full((nt, rows), float("nan"), dtype=torch.float32, device=dev)
+    gu = torch.zeros((2, nt, rows), dtype=torch.float32, device=dev) if nt <= 8 else None
+    ops.expert_gate_up_rows(fmt, to_dev(gate, dev), to_dev(up, dev), act, n, r0=r0, r1=r1, out=out, gu=gu)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    want, wgu = oracle.expert_gu_rows(fmt, gate, up, act.cpu().numpy(), n, r0=r0, r1=r1, want_gu=True)
+    assert np.array_equal(bits(got[:, r0:r1]), bits(want[:, r0:r1]))
+    assert np.isnan(got[:, :r0]).all() and np.isnan(got[:, r1:]).all()
+    if gu is not None:
+        assert np.array_equal(bits(gu.cpu().numpy()[:, :, r0:r1]), bits(wgu[:, :, r0:r1]))
+    assert np.abs(wgu[0][:, r0:r1]).std() > 0.2
+
+
 @pytest.mark.parametrize("fmt", ["q4_k", "q5_k", "iq3_xxs", "iq3_s"])
 def test_expert_ffn_for_a_decode_window_stage_by_stage(dev, oracle, fmt):
     """One routed expert for a window of three rows, every hand-over on the device: RMSNorm -> Q8_K -> gate / up mat-vec

@@ -194,6 +194,18 @@ def test_expert_gate_up_rows_iq3_s_match_the_reference_avx2_kernel(oracle):
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
+@pytest.mark.parametrize("fmt", ["iq2_xxs", "iq2_xs", "iq2_s"])
+def test_expert_gate_up_rows_iq2_match_the_reference_avx2_kernel(oracle, fmt):
+    """tests/golden/gate_up_rows_iq2.npz: ff of the reference's own iq_gu_rows for the three IQ2 formats, also with -128
+    codes; the scalar restatement reproduces every bit."""
+    gold = np.load(os.path.join(GOLD, "gate_up_rows_iq2.npz"))
+    gate, up = gold[fmt + "_gate"], gold[fmt + "_up"]
+    for act, want in ((gold[fmt + "_act"], gold[fmt + "_ff"]), (gold[fmt + "_act_m128"], gold[fmt + "_ff_m128"])):
+        got = oracle.expert_gu_rows(fmt, gate, up, act, 2560)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    assert not np.array_equal(gold[fmt + "_ff"], gold[fmt + "_ff_m128"])
+
+
 def test_expert_gate_up_rows_match_the_reference_avx2_kernel(oracle):
     """tests/golden/gate_up_rows.npz: ff of the reference's own kq_gu_rows (fmt q4_k, GLU included); the scalar
     restatement reproduces every bit, also on a sub-range of rows."""
