@@ -342,35 +342,11 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
     // the codebook copies, the sign masks' copies, the window's codes [NT][nb][256] and scales [NT][nb], then each
     // warp's two units
     extern __shared__ __align__(16) uint8_t smem[];
-    __shared__ uint32_t s_grid[shape<FMT>::kGridEntries * (shape<FMT>::kTwo ? 2 : 1)];  // the codebook's magnitudes as bytes
     uint32_t * grid_sm = reinterpret_cast<uint32_t *>(smem);
     uint2 * sign_sm = reinterpret_cast<uint2 *>(smem + shape<FMT>::kGridBytes);
     uint8_t * codes_sm = smem + shape<FMT>::kTableBytes;
     float * d_sm = reinterpret_cast<float *>(codes_sm + size_t(NT) * nb * 256);
     load_exp2_table();
-    // the codebook's magnitudes as bytes, expanded from the packed level indices: one word an entry (IQ3), or two
-    for (int i = threadIdx.x; i < shape<FMT>::kGridEntries; i += blockDim.x) {
-        if (!shape<FMT>::kTwo) {
-            const uint32_t c = FMT == kIq3S ? c_grid3s_packed[i] : c_grid_packed[i];  // four 3-bit levels
-            uint32_t w = 0;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const uint32_t lvl = (c >> (3 * j)) & 7u;
-                // IQ3_S: 1, 3 .. 15; IQ3_XXS: 4, 12 .. 52, 62
-                w |= (FMT == kIq3S ? 2u * lvl + 1u : (lvl == 7u ? 62u : 4u + 8u * lvl)) << (8 * j);
-            }
-            s_grid[i] = w;
-        } else {
-            const uint32_t c = FMT == kIq2Xxs ? c_grid2xxs_packed[i] : FMT == kIq2Xs ? c_grid2xs_packed[i] : c_grid2s_packed[i];
-            uint32_t w[2] = {0u, 0u};
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const uint32_t lvl = (c >> (2 * j)) & 3u;  // 8, 25, 43
-                w[j >> 2] |= (lvl == 0u ? 8u : lvl == 1u ? 25u : 43u) << (8 * (j & 3));
-            }
-            s_grid[2 * i] = w[0], s_grid[2 * i + 1] = w[1];
-        }
-    }
     int has_m128 = 0;
     for (int i = threadIdx.x; i < NT * nb * 65; i += blockDim.x) {  // the scale and the 64 code words of every block
         const int blk = i / 65, word = i - blk * 65;
@@ -388,12 +364,29 @@ __global__ void __launch_bounds__(kMaxWarps * 32)
         }
     }
     __syncthreads();
-    if (!shape<FMT>::kTwo) {
-        for (int i = threadIdx.x; i < shape<FMT>::kGridEntries * kGridCopies; i += blockDim.x) grid_sm[i] = s_grid[i / kGridCopies];
-    } else {  // entry e's copy j at uint2 index e kCopies + j
-        for (int i = threadIdx.x; i < shape<FMT>::kGridEntries * shape<FMT>::kCopies; i += blockDim.x) {
-            const int e = i / shape<FMT>::kCopies;
-            reinterpret_cast<uint2 *>(grid_sm)[i] = make_uint2(s_grid[2 * e], s_grid[2 * e + 1]);
+    // the codebook's magnitudes as bytes, expanded from the packed level indices straight into the copies: one word an
+    // entry (IQ3: entry e's copy j at word e kGridCopies + j), or two (IQ2: at uint2 index e kCopies + j)
+    for (int i = threadIdx.x; i < shape<FMT>::kGridEntries * shape<FMT>::kCopies; i += blockDim.x) {
+        const int e = i / shape<FMT>::kCopies;
+        if (!shape<FMT>::kTwo) {
+            const uint32_t c = FMT == kIq3S ? c_grid3s_packed[e] : c_grid_packed[e];  // four 3-bit levels
+            uint32_t w = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t lvl = (c >> (3 * j)) & 7u;
+                // IQ3_S: 1, 3 .. 15; IQ3_XXS: 4, 12 .. 52, 62
+                w |= (FMT == kIq3S ? 2u * lvl + 1u : (lvl == 7u ? 62u : 4u + 8u * lvl)) << (8 * j);
+            }
+            grid_sm[i] = w;
+        } else {
+            const uint32_t c = FMT == kIq2Xxs ? c_grid2xxs_packed[e] : FMT == kIq2Xs ? c_grid2xs_packed[e] : c_grid2s_packed[e];
+            uint32_t w[2] = {0u, 0u};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t lvl = (c >> (2 * j)) & 3u;  // 8, 25, 43
+                w[j >> 2] |= (lvl == 0u ? 8u : lvl == 1u ? 25u : 43u) << (8 * (j & 3));
+            }
+            reinterpret_cast<uint2 *>(grid_sm)[i] = make_uint2(w[0], w[1]);
         }
     }
     for (int i = threadIdx.x; i < (shape<FMT>::kSignTable ? 128 * kSignCopies : 0); i += blockDim.x) {

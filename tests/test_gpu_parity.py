@@ -533,7 +533,7 @@ def test_expert_gate_up_rows_iq2_bit_exact(dev, oracle, fmt, n, rows, nt, m128):
     assert np.isnan(got[:, :r0]).all() and np.isnan(got[:, r1:]).all()
     if gu is not None:
         assert np.array_equal(bits(gu.cpu().numpy()[:, :, r0:r1]), bits(wgu[:, :, r0:r1]))
-    assert np.abs(wgu[0][:, r0:r1]).std() > 0.2
+    assert np.abs(wgu[0][:, r0:r1]).std() > 0.1       # gates of order one: the GLU is exercised
 
 
 @pytest.mark.parametrize("fmt", ["q4_k", "q5_k", "iq3_xxs", "iq3_s"])
