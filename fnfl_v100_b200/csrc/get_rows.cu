@@ -99,6 +99,8 @@ __device__ __forceinline__ void q4_k_fetch_row(const uint8_t * __restrict__ tabl
 __global__ void __launch_bounds__(kWarpsPerCta * 32, kStagedCtasPerSm)
     get_rows_q4_k_staged_kernel(const uint8_t * __restrict__ table, int64_t n_vocab, const int32_t * __restrict__ ids,
                                 float * __restrict__ out, uint32_t * err, int64_t rows) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ __align__(16) uint8_t s_rows[kWarpsPerCta][kQ4kRowBytes];
     const int lane = threadIdx.x & 31;
     const int64_t warp = int64_t(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
@@ -143,6 +145,8 @@ template <int NSB>  // super-blocks per row held in flight at once
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
     get_rows_q4_k_kernel(const uint8_t * __restrict__ table, int64_t n_vocab, const int32_t * __restrict__ ids,
                          float * __restrict__ out, uint32_t * err, int64_t rows, int cols) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int64_t warp = int64_t(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
     const int64_t n_warps = int64_t(gridDim.x) * kWarpsPerCta;
@@ -238,6 +242,8 @@ __device__ __forceinline__ void iq3_finish(const iq3_sb_regs & r, float * dst256
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
     get_rows_iq3_xxs_kernel(const uint8_t * __restrict__ table, int64_t n_vocab, const int32_t * __restrict__ ids,
                             float * __restrict__ out, uint32_t * err, int64_t rows, int cols) {
+    pdl_launch_dependents();
+    pdl_wait();
     // The codebook's four magnitudes per entry as BYTES (one 32-bit word per entry): a lookup is a 32-bit shared
     // load, where 32 random entries collide on a bank about three deep.  As float4 entries (one 128-bit load, no
     // conversion) the same lookup took about eleven wavefronts and the kernel ran against the shared-memory pipe.
@@ -311,6 +317,8 @@ __device__ __forceinline__ void iq3_finish_staged(const uint8_t * buf, float * d
 __global__ void __launch_bounds__(kWarpsPerCta * 32, kStagedCtasPerSm)
     get_rows_iq3_xxs_staged_kernel(const uint8_t * __restrict__ table, int64_t n_vocab, const int32_t * __restrict__ ids,
                                    float * __restrict__ out, uint32_t * err, int64_t rows) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ uint32_t s_grid[256];
     __shared__ __align__(16) uint8_t s_rows[kWarpsPerCta][kIq3RowBytes];
     for (int i = threadIdx.x; i < 256; i += blockDim.x) {
@@ -371,6 +379,8 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, kStagedCtasPerSm)
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
     get_rows_q8_0_kernel(const uint8_t * __restrict__ table, int64_t n_vocab, const int32_t * __restrict__ ids,
                          float * __restrict__ out, uint32_t * err, int64_t rows, int cols) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int64_t warp = int64_t(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
     const int64_t n_warps = int64_t(gridDim.x) * kWarpsPerCta;
@@ -421,7 +431,7 @@ extern "C" int32_t fnb_get_rows_q4_k(const void * table, int64_t n_vocab, const 
     const cudaStream_t s = static_cast<cudaStream_t>(stream);
     const uint8_t * tb = static_cast<const uint8_t *>(table);
     if (cols == 2048) {
-        get_rows_q4_k_staged_kernel<<<persistent_grid(rows, kStagedGridPerSm), kWarpsPerCta * 32, 0, s>>>(tb, n_vocab, ids, out, err, rows);
+        launch_pdl(get_rows_q4_k_staged_kernel, persistent_grid(rows, kStagedGridPerSm), kWarpsPerCta * 32, 0, s, tb, n_vocab, ids, out, err, rows);
     } else {
         get_rows_q4_k_kernel<8><<<persistent_grid(rows, kStagedGridPerSm), kWarpsPerCta * 32, 0, s>>>(tb, n_vocab, ids, out, err, rows, cols);
     }
@@ -435,7 +445,7 @@ extern "C" int32_t fnb_get_rows_iq3_xxs(const void * table, int64_t n_vocab, con
     const cudaStream_t s = static_cast<cudaStream_t>(stream);
     const uint8_t * tb = static_cast<const uint8_t *>(table);
     if (cols == 2048) {
-        get_rows_iq3_xxs_staged_kernel<<<persistent_grid(rows, kStagedGridPerSm), kWarpsPerCta * 32, 0, s>>>(tb, n_vocab, ids, out, err, rows);
+        launch_pdl(get_rows_iq3_xxs_staged_kernel, persistent_grid(rows, kStagedGridPerSm), kWarpsPerCta * 32, 0, s, tb, n_vocab, ids, out, err, rows);
     } else {
         get_rows_iq3_xxs_kernel<<<persistent_grid(rows, kStagedGridPerSm), kWarpsPerCta * 32, 0, s>>>(tb, n_vocab, ids, out, err, rows, cols);
     }

@@ -29,6 +29,8 @@ __device__ __forceinline__ double sq_acc(double acc, float v) { return __dadd_rn
 template <int V, int R>
 __global__ void __launch_bounds__(128) rms_norm_warp_kernel(const float * __restrict__ x, const float * __restrict__ w,
                                                             float eps, float * __restrict__ y, int64_t rows) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int cols = 128 * V;
     const int lane = threadIdx.x & 31;
     const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -82,6 +84,8 @@ __global__ void __launch_bounds__(128) rms_norm_warp_kernel(const float * __rest
 __global__ void __launch_bounds__(256) rms_norm_generic_kernel(const float * __restrict__ x, const float * __restrict__ w,
                                                                float eps, float * __restrict__ y, int64_t rows,
                                                                int cols) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ double part[8];
     __shared__ float s_scale;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
@@ -132,7 +136,7 @@ void launch_warp(const float * x, const float * w, float eps, float * y, int64_t
     const int64_t ctas = (warps_needed + 3) / 4;
     // register-resident rows: occupancy is register-bound, 16 CTAs of 4 warps is an upper bound per SM
     const int grid = grid_for(ctas, 16);
-    rms_norm_warp_kernel<V, R><<<grid, 128, 0, s>>>(x, w, eps, y, rows);
+    launch_pdl(rms_norm_warp_kernel<V, R>, grid, 128, 0, s, x, w, eps, y, rows);
 }
 
 }  // namespace

@@ -55,6 +55,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                           int groups, uint32_t * err) {
     constexpr int BB = block_bytes<F>();
     extern __shared__ __align__(128) uint8_t smem[];
+    pdl_launch_dependents();
     const int nb = cols / 32;                            // blocks per row
     const uint32_t row_bytes = uint32_t(cols) * 4;
     const uint32_t tile_bytes = row_bytes * kGroupWarps;
@@ -74,6 +75,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         mbar_init_fence();
     }
     __syncthreads();  // nothing slow before this point: the producer starts streaming at once
+    pdl_wait();       // the predecessor's writes are visible from here on; no global memory was touched before
 
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int64_t n_tiles = (rows + kGroupWarps - 1) / kGroupWarps;
@@ -273,8 +275,8 @@ int32_t launch_one(const float * x, const float * w, float eps, uint8_t * out, f
     const int64_t n_tiles = (rows + kGroupWarps - 1) / kGroupWarps;
     const int grid = int(n_tiles < kSmCount ? n_tiles : kSmCount);
     const int groups = stages < kGroups ? stages : kGroups;
-    rms_norm_quant_kernel<F, BPL, F32OUT><<<grid, kThreads, smem, s>>>(x, w, eps, out, scales, out_f32, rows, cols, stages,
-                                                                       groups, err);
+    launch_pdl(rms_norm_quant_kernel<F, BPL, F32OUT>, grid, kThreads, smem, s, x, w, eps, out, scales, out_f32, rows, cols, stages,
+               groups, err);
     return launch_status();
 }
 

@@ -111,6 +111,7 @@ template <int HD, kv_fmt F>
 __global__ void __launch_bounds__(kThreads, 1) rope_kv_pipe_kernel(const rope_kernel_args a, const pipe_shape sh) {
     constexpr int NJ = HD / 32;  // 32-value blocks per row = 128-bit vectors per lane
     extern __shared__ __align__(128) uint8_t smem[];
+    pdl_launch_dependents();
     const int tt = sh.tt, stages = sh.stages;
     const int n_q = a.n_q, n_kv = a.n_kv, rpt = n_q + 2 * n_kv;
     const uint32_t q_tok = uint32_t(n_q) * HD * 4, kv_tok = uint32_t(n_kv) * HD * 4;
@@ -133,6 +134,7 @@ __global__ void __launch_bounds__(kThreads, 1) rope_kv_pipe_kernel(const rope_ke
         mbar_init_fence();
     }
     __syncthreads();  // nothing slow before this point: the producers start streaming at once
+    pdl_wait();       // the predecessor's writes are visible from here on; no global memory was touched before
 
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int64_t n_tiles = (a.rows + tt - 1) / tt;
@@ -405,7 +407,7 @@ bool launch_one(const rope_kernel_args & a, cudaStream_t s) {
     const int64_t n_tiles = (a.rows + tt - 1) / tt;
     const int grid = int(n_tiles < kSmCount ? n_tiles : kSmCount);
     const pipe_shape sh{tt, stages, nbh, uint32_t((0x100000000ull + uint64_t(rpt) - 1) / uint64_t(rpt))};
-    rope_kv_pipe_kernel<HD, F><<<grid, kThreads, smem, s>>>(a, sh);
+    launch_pdl(rope_kv_pipe_kernel<HD, F>, grid, kThreads, smem, s, a, sh);
     return true;
 }
 
