@@ -19,11 +19,13 @@
 //     q . K costs two tensor products, not three;  V = d x code is split exactly (hi = the rounded product, lo = the
 //     fused residual, both one half2 instruction per two values) and p = p_hi + p_lo (scaled by 2^12 to stay clear of
 //     FP16's subnormals), so p . V costs three (the lo x lo term is below 2^-22).
-//   * One warp owns 16 query rows (an m16n8k16 tile row) and all head_dim output columns: its running maximum, sum and
-//     output accumulators never leave registers.  A CTA's four warps take up to four such row tiles; with one or two
-//     row tiles the warps split the CTA's 64-cell tile four or two ways instead, each part an independent partial
-//     result, so that all four tensor cores work whatever the number of rows.  A warp walks its cells in steps of 16
-//     (two score tiles, one step of the output product), with the online-softmax update per step.
+//   * A PAIR of warps owns 16 query rows (an m16n8k16 tile row): both form the rows' scores and softmax statistics (the
+//     same instructions on the same data, so the same bits), and each accumulates one half of the head_dim output
+//     columns, so that running maximum, sum and output accumulators never leave registers and eight warps (two per
+//     scheduler) hide each other's latencies.  A CTA's four pairs take up to four such row tiles; with one or two row
+//     tiles the pairs split the CTA's 64-cell tile four or two ways instead, each part an independent partial result,
+//     so that all four tensor cores work whatever the number of rows.  A warp walks its cells in steps of 16 (two
+//     score tiles, one step of the output product), with the online-softmax update per step.
 //   * Cells arrive by 16-byte cp.async into a two-stage ring of raw tiles (the next tile's copies are in flight while
 //     this one is computed); all 128 threads widen a raw tile into the operand tiles (XOR-swizzled rows, so that
 //     ldmatrix is conflict-free), K first, then V into the same shared memory once the scores are done.
@@ -43,7 +45,7 @@
 namespace fnb {
 namespace {
 
-constexpr int kWarps = 4;
+constexpr int kWarps = 8;  // four score / step owners x two halves of the output columns
 constexpr int kThreads = kWarps * 32;
 constexpr int kStep = 16;  // cells of one step of a warp: two 8-cell score tiles, one k-step of the output product
 constexpr int kTile = 64;  // cells a CTA stages at once: four steps
@@ -221,7 +223,8 @@ template <int HD, bool KV8>
 __global__ void __launch_bounds__(kThreads, 1) attend_kernel(const attend_params p) {
     using L = smem_layout<HD, KV8>;
     constexpr int NB = HD / 32;      // 32-dim blocks
-    constexpr int NT = HD / 8;       // 8-dim output tiles
+    constexpr int NT = HD / 16;      // 8-dim output tiles of this warp's half of the columns
+    constexpr int kHalfChunks = HD / 16;  // 16-byte chunks (8 FP16 values) in half a row
     constexpr int kRow = L::kRow;
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t * q_hi = smem + L::q_hi;
@@ -233,8 +236,9 @@ __global__ void __launch_bounds__(kThreads, 1) attend_kernel(const attend_params
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const int g = lane >> 2, t4 = lane & 3;
     // this warp's row tile and its steps of the CTA tile: one row tile -> a step each, two -> two each, more -> all four
-    const int mt = p.parts == 4 ? 0 : p.parts == 2 ? (wid & 1) : wid;
-    const int part = p.parts == 4 ? wid : p.parts == 2 ? (wid >> 1) : 0;
+    const int dh = wid & 1, pair = wid >> 1;  // which half of the output columns; which of the four warp pairs
+    const int mt = p.parts == 4 ? 0 : p.parts == 2 ? (pair & 1) : pair;
+    const int part = p.parts == 4 ? pair : p.parts == 2 ? (pair >> 1) : 0;
     const int n_steps = 4 / p.parts, step0 = part * n_steps;
     const bool mma_warp = mt < p.m_tiles;
     const int r0 = 16 * mt + g, r1 = r0 + 8;  // the two query rows this lane's accumulators belong to
@@ -289,21 +293,29 @@ __global__ void __launch_bounds__(kThreads, 1) attend_kernel(const attend_params
         auto issue = [&](int tile, int st) {
             uint8_t * base = smem + L::raw + st * 2 * L::kRawTensor;
             const int64_t c0 = c_begin + int64_t(tile) * kTile;
-            // a 256-wide Q8_0 cell is 272 bytes = 17 x 16; a 128-wide one 136 = 17 x 8, only 8-byte aligned
+            // a thread copies one whole cell of one tensor (2 x 64 cells = the CTA's 128 threads): no index arithmetic
+            // per piece.  A 256-wide Q8_0 cell is 272 bytes = 17 x 16; a 128-wide one 136 = 17 x 8, only 8-byte aligned.
             constexpr int kPiece = L::kCell % 16 == 0 ? 16 : 8;
             constexpr int kChunks = L::kCell / kPiece;
-#pragma unroll 1
-            for (int i = tid; i < 2 * kTile * kChunks; i += kThreads) {
-                const int tensor = i / (kTile * kChunks), rem = i - tensor * (kTile * kChunks);
-                const int cell = rem / kChunks, ch = rem - cell * kChunks;
+            static_assert(4 * kTile == kThreads, "two threads a (tensor, cell)");
+            {
+                const int item = tid >> 1, second = tid & 1;
+                const int tensor = item / kTile, cell = item - tensor * kTile;
                 const int64_t c = c0 + cell;
                 const bool valid = c < c_end;
-                const uint8_t * src = (tensor == 0 ? p.k_cache : p.v_cache) + ((valid ? c : c_begin) * p.n_kv + head) * L::kCell + kPiece * ch;
-                uint8_t * dst = base + tensor * L::kRawTensor + cell * L::kCell + kPiece * ch;
-                if (kPiece == 16) {
-                    cp_async16(dst, src, valid);
-                } else {
-                    cp_async8(dst, src, valid);
+                const uint8_t * src = (tensor == 0 ? p.k_cache : p.v_cache) + ((valid ? c : c_begin) * p.n_kv + head) * L::kCell;
+                uint8_t * dst = base + tensor * L::kRawTensor + cell * L::kCell;
+                constexpr int kFirst = (kChunks + 1) / 2;  // pieces the first thread of the pair copies
+#pragma unroll
+                for (int j = 0; j < kFirst; ++j) {
+                    const int ch = second ? kFirst + j : j;
+                    if (ch < kChunks) {
+                        if (kPiece == 16) {
+                            cp_async16(dst + kPiece * ch, src + kPiece * ch, valid);
+                        } else {
+                            cp_async8(dst + kPiece * ch, src + kPiece * ch, valid);
+                        }
+                    }
                 }
             }
             if (KV8) {
@@ -488,7 +500,7 @@ __global__ void __launch_bounds__(kThreads, 1) attend_kernel(const attend_params
 #pragma unroll
                     for (int dp = 0; dp < NT / 2; ++dp) {
                         uint32_t bh[4], bl[4];
-                        const int vrow = cell0 + (lane & 7) + 8 * ((lane >> 3) & 1), vchunk = 2 * dp + (lane >> 4);
+                        const int vrow = cell0 + (lane & 7) + 8 * ((lane >> 3) & 1), vchunk = dh * kHalfChunks + 2 * dp + (lane >> 4);
                         ldsm4_t(bh, s_addr(v_hi + swz<kRow>(vrow, vchunk)));
                         ldsm4_t(bl, s_addr(v_lo + swz<kRow>(vrow, vchunk)));
                         mma16816(o[2 * dp], p_hi[st4], bh[0], bh[1]);
@@ -510,18 +522,19 @@ __global__ void __launch_bounds__(kThreads, 1) attend_kernel(const attend_params
             const int64_t slot = (int64_t(head) * p.n_units + u) * p.parts + part;
             float * ml = p.ws_ml + slot * p.m * 2;
             float * acc = p.ws_acc + slot * p.m * HD;
+            const int col0 = dh * (HD / 2);  // this warp's half of the output columns; the pair's first warp writes (max, sum)
             if (r0 < p.m) {
-                if (t4 == 0) ml[2 * r0] = m_run[0], ml[2 * r0 + 1] = l0;
+                if (t4 == 0 && dh == 0) ml[2 * r0] = m_run[0], ml[2 * r0 + 1] = l0;
 #pragma unroll
                 for (int d = 0; d < NT; ++d) {
-                    *reinterpret_cast<float2 *>(acc + int64_t(r0) * HD + 8 * d + 2 * t4) = make_float2(o[d][0] * kPUnscale, o[d][1] * kPUnscale);
+                    *reinterpret_cast<float2 *>(acc + int64_t(r0) * HD + col0 + 8 * d + 2 * t4) = make_float2(o[d][0] * kPUnscale, o[d][1] * kPUnscale);
                 }
             }
             if (r1 < p.m) {
-                if (t4 == 0) ml[2 * r1] = m_run[1], ml[2 * r1 + 1] = l1;
+                if (t4 == 0 && dh == 0) ml[2 * r1] = m_run[1], ml[2 * r1 + 1] = l1;
 #pragma unroll
                 for (int d = 0; d < NT; ++d) {
-                    *reinterpret_cast<float2 *>(acc + int64_t(r1) * HD + 8 * d + 2 * t4) = make_float2(o[d][2] * kPUnscale, o[d][3] * kPUnscale);
+                    *reinterpret_cast<float2 *>(acc + int64_t(r1) * HD + col0 + 8 * d + 2 * t4) = make_float2(o[d][2] * kPUnscale, o[d][3] * kPUnscale);
                 }
             }
         }
@@ -533,18 +546,22 @@ __global__ void __launch_bounds__(kThreads, 1) attend_kernel(const attend_params
 // are formed once per CTA in shared memory (slots in parallel), then every thread streams its column of the partials
 // with independent loads.
 constexpr int kFoldMaxSlots = 4096;
+constexpr int kFoldLanes = 4;  // threads a value: each streams every fourth partial
 
 template <int HD>
-__global__ void __launch_bounds__(HD) attend_fold_kernel(const attend_params p) {
+__global__ void __launch_bounds__(HD * kFoldLanes) attend_fold_kernel(const attend_params p) {
     __shared__ float w_of[kFoldMaxSlots];
-    __shared__ float red[HD / 32];
+    __shared__ float red[HD * kFoldLanes / 32];
+    __shared__ float part_a[kFoldLanes][HD];
     const int t = blockIdx.x / p.n_q, h = blockIdx.x - t * p.n_q;
     const int head = h / p.n_rep, row = t * p.n_rep + (h - head * p.n_rep);
-    const int d = threadIdx.x, lane = d & 31, wid = d >> 5;
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int d = tid % HD, q = tid / HD;
+    constexpr int kThreadsF = HD * kFoldLanes, kWarpsF = kThreadsF / 32;
     const int n = p.n_units * p.parts;
     const int64_t slot0 = int64_t(head) * n;
     float big = -INFINITY;
-    for (int j = d; j < n; j += HD) {
+    for (int j = tid; j < n; j += kThreadsF) {
         const float mj = __ldg(p.ws_ml + ((slot0 + j) * p.m + row) * 2);
         w_of[j] = mj;
         big = fmaxf(big, mj);
@@ -555,11 +572,11 @@ __global__ void __launch_bounds__(HD) attend_fold_kernel(const attend_params p) 
     __syncthreads();
     big = red[0];
 #pragma unroll
-    for (int i = 1; i < HD / 32; ++i) big = fmaxf(big, red[i]);
+    for (int i = 1; i < kWarpsF; ++i) big = fmaxf(big, red[i]);
     __syncthreads();
     // weights (0 for a partial with no live cell for this row, and for every partial of a row with none at all)
     float part_sum = 0.0f;
-    for (int j = d; j < n; j += HD) {
+    for (int j = tid; j < n; j += kThreadsF) {
         const float mj = w_of[j];
         const float w = mj == -INFINITY ? 0.0f : fast_exp2(mj - big);
         w_of[j] = w;
@@ -571,12 +588,16 @@ __global__ void __launch_bounds__(HD) attend_fold_kernel(const attend_params p) 
     __syncthreads();
     float sum = 0.0f;
 #pragma unroll
-    for (int i = 0; i < HD / 32; ++i) sum += red[i];
+    for (int i = 0; i < kWarpsF; ++i) sum += red[i];
     float a = 0.0f;
     const float * col = p.ws_acc + (slot0 * p.m + row) * HD + d;
     const int64_t stride = int64_t(p.m) * HD;
 #pragma unroll 8
-    for (int j = 0; j < n; ++j) a = fmaf(__ldg(col + j * stride), w_of[j], a);
+    for (int j = q; j < n; j += kFoldLanes) a = fmaf(__ldg(col + j * stride), w_of[j], a);
+    part_a[q][d] = a;
+    __syncthreads();
+    if (q != 0) return;
+    a = (part_a[0][d] + part_a[1][d]) + (part_a[2][d] + part_a[3][d]);
     float y = sum > 0.0f ? a / sum : 0.0f;  // a row with no cell at all gives zeros
     const int64_t at = (int64_t(t) * p.n_q + h) * HD + d;
     if (p.gate != nullptr) y *= 1.0f / (1.0f + expf(-__ldg(p.gate + at)));
@@ -604,7 +625,7 @@ int32_t launch_hd(const attend_params & p, cudaStream_t s) {
     const int units = p.n_kv * p.n_units;
     attend_kernel<HD, KV8><<<units < kSmCount ? units : kSmCount, kThreads, smem_layout<HD, KV8>::total, s>>>(p);
     if (cudaPeekAtLastError() != cudaSuccess) return FNB_LAUNCH_FAILED;
-    attend_fold_kernel<HD><<<p.rows * p.n_q, HD, 0, s>>>(p);
+    attend_fold_kernel<HD><<<p.rows * p.n_q, HD * kFoldLanes, 0, s>>>(p);
     return launch_status();
 }
 

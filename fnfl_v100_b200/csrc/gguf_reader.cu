@@ -14,6 +14,9 @@
 
 namespace {
 
+inline bool mul_ok(uint64_t a, uint64_t b, uint64_t & out) { return !__builtin_mul_overflow(a, b, &out); }
+inline bool add_ok(uint64_t a, uint64_t b, uint64_t & out) { return !__builtin_add_overflow(a, b, &out); }
+
 struct tensor_rec {
     std::string name;
     fnb_gguf_tensor t;
@@ -64,7 +67,9 @@ bool skip_value(FILE * f, uint32_t type, uint64_t file_size, uint64_t * as_u64) 
         uint32_t et = 0;
         uint64_t cnt = 0;
         if (!rd(f, et) || !rd(f, cnt) || cnt > file_size) return false;
-        if (const size_t n = scalar_bytes(et)) return std::fseek(f, long(cnt * n), SEEK_CUR) == 0;
+        if (const size_t n = scalar_bytes(et)) {  // cnt <= file_size and n <= 8: the product cannot wrap
+            return cnt * n <= file_size && fseeko(f, off_t(cnt * n), SEEK_CUR) == 0;
+        }
         for (uint64_t i = 0; i < cnt; ++i) {
             if (!skip_value(f, et, file_size, nullptr)) return false;
         }
@@ -128,18 +133,25 @@ extern "C" fnb_gguf * fnb_gguf_open(const char * path) {
         t.t.offset = int64_t(off);
         uint32_t bv = 0, bb = 0;
         if (ok && block_of(type, bv, bb) && uint64_t(t.t.ne[0]) % bv == 0) {
-            t.t.row_bytes = int64_t(uint64_t(t.t.ne[0]) / bv * bb);
-            t.t.n_rows = t.t.ne[1] * t.t.ne[2] * t.t.ne[3];
+            // every product checked: a hostile or corrupt directory must not wrap its way past the bounds test below
+            uint64_t rows = 0, row_bytes = 0;
+            ok = mul_ok(uint64_t(t.t.ne[1]), uint64_t(t.t.ne[2]), rows) && mul_ok(rows, uint64_t(t.t.ne[3]), rows) &&
+                 mul_ok(uint64_t(t.t.ne[0]) / bv, bb, row_bytes) && rows <= uint64_t(INT64_MAX) && row_bytes <= uint64_t(INT64_MAX);
+            t.t.row_bytes = int64_t(row_bytes);
+            t.t.n_rows = int64_t(rows);
         }  // else row_bytes stays 0: a type this library does not decode
+        ok = ok && off % alignment == 0 && off <= uint64_t(INT64_MAX);
         if (ok) r->tensors.push_back(t);
     }
     if (ok) {
         const uint64_t here = uint64_t(std::ftell(r->f));
         r->data_start = (here + alignment - 1) / alignment * alignment;
         for (const tensor_rec & t : r->tensors) {
+            uint64_t bytes = 0, end = 0;
             if (t.t.row_bytes > 0 &&
-                r->data_start + uint64_t(t.t.offset) + uint64_t(t.t.row_bytes) * uint64_t(t.t.n_rows) > r->file_size) {
-                ok = false;  // a tensor that runs past the end of the file
+                !(mul_ok(uint64_t(t.t.row_bytes), uint64_t(t.t.n_rows), bytes) && add_ok(r->data_start, uint64_t(t.t.offset), end) &&
+                  add_ok(end, bytes, end) && end <= r->file_size)) {
+                ok = false;  // a tensor that runs past the end of the file, or whose size does not fit 64 bits
             }
         }
     }
@@ -174,10 +186,16 @@ extern "C" int32_t fnb_gguf_find(const fnb_gguf * g, const char * name, fnb_gguf
 }
 
 extern "C" int32_t fnb_gguf_read_rows(fnb_gguf * g, const fnb_gguf_tensor * t, int64_t row0, int64_t n_rows, void * dst) {
-    if (g == nullptr || t == nullptr || dst == nullptr || t->row_bytes <= 0) return FNB_REJECTED;
-    if (row0 < 0 || n_rows < 1 || row0 + n_rows > t->n_rows) return FNB_REJECTED;
+    if (g == nullptr || t == nullptr || dst == nullptr || t->row_bytes <= 0 || t->offset < 0 || t->n_rows < 0) return FNB_REJECTED;
+    if (row0 < 0 || n_rows < 1 || row0 > t->n_rows || n_rows > t->n_rows - row0) return FNB_REJECTED;
     reader * r = reinterpret_cast<reader *>(g);
-    const uint64_t at = r->data_start + uint64_t(t->offset) + uint64_t(row0) * uint64_t(t->row_bytes);
-    if (std::fseek(r->f, long(at), SEEK_SET) != 0) return FNB_REJECTED;
-    return rd(r->f, dst, size_t(n_rows) * size_t(t->row_bytes)) ? FNB_OK : FNB_REJECTED;
+    // the descriptor is the caller's: it is checked against the file again, whatever the directory said
+    uint64_t skip = 0, at = 0, bytes = 0, end = 0;
+    if (!mul_ok(uint64_t(row0), uint64_t(t->row_bytes), skip) || !add_ok(r->data_start, uint64_t(t->offset), at) ||
+        !add_ok(at, skip, at) || !mul_ok(uint64_t(n_rows), uint64_t(t->row_bytes), bytes) || !add_ok(at, bytes, end) ||
+        end > r->file_size || at > uint64_t(INT64_MAX)) {
+        return FNB_REJECTED;
+    }
+    if (fseeko(r->f, off_t(at), SEEK_SET) != 0) return FNB_REJECTED;
+    return rd(r->f, dst, size_t(bytes)) ? FNB_OK : FNB_REJECTED;
 }

@@ -453,6 +453,9 @@ int32_t fnb_expert_down_rows_q5_1(const void * w, int64_t row_bytes, int32_t n, 
  * The same mat-vec with ggml Q8_0 weights (34-byte blocks) against Q8_0 activations (fnb_quantize_q8_0 /
  * fnb_rms_norm_q8_0 blocks): fn::experts::cpu::kq_down_rows for fmt q8_0 (cpu_kq_avx2.cpp:322-344), same bits (eight
  * accumulators, one fused multiply-add per block and lane with the product of the two block scales, no side sum).
+ * The same bits hold for activation codes in [-127, 127], which is every code ggml's Q8_0 quantiser and
+ * fnb_quantize_q8_0 emit; a hand-made -128 code under a negative weight differs (the AVX2 kernel's sign step leaves
+ * -128 as it is; only the IQ4_NL and IQ gate / up entry points reproduce that corner).
  * n a multiple of 128 (rows are whole 8-byte pairs); row_bytes = n / 32 * 34; w 8-byte, act 2-byte aligned.
  */
 int32_t fnb_expert_down_rows_q8_0(const void * w, int64_t row_bytes, int32_t n, const void * act, int64_t act_stride,
