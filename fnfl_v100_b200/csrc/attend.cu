@@ -151,16 +151,15 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
 }
 
 // One pair of Q8_0 blocks of a cell (68 bytes = 17 aligned words x: d0 | 32 codes | d1 | 32 codes) widened into the
-// operand tile(s): 64 values = eight 16-byte chunks.  PR (the pair's index in the cell) rotates the order the chunks
-// are written in, so that the four threads of a cell do not hit one bank group at a time.
+// operand tile(s): 64 values = eight 16-byte chunks.  The four threads of a cell (pair index pr = 0 .. 3) run the same
+// instructions: a warp's raw loads fall on 32 different banks (word 68 cell + 17 pr + j), and its 16-byte stores, 512
+// bytes an instruction, take the four wavefronts that much data needs whatever the order.
 //   V = false: the codes as FP16 integers (the K operand).  V = true: hi = rn(d x code) and lo = fma(d, code, -hi).
-template <int PR, bool V, int ROW_BYTES>
-__device__ __forceinline__ void widen_pair(const uint32_t (&x)[17], int cell, uint8_t * t_hi, uint8_t * t_lo) {
+template <bool V, int ROW_BYTES>
+__device__ __forceinline__ void widen_pair(const uint32_t (&x)[17], int cell, int pr, uint8_t * t_hi, uint8_t * t_lo) {
     const __half d_first = __ushort_as_half(uint16_t(x[0] & 0xffffu)), d_second = __ushort_as_half(uint16_t(x[8] >> 16));
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        constexpr int kRot = 2 * PR;
-        const int jj = (j + kRot) & 7;  // static after unrolling
+    for (int jj = 0; jj < 8; ++jj) {
         uint32_t c0, c1;
         if (jj < 4) {
             c0 = __funnelshift_r(x[2 * jj], x[2 * jj + 1], 16), c1 = __funnelshift_r(x[2 * jj + 1], x[2 * jj + 2], 16);
@@ -170,7 +169,7 @@ __device__ __forceinline__ void widen_pair(const uint32_t (&x)[17], int cell, ui
         __half2 c[4];
         codes_to_h2(c0, c[0], c[1]);
         codes_to_h2(c1, c[2], c[3]);
-        const uint32_t at = swz<ROW_BYTES>(cell, 8 * PR + jj);
+        const uint32_t at = swz<ROW_BYTES>(cell, 8 * pr + jj);
         if (!V) {
             *reinterpret_cast<uint4 *>(t_hi + at) = make_uint4(h2_bits(c[0]), h2_bits(c[1]), h2_bits(c[2]), h2_bits(c[3]));
         } else {
@@ -194,12 +193,7 @@ __device__ __forceinline__ void widen_q8_0_tile(const uint8_t * raw, int cell_by
         uint32_t x[17];
 #pragma unroll
         for (int j = 0; j < 17; ++j) x[j] = w[j];
-        switch (pr) {
-            case 0: widen_pair<0, V, ROW_BYTES>(x, cell, t_hi, t_lo); break;
-            case 1: widen_pair<1, V, ROW_BYTES>(x, cell, t_hi, t_lo); break;
-            case 2: widen_pair<2, V, ROW_BYTES>(x, cell, t_hi, t_lo); break;
-            default: widen_pair<3, V, ROW_BYTES>(x, cell, t_hi, t_lo); break;
-        }
+        widen_pair<V, ROW_BYTES>(x, cell, pr, t_hi, t_lo);
     }
 }
 

@@ -26,7 +26,9 @@ OPS = ("get_rows_q4_k", "get_rows_iq3_xxs", "rms_norm", "rms_norm_heads", "rope_
        "expert_gate_up_iq3_s_nt1", "expert_gate_up_iq3_s_nt3", "expert_gate_up_iq3_s_nt8",
        "expert_gate_up_iq3_xxs_nt1", "expert_gate_up_iq3_xxs_nt3", "expert_gate_up_iq3_xxs_nt8",
        "expert_gate_up_iq2_xxs_nt1", "expert_gate_up_iq2_xxs_nt3", "expert_gate_up_iq2_xs_nt1", "expert_gate_up_iq2_s_nt1",
-       "attend_q8_0_b1", "attend_q8_0_b3", "attend_q8_0_b5", "attend_kv8_b1", "attend_kv8_b5")
+       "attend_q8_0_b1", "attend_q8_0_b3", "attend_q8_0_b5", "attend_kv8_b1", "attend_kv8_b5",
+       # shapes that take the general kernels instead of the tuned ones: 64-wide heads with 32 rotated dims, 4096 columns
+       "rope_kv_fallback", "get_rows_q4_k_c4096", "get_rows_iq3_xxs_c4096")
 
 
 def hbm_peak() -> float:
@@ -42,13 +44,28 @@ def make_case(op: str, T: int, dev, gen, c: ChainConfig):
     """Returns (launch, algorithmic bytes)."""
     N = synth.torch_normal
     if op.startswith("get_rows"):
-        fmt = op[len("get_rows_"):]
-        table = synth.torch_table(fmt, gen, c.n_vocab, c.hidden, dev)
+        fmt, cols = op[len("get_rows_"):], c.hidden
+        if fmt.endswith("_c4096"):
+            fmt, cols = fmt[:-len("_c4096")], 4096
+        table = synth.torch_table(fmt, gen, c.n_vocab, cols, dev)
         ids = torch.randint(0, c.n_vocab, (T,), dtype=torch.int32, device=dev, generator=gen)
-        out = torch.empty((T, c.hidden), dtype=torch.float32, device=dev)
+        out = torch.empty((T, cols), dtype=torch.float32, device=dev)
         err = ops.new_err(dev)
-        return (lambda: ops.get_rows(fmt, table, ids, c.hidden, out=out, err=err),
-                T * (ops.table_row_bytes(fmt, c.hidden) + 4 + c.hidden * 4))
+        return (lambda: ops.get_rows(fmt, table, ids, cols, out=out, err=err),
+                T * (ops.table_row_bytes(fmt, cols) + 4 + cols * 4))
+    if op == "rope_kv_fallback":
+        # 64 heads of 64 (the same bytes a token as the chain's 16 x 256), 32 rotated dims: the row-per-warp kernel
+        hq, hk, hd, n_rot = 64, 8, 64, 32
+        q, k, v = N(gen, (T, hq, hd), 1.0, dev), N(gen, (T, hk, hd), 1.0, dev), N(gen, (T, hk, hd), 1.0, dev)
+        wq, wk = 1 + 0.1 * N(gen, (hd,), 1.0, dev), 1 + 0.1 * N(gen, (hd,), 1.0, dev)
+        pos = (c.depth + torch.arange(T, device=dev)).to(torch.int32)
+        q_out = torch.empty_like(q)
+        err = ops.new_err(dev)
+        kc, vc = ops.new_kv_cache(c.cache_slots, hk, hd, dev), ops.new_kv_cache(c.cache_slots, hk, hd, dev)
+        ts = ops.theta_scale(c.freq_base, n_rot)
+        return (lambda: ops.rope_neox_q8_0_append(q, k, v, pos, n_rot=n_rot, theta_scale=ts, k_cache=kc, v_cache=vc,
+                                                  q_norm_w=wq, k_norm_w=wk, eps=c.eps, q_out=q_out, err=err)), \
+            T * (2 * hq * hd * 4 + 2 * hk * hd * 4 + 4 + 2 * hk * hd // 32 * ops.Q8_0_BLOCK)
     if op == "embed_iq3_s":
         # the reference's two-card layout (fn/kernels/embed/embed.h:70-87): 1280 own features of 2560, four streams
         n_own, n_full, n_streams, vocab = 1280, 2560, 4, 248320
