@@ -10,66 +10,78 @@
 // head against an FP64 reference over the decoded cache (fn/kernels/qsa/qa2_test.cpp:469-520).
 //
 // Roofline: the cache is read once, 2 x 272 bytes per cell and KV head (Q8_0), shared by every query row of the
-// head's group; the work per byte is a contraction (M = rows x heads per group query rows against every cell), so the
-// products run on the tensor pipe and everything else is shaped around feeding it:
+// head's group; the work per byte is a contraction (M = rows x heads per group query rows against every cell), so both
+// products run on the 5th-generation tensor cores (tcgen05.mma, accumulators in tensor memory) and everything else is
+// shaped around feeding them:
 //
-//   * Split precision.  The 1e-5 bound needs products far more exact than 11-bit operands give, so every F32 operand
-//     becomes two FP16 operands (value = hi + lo, about 22 bits):  q = q_hi + q_lo;  K stays the INTEGER codes (exact in
-//     FP16) and each 32-dim block's partial dot product is multiplied by the block's scale in F32 afterwards, so
-//     q . K costs two tensor products, not three;  V = d x code is split exactly (hi = the rounded product, lo = the
-//     fused residual, both one half2 instruction per two values) and p = p_hi + p_lo (scaled by 2^12 to stay clear of
-//     FP16's subnormals), so p . V costs three (the lo x lo term is below 2^-22).
-//   * A PAIR of warps owns 16 query rows (an m16n8k16 tile row): both form the rows' scores and softmax statistics (the
-//     same instructions on the same data, so the same bits), and each accumulates one half of the head_dim output
-//     columns, so that running maximum, sum and output accumulators never leave registers and eight warps (two per
-//     scheduler) hide each other's latencies.  A CTA's four pairs take up to four such row tiles; with one or two row
-//     tiles the pairs split the CTA's 64-cell tile four or two ways instead, each part an independent partial result,
-//     so that all four tensor cores work whatever the number of rows.  A warp walks its cells in steps of 16 (two
-//     score tiles, one step of the output product), with the online-softmax update per step.
-//   * Cells arrive by 16-byte cp.async into a two-stage ring of raw tiles (the next tile's copies are in flight while
-//     this one is computed); all 128 threads widen a raw tile into the operand tiles (XOR-swizzled rows, so that
-//     ldmatrix is conflict-free), K first, then V into the same shared memory once the scores are done.
-//   * Split over cells (flash decoding): a work unit is (KV head, range of cells); units and tile parts write
-//     (max, sum, unnormalised output) partials into a caller-supplied workspace, and a second small kernel folds them
-//     in a fixed order, divides, gates and writes the rows.  The workspace is the only global memory beyond inputs and
-//     outputs; its size is a function of the shape (fnb_attend_workspace_bytes).
+//   * Split precision.  The 1e-5 bound needs products far more exact than 11-bit operands give, so every operand is
+//     two FP16 operands, value = hi + lo (about 22 bits):  q = q_hi + q_lo (rounded residual);  K and V = d x code,
+//     split EXACTLY (hi = the rounded product, lo = the fused residual, one half2 instruction each per two values);
+//     p = p_hi + p_lo (scaled by 2^12 to stay clear of FP16's subnormals).
+//   * Stacked rows.  A group has at most 64 query rows and the MMA is 128 rows tall: rows 0 .. 63 of the A operand hold
+//     the hi parts and rows 64 .. 127 the lo parts, so ONE pass over the B operand gives hi . B in accumulator rows
+//     0 .. 63 and lo . B in rows 64 .. 127, and the sum of the two rows is the product of the full-precision operand.
+//     Scores: S = [q_hi; q_lo] . (K_hi + K_lo)^T (two accumulating MMAs per 16 dims).  Outputs: O += [p_hi; p_lo] .
+//     (V_hi + V_lo) (two per 16 cells).  All four partial products are kept.
+//   * Operand tiles in shared memory are written directly in the MMA's canonical layout: 64-dim blocks of [row][128
+//     bytes] with the 16-byte chunks XOR-swizzled by the row's low three bits (the 128-byte swizzle).  The same bytes
+//     serve as a K-major operand (rows = cells, for the scores) and as an MN-major operand (contiguous = dims, for the
+//     outputs), so K and V are widened by the same code: a thread takes a pair of Q8_0 blocks (or 64 KV8 codes) of one
+//     cell from registers and stores eight 16-byte chunks each of hi and lo.
+//   * The cache is read straight into registers one tile (64 cells) ahead: shared memory is full of operands.
+//   * One thread issues the MMAs; completion comes back through mbarriers (tcgen05.commit).  While the score MMAs of a
+//     tile run, all warps widen its V; while the output MMAs run, they widen the next tile's K.  Warps 0 .. 3 (the
+//     four 32-lane quarters of tensor memory) read the scores, warps 2 and 3 hand their rows (the lo parts) to warps 0
+//     and 1 through shared memory, and a thread of warps 0 / 1 owns one query row: mask, running maximum and sum,
+//     probabilities, all without shuffles.  The maximum is lazy: the reference point moves only when a row's maximum
+//     has grown by more than 2^3, and only then are the row's accumulators rescaled in tensor memory.
+//   * Split over cells (flash decoding): a work unit is (KV head, range of cells), about one per SM; a unit writes
+//     (reference point, sum, unnormalised output) partials into a caller-supplied workspace, and a second small kernel
+//     folds them in a fixed order, divides, gates and writes the rows.  The workspace is the only global memory beyond
+//     inputs and outputs; its size is a function of the shape (fnb_attend_workspace_bytes).
 //
-// No kernel here waits on another: the fold is a second launch on the same stream.
+// Every wait is bounded (bulk_pipe.cuh): one that runs out ORs FNB_ERR_TIMEOUT into the error word and the kernel
+// carries on to its end, where tensor memory is freed.  No kernel here waits on another: the fold is a second launch
+// on the same stream.  Nothing here reads another GPU's memory.
 #include <atomic>
 #include <cstdio>
 
 #include <cuda_fp16.h>
 
+#include "bulk_pipe.cuh"
 #include "common.cuh"
 
 namespace fnb {
 namespace {
 
-constexpr int kWarps = 8;  // four score / step owners x two halves of the output columns
-constexpr int kThreads = kWarps * 32;
-constexpr int kStep = 16;  // cells of one step of a warp: two 8-cell score tiles, one k-step of the output product
-constexpr int kTile = 64;  // cells a CTA stages at once: four steps
-constexpr int kMaxM = 64;  // query rows of one KV head's group: rows x (n_q_heads / n_kv_heads)
+constexpr int kThreads = 256;
+constexpr int kTile = 64;   // cells per tile: the N of the score MMA, four K steps of the output MMA
+constexpr int kMaxM = 64;   // query rows of one KV head's group: rows x (n_q_heads / n_kv_heads)
 constexpr float kPScale = 4096.0f, kPUnscale = 1.0f / 4096.0f;
+constexpr float kLazy = 3.0f;  // log2 units a row's maximum may exceed its reference point: p <= 8, p x 2^12 fits FP16
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct attend_plan {
-    int m, m_tiles, parts;   // query rows per group, their 16-row tiles, partial results a unit writes (1, 2 or 4)
+    int m, parts;            // query rows per group; partial results a unit writes (1)
     int64_t unit_cells;      // cells per work unit (a multiple of kTile)
     int n_units;             // units per KV head
     int64_t slots;           // partial results in the workspace: n_kv x n_units x parts
 };
 
-// the split the launcher and the workspace size agree on: about two units per SM over all KV heads, never shorter
-// than 256 cells
+// The split the launcher and the workspace size agree on: about two units per SM over all KV heads, never shorter than
+// 256 cells and never longer than 24 tiles.  The cap is a matter of accuracy, not speed: the tensor core adds into its
+// F32 accumulator by truncation, about 0.7 x 2^-24 of relative bias per accumulation step, and a unit's output rows take
+// four such steps per tile; 24 tiles keep that below 5e-6 of the 1e-5 bound.  Partials are combined by the fold kernel
+// in round-to-nearest F32.
+constexpr int kMaxUnitTiles = 24;
 inline attend_plan make_plan(int rows, int n_q, int n_kv, int64_t range) {
     attend_plan p;
     p.m = rows * (n_q / n_kv);
-    p.m_tiles = (p.m + 15) / 16;
-    p.parts = p.m_tiles == 1 ? 4 : p.m_tiles == 2 ? 2 : 1;
+    p.parts = 1;
     int64_t want = (2 * int64_t(kSmCount) + n_kv - 1) / n_kv;
     int64_t cells = (range + want - 1) / want;
     cells = cells < 256 ? 256 : cells;
+    cells = cells > int64_t(kMaxUnitTiles) * kTile ? int64_t(kMaxUnitTiles) * kTile : cells;
     p.unit_cells = (cells + kTile - 1) / kTile * kTile;
     p.n_units = int((range + p.unit_cells - 1) / p.unit_cells);
     if (p.n_units < 1) p.n_units = 1;
@@ -88,45 +100,15 @@ struct attend_params {
     const int32_t * first_cell;
     const int32_t * n_cells;
     float * out;
-    float * ws_ml;   // [slots][m][2]: running maximum (in log2 units) and sum
+    float * ws_ml;   // [slots][m][2]: reference point (in log2 units) and sum
     float * ws_acc;  // [slots][m][head_dim]
     uint32_t * err;
     int64_t cache_slots, range_begin, range_end, unit_cells;
-    int rows, n_q, n_kv, n_rep, m, m_tiles, parts, n_units;
+    int rows, n_q, n_kv, n_rep, m, parts, n_units;
     float scale_log2;  // softmax scale x log2(e)
 };
 
-// ---- small PTX wrappers ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t s_addr(const void * p) { return uint32_t(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(addr));
-}
-__device__ __forceinline__ void ldsm4_t(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(addr));
-}
-// d += a (16 x 16, row) x b (16 x 8, col), FP16 operands, F32 accumulators
-__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-// 16 (or 8) bytes global -> shared; src_bytes = 0 writes zeros instead (cells past the end of a range)
-__device__ __forceinline__ void cp_async16(void * dst, const void * src, bool valid) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s_addr(dst)), "l"(src), "r"(valid ? 16 : 0) : "memory");
-}
-__device__ __forceinline__ void cp_async8(void * dst, const void * src, bool valid) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(s_addr(dst)), "l"(src), "r"(valid ? 8 : 0) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
+// ---- small wrappers -------------------------------------------------------------------------------------------------
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -144,99 +126,215 @@ __device__ __forceinline__ void codes_to_h2(uint32_t w, __half2 & lo, __half2 & 
     hi = __hsub2(bits_h2(__byte_perm(b, 0x64646464u, 0x4342u)), bias);
 }
 
-// operand tiles: rows of ROW_BYTES bytes (a power of two >= 128), 16-byte chunks XOR-swizzled by the row's low three bits
-template <int ROW_BYTES>
-__device__ __forceinline__ uint32_t swz(int row, int chunk) {
-    return uint32_t(row) * ROW_BYTES + (uint32_t(chunk ^ (row & 7)) << 4);
+// ---- tensor memory and the MMA --------------------------------------------------------------------------------------
+// Shared-memory matrix descriptor of an operand in the 128-byte-swizzled canonical layout: start address, leading and
+// stride byte offsets (in 16-byte units), descriptor version 1, layout type 2 (128-byte swizzle).
+//   K-major (rows of 128 bytes = 64 FP16 along K): stride offset = bytes between 8-row groups; leading offset unused.
+//   MN-major (rows of 128 bytes = 64 FP16 along MN, one row per K index): stride offset = bytes between groups of 8 K
+//   indices, leading offset = bytes between 64-element blocks along MN.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t leading_bytes, uint32_t stride_bytes) {
+    return uint64_t((saddr & 0x3ffffu) >> 4) | (uint64_t(leading_bytes >> 4) << 16) | (uint64_t(stride_bytes >> 4) << 32) |
+           (1ull << 46) | (2ull << 61);
 }
+// instruction descriptor, kind::f16: F32 accumulator, FP16 A and B, A K-major, B K-major or MN-major, M = 128, N
+__host__ __device__ constexpr uint32_t umma_idesc(int n, bool b_mn_major) {
+    return (1u << 4) | (b_mn_major ? (1u << 16) : 0u) | (uint32_t(n >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// the barrier gets one arrival when every MMA issued so far by this thread has completed
+__device__ __forceinline__ void umma_commit(uint64_t * bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// generic-proxy writes to shared memory made visible to the tensor core's (async proxy) reads
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-// One pair of Q8_0 blocks of a cell (68 bytes = 17 aligned words x: d0 | 32 codes | d1 | 32 codes) widened into the
-// operand tile(s): 64 values = eight 16-byte chunks.  The four threads of a cell (pair index pr = 0 .. 3) run the same
-// instructions: a warp's raw loads fall on 32 different banks (word 68 cell + 17 pr + j), and its 16-byte stores, 512
-// bytes an instruction, take the four wavefronts that much data needs whatever the order.
-//   V = false: the codes as FP16 integers (the K operand).  V = true: hi = rn(d x code) and lo = fma(d, code, -hi).
-template <bool V, int ROW_BYTES>
-__device__ __forceinline__ void widen_pair(const uint32_t (&x)[17], int cell, int pr, uint8_t * t_hi, uint8_t * t_lo) {
-    const __half d_first = __ushort_as_half(uint16_t(x[0] & 0xffffu)), d_second = __ushort_as_half(uint16_t(x[8] >> 16));
+__device__ __forceinline__ void tmem_alloc(uint32_t * slot, uint32_t cols) {  // one whole warp
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {  // the same warp
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+// 32 consecutive columns of this thread's lane (the warp's quarter of tensor memory: lanes 32 (warp % 4) ..)
+__device__ __forceinline__ void tmem_ld32(uint32_t addr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(addr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t addr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(addr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+          "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+          "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+          "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+          "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])),
+          "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+          "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+          "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])),
+          "r"(__float_as_uint(v[31]))
+        : "memory");
+}
+// barrier among `threads` threads on hardware barrier `id` chosen at run time
+__device__ __forceinline__ void named_barrier_id(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// ---- shared memory --------------------------------------------------------------------------------------------------
+// Operand tiles: 64-dim (or, for P, 64-cell) blocks of [rows][128 bytes]; chunk c of row r sits at chunk c ^ (r & 7).
+// Stacked operands interleave the parts: row 2 r holds query row r's hi part, row 2 r + 1 its lo part, so the two
+// accumulator rows of a query row sit in adjacent lanes of one 32-lane quarter of tensor memory.
+template <int HD>
+struct tc_layout {
+    static constexpr int kBlocks = HD / 64;
+    static constexpr int kQBlock = 128 * 128;                 // a block of a stacked operand
+    static constexpr int kCBlock = kTile * 128;               // a block of a cell operand
+    static constexpr int a_q = 0;                             // [kBlocks][128][128 B]: rows 2 r: q_hi, 2 r + 1: q_lo
+    static constexpr int k_hi = a_q + kBlocks * kQBlock;
+    static constexpr int k_lo = k_hi + kBlocks * kCBlock;
+    static constexpr int v_hi = k_lo + kBlocks * kCBlock;
+    static constexpr int v_lo = v_hi + kBlocks * kCBlock;
+    static constexpr int p_op = v_lo + kBlocks * kCBlock;     // [128][128 B]: rows 2 r: p_hi, 2 r + 1: p_lo
+    static constexpr int p_alt = p_op + kQBlock;              // [128][128 B]: rows 2 r: zeros, 2 r + 1: p_hi
+    static constexpr int ranges = p_alt + kQBlock;            // int32 lo[64], hi[64]
+    static constexpr int half_max = ranges + 2 * kMaxM * 4;   // float [2][64]: a row's maximum over each half of a tile
+    static constexpr int bars = half_max + 2 * kMaxM * 4;     // two mbarriers
+    static constexpr int misc = bars + 16;                    // tensor-memory base
+    static constexpr int total = misc + 16 + 1024;            // + slack to align the base to 1024 bytes
+    static constexpr uint32_t kTmemCols = HD == 256 ? 512 : 256;  // 64 score columns + HD output columns, a power of two
+    static_assert(total <= 232448, "shared memory of one CTA");
+};
+__device__ __forceinline__ uint32_t op_at(int row, int chunk) { return uint32_t(row) * 128u + (uint32_t(chunk ^ (row & 7)) << 4); }
+
+// ---- a thread's share of a tile of raw cells, in registers ----------------------------------------------------------
+// Q8_0: one pair of blocks of a cell, 68 bytes = 17 aligned words: d0 | 32 codes | d1 | 32 codes.  KV8: 64 codes and
+// their group's scale.  Cells past the end of the unit read as zeros.
+template <bool KV8>
+struct raw_item {
+    uint32_t w[KV8 ? 16 : 17];
+    uint32_t scale;  // KV8: the group's FP16 scale bits
+};
+template <int HD, bool KV8>
+__device__ __forceinline__ void load_item(raw_item<KV8> & r, const uint8_t * cache, const uint16_t * scales, int64_t cell_head,
+                                          int pr, bool valid) {
+    if (KV8) {
+        const uint4 * src = reinterpret_cast<const uint4 *>(cache + cell_head * HD + 64 * pr);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint4 v = valid ? __ldg(src + j) : make_uint4(0, 0, 0, 0);
+            r.w[4 * j] = v.x, r.w[4 * j + 1] = v.y, r.w[4 * j + 2] = v.z, r.w[4 * j + 3] = v.w;
+        }
+        r.scale = valid ? uint32_t(__ldg(scales + cell_head * (HD / 64) + pr)) : 0u;
+    } else {
+        const uint32_t * src = reinterpret_cast<const uint32_t *>(cache + cell_head * (HD / 32 * 34) + 68 * pr);
+#pragma unroll
+        for (int j = 0; j < 17; ++j) r.w[j] = valid ? __ldg(src + j) : 0u;
+        r.scale = 0;
+    }
+}
+// widen the item into block `pr` of the hi and lo operand tiles: value = d x code, hi = rn(value), lo = value - hi
+template <bool KV8>
+__device__ __forceinline__ void widen_item(const raw_item<KV8> & r, int cell, int pr, uint8_t * t_hi, uint8_t * t_lo) {
+    __half d_first, d_second;
+    if (KV8) {
+        d_first = d_second = __ushort_as_half(uint16_t(r.scale));
+    } else {
+        d_first = __ushort_as_half(uint16_t(r.w[0] & 0xffffu)), d_second = __ushort_as_half(uint16_t(r.w[8] >> 16));
+    }
 #pragma unroll
     for (int jj = 0; jj < 8; ++jj) {
         uint32_t c0, c1;
-        if (jj < 4) {
-            c0 = __funnelshift_r(x[2 * jj], x[2 * jj + 1], 16), c1 = __funnelshift_r(x[2 * jj + 1], x[2 * jj + 2], 16);
+        if (KV8) {
+            c0 = r.w[2 * jj], c1 = r.w[2 * jj + 1];
+        } else if (jj < 4) {
+            c0 = __funnelshift_r(r.w[2 * jj], r.w[2 * jj + 1], 16), c1 = __funnelshift_r(r.w[2 * jj + 1], r.w[2 * jj + 2], 16);
         } else {
-            c0 = x[2 * jj + 1], c1 = x[2 * jj + 2];
+            c0 = r.w[2 * jj + 1], c1 = r.w[2 * jj + 2];
         }
-        __half2 c[4];
+        __half2 c[4], h[4], l[4];
         codes_to_h2(c0, c[0], c[1]);
         codes_to_h2(c1, c[2], c[3]);
-        const uint32_t at = swz<ROW_BYTES>(cell, 8 * pr + jj);
-        if (!V) {
-            *reinterpret_cast<uint4 *>(t_hi + at) = make_uint4(h2_bits(c[0]), h2_bits(c[1]), h2_bits(c[2]), h2_bits(c[3]));
-        } else {
-            const __half2 d2 = __half2half2(jj < 4 ? d_first : d_second);
-            __half2 h[4], l[4];
+        const __half2 d2 = __half2half2(jj < 4 ? d_first : d_second);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                h[e] = __hmul2(d2, c[e]);
-                l[e] = __hfma2(d2, c[e], __hneg2(h[e]));
-            }
-            *reinterpret_cast<uint4 *>(t_hi + at) = make_uint4(h2_bits(h[0]), h2_bits(h[1]), h2_bits(h[2]), h2_bits(h[3]));
-            *reinterpret_cast<uint4 *>(t_lo + at) = make_uint4(h2_bits(l[0]), h2_bits(l[1]), h2_bits(l[2]), h2_bits(l[3]));
+        for (int e = 0; e < 4; ++e) {
+            h[e] = __hmul2(d2, c[e]);
+            l[e] = __hfma2(d2, c[e], __hneg2(h[e]));
         }
+        const uint32_t at = uint32_t(pr) * (kTile * 128) + op_at(cell, jj);
+        *reinterpret_cast<uint4 *>(t_hi + at) = make_uint4(h2_bits(h[0]), h2_bits(h[1]), h2_bits(h[2]), h2_bits(h[3]));
+        *reinterpret_cast<uint4 *>(t_lo + at) = make_uint4(h2_bits(l[0]), h2_bits(l[1]), h2_bits(l[2]), h2_bits(l[3]));
     }
 }
-template <bool V, int ROW_BYTES>
-__device__ __forceinline__ void widen_q8_0_tile(const uint8_t * raw, int cell_bytes, int pairs, uint8_t * t_hi, uint8_t * t_lo, int tid) {
-    for (int i = tid; i < kTile * pairs; i += kThreads) {
-        const int cell = i / pairs, pr = i - cell * pairs;
-        const uint32_t * w = reinterpret_cast<const uint32_t *>(raw + cell * cell_bytes + 68 * pr);
-        uint32_t x[17];
-#pragma unroll
-        for (int j = 0; j < 17; ++j) x[j] = w[j];
-        widen_pair<V, ROW_BYTES>(x, cell, pr, t_hi, t_lo);
-    }
-}
-
-// ---- shared memory layout -------------------------------------------------------------------------------------------
-template <int HD, bool KV8>
-struct smem_layout {
-    static constexpr int kRow = HD * 2;                                 // bytes of an FP16 row
-    static constexpr int kCell = KV8 ? HD : HD / 32 * 34;                // raw bytes of a cell
-    static constexpr int kScale = KV8 ? HD / 64 * 2 : 0;                 // raw bytes of a cell's KV8 scales
-    static constexpr int kRawTensor = kTile * kCell + kTile * (KV8 ? 8 : 0);  // one tensor's raw tile (scales in 8-byte slots)
-    static constexpr int q_hi = 0;
-    static constexpr int q_lo = q_hi + kMaxM * kRow;
-    static constexpr int op = q_lo + kMaxM * kRow;                      // K codes as FP16 [64][HD], or V hi | V lo [64][HD] each
-    static constexpr int raw = op + 2 * kTile * kRow;                   // [2 stages][K raw | V raw]
-    static constexpr int ranges = raw + 2 * 2 * kRawTensor;             // int32 lo[kMaxM], hi[kMaxM]
-    static constexpr int total = ranges + 2 * kMaxM * 4;
-};
 
 // ---- the attention kernel -------------------------------------------------------------------------------------------
 template <int HD, bool KV8>
 __global__ void __launch_bounds__(kThreads, 1) attend_kernel(const attend_params p) {
-    using L = smem_layout<HD, KV8>;
-    constexpr int NB = HD / 32;      // 32-dim blocks
-    constexpr int NT = HD / 16;      // 8-dim output tiles of this warp's half of the columns
-    constexpr int kHalfChunks = HD / 16;  // 16-byte chunks (8 FP16 values) in half a row
-    constexpr int kRow = L::kRow;
-    extern __shared__ __align__(128) uint8_t smem[];
-    uint8_t * q_hi = smem + L::q_hi;
-    uint8_t * q_lo = smem + L::q_lo;
-    uint8_t * op = smem + L::op;
+    using L = tc_layout<HD>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t * smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t * a_q = smem + L::a_q;
+    uint8_t * k_hi = smem + L::k_hi;
+    uint8_t * k_lo = smem + L::k_lo;
+    uint8_t * v_hi = smem + L::v_hi;
+    uint8_t * v_lo = smem + L::v_lo;
+    uint8_t * p_op = smem + L::p_op;
+    uint8_t * p_alt = smem + L::p_alt;
     int32_t * row_lo = reinterpret_cast<int32_t *>(smem + L::ranges);
     int32_t * row_hi = row_lo + kMaxM;
+    float * half_max = reinterpret_cast<float *>(smem + L::half_max);
+    uint64_t * bar_s = reinterpret_cast<uint64_t *>(smem + L::bars);
+    uint64_t * bar_o = bar_s + 1;
+    uint32_t * tmem_slot = reinterpret_cast<uint32_t *>(smem + L::misc);
 
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-    const int g = lane >> 2, t4 = lane & 3;
-    // this warp's row tile and its steps of the CTA tile: one row tile -> a step each, two -> two each, more -> all four
-    const int dh = wid & 1, pair = wid >> 1;  // which half of the output columns; which of the four warp pairs
-    const int mt = p.parts == 4 ? 0 : p.parts == 2 ? (pair & 1) : pair;
-    const int part = p.parts == 4 ? pair : p.parts == 2 ? (pair >> 1) : 0;
-    const int n_steps = 4 / p.parts, step0 = part * n_steps;
-    const bool mma_warp = mt < p.m_tiles;
-    const int r0 = 16 * mt + g, r1 = r0 + 8;  // the two query rows this lane's accumulators belong to
+    // widening: a thread's item is (cell, 64-dim block); consecutive lanes take consecutive cells, so that the eight
+    // lanes of a 16-byte store phase fall on eight different chunks of the swizzle
+    constexpr int kPairs = HD / 64;
+    const bool has_item = tid < kTile * kPairs;
+    const int cell = tid & (kTile - 1), pr = tid >> 6;
+    // softmax: warps w and w + 4 share tensor-memory quarter w & 3 (lanes 32 (w & 3) ..); a lane pair is one query row
+    // (even lane: the hi accumulator row, odd lane: the lo row); this thread owns 16 of the tile's 64 cells of its row
+    const int quarter = wid & 3, col_half = wid >> 2, part = lane & 1;
+    const int row = 16 * quarter + (lane >> 1);
+    const int col0 = 32 * col_half + 16 * part;  // first cell (of the tile) this thread owns
+    const uint32_t lane_base = uint32_t(32 * quarter) << 16;
 
+    if (tid == 0) {
+        mbar_init(bar_s, 1);
+        mbar_init(bar_o, 1);
+        mbar_init_fence();
+    }
+    if (wid == 0) tmem_alloc(tmem_slot, L::kTmemCols);
+    // the alternate P operand's even rows stay zero for the whole kernel
+    for (int i = tid; i < 64 * 8; i += kThreads) *reinterpret_cast<uint4 *>(p_alt + op_at(2 * (i >> 3), i & 7)) = make_uint4(0, 0, 0, 0);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem_s = tmem, tmem_o = tmem + 64;  // columns 0 .. 63: scores; 64 ..: outputs
+    constexpr uint32_t kIdescS = umma_idesc(kTile, false), kIdescO = umma_idesc(HD, true);
+
+    uint32_t it = 0;  // tiles this CTA has issued: phase counter of both barriers
     const int total_units = p.n_kv * p.n_units;
     for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
         const int head = unit / p.n_units, u = unit - head * p.n_units;
@@ -245,13 +343,13 @@ __global__ void __launch_bounds__(kThreads, 1) attend_kernel(const attend_params
         const int n_tiles = int((c_end - c_begin + kTile - 1) / kTile);
 
         __syncthreads();  // the previous unit's readers of q and the ranges are done
-        // ---- the group's query rows: F32 -> hi + lo FP16 (rows past m are zero); each row's cell range ----
+        // ---- the group's query rows: F32 -> hi (row 2 r) + lo (row 2 r + 1) FP16, rows past m zero ----
         for (int i = tid; i < kMaxM * (HD / 8); i += kThreads) {
-            const int row = i / (HD / 8), chunk = i - row * (HD / 8);
+            const int r = i / (HD / 8), chunk = i - r * (HD / 8);
             uint4 hi4 = make_uint4(0, 0, 0, 0), lo4 = hi4;
-            if (row < p.m) {
-                const int t = row / p.n_rep, r = row - t * p.n_rep;
-                const float4 * src = reinterpret_cast<const float4 *>(p.q + (int64_t(t) * p.n_q + head * p.n_rep + r) * HD) + 2 * chunk;
+            if (r < p.m) {
+                const int t = r / p.n_rep, rr = r - t * p.n_rep;
+                const float4 * src = reinterpret_cast<const float4 *>(p.q + (int64_t(t) * p.n_q + head * p.n_rep + rr) * HD) + 2 * chunk;
                 const float4 a = __ldg(src), b = __ldg(src + 1);
                 const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
                 uint32_t h[4], l[4];
@@ -264,274 +362,202 @@ __global__ void __launch_bounds__(kThreads, 1) attend_kernel(const attend_params
                 }
                 hi4 = make_uint4(h[0], h[1], h[2], h[3]), lo4 = make_uint4(l[0], l[1], l[2], l[3]);
             }
-            *reinterpret_cast<uint4 *>(q_hi + swz<kRow>(row, chunk)) = hi4;
-            *reinterpret_cast<uint4 *>(q_lo + swz<kRow>(row, chunk)) = lo4;
+            uint8_t * blk = a_q + uint32_t(chunk >> 3) * L::kQBlock;
+            *reinterpret_cast<uint4 *>(blk + op_at(2 * r, chunk & 7)) = hi4;
+            *reinterpret_cast<uint4 *>(blk + op_at(2 * r + 1, chunk & 7)) = lo4;
         }
-        for (int row = tid; row < kMaxM; row += kThreads) {
+        for (int r = tid; r < kMaxM; r += kThreads) {
             int64_t lo = 0, hi = 0;  // rows past m: an empty range, so every cell is masked
-            if (row < p.m) {
-                const int t = row / p.n_rep;
+            if (r < p.m) {
+                const int t = r / p.n_rep;
                 lo = p.first_cell != nullptr ? int64_t(__ldg(p.first_cell + t)) : p.range_begin;
                 hi = p.n_cells != nullptr ? lo + int64_t(__ldg(p.n_cells + t)) : p.range_end;
                 if (lo < 0 || hi > p.cache_slots || hi < lo) {
                     if (p.err != nullptr) atomicOr(p.err, FNB_ERR_SLOT);
                     lo = hi = 0;
                 }
-                lo = lo < p.range_begin ? p.range_begin : lo;
-                hi = hi > p.range_end ? p.range_end : hi;
+                lo = lo < c_begin ? c_begin : lo;
+                hi = hi > c_end ? c_end : hi;
             }
-            row_lo[row] = int32_t(lo), row_hi[row] = int32_t(hi);
+            row_lo[r] = int32_t(lo), row_hi[r] = int32_t(hi);
         }
 
-        // ---- raw tiles: cp.async of the tile's cells of this KV head into stage `st` ----
-        auto issue = [&](int tile, int st) {
-            uint8_t * base = smem + L::raw + st * 2 * L::kRawTensor;
-            const int64_t c0 = c_begin + int64_t(tile) * kTile;
-            // a thread copies one whole cell of one tensor (2 x 64 cells = the CTA's 128 threads): no index arithmetic
-            // per piece.  A 256-wide Q8_0 cell is 272 bytes = 17 x 16; a 128-wide one 136 = 17 x 8, only 8-byte aligned.
-            constexpr int kPiece = L::kCell % 16 == 0 ? 16 : 8;
-            constexpr int kChunks = L::kCell / kPiece;
-            static_assert(4 * kTile == kThreads, "two threads a (tensor, cell)");
-            {
-                const int item = tid >> 1, second = tid & 1;
-                const int tensor = item / kTile, cell = item - tensor * kTile;
-                const int64_t c = c0 + cell;
-                const bool valid = c < c_end;
-                const uint8_t * src = (tensor == 0 ? p.k_cache : p.v_cache) + ((valid ? c : c_begin) * p.n_kv + head) * L::kCell;
-                uint8_t * dst = base + tensor * L::kRawTensor + cell * L::kCell;
-                constexpr int kFirst = (kChunks + 1) / 2;  // pieces the first thread of the pair copies
-#pragma unroll
-                for (int j = 0; j < kFirst; ++j) {
-                    const int ch = second ? kFirst + j : j;
-                    if (ch < kChunks) {
-                        if (kPiece == 16) {
-                            cp_async16(dst + kPiece * ch, src + kPiece * ch, valid);
-                        } else {
-                            cp_async8(dst + kPiece * ch, src + kPiece * ch, valid);
-                        }
-                    }
-                }
-            }
-            if (KV8) {
-                for (int i = tid; i < 2 * kTile; i += kThreads) {
-                    const int tensor = i / kTile, cell = i - tensor * kTile;
-                    const int64_t c = c0 + cell;
-                    const bool valid = c < c_end;
-                    const uint16_t * src = (tensor == 0 ? p.k_scale : p.v_scale) + ((valid ? c : c_begin) * p.n_kv + head) * (HD / 64);
-                    uint8_t * dst = base + tensor * L::kRawTensor + kTile * L::kCell + cell * 8;
-                    if (HD == 256) {
-                        cp_async8(dst, src, valid);
-                    } else {  // two scales a cell: 4 bytes, plain loads
-                        *reinterpret_cast<uint32_t *>(dst) = valid ? __ldg(reinterpret_cast<const uint32_t *>(src)) : 0u;
-                    }
-                }
-            }
-            cp_async_commit();
+        // this thread's raw items of a tile
+        raw_item<KV8> rk, rv;
+        const auto fetch = [&](raw_item<KV8> & r, const uint8_t * cache, const uint16_t * scales, int tile) {
+            if (!has_item) return;
+            const int64_t c = c_begin + int64_t(tile) * kTile + cell;
+            const bool valid = c < c_end;
+            load_item<HD, KV8>(r, cache, scales, (valid ? c : c_begin) * p.n_kv + head, pr, valid);
         };
+        fetch(rk, p.k_cache, p.k_scale, 0);
+        fetch(rv, p.v_cache, p.v_scale, 0);
 
-        // running state of this lane's two rows
-        float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
-        float o[NT][4];
-#pragma unroll
-        for (int d = 0; d < NT; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.0f;
+        // this thread's view of its row: the reference point (the same in the row's four threads) and the sum over
+        // this thread's cells
+        float m_ref = -INFINITY, l_run = 0.0f;
 
-        issue(0, 0);
-        for (int tile = 0; tile < n_tiles; ++tile) {
-            const int st = tile & 1;
-            if (tile + 1 < n_tiles) {
-                issue(tile + 1, st ^ 1);
-                cp_async_wait<1>();
-            } else {
-                cp_async_wait<0>();
-            }
-            __syncthreads();  // the raw tile has landed for every thread; the previous tile's operand readers are done
-            const uint8_t * raw_k = smem + L::raw + st * 2 * L::kRawTensor;
-            const uint8_t * raw_v = raw_k + L::kRawTensor;
-            const int64_t tile_c0 = c_begin + int64_t(tile) * kTile;
-
-            // ---- K: the codes as FP16 integers, [cell][dim] ----
-            if (!KV8) {
-                widen_q8_0_tile<false, kRow>(raw_k, L::kCell, NB / 2, op, nullptr, tid);
-            } else {
-                for (int i = tid; i < kTile * (HD / 8); i += kThreads) {
-                    const int cell = i / (HD / 8), ch = i - cell * (HD / 8);
-                    const uint2 w = *reinterpret_cast<const uint2 *>(raw_k + cell * L::kCell + 8 * ch);
-                    __half2 a, b, c, d;
-                    codes_to_h2(w.x, a, b);
-                    codes_to_h2(w.y, c, d);
-                    *reinterpret_cast<uint4 *>(op + swz<kRow>(cell, ch)) = make_uint4(h2_bits(a), h2_bits(b), h2_bits(c), h2_bits(d));
-                }
-            }
+        for (int tile = 0; tile < n_tiles; ++tile, ++it) {
+            // ---- A: K of this tile into its operand tiles (the previous tile's score MMAs are done: every thread
+            //      passed the barrier behind the softmax that waited for them); the next tile's K into registers ----
+            if (has_item) widen_item<KV8>(rk, cell, pr, k_hi, k_lo);
+            if (tile + 1 < n_tiles) fetch(rk, p.k_cache, p.k_scale, tile + 1);
+            fence_proxy_async();
             __syncthreads();
-
-            // ---- scores, softmax and the P operands, step by step ----
-            uint32_t p_hi[4][4], p_lo[4][4];  // [step][A fragment]
-            float alpha[4][2];
-            const int lo0 = row_lo[r0], hi0 = row_hi[r0], lo1 = row_lo[r1], hi1 = row_hi[r1];
+            // ---- B: scores on the tensor core, S = [q_hi; q_lo] . (K_lo + K_hi)^T: the small products first, so
+            //      that only the sixteen K_hi steps round a large accumulator; meanwhile V of this tile ----
+            if (tid == 0) {
+                tc_fence_after();
+                const uint32_t qa = smem_u32(a_q), kh = smem_u32(k_hi), kl = smem_u32(k_lo);
 #pragma unroll
-            for (int st4 = 0; st4 < 4; ++st4) {
-                if (st4 >= n_steps) break;
-                const int cell0 = (step0 + st4) * kStep;  // first cell of this step within the tile
-                float s[2][4];
+                for (int kb = 0; kb < L::kBlocks; ++kb) {
 #pragma unroll
-                for (int n = 0; n < 2; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
-                if (mma_warp) {
-#pragma unroll
-                    for (int b = 0; b < NB; ++b) {
-                        float blk[2][4];
-#pragma unroll
-                        for (int n = 0; n < 2; ++n) blk[n][0] = blk[n][1] = blk[n][2] = blk[n][3] = 0.0f;
-#pragma unroll
-                        for (int kk = 0; kk < 2; ++kk) {
-                            const int ks = 2 * b + kk;
-                            uint32_t ah[4], al[4], kb[4];
-                            const int arow = 16 * mt + (lane & 15), achunk = 2 * ks + (lane >> 4);
-                            ldsm4(ah, s_addr(q_hi + swz<kRow>(arow, achunk)));
-                            ldsm4(al, s_addr(q_lo + swz<kRow>(arow, achunk)));
-                            const int krow = cell0 + (lane & 7) + 8 * (lane >> 4), kchunk = 2 * ks + ((lane >> 3) & 1);
-                            ldsm4(kb, s_addr(op + swz<kRow>(krow, kchunk)));
-                            mma16816(blk[0], ah, kb[0], kb[1]);
-                            mma16816(blk[0], al, kb[0], kb[1]);
-                            mma16816(blk[1], ah, kb[2], kb[3]);
-                            mma16816(blk[1], al, kb[2], kb[3]);
-                        }
-                        // the block's scale of this lane's two cells of each 8-cell tile
-#pragma unroll
-                        for (int n = 0; n < 2; ++n) {
-                            const int c = cell0 + 8 * n + 2 * t4;
-                            float d0, d1;
-                            if (KV8) {
-                                const uint16_t * sc = reinterpret_cast<const uint16_t *>(raw_k + kTile * L::kCell);
-                                d0 = f16_bits_to_f32(sc[4 * c + b / 2]), d1 = f16_bits_to_f32(sc[4 * (c + 1) + b / 2]);
-                            } else {
-                                d0 = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(raw_k + c * L::kCell + 34 * b));
-                                d1 = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(raw_k + (c + 1) * L::kCell + 34 * b));
-                            }
-                            s[n][0] = fmaf(blk[n][0], d0, s[n][0]), s[n][1] = fmaf(blk[n][1], d1, s[n][1]);
-                            s[n][2] = fmaf(blk[n][2], d0, s[n][2]), s[n][3] = fmaf(blk[n][3], d1, s[n][3]);
-                        }
+                    for (int ks = 0; ks < 4; ++ks) {
+                        umma_f16(tmem_s, umma_desc(qa + kb * L::kQBlock + 32 * ks, 16, 1024),
+                                 umma_desc(kl + kb * L::kCBlock + 32 * ks, 16, 1024), kIdescS, (kb | ks) != 0);
                     }
                 }
-                // mask, running maximum, probabilities (rows r0 and r1; log2 units)
-                float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-                for (int n = 0; n < 2; ++n) {
+                for (int kb = 0; kb < L::kBlocks; ++kb) {
 #pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        const int64_t c = tile_c0 + cell0 + 8 * n + 2 * t4 + j;
-                        s[n][j] = c >= lo0 && c < hi0 ? s[n][j] * p.scale_log2 : -INFINITY;
-                        s[n][2 + j] = c >= lo1 && c < hi1 ? s[n][2 + j] * p.scale_log2 : -INFINITY;
-                        mx0 = fmaxf(mx0, s[n][j]), mx1 = fmaxf(mx1, s[n][2 + j]);
+                    for (int ks = 0; ks < 4; ++ks) {
+                        umma_f16(tmem_s, umma_desc(qa + kb * L::kQBlock + 32 * ks, 16, 1024),
+                                 umma_desc(kh + kb * L::kCBlock + 32 * ks, 16, 1024), kIdescS, 1);
                     }
                 }
-                mx0 = fmaxf(mx0, __shfl_xor_sync(kFull, mx0, 1)), mx0 = fmaxf(mx0, __shfl_xor_sync(kFull, mx0, 2));
-                mx1 = fmaxf(mx1, __shfl_xor_sync(kFull, mx1, 1)), mx1 = fmaxf(mx1, __shfl_xor_sync(kFull, mx1, 2));
-                const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
-                // a row with no live cell so far keeps reference 0 (exp2 of -inf is 0; -inf minus -inf is never formed)
-                const float ref0 = mn0 == -INFINITY ? 0.0f : mn0, ref1 = mn1 == -INFINITY ? 0.0f : mn1;
-                alpha[st4][0] = fast_exp2(m_run[0] - ref0), alpha[st4][1] = fast_exp2(m_run[1] - ref1);
-                m_run[0] = mn0, m_run[1] = mn1;
-                float pr[2][4];
+                umma_commit(bar_s);
+            }
+            if (it > 0) {  // the previous output MMAs read V and P and wrote O
+                mbar_wait(bar_o, (it - 1) & 1, p.err);
+                tc_fence_after();
+            }
+            if (has_item) widen_item<KV8>(rv, cell, pr, v_hi, v_lo);
+            if (tile + 1 < n_tiles) fetch(rv, p.v_cache, p.v_scale, tile + 1);
+            // ---- C: softmax of the tile: every thread 16 cells of one query row ----
+            mbar_wait(bar_s, it & 1, p.err);
+            tc_fence_after();
+            float s[16];
+            {
+                float mine[32];
+                tmem_ld32(tmem_s + lane_base + 32 * col_half, mine);
+                // the pair's other lane holds the row's other part: keep my 16 cells, hand over the other 16
 #pragma unroll
-                for (int n = 0; n < 2; ++n) {
-                    pr[n][0] = fast_exp2(s[n][0] - ref0), pr[n][1] = fast_exp2(s[n][1] - ref0);
-                    pr[n][2] = fast_exp2(s[n][2] - ref1), pr[n][3] = fast_exp2(s[n][3] - ref1);
-                }
-                l_run[0] = l_run[0] * alpha[st4][0] + ((pr[0][0] + pr[0][1]) + (pr[1][0] + pr[1][1]));
-                l_run[1] = l_run[1] * alpha[st4][1] + ((pr[0][2] + pr[0][3]) + (pr[1][2] + pr[1][3]));
-                // P as the A fragment of the step: hi + lo of p x 2^12
-#pragma unroll
-                for (int f = 0; f < 4; ++f) {
-                    const int n = f >> 1, jb = (f & 1) * 2;  // a0: (g, tile 0), a1: (g + 8, tile 0), a2: (g, tile 1), a3: (g + 8, tile 1)
-                    const float x = pr[n][jb] * kPScale, y = pr[n][jb + 1] * kPScale;
-                    const __half2 hv = __floats2half2_rn(x, y);
-                    const float2 back = __half22float2(hv);
-                    p_hi[st4][f] = h2_bits(hv);
-                    p_lo[st4][f] = h2_bits(__floats2half2_rn(x - back.x, y - back.y));
+                for (int j = 0; j < 16; ++j) {
+                    const float keep = part ? mine[16 + j] : mine[j], give = part ? mine[j] : mine[16 + j];
+                    s[j] = keep + __shfl_xor_sync(kFull, give, 1);
                 }
             }
-            __syncthreads();  // every warp is done with the K operand tile
-
-            // ---- V: hi = rn(d x code), lo = fma(d, code, -hi) exactly, [cell][dim] each ----
-            uint8_t * v_hi = op;
-            uint8_t * v_lo = op + kTile * kRow;
-            if (!KV8) {
-                widen_q8_0_tile<true, kRow>(raw_v, L::kCell, NB / 2, v_hi, v_lo, tid);
-            } else {
-                const uint16_t * sc = reinterpret_cast<const uint16_t *>(raw_v + kTile * L::kCell);
-                for (int i = tid; i < kTile * (HD / 8); i += kThreads) {
-                    const int cell = i / (HD / 8), ch = i - cell * (HD / 8);
-                    const uint2 w = *reinterpret_cast<const uint2 *>(raw_v + cell * L::kCell + 8 * ch);
-                    const __half2 d2 = __half2half2(__ushort_as_half(sc[4 * cell + ch / 8]));
-                    __half2 c[4], h[4], l[4];
-                    codes_to_h2(w.x, c[0], c[1]);
-                    codes_to_h2(w.y, c[2], c[3]);
+            const int c0 = int(c_begin + int64_t(tile) * kTile) + col0;
+            const int lo = row_lo[row] - c0, hi = row_hi[row] - c0;  // this thread's live cells: lo <= j < hi
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                s[j] = j >= lo && j < hi ? s[j] * p.scale_log2 : -INFINITY;
+                mx = fmaxf(mx, s[j]);
+            }
+            mx = fmaxf(mx, __shfl_xor_sync(kFull, mx, 1));
+            if (part == 0) half_max[col_half * kMaxM + row] = mx;
+            named_barrier_id(2 + quarter, 64);  // warps quarter and quarter + 4
+            mx = fmaxf(mx, half_max[(col_half ^ 1) * kMaxM + row]);
+            // lazy reference point: it moves only when the row's maximum has outgrown it by more than 2^kLazy
+            float a_row = 1.0f;
+            if (mx > m_ref + kLazy || (m_ref == -INFINITY && mx > -INFINITY)) {
+                if (m_ref != -INFINITY) a_row = fast_exp2(m_ref - mx);
+                m_ref = mx;
+            }
+            if (__any_sync(kFull, a_row != 1.0f)) {  // this warp's half of the output columns of its lanes' rows
+#pragma unroll 1
+                for (int cb = 0; cb < HD / 64; ++cb) {
+                    float o[32];
+                    const uint32_t at = tmem_o + lane_base + uint32_t(HD / 2 * col_half + 32 * cb);
+                    tmem_ld32(at, o);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) o[j] *= a_row;
+                    tmem_st32(at, o);
+                }
+                tmem_wait_st();
+            }
+            {
+                const float ref = m_ref == -INFINITY ? 0.0f : m_ref;
+                float sum = 0.0f;
+#pragma unroll
+                for (int cb = 0; cb < 2; ++cb) {
+                    uint32_t hi4[4], lo4[4];
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        h[e] = __hmul2(d2, c[e]);
-                        l[e] = __hfma2(d2, c[e], __hneg2(h[e]));
+                        const float p0 = fast_exp2(s[8 * cb + 2 * e] - ref), p1 = fast_exp2(s[8 * cb + 2 * e + 1] - ref);
+                        sum += p0 + p1;
+                        const float x0 = p0 * kPScale, x1 = p1 * kPScale;
+                        const __half2 hv = __floats2half2_rn(x0, x1);
+                        const float2 back = __half22float2(hv);
+                        hi4[e] = h2_bits(hv);
+                        lo4[e] = h2_bits(__floats2half2_rn(x0 - back.x, x1 - back.y));
                     }
-                    *reinterpret_cast<uint4 *>(v_hi + swz<kRow>(cell, ch)) = make_uint4(h2_bits(h[0]), h2_bits(h[1]), h2_bits(h[2]), h2_bits(h[3]));
-                    *reinterpret_cast<uint4 *>(v_lo + swz<kRow>(cell, ch)) = make_uint4(h2_bits(l[0]), h2_bits(l[1]), h2_bits(l[2]), h2_bits(l[3]));
+                    const int chunk = col0 / 8 + cb;
+                    const uint4 h = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
+                    *reinterpret_cast<uint4 *>(p_op + op_at(2 * row, chunk)) = h;
+                    *reinterpret_cast<uint4 *>(p_op + op_at(2 * row + 1, chunk)) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
+                    *reinterpret_cast<uint4 *>(p_alt + op_at(2 * row + 1, chunk)) = h;
                 }
+                l_run = l_run * a_row + sum;
             }
+            fence_proxy_async();
+            tc_fence_before();
             __syncthreads();
-
-            // ---- outputs: o = o alpha + (p_hi + p_lo) (v_hi + v_lo) without the lo x lo term ----
-            if (mma_warp) {
+            // ---- D: outputs on the tensor core.  Row 2 r: p_hi . V_hi only (four roundings of the large accumulator
+            //      per tile); row 2 r + 1: p_lo . V_hi + p_hi . V_lo (small) ----
+            if (tid == 0) {
+                tc_fence_after();
+                const uint32_t pa = smem_u32(p_op), pb = smem_u32(p_alt), vh = smem_u32(v_hi), vl = smem_u32(v_lo);
 #pragma unroll
-                for (int st4 = 0; st4 < 4; ++st4) {
-                    if (st4 >= n_steps) break;
-                    const int cell0 = (step0 + st4) * kStep;
-                    // the maximum seldom moves once a few tiles are in: skip the rescaling when no row of the warp needs it
-                    if (__any_sync(kFull, alpha[st4][0] != 1.0f || alpha[st4][1] != 1.0f)) {
-#pragma unroll
-                        for (int d = 0; d < NT; ++d) {
-                            o[d][0] *= alpha[st4][0], o[d][1] *= alpha[st4][0];
-                            o[d][2] *= alpha[st4][1], o[d][3] *= alpha[st4][1];
-                        }
-                    }
-#pragma unroll
-                    for (int dp = 0; dp < NT / 2; ++dp) {
-                        uint32_t bh[4], bl[4];
-                        const int vrow = cell0 + (lane & 7) + 8 * ((lane >> 3) & 1), vchunk = dh * kHalfChunks + 2 * dp + (lane >> 4);
-                        ldsm4_t(bh, s_addr(v_hi + swz<kRow>(vrow, vchunk)));
-                        ldsm4_t(bl, s_addr(v_lo + swz<kRow>(vrow, vchunk)));
-                        mma16816(o[2 * dp], p_hi[st4], bh[0], bh[1]);
-                        mma16816(o[2 * dp], p_lo[st4], bh[0], bh[1]);
-                        mma16816(o[2 * dp], p_hi[st4], bl[0], bl[1]);
-                        mma16816(o[2 * dp + 1], p_hi[st4], bh[2], bh[3]);
-                        mma16816(o[2 * dp + 1], p_lo[st4], bh[2], bh[3]);
-                        mma16816(o[2 * dp + 1], p_hi[st4], bl[2], bl[3]);
-                    }
+                for (int ks = 0; ks < 4; ++ks) {  // 16 cells a step: two groups of eight 128-byte rows
+                    umma_f16(tmem_o, umma_desc(pa + 32 * ks, 16, 1024), umma_desc(vh + 2048 * ks, L::kCBlock, 1024), kIdescO,
+                             (tile | ks) != 0);
+                    umma_f16(tmem_o, umma_desc(pb + 32 * ks, 16, 1024), umma_desc(vl + 2048 * ks, L::kCBlock, 1024), kIdescO, 1);
                 }
+                umma_commit(bar_o);
             }
         }
 
-        // ---- the unit's partial result of this warp: (max, sum, output / 2^12) of its rows ----
-        if (mma_warp) {
-            float l0 = l_run[0], l1 = l_run[1];
-            l0 += __shfl_xor_sync(kFull, l0, 1), l0 += __shfl_xor_sync(kFull, l0, 2);
-            l1 += __shfl_xor_sync(kFull, l1, 1), l1 += __shfl_xor_sync(kFull, l1, 2);
-            const int64_t slot = (int64_t(head) * p.n_units + u) * p.parts + part;
+        // ---- the unit's partial result: (reference point, sum, (O[2 r] + O[2 r + 1]) / 2^12) of its rows ----
+        mbar_wait(bar_o, (it - 1) & 1, p.err);
+        tc_fence_after();
+        {
+            const int64_t slot = int64_t(head) * p.n_units + u;
             float * ml = p.ws_ml + slot * p.m * 2;
             float * acc = p.ws_acc + slot * p.m * HD;
-            const int col0 = dh * (HD / 2);  // this warp's half of the output columns; the pair's first warp writes (max, sum)
-            if (r0 < p.m) {
-                if (t4 == 0 && dh == 0) ml[2 * r0] = m_run[0], ml[2 * r0 + 1] = l0;
+            // the row's sum: its four threads' shares (two lanes here, two in the partner warp)
+            float l_pair = l_run + __shfl_xor_sync(kFull, l_run, 1);
+            if (part == 0) half_max[col_half * kMaxM + row] = l_pair;
+            named_barrier_id(2 + quarter, 64);
+            if (col_half == 0 && part == 0 && row < p.m) {
+                ml[2 * row] = m_ref, ml[2 * row + 1] = l_pair + half_max[kMaxM + row];
+            }
+#pragma unroll 1
+            for (int cb = 0; cb < HD / 64; ++cb) {
+                float o[32];
+                const int col = HD / 2 * col_half + 32 * cb;
+                tmem_ld32(tmem_o + lane_base + uint32_t(col), o);
 #pragma unroll
-                for (int d = 0; d < NT; ++d) {
-                    *reinterpret_cast<float2 *>(acc + int64_t(r0) * HD + col0 + 8 * d + 2 * t4) = make_float2(o[d][0] * kPUnscale, o[d][1] * kPUnscale);
+                for (int j = 0; j < 32; ++j) o[j] += __shfl_xor_sync(kFull, o[j], 1);
+                // the pair's even lane writes the first 16 columns, the odd lane the other 16
+                if (row < p.m) {
+                    float4 * dst = reinterpret_cast<float4 *>(acc + int64_t(row) * HD + col + 16 * part);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int b = 4 * j;
+                        dst[j] = part ? make_float4(o[16 + b] * kPUnscale, o[17 + b] * kPUnscale, o[18 + b] * kPUnscale, o[19 + b] * kPUnscale)
+                                      : make_float4(o[b] * kPUnscale, o[b + 1] * kPUnscale, o[b + 2] * kPUnscale, o[b + 3] * kPUnscale);
+                    }
                 }
             }
-            if (r1 < p.m) {
-                if (t4 == 0 && dh == 0) ml[2 * r1] = m_run[1], ml[2 * r1 + 1] = l1;
-#pragma unroll
-                for (int d = 0; d < NT; ++d) {
-                    *reinterpret_cast<float2 *>(acc + int64_t(r1) * HD + col0 + 8 * d + 2 * t4) = make_float2(o[d][2] * kPUnscale, o[d][3] * kPUnscale);
-                }
-            }
+            tc_fence_before();
         }
+    }
+    __syncthreads();
+    if (wid == 0) {
+        tc_fence_after();
+        tmem_dealloc(tmem, L::kTmemCols);
     }
 }
 
@@ -605,7 +631,7 @@ bool configure() {
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
     if (!done[dev].load(std::memory_order_acquire)) {
         if (cudaFuncSetAttribute(attend_kernel<HD, KV8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 smem_layout<HD, KV8>::total) != cudaSuccess) {
+                                 tc_layout<HD>::total) != cudaSuccess) {
             return false;
         }
         done[dev].store(true, std::memory_order_release);
@@ -617,7 +643,7 @@ template <int HD, bool KV8>
 int32_t launch_hd(const attend_params & p, cudaStream_t s) {
     if (!configure<HD, KV8>()) return FNB_LAUNCH_FAILED;
     const int units = p.n_kv * p.n_units;
-    attend_kernel<HD, KV8><<<units < kSmCount ? units : kSmCount, kThreads, smem_layout<HD, KV8>::total, s>>>(p);
+    attend_kernel<HD, KV8><<<units < kSmCount ? units : kSmCount, kThreads, tc_layout<HD>::total, s>>>(p);
     if (cudaPeekAtLastError() != cudaSuccess) return FNB_LAUNCH_FAILED;
     attend_fold_kernel<HD><<<p.rows * p.n_q, HD * kFoldLanes, 0, s>>>(p);
     return launch_status();
@@ -650,7 +676,7 @@ int32_t attend_launch(const fnb_attend_args * a, void * ws, size_t ws_bytes, cud
     if (!ok_opt(a->first_cell, 4) || !ok_opt(a->n_cells, 4) || !ok_opt(a->err, 4)) return FNB_REJECTED;
     if (!(a->scale > 0.0f) || !(a->scale < INFINITY)) return FNB_REJECTED;
     const attend_plan plan = make_plan(a->rows, a->n_q_heads, a->n_kv_heads, a->range_end - a->range_begin);
-    if (plan.n_units * plan.parts > kFoldMaxSlots) return FNB_REJECTED;  // cannot happen with the plan's two units an SM
+    if (plan.n_units * plan.parts > kFoldMaxSlots) return FNB_REJECTED;  // cannot happen with the plan's one unit an SM
     if (!ok_ptr(ws, 16) || ws_bytes < plan_bytes(plan, a->head_dim)) return FNB_REJECTED;
 
     attend_params p;
@@ -662,7 +688,7 @@ int32_t attend_launch(const fnb_attend_args * a, void * ws, size_t ws_bytes, cud
     p.ws_acc = p.ws_ml + plan.slots * plan.m * 2;
     p.cache_slots = a->cache_slots, p.range_begin = a->range_begin, p.range_end = a->range_end, p.unit_cells = plan.unit_cells;
     p.rows = a->rows, p.n_q = a->n_q_heads, p.n_kv = a->n_kv_heads, p.n_rep = a->n_q_heads / a->n_kv_heads;
-    p.m = plan.m, p.m_tiles = plan.m_tiles, p.parts = plan.parts, p.n_units = plan.n_units;
+    p.m = plan.m, p.parts = plan.parts, p.n_units = plan.n_units;
     p.scale_log2 = a->scale * kLog2e;
     if (a->head_dim == 256) return kv8 ? launch_hd<256, true>(p, s) : launch_hd<256, false>(p, s);
     return kv8 ? launch_hd<128, true>(p, s) : launch_hd<128, false>(p, s);

@@ -93,6 +93,23 @@ def test_attend_many_units_no_gate_whole_range(dev, oracle):
     check(out.cpu().numpy(), ref, "40000 cells, whole range")
 
 
+@pytest.mark.parametrize("fmt,rows,q_scale", [("q8_0", 1, 1.0), ("q8_0", 5, 3.0), ("kv8", 3, 2.0)])
+def test_attend_full_depth_cache(dev, oracle, fmt, rows, q_scale):
+    """The bench's depth: 196 608 cells of 2 KV heads under 16 query heads, whole range: every work unit is at its
+    longest (the most accumulation steps between two partial results), flat and peaked scores."""
+    g = synth.rng(35 + rows)
+    cells, n_kv, hd, n_q = 196608, 2, 256, 16
+    planes, kf, vf = make_cache(oracle, g, cells, n_kv, hd, fmt)
+    q = synth.normal(g, (rows, n_q, hd), q_scale)
+    d = [None if p is None else to_dev(p, dev) for p in planes]
+    err = ops.new_err(dev)
+    out = ops.attend(to_dev(q, dev), d[0], d[1], k_scale=d[2], v_scale=d[3], range_begin=0, range_end=cells, err=err)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    ref = oracle.attend_f64(q, kf, vf, np.zeros(rows, np.int32), np.full(rows, cells, np.int32), hd ** -0.5)
+    check(out.cpu().numpy(), ref, "%s, 196608 cells, %d rows, q x %g" % (fmt, rows, q_scale))
+
+
 def test_attend_empty_rows_bad_ranges_and_rejections(dev, oracle):
     g = synth.rng(33)
     cells, n_kv, hd, rows, n_q = 512, 1, 256, 4, 4

@@ -62,7 +62,7 @@ def test_static_scratch_attention_equals_the_workspace_form_twice_in_a_row(dev):
 def test_static_scratch_attention_refuses_what_does_not_fit(dev, capfd):
     L = _lib.lib()
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
-    q, kc, vc = _case(dev, 43, 4, 64, 16, 40000)            # sixteen KV heads on a long range: well over 16 MiB of partials
+    q, kc, vc = _case(dev, 43, 4, 256, 16, 40000)           # 64 query rows a group, sixteen KV heads, a long range: over 16 MiB of partials
     out = torch.full_like(q, 7.0)
     a = _args(q, kc, vc, out, 0, kc.shape[0])
     assert int(L.fnb_attend_workspace_bytes(C.byref(a))) > 16 << 20
