@@ -54,7 +54,8 @@
 namespace fnb {
 namespace {
 
-constexpr int kThreads = 256;
+constexpr int kThreads = 512;  // sixteen worker warps: four per scheduler hide each other's latencies
+constexpr int kLaunchThreads = kThreads + 32;  // and a warp that only issues the MMAs (a thread that issues them waits on the tensor core's queue: as a worker it held up every barrier)
 constexpr int kTile = 64;   // cells per tile: the N of the score MMA, four K steps of the output MMA
 constexpr int kMaxM = 64;   // query rows of one KV head's group: rows x (n_q_heads / n_kv_heads)
 constexpr float kPScale = 4096.0f, kPUnscale = 1.0f / 4096.0f;
@@ -147,6 +148,14 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// the same with the A operand in tensor memory (one operand row per lane, two FP16 values per column)
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // the barrier gets one arrival when every MMA issued so far by this thread has completed
 __device__ __forceinline__ void umma_commit(uint64_t * bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -179,6 +188,18 @@ __device__ __forceinline__ void tmem_ld32(uint32_t addr, float (&v)[32]) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t addr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(addr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
 __device__ __forceinline__ void tmem_st32(uint32_t addr, const float (&v)[32]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
@@ -194,34 +215,53 @@ __device__ __forceinline__ void tmem_st32(uint32_t addr, const float (&v)[32]) {
           "r"(__float_as_uint(v[31]))
         : "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t addr, const float (&v)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(addr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+          "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+          "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+          "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+          "r"(__float_as_uint(v[15]))
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t addr, const float (&v)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"r"(addr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+                   "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+                   "r"(__float_as_uint(v[7]))
+                 : "memory");
+}
 // barrier among `threads` threads on hardware barrier `id` chosen at run time
 __device__ __forceinline__ void named_barrier_id(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// ---- shared memory --------------------------------------------------------------------------------------------------
-// Operand tiles: 64-dim (or, for P, 64-cell) blocks of [rows][128 bytes]; chunk c of row r sits at chunk c ^ (r & 7).
-// Stacked operands interleave the parts: row 2 r holds query row r's hi part, row 2 r + 1 its lo part, so the two
-// accumulator rows of a query row sit in adjacent lanes of one 32-lane quarter of tensor memory.
+// ---- shared and tensor memory ---------------------------------------------------------------------------------------
+// Cell operand tiles in shared memory: 64-dim blocks of [cell][128 bytes]; chunk c of cell r sits at chunk c ^ (r & 7).
+// The stacked operands (query rows, probabilities) live in TENSOR memory, one operand row per lane, two FP16 values per
+// 32-bit column: the tensor core then reads only the cell operand from shared memory (with the stacked operand there
+// too, its 4 KB per MMA made shared-memory bandwidth the bound).  Stacked rows interleave the parts: lane 2 r holds
+// query row r's hi part, lane 2 r + 1 its lo part, so a query row's two accumulator rows sit in adjacent lanes of one
+// 32-lane quarter.
 template <int HD>
 struct tc_layout {
     static constexpr int kBlocks = HD / 64;
-    static constexpr int kQBlock = 128 * 128;                 // a block of a stacked operand
     static constexpr int kCBlock = kTile * 128;               // a block of a cell operand
-    static constexpr int a_q = 0;                             // [kBlocks][128][128 B]: rows 2 r: q_hi, 2 r + 1: q_lo
-    static constexpr int k_hi = a_q + kBlocks * kQBlock;
+    static constexpr int k_hi = 0;
     static constexpr int k_lo = k_hi + kBlocks * kCBlock;
     static constexpr int v_hi = k_lo + kBlocks * kCBlock;
     static constexpr int v_lo = v_hi + kBlocks * kCBlock;
-    static constexpr int p_op = v_lo + kBlocks * kCBlock;     // [128][128 B]: rows 2 r: p_hi, 2 r + 1: p_lo
-    static constexpr int p_alt = p_op + kQBlock;              // [128][128 B]: rows 2 r: zeros, 2 r + 1: p_hi
-    static constexpr int ranges = p_alt + kQBlock;            // int32 lo[64], hi[64]
-    static constexpr int half_max = ranges + 2 * kMaxM * 4;   // float [2][64]: a row's maximum over each half of a tile
-    static constexpr int bars = half_max + 2 * kMaxM * 4;     // two mbarriers
+    static constexpr int ranges = v_lo + kBlocks * kCBlock;   // int32 lo[64], hi[64]
+    static constexpr int part_max = ranges + 2 * kMaxM * 4;   // float [4][64]: a row's maximum over each quarter of a tile
+    static constexpr int bars = part_max + 4 * kMaxM * 4;     // two mbarriers
     static constexpr int misc = bars + 16;                    // tensor-memory base
     static constexpr int total = misc + 16 + 1024;            // + slack to align the base to 1024 bytes
-    static constexpr uint32_t kTmemCols = HD == 256 ? 512 : 256;  // 64 score columns + HD output columns, a power of two
+    // tensor-memory columns: scores | outputs | stacked query rows | stacked probabilities | the alternate probabilities
+    static constexpr uint32_t t_s = 0, t_o = 64, t_q = t_o + HD, t_p = t_q + HD / 2, t_alt = t_p + 32;
+    static constexpr uint32_t kTmemCols = 512;
+    static_assert(t_alt + 32 <= kTmemCols, "tensor memory of one SM");
     static_assert(total <= 232448, "shared memory of one CTA");
 };
 __device__ __forceinline__ uint32_t op_at(int row, int chunk) { return uint32_t(row) * 128u + (uint32_t(chunk ^ (row & 7)) << 4); }
@@ -231,92 +271,97 @@ __device__ __forceinline__ uint32_t op_at(int row, int chunk) { return uint32_t(
 // their group's scale.  Cells past the end of the unit read as zeros.
 template <bool KV8>
 struct raw_item {
-    uint32_t w[KV8 ? 16 : 17];
+    uint32_t w[KV8 ? 8 : 9];
     uint32_t scale;  // KV8: the group's FP16 scale bits
 };
+// blk: the item's 32-dim block of the cell.  Q8_0: the block's 34 bytes lie in nine aligned words of its pair of blocks
+// (68 bytes = 17 words): words 0 .. 8 for the pair's first block (d in the low half of word 0, codes from its high
+// half on), words 8 .. 16 for the second (d in the high half of word 8, codes in words 9 .. 16).
 template <int HD, bool KV8>
 __device__ __forceinline__ void load_item(raw_item<KV8> & r, const uint8_t * cache, const uint16_t * scales, int64_t cell_head,
-                                          int pr, bool valid) {
+                                          int blk, bool valid) {
     if (KV8) {
-        const uint4 * src = reinterpret_cast<const uint4 *>(cache + cell_head * HD + 64 * pr);
+        const uint4 * src = reinterpret_cast<const uint4 *>(cache + cell_head * HD + 32 * blk);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < 2; ++j) {
             const uint4 v = valid ? __ldg(src + j) : make_uint4(0, 0, 0, 0);
             r.w[4 * j] = v.x, r.w[4 * j + 1] = v.y, r.w[4 * j + 2] = v.z, r.w[4 * j + 3] = v.w;
         }
-        r.scale = valid ? uint32_t(__ldg(scales + cell_head * (HD / 64) + pr)) : 0u;
+        r.scale = valid ? uint32_t(__ldg(scales + cell_head * (HD / 64) + (blk >> 1))) : 0u;
     } else {
-        const uint32_t * src = reinterpret_cast<const uint32_t *>(cache + cell_head * (HD / 32 * 34) + 68 * pr);
+        const uint32_t * src = reinterpret_cast<const uint32_t *>(cache + cell_head * (HD / 32 * 34) + 68 * (blk >> 1)) + 8 * (blk & 1);
 #pragma unroll
-        for (int j = 0; j < 17; ++j) r.w[j] = valid ? __ldg(src + j) : 0u;
+        for (int j = 0; j < 9; ++j) r.w[j] = valid ? __ldg(src + j) : 0u;
         r.scale = 0;
     }
 }
-// widen the item into block `pr` of the hi and lo operand tiles: value = d x code, hi = rn(value), lo = value - hi
-template <bool KV8>
-__device__ __forceinline__ void widen_item(const raw_item<KV8> & r, int cell, int pr, uint8_t * t_hi, uint8_t * t_lo) {
-    __half d_first, d_second;
-    if (KV8) {
-        d_first = d_second = __ushort_as_half(uint16_t(r.scale));
-    } else {
-        d_first = __ushort_as_half(uint16_t(r.w[0] & 0xffffu)), d_second = __ushort_as_half(uint16_t(r.w[8] >> 16));
-    }
+// widen the item into the hi and lo operand tiles: value = d x code, hi = rn(value), lo = value - hi.  SECOND: the
+// item is the second block of its pair (the same for every thread of a warp).
+template <bool KV8, bool SECOND>
+__device__ __forceinline__ void widen_half(const raw_item<KV8> & r, int cell, int blk, uint8_t * t_hi, uint8_t * t_lo) {
+    const __half d = __ushort_as_half(uint16_t(KV8 ? r.scale : SECOND ? r.w[0] >> 16 : r.w[0] & 0xffffu));
+    const __half2 d2 = __half2half2(d);
 #pragma unroll
-    for (int jj = 0; jj < 8; ++jj) {
+    for (int j = 0; j < 4; ++j) {
         uint32_t c0, c1;
         if (KV8) {
-            c0 = r.w[2 * jj], c1 = r.w[2 * jj + 1];
-        } else if (jj < 4) {
-            c0 = __funnelshift_r(r.w[2 * jj], r.w[2 * jj + 1], 16), c1 = __funnelshift_r(r.w[2 * jj + 1], r.w[2 * jj + 2], 16);
+            c0 = r.w[2 * j], c1 = r.w[2 * j + 1];
+        } else if (!SECOND) {
+            c0 = __funnelshift_r(r.w[2 * j], r.w[2 * j + 1], 16), c1 = __funnelshift_r(r.w[2 * j + 1], r.w[2 * j + 2], 16);
         } else {
-            c0 = r.w[2 * jj + 1], c1 = r.w[2 * jj + 2];
+            c0 = r.w[2 * j + 1], c1 = r.w[2 * j + 2];
         }
         __half2 c[4], h[4], l[4];
         codes_to_h2(c0, c[0], c[1]);
         codes_to_h2(c1, c[2], c[3]);
-        const __half2 d2 = __half2half2(jj < 4 ? d_first : d_second);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             h[e] = __hmul2(d2, c[e]);
             l[e] = __hfma2(d2, c[e], __hneg2(h[e]));
         }
-        const uint32_t at = uint32_t(pr) * (kTile * 128) + op_at(cell, jj);
+        const uint32_t at = uint32_t(blk >> 1) * (kTile * 128) + op_at(cell, 4 * (blk & 1) + j);
         *reinterpret_cast<uint4 *>(t_hi + at) = make_uint4(h2_bits(h[0]), h2_bits(h[1]), h2_bits(h[2]), h2_bits(h[3]));
         *reinterpret_cast<uint4 *>(t_lo + at) = make_uint4(h2_bits(l[0]), h2_bits(l[1]), h2_bits(l[2]), h2_bits(l[3]));
+    }
+}
+template <bool KV8>
+__device__ __forceinline__ void widen_item(const raw_item<KV8> & r, int cell, int blk, uint8_t * t_hi, uint8_t * t_lo) {
+    if (blk & 1) {  // uniform in a warp
+        widen_half<KV8, true>(r, cell, blk, t_hi, t_lo);
+    } else {
+        widen_half<KV8, false>(r, cell, blk, t_hi, t_lo);
     }
 }
 
 // ---- the attention kernel -------------------------------------------------------------------------------------------
 template <int HD, bool KV8>
-__global__ void __launch_bounds__(kThreads, 1) attend_kernel(const attend_params p) {
+__global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_params p) {
     using L = tc_layout<HD>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t * smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    uint8_t * a_q = smem + L::a_q;
     uint8_t * k_hi = smem + L::k_hi;
     uint8_t * k_lo = smem + L::k_lo;
     uint8_t * v_hi = smem + L::v_hi;
     uint8_t * v_lo = smem + L::v_lo;
-    uint8_t * p_op = smem + L::p_op;
-    uint8_t * p_alt = smem + L::p_alt;
     int32_t * row_lo = reinterpret_cast<int32_t *>(smem + L::ranges);
     int32_t * row_hi = row_lo + kMaxM;
-    float * half_max = reinterpret_cast<float *>(smem + L::half_max);
+    float * part_max = reinterpret_cast<float *>(smem + L::part_max);
     uint64_t * bar_s = reinterpret_cast<uint64_t *>(smem + L::bars);
     uint64_t * bar_o = bar_s + 1;
     uint32_t * tmem_slot = reinterpret_cast<uint32_t *>(smem + L::misc);
 
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-    // widening: a thread's item is (cell, 64-dim block); consecutive lanes take consecutive cells, so that the eight
+    const bool worker = wid < kThreads / 32, issuer = tid == kThreads;  // the last warp's first lane issues the MMAs
+    // widening: a thread's item is (cell, 32-dim block); consecutive lanes take consecutive cells, so that the eight
     // lanes of a 16-byte store phase fall on eight different chunks of the swizzle
-    constexpr int kPairs = HD / 64;
-    const bool has_item = tid < kTile * kPairs;
-    const int cell = tid & (kTile - 1), pr = tid >> 6;
-    // softmax: warps w and w + 4 share tensor-memory quarter w & 3 (lanes 32 (w & 3) ..); a lane pair is one query row
-    // (even lane: the hi accumulator row, odd lane: the lo row); this thread owns 16 of the tile's 64 cells of its row
-    const int quarter = wid & 3, col_half = wid >> 2, part = lane & 1;
+    const bool has_item = tid < kTile * (HD / 32);  // workers only: kTile * (HD / 32) <= kThreads
+    const int cell = tid & (kTile - 1), blk = tid >> 6;
+    // tensor memory: warps w, w + 4, w + 8, w + 12 share quarter w & 3 (lanes 32 (w & 3) ..); a lane pair is one query
+    // row (even lane: the hi operand / accumulator row, odd lane: the lo row).  Softmax: each of the quarter's warps
+    // takes a quarter of the tile's cells, this thread 8 of the tile's 64 cells of its row.
+    const int quarter = wid & 3, col_q = wid >> 2, part = lane & 1;
     const int row = 16 * quarter + (lane >> 1);
-    const int col0 = 32 * col_half + 16 * part;  // first cell (of the tile) this thread owns
+    const int col0 = 16 * col_q + 8 * part;  // first cell (of the tile) this thread owns
     const uint32_t lane_base = uint32_t(32 * quarter) << 16;
 
     if (tid == 0) {
@@ -325,13 +370,12 @@ __global__ void __launch_bounds__(kThreads, 1) attend_kernel(const attend_params
         mbar_init_fence();
     }
     if (wid == 0) tmem_alloc(tmem_slot, L::kTmemCols);
-    // the alternate P operand's even rows stay zero for the whole kernel
-    for (int i = tid; i < 64 * 8; i += kThreads) *reinterpret_cast<uint4 *>(p_alt + op_at(2 * (i >> 3), i & 7)) = make_uint4(0, 0, 0, 0);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tmem_s = tmem, tmem_o = tmem + 64;  // columns 0 .. 63: scores; 64 ..: outputs
+    const uint32_t tmem_s = tmem + L::t_s, tmem_o = tmem + L::t_o, tmem_q = tmem + L::t_q, tmem_p = tmem + L::t_p,
+                   tmem_alt = tmem + L::t_alt;
     constexpr uint32_t kIdescS = umma_idesc(kTile, false), kIdescO = umma_idesc(HD, true);
 
     uint32_t it = 0;  // tiles this CTA has issued: phase counter of both barriers
@@ -342,31 +386,38 @@ __global__ void __launch_bounds__(kThreads, 1) attend_kernel(const attend_params
         const int64_t c_end = c_begin + p.unit_cells < p.range_end ? c_begin + p.unit_cells : p.range_end;
         const int n_tiles = int((c_end - c_begin + kTile - 1) / kTile);
 
-        __syncthreads();  // the previous unit's readers of q and the ranges are done
-        // ---- the group's query rows: F32 -> hi (row 2 r) + lo (row 2 r + 1) FP16, rows past m zero ----
-        for (int i = tid; i < kMaxM * (HD / 8); i += kThreads) {
-            const int r = i / (HD / 8), chunk = i - r * (HD / 8);
-            uint4 hi4 = make_uint4(0, 0, 0, 0), lo4 = hi4;
-            if (r < p.m) {
-                const int t = r / p.n_rep, rr = r - t * p.n_rep;
-                const float4 * src = reinterpret_cast<const float4 *>(p.q + (int64_t(t) * p.n_q + head * p.n_rep + rr) * HD) + 2 * chunk;
-                const float4 a = __ldg(src), b = __ldg(src + 1);
-                const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-                uint32_t h[4], l[4];
+        __syncthreads();  // the previous unit's readers of the ranges are done (its MMAs were waited for)
+        // ---- the group's query rows into tensor memory: lane 2 r the hi part of row r, lane 2 r + 1 the rounded
+        //      residual, rows past m zero; this warp the 64 dims of its column quarter ----
+        if (worker && col_q < HD / 64) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const __half2 hh = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
-                    const float2 back = __half22float2(hh);
-                    h[e] = h2_bits(hh);
-                    l[e] = h2_bits(__floats2half2_rn(v[2 * e] - back.x, v[2 * e + 1] - back.y));
+            for (int h = 0; h < 2; ++h) {  // 32 dims = 16 columns at a time
+                float w[16];
+                if (row < p.m) {
+                    const int t = row / p.n_rep, rr = row - t * p.n_rep;
+                    const float4 * src = reinterpret_cast<const float4 *>(p.q + (int64_t(t) * p.n_q + head * p.n_rep + rr) * HD +
+                                                                          64 * col_q + 32 * h);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 x = __ldg(src + j);
+                        const __half2 a = __floats2half2_rn(x.x, x.y), b = __floats2half2_rn(x.z, x.w);
+                        if (part) {
+                            const float2 fa = __half22float2(a), fb = __half22float2(b);
+                            w[2 * j] = __uint_as_float(h2_bits(__floats2half2_rn(x.x - fa.x, x.y - fa.y)));
+                            w[2 * j + 1] = __uint_as_float(h2_bits(__floats2half2_rn(x.z - fb.x, x.w - fb.y)));
+                        } else {
+                            w[2 * j] = __uint_as_float(h2_bits(a)), w[2 * j + 1] = __uint_as_float(h2_bits(b));
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) w[j] = 0.0f;
                 }
-                hi4 = make_uint4(h[0], h[1], h[2], h[3]), lo4 = make_uint4(l[0], l[1], l[2], l[3]);
+                tmem_st16(tmem_q + lane_base + uint32_t(32 * col_q + 16 * h), w);
             }
-            uint8_t * blk = a_q + uint32_t(chunk >> 3) * L::kQBlock;
-            *reinterpret_cast<uint4 *>(blk + op_at(2 * r, chunk & 7)) = hi4;
-            *reinterpret_cast<uint4 *>(blk + op_at(2 * r + 1, chunk & 7)) = lo4;
+            tmem_wait_st();
         }
-        for (int r = tid; r < kMaxM; r += kThreads) {
+        for (int r = tid; r < kMaxM; r += kLaunchThreads) {
             int64_t lo = 0, hi = 0;  // rows past m: an empty range, so every cell is masked
             if (r < p.m) {
                 const int t = r / p.n_rep;
@@ -388,62 +439,63 @@ __global__ void __launch_bounds__(kThreads, 1) attend_kernel(const attend_params
             if (!has_item) return;
             const int64_t c = c_begin + int64_t(tile) * kTile + cell;
             const bool valid = c < c_end;
-            load_item<HD, KV8>(r, cache, scales, (valid ? c : c_begin) * p.n_kv + head, pr, valid);
+            load_item<HD, KV8>(r, cache, scales, (valid ? c : c_begin) * p.n_kv + head, blk, valid);
         };
         fetch(rk, p.k_cache, p.k_scale, 0);
         fetch(rv, p.v_cache, p.v_scale, 0);
 
-        // this thread's view of its row: the reference point (the same in the row's four threads) and the sum over
+        // this thread's view of its row: the reference point (the same in the row's eight threads) and the sum over
         // this thread's cells
         float m_ref = -INFINITY, l_run = 0.0f;
 
         for (int tile = 0; tile < n_tiles; ++tile, ++it) {
             // ---- A: K of this tile into its operand tiles (the previous tile's score MMAs are done: every thread
-            //      passed the barrier behind the softmax that waited for them); the next tile's K into registers ----
-            if (has_item) widen_item<KV8>(rk, cell, pr, k_hi, k_lo);
+            //      waited for them before its softmax); the next tile's K into registers ----
+            if (has_item) widen_item<KV8>(rk, cell, blk, k_hi, k_lo);
             if (tile + 1 < n_tiles) fetch(rk, p.k_cache, p.k_scale, tile + 1);
             fence_proxy_async();
+            tc_fence_before();
             __syncthreads();
             // ---- B: scores on the tensor core, S = [q_hi; q_lo] . (K_lo + K_hi)^T: the small products first, so
             //      that only the sixteen K_hi steps round a large accumulator; meanwhile V of this tile ----
-            if (tid == 0) {
+            if (issuer) {
                 tc_fence_after();
-                const uint32_t qa = smem_u32(a_q), kh = smem_u32(k_hi), kl = smem_u32(k_lo);
+                const uint32_t kh = smem_u32(k_hi), kl = smem_u32(k_lo);
 #pragma unroll
                 for (int kb = 0; kb < L::kBlocks; ++kb) {
 #pragma unroll
                     for (int ks = 0; ks < 4; ++ks) {
-                        umma_f16(tmem_s, umma_desc(qa + kb * L::kQBlock + 32 * ks, 16, 1024),
-                                 umma_desc(kl + kb * L::kCBlock + 32 * ks, 16, 1024), kIdescS, (kb | ks) != 0);
+                        umma_f16_ts(tmem_s, tmem_q + 32 * kb + 8 * ks, umma_desc(kl + kb * L::kCBlock + 32 * ks, 16, 1024), kIdescS,
+                                    (kb | ks) != 0);
                     }
                 }
 #pragma unroll
                 for (int kb = 0; kb < L::kBlocks; ++kb) {
 #pragma unroll
                     for (int ks = 0; ks < 4; ++ks) {
-                        umma_f16(tmem_s, umma_desc(qa + kb * L::kQBlock + 32 * ks, 16, 1024),
-                                 umma_desc(kh + kb * L::kCBlock + 32 * ks, 16, 1024), kIdescS, 1);
+                        umma_f16_ts(tmem_s, tmem_q + 32 * kb + 8 * ks, umma_desc(kh + kb * L::kCBlock + 32 * ks, 16, 1024), kIdescS, 1);
                     }
                 }
                 umma_commit(bar_s);
             }
+            if (worker) {
             if (it > 0) {  // the previous output MMAs read V and P and wrote O
                 mbar_wait(bar_o, (it - 1) & 1, p.err);
                 tc_fence_after();
             }
-            if (has_item) widen_item<KV8>(rv, cell, pr, v_hi, v_lo);
+            if (has_item) widen_item<KV8>(rv, cell, blk, v_hi, v_lo);
             if (tile + 1 < n_tiles) fetch(rv, p.v_cache, p.v_scale, tile + 1);
-            // ---- C: softmax of the tile: every thread 16 cells of one query row ----
+            // ---- C: softmax of the tile: every thread 8 cells of one query row ----
             mbar_wait(bar_s, it & 1, p.err);
             tc_fence_after();
-            float s[16];
+            float s[8];
             {
-                float mine[32];
-                tmem_ld32(tmem_s + lane_base + 32 * col_half, mine);
-                // the pair's other lane holds the row's other part: keep my 16 cells, hand over the other 16
+                float mine[16];
+                tmem_ld16(tmem_s + lane_base + 16 * col_q, mine);
+                // the pair's other lane holds the row's other part: keep my 8 cells, hand over the other 8
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const float keep = part ? mine[16 + j] : mine[j], give = part ? mine[j] : mine[16 + j];
+                for (int j = 0; j < 8; ++j) {
+                    const float keep = part ? mine[8 + j] : mine[j], give = part ? mine[j] : mine[8 + j];
                     s[j] = keep + __shfl_xor_sync(kFull, give, 1);
                 }
             }
@@ -451,92 +503,100 @@ __global__ void __launch_bounds__(kThreads, 1) attend_kernel(const attend_params
             const int lo = row_lo[row] - c0, hi = row_hi[row] - c0;  // this thread's live cells: lo <= j < hi
             float mx = -INFINITY;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
+            for (int j = 0; j < 8; ++j) {
                 s[j] = j >= lo && j < hi ? s[j] * p.scale_log2 : -INFINITY;
                 mx = fmaxf(mx, s[j]);
             }
             mx = fmaxf(mx, __shfl_xor_sync(kFull, mx, 1));
-            if (part == 0) half_max[col_half * kMaxM + row] = mx;
-            named_barrier_id(2 + quarter, 64);  // warps quarter and quarter + 4
-            mx = fmaxf(mx, half_max[(col_half ^ 1) * kMaxM + row]);
+            if (part == 0) part_max[col_q * kMaxM + row] = mx;
+            named_barrier_id(2 + quarter, 128);  // the four warps of this quarter
+            mx = fmaxf(fmaxf(part_max[row], part_max[kMaxM + row]), fmaxf(part_max[2 * kMaxM + row], part_max[3 * kMaxM + row]));
             // lazy reference point: it moves only when the row's maximum has outgrown it by more than 2^kLazy
             float a_row = 1.0f;
             if (mx > m_ref + kLazy || (m_ref == -INFINITY && mx > -INFINITY)) {
                 if (m_ref != -INFINITY) a_row = fast_exp2(m_ref - mx);
                 m_ref = mx;
             }
-            if (__any_sync(kFull, a_row != 1.0f)) {  // this warp's half of the output columns of its lanes' rows
+            if (__any_sync(kFull, a_row != 1.0f)) {  // this warp's quarter of the output columns of its lanes' rows
 #pragma unroll 1
-                for (int cb = 0; cb < HD / 64; ++cb) {
+                for (int cb = 0; cb < HD / 128; ++cb) {
                     float o[32];
-                    const uint32_t at = tmem_o + lane_base + uint32_t(HD / 2 * col_half + 32 * cb);
+                    const uint32_t at = tmem_o + lane_base + uint32_t(HD / 4 * col_q + 32 * cb);
                     tmem_ld32(at, o);
 #pragma unroll
                     for (int j = 0; j < 32; ++j) o[j] *= a_row;
                     tmem_st32(at, o);
                 }
-                tmem_wait_st();
             }
             {
+                // probabilities of this thread's 8 cells as four words each of hi and lo parts (x 2^12)
                 const float ref = m_ref == -INFINITY ? 0.0f : m_ref;
                 float sum = 0.0f;
+                uint32_t hi4[4], lo4[4];
 #pragma unroll
-                for (int cb = 0; cb < 2; ++cb) {
-                    uint32_t hi4[4], lo4[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float p0 = fast_exp2(s[8 * cb + 2 * e] - ref), p1 = fast_exp2(s[8 * cb + 2 * e + 1] - ref);
-                        sum += p0 + p1;
-                        const float x0 = p0 * kPScale, x1 = p1 * kPScale;
-                        const __half2 hv = __floats2half2_rn(x0, x1);
-                        const float2 back = __half22float2(hv);
-                        hi4[e] = h2_bits(hv);
-                        lo4[e] = h2_bits(__floats2half2_rn(x0 - back.x, x1 - back.y));
-                    }
-                    const int chunk = col0 / 8 + cb;
-                    const uint4 h = make_uint4(hi4[0], hi4[1], hi4[2], hi4[3]);
-                    *reinterpret_cast<uint4 *>(p_op + op_at(2 * row, chunk)) = h;
-                    *reinterpret_cast<uint4 *>(p_op + op_at(2 * row + 1, chunk)) = make_uint4(lo4[0], lo4[1], lo4[2], lo4[3]);
-                    *reinterpret_cast<uint4 *>(p_alt + op_at(2 * row + 1, chunk)) = h;
+                for (int e = 0; e < 4; ++e) {
+                    const float p0 = fast_exp2(s[2 * e] - ref), p1 = fast_exp2(s[2 * e + 1] - ref);
+                    sum += p0 + p1;
+                    const float x0 = p0 * kPScale, x1 = p1 * kPScale;
+                    const __half2 hv = __floats2half2_rn(x0, x1);
+                    const float2 back = __half22float2(hv);
+                    hi4[e] = h2_bits(hv);
+                    lo4[e] = h2_bits(__floats2half2_rn(x0 - back.x, x1 - back.y));
                 }
                 l_run = l_run * a_row + sum;
+                // The warp's 16 cells of a row are 8 columns of the row's two operand lanes.  Even lane (the hi lane,
+                // owner of the first 8 cells): P = hi of all 16, alternate P = zeros.  Odd lane (the lo lane, owner of
+                // the last 8): P = lo of all 16, alternate P = hi of all 16.
+                float w_op[8], w_alt[8];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const uint32_t other_hi = __shfl_xor_sync(kFull, hi4[e], 1), other_lo = __shfl_xor_sync(kFull, lo4[e], 1);
+                    w_op[e] = __uint_as_float(part ? other_lo : hi4[e]);
+                    w_op[4 + e] = __uint_as_float(part ? lo4[e] : other_hi);
+                    w_alt[e] = __uint_as_float(part ? other_hi : 0u);
+                    w_alt[4 + e] = __uint_as_float(part ? hi4[e] : 0u);
+                }
+                tmem_st8(tmem_p + lane_base + uint32_t(8 * col_q), w_op);
+                tmem_st8(tmem_alt + lane_base + uint32_t(8 * col_q), w_alt);
+                tmem_wait_st();
             }
+            }  // worker
             fence_proxy_async();
             tc_fence_before();
             __syncthreads();
-            // ---- D: outputs on the tensor core.  Row 2 r: p_hi . V_hi only (four roundings of the large accumulator
-            //      per tile); row 2 r + 1: p_lo . V_hi + p_hi . V_lo (small) ----
-            if (tid == 0) {
+            // ---- D: outputs on the tensor core.  Lane 2 r: p_hi . V_hi only (four roundings of the large accumulator
+            //      per tile); lane 2 r + 1: p_lo . V_hi + p_hi . V_lo (small) ----
+            if (issuer) {
                 tc_fence_after();
-                const uint32_t pa = smem_u32(p_op), pb = smem_u32(p_alt), vh = smem_u32(v_hi), vl = smem_u32(v_lo);
+                const uint32_t vh = smem_u32(v_hi), vl = smem_u32(v_lo);
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {  // 16 cells a step: two groups of eight 128-byte rows
-                    umma_f16(tmem_o, umma_desc(pa + 32 * ks, 16, 1024), umma_desc(vh + 2048 * ks, L::kCBlock, 1024), kIdescO,
-                             (tile | ks) != 0);
-                    umma_f16(tmem_o, umma_desc(pb + 32 * ks, 16, 1024), umma_desc(vl + 2048 * ks, L::kCBlock, 1024), kIdescO, 1);
+                for (int ks = 0; ks < 4; ++ks) {  // 16 cells a step: two groups of eight 128-byte rows, 8 columns of P
+                    umma_f16_ts(tmem_o, tmem_p + 8 * ks, umma_desc(vh + 2048 * ks, L::kCBlock, 1024), kIdescO, (tile | ks) != 0);
+                    umma_f16_ts(tmem_o, tmem_alt + 8 * ks, umma_desc(vl + 2048 * ks, L::kCBlock, 1024), kIdescO, 1);
                 }
                 umma_commit(bar_o);
             }
         }
 
         // ---- the unit's partial result: (reference point, sum, (O[2 r] + O[2 r + 1]) / 2^12) of its rows ----
-        mbar_wait(bar_o, (it - 1) & 1, p.err);
-        tc_fence_after();
-        {
+        if (worker) {
+            mbar_wait(bar_o, (it - 1) & 1, p.err);
+            tc_fence_after();
             const int64_t slot = int64_t(head) * p.n_units + u;
             float * ml = p.ws_ml + slot * p.m * 2;
             float * acc = p.ws_acc + slot * p.m * HD;
-            // the row's sum: its four threads' shares (two lanes here, two in the partner warp)
-            float l_pair = l_run + __shfl_xor_sync(kFull, l_run, 1);
-            if (part == 0) half_max[col_half * kMaxM + row] = l_pair;
-            named_barrier_id(2 + quarter, 64);
-            if (col_half == 0 && part == 0 && row < p.m) {
-                ml[2 * row] = m_ref, ml[2 * row + 1] = l_pair + half_max[kMaxM + row];
+            // the row's sum: its eight threads' shares (two lanes in each of the quarter's four warps)
+            const float l_pair = l_run + __shfl_xor_sync(kFull, l_run, 1);
+            if (part == 0) part_max[col_q * kMaxM + row] = l_pair;
+            named_barrier_id(2 + quarter, 128);
+            if (col_q == 0 && part == 0 && row < p.m) {
+                ml[2 * row] = m_ref;
+                ml[2 * row + 1] = (part_max[row] + part_max[kMaxM + row]) + (part_max[2 * kMaxM + row] + part_max[3 * kMaxM + row]);
             }
 #pragma unroll 1
-            for (int cb = 0; cb < HD / 64; ++cb) {
+            for (int cb = 0; cb < HD / 128; ++cb) {
                 float o[32];
-                const int col = HD / 2 * col_half + 32 * cb;
+                const int col = HD / 4 * col_q + 32 * cb;
                 tmem_ld32(tmem_o + lane_base + uint32_t(col), o);
 #pragma unroll
                 for (int j = 0; j < 32; ++j) o[j] += __shfl_xor_sync(kFull, o[j], 1);
@@ -643,7 +703,7 @@ template <int HD, bool KV8>
 int32_t launch_hd(const attend_params & p, cudaStream_t s) {
     if (!configure<HD, KV8>()) return FNB_LAUNCH_FAILED;
     const int units = p.n_kv * p.n_units;
-    attend_kernel<HD, KV8><<<units < kSmCount ? units : kSmCount, kThreads, tc_layout<HD>::total, s>>>(p);
+    attend_kernel<HD, KV8><<<units < kSmCount ? units : kSmCount, kLaunchThreads, tc_layout<HD>::total, s>>>(p);
     if (cudaPeekAtLastError() != cudaSuccess) return FNB_LAUNCH_FAILED;
     attend_fold_kernel<HD><<<p.rows * p.n_q, HD * kFoldLanes, 0, s>>>(p);
     return launch_status();
