@@ -27,8 +27,10 @@
 //     bytes] with the 16-byte chunks XOR-swizzled by the row's low three bits (the 128-byte swizzle).  The same bytes
 //     serve as a K-major operand (rows = cells, for the scores) and as an MN-major operand (contiguous = dims, for the
 //     outputs), so K and V are widened by the same code: a thread takes a pair of Q8_0 blocks (or 64 KV8 codes) of one
-//     cell from registers and stores eight 16-byte chunks each of hi and lo.
-//   * The cache is read straight into registers one tile (64 cells) ahead: shared memory is full of operands.
+//     cell and stores 16-byte chunks of hi and lo.
+//   * Cells arrive by 16-byte asynchronous copies into a two-stage ring of raw tiles, one tile (64 cells) ahead;
+//     consecutive threads copy consecutive pieces, so that the copies cover whole cache lines (a thread reading its
+//     own cell straight from the cache touched 32 lines per warp instruction and kept the L1 pipe busy 80 % of the time).
 //   * One thread issues the MMAs; completion comes back through mbarriers (tcgen05.commit).  While the score MMAs of a
 //     tile run, all warps widen its V; while the output MMAs run, they widen the next tile's K.  Warps 0 .. 3 (the
 //     four 32-lane quarters of tensor memory) read the scores, warps 2 and 3 hand their rows (the lo parts) to warps 0
@@ -110,6 +112,15 @@ struct attend_params {
 };
 
 // ---- small wrappers -------------------------------------------------------------------------------------------------
+// 16 (or 8) bytes global -> shared; src_bytes = 0 writes zeros instead (cells past the end of a unit)
+__device__ __forceinline__ void cp_async16(void * dst, const void * src, bool valid) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(valid ? 16 : 0) : "memory");
+}
+__device__ __forceinline__ void cp_async8(void * dst, const void * src, bool valid) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(valid ? 8 : 0) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -245,15 +256,19 @@ __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.
 // too, its 4 KB per MMA made shared-memory bandwidth the bound).  Stacked rows interleave the parts: lane 2 r holds
 // query row r's hi part, lane 2 r + 1 its lo part, so a query row's two accumulator rows sit in adjacent lanes of one
 // 32-lane quarter.
-template <int HD>
+template <int HD, bool KV8>
 struct tc_layout {
     static constexpr int kBlocks = HD / 64;
     static constexpr int kCBlock = kTile * 128;               // a block of a cell operand
+    static constexpr int kCell = KV8 ? HD : HD / 32 * 34;     // raw bytes of a cell
+    static constexpr int kRawTensor = kTile * kCell + (KV8 ? kTile * 8 : 0);  // a tensor's raw tile (KV8: + scales, 8-byte slots)
+    static constexpr int kRawStage = 2 * kRawTensor;          // K raw | V raw
     static constexpr int k_hi = 0;
     static constexpr int k_lo = k_hi + kBlocks * kCBlock;
     static constexpr int v_hi = k_lo + kBlocks * kCBlock;
     static constexpr int v_lo = v_hi + kBlocks * kCBlock;
-    static constexpr int ranges = v_lo + kBlocks * kCBlock;   // int32 lo[64], hi[64]
+    static constexpr int raw = v_lo + kBlocks * kCBlock;      // [2 stages][K raw | V raw]: the cells as they lie in the cache
+    static constexpr int ranges = raw + 2 * kRawStage;        // int32 lo[64], hi[64]
     static constexpr int part_max = ranges + 2 * kMaxM * 4;   // float [4][64]: a row's maximum over each quarter of a tile
     static constexpr int bars = part_max + 4 * kMaxM * 4;     // two mbarriers
     static constexpr int misc = bars + 16;                    // tensor-memory base
@@ -277,21 +292,21 @@ struct raw_item {
 // blk: the item's 32-dim block of the cell.  Q8_0: the block's 34 bytes lie in nine aligned words of its pair of blocks
 // (68 bytes = 17 words): words 0 .. 8 for the pair's first block (d in the low half of word 0, codes from its high
 // half on), words 8 .. 16 for the second (d in the high half of word 8, codes in words 9 .. 16).
+// from the staged raw tile: `cell_raw` the cell's bytes, `cell_scales` (KV8) its FP16 group scales
 template <int HD, bool KV8>
-__device__ __forceinline__ void load_item(raw_item<KV8> & r, const uint8_t * cache, const uint16_t * scales, int64_t cell_head,
-                                          int blk, bool valid) {
+__device__ __forceinline__ void load_item(raw_item<KV8> & r, const uint8_t * cell_raw, const uint8_t * cell_scales, int blk) {
     if (KV8) {
-        const uint4 * src = reinterpret_cast<const uint4 *>(cache + cell_head * HD + 32 * blk);
+        const uint4 * src = reinterpret_cast<const uint4 *>(cell_raw + 32 * blk);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-            const uint4 v = valid ? __ldg(src + j) : make_uint4(0, 0, 0, 0);
+            const uint4 v = src[j];
             r.w[4 * j] = v.x, r.w[4 * j + 1] = v.y, r.w[4 * j + 2] = v.z, r.w[4 * j + 3] = v.w;
         }
-        r.scale = valid ? uint32_t(__ldg(scales + cell_head * (HD / 64) + (blk >> 1))) : 0u;
+        r.scale = reinterpret_cast<const uint16_t *>(cell_scales)[blk >> 1];
     } else {
-        const uint32_t * src = reinterpret_cast<const uint32_t *>(cache + cell_head * (HD / 32 * 34) + 68 * (blk >> 1)) + 8 * (blk & 1);
+        const uint32_t * src = reinterpret_cast<const uint32_t *>(cell_raw + 68 * (blk >> 1)) + 8 * (blk & 1);
 #pragma unroll
-        for (int j = 0; j < 9; ++j) r.w[j] = valid ? __ldg(src + j) : 0u;
+        for (int j = 0; j < 9; ++j) r.w[j] = src[j];
         r.scale = 0;
     }
 }
@@ -336,13 +351,14 @@ __device__ __forceinline__ void widen_item(const raw_item<KV8> & r, int cell, in
 // ---- the attention kernel -------------------------------------------------------------------------------------------
 template <int HD, bool KV8>
 __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_params p) {
-    using L = tc_layout<HD>;
+    using L = tc_layout<HD, KV8>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t * smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t * k_hi = smem + L::k_hi;
     uint8_t * k_lo = smem + L::k_lo;
     uint8_t * v_hi = smem + L::v_hi;
     uint8_t * v_lo = smem + L::v_lo;
+    uint8_t * raw = smem + L::raw;
     int32_t * row_lo = reinterpret_cast<int32_t *>(smem + L::ranges);
     int32_t * row_hi = row_lo + kMaxM;
     float * part_max = reinterpret_cast<float *>(smem + L::part_max);
@@ -433,16 +449,66 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
             row_lo[r] = int32_t(lo), row_hi[r] = int32_t(hi);
         }
 
-        // this thread's raw items of a tile
-        raw_item<KV8> rk, rv;
-        const auto fetch = [&](raw_item<KV8> & r, const uint8_t * cache, const uint16_t * scales, int tile) {
-            if (!has_item) return;
-            const int64_t c = c_begin + int64_t(tile) * kTile + cell;
-            const bool valid = c < c_end;
-            load_item<HD, KV8>(r, cache, scales, (valid ? c : c_begin) * p.n_kv + head, blk, valid);
+        // ---- raw tiles: the tile's cells of this KV head, as they lie in the cache, into stage `st` of the ring by
+        //      16-byte (8-byte for 136-byte cells) asynchronous copies; consecutive threads take consecutive pieces, so
+        //      a warp's copies cover whole cells ----
+        // a thread's pieces are the same in every tile: (tensor, cell of the tile, piece of the cell) worked out once
+        constexpr int kPiece = L::kCell % 16 == 0 ? 16 : 8;
+        constexpr int kPieces = L::kCell / kPiece;  // pieces of a cell
+        constexpr int kMine = (2 * kTile * kPieces + kThreads - 1) / kThreads;
+        int piece_cell[kMine];      // cell of the tile, or -1: no such piece
+        uint32_t piece_src[kMine];  // byte offset from the tile's first cell of this head in the tensor
+        int piece_dst[kMine];       // byte offset in a stage; odd: the piece is V's (offsets are even)
+#pragma unroll
+        for (int k = 0; k < kMine; ++k) {
+            const int i = tid + k * kThreads;
+            const int tensor = i / (kTile * kPieces), rest = i - tensor * (kTile * kPieces);
+            const int cl = rest / kPieces, piece = rest - cl * kPieces;
+            piece_cell[k] = worker && i < 2 * kTile * kPieces ? cl : -1;
+            piece_src[k] = uint32_t(cl) * uint32_t(p.n_kv) * L::kCell + kPiece * piece;  // < 64 cells x n_kv x 272
+            piece_dst[k] = (tensor * L::kRawTensor + cl * L::kCell + kPiece * piece) | tensor;
+        }
+        const auto issue = [&](int tile, int st) {
+            uint8_t * base = raw + st * L::kRawStage;
+            const int64_t t0 = c_begin + int64_t(tile) * kTile;
+            const int64_t head_at = (t0 * p.n_kv + head) * L::kCell;
+#pragma unroll
+            for (int k = 0; k < kMine; ++k) {
+                if (piece_cell[k] >= 0) {
+                    const bool valid = t0 + piece_cell[k] < c_end;
+                    const uint8_t * src = ((piece_dst[k] & 1) ? p.v_cache : p.k_cache) + (valid ? head_at + piece_src[k] : 0);
+                    uint8_t * dst = base + (piece_dst[k] & ~1);
+                    if (kPiece == 16) {
+                        cp_async16(dst, src, valid);
+                    } else {
+                        cp_async8(dst, src, valid);
+                    }
+                }
+            }
+            if (KV8 && worker) {
+                for (int i = tid; i < 2 * kTile; i += kThreads) {
+                    const int tensor = i / kTile, cl = i - tensor * kTile;
+                    const int64_t c = t0 + cl;
+                    const bool valid = c < c_end;
+                    const uint16_t * src = (tensor == 0 ? p.k_scale : p.v_scale) + ((valid ? c : c_begin) * p.n_kv + head) * (HD / 64);
+                    uint8_t * dst = base + tensor * L::kRawTensor + kTile * L::kCell + cl * 8;
+                    if (HD == 256) {
+                        cp_async8(dst, src, valid);
+                    } else {  // two scales a cell: 4 bytes, a plain load
+                        *reinterpret_cast<uint32_t *>(dst) = valid ? __ldg(reinterpret_cast<const uint32_t *>(src)) : 0u;
+                    }
+                }
+            }
+            cp_async_commit();
         };
-        fetch(rk, p.k_cache, p.k_scale, 0);
-        fetch(rv, p.v_cache, p.v_scale, 0);
+        // this thread's item of a staged tensor
+        const auto item_of = [&](raw_item<KV8> & r, int st, int tensor) {
+            const uint8_t * t = raw + st * L::kRawStage + tensor * L::kRawTensor;
+            load_item<HD, KV8>(r, t + cell * L::kCell, t + kTile * L::kCell + cell * 8, blk);
+        };
+        issue(0, 0);
+        cp_async_wait_all();
+        __syncthreads();  // the first tile has landed for every thread
 
         // this thread's view of its row: the reference point (the same in the row's eight threads) and the sum over
         // this thread's cells
@@ -451,8 +517,13 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
         for (int tile = 0; tile < n_tiles; ++tile, ++it) {
             // ---- A: K of this tile into its operand tiles (the previous tile's score MMAs are done: every thread
             //      waited for them before its softmax); the next tile's K into registers ----
-            if (has_item) widen_item<KV8>(rk, cell, blk, k_hi, k_lo);
-            if (tile + 1 < n_tiles) fetch(rk, p.k_cache, p.k_scale, tile + 1);
+            const int st = tile & 1;
+            if (tile + 1 < n_tiles) issue(tile + 1, st ^ 1);  // its last readers (the tile before this one) are behind a barrier
+            if (has_item) {
+                raw_item<KV8> r;
+                item_of(r, st, 0);
+                widen_item<KV8>(r, cell, blk, k_hi, k_lo);
+            }
             fence_proxy_async();
             tc_fence_before();
             __syncthreads();
@@ -483,8 +554,11 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
                 mbar_wait(bar_o, (it - 1) & 1, p.err);
                 tc_fence_after();
             }
-            if (has_item) widen_item<KV8>(rv, cell, blk, v_hi, v_lo);
-            if (tile + 1 < n_tiles) fetch(rv, p.v_cache, p.v_scale, tile + 1);
+            if (has_item) {
+                raw_item<KV8> r;
+                item_of(r, st, 1);
+                widen_item<KV8>(r, cell, blk, v_hi, v_lo);
+            }
             // ---- C: softmax of the tile: every thread 8 cells of one query row ----
             mbar_wait(bar_s, it & 1, p.err);
             tc_fence_after();
@@ -561,6 +635,7 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
                 tmem_wait_st();
             }
             }  // worker
+            cp_async_wait_all();  // the next tile's cells, asked for a tile ago: the barrier below publishes them
             fence_proxy_async();
             tc_fence_before();
             __syncthreads();
@@ -691,7 +766,7 @@ bool configure() {
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
     if (!done[dev].load(std::memory_order_acquire)) {
         if (cudaFuncSetAttribute(attend_kernel<HD, KV8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 tc_layout<HD>::total) != cudaSuccess) {
+                                 tc_layout<HD, KV8>::total) != cudaSuccess) {
             return false;
         }
         done[dev].store(true, std::memory_order_release);
@@ -703,7 +778,7 @@ template <int HD, bool KV8>
 int32_t launch_hd(const attend_params & p, cudaStream_t s) {
     if (!configure<HD, KV8>()) return FNB_LAUNCH_FAILED;
     const int units = p.n_kv * p.n_units;
-    attend_kernel<HD, KV8><<<units < kSmCount ? units : kSmCount, kLaunchThreads, tc_layout<HD>::total, s>>>(p);
+    attend_kernel<HD, KV8><<<units < kSmCount ? units : kSmCount, kLaunchThreads, tc_layout<HD, KV8>::total, s>>>(p);
     if (cudaPeekAtLastError() != cudaSuccess) return FNB_LAUNCH_FAILED;
     attend_fold_kernel<HD><<<p.rows * p.n_q, HD * kFoldLanes, 0, s>>>(p);
     return launch_status();
@@ -712,7 +787,7 @@ int32_t launch_hd(const attend_params & p, cudaStream_t s) {
 bool shape_ok(const fnb_attend_args * a) {
     if (a == nullptr) return false;
     if (a->head_dim != 128 && a->head_dim != 256) return false;
-    if (a->rows < 1 || a->n_q_heads < 1 || a->n_kv_heads < 1 || a->n_q_heads % a->n_kv_heads != 0) return false;
+    if (a->rows < 1 || a->n_q_heads < 1 || a->n_kv_heads < 1 || a->n_kv_heads > 1024 || a->n_q_heads % a->n_kv_heads != 0) return false;
     if (int64_t(a->rows) * (a->n_q_heads / a->n_kv_heads) > kMaxM) return false;
     if (a->cache_slots < 1 || a->cache_slots > INT32_MAX) return false;
     if (a->range_begin < 0 || a->range_end <= a->range_begin || a->range_end > a->cache_slots) return false;
