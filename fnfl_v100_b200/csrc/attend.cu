@@ -18,26 +18,35 @@
 //     two FP16 operands, value = hi + lo (about 22 bits):  q = q_hi + q_lo (rounded residual);  K and V = d x code,
 //     split EXACTLY (hi = the rounded product, lo = the fused residual, one half2 instruction each per two values);
 //     p = p_hi + p_lo (scaled by 2^12 to stay clear of FP16's subnormals).
-//   * Stacked rows.  A group has at most 64 query rows and the MMA is 128 rows tall: rows 0 .. 63 of the A operand hold
-//     the hi parts and rows 64 .. 127 the lo parts, so ONE pass over the B operand gives hi . B in accumulator rows
-//     0 .. 63 and lo . B in rows 64 .. 127, and the sum of the two rows is the product of the full-precision operand.
-//     Scores: S = [q_hi; q_lo] . (K_hi + K_lo)^T (two accumulating MMAs per 16 dims).  Outputs: O += [p_hi; p_lo] .
-//     (V_hi + V_lo) (two per 16 cells).  All four partial products are kept.
-//   * Operand tiles in shared memory are written directly in the MMA's canonical layout: 64-dim blocks of [row][128
-//     bytes] with the 16-byte chunks XOR-swizzled by the row's low three bits (the 128-byte swizzle).  The same bytes
-//     serve as a K-major operand (rows = cells, for the scores) and as an MN-major operand (contiguous = dims, for the
-//     outputs), so K and V are widened by the same code: a thread takes a pair of Q8_0 blocks (or 64 KV8 codes) of one
-//     cell and stores 16-byte chunks of hi and lo.
+//   * Stacked rows.  A group has at most 64 query rows and the MMA is 128 rows tall: row 2 r of the A operand holds
+//     query row r's hi part and row 2 r + 1 its lo part, so ONE pass over the B operand gives hi . B and lo . B in
+//     adjacent accumulator rows (adjacent lanes of tensor memory: a shuffle adds them).  Scores: S = [q_hi; q_lo] .
+//     (K_lo + K_hi)^T, the small K_lo products first.  Outputs: row 2 r: p_hi . V_hi; row 2 r + 1: p_lo . V_hi +
+//     p_hi . V_lo, through an alternate probability operand whose even rows are zero.  The order matters: the tensor
+//     core adds into its F32 accumulator by truncation (about 0.7 x 2^-24 of relative bias per accumulating MMA), so
+//     the large accumulator rows take as few steps as possible (16 per score tile, 4 per tile of outputs) and a work
+//     unit is capped at 24 tiles (make_plan); partial results of units are combined in round-to-nearest F32.
+//   * The stacked operands (query rows, probabilities) live in TENSOR memory, a row per lane, two FP16 values per
+//     column, written by tcgen05.st straight from the registers that made them; only the cell operands are in shared
+//     memory.  Tensor-memory columns: 64 scores | head_dim outputs | head_dim / 2 query | 32 + 32 probabilities = 512
+//     at head_dim 256, all there are.
+//   * Cell operand tiles in shared memory are written directly in the MMA's canonical layout: 64-dim blocks of
+//     [cell][128 bytes] with the 16-byte chunks XOR-swizzled by the cell's low three bits (the 128-byte swizzle).  The
+//     same bytes serve as a K-major operand (rows = cells, for the scores) and as an MN-major operand (contiguous =
+//     dims, for the outputs), so K and V are widened by the same code: a thread takes one Q8_0 block (or 32 KV8 codes)
+//     of one cell and stores four 16-byte chunks each of hi and lo; consecutive lanes take consecutive cells, so the
+//     eight lanes of a store phase fall on eight different chunks.
 //   * Cells arrive by 16-byte asynchronous copies into a two-stage ring of raw tiles, one tile (64 cells) ahead;
 //     consecutive threads copy consecutive pieces, so that the copies cover whole cache lines (a thread reading its
 //     own cell straight from the cache touched 32 lines per warp instruction and kept the L1 pipe busy 80 % of the time).
-//   * One thread issues the MMAs; completion comes back through mbarriers (tcgen05.commit).  While the score MMAs of a
-//     tile run, all warps widen its V; while the output MMAs run, they widen the next tile's K.  Warps 0 .. 3 (the
-//     four 32-lane quarters of tensor memory) read the scores, warps 2 and 3 hand their rows (the lo parts) to warps 0
-//     and 1 through shared memory, and a thread of warps 0 / 1 owns one query row: mask, running maximum and sum,
-//     probabilities, all without shuffles.  The maximum is lazy: the reference point moves only when a row's maximum
-//     has grown by more than 2^3, and only then are the row's accumulators rescaled in tensor memory.
-//   * Split over cells (flash decoding): a work unit is (KV head, range of cells), about one per SM; a unit writes
+//   * Sixteen worker warps and one that only issues the MMAs; completion comes back through mbarriers
+//     (tcgen05.commit).  While the score MMAs of a tile run, the workers widen its V; while the output MMAs run, they
+//     widen the next tile's K.  Softmax: warps w, w + 4, w + 8, w + 12 share tensor-memory quarter w & 3 and take a
+//     quarter of the tile's cells each; a lane pair is one query row (hi lane, lo lane), a thread 8 cells of it.  The
+//     row maximum crosses the quarter's four warps through shared memory and a 128-thread barrier.  The maximum is
+//     lazy: the reference point moves only when a row's maximum has outgrown it by more than 2^3, and only then are the
+//     row's accumulators rescaled in tensor memory.
+//   * Split over cells (flash decoding): a work unit is (KV head, range of cells), about two per SM; a unit writes
 //     (reference point, sum, unnormalised output) partials into a caller-supplied workspace, and a second small kernel
 //     folds them in a fixed order, divides, gates and writes the rows.  The workspace is the only global memory beyond
 //     inputs and outputs; its size is a function of the shape (fnb_attend_workspace_bytes).
