@@ -372,6 +372,26 @@ def extra_configs(dev, k: int, peak: float, rest_s: float) -> dict:
         y = torch.empty_like(x)
         return lambda: ops.rms_norm(x, w, c.eps, out=y)
     both("rms_norm_R512", make_norm, 2 * R1 * c.hidden * 4 + c.hidden * 4, "configuration 1: x [512][2048]")
+    del kc, vc
+
+    # the consumer of the cache the chain appends to: decode attention of 1 and 5 rows over the chain's depth (196608
+    # cells, 2 KV heads under 16 query heads); the roofline counts the cache bytes, read once whatever the row count
+    cells = c.depth
+
+    def plane():
+        t = torch.randint(0, 256, (cells, c.n_kv_heads, c.head_dim // 32, ops.Q8_0_BLOCK), dtype=torch.uint8, device=dev, generator=gen)
+        t.view(torch.float16).reshape(cells, c.n_kv_heads, c.head_dim // 32, ops.Q8_0_BLOCK // 2)[..., 0] = 0.01
+        return t.reshape(cells, c.n_kv_heads, c.head_dim // 32 * ops.Q8_0_BLOCK)
+    ka, va = plane(), plane()
+    ws = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
+    att = {"what": "fnb_attend over 196608 Q8_0 cells x 2 KV heads, 16 query heads of 256 (tcgen05.mma); bytes = the cache read once"}
+    for rows in (1, 5):
+        qa = synth.counter_normal(seed + 6, rows, 0, rows, c.n_q_heads * c.head_dim, 1.0, dev).view(rows, c.n_q_heads, c.head_dim)
+        oa = torch.empty_like(qa)
+        g = capture(lambda: ops.attend(qa, ka, va, range_begin=0, range_end=cells, out=oa, workspace=ws, err=err))
+        time.sleep(rest_s)
+        att["rows%d" % rows] = op_report(time_replays([g], k), cells * c.n_kv_heads * 2 * cell + 2 * qa.numel() * 4, peak)
+    out["attend_q8_0_C196608"] = att
     if int(err.item()) != 0:
         raise RuntimeError("device error word %d in the extra configurations" % int(err.item()))
     return out

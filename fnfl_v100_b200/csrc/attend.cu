@@ -128,6 +128,9 @@ __device__ __forceinline__ void cp_async16(void * dst, const void * src, bool va
 __device__ __forceinline__ void cp_async8(void * dst, const void * src, bool valid) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(valid ? 8 : 0) : "memory");
 }
+__device__ __forceinline__ void cp_async4(void * dst, const void * src, bool valid) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(valid ? 4 : 0) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -277,10 +280,9 @@ struct tc_layout {
     static constexpr int v_hi = k_lo + kBlocks * kCBlock;
     static constexpr int v_lo = v_hi + kBlocks * kCBlock;
     static constexpr int raw = v_lo + kBlocks * kCBlock;      // [2 stages][K raw | V raw]: the cells as they lie in the cache
-    static constexpr int ranges = raw + 2 * kRawStage;        // int32 lo[64], hi[64]
-    static constexpr int part_max = ranges + 2 * kMaxM * 4;   // float [4][64]: a row's maximum over each quarter of a tile
-    static constexpr int bars = part_max + 4 * kMaxM * 4;     // two mbarriers
-    static constexpr int misc = bars + 16;                    // tensor-memory base
+    static constexpr int part_max = raw + 2 * kRawStage;      // float [4][64]: a row's maximum over each quarter of a tile
+    static constexpr int bars = part_max + 4 * kMaxM * 4;     // eight mbarriers
+    static constexpr int misc = bars + 64;                    // tensor-memory base, the give-up flag
     static constexpr int total = misc + 16 + 1024;            // + slack to align the base to 1024 bytes
     // tensor-memory columns: scores | outputs | stacked query rows | stacked probabilities | the alternate probabilities
     static constexpr uint32_t t_s = 0, t_o = 64, t_q = t_o + HD, t_p = t_q + HD / 2, t_alt = t_p + 32;
@@ -358,6 +360,33 @@ __device__ __forceinline__ void widen_item(const raw_item<KV8> & r, int cell, in
 }
 
 // ---- the attention kernel -------------------------------------------------------------------------------------------
+// Waits of this kernel: bounded, and once one has run out every other wait of the CTA returns at its next look (the
+// CTA then runs to its end on whatever data it has, with FNB_ERR_TIMEOUT set).
+__device__ __forceinline__ bool tc_wait(uint64_t * bar, uint32_t parity, volatile uint32_t * gave_up, uint32_t * err) {
+    for (uint32_t i = 0; i < kPrimarySpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63u) == 63u && *gave_up != 0) return false;
+    }
+    *gave_up = 1;
+    if (err != nullptr) atomicOr(err, FNB_ERR_TIMEOUT);
+    return false;
+}
+// the barrier gets one of its expected arrivals when this thread's asynchronous copies issued so far have landed
+__device__ __forceinline__ void cp_async_arrive(uint64_t * bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Roles.  Sixteen worker warps stage, widen and run the softmax; the last warp's first lane issues the MMAs.  Nothing
+// in the tile loop is a block-wide barrier: every hand-over is an mbarrier, so warps drift apart by as much as the
+// data allows and widening, softmax and tensor work overlap.
+//   raw_k[2], raw_v[2]  (512 arrivals)  a stage of the raw ring has landed: each worker's copies arrive on completion
+//   k_ready             (512)           every worker has widened its share of K (and, on a unit's first tile, stored
+//                                       its share of the query operand): the issuer starts the score MMAs
+//   bar_s               (commit)        the score MMAs are done: S readable, the K operand and - because k_ready
+//                                       needed every worker - every worker's reads of the PREVIOUS tile are done
+//   pv_ready            (512)           every worker has widened its share of V and stored its probabilities
+//   bar_o               (commit)        the output MMAs are done: O, P and the V operand are free
+// Tile g (counted over the CTA's units) uses stage g & 1 of both rings and phase g of the four tile barriers.
 template <int HD, bool KV8>
 __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_params p) {
     using L = tc_layout<HD, KV8>;
@@ -368,30 +397,26 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
     uint8_t * v_hi = smem + L::v_hi;
     uint8_t * v_lo = smem + L::v_lo;
     uint8_t * raw = smem + L::raw;
-    int32_t * row_lo = reinterpret_cast<int32_t *>(smem + L::ranges);
-    int32_t * row_hi = row_lo + kMaxM;
     float * part_max = reinterpret_cast<float *>(smem + L::part_max);
     uint64_t * bar_s = reinterpret_cast<uint64_t *>(smem + L::bars);
     uint64_t * bar_o = bar_s + 1;
+    uint64_t * k_ready = bar_s + 2;
+    uint64_t * pv_ready = bar_s + 3;
+    uint64_t * raw_k = bar_s + 4;  // [2]
+    uint64_t * raw_v = bar_s + 6;  // [2]
     uint32_t * tmem_slot = reinterpret_cast<uint32_t *>(smem + L::misc);
+    volatile uint32_t * gave_up = tmem_slot + 1;
 
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-    const bool worker = wid < kThreads / 32, issuer = tid == kThreads;  // the last warp's first lane issues the MMAs
-    // widening: a thread's item is (cell, 32-dim block); consecutive lanes take consecutive cells, so that the eight
-    // lanes of a 16-byte store phase fall on eight different chunks of the swizzle
-    const bool has_item = tid < kTile * (HD / 32);  // workers only: kTile * (HD / 32) <= kThreads
-    const int cell = tid & (kTile - 1), blk = tid >> 6;
-    // tensor memory: warps w, w + 4, w + 8, w + 12 share quarter w & 3 (lanes 32 (w & 3) ..); a lane pair is one query
-    // row (even lane: the hi operand / accumulator row, odd lane: the lo row).  Softmax: each of the quarter's warps
-    // takes a quarter of the tile's cells, this thread 8 of the tile's 64 cells of its row.
-    const int quarter = wid & 3, col_q = wid >> 2, part = lane & 1;
-    const int row = 16 * quarter + (lane >> 1);
-    const int col0 = 16 * col_q + 8 * part;  // first cell (of the tile) this thread owns
-    const uint32_t lane_base = uint32_t(32 * quarter) << 16;
+    const bool worker = wid < kThreads / 32;
 
     if (tid == 0) {
         mbar_init(bar_s, 1);
         mbar_init(bar_o, 1);
+        mbar_init(k_ready, kThreads);
+        mbar_init(pv_ready, kThreads);
+        for (int i = 0; i < 2; ++i) mbar_init(raw_k + i, kThreads), mbar_init(raw_v + i, kThreads);
+        *gave_up = 0;
         mbar_init_fence();
     }
     if (wid == 0) tmem_alloc(tmem_slot, L::kTmemCols);
@@ -402,269 +427,291 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
     const uint32_t tmem_s = tmem + L::t_s, tmem_o = tmem + L::t_o, tmem_q = tmem + L::t_q, tmem_p = tmem + L::t_p,
                    tmem_alt = tmem + L::t_alt;
     constexpr uint32_t kIdescS = umma_idesc(kTile, false), kIdescO = umma_idesc(HD, true);
-
-    uint32_t it = 0;  // tiles this CTA has issued: phase counter of both barriers
     const int total_units = p.n_kv * p.n_units;
-    for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
-        const int head = unit / p.n_units, u = unit - head * p.n_units;
-        const int64_t c_begin = p.range_begin + int64_t(u) * p.unit_cells;
-        const int64_t c_end = c_begin + p.unit_cells < p.range_end ? c_begin + p.unit_cells : p.range_end;
-        const int n_tiles = int((c_end - c_begin + kTile - 1) / kTile);
+    const auto tiles_of = [&](int unit, int & head, int & u, int64_t & c_begin, int64_t & c_end) {
+        head = unit / p.n_units, u = unit - head * p.n_units;
+        c_begin = p.range_begin + int64_t(u) * p.unit_cells;
+        c_end = c_begin + p.unit_cells < p.range_end ? c_begin + p.unit_cells : p.range_end;
+        return int((c_end - c_begin + kTile - 1) / kTile);
+    };
 
-        __syncthreads();  // the previous unit's readers of the ranges are done (its MMAs were waited for)
-        // ---- the group's query rows into tensor memory: lane 2 r the hi part of row r, lane 2 r + 1 the rounded
-        //      residual, rows past m zero; this warp the 64 dims of its column quarter ----
-        if (worker && col_q < HD / 64) {
+    if (!worker) {
+        // ---- the issuer: S = [q_hi; q_lo] . (K_lo + K_hi)^T, the small products first, so that only the sixteen K_hi
+        //      steps round a large accumulator; then lane 2 r: p_hi . V_hi only (four roundings of the large
+        //      accumulator per tile), lane 2 r + 1: p_lo . V_hi + p_hi . V_lo (small) ----
+        if (lane == 0) {
+            // the operand tiles never move: their descriptors are made once, and an MMA's is its tile's plus a constant
+            // (byte offset / 16 in the address field; no offset here carries out of it)
+            const uint64_t d_kh = umma_desc(smem_u32(k_hi), 16, 1024), d_kl = umma_desc(smem_u32(k_lo), 16, 1024);
+            const uint64_t d_vh = umma_desc(smem_u32(v_hi), L::kCBlock, 1024), d_vl = umma_desc(smem_u32(v_lo), L::kCBlock, 1024);
+            uint32_t g = 0;
+            for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
+                int head, u;
+                int64_t c_begin, c_end;
+                const int n_tiles = tiles_of(unit, head, u, c_begin, c_end);
+                for (int tile = 0; tile < n_tiles; ++tile, ++g) {
+                    tc_wait(k_ready, g & 1, gave_up, p.err);
+                    tc_fence_after();
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {  // 32 dims = 16 columns at a time
-                float w[16];
-                if (row < p.m) {
-                    const int t = row / p.n_rep, rr = row - t * p.n_rep;
-                    const float4 * src = reinterpret_cast<const float4 *>(p.q + (int64_t(t) * p.n_q + head * p.n_rep + rr) * HD +
-                                                                          64 * col_q + 32 * h);
+                    for (int kb = 0; kb < L::kBlocks; ++kb) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const float4 x = __ldg(src + j);
-                        const __half2 a = __floats2half2_rn(x.x, x.y), b = __floats2half2_rn(x.z, x.w);
-                        if (part) {
-                            const float2 fa = __half22float2(a), fb = __half22float2(b);
-                            w[2 * j] = __uint_as_float(h2_bits(__floats2half2_rn(x.x - fa.x, x.y - fa.y)));
-                            w[2 * j + 1] = __uint_as_float(h2_bits(__floats2half2_rn(x.z - fb.x, x.w - fb.y)));
-                        } else {
-                            w[2 * j] = __uint_as_float(h2_bits(a)), w[2 * j + 1] = __uint_as_float(h2_bits(b));
+                        for (int ks = 0; ks < 4; ++ks) {
+                            umma_f16_ts(tmem_s, tmem_q + 32 * kb + 8 * ks, d_kl + uint64_t((kb * L::kCBlock + 32 * ks) >> 4), kIdescS, (kb | ks) != 0);
                         }
                     }
-                } else {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) w[j] = 0.0f;
+                    for (int kb = 0; kb < L::kBlocks; ++kb) {
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks) {
+                            umma_f16_ts(tmem_s, tmem_q + 32 * kb + 8 * ks, d_kh + uint64_t((kb * L::kCBlock + 32 * ks) >> 4), kIdescS, 1);
+                        }
+                    }
+                    umma_commit(bar_s);
+                    tc_wait(pv_ready, g & 1, gave_up, p.err);
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {  // 16 cells a step: two groups of eight 128-byte rows, 8 columns of P
+                        umma_f16_ts(tmem_o, tmem_p + 8 * ks, d_vh + uint64_t((2048 * ks) >> 4), kIdescO, (tile | ks) != 0);
+                        umma_f16_ts(tmem_o, tmem_alt + 8 * ks, d_vl + uint64_t((2048 * ks) >> 4), kIdescO, 1);
+                    }
+                    umma_commit(bar_o);
                 }
-                tmem_st16(tmem_q + lane_base + uint32_t(32 * col_q + 16 * h), w);
             }
-            tmem_wait_st();
         }
-        for (int r = tid; r < kMaxM; r += kLaunchThreads) {
-            int64_t lo = 0, hi = 0;  // rows past m: an empty range, so every cell is masked
-            if (r < p.m) {
-                const int t = r / p.n_rep;
-                lo = p.first_cell != nullptr ? int64_t(__ldg(p.first_cell + t)) : p.range_begin;
-                hi = p.n_cells != nullptr ? lo + int64_t(__ldg(p.n_cells + t)) : p.range_end;
-                if (lo < 0 || hi > p.cache_slots || hi < lo) {
-                    if (p.err != nullptr) atomicOr(p.err, FNB_ERR_SLOT);
-                    lo = hi = 0;
-                }
-                lo = lo < c_begin ? c_begin : lo;
-                hi = hi > c_end ? c_end : hi;
-            }
-            row_lo[r] = int32_t(lo), row_hi[r] = int32_t(hi);
-        }
+    } else {
+        // ---- the workers ----
+        // widening: a thread's item is (cell, 32-dim block); consecutive lanes take consecutive cells, so that the
+        // eight lanes of a 16-byte store phase fall on eight different chunks of the swizzle
+        const bool has_item = tid < kTile * (HD / 32);
+        const int cell = tid & (kTile - 1), blk = tid >> 6;
+        // tensor memory: warps w, w + 4, w + 8, w + 12 share quarter w & 3 (lanes 32 (w & 3) ..); a lane pair is one
+        // query row (even lane: the hi operand / accumulator row, odd lane: the lo row).  Softmax: each of the
+        // quarter's warps takes a quarter of the tile's cells, this thread 8 of the tile's 64 cells of its row.
+        const int quarter = wid & 3, col_q = wid >> 2, part = lane & 1;
+        const int row = 16 * quarter + (lane >> 1);
+        const int col0 = 16 * col_q + 8 * part;  // first cell (of the tile) this thread owns
+        const uint32_t lane_base = uint32_t(32 * quarter) << 16;
 
-        // ---- raw tiles: the tile's cells of this KV head, as they lie in the cache, into stage `st` of the ring by
-        //      16-byte (8-byte for 136-byte cells) asynchronous copies; consecutive threads take consecutive pieces, so
-        //      a warp's copies cover whole cells ----
-        // a thread's pieces are the same in every tile: (tensor, cell of the tile, piece of the cell) worked out once
+        // a thread's pieces of a raw tile are the same in every tile: (cell of the tile, piece of the cell), for K
+        // and for V alike; consecutive threads take consecutive pieces, so a warp's copies cover whole cells
         constexpr int kPiece = L::kCell % 16 == 0 ? 16 : 8;
-        constexpr int kPieces = L::kCell / kPiece;  // pieces of a cell
-        constexpr int kMine = (2 * kTile * kPieces + kThreads - 1) / kThreads;
+        constexpr int kPieces = L::kCell / kPiece;
+        constexpr int kMine = (kTile * kPieces + kThreads - 1) / kThreads;
         int piece_cell[kMine];      // cell of the tile, or -1: no such piece
-        uint32_t piece_src[kMine];  // byte offset from the tile's first cell of this head in the tensor
-        int piece_dst[kMine];       // byte offset in a stage; odd: the piece is V's (offsets are even)
+        uint32_t piece_src[kMine];  // byte offset from the tile's first cell of this head
+        int piece_dst[kMine];       // byte offset in a raw tensor tile
 #pragma unroll
         for (int k = 0; k < kMine; ++k) {
             const int i = tid + k * kThreads;
-            const int tensor = i / (kTile * kPieces), rest = i - tensor * (kTile * kPieces);
-            const int cl = rest / kPieces, piece = rest - cl * kPieces;
-            piece_cell[k] = worker && i < 2 * kTile * kPieces ? cl : -1;
+            const int cl = i / kPieces, piece = i - cl * kPieces;
+            piece_cell[k] = i < kTile * kPieces ? cl : -1;
             piece_src[k] = uint32_t(cl) * uint32_t(p.n_kv) * L::kCell + kPiece * piece;  // < 64 cells x n_kv x 272
-            piece_dst[k] = (tensor * L::kRawTensor + cl * L::kCell + kPiece * piece) | tensor;
+            piece_dst[k] = cl * L::kCell + kPiece * piece;
         }
-        const auto issue = [&](int tile, int st) {
-            uint8_t * base = raw + st * L::kRawStage;
-            const int64_t t0 = c_begin + int64_t(tile) * kTile;
-            const int64_t head_at = (t0 * p.n_kv + head) * L::kCell;
+
+        uint32_t g = 0;
+        for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
+            int head, u;
+            int64_t c_begin, c_end;
+            const int n_tiles = tiles_of(unit, head, u, c_begin, c_end);
+
+            // ---- raw tiles of one tensor into stage `st` of its ring; the stage's barrier hears of this thread's
+            //      copies when they land ----
+            const auto issue = [&](int tile, int st, int tensor) {
+                uint8_t * base = raw + st * L::kRawStage + tensor * L::kRawTensor;
+                const uint8_t * cache = tensor == 0 ? p.k_cache : p.v_cache;
+                const int64_t t0 = c_begin + int64_t(tile) * kTile;
+                const int64_t head_at = (t0 * p.n_kv + head) * L::kCell;
 #pragma unroll
-            for (int k = 0; k < kMine; ++k) {
-                if (piece_cell[k] >= 0) {
-                    const bool valid = t0 + piece_cell[k] < c_end;
-                    const uint8_t * src = ((piece_dst[k] & 1) ? p.v_cache : p.k_cache) + (valid ? head_at + piece_src[k] : 0);
-                    uint8_t * dst = base + (piece_dst[k] & ~1);
-                    if (kPiece == 16) {
-                        cp_async16(dst, src, valid);
-                    } else {
-                        cp_async8(dst, src, valid);
+                for (int k = 0; k < kMine; ++k) {
+                    if (piece_cell[k] >= 0) {
+                        const bool valid = t0 + piece_cell[k] < c_end;
+                        const uint8_t * src = cache + (valid ? head_at + piece_src[k] : 0);
+                        if (kPiece == 16) {
+                            cp_async16(base + piece_dst[k], src, valid);
+                        } else {
+                            cp_async8(base + piece_dst[k], src, valid);
+                        }
                     }
                 }
-            }
-            if (KV8 && worker) {
-                for (int i = tid; i < 2 * kTile; i += kThreads) {
-                    const int tensor = i / kTile, cl = i - tensor * kTile;
-                    const int64_t c = t0 + cl;
+                if (KV8 && tid < kTile) {
+                    const int64_t c = t0 + tid;
                     const bool valid = c < c_end;
                     const uint16_t * src = (tensor == 0 ? p.k_scale : p.v_scale) + ((valid ? c : c_begin) * p.n_kv + head) * (HD / 64);
-                    uint8_t * dst = base + tensor * L::kRawTensor + kTile * L::kCell + cl * 8;
+                    uint8_t * dst = base + kTile * L::kCell + tid * 8;
                     if (HD == 256) {
                         cp_async8(dst, src, valid);
-                    } else {  // two scales a cell: 4 bytes, a plain load
-                        *reinterpret_cast<uint32_t *>(dst) = valid ? __ldg(reinterpret_cast<const uint32_t *>(src)) : 0u;
+                    } else {  // two scales a cell
+                        cp_async4(dst, src, valid);
                     }
                 }
-            }
-            cp_async_commit();
-        };
-        // this thread's item of a staged tensor
-        const auto item_of = [&](raw_item<KV8> & r, int st, int tensor) {
-            const uint8_t * t = raw + st * L::kRawStage + tensor * L::kRawTensor;
-            load_item<HD, KV8>(r, t + cell * L::kCell, t + kTile * L::kCell + cell * 8, blk);
-        };
-        issue(0, 0);
-        cp_async_wait_all();
-        __syncthreads();  // the first tile has landed for every thread
+                cp_async_arrive((tensor == 0 ? raw_k : raw_v) + st);
+            };
+            // this thread's item of a staged tensor, widened into the operand tiles
+            const auto widen = [&](int st, int tensor, uint8_t * t_hi, uint8_t * t_lo) {
+                if (has_item) {
+                    const uint8_t * t = raw + st * L::kRawStage + tensor * L::kRawTensor;
+                    raw_item<KV8> r;
+                    load_item<HD, KV8>(r, t + cell * L::kCell, t + kTile * L::kCell + cell * 8, blk);
+                    widen_item<KV8>(r, cell, blk, t_hi, t_lo);
+                }
+            };
 
-        // this thread's view of its row: the reference point (the same in the row's eight threads) and the sum over
-        // this thread's cells
-        float m_ref = -INFINITY, l_run = 0.0f;
+            // ---- this thread's row: its live cells [lo, hi) within the unit, an empty range for rows past m ----
+            int64_t r_lo = 0, r_hi = 0;
+            if (row < p.m) {
+                const int t = row / p.n_rep;
+                r_lo = p.first_cell != nullptr ? int64_t(__ldg(p.first_cell + t)) : p.range_begin;
+                r_hi = p.n_cells != nullptr ? r_lo + int64_t(__ldg(p.n_cells + t)) : p.range_end;
+                if (r_lo < 0 || r_hi > p.cache_slots || r_hi < r_lo) {
+                    if (p.err != nullptr && col_q == 0 && part == 0) atomicOr(p.err, FNB_ERR_SLOT);
+                    r_lo = r_hi = 0;
+                }
+                r_lo = r_lo < c_begin ? c_begin : r_lo;
+                r_hi = r_hi > c_end ? c_end : r_hi;
+            }
 
-        for (int tile = 0; tile < n_tiles; ++tile, ++it) {
-            // ---- A: K of this tile into its operand tiles (the previous tile's score MMAs are done: every thread
-            //      waited for them before its softmax); the next tile's K into registers ----
-            const int st = tile & 1;
-            if (tile + 1 < n_tiles) issue(tile + 1, st ^ 1);  // its last readers (the tile before this one) are behind a barrier
-            if (has_item) {
-                raw_item<KV8> r;
-                item_of(r, st, 0);
-                widen_item<KV8>(r, cell, blk, k_hi, k_lo);
-            }
-            fence_proxy_async();
-            tc_fence_before();
-            __syncthreads();
-            // ---- B: scores on the tensor core, S = [q_hi; q_lo] . (K_lo + K_hi)^T: the small products first, so
-            //      that only the sixteen K_hi steps round a large accumulator; meanwhile V of this tile ----
-            if (issuer) {
-                tc_fence_after();
-                const uint32_t kh = smem_u32(k_hi), kl = smem_u32(k_lo);
+            // ---- the unit's first tile on its way (both stages are free: the previous unit's last tile was waited
+            //      for by every worker before its partial result) ----
+            issue(0, g & 1, 0);
+            issue(0, g & 1, 1);
+
+            // ---- the group's query rows into tensor memory: lane 2 r the hi part of row r, lane 2 r + 1 the rounded
+            //      residual, rows past m zero; this warp the 64 dims of its column quarter (the previous unit's score
+            //      MMAs are done) ----
+            if (col_q < HD / 64) {
 #pragma unroll
-                for (int kb = 0; kb < L::kBlocks; ++kb) {
+                for (int h = 0; h < 2; ++h) {  // 32 dims = 16 columns at a time
+                    float w[16];
+                    if (row < p.m) {
+                        const int t = row / p.n_rep, rr = row - t * p.n_rep;
+                        const float4 * src = reinterpret_cast<const float4 *>(p.q + (int64_t(t) * p.n_q + head * p.n_rep + rr) * HD +
+                                                                              64 * col_q + 32 * h);
 #pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        umma_f16_ts(tmem_s, tmem_q + 32 * kb + 8 * ks, umma_desc(kl + kb * L::kCBlock + 32 * ks, 16, 1024), kIdescS,
-                                    (kb | ks) != 0);
+                        for (int j = 0; j < 8; ++j) {
+                            const float4 x = __ldg(src + j);
+                            const __half2 a = __floats2half2_rn(x.x, x.y), b = __floats2half2_rn(x.z, x.w);
+                            if (part) {
+                                const float2 fa = __half22float2(a), fb = __half22float2(b);
+                                w[2 * j] = __uint_as_float(h2_bits(__floats2half2_rn(x.x - fa.x, x.y - fa.y)));
+                                w[2 * j + 1] = __uint_as_float(h2_bits(__floats2half2_rn(x.z - fb.x, x.w - fb.y)));
+                            } else {
+                                w[2 * j] = __uint_as_float(h2_bits(a)), w[2 * j + 1] = __uint_as_float(h2_bits(b));
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) w[j] = 0.0f;
                     }
+                    tmem_st16(tmem_q + lane_base + uint32_t(32 * col_q + 16 * h), w);
                 }
-#pragma unroll
-                for (int kb = 0; kb < L::kBlocks; ++kb) {
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        umma_f16_ts(tmem_s, tmem_q + 32 * kb + 8 * ks, umma_desc(kh + kb * L::kCBlock + 32 * ks, 16, 1024), kIdescS, 1);
-                    }
-                }
-                umma_commit(bar_s);
-            }
-            if (worker) {
-            if (it > 0) {  // the previous output MMAs read V and P and wrote O
-                mbar_wait(bar_o, (it - 1) & 1, p.err);
-                tc_fence_after();
-            }
-            if (has_item) {
-                raw_item<KV8> r;
-                item_of(r, st, 1);
-                widen_item<KV8>(r, cell, blk, v_hi, v_lo);
-            }
-            // ---- C: softmax of the tile: every thread 8 cells of one query row ----
-            mbar_wait(bar_s, it & 1, p.err);
-            tc_fence_after();
-            float s[8];
-            {
-                float mine[16];
-                tmem_ld16(tmem_s + lane_base + 16 * col_q, mine);
-                // the pair's other lane holds the row's other part: keep my 8 cells, hand over the other 8
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const float keep = part ? mine[8 + j] : mine[j], give = part ? mine[j] : mine[8 + j];
-                    s[j] = keep + __shfl_xor_sync(kFull, give, 1);
-                }
-            }
-            const int c0 = int(c_begin + int64_t(tile) * kTile) + col0;
-            const int lo = row_lo[row] - c0, hi = row_hi[row] - c0;  // this thread's live cells: lo <= j < hi
-            float mx = -INFINITY;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                s[j] = j >= lo && j < hi ? s[j] * p.scale_log2 : -INFINITY;
-                mx = fmaxf(mx, s[j]);
-            }
-            mx = fmaxf(mx, __shfl_xor_sync(kFull, mx, 1));
-            if (part == 0) part_max[col_q * kMaxM + row] = mx;
-            named_barrier_id(2 + quarter, 128);  // the four warps of this quarter
-            mx = fmaxf(fmaxf(part_max[row], part_max[kMaxM + row]), fmaxf(part_max[2 * kMaxM + row], part_max[3 * kMaxM + row]));
-            // lazy reference point: it moves only when the row's maximum has outgrown it by more than 2^kLazy
-            float a_row = 1.0f;
-            if (mx > m_ref + kLazy || (m_ref == -INFINITY && mx > -INFINITY)) {
-                if (m_ref != -INFINITY) a_row = fast_exp2(m_ref - mx);
-                m_ref = mx;
-            }
-            if (__any_sync(kFull, a_row != 1.0f)) {  // this warp's quarter of the output columns of its lanes' rows
-#pragma unroll 1
-                for (int cb = 0; cb < HD / 128; ++cb) {
-                    float o[32];
-                    const uint32_t at = tmem_o + lane_base + uint32_t(HD / 4 * col_q + 32 * cb);
-                    tmem_ld32(at, o);
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) o[j] *= a_row;
-                    tmem_st32(at, o);
-                }
-            }
-            {
-                // probabilities of this thread's 8 cells as four words each of hi and lo parts (x 2^12)
-                const float ref = m_ref == -INFINITY ? 0.0f : m_ref;
-                float sum = 0.0f;
-                uint32_t hi4[4], lo4[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float p0 = fast_exp2(s[2 * e] - ref), p1 = fast_exp2(s[2 * e + 1] - ref);
-                    sum += p0 + p1;
-                    const float x0 = p0 * kPScale, x1 = p1 * kPScale;
-                    const __half2 hv = __floats2half2_rn(x0, x1);
-                    const float2 back = __half22float2(hv);
-                    hi4[e] = h2_bits(hv);
-                    lo4[e] = h2_bits(__floats2half2_rn(x0 - back.x, x1 - back.y));
-                }
-                l_run = l_run * a_row + sum;
-                // The warp's 16 cells of a row are 8 columns of the row's two operand lanes.  Even lane (the hi lane,
-                // owner of the first 8 cells): P = hi of all 16, alternate P = zeros.  Odd lane (the lo lane, owner of
-                // the last 8): P = lo of all 16, alternate P = hi of all 16.
-                float w_op[8], w_alt[8];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const uint32_t other_hi = __shfl_xor_sync(kFull, hi4[e], 1), other_lo = __shfl_xor_sync(kFull, lo4[e], 1);
-                    w_op[e] = __uint_as_float(part ? other_lo : hi4[e]);
-                    w_op[4 + e] = __uint_as_float(part ? lo4[e] : other_hi);
-                    w_alt[e] = __uint_as_float(part ? other_hi : 0u);
-                    w_alt[4 + e] = __uint_as_float(part ? hi4[e] : 0u);
-                }
-                tmem_st8(tmem_p + lane_base + uint32_t(8 * col_q), w_op);
-                tmem_st8(tmem_alt + lane_base + uint32_t(8 * col_q), w_alt);
                 tmem_wait_st();
             }
-            }  // worker
-            cp_async_wait_all();  // the next tile's cells, asked for a tile ago: the barrier below publishes them
-            fence_proxy_async();
-            tc_fence_before();
-            __syncthreads();
-            // ---- D: outputs on the tensor core.  Lane 2 r: p_hi . V_hi only (four roundings of the large accumulator
-            //      per tile); lane 2 r + 1: p_lo . V_hi + p_hi . V_lo (small) ----
-            if (issuer) {
-                tc_fence_after();
-                const uint32_t vh = smem_u32(v_hi), vl = smem_u32(v_lo);
-#pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {  // 16 cells a step: two groups of eight 128-byte rows, 8 columns of P
-                    umma_f16_ts(tmem_o, tmem_p + 8 * ks, umma_desc(vh + 2048 * ks, L::kCBlock, 1024), kIdescO, (tile | ks) != 0);
-                    umma_f16_ts(tmem_o, tmem_alt + 8 * ks, umma_desc(vl + 2048 * ks, L::kCBlock, 1024), kIdescO, 1);
-                }
-                umma_commit(bar_o);
-            }
-        }
 
-        // ---- the unit's partial result: (reference point, sum, (O[2 r] + O[2 r + 1]) / 2^12) of its rows ----
-        if (worker) {
-            mbar_wait(bar_o, (it - 1) & 1, p.err);
+            // the reference point (the same in the row's eight threads) and the sum over this thread's cells
+            float m_ref = -INFINITY, l_run = 0.0f;
+
+            for (int tile = 0; tile < n_tiles; ++tile, ++g) {
+                const int st = g & 1;
+                // ---- K: the staged cells into the operand tiles; the next tile's K on its way (its stage was last
+                //      read for tile g - 1's K, and every worker was past that when tile g - 1's scores completed) ----
+                tc_wait(raw_k + st, (g >> 1) & 1, gave_up, p.err);
+                if (tile + 1 < n_tiles) issue(tile + 1, st ^ 1, 0);
+                widen(st, 0, k_hi, k_lo);
+                fence_proxy_async();
+                tc_fence_before();
+                mbar_arrive(k_ready);
+                // ---- V, once the previous output MMAs have let go of the operand ----
+                if (g > 0) {
+                    tc_wait(bar_o, (g - 1) & 1, gave_up, p.err);
+                    tc_fence_after();
+                }
+                tc_wait(raw_v + st, (g >> 1) & 1, gave_up, p.err);
+                widen(st, 1, v_hi, v_lo);
+                // ---- softmax of the tile: every thread 8 cells of one query row ----
+                tc_wait(bar_s, g & 1, gave_up, p.err);
+                tc_fence_after();
+                // every worker is past tile g - 1 now: the next tile's V may overwrite that tile's stage
+                if (tile + 1 < n_tiles) issue(tile + 1, st ^ 1, 1);
+                float s[8];
+                {
+                    float mine[16];
+                    tmem_ld16(tmem_s + lane_base + 16 * col_q, mine);
+                    // the pair's other lane holds the row's other part: keep my 8 cells, hand over the other 8
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float keep = part ? mine[8 + j] : mine[j], give = part ? mine[j] : mine[8 + j];
+                        s[j] = keep + __shfl_xor_sync(kFull, give, 1);
+                    }
+                }
+                const int64_t c0 = c_begin + int64_t(tile) * kTile + col0;
+                const int lo = int(r_lo - c0), hi = int(r_hi - c0);  // this thread's live cells: lo <= j < hi
+                float mx = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    s[j] = j >= lo && j < hi ? s[j] * p.scale_log2 : -INFINITY;
+                    mx = fmaxf(mx, s[j]);
+                }
+                mx = fmaxf(mx, __shfl_xor_sync(kFull, mx, 1));
+                if (part == 0) part_max[col_q * kMaxM + row] = mx;
+                named_barrier_id(2 + quarter, 128);  // the four warps of this quarter
+                mx = fmaxf(fmaxf(part_max[row], part_max[kMaxM + row]), fmaxf(part_max[2 * kMaxM + row], part_max[3 * kMaxM + row]));
+                // lazy reference point: it moves only when the row's maximum has outgrown it by more than 2^kLazy
+                float a_row = 1.0f;
+                if (mx > m_ref + kLazy || (m_ref == -INFINITY && mx > -INFINITY)) {
+                    if (m_ref != -INFINITY) a_row = fast_exp2(m_ref - mx);
+                    m_ref = mx;
+                }
+                if (__any_sync(kFull, a_row != 1.0f)) {  // this warp's quarter of the output columns of its lanes' rows
+#pragma unroll 1
+                    for (int cb = 0; cb < HD / 128; ++cb) {
+                        float o[32];
+                        const uint32_t at = tmem_o + lane_base + uint32_t(HD / 4 * col_q + 32 * cb);
+                        tmem_ld32(at, o);
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) o[j] *= a_row;
+                        tmem_st32(at, o);
+                    }
+                }
+                {
+                    // probabilities of this thread's 8 cells as four words each of hi and lo parts (x 2^12)
+                    const float ref = m_ref == -INFINITY ? 0.0f : m_ref;
+                    float sum = 0.0f;
+                    uint32_t hi4[4], lo4[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float p0 = fast_exp2(s[2 * e] - ref), p1 = fast_exp2(s[2 * e + 1] - ref);
+                        sum += p0 + p1;
+                        const float x0 = p0 * kPScale, x1 = p1 * kPScale;
+                        const __half2 hv = __floats2half2_rn(x0, x1);
+                        const float2 back = __half22float2(hv);
+                        hi4[e] = h2_bits(hv);
+                        lo4[e] = h2_bits(__floats2half2_rn(x0 - back.x, x1 - back.y));
+                    }
+                    l_run = l_run * a_row + sum;
+                    // The warp's 16 cells of a row are 8 columns of the row's two operand lanes.  Even lane (the hi lane,
+                    // owner of the first 8 cells): P = hi of all 16, alternate P = zeros.  Odd lane (the lo lane, owner
+                    // of the last 8): P = lo of all 16, alternate P = hi of all 16.
+                    float w_op[8], w_alt[8];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const uint32_t other_hi = __shfl_xor_sync(kFull, hi4[e], 1), other_lo = __shfl_xor_sync(kFull, lo4[e], 1);
+                        w_op[e] = __uint_as_float(part ? other_lo : hi4[e]);
+                        w_op[4 + e] = __uint_as_float(part ? lo4[e] : other_hi);
+                        w_alt[e] = __uint_as_float(part ? other_hi : 0u);
+                        w_alt[4 + e] = __uint_as_float(part ? hi4[e] : 0u);
+                    }
+                    tmem_st8(tmem_p + lane_base + uint32_t(8 * col_q), w_op);
+                    tmem_st8(tmem_alt + lane_base + uint32_t(8 * col_q), w_alt);
+                    tmem_wait_st();
+                }
+                fence_proxy_async();
+                tc_fence_before();
+                mbar_arrive(pv_ready);
+            }
+
+            // ---- the unit's partial result: (reference point, sum, (O[2 r] + O[2 r + 1]) / 2^12) of its rows ----
+            tc_wait(bar_o, (g - 1) & 1, gave_up, p.err);
             tc_fence_after();
             const int64_t slot = int64_t(head) * p.n_units + u;
             float * ml = p.ws_ml + slot * p.m * 2;
@@ -695,6 +742,8 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
                     }
                 }
             }
+            // the sums in part_max are read before any warp of the quarter can write a maximum there: that write
+            // follows the next tile's scores, which need this warp's arrival on k_ready
             tc_fence_before();
         }
     }
