@@ -299,12 +299,15 @@ int32_t fnb_kv_read_f32(const fnb_kv_read_args * args, void * stream);
  * first_cell[t] .. first_cell[t] + n_cells[t] - 1 (device arrays; null: every row attends the whole range); every row's
  * cells must lie inside [range_begin, range_end), a host-known bound from which the split over cells is laid out (cells
  * of the bound outside a row's own range are masked); a row range outside the cache sets FNB_ERR_SLOT and the row
- * attends nothing; a row with no cell gives zeros.  F32 softmax statistics and accumulators; the products run on the
- * tensor cores with every operand split into two FP16 halves (K's integer codes exact, each 32-value block's scale
- * applied in F32), which keeps the reference's bound: max |error| / max |reference| <= 1e-5 per row and head against
- * an FP64 evaluation over the decoded cache (fn/kernels/qsa/qa2_test.cpp:469-520).  Values whose magnitude exceeds
- * FP16's range (65504) are outside the contract.
- * head_dim 128 or 256; rows x (n_q_heads / n_kv_heads) <= 64; q, gate, out, caches 16-byte, scale planes 8-byte aligned.
+ * attends nothing; a row with no cell gives zeros.  F32 softmax statistics; the products run on the 5th-generation
+ * tensor cores (tcgen05.mma, F32 accumulators in tensor memory) with every operand split into two FP16 halves (q into a
+ * rounded value and its rounded residual; K and V = d x code into the rounded product and its exact residual), which
+ * keeps the reference's bound: max |error| / max |reference| <= 1e-5 per row and head against an FP64 evaluation over
+ * the decoded cache (fn/kernels/qsa/qa2_test.cpp:469-520), for ranges of any length.  Values whose magnitude exceeds
+ * FP16's range (65504) are outside the contract, and cache scales d below about 2^-10 lose low bits of d x code to
+ * FP16 subnormals.  A kernel of this call holds all 512 columns of its SMs' tensor memory while it runs.
+ * head_dim 128 or 256; rows x (n_q_heads / n_kv_heads) <= 64; n_kv_heads <= 1024; q, gate, out, caches 16-byte, scale
+ * planes 8-byte aligned.
  * workspace: device memory of at least fnb_attend_workspace_bytes(args) bytes (16-byte aligned), the partial results of
  * the split over cells, folded by a second kernel of the same call; its contents need no initialisation and mean
  * nothing afterwards.  Calls that share a workspace must not overlap on the GPU.  The first call per device and shape
