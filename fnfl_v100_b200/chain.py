@@ -6,7 +6,8 @@
     gate, up --SwiGLU + Q8_1--> activations for the expert down product
 
 Only get_rows -> RMSNorm is truly chained; the tensors a dense product would produce (q, k, v, gate, up) are
-seeded synthetic inputs, because contractions are outside this path.  Five launches per step, no host
+seeded synthetic inputs, because contractions are outside this path.  The chained pair is ONE launch (the decoded row
+stays in registers between the two steps), so a step is four launches: no host
 synchronisation, no allocation after construction, so a step can be captured in a CUDA graph and replayed,
 which is how the reference's prompt path replays its unit graphs.
 
@@ -51,14 +52,17 @@ class ChainConfig:
         glu_rows = self.top_k
         glu = glu_rows * (2 * self.inter * 4 + self.inter // 32 * ops.Q8_1_BLOCK)
         norm = 2 * self.hidden * 4
-        return {"get_rows": row_b + 4 + self.hidden * 4, "rms_norm_attn": norm, "rope_kv": rope,
-                "rms_norm_ffn": norm, "swiglu_q8_1": glu}
+        return {"get_rows_rms_norm": row_b + 4 + 2 * self.hidden * 4, "get_rows": row_b + 4 + self.hidden * 4,
+                "rms_norm_attn": norm, "rope_kv": rope, "rms_norm_ffn": norm, "swiglu_q8_1": glu}
 
 
 class PrefillChain:
-    """Owns every buffer of the chain for one shard; `step()` enqueues the five launches."""
+    """Owns every buffer of the chain for one shard; `step()` enqueues the four launches."""
 
-    STAGES = ("get_rows", "rms_norm_attn", "rope_kv", "rms_norm_ffn", "swiglu_q8_1")
+    # get_rows and the attention norm that reads its rows are one launch (the row stays in registers between them);
+    # the two separately callable stages remain for tests and for tables in other formats
+    STAGES = ("get_rows_rms_norm", "rope_kv", "rms_norm_ffn", "swiglu_q8_1")
+    UNFUSED = ("get_rows", "rms_norm_attn", "rope_kv", "rms_norm_ffn", "swiglu_q8_1")
 
     SHARED = ("table", "w_attn", "w_ffn", "w_q", "w_k")   # replicated on every GPU
 
@@ -104,6 +108,14 @@ class PrefillChain:
         self.err = ops.new_err(dev)
 
     # ---- stages, individually callable so each can be timed alone ----
+    def get_rows_rms_norm(self):
+        if self.cfg.table_fmt != "q4_k":
+            self.get_rows()
+            self.rms_norm_attn()
+            return
+        ops.get_rows_rms_norm("q4_k", self.table, self.ids, self.cfg.hidden, self.w_attn, self.cfg.eps, out=self.hidden,
+                              normed=self.normed_attn, err=self.err)
+
     def get_rows(self):
         ops.get_rows(self.cfg.table_fmt, self.table, self.ids, self.cfg.hidden, out=self.hidden, err=self.err)
 
@@ -126,7 +138,7 @@ class PrefillChain:
         for name in self.STAGES:
             getattr(self, name)()
 
-    launches_per_step = 5
+    launches_per_step = 4
 
     def capture(self) -> torch.cuda.CUDAGraph:
         """Record one step into a CUDA graph (the launchers neither synchronise nor allocate)."""

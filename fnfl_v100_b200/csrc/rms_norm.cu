@@ -12,18 +12,10 @@
 // to keep the same number of bytes in flight.
 // Generic path (any cols that is a multiple of 4): one CTA per row, two passes, the second served by L2.
 #include "common.cuh"
+#include "norm_math.cuh"
 
 namespace fnb {
 namespace {
-
-__device__ __forceinline__ float norm_scale(double sum, int cols, float eps) {
-    // sum / cols; for a power-of-two cols the product with the exact reciprocal is the same double and much cheaper
-    const double m = (cols & (cols - 1)) == 0 ? __dmul_rn(sum, 1.0 / double(cols)) : __ddiv_rn(sum, double(cols));
-    const float mean = __double2float_rn(m);
-    return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
-}
-
-__device__ __forceinline__ double sq_acc(double acc, float v) { return __dadd_rn(acc, double(__fmul_rn(v, v))); }
 
 // V vectors per lane per row, R rows per warp per trip
 template <int V, int R>

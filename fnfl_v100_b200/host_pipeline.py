@@ -2,7 +2,7 @@
 
 A prefill of T tokens is cut into chunks (8192 rows, the reference's prompt chunk: fn/runtime/prefill.cpp
 cuts chunks of at most 8192 rows) and pipelined over three streams - host-to-device copies of chunk c + 1,
-the five kernels of chunk c, device-to-host copies of chunk c - 1 - with two device slots.  Inputs are the
+the chain's kernels of chunk c, device-to-host copies of chunk c - 1 - with two device slots.  Inputs are the
 tensors the kernels consume (ids, positions, q, k, v, gate, up); results returned to the host are what a
 host-side consumer needs: the Q8_1 activations, the appended K/V cells and the error word.
 """
@@ -104,4 +104,4 @@ class HostChunkPipeline:
         cur.wait_stream(self.s_out)
         cur.wait_stream(self.s_in)
 
-    launches_per_step = property(lambda self: 5 * self.n_chunks)
+    launches_per_step = property(lambda self: PrefillChain.launches_per_step * self.n_chunks)

@@ -374,6 +374,37 @@ def get_rows(fmt: str, table: torch.Tensor, ids: torch.Tensor, cols: int, out: t
     return out
 
 
+def get_rows_rms_norm(fmt: str, table: torch.Tensor, ids: torch.Tensor, cols: int, w: torch.Tensor | None, eps: float,
+                      out: torch.Tensor | None = None, normed: torch.Tensor | None = None,
+                      err: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """get_rows and the RMSNorm of each row in one launch (Q4_K tables): returns (rows, normalised rows), the same
+    values as get_rows followed by rms_norm."""
+    if fmt != "q4_k":
+        raise ValueError("get_rows_rms_norm: only Q4_K tables")
+    _dev(table, torch.uint8, "table")
+    _dev(ids, torch.int32, "ids")
+    rb = table_row_bytes(fmt, cols)
+    if table.numel() % rb != 0:
+        raise ValueError("table: size is not a whole number of rows")
+    n_vocab = table.numel() // rb
+    n = ids.numel()
+    if out is None:
+        out = torch.empty((n, cols), dtype=torch.float32, device=table.device)
+    if normed is None:
+        normed = torch.empty((n, cols), dtype=torch.float32, device=table.device)
+    _dev(out, torch.float32, "out")
+    _dev(normed, torch.float32, "normed")
+    _numel(out, n * cols, "out")
+    _numel(normed, n * cols, "normed")
+    if w is not None:
+        _dev(w, torch.float32, "w")
+        _numel(w, cols, "w")
+    _same_device(table, ids, out, normed, w, err)
+    _check(_lib.lib().fnb_get_rows_rms_norm_q4_k(_ptr(table), n_vocab, _ptr(ids), _ptr(w), float(eps), _ptr(out), _ptr(normed),
+                                                 _ptr(err), n, cols, _stream()), "get_rows_rms_norm_q4_k")
+    return out, normed
+
+
 def _embed_args(fmt, table, tok, n_own, own, full, streams, col0, err):
     _dev(table, torch.uint8, "table")
     _dev(tok, torch.int32, "tok")

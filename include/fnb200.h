@@ -198,6 +198,20 @@ float fnb_rope_theta_scale(float freq_base, int32_t n_rot);
  */
 int32_t fnb_get_rows_q4_k(const void * table, int64_t n_vocab, const int32_t * ids, float * out, uint32_t * err,
                           int64_t rows, int32_t cols, void * stream);
+
+/*
+ * fnb_get_rows_q4_k and the RMSNorm of the row in one pass: out[t] = the dequantised row ids[t] (the same bytes
+ * fnb_get_rows_q4_k writes) and normed[t] = (out[t] * scale) * w, scale = 1 / sqrtf(mean(out[t]^2) + eps), the definition
+ * of fnb_rms_norm_f32 (w may be null).  At cols = 2048 the decoded row never leaves the warp's registers between the two
+ * steps, which saves the norm's read of the row (17.5 KB instead of 25.7 KB of traffic a token); other widths run the
+ * two kernels in turn.  out and normed are distinct F32 [rows][cols] buffers, 16-byte aligned; the other arguments are
+ * fnb_get_rows_q4_k's and fnb_rms_norm_f32's.  An id outside [0, n_vocab) sets FNB_ERR_TOKEN and leaves both rows
+ * unwritten (other widths: the normalised row is then formed from whatever out held).
+ * Replaces fn::embed::embed_rows followed by the hidden norm that reads its output (fn/kernels/embed/embed.h:56-87,
+ * fn/kernels/draft/draft_prompt.cu:26-68).
+ */
+int32_t fnb_get_rows_rms_norm_q4_k(const void * table, int64_t n_vocab, const int32_t * ids, const float * w, float eps,
+                                   float * out, float * normed, uint32_t * err, int64_t rows, int32_t cols, void * stream);
 int32_t fnb_get_rows_iq3_xxs(const void * table, int64_t n_vocab, const int32_t * ids, float * out,
                              uint32_t * err, int64_t rows, int32_t cols, void * stream);
 int32_t fnb_get_rows_q8_0(const void * table, int64_t n_vocab, const int32_t * ids, float * out, uint32_t * err,
