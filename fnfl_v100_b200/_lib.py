@@ -86,6 +86,7 @@ SIGNATURES = {
     "fnb_rope_theta_scale": (_F, [_F, _I32]),
     "fnb_get_rows_q4_k": (_I32, [_P, _I64, _P, _P, _P, _I64, _I32, _P]),
     "fnb_get_rows_rms_norm_q4_k": (_I32, [_P, _I64, _P, _P, _F, _P, _P, _P, _I64, _I32, _P]),
+    "fnb_get_rows_rms_norm_iq3_xxs": (_I32, [_P, _I64, _P, _P, _F, _P, _P, _P, _I64, _I32, _P]),
     "fnb_get_rows_iq3_xxs": (_I32, [_P, _I64, _P, _P, _P, _I64, _I32, _P]),
     "fnb_get_rows_q8_0": (_I32, [_P, _I64, _P, _P, _P, _I64, _I32, _P]),
     "fnb_embed_rows": (_I32, [C.POINTER(EmbedArgs), _P]),

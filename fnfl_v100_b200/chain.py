@@ -109,11 +109,11 @@ class PrefillChain:
 
     # ---- stages, individually callable so each can be timed alone ----
     def get_rows_rms_norm(self):
-        if self.cfg.table_fmt != "q4_k":
+        if self.cfg.table_fmt not in ("q4_k", "iq3_xxs"):
             self.get_rows()
             self.rms_norm_attn()
             return
-        ops.get_rows_rms_norm("q4_k", self.table, self.ids, self.cfg.hidden, self.w_attn, self.cfg.eps, out=self.hidden,
+        ops.get_rows_rms_norm(self.cfg.table_fmt, self.table, self.ids, self.cfg.hidden, self.w_attn, self.cfg.eps, out=self.hidden,
                               normed=self.normed_attn, err=self.err)
 
     def get_rows(self):

@@ -374,8 +374,9 @@ __device__ __forceinline__ void iq3_fetch_row(const uint8_t * __restrict__ table
     a = __ldg(p + lane);
     b = lane < kIq3RowBytes / 16 - 32 ? __ldg(p + 32 + lane) : make_uint4(0u, 0u, 0u, 0u);
 }
+// super-block SB of the staged row: this lane's outputs 4 lane .. + 3 (lo) and 128 further on (hi)
 template <int SB>
-__device__ __forceinline__ void iq3_finish_staged(const uint8_t * buf, float * dst, int lane, const uint32_t * s_grid) {
+__device__ __forceinline__ void iq3_values_staged(const uint8_t * buf, int lane, const uint32_t * s_grid, float4 & lo, float4 & hi) {
     const uint8_t * blk = buf + 98 * SB;
     const int o_aux = 66 + 4 * (lane >> 3);
     const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(blk));
@@ -389,9 +390,27 @@ __device__ __forceinline__ void iq3_finish_staged(const uint8_t * buf, float * d
         a0 = uint32_t(h[0]) | (uint32_t(h[1]) << 16);
         a1 = uint32_t(h[8]) | (uint32_t(h[9]) << 16);
     }
+    lo = iq3_decode(d, q0, a0, lane, s_grid);
+    hi = iq3_decode(d, q1, a1, lane, s_grid);  // n = lane + 32: same parity bits
+}
+template <int SB>
+__device__ __forceinline__ void iq3_finish_staged(const uint8_t * buf, float * dst, int lane, const uint32_t * s_grid) {
+    float4 lo, hi;
+    iq3_values_staged<SB>(buf, lane, s_grid, lo, hi);
     float4 * o = reinterpret_cast<float4 *>(dst + 256 * SB) + lane;
-    st_stream(o, iq3_decode(d, q0, a0, lane, s_grid));
-    st_stream(o + 32, iq3_decode(d, q1, a1, lane, s_grid));  // n = lane + 32: same parity bits
+    st_stream(o, lo);
+    st_stream(o + 32, hi);
+}
+// the fused form's share of a super-block: the values kept, written out and their squares added
+template <int SB>
+__device__ __forceinline__ void iq3_keep_staged(const uint8_t * buf, float * dst, int lane, const uint32_t * s_grid, float4 (&lo)[8],
+                                                float4 (&hi)[8], double & acc) {
+    iq3_values_staged<SB>(buf, lane, s_grid, lo[SB], hi[SB]);
+    float4 * o = reinterpret_cast<float4 *>(dst + 256 * SB) + lane;
+    st_stream(o, lo[SB]);
+    st_stream(o + 32, hi[SB]);
+    acc = sq_acc(sq_acc(sq_acc(sq_acc(acc, lo[SB].x), lo[SB].y), lo[SB].z), lo[SB].w);
+    acc = sq_acc(sq_acc(sq_acc(sq_acc(acc, hi[SB].x), hi[SB].y), hi[SB].z), hi[SB].w);
 }
 __global__ void __launch_bounds__(kWarpsPerCta * 32, kStagedCtasPerSm)
     get_rows_iq3_xxs_staged_kernel(const uint8_t * __restrict__ table, int64_t n_vocab, const int32_t * __restrict__ ids,
@@ -445,6 +464,85 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, kStagedCtasPerSm)
             iq3_finish_staged<5>(buf, dst, lane, s_grid);
             iq3_finish_staged<6>(buf, dst, lane, s_grid);
             iq3_finish_staged<7>(buf, dst, lane, s_grid);
+        }
+        __syncwarp();  // every lane is done with the slot before the next row overwrites it
+        id = id_next;
+        id_next = id_after;
+    }
+}
+
+// the IQ3_XXS form of get_rows_norm_q4_k_kernel
+__global__ void __launch_bounds__(kWarpsPerCta * 32, kFusedCtasPerSm)
+    get_rows_norm_iq3_xxs_kernel(const uint8_t * __restrict__ table, int64_t n_vocab, const int32_t * __restrict__ ids,
+                                 const float * __restrict__ w, float eps, float * __restrict__ out, float * __restrict__ normed,
+                                 uint32_t * err, int64_t rows) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ uint32_t s_grid[256];
+    __shared__ __align__(16) uint8_t s_rows[kWarpsPerCta][kIq3RowBytes];
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+        const uint32_t c = c_iq3xxs_grid_packed[i];
+        uint32_t g = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t lvl = (c >> (3 * j)) & 7u;
+            g |= (lvl == 7u ? 62u : 4u + 8u * lvl) << (8 * j);
+        }
+        s_grid[i] = g;
+    }
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = int64_t(blockIdx.x) * kWarpsPerCta + (threadIdx.x >> 5);
+    const int64_t n_warps = int64_t(gridDim.x) * kWarpsPerCta;
+    uint8_t * buf = s_rows[threadIdx.x >> 5];
+    const float4 * w4 = reinterpret_cast<const float4 *>(w);
+    auto valid = [&](int32_t id) { return id >= 0 && id < n_vocab; };
+
+    int32_t id = warp < rows ? __ldg(ids + warp) : -1;
+    int32_t id_next = warp + n_warps < rows ? __ldg(ids + warp + n_warps) : -1;
+    uint4 a = make_uint4(0u, 0u, 0u, 0u), b = a;
+    if (valid(id)) iq3_fetch_row(table, id, lane, a, b);
+    for (int64_t t = warp; t < rows; t += n_warps) {
+        const bool ok = valid(id);
+        if (ok) {
+            reinterpret_cast<uint4 *>(buf)[lane] = a;
+            if (lane < kIq3RowBytes / 16 - 32) reinterpret_cast<uint4 *>(buf)[32 + lane] = b;
+        } else if (lane == 0 && err != nullptr) {
+            atomicOr(err, FNB_ERR_TOKEN);
+        }
+        __syncwarp();
+        const int64_t t2 = t + 2 * n_warps;
+        const int32_t id_after = t2 < rows ? __ldg(ids + t2) : -1;
+        if (valid(id_next)) iq3_fetch_row(table, id_next, lane, a, b);
+        if (ok) {
+            float * dst = out + t * 2048;
+            float4 lo[8], hi[8];
+            double acc = 0.0;
+            iq3_keep_staged<0>(buf, dst, lane, s_grid, lo, hi, acc);
+            iq3_keep_staged<1>(buf, dst, lane, s_grid, lo, hi, acc);
+            iq3_keep_staged<2>(buf, dst, lane, s_grid, lo, hi, acc);
+            iq3_keep_staged<3>(buf, dst, lane, s_grid, lo, hi, acc);
+            iq3_keep_staged<4>(buf, dst, lane, s_grid, lo, hi, acc);
+            iq3_keep_staged<5>(buf, dst, lane, s_grid, lo, hi, acc);
+            iq3_keep_staged<6>(buf, dst, lane, s_grid, lo, hi, acc);
+            iq3_keep_staged<7>(buf, dst, lane, s_grid, lo, hi, acc);
+            const float scale = norm_scale(warp_sum_f64(acc), 2048, eps);
+#pragma unroll
+            for (int sb = 0; sb < 8; ++sb) {
+                const int at = 64 * sb + lane;  // float4 index of lo in the row; hi is 32 further on
+                float4 x = lo[sb], y = hi[sb];
+                x.x = __fmul_rn(x.x, scale), x.y = __fmul_rn(x.y, scale), x.z = __fmul_rn(x.z, scale), x.w = __fmul_rn(x.w, scale);
+                y.x = __fmul_rn(y.x, scale), y.y = __fmul_rn(y.y, scale), y.z = __fmul_rn(y.z, scale), y.w = __fmul_rn(y.w, scale);
+                if (w != nullptr) {
+                    const float4 gx = __ldg(w4 + at), gy = __ldg(w4 + at + 32);
+                    x.x = __fmul_rn(x.x, gx.x), x.y = __fmul_rn(x.y, gx.y), x.z = __fmul_rn(x.z, gx.z), x.w = __fmul_rn(x.w, gx.w);
+                    y.x = __fmul_rn(y.x, gy.x), y.y = __fmul_rn(y.y, gy.y), y.z = __fmul_rn(y.z, gy.z), y.w = __fmul_rn(y.w, gy.w);
+                }
+                float4 * o = reinterpret_cast<float4 *>(normed + t * 2048) + at;
+                st_stream(o, x);
+                st_stream(o + 32, y);
+            }
         }
         __syncwarp();  // every lane is done with the slot before the next row overwrites it
         id = id_next;
@@ -548,6 +646,23 @@ extern "C" int32_t fnb_get_rows_iq3_xxs(const void * table, int64_t n_vocab, con
         get_rows_iq3_xxs_kernel<<<persistent_grid(rows, kStagedGridPerSm), kWarpsPerCta * 32, 0, s>>>(tb, n_vocab, ids, out, err, rows, cols);
     }
     return launch_status();
+}
+
+extern "C" int32_t fnb_get_rows_rms_norm_iq3_xxs(const void * table, int64_t n_vocab, const int32_t * ids, const float * w, float eps,
+                                                 float * out, float * normed, uint32_t * err, int64_t rows, int32_t cols, void * stream) {
+    using namespace fnb;
+    if (!common_ok(table, n_vocab, ids, out, err, rows, cols, 256, 98, 2)) return FNB_REJECTED;
+    if (!ok_ptr(normed, 16) || !ok_opt(w, 16) || !(eps >= 0.0f) || normed == out) return FNB_REJECTED;
+    const cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const uint8_t * tb = static_cast<const uint8_t *>(table);
+    if (cols == 2048) {
+        launch_pdl(get_rows_norm_iq3_xxs_kernel, persistent_grid(rows, kFusedGridPerSm), kWarpsPerCta * 32, 0, s, tb, n_vocab, ids, w,
+                   eps, out, normed, err, rows);
+        return launch_status();
+    }
+    get_rows_iq3_xxs_kernel<<<persistent_grid(rows, kStagedGridPerSm), kWarpsPerCta * 32, 0, s>>>(tb, n_vocab, ids, out, err, rows, cols);
+    if (cudaPeekAtLastError() != cudaSuccess) return FNB_LAUNCH_FAILED;
+    return rms_norm_launch(out, w, eps, normed, rows, cols, s);
 }
 
 extern "C" int32_t fnb_get_rows_q8_0(const void * table, int64_t n_vocab, const int32_t * ids, float * out,

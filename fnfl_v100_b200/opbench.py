@@ -29,7 +29,7 @@ OPS = ("get_rows_q4_k", "get_rows_iq3_xxs", "rms_norm", "rms_norm_heads", "rope_
        "attend_q8_0_b1", "attend_q8_0_b3", "attend_q8_0_b5", "attend_kv8_b1", "attend_kv8_b5",
        # shapes that take the general kernels instead of the tuned ones: 64-wide heads with 32 rotated dims, 4096 columns
        "rope_kv_fallback", "get_rows_q4_k_c4096", "get_rows_iq3_xxs_c4096",
-       "fused_get_rows_rms_norm_q4_k")
+       "fused_get_rows_rms_norm_q4_k", "fused_get_rows_rms_norm_iq3_xxs")
 
 
 def hbm_peak() -> float:
@@ -44,15 +44,16 @@ def hbm_peak() -> float:
 def make_case(op: str, T: int, dev, gen, c: ChainConfig):
     """Returns (launch, algorithmic bytes)."""
     N = synth.torch_normal
-    if op == "fused_get_rows_rms_norm_q4_k":
-        table = synth.torch_table("q4_k", gen, c.n_vocab, c.hidden, dev)
+    if op.startswith("fused_get_rows_rms_norm_"):
+        fmt = op[len("fused_get_rows_rms_norm_"):]
+        table = synth.torch_table(fmt, gen, c.n_vocab, c.hidden, dev)
         ids = torch.randint(0, c.n_vocab, (T,), dtype=torch.int32, device=dev, generator=gen)
         w = 1 + 0.1 * N(gen, (c.hidden,), 1.0, dev)
         out = torch.empty((T, c.hidden), dtype=torch.float32, device=dev)
         normed = torch.empty_like(out)
         err = ops.new_err(dev)
-        return (lambda: ops.get_rows_rms_norm("q4_k", table, ids, c.hidden, w, c.eps, out=out, normed=normed, err=err),
-                T * (ops.table_row_bytes("q4_k", c.hidden) + 4 + 2 * c.hidden * 4) + c.hidden * 4)
+        return (lambda: ops.get_rows_rms_norm(fmt, table, ids, c.hidden, w, c.eps, out=out, normed=normed, err=err),
+                T * (ops.table_row_bytes(fmt, c.hidden) + 4 + 2 * c.hidden * 4) + c.hidden * 4)
     if op.startswith("get_rows"):
         fmt, cols = op[len("get_rows_"):], c.hidden
         if fmt.endswith("_c4096"):

@@ -377,10 +377,10 @@ def get_rows(fmt: str, table: torch.Tensor, ids: torch.Tensor, cols: int, out: t
 def get_rows_rms_norm(fmt: str, table: torch.Tensor, ids: torch.Tensor, cols: int, w: torch.Tensor | None, eps: float,
                       out: torch.Tensor | None = None, normed: torch.Tensor | None = None,
                       err: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
-    """get_rows and the RMSNorm of each row in one launch (Q4_K tables): returns (rows, normalised rows), the same
-    values as get_rows followed by rms_norm."""
-    if fmt != "q4_k":
-        raise ValueError("get_rows_rms_norm: only Q4_K tables")
+    """get_rows and the RMSNorm of each row in one launch (Q4_K and IQ3_XXS tables): returns (rows, normalised rows),
+    the same values as get_rows followed by rms_norm."""
+    if fmt not in ("q4_k", "iq3_xxs"):
+        raise ValueError("get_rows_rms_norm: Q4_K and IQ3_XXS tables")
     _dev(table, torch.uint8, "table")
     _dev(ids, torch.int32, "ids")
     rb = table_row_bytes(fmt, cols)
@@ -400,8 +400,9 @@ def get_rows_rms_norm(fmt: str, table: torch.Tensor, ids: torch.Tensor, cols: in
         _dev(w, torch.float32, "w")
         _numel(w, cols, "w")
     _same_device(table, ids, out, normed, w, err)
-    _check(_lib.lib().fnb_get_rows_rms_norm_q4_k(_ptr(table), n_vocab, _ptr(ids), _ptr(w), float(eps), _ptr(out), _ptr(normed),
-                                                 _ptr(err), n, cols, _stream()), "get_rows_rms_norm_q4_k")
+    fn = getattr(_lib.lib(), "fnb_get_rows_rms_norm_" + fmt)
+    _check(fn(_ptr(table), n_vocab, _ptr(ids), _ptr(w), float(eps), _ptr(out), _ptr(normed), _ptr(err), n, cols, _stream()),
+           "get_rows_rms_norm_" + fmt)
     return out, normed
 
 

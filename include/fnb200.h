@@ -200,7 +200,7 @@ int32_t fnb_get_rows_q4_k(const void * table, int64_t n_vocab, const int32_t * i
                           int64_t rows, int32_t cols, void * stream);
 
 /*
- * fnb_get_rows_q4_k and the RMSNorm of the row in one pass: out[t] = the dequantised row ids[t] (the same bytes
+ * fnb_get_rows_q4_k (or _iq3_xxs) and the RMSNorm of the row in one pass: out[t] = the dequantised row ids[t] (the same bytes
  * fnb_get_rows_q4_k writes) and normed[t] = (out[t] * scale) * w, scale = 1 / sqrtf(mean(out[t]^2) + eps), the definition
  * of fnb_rms_norm_f32 (w may be null).  At cols = 2048 the decoded row never leaves the warp's registers between the two
  * steps, which saves the norm's read of the row (17.5 KB instead of 25.7 KB of traffic a token); other widths run the
@@ -212,6 +212,9 @@ int32_t fnb_get_rows_q4_k(const void * table, int64_t n_vocab, const int32_t * i
  */
 int32_t fnb_get_rows_rms_norm_q4_k(const void * table, int64_t n_vocab, const int32_t * ids, const float * w, float eps,
                                    float * out, float * normed, uint32_t * err, int64_t rows, int32_t cols, void * stream);
+/* the same for an IQ3_XXS table (row bytes a multiple of 2, as fnb_get_rows_iq3_xxs) */
+int32_t fnb_get_rows_rms_norm_iq3_xxs(const void * table, int64_t n_vocab, const int32_t * ids, const float * w, float eps,
+                                      float * out, float * normed, uint32_t * err, int64_t rows, int32_t cols, void * stream);
 int32_t fnb_get_rows_iq3_xxs(const void * table, int64_t n_vocab, const int32_t * ids, float * out,
                              uint32_t * err, int64_t rows, int32_t cols, void * stream);
 int32_t fnb_get_rows_q8_0(const void * table, int64_t n_vocab, const int32_t * ids, float * out, uint32_t * err,

@@ -224,10 +224,15 @@ inline bool embed_rows(const rows_args & a, void * stream) {
     }
     return false;
 }
-// embed_rows and the hidden RMSNorm of each row in one launch (Q4_K tables): normed = (out * scale) * w
+// embed_rows and the hidden RMSNorm of each row in one launch (Q4_K and IQ3_XXS tables): normed = (out * scale) * w
 inline bool embed_rows_norm(const rows_args & a, const float * w, float eps, float * normed, void * stream) {
-    if (a.fmt != table_fmt::q4_k) return false;
-    return fnb_get_rows_rms_norm_q4_k(a.table, a.n_vocab, a.tok, w, eps, a.out, normed, a.err, a.rows, a.cols, stream) == FNB_OK;
+    if (a.fmt == table_fmt::q4_k) {
+        return fnb_get_rows_rms_norm_q4_k(a.table, a.n_vocab, a.tok, w, eps, a.out, normed, a.err, a.rows, a.cols, stream) == FNB_OK;
+    }
+    if (a.fmt == table_fmt::iq3_xxs) {
+        return fnb_get_rows_rms_norm_iq3_xxs(a.table, a.n_vocab, a.tok, w, eps, a.out, normed, a.err, a.rows, a.cols, stream) == FNB_OK;
+    }
+    return false;
 }
 // The reference's own layout (fn::embed::rows_args, fn/kernels/embed/embed.h:70-87): a card's IQ3_S or Q8_0 table of
 // n_own features per token, decoded into own [rows][n_own], the card's columns of full [rows][n_full] and of all

@@ -988,28 +988,29 @@ def test_reference_embedding_layout_two_cards(dev, oracle, fmt, rows):
         assert np.array_equal(bits(streams.numpy()[2:5, 3, :n_own]), bits(src))
 
 
+@pytest.mark.parametrize("fmt", ["q4_k", "iq3_xxs"])
 @pytest.mark.parametrize("rows,cols", [(1, 2048), (37, 2048), (3000, 2048), (65, 1024), (40, 4096)])
-def test_get_rows_rms_norm_is_get_rows_then_rms_norm(dev, oracle, rows, cols):
+def test_get_rows_rms_norm_is_get_rows_then_rms_norm(dev, oracle, fmt, rows, cols):
     """The fused launch against the oracle (rows bit for bit, normalised rows within 2 units in the last place: the
     double sum runs in another order) and against the two stand-alone kernels; a refused id leaves both rows unwritten
     at the fused width."""
     g = synth.rng(77 + rows)
     n_vocab = 5000
-    table = synth.q4_k_table(g, n_vocab, cols)
+    table = {"q4_k": synth.q4_k_table, "iq3_xxs": synth.iq3_xxs_table}[fmt](g, n_vocab, cols)
     ids = g.integers(0, n_vocab, rows).astype(np.int32)
     w = synth.norm_weight(g, cols)
     eps = 1e-6
     d_table, d_ids, d_w = (torch.from_numpy(a).to(dev) for a in (table, ids, w))
     err = ops.new_err(dev)
-    out, normed = ops.get_rows_rms_norm("q4_k", d_table, d_ids, cols, d_w, eps, err=err)
+    out, normed = ops.get_rows_rms_norm(fmt, d_table, d_ids, cols, d_w, eps, err=err)
     torch.cuda.synchronize()
     assert int(err.item()) == 0
-    want_rows, _ = oracle.get_rows("q4_k", table, n_vocab, ids, cols)
+    want_rows, _ = oracle.get_rows(fmt, table, n_vocab, ids, cols)
     want_norm = oracle.rms_norm(want_rows, w, eps)
     assert np.array_equal(out.cpu().numpy().view(np.uint32), want_rows.view(np.uint32))
     got = normed.cpu().numpy()
     assert np.abs(got.view(np.int32).astype(np.int64) - want_norm.view(np.int32)).max() <= 2
-    alone_rows = ops.get_rows("q4_k", d_table, d_ids, cols)
+    alone_rows = ops.get_rows(fmt, d_table, d_ids, cols)
     alone_norm = ops.rms_norm(alone_rows, d_w, eps)
     assert torch.equal(out, alone_rows)
     differing = int((normed.view(torch.int32) != alone_norm.view(torch.int32)).sum())
@@ -1020,7 +1021,7 @@ def test_get_rows_rms_norm_is_get_rows_then_rms_norm(dev, oracle, rows, cols):
         bad[1] = n_vocab
         out2 = torch.full((rows, cols), 7.0, dtype=torch.float32, device=dev)
         norm2 = torch.full((rows, cols), 9.0, dtype=torch.float32, device=dev)
-        ops.get_rows_rms_norm("q4_k", d_table, torch.from_numpy(bad).to(dev), cols, d_w, eps, out=out2, normed=norm2, err=err)
+        ops.get_rows_rms_norm(fmt, d_table, torch.from_numpy(bad).to(dev), cols, d_w, eps, out=out2, normed=norm2, err=err)
         torch.cuda.synchronize()
         assert int(err.item()) == ops.ERR_TOKEN
         assert bool((out2[1] == 7.0).all()) and bool((norm2[1] == 9.0).all())
