@@ -131,8 +131,6 @@ __device__ __forceinline__ void cp_async8(void * dst, const void * src, bool val
 __device__ __forceinline__ void cp_async4(void * dst, const void * src, bool valid) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(valid ? 4 : 0) : "memory");
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -164,14 +162,7 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t leading_b
 __host__ __device__ constexpr uint32_t umma_idesc(int n, bool b_mn_major) {
     return (1u << 4) | (b_mn_major ? (1u << 16) : 0u) | (uint32_t(n >> 3) << 17) | (uint32_t(128 >> 4) << 24);
 }
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// the same with the A operand in tensor memory (one operand row per lane, two FP16 values per column)
+// D (+)= A . B: the A operand in tensor memory (one operand row per lane, two FP16 values per column), B in shared memory
 __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
