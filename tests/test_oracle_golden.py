@@ -6,6 +6,8 @@ import os
 import numpy as np
 import pytest
 
+from fnfl_v100_b200 import synth
+
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
 
@@ -215,3 +217,36 @@ def test_expert_gate_up_rows_match_the_reference_avx2_kernel(oracle):
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
     part = oracle.expert_gu_rows_q4_k(gate, up, act, 2560, r0=7, r1=19)
     assert np.array_equal(part[:, 7:19].view(np.uint32), want[:, 7:19].view(np.uint32)) and not part[:, :7].any()
+
+
+def test_attention_reference_against_numpy_and_the_kv_decoders(oracle):
+    """The FP64 attention the GPU tests hold fnb_attend to, against the same sum written in numpy over cells decoded
+    by the oracle's cache decoders (pinned above to fn::quant::kv_q8_value and ggml's Q8_0 decode): ragged ranges, a
+    row with no cell, the output gate, both cache formats."""
+    g = synth.rng(0xA77)
+    cells, n_kv, n_q, hd, rows = 300, 2, 6, 128, 4
+    q = synth.normal(g, (rows, n_q, hd), 1.5)
+    gate = synth.normal(g, (rows, n_q, hd), 1.0)
+    first = np.array([0, 17, 120, 50], np.int32)
+    count = np.array([300, 100, 0, 250], np.int32)
+    for fmt in ("q8_0", "kv8"):
+        k, v = synth.normal(g, (cells, n_kv, hd)), synth.normal(g, (cells, n_kv, hd))
+        if fmt == "q8_0":
+            kf = oracle.dequantize_q8_0(oracle.quantize_q8_0(k)).reshape(k.shape)
+            vf = oracle.dequantize_q8_0(oracle.quantize_q8_0(v)).reshape(v.shape)
+        else:
+            kf = oracle.kv8_dequantize(*oracle.kv8_quantize(k)).reshape(k.shape)
+            vf = oracle.kv8_dequantize(*oracle.kv8_quantize(v)).reshape(v.shape)
+        got = oracle.attend_f64(q, kf, vf, first, count, hd ** -0.5, gate=gate)
+        want = np.zeros((rows, n_q, hd))
+        for t in range(rows):
+            lo, hi = int(first[t]), int(first[t] + count[t])
+            if hi == lo:
+                continue
+            for h in range(n_q):
+                kk, vv = kf[lo:hi, h // (n_q // n_kv)].astype(np.float64), vf[lo:hi, h // (n_q // n_kv)].astype(np.float64)
+                s = kk @ q[t, h].astype(np.float64) * hd ** -0.5
+                p = np.exp(s - s.max())
+                want[t, h] = (p / p.sum()) @ vv / (1.0 + np.exp(-np.float64(gate[t, h])))
+        assert not got[2].any()
+        assert np.abs(got - want).max() <= 1e-12 * max(1.0, np.abs(want).max())
