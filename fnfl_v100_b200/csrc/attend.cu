@@ -100,7 +100,12 @@ inline attend_plan make_plan(int rows, int n_q, int n_kv, int64_t range) {
     p.slots = int64_t(n_kv) * p.n_units * p.parts;
     return p;
 }
-inline size_t plan_bytes(const attend_plan & p, int head_dim) { return size_t(p.slots) * p.m * (head_dim + 2) * 4; }
+// workspace: (reference point, sum) pairs, padded to 16 bytes so that the outputs behind them take 128-bit stores, then
+// the outputs
+inline size_t plan_ml_floats(const attend_plan & p) { return (size_t(p.slots) * p.m * 2 + 3) / 4 * 4; }
+inline size_t plan_bytes(const attend_plan & p, int head_dim) {
+    return (plan_ml_floats(p) + size_t(p.slots) * p.m * head_dim) * 4;
+}
 
 struct attend_params {
     const float * q;
@@ -869,7 +874,7 @@ int32_t attend_launch(const fnb_attend_args * a, void * ws, size_t ws_bytes, cud
     p.k_scale = a->k_scale, p.v_scale = a->v_scale, p.first_cell = a->first_cell, p.n_cells = a->n_cells;
     p.out = a->out, p.err = a->err;
     p.ws_ml = static_cast<float *>(ws);
-    p.ws_acc = p.ws_ml + plan.slots * plan.m * 2;
+    p.ws_acc = p.ws_ml + plan_ml_floats(plan);
     p.cache_slots = a->cache_slots, p.range_begin = a->range_begin, p.range_end = a->range_end, p.unit_cells = plan.unit_cells;
     p.rows = a->rows, p.n_q = a->n_q_heads, p.n_kv = a->n_kv_heads, p.n_rep = a->n_q_heads / a->n_kv_heads;
     p.m = plan.m, p.parts = plan.parts, p.n_units = plan.n_units;

@@ -159,3 +159,33 @@ def test_attend_over_the_cells_the_append_wrote(dev, oracle):
     vf = oracle.dequantize_q8_0(vc.cpu().numpy()[:total]).reshape(total, n_kv, hd)
     ref = oracle.attend_f64(q_out[hist:].cpu().numpy(), kf, vf, first, count, hd ** -0.5)
     check(out.cpu().numpy(), ref, "causal rows over appended cells")
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_attend_random_shapes(dev, oracle, seed):
+    """Shapes and ranges drawn at random: both formats and head widths, 1 to 5 rows, 1 to 4 KV heads, groups of up to 64
+    query rows, ranges from a single cell to a few thousand that start and end anywhere, with and without the gate."""
+    g = synth.rng(1000 + seed)
+    fmt = ("q8_0", "kv8")[int(g.integers(0, 2))]
+    hd = (128, 256)[int(g.integers(0, 2))]
+    rows = int(g.integers(1, 6))
+    n_kv = int(g.integers(1, 5))
+    n_rep = int(g.integers(1, 64 // rows + 1))
+    n_q = n_kv * n_rep
+    cells = int(g.integers(1, 5000))
+    lo = int(g.integers(0, cells))
+    hi = int(g.integers(lo + 1, cells + 1))
+    planes, kf, vf = make_cache(oracle, g, cells, n_kv, hd, fmt)
+    q = synth.normal(g, (rows, n_q, hd), float(g.uniform(0.5, 2.5)))
+    first = g.integers(lo, hi, rows).astype(np.int32)
+    count = np.array([int(g.integers(0, hi - f + 1)) for f in first], np.int32)
+    gate = synth.normal(g, (rows, n_q, hd), 1.0) if g.integers(0, 2) else None
+    d = [None if p is None else to_dev(p, dev) for p in planes]
+    err = ops.new_err(dev)
+    out = ops.attend(to_dev(q, dev), d[0], d[1], k_scale=d[2], v_scale=d[3], range_begin=lo, range_end=hi,
+                     first_cell=to_dev(first, dev), n_cells=to_dev(count, dev),
+                     gate=None if gate is None else to_dev(gate, dev), err=err)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    ref = oracle.attend_f64(q, kf, vf, first, count, hd ** -0.5, gate=gate)
+    check(out.cpu().numpy(), ref, "%s hd %d rows %d heads %d/%d range [%d, %d)" % (fmt, hd, rows, n_q, n_kv, lo, hi))
