@@ -161,7 +161,7 @@ def test_attend_over_the_cells_the_append_wrote(dev, oracle):
     check(out.cpu().numpy(), ref, "causal rows over appended cells")
 
 
-@pytest.mark.parametrize("seed", range(12))
+@pytest.mark.parametrize("seed", range(32))
 def test_attend_random_shapes(dev, oracle, seed):
     """Shapes and ranges drawn at random: both formats and head widths, 1 to 5 rows, 1 to 4 KV heads, groups of up to 64
     query rows, ranges from a single cell to a few thousand that start and end anywhere, with and without the gate."""
