@@ -487,6 +487,9 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
         const int row = 16 * quarter + (lane >> 1);
         const int col0 = 16 * col_q + 8 * part;  // first cell (of the tile) this thread owns
         const uint32_t lane_base = uint32_t(32 * quarter) << 16;
+        // a quarter holds 16 query rows: one with no live row (rows past m) has no softmax to run; its probability
+        // lanes are zeroed once per unit and its warps only stage and widen
+        const bool quarter_live = 16 * quarter < p.m;
 
         // a thread's pieces of a raw tile are the same in every tile: (cell of the tile, piece of the cell), for K
         // and for V alike; consecutive threads take consecutive pieces, so a warp's copies cover whole cells
@@ -603,6 +606,12 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
                 }
                 tmem_wait_st();
             }
+            if (!quarter_live) {  // the previous unit's output MMAs, the last readers of P, were waited for
+                float z[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+                tmem_st8(tmem_p + lane_base + uint32_t(8 * col_q), z);
+                tmem_st8(tmem_alt + lane_base + uint32_t(8 * col_q), z);
+                tmem_wait_st();
+            }
 
             // the reference point (the same in the row's eight threads) and the sum over this thread's cells
             float m_ref = -INFINITY, l_run = 0.0f;
@@ -629,6 +638,7 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
                 tc_fence_after();
                 // every worker is past tile g - 1 now: the next tile's V may overwrite that tile's stage
                 if (tile + 1 < n_tiles) issue(tile + 1, st ^ 1, 1);
+                if (quarter_live) {
                 float s[8];
                 {
                     float mine[16];
@@ -701,6 +711,7 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
                     tmem_st8(tmem_alt + lane_base + uint32_t(8 * col_q), w_alt);
                     tmem_wait_st();
                 }
+                }
                 fence_proxy_async();
                 tc_fence_before();
                 mbar_arrive(pv_ready);
@@ -709,6 +720,7 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
             // ---- the unit's partial result: (reference point, sum, (O[2 r] + O[2 r + 1]) / 2^12) of its rows ----
             tc_wait(bar_o, (g - 1) & 1, gave_up, p.err);
             tc_fence_after();
+            if (quarter_live) {
             const int64_t slot = int64_t(head) * p.n_units + u;
             float * ml = p.ws_ml + slot * p.m * 2;
             float * acc = p.ws_acc + slot * p.m * HD;
@@ -737,6 +749,7 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
                                       : make_float4(o[b] * kPUnscale, o[b + 1] * kPUnscale, o[b + 2] * kPUnscale, o[b + 3] * kPUnscale);
                     }
                 }
+            }
             }
             // the sums in part_max are read before any warp of the quarter can write a maximum there: that write
             // follows the next tile's scores, which need this warp's arrival on k_ready
