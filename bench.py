@@ -300,7 +300,8 @@ def op_report(ms: list, nbytes: int, peak: float) -> dict:
 
 def extra_configs(dev, k: int, peak: float, rest_s: float) -> dict:
     """The stated configurations the chain does not run at their own sizes, each replayed from graphs: cold (instances
-    rotated so that more bytes than L2 holds pass between two replays of one instance) and hot (one instance)."""
+    rotated so that more bytes than L2 holds pass between two replays of one instance) and hot (one instance), with
+    one graph per launch and, `*_in_stream`, with the launches following one another inside one graph."""
     import torch
     from fnfl_v100_b200 import ops, synth
     from fnfl_v100_b200.chain import ChainConfig
@@ -317,6 +318,20 @@ def extra_configs(dev, k: int, peak: float, rest_s: float) -> dict:
         time.sleep(rest_s)
         r = {"cold": op_report(time_replays(graphs, k), nbytes, peak), "hot": op_report(time_replays(graphs[:1], k), nbytes, peak),
              "instances_rotated": n_inst, "what": note}
+        # the same launches as their caller issues them: one after the other in a stream (here: one graph of two
+        # rounds over the instances), so that a launch's start-up overlaps its predecessor's end
+        per = 2 * n_inst
+
+        def in_stream(one: bool):
+            def run():
+                for j in range(per):
+                    fns[0 if one else j % n_inst]()
+            return run
+        for key, one in (("cold_in_stream", False), ("hot_in_stream", True)):
+            g = capture(in_stream(one))
+            r[key] = op_report([t / per for t in time_replays([g], k)], nbytes, peak)
+            del g
+        r["launches_per_in_stream_graph"] = per
         out[name] = r
 
     seed = synth.SEED_BASE

@@ -1026,3 +1026,91 @@ def test_get_rows_rms_norm_is_get_rows_then_rms_norm(dev, oracle, fmt, rows, col
         assert int(err.item()) == ops.ERR_TOKEN
         assert bool((out2[1] == 7.0).all()) and bool((norm2[1] == 9.0).all())
         assert torch.equal(out2[0], out[0]) and torch.equal(norm2[2], normed[2])
+
+
+# ---- the four launches of the path at shapes drawn at random ------------------------------------------------------------
+
+@pytest.mark.parametrize("seed", range(16))
+def test_hot_path_random_shapes(dev, oracle, seed):
+    """Each seed draws its own shape for every kernel of the path (ragged row counts, widths from one block up, head
+    counts and rotary widths that are no power of two) and holds it to the same bar as the fixed cases above."""
+    g = synth.rng(1000 + seed)
+    D = lambda a: None if a is None else to_dev(a, dev)  # noqa: E731
+
+    # RMSNorm
+    rows, cols = int(g.integers(1, 700)), 4 * int(g.integers(1, 1200))
+    x, w = synth.normal(g, (rows, cols)), synth.norm_weight(g, cols)
+    out = Guarded((rows, cols), torch.float32, dev)
+    ops.rms_norm(D(x), D(w), 1e-6, out=out.live)
+    torch.cuda.synchronize()
+    out.check_guards()
+    d = ulp_diff(out.numpy(), oracle.rms_norm(x, w, 1e-6))
+    assert d.max() <= 2, f"rms_norm {rows} x {cols}: max ulp {d.max()}"
+
+    # SwiGLU + Q8_1
+    rows, cols = int(g.integers(1, 900)), 32 * int(g.integers(1, 40))
+    gate, up = synth.normal(g, (rows, cols), 2.0), synth.normal(g, (rows, cols), 0.5)
+    q = Guarded((rows, cols // 32 * 36), torch.uint8, dev)
+    f32 = Guarded((rows, cols), torch.float32, dev)
+    ops.swiglu_q8_1(D(gate), D(up), out=q.live, out_f32=f32.live)
+    torch.cuda.synchronize()
+    q.check_guards()
+    f32.check_guards()
+    want, want_f32 = oracle.swiglu_q8_1(gate, up, want_f32=True)
+    assert np.array_equal(bits(f32.numpy()), bits(want_f32)), f"swiglu {rows} x {cols}"
+    assert np.array_equal(q.numpy(), want), f"swiglu {rows} x {cols}"
+
+    # head norm + RoPE + Q8_0 append
+    hd = int(g.choice([64, 128, 256]))
+    rows, nq, nkv = int(g.integers(1, 300)), int(g.integers(1, 21)), int(g.integers(1, 5))
+    n_rot = 2 * (hd // 32) * int(g.integers(0, 16 + 1))
+    norm = bool(g.integers(0, 2))
+    qx, kx, vx, wq, wk = _rope_case(g, rows, nq, nkv, hd, norm)
+    slots_total = 1024
+    pos = synth.positions(g, rows)
+    slot = (g.permutation(slots_total - 8)[:rows] + 4).astype(np.int32)
+    ts = oracle.theta_scale(1e7, max(n_rot, 2))
+    cell = hd // 32 * 34
+    kc = Guarded((slots_total, nkv, cell), torch.uint8, dev)
+    vc = Guarded((slots_total, nkv, cell), torch.uint8, dev)
+    qo = Guarded((rows, nq, hd), torch.float32, dev)
+    err = ops.new_err(dev)
+    ops.rope_neox_q8_0_append(D(qx), D(kx), D(vx), D(pos), n_rot=n_rot, theta_scale=ts, k_cache=kc.live, v_cache=vc.live,
+                              slots=D(slot), q_norm_w=D(wq), k_norm_w=D(wk), q_out=qo.live, err=err)
+    torch.cuda.synchronize()
+    wkc = np.full((slots_total, nkv, cell), POISON, np.uint8)
+    wvc = wkc.copy()
+    want_q, _, werr = oracle.rope_kv_append(qx, kx, vx, pos, n_rot=n_rot, theta_scale=ts, k_cache=wkc, v_cache=wvc,
+                                            cache_slots=slots_total, slots=slot, q_norm_w=wq, k_norm_w=wk)
+    what = f"rope rows {rows} heads {nq}+{nkv} x {hd} n_rot {n_rot} norm {norm}"
+    assert int(err.item()) == werr == 0, what
+    for o in (kc, vc, qo):
+        o.check_guards()
+    if norm:
+        assert ulp_diff(qo.numpy(), want_q).max() <= 2, what
+    else:
+        assert np.array_equal(bits(qo.numpy()), bits(want_q)), what
+    assert np.array_equal(vc.numpy(), wvc), what
+    assert int((kc.numpy() != wkc).sum()) == 0, what
+
+    # get_rows, alone and with the norm
+    for fmt in ("q4_k", "iq3_xxs"):
+        rows, cols, vocab = int(g.integers(1, 500)), 256 * int(g.integers(1, 17)), int(g.integers(1, 300))
+        table = {"q4_k": synth.q4_k_table, "iq3_xxs": synth.iq3_xxs_table}[fmt](g, vocab, cols)
+        ids = g.integers(0, vocab, rows).astype(np.int32)
+        w = synth.norm_weight(g, cols)
+        out = Guarded((rows, cols), torch.float32, dev)
+        ops.get_rows(fmt, D(table), D(ids), cols, out=out.live, err=err)
+        torch.cuda.synchronize()
+        out.check_guards()
+        want_rows, werr = oracle.get_rows(fmt, table, vocab, ids, cols)
+        what = f"get_rows {fmt} {rows} x {cols} of {vocab}"
+        assert int(err.item()) == werr == 0, what
+        assert np.array_equal(bits(out.numpy()), bits(want_rows)), what
+        out2, normed = Guarded((rows, cols), torch.float32, dev), Guarded((rows, cols), torch.float32, dev)
+        ops.get_rows_rms_norm(fmt, D(table), D(ids), cols, D(w), 1e-6, out=out2.live, normed=normed.live, err=err)
+        torch.cuda.synchronize()
+        out2.check_guards()
+        normed.check_guards()
+        assert np.array_equal(bits(out2.numpy()), bits(want_rows)), what
+        assert ulp_diff(normed.numpy(), oracle.rms_norm(want_rows, w, 1e-6)).max() <= 2, what
