@@ -36,6 +36,7 @@ def selftest_lib():
     lib = C.CDLL(native_build.build_selftest())
     P, U64 = C.c_void_p, C.c_uint64
     lib.fnbt_selftest_glu_math.argtypes, lib.fnbt_selftest_glu_math.restype = [U64, U64, P, P], C.c_int32
+    lib.fnbt_selftest_q8_rule.argtypes, lib.fnbt_selftest_q8_rule.restype = [P, P], C.c_int32
     lib.fnbt_selftest_kv8_math.argtypes, lib.fnbt_selftest_kv8_math.restype = [U64, U64, P, P], C.c_int32
     lib.fnbt_selftest_expf.argtypes, lib.fnbt_selftest_expf.restype = [P, P], C.c_int32
     return lib

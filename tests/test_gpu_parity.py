@@ -878,6 +878,17 @@ def test_glu_fast_path_equals_generic_path_on_its_whole_domain(dev, selftest_lib
     assert int(bad.item()) == 0
 
 
+def test_q8_rule_divisions_written_out_equal_ieee_division_for_every_amax(dev, selftest_lib):
+    """Every non-negative float as a block's amax (and infinity, and NaNs): d and id of the Q8_0 / Q8_1 rule as the
+    kernels compute them are the bits of amax / 127 and 1 / d."""
+    import ctypes as C
+    bad = torch.zeros(1, dtype=torch.int64, device=dev)
+    st = selftest_lib.fnbt_selftest_q8_rule(C.c_void_p(bad.data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert st == 0
+    torch.cuda.synchronize()
+    assert int(bad.item()) == 0
+
+
 def test_fused_expf_equals_the_definition_for_every_float(dev, selftest_lib):
     """All 2 x 0x42b00000 floats |x| < 88: the 8-operation evaluation rounds to the same float as the 12-operation one."""
     import ctypes as C
