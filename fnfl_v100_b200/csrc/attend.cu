@@ -40,8 +40,11 @@
 //     consecutive threads copy consecutive pieces, so that the copies cover whole cache lines (a thread reading its
 //     own cell straight from the cache touched 32 lines per warp instruction and kept the L1 pipe busy 80 % of the time).
 //   * Sixteen worker warps and one that only issues the MMAs; completion comes back through mbarriers
-//     (tcgen05.commit).  While the score MMAs of a tile run, the workers widen its V; while the output MMAs run, they
-//     widen the next tile's K.  Softmax: warps w, w + 4, w + 8, w + 12 share tensor-memory quarter w & 3 and take a
+//     (tcgen05.commit).  A worker's tile: read the tile's scores into registers; widen the NEXT tile's K (its operand
+//     is free, and with S read the next scores can run at once); then this tile's softmax and its V.  The issuer sends
+//     the next tile's scores before this tile's outputs, so both products run under the workers' arithmetic (a
+//     timeline of one CTA showed the old order - K, V, softmax, each tile's scores waited for - spending a third of a
+//     tile waiting on the score MMAs).  Softmax: warps w, w + 4, w + 8, w + 12 share tensor-memory quarter w & 3 and take a
 //     quarter of the tile's cells each; a lane pair is one query row (hi lane, lo lane), a thread 8 cells of it.  The
 //     row maximum crosses the quarter's four warps through shared memory and a 128-thread barrier.  The maximum is
 //     lazy: the reference point moves only when a row's maximum has outgrown it by more than 2^3, and only then are the
@@ -276,8 +279,8 @@ struct tc_layout {
     static constexpr int v_hi = k_lo + kBlocks * kCBlock;
     static constexpr int v_lo = v_hi + kBlocks * kCBlock;
     static constexpr int raw = v_lo + kBlocks * kCBlock;      // [2 stages][K raw | V raw]: the cells as they lie in the cache
-    static constexpr int part_max = raw + 2 * kRawStage;      // float [4][64]: a row's maximum over each quarter of a tile
-    static constexpr int bars = part_max + 4 * kMaxM * 4;     // eight mbarriers
+    static constexpr int part_max = raw + 2 * kRawStage;      // float [2][4][64]: a row's maximum over each quarter of a tile, by tile parity
+    static constexpr int bars = part_max + 2 * 4 * kMaxM * 4; // eight mbarriers
     static constexpr int misc = bars + 64;                    // tensor-memory base, the give-up flag
     static constexpr int total = misc + 16 + 1024;            // + slack to align the base to 1024 bytes
     // tensor-memory columns: scores | outputs | stacked query rows | stacked probabilities | the alternate probabilities
@@ -376,13 +379,15 @@ __device__ __forceinline__ void cp_async_arrive(uint64_t * bar) {
 // in the tile loop is a block-wide barrier: every hand-over is an mbarrier, so warps drift apart by as much as the
 // data allows and widening, softmax and tensor work overlap.
 //   raw_k[2], raw_v[2]  (512 arrivals)  a stage of the raw ring has landed: each worker's copies arrive on completion
-//   k_ready             (512)           every worker has widened its share of K (and, on a unit's first tile, stored
-//                                       its share of the query operand): the issuer starts the score MMAs
-//   bar_s               (commit)        the score MMAs are done: S readable, the K operand and - because k_ready
-//                                       needed every worker - every worker's reads of the PREVIOUS tile are done
-//   pv_ready            (512)           every worker has widened its share of V and stored its probabilities
+//   k_ready             (512)           every worker has widened its share of a tile's K - on a unit's first tile after
+//                                       storing its share of the query operand, on the others after reading the
+//                                       previous tile's scores: the issuer starts the tile's score MMAs
+//   bar_s               (commit)        the score MMAs are done: S readable, the K operand free and - because k_ready
+//                                       needed every worker - its raw stage read by all
+//   pv_ready            (512)           every worker has stored its probabilities and widened its share of V
 //   bar_o               (commit)        the output MMAs are done: O, P and the V operand are free
-// Tile g (counted over the CTA's units) uses stage g & 1 of both rings and phase g of the four tile barriers.
+// Tile g (counted over the CTA's units) uses stage g & 1 of both rings and phase g of the four tile barriers.  Within a
+// unit K runs a tile ahead: tile g + 1's K is widened, and its scores issued, during tile g.
 template <int HD, bool KV8>
 __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_params p) {
     using L = tc_layout<HD, KV8>;
@@ -445,9 +450,7 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
                 int head, u;
                 int64_t c_begin, c_end;
                 const int n_tiles = tiles_of(unit, head, u, c_begin, c_end);
-                for (int tile = 0; tile < n_tiles; ++tile, ++g) {
-                    tc_wait(k_ready, g & 1, gave_up, p.err);
-                    tc_fence_after();
+                const auto scores = [&]() {
 #pragma unroll
                     for (int kb = 0; kb < L::kBlocks; ++kb) {
 #pragma unroll
@@ -463,6 +466,18 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
                         }
                     }
                     umma_commit(bar_s);
+                };
+                // the unit's first scores; then, tile by tile, the NEXT tile's scores before this tile's outputs: the
+                // workers widen the next K as soon as they have read this tile's scores, and only then run its softmax
+                tc_wait(k_ready, g & 1, gave_up, p.err);
+                tc_fence_after();
+                scores();
+                for (int tile = 0; tile < n_tiles; ++tile, ++g) {
+                    if (tile + 1 < n_tiles) {
+                        tc_wait(k_ready, (g + 1) & 1, gave_up, p.err);
+                        tc_fence_after();
+                        scores();
+                    }
                     tc_wait(pv_ready, g & 1, gave_up, p.err);
                     tc_fence_after();
 #pragma unroll
@@ -574,6 +589,7 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
             //      for by every worker before its partial result) ----
             issue(0, g & 1, 0);
             issue(0, g & 1, 1);
+            if (n_tiles > 1) issue(1, (g & 1) ^ 1, 0);
 
             // ---- the group's query rows into tensor memory: lane 2 r the hi part of row r, lane 2 r + 1 the rounded
             //      residual, rows past m zero; this warp the 64 dims of its column quarter (the previous unit's score
@@ -616,31 +632,21 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
             // the reference point (the same in the row's eight threads) and the sum over this thread's cells
             float m_ref = -INFINITY, l_run = 0.0f;
 
+            // ---- K of the unit's first tile (the operand is free: the previous unit's last scores were read by all) ----
+            tc_wait(raw_k + (g & 1), (g >> 1) & 1, gave_up, p.err);
+            widen(g & 1, 0, k_hi, k_lo);
+            fence_proxy_async();
+            tc_fence_before();
+            mbar_arrive(k_ready);
+
             for (int tile = 0; tile < n_tiles; ++tile, ++g) {
                 const int st = g & 1;
-                // ---- K: the staged cells into the operand tiles; the next tile's K on its way (its stage was last
-                //      read for tile g - 1's K, and every worker was past that when tile g - 1's scores completed) ----
-                tc_wait(raw_k + st, (g >> 1) & 1, gave_up, p.err);
-                if (tile + 1 < n_tiles) issue(tile + 1, st ^ 1, 0);
-                widen(st, 0, k_hi, k_lo);
-                fence_proxy_async();
-                tc_fence_before();
-                mbar_arrive(k_ready);
-                // ---- V, once the previous output MMAs have let go of the operand ----
-                if (g > 0) {
-                    tc_wait(bar_o, (g - 1) & 1, gave_up, p.err);
-                    tc_fence_after();
-                }
-                tc_wait(raw_v + st, (g >> 1) & 1, gave_up, p.err);
-                widen(st, 1, v_hi, v_lo);
-                // ---- softmax of the tile: every thread 8 cells of one query row ----
+                float * pm = part_max + st * (4 * kMaxM);  // by tile parity: a warp a tile ahead writes the other half
+                // ---- the tile's scores into registers: every thread 8 cells of one query row ----
                 tc_wait(bar_s, g & 1, gave_up, p.err);
                 tc_fence_after();
-                // every worker is past tile g - 1 now: the next tile's V may overwrite that tile's stage
-                if (tile + 1 < n_tiles) issue(tile + 1, st ^ 1, 1);
-                if (quarter_live) {
                 float s[8];
-                {
+                if (quarter_live) {
                     float mine[16];
                     tmem_ld16(tmem_s + lane_base + 16 * col_q, mine);
                     // the pair's other lane holds the row's other part: keep my 8 cells, hand over the other 8
@@ -650,6 +656,19 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
                         s[j] = keep + __shfl_xor_sync(kFull, give, 1);
                     }
                 }
+                // ---- K of the NEXT tile: the operand is free (this tile's scores are done) and S has been read, so the
+                //      next scores can run under this tile's softmax.  The raw K after that takes this tile's stage,
+                //      which every worker read before the scores just waited for could be issued ----
+                if (tile + 1 < n_tiles) {
+                    tc_wait(raw_k + (st ^ 1), ((g + 1) >> 1) & 1, gave_up, p.err);
+                    if (tile + 2 < n_tiles) issue(tile + 2, st, 0);
+                    widen(st ^ 1, 0, k_hi, k_lo);
+                    fence_proxy_async();
+                    tc_fence_before();
+                    mbar_arrive(k_ready);
+                }
+                float a_row = 1.0f;
+                if (quarter_live) {
                 const int64_t c0 = c_begin + int64_t(tile) * kTile + col0;
                 const int lo = int(r_lo - c0), hi = int(r_hi - c0);  // this thread's live cells: lo <= j < hi
                 float mx = -INFINITY;
@@ -659,15 +678,22 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
                     mx = fmaxf(mx, s[j]);
                 }
                 mx = fmaxf(mx, __shfl_xor_sync(kFull, mx, 1));
-                if (part == 0) part_max[col_q * kMaxM + row] = mx;
+                if (part == 0) pm[col_q * kMaxM + row] = mx;
                 named_barrier_id(2 + quarter, 128);  // the four warps of this quarter
-                mx = fmaxf(fmaxf(part_max[row], part_max[kMaxM + row]), fmaxf(part_max[2 * kMaxM + row], part_max[3 * kMaxM + row]));
+                mx = fmaxf(fmaxf(pm[row], pm[kMaxM + row]), fmaxf(pm[2 * kMaxM + row], pm[3 * kMaxM + row]));
                 // lazy reference point: it moves only when the row's maximum has outgrown it by more than 2^kLazy
-                float a_row = 1.0f;
                 if (mx > m_ref + kLazy || (m_ref == -INFINITY && mx > -INFINITY)) {
                     if (m_ref != -INFINITY) a_row = fast_exp2(m_ref - mx);
                     m_ref = mx;
                 }
+                }
+                // ---- the previous tile's output MMAs: after them O may be rescaled, P overwritten and the V operand
+                //      refilled ----
+                if (g > 0) {
+                    tc_wait(bar_o, (g - 1) & 1, gave_up, p.err);
+                    tc_fence_after();
+                }
+                if (quarter_live) {
                 if (__any_sync(kFull, a_row != 1.0f)) {  // this warp's quarter of the output columns of its lanes' rows
 #pragma unroll 1
                     for (int cb = 0; cb < HD / 128; ++cb) {
@@ -712,6 +738,11 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
                     tmem_wait_st();
                 }
                 }
+                // ---- V of the tile; the next tile's raw V takes the stage of tile g - 1's, which every worker read
+                //      before the output MMAs just waited for could be issued ----
+                tc_wait(raw_v + st, (g >> 1) & 1, gave_up, p.err);
+                if (tile + 1 < n_tiles) issue(tile + 1, st ^ 1, 1);
+                widen(st, 1, v_hi, v_lo);
                 fence_proxy_async();
                 tc_fence_before();
                 mbar_arrive(pv_ready);
@@ -726,11 +757,12 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
             float * acc = p.ws_acc + slot * p.m * HD;
             // the row's sum: its eight threads' shares (two lanes in each of the quarter's four warps)
             const float l_pair = l_run + __shfl_xor_sync(kFull, l_run, 1);
-            if (part == 0) part_max[col_q * kMaxM + row] = l_pair;
+            float * pm = part_max + (g & 1) * (4 * kMaxM);
+            if (part == 0) pm[col_q * kMaxM + row] = l_pair;
             named_barrier_id(2 + quarter, 128);
             if (col_q == 0 && part == 0 && row < p.m) {
                 ml[2 * row] = m_ref;
-                ml[2 * row + 1] = (part_max[row] + part_max[kMaxM + row]) + (part_max[2 * kMaxM + row] + part_max[3 * kMaxM + row]);
+                ml[2 * row + 1] = (pm[row] + pm[kMaxM + row]) + (pm[2 * kMaxM + row] + pm[3 * kMaxM + row]);
             }
 #pragma unroll 1
             for (int cb = 0; cb < HD / 128; ++cb) {
