@@ -272,7 +272,10 @@ struct tc_layout {
     static constexpr int kBlocks = HD / 64;
     static constexpr int kCBlock = kTile * 128;               // a block of a cell operand
     static constexpr int kCell = KV8 ? HD : HD / 32 * 34;     // raw bytes of a cell
-    static constexpr int kRawTensor = kTile * kCell + (KV8 ? kTile * 8 : 0);  // a tensor's raw tile (KV8: + scales, 8-byte slots)
+    // a cell's stride in the raw tile: a multiple of 16 bytes (the copies) that is NOT a multiple of 128, so that the
+    // 16-byte loads of eight consecutive cells fall on different banks (KV8's 256 put all eight on the same four)
+    static constexpr int kRawCell = kCell % 128 == 0 ? kCell + 16 : kCell;
+    static constexpr int kRawTensor = kTile * kRawCell + (KV8 ? kTile * 8 : 0);  // a tensor's raw tile (KV8: + scales, 8-byte slots)
     static constexpr int kRawStage = 2 * kRawTensor;          // K raw | V raw
     static constexpr int k_hi = 0;
     static constexpr int k_lo = k_hi + kBlocks * kCBlock;
@@ -491,10 +494,20 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
         }
     } else {
         // ---- the workers ----
-        // widening: a thread's item is (cell, 32-dim block); consecutive lanes take consecutive cells, so that the
-        // eight lanes of a 16-byte store phase fall on eight different chunks of the swizzle
+        // widening: a thread's item is (cell, 32-dim block).  A warp takes eight consecutive cells (the eight lanes of a
+        // 16-byte store phase: eight different chunks of the swizzle) times four blocks of one parity (the parity picks
+        // the code path, so it is the same in a warp).  The four blocks start 17 words apart in a raw cell and the
+        // cells 68 words: the 32 lanes of every raw load then fall on 32 different banks (32 consecutive cells of one
+        // block fell on eight).  head_dim 128 has two blocks a parity: a warp takes two groups of eight cells.
         const bool has_item = tid < kTile * (HD / 32);
+#ifndef FNB_ATT_OLD_ITEM_MAP
+        constexpr int kPairs = HD / 64, kItemWarps = 2 * (HD / 32);  // block pairs of a cell; warps that hold items
+        const int wq = lane >> 3, wparity = wid / (kItemWarps / 2);
+        const int cell = 8 * ((wid % (kItemWarps / 2)) * (4 / kPairs) + wq / kPairs) + (lane & 7);
+        const int blk = 2 * (wq % kPairs) + wparity;
+#else
         const int cell = tid & (kTile - 1), blk = tid >> 6;
+#endif
         // tensor memory: warps w, w + 4, w + 8, w + 12 share quarter w & 3 (lanes 32 (w & 3) ..); a lane pair is one
         // query row (even lane: the hi operand / accumulator row, odd lane: the lo row).  Softmax: each of the
         // quarter's warps takes a quarter of the tile's cells, this thread 8 of the tile's 64 cells of its row.
@@ -520,7 +533,7 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
             const int cl = i / kPieces, piece = i - cl * kPieces;
             piece_cell[k] = i < kTile * kPieces ? cl : -1;
             piece_src[k] = uint32_t(cl) * uint32_t(p.n_kv) * L::kCell + kPiece * piece;  // < 64 cells x n_kv x 272
-            piece_dst[k] = cl * L::kCell + kPiece * piece;
+            piece_dst[k] = cl * L::kRawCell + kPiece * piece;
         }
 
         uint32_t g = 0;
@@ -552,7 +565,7 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
                     const int64_t c = t0 + tid;
                     const bool valid = c < c_end;
                     const uint16_t * src = (tensor == 0 ? p.k_scale : p.v_scale) + ((valid ? c : c_begin) * p.n_kv + head) * (HD / 64);
-                    uint8_t * dst = base + kTile * L::kCell + tid * 8;
+                    uint8_t * dst = base + kTile * L::kRawCell + tid * 8;
                     if (HD == 256) {
                         cp_async8(dst, src, valid);
                     } else {  // two scales a cell
@@ -566,7 +579,7 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
                 if (has_item) {
                     const uint8_t * t = raw + st * L::kRawStage + tensor * L::kRawTensor;
                     raw_item<KV8> r;
-                    load_item<HD, KV8>(r, t + cell * L::kCell, t + kTile * L::kCell + cell * 8, blk);
+                    load_item<HD, KV8>(r, t + cell * L::kRawCell, t + kTile * L::kRawCell + cell * 8, blk);
                     widen_item<KV8>(r, cell, blk, t_hi, t_lo);
                 }
             };
