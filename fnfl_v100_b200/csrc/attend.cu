@@ -500,14 +500,10 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
         // cells 68 words: the 32 lanes of every raw load then fall on 32 different banks (32 consecutive cells of one
         // block fell on eight).  head_dim 128 has two blocks a parity: a warp takes two groups of eight cells.
         const bool has_item = tid < kTile * (HD / 32);
-#ifndef FNB_ATT_OLD_ITEM_MAP
         constexpr int kPairs = HD / 64, kItemWarps = 2 * (HD / 32);  // block pairs of a cell; warps that hold items
         const int wq = lane >> 3, wparity = wid / (kItemWarps / 2);
         const int cell = 8 * ((wid % (kItemWarps / 2)) * (4 / kPairs) + wq / kPairs) + (lane & 7);
         const int blk = 2 * (wq % kPairs) + wparity;
-#else
-        const int cell = tid & (kTile - 1), blk = tid >> 6;
-#endif
         // tensor memory: warps w, w + 4, w + 8, w + 12 share quarter w & 3 (lanes 32 (w & 3) ..); a lane pair is one
         // query row (even lane: the hi operand / accumulator row, odd lane: the lo row).  Softmax: each of the
         // quarter's warps takes a quarter of the tile's cells, this thread 8 of the tile's 64 cells of its row.
