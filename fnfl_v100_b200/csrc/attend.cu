@@ -36,9 +36,15 @@
 //     dims, for the outputs), so K and V are widened by the same code: a thread takes one Q8_0 block (or 32 KV8 codes)
 //     of one cell and stores four 16-byte chunks each of hi and lo; consecutive lanes take consecutive cells, so the
 //     eight lanes of a store phase fall on eight different chunks.
-//   * Cells arrive by 16-byte asynchronous copies into a two-stage ring of raw tiles, one tile (64 cells) ahead;
-//     consecutive threads copy consecutive pieces, so that the copies cover whole cache lines (a thread reading its
-//     own cell straight from the cache touched 32 lines per warp instruction and kept the L1 pipe busy 80 % of the time).
+//   * Cells arrive in a two-stage ring of raw tiles, a tile or two ahead.  At head_dim 256 in Q8_0 one thread of a warp
+//     of its own asks for them: ONE tensor-map copy (cp.async.bulk.tensor, box = 64 cells x one head's 272 bytes) per
+//     tensor and tile, completion counted in bytes on the stage's mbarrier.  The other shapes (KV8, whose raw tile is
+//     padded against bank conflicts and whose scales are 8 bytes a cell; Q8_0 at head_dim 128, 136 bytes a cell) use
+//     16-byte asynchronous copies issued by the workers, consecutive threads taking consecutive pieces so that the
+//     copies cover whole cache lines (a thread reading its own cell straight from the cache touched 32 lines per warp
+//     instruction and kept the L1 pipe busy 80 % of the time).  Those 2 x 1088 copies a tile cost each worker 0.29 us
+//     per tensor - more than widening its item - because they are bound by the load / store unit's rate; the
+//     tensor-map copies do not pass through it (0.142 -> 0.123 ms).
 //   * Sixteen worker warps and one that only issues the MMAs; completion comes back through mbarriers
 //     (tcgen05.commit).  A worker's tile: read the tile's scores into registers; widen the NEXT tile's K (its operand
 //     is free, and with S read the next scores can run at once); then this tile's softmax and its V.  The issuer sends
@@ -60,6 +66,7 @@
 #include <atomic>
 #include <cstdio>
 
+#include <cuda.h>  // CUtensorMap and the type of cuTensorMapEncodeTiled (reached through cudaGetDriverEntryPoint: nothing links to the driver library)
 #include <cuda_fp16.h>
 
 #include "bulk_pipe.cuh"
@@ -69,7 +76,8 @@ namespace fnb {
 namespace {
 
 constexpr int kThreads = 512;  // sixteen worker warps: four per scheduler hide each other's latencies
-constexpr int kLaunchThreads = kThreads + 32;  // and a warp that only issues the MMAs (a thread that issues them waits on the tensor core's queue: as a worker it held up every barrier)
+constexpr int kLaunchThreads = kThreads + 32;
+constexpr int kLaunchThreadsTma = kLaunchThreads + 32;  // + the warp whose first lane asks for the tiles (tensor-map copies)  // and a warp that only issues the MMAs (a thread that issues them waits on the tensor core's queue: as a worker it held up every barrier)
 constexpr int kTile = 64;   // cells per tile: the N of the score MMA, four K steps of the output MMA
 constexpr int kMaxM = 64;   // query rows of one KV head's group: rows x (n_q_heads / n_kv_heads)
 constexpr float kPScale = 4096.0f, kPUnscale = 1.0f / 4096.0f;
@@ -154,6 +162,16 @@ __device__ __forceinline__ void codes_to_h2(uint32_t w, __half2 & lo, __half2 & 
     const __half2 bias = bits_h2(0x64806480u);
     lo = __hsub2(bits_h2(__byte_perm(b, 0x64646464u, 0x4140u)), bias);
     hi = __hsub2(bits_h2(__byte_perm(b, 0x64646464u, 0x4342u)), bias);
+}
+
+// one tile of a 3-D tensor (box given by the tensor map) global -> shared, completion counted in bytes on `bar`; x, y, z
+// from the innermost dimension out (x times the element size must be a multiple of 16 bytes: it is always 0 here)
+__device__ __forceinline__ void tensor_g2s(void * dst_smem, const CUtensorMap * map, int x, int y, int z, uint64_t * bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+            smem_u32(dst_smem)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+        : "memory");
 }
 
 // ---- tensor memory and the MMA --------------------------------------------------------------------------------------
@@ -283,8 +301,8 @@ struct tc_layout {
     static constexpr int v_lo = v_hi + kBlocks * kCBlock;
     static constexpr int raw = v_lo + kBlocks * kCBlock;      // [2 stages][K raw | V raw]: the cells as they lie in the cache
     static constexpr int part_max = raw + 2 * kRawStage;      // float [2][4][64]: a row's maximum over each quarter of a tile, by tile parity
-    static constexpr int bars = part_max + 2 * 4 * kMaxM * 4; // eight mbarriers
-    static constexpr int misc = bars + 64;                    // tensor-memory base, the give-up flag
+    static constexpr int bars = part_max + 2 * 4 * kMaxM * 4; // ten mbarriers
+    static constexpr int misc = bars + 128;                    // tensor-memory base, the give-up flag
     static constexpr int total = misc + 16 + 1024;            // + slack to align the base to 1024 bytes
     // tensor-memory columns: scores | outputs | stacked query rows | stacked probabilities | the alternate probabilities
     static constexpr uint32_t t_s = 0, t_o = 64, t_q = t_o + HD, t_p = t_q + HD / 2, t_alt = t_p + 32;
@@ -391,8 +409,13 @@ __device__ __forceinline__ void cp_async_arrive(uint64_t * bar) {
 //   bar_o               (commit)        the output MMAs are done: O, P and the V operand are free
 // Tile g (counted over the CTA's units) uses stage g & 1 of both rings and phase g of the four tile barriers.  Within a
 // unit K runs a tile ahead: tile g + 1's K is widened, and its scores issued, during tile g.
-template <int HD, bool KV8>
-__global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_params p) {
+// TMA: the raw tiles are asked for by one thread, one tensor-map copy per tensor and tile (box: 64 cells x one head's
+// bytes of a cell), instead of 2 x 1088 16-byte copies issued by the workers, which cost each worker more than widening
+// its item: the copies then bypass the load / store unit.  Built for the shape whose raw tile is dense and free of bank
+// conflicts as the copy lays it out (Q8_0 at head_dim 256: 272 bytes a cell).
+template <int HD, bool KV8, bool TMA>
+__global__ void __launch_bounds__(kLaunchThreadsTma, 1)
+    attend_kernel(const attend_params p, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
     using L = tc_layout<HD, KV8>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t * smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -404,22 +427,30 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
     float * part_max = reinterpret_cast<float *>(smem + L::part_max);
     uint64_t * bar_s = reinterpret_cast<uint64_t *>(smem + L::bars);
     uint64_t * bar_o = bar_s + 1;
-    uint64_t * k_ready = bar_s + 2;
-    uint64_t * pv_ready = bar_s + 3;
-    uint64_t * raw_k = bar_s + 4;  // [2]
-    uint64_t * raw_v = bar_s + 6;  // [2]
+    uint64_t * k_ready = bar_s + 2;   // [2]
+    uint64_t * pv_ready = bar_s + 4;  // [2]
+    uint64_t * raw_k = bar_s + 6;     // [2]
+    uint64_t * raw_v = bar_s + 8;     // [2]
+    // Without the copier k_ready and pv_ready are one barrier each, phase g for tile g.  With it they are split by tile
+    // parity (tile g on barrier g & 1, phase g >> 1): the copier waits for the tile two back, and a waiter may be one
+    // phase behind its barrier, never two.
+    const auto kr = [&](uint32_t g) { return k_ready + (TMA ? g & 1u : 0u); };
+    const auto pr = [&](uint32_t g) { return pv_ready + (TMA ? g & 1u : 0u); };
+    const auto par = [&](uint32_t g) { return TMA ? (g >> 1) & 1u : g & 1u; };
     uint32_t * tmem_slot = reinterpret_cast<uint32_t *>(smem + L::misc);
     volatile uint32_t * gave_up = tmem_slot + 1;
 
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-    const bool worker = wid < kThreads / 32;
+    const bool worker = wid < kThreads / 32, copier = TMA && wid == kThreads / 32 + 1;
 
     if (tid == 0) {
         mbar_init(bar_s, 1);
         mbar_init(bar_o, 1);
-        mbar_init(k_ready, kThreads);
-        mbar_init(pv_ready, kThreads);
-        for (int i = 0; i < 2; ++i) mbar_init(raw_k + i, kThreads), mbar_init(raw_v + i, kThreads);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(k_ready + i, kThreads), mbar_init(pv_ready + i, kThreads);
+            // a raw stage hears of every worker's copies, or of the copier's one arrival and its bytes
+            mbar_init(raw_k + i, TMA ? 1 : kThreads), mbar_init(raw_v + i, TMA ? 1 : kThreads);
+        }
         *gave_up = 0;
         mbar_init_fence();
     }
@@ -439,7 +470,39 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
         return int((c_end - c_begin + kTile - 1) / kTile);
     };
 
-    if (!worker) {
+    if (copier) {
+        // ---- the copier: every tile of this CTA in order, tile g's K and V into stage g & 1 of the raw rings, one
+        //      tensor-map copy each.  A stage is free when every worker has read it, which is what its tile's k_ready /
+        //      pv_ready phase says.  The box is always 64 cells: cells past the unit's end come along (the workers widen
+        //      them as zeros), cells past the cache's end are filled with zeros by the copy. ----
+        if (lane == 0) {
+            uint32_t g = 0;
+            for (int unit = blockIdx.x; unit < total_units; unit += gridDim.x) {
+                int head, u;
+                int64_t c_begin, c_end;
+                const int n_tiles = tiles_of(unit, head, u, c_begin, c_end);
+                for (int tile = 0; tile < n_tiles; ++tile, ++g) {
+                    const int st = g & 1;
+                    const int t0 = int(c_begin + int64_t(tile) * kTile);
+                    if (g >= 2) tc_wait(kr(g), par(g - 2), gave_up, p.err);
+                    mbar_expect_tx(raw_k + st, kTile * L::kCell);
+                    tensor_g2s(raw + st * L::kRawStage, &map_k, 0, head, t0, raw_k + st);
+                    mbar_arrive(raw_k + st);
+                    if (g >= 2) tc_wait(pr(g), par(g - 2), gave_up, p.err);
+                    mbar_expect_tx(raw_v + st, kTile * L::kCell);
+                    tensor_g2s(raw + st * L::kRawStage + L::kRawTensor, &map_v, 0, head, t0, raw_v + st);
+                    mbar_arrive(raw_v + st);
+                }
+            }
+            // every copy issued has landed before the CTA's shared memory can go to another CTA (at once when the
+            // workers ran to the end; after a wait that gave up, this is what keeps the exit safe)
+            for (uint32_t back = 1; back <= 2 && back <= g; ++back) {
+                const uint32_t gg = g - back;
+                mbar_wait_landed(raw_k + (gg & 1), (gg >> 1) & 1);
+                mbar_wait_landed(raw_v + (gg & 1), (gg >> 1) & 1);
+            }
+        }
+    } else if (!worker) {
         // ---- the issuer: S = [q_hi; q_lo] . (K_lo + K_hi)^T, the small products first, so that only the sixteen K_hi
         //      steps round a large accumulator; then lane 2 r: p_hi . V_hi only (four roundings of the large
         //      accumulator per tile), lane 2 r + 1: p_lo . V_hi + p_hi . V_lo (small) ----
@@ -472,16 +535,16 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
                 };
                 // the unit's first scores; then, tile by tile, the NEXT tile's scores before this tile's outputs: the
                 // workers widen the next K as soon as they have read this tile's scores, and only then run its softmax
-                tc_wait(k_ready, g & 1, gave_up, p.err);
+                tc_wait(kr(g), par(g), gave_up, p.err);
                 tc_fence_after();
                 scores();
                 for (int tile = 0; tile < n_tiles; ++tile, ++g) {
                     if (tile + 1 < n_tiles) {
-                        tc_wait(k_ready, (g + 1) & 1, gave_up, p.err);
+                        tc_wait(kr(g + 1), par(g + 1), gave_up, p.err);
                         tc_fence_after();
                         scores();
                     }
-                    tc_wait(pv_ready, g & 1, gave_up, p.err);
+                    tc_wait(pr(g), par(g), gave_up, p.err);
                     tc_fence_after();
 #pragma unroll
                     for (int ks = 0; ks < 4; ++ks) {  // 16 cells a step: two groups of eight 128-byte rows, 8 columns of P
@@ -541,6 +604,7 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
             // ---- raw tiles of one tensor into stage `st` of its ring; the stage's barrier hears of this thread's
             //      copies when they land ----
             const auto issue = [&](int tile, int st, int tensor) {
+                if (TMA) return;  // the copier asks for the tiles
                 uint8_t * base = raw + st * L::kRawStage + tensor * L::kRawTensor;
                 const uint8_t * cache = tensor == 0 ? p.k_cache : p.v_cache;
                 const int64_t t0 = c_begin + int64_t(tile) * kTile;
@@ -571,11 +635,16 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
                 cp_async_arrive((tensor == 0 ? raw_k : raw_v) + st);
             };
             // this thread's item of a staged tensor, widened into the operand tiles
-            const auto widen = [&](int st, int tensor, uint8_t * t_hi, uint8_t * t_lo) {
+            const auto widen = [&](int tile, int st, int tensor, uint8_t * t_hi, uint8_t * t_lo) {
                 if (has_item) {
                     const uint8_t * t = raw + st * L::kRawStage + tensor * L::kRawTensor;
                     raw_item<KV8> r;
                     load_item<HD, KV8>(r, t + cell * L::kRawCell, t + kTile * L::kRawCell + cell * 8, blk);
+                    if (TMA && c_begin + int64_t(tile) * kTile + cell >= c_end) {  // the box brought a cell past the unit's end
+#pragma unroll
+                        for (int j = 0; j < (KV8 ? 8 : 9); ++j) r.w[j] = 0u;
+                        r.scale = 0u;
+                    }
                     widen_item<KV8>(r, cell, blk, t_hi, t_lo);
                 }
             };
@@ -643,10 +712,10 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
 
             // ---- K of the unit's first tile (the operand is free: the previous unit's last scores were read by all) ----
             tc_wait(raw_k + (g & 1), (g >> 1) & 1, gave_up, p.err);
-            widen(g & 1, 0, k_hi, k_lo);
+            widen(0, g & 1, 0, k_hi, k_lo);
             fence_proxy_async();
             tc_fence_before();
-            mbar_arrive(k_ready);
+            mbar_arrive(kr(g));
 
             for (int tile = 0; tile < n_tiles; ++tile, ++g) {
                 const int st = g & 1;
@@ -671,10 +740,10 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
                 if (tile + 1 < n_tiles) {
                     tc_wait(raw_k + (st ^ 1), ((g + 1) >> 1) & 1, gave_up, p.err);
                     if (tile + 2 < n_tiles) issue(tile + 2, st, 0);
-                    widen(st ^ 1, 0, k_hi, k_lo);
+                    widen(tile + 1, st ^ 1, 0, k_hi, k_lo);
                     fence_proxy_async();
                     tc_fence_before();
-                    mbar_arrive(k_ready);
+                    mbar_arrive(kr(g + 1));
                 }
                 float a_row = 1.0f;
                 if (quarter_live) {
@@ -751,10 +820,10 @@ __global__ void __launch_bounds__(kLaunchThreads, 1) attend_kernel(const attend_
                 //      before the output MMAs just waited for could be issued ----
                 tc_wait(raw_v + st, (g >> 1) & 1, gave_up, p.err);
                 if (tile + 1 < n_tiles) issue(tile + 1, st ^ 1, 1);
-                widen(st, 1, v_hi, v_lo);
+                widen(tile, st, 1, v_hi, v_lo);
                 fence_proxy_async();
                 tc_fence_before();
-                mbar_arrive(pv_ready);
+                mbar_arrive(pr(g));
             }
 
             // ---- the unit's partial result: (reference point, sum, (O[2 r] + O[2 r + 1]) / 2^12) of its rows ----
@@ -867,13 +936,13 @@ __global__ void __launch_bounds__(HD * kFoldLanes) attend_fold_kernel(const atte
     p.out[at] = y;
 }
 
-template <int HD, bool KV8>
+template <int HD, bool KV8, bool TMA>
 bool configure() {
     static std::atomic<bool> done[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
     if (!done[dev].load(std::memory_order_acquire)) {
-        if (cudaFuncSetAttribute(attend_kernel<HD, KV8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(attend_kernel<HD, KV8, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  tc_layout<HD, KV8>::total) != cudaSuccess) {
             return false;
         }
@@ -882,11 +951,53 @@ bool configure() {
     return true;
 }
 
+// The tensor map of one cache tensor as the copier reads it: [cache_slots][n_kv][cell bytes] seen as 16-bit elements, a
+// box of 64 cells x one head x the whole cell.  Encoded on the host by the driver's cuTensorMapEncodeTiled, looked up
+// once through the runtime (no link against the driver library); false when the driver does not offer it or refuses
+// the shape, and the caller then launches the kernel whose workers copy the cells themselves.
+using encode_tiled_fn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                     const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+inline encode_tiled_fn encode_tiled() {
+    static const encode_tiled_fn fn = [] {
+        void * f = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) {
+            (void) cudaGetLastError();
+            return encode_tiled_fn(nullptr);
+        }
+        return reinterpret_cast<encode_tiled_fn>(f);
+    }();
+    return fn;
+}
+inline bool make_cell_map(CUtensorMap * map, const uint8_t * cache, int64_t cache_slots, int n_kv, int cell_bytes) {
+    const encode_tiled_fn enc = encode_tiled();
+    if (enc == nullptr || cell_bytes % 16 != 0 || cell_bytes / 2 > 256) return false;
+    const cuuint64_t dims[3] = {cuuint64_t(cell_bytes / 2), cuuint64_t(n_kv), cuuint64_t(cache_slots)};
+    const cuuint64_t strides[2] = {cuuint64_t(cell_bytes), cuuint64_t(n_kv) * cuuint64_t(cell_bytes)};  // bytes, from the second dimension on
+    const cuuint32_t box[3] = {cuuint32_t(cell_bytes / 2), 1u, cuuint32_t(kTile)};
+    const cuuint32_t elem[3] = {1u, 1u, 1u};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<uint8_t *>(cache), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int HD, bool KV8>
 int32_t launch_hd(const attend_params & p, cudaStream_t s) {
-    if (!configure<HD, KV8>()) return FNB_LAUNCH_FAILED;
     const int units = p.n_kv * p.n_units;
-    attend_kernel<HD, KV8><<<units < kSmCount ? units : kSmCount, kLaunchThreads, tc_layout<HD, KV8>::total, s>>>(p);
+    const int grid = units < kSmCount ? units : kSmCount;
+    using L = tc_layout<HD, KV8>;
+    CUtensorMap map_k = {}, map_v = {};
+    // the tensor-map copies want the raw tile dense (a cell's stride in shared memory = its bytes) and their stride in
+    // the cache a multiple of 16 bytes; of the four shapes that is Q8_0 at head_dim 256
+    constexpr bool kTmaShape = !KV8 && L::kRawCell == L::kCell && L::kCell % 16 == 0;
+    if (kTmaShape && make_cell_map(&map_k, p.k_cache, p.cache_slots, p.n_kv, L::kCell) &&
+        make_cell_map(&map_v, p.v_cache, p.cache_slots, p.n_kv, L::kCell)) {
+        if (!configure<HD, KV8, kTmaShape>()) return FNB_LAUNCH_FAILED;
+        attend_kernel<HD, KV8, kTmaShape><<<grid, kLaunchThreadsTma, L::total, s>>>(p, map_k, map_v);
+    } else {
+        if (!configure<HD, KV8, false>()) return FNB_LAUNCH_FAILED;
+        attend_kernel<HD, KV8, false><<<grid, kLaunchThreads, L::total, s>>>(p, map_k, map_v);
+    }
     if (cudaPeekAtLastError() != cudaSuccess) return FNB_LAUNCH_FAILED;
     attend_fold_kernel<HD><<<p.rows * p.n_q, HD * kFoldLanes, 0, s>>>(p);
     return launch_status();
@@ -905,7 +1016,9 @@ bool shape_ok(const fnb_attend_args * a) {
 }  // namespace
 
 bool attend_prepare_device() {
-    return configure<256, false>() && configure<256, true>() && configure<128, false>() && configure<128, true>();
+    (void) encode_tiled();
+    return configure<256, false, false>() && configure<256, false, true>() && configure<256, true, false>() &&
+           configure<128, false, false>() && configure<128, true, false>();
 }
 
 // shared by the two entry points: everything but where the workspace lives
