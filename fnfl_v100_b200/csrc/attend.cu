@@ -36,15 +36,18 @@
 //     dims, for the outputs), so K and V are widened by the same code: a thread takes one Q8_0 block (or 32 KV8 codes)
 //     of one cell and stores four 16-byte chunks each of hi and lo; consecutive lanes take consecutive cells, so the
 //     eight lanes of a store phase fall on eight different chunks.
-//   * Cells arrive in a two-stage ring of raw tiles, a tile or two ahead.  At head_dim 256 in Q8_0 one thread of a warp
-//     of its own asks for them: ONE tensor-map copy (cp.async.bulk.tensor, box = 64 cells x one head's 272 bytes) per
-//     tensor and tile, completion counted in bytes on the stage's mbarrier.  The other shapes (KV8, whose raw tile is
-//     padded against bank conflicts and whose scales are 8 bytes a cell; Q8_0 at head_dim 128, 136 bytes a cell) use
+//   * Cells arrive in a two-stage ring of raw tiles, a tile or two ahead.  One thread of a warp of its own asks for
+//     them: ONE tensor-map copy (cp.async.bulk.tensor) per tensor and tile, completion counted in bytes on the stage's
+//     mbarrier.  Q8_0 at head_dim 256: box = 64 cells x one head's 272 bytes, laid out densely (68 words a cell: the
+//     raw loads of eight consecutive cells fall on different banks).  KV8: a cell is one or two rows of 128 bytes, box =
+//     64 cells x one head's rows with the copy's 128-byte swizzle, which the raw loads undo (two-way conflicts instead
+//     of the eight-way ones of dense 256-byte cells); its scales, 8 bytes a cell, stay 8-byte asynchronous copies by
+//     64 workers.  Q8_0 at head_dim 128 (136 bytes a cell: no 16-byte stride) and drivers without the encoder use
 //     16-byte asynchronous copies issued by the workers, consecutive threads taking consecutive pieces so that the
 //     copies cover whole cache lines (a thread reading its own cell straight from the cache touched 32 lines per warp
 //     instruction and kept the L1 pipe busy 80 % of the time).  Those 2 x 1088 copies a tile cost each worker 0.29 us
 //     per tensor - more than widening its item - because they are bound by the load / store unit's rate; the
-//     tensor-map copies do not pass through it (0.142 -> 0.123 ms).
+//     tensor-map copies do not pass through it (Q8_0 0.142 -> 0.123 ms, KV8 0.138 -> 0.130).
 //   * Sixteen worker warps and one that only issues the MMAs; completion comes back through mbarriers
 //     (tcgen05.commit).  A worker's tile: read the tile's scores into registers; widen the NEXT tile's K (its operand
 //     is free, and with S read the next scores can run at once); then this tile's softmax and its V.  The issuer sends
@@ -174,6 +177,14 @@ __device__ __forceinline__ void tensor_g2s(void * dst_smem, const CUtensorMap * 
         : "memory");
 }
 
+__device__ __forceinline__ void tensor_g2s4(void * dst_smem, const CUtensorMap * map, int x, int y, int z, int w, uint64_t * bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
+            smem_u32(dst_smem)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar))
+        : "memory");
+}
+
 // ---- tensor memory and the MMA --------------------------------------------------------------------------------------
 // Shared-memory matrix descriptor of an operand in the 128-byte-swizzled canonical layout: start address, leading and
 // stride byte offsets (in 16-byte units), descriptor version 1, layout type 2 (128-byte swizzle).
@@ -285,15 +296,20 @@ __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.
 // too, its 4 KB per MMA made shared-memory bandwidth the bound).  Stacked rows interleave the parts: lane 2 r holds
 // query row r's hi part, lane 2 r + 1 its lo part, so a query row's two accumulator rows sit in adjacent lanes of one
 // 32-lane quarter.
-template <int HD, bool KV8>
+template <int HD, bool KV8, bool TMA = false>
 struct tc_layout {
     static constexpr int kBlocks = HD / 64;
     static constexpr int kCBlock = kTile * 128;               // a block of a cell operand
     static constexpr int kCell = KV8 ? HD : HD / 32 * 34;     // raw bytes of a cell
     // a cell's stride in the raw tile: a multiple of 16 bytes (the copies) that is NOT a multiple of 128, so that the
-    // 16-byte loads of eight consecutive cells fall on different banks (KV8's 256 put all eight on the same four)
-    static constexpr int kRawCell = kCell % 128 == 0 ? kCell + 16 : kCell;
-    static constexpr int kRawTensor = kTile * kRawCell + (KV8 ? kTile * 8 : 0);  // a tensor's raw tile (KV8: + scales, 8-byte slots)
+    // 16-byte loads of eight consecutive cells fall on different banks (KV8's 256 put all eight on the same four).
+    // A tensor-map copy lays the box out densely; KV8's cells are then kept apart by the copy's own 128-byte swizzle
+    // (16-byte chunk c of the 128-byte row at address a sits at chunk c ^ ((a >> 7) & 7)), which wants the tile's base
+    // on a 1024-byte boundary.
+    static constexpr bool kSwizzled = KV8 && TMA;
+    static constexpr int kRawCell = kSwizzled ? kCell : kCell % 128 == 0 ? kCell + 16 : kCell;
+    static constexpr int kRawTensor = kSwizzled ? (kTile * kCell + kTile * 8 + 1023) / 1024 * 1024
+                                                : kTile * kRawCell + (KV8 ? kTile * 8 : 0);  // a tensor's raw tile (KV8: + scales, 8-byte slots)
     static constexpr int kRawStage = 2 * kRawTensor;          // K raw | V raw
     static constexpr int k_hi = 0;
     static constexpr int k_lo = k_hi + kBlocks * kCBlock;
@@ -324,13 +340,19 @@ struct raw_item {
 // (68 bytes = 17 words): words 0 .. 8 for the pair's first block (d in the low half of word 0, codes from its high
 // half on), words 8 .. 16 for the second (d in the high half of word 8, codes in words 9 .. 16).
 // from the staged raw tile: `cell_raw` the cell's bytes, `cell_scales` (KV8) its FP16 group scales
-template <int HD, bool KV8>
-__device__ __forceinline__ void load_item(raw_item<KV8> & r, const uint8_t * cell_raw, const uint8_t * cell_scales, int blk) {
+// SWZ: the raw tile was laid out by a tensor-map copy with the 128-byte swizzle (its base on a 1024-byte boundary):
+// chunk c of a cell's 128-byte row number `row` (counted from the tile's base) sits at chunk c ^ (row & 7).
+template <int HD, bool KV8, bool SWZ = false>
+__device__ __forceinline__ void load_item(raw_item<KV8> & r, const uint8_t * cell_raw, const uint8_t * cell_scales, int blk, int cell = 0) {
     if (KV8) {
-        const uint4 * src = reinterpret_cast<const uint4 *>(cell_raw + 32 * blk);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-            const uint4 v = src[j];
+            int at = 32 * blk + 16 * j;
+            if (SWZ) {
+                const int row = cell * (HD / 128) + (blk >> 2), chunk = (2 * (blk & 3) + j) ^ (row & 7);
+                at = 128 * (blk >> 2) + 16 * chunk;
+            }
+            const uint4 v = *reinterpret_cast<const uint4 *>(cell_raw + at);
             r.w[4 * j] = v.x, r.w[4 * j + 1] = v.y, r.w[4 * j + 2] = v.z, r.w[4 * j + 3] = v.w;
         }
         r.scale = reinterpret_cast<const uint16_t *>(cell_scales)[blk >> 1];
@@ -411,12 +433,12 @@ __device__ __forceinline__ void cp_async_arrive(uint64_t * bar) {
 // unit K runs a tile ahead: tile g + 1's K is widened, and its scores issued, during tile g.
 // TMA: the raw tiles are asked for by one thread, one tensor-map copy per tensor and tile (box: 64 cells x one head's
 // bytes of a cell), instead of 2 x 1088 16-byte copies issued by the workers, which cost each worker more than widening
-// its item: the copies then bypass the load / store unit.  Built for the shape whose raw tile is dense and free of bank
-// conflicts as the copy lays it out (Q8_0 at head_dim 256: 272 bytes a cell).
+// its item: the copies then bypass the load / store unit.  For every shape whose cells lie a multiple of 16 bytes apart
+// in the cache (all but Q8_0 at head_dim 128).
 template <int HD, bool KV8, bool TMA>
 __global__ void __launch_bounds__(kLaunchThreadsTma, 1)
     attend_kernel(const attend_params p, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
-    using L = tc_layout<HD, KV8>;
+    using L = tc_layout<HD, KV8, TMA>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t * smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t * k_hi = smem + L::k_hi;
@@ -448,8 +470,9 @@ __global__ void __launch_bounds__(kLaunchThreadsTma, 1)
         mbar_init(bar_o, 1);
         for (int i = 0; i < 2; ++i) {
             mbar_init(k_ready + i, kThreads), mbar_init(pv_ready + i, kThreads);
-            // a raw stage hears of every worker's copies, or of the copier's one arrival and its bytes
-            mbar_init(raw_k + i, TMA ? 1 : kThreads), mbar_init(raw_v + i, TMA ? 1 : kThreads);
+            // a raw stage hears of every worker's copies, or of the copier's one arrival and its bytes (KV8: and of the
+            // 64 threads that copy the cells' scales, 8 bytes each)
+            mbar_init(raw_k + i, TMA ? 1 + (KV8 ? kTile : 0) : kThreads), mbar_init(raw_v + i, TMA ? 1 + (KV8 ? kTile : 0) : kThreads);
         }
         *gave_up = 0;
         mbar_init_fence();
@@ -486,11 +509,19 @@ __global__ void __launch_bounds__(kLaunchThreadsTma, 1)
                     const int t0 = int(c_begin + int64_t(tile) * kTile);
                     if (g >= 2) tc_wait(kr(g), par(g - 2), gave_up, p.err);
                     mbar_expect_tx(raw_k + st, kTile * L::kCell);
-                    tensor_g2s(raw + st * L::kRawStage, &map_k, 0, head, t0, raw_k + st);
+                    if (KV8) {
+                        tensor_g2s4(raw + st * L::kRawStage, &map_k, 0, 0, head, t0, raw_k + st);
+                    } else {
+                        tensor_g2s(raw + st * L::kRawStage, &map_k, 0, head, t0, raw_k + st);
+                    }
                     mbar_arrive(raw_k + st);
                     if (g >= 2) tc_wait(pr(g), par(g - 2), gave_up, p.err);
                     mbar_expect_tx(raw_v + st, kTile * L::kCell);
-                    tensor_g2s(raw + st * L::kRawStage + L::kRawTensor, &map_v, 0, head, t0, raw_v + st);
+                    if (KV8) {
+                        tensor_g2s4(raw + st * L::kRawStage + L::kRawTensor, &map_v, 0, 0, head, t0, raw_v + st);
+                    } else {
+                        tensor_g2s(raw + st * L::kRawStage + L::kRawTensor, &map_v, 0, head, t0, raw_v + st);
+                    }
                     mbar_arrive(raw_v + st);
                 }
             }
@@ -604,20 +635,22 @@ __global__ void __launch_bounds__(kLaunchThreadsTma, 1)
             // ---- raw tiles of one tensor into stage `st` of its ring; the stage's barrier hears of this thread's
             //      copies when they land ----
             const auto issue = [&](int tile, int st, int tensor) {
-                if (TMA) return;  // the copier asks for the tiles
+                if (TMA && !KV8) return;  // the copier asks for the tiles; KV8: for the cells, the scales are copied here
                 uint8_t * base = raw + st * L::kRawStage + tensor * L::kRawTensor;
                 const uint8_t * cache = tensor == 0 ? p.k_cache : p.v_cache;
                 const int64_t t0 = c_begin + int64_t(tile) * kTile;
                 const int64_t head_at = (t0 * p.n_kv + head) * L::kCell;
+                if (!TMA) {
 #pragma unroll
-                for (int k = 0; k < kMine; ++k) {
-                    if (piece_cell[k] >= 0) {
-                        const bool valid = t0 + piece_cell[k] < c_end;
-                        const uint8_t * src = cache + (valid ? head_at + piece_src[k] : 0);
-                        if (kPiece == 16) {
-                            cp_async16(base + piece_dst[k], src, valid);
-                        } else {
-                            cp_async8(base + piece_dst[k], src, valid);
+                    for (int k = 0; k < kMine; ++k) {
+                        if (piece_cell[k] >= 0) {
+                            const bool valid = t0 + piece_cell[k] < c_end;
+                            const uint8_t * src = cache + (valid ? head_at + piece_src[k] : 0);
+                            if (kPiece == 16) {
+                                cp_async16(base + piece_dst[k], src, valid);
+                            } else {
+                                cp_async8(base + piece_dst[k], src, valid);
+                            }
                         }
                     }
                 }
@@ -632,14 +665,14 @@ __global__ void __launch_bounds__(kLaunchThreadsTma, 1)
                         cp_async4(dst, src, valid);
                     }
                 }
-                cp_async_arrive((tensor == 0 ? raw_k : raw_v) + st);
+                if (!TMA || tid < kTile) cp_async_arrive((tensor == 0 ? raw_k : raw_v) + st);
             };
             // this thread's item of a staged tensor, widened into the operand tiles
             const auto widen = [&](int tile, int st, int tensor, uint8_t * t_hi, uint8_t * t_lo) {
                 if (has_item) {
                     const uint8_t * t = raw + st * L::kRawStage + tensor * L::kRawTensor;
                     raw_item<KV8> r;
-                    load_item<HD, KV8>(r, t + cell * L::kRawCell, t + kTile * L::kRawCell + cell * 8, blk);
+                    load_item<HD, KV8, L::kSwizzled>(r, t + cell * L::kRawCell, t + kTile * L::kRawCell + cell * 8, blk, cell);
                     if (TMA && c_begin + int64_t(tile) * kTile + cell >= c_end) {  // the box brought a cell past the unit's end
 #pragma unroll
                         for (int j = 0; j < (KV8 ? 8 : 9); ++j) r.w[j] = 0u;
@@ -943,7 +976,7 @@ bool configure() {
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
     if (!done[dev].load(std::memory_order_acquire)) {
         if (cudaFuncSetAttribute(attend_kernel<HD, KV8, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 tc_layout<HD, KV8>::total) != cudaSuccess) {
+                                 tc_layout<HD, KV8, TMA>::total) != cudaSuccess) {
             return false;
         }
         done[dev].store(true, std::memory_order_release);
@@ -970,13 +1003,26 @@ inline encode_tiled_fn encode_tiled() {
     }();
     return fn;
 }
-inline bool make_cell_map(CUtensorMap * map, const uint8_t * cache, int64_t cache_slots, int n_kv, int cell_bytes) {
+// Q8_0 (swizzled = false): three dimensions, [slots][heads][cell as u16], the box one head's whole cell of 64 slots, laid
+// out densely.  KV8 (swizzled = true): a cell is one or two rows of 128 bytes, four dimensions [slots][heads][rows][64 x
+// u16], the box 64 slots x one head x its rows, with the 128-byte swizzle.
+inline bool make_cell_map(CUtensorMap * map, const uint8_t * cache, int64_t cache_slots, int n_kv, int cell_bytes, bool swizzled) {
     const encode_tiled_fn enc = encode_tiled();
-    if (enc == nullptr || cell_bytes % 16 != 0 || cell_bytes / 2 > 256) return false;
+    if (enc == nullptr || cell_bytes % 16 != 0) return false;
+    const cuuint32_t elem[4] = {1u, 1u, 1u, 1u};
+    if (swizzled) {
+        if (cell_bytes % 128 != 0) return false;
+        const cuuint64_t dims[4] = {64u, cuuint64_t(cell_bytes / 128), cuuint64_t(n_kv), cuuint64_t(cache_slots)};
+        const cuuint64_t strides[3] = {128u, cuuint64_t(cell_bytes), cuuint64_t(n_kv) * cuuint64_t(cell_bytes)};
+        const cuuint32_t box[4] = {64u, cuuint32_t(cell_bytes / 128), 1u, cuuint32_t(kTile)};
+        return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<uint8_t *>(cache), dims, strides, box, elem,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    }
+    if (cell_bytes / 2 > 256) return false;
     const cuuint64_t dims[3] = {cuuint64_t(cell_bytes / 2), cuuint64_t(n_kv), cuuint64_t(cache_slots)};
     const cuuint64_t strides[2] = {cuuint64_t(cell_bytes), cuuint64_t(n_kv) * cuuint64_t(cell_bytes)};  // bytes, from the second dimension on
     const cuuint32_t box[3] = {cuuint32_t(cell_bytes / 2), 1u, cuuint32_t(kTile)};
-    const cuuint32_t elem[3] = {1u, 1u, 1u};
     return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<uint8_t *>(cache), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -985,18 +1031,17 @@ template <int HD, bool KV8>
 int32_t launch_hd(const attend_params & p, cudaStream_t s) {
     const int units = p.n_kv * p.n_units;
     const int grid = units < kSmCount ? units : kSmCount;
-    using L = tc_layout<HD, KV8>;
     CUtensorMap map_k = {}, map_v = {};
-    // the tensor-map copies want the raw tile dense (a cell's stride in shared memory = its bytes) and their stride in
-    // the cache a multiple of 16 bytes; of the four shapes that is Q8_0 at head_dim 256
-    constexpr bool kTmaShape = !KV8 && L::kRawCell == L::kCell && L::kCell % 16 == 0;
-    if (kTmaShape && make_cell_map(&map_k, p.k_cache, p.cache_slots, p.n_kv, L::kCell) &&
-        make_cell_map(&map_v, p.v_cache, p.cache_slots, p.n_kv, L::kCell)) {
+    // the tensor-map copies want a cell's stride in the cache a multiple of 16 bytes: every shape but Q8_0 at head_dim 128
+    constexpr int kCell = tc_layout<HD, KV8, false>::kCell;
+    constexpr bool kTmaShape = kCell % 16 == 0;
+    if (kTmaShape && make_cell_map(&map_k, p.k_cache, p.cache_slots, p.n_kv, kCell, KV8) &&
+        make_cell_map(&map_v, p.v_cache, p.cache_slots, p.n_kv, kCell, KV8)) {
         if (!configure<HD, KV8, kTmaShape>()) return FNB_LAUNCH_FAILED;
-        attend_kernel<HD, KV8, kTmaShape><<<grid, kLaunchThreadsTma, L::total, s>>>(p, map_k, map_v);
+        attend_kernel<HD, KV8, kTmaShape><<<grid, kLaunchThreadsTma, tc_layout<HD, KV8, kTmaShape>::total, s>>>(p, map_k, map_v);
     } else {
         if (!configure<HD, KV8, false>()) return FNB_LAUNCH_FAILED;
-        attend_kernel<HD, KV8, false><<<grid, kLaunchThreads, L::total, s>>>(p, map_k, map_v);
+        attend_kernel<HD, KV8, false><<<grid, kLaunchThreads, tc_layout<HD, KV8, false>::total, s>>>(p, map_k, map_v);
     }
     if (cudaPeekAtLastError() != cudaSuccess) return FNB_LAUNCH_FAILED;
     attend_fold_kernel<HD><<<p.rows * p.n_q, HD * kFoldLanes, 0, s>>>(p);
@@ -1018,7 +1063,8 @@ bool shape_ok(const fnb_attend_args * a) {
 bool attend_prepare_device() {
     (void) encode_tiled();
     return configure<256, false, false>() && configure<256, false, true>() && configure<256, true, false>() &&
-           configure<128, false, false>() && configure<128, true, false>();
+           configure<256, true, true>() && configure<128, false, false>() && configure<128, true, false>() &&
+           configure<128, true, true>();
 }
 
 // shared by the two entry points: everything but where the workspace lives
